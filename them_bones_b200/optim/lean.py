@@ -1,0 +1,321 @@
+"""``LeanDistMuonAdamW``: the production optimizer.
+
+What it keeps from the reference's lean class (round2/source/train.py:12253-13411): low-precision replicas with fp32
+masters that exist only on the owning rank; gradients accumulated in fp32 *directly in the communication buffers*
+(``accumulate()`` after every backward, :12530; every Muon parameter's gradient target is a view of its shape group's
+slab, and every parameter itself is a view of the matching weight slab, so publishing updated weights is one gather
+into the buffer the model already reads, :13225-13247); one reduce-scatter per slab; row-sharded AdamW tables
+(:13136-13148, :13211-13219); all small scalars in one stacked vector reduced by a single all-reduce (:13183-13186);
+expert groups stepped locally with gradients scaled by ``1/world`` (:13272-13286); an optional device-side finiteness
+gate that zeroes a non-finite step's gradients (:13188-13204); a live cross-check of the fused collectives against the
+library ones on the same inputs (``_ovl_check``, :13092-13116).
+
+What is B200-specific: the slabs are allocated from a ``Comm`` object.  ``TorchComm`` uses NCCL/gloo collectives (the
+baseline); ``parallel.symm.PeerComm`` places the slabs in NVLink peer-mapped memory and runs the fused kernels: the
+reduce-scatter reads every peer's slab chunk by peer loads and feeds the sum straight into the Muon momentum / AdamW
+update (no NCCL call, no intermediate buffer), and the updated low-precision shard is stored into every peer's weight
+slab by peer stores.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..ref import functional as RF
+
+
+class TorchComm:
+    """Collectives through ``torch.distributed`` (NCCL on GPUs, gloo on CPU)."""
+
+    fused = False
+
+    def __init__(self, group=None):
+        self.group = group
+        on = dist.is_available() and dist.is_initialized()
+        self.world = dist.get_world_size(group) if on else 1
+        self.rank = dist.get_rank(group) if on else 0
+
+    def alloc(self, shape, dtype, device):
+        return torch.zeros(shape, dtype=dtype, device=device)
+
+    def reduce_scatter_mean(self, full: torch.Tensor, chunk_numel: int) -> torch.Tensor:
+        """``full`` is ``[W * chunk]`` flat fp32; returns this rank's averaged chunk (fp32)."""
+        if self.world == 1:
+            return full.view(-1)[:chunk_numel]
+        out = torch.empty(chunk_numel, dtype=full.dtype, device=full.device)
+        dist.reduce_scatter_tensor(out, full.view(-1), op=dist.ReduceOp.SUM, group=self.group)
+        return out.div_(self.world)
+
+    def all_gather(self, full: torch.Tensor, chunk: torch.Tensor):
+        """Publish ``chunk`` (this rank's slice) into every rank's ``full`` (flat ``[W * chunk]``)."""
+        if self.world == 1:
+            full.view(-1)[:chunk.numel()].copy_(chunk.view(-1))
+            return
+        dist.all_gather_into_tensor(full.view(-1), chunk.reshape(-1).contiguous(), group=self.group)
+
+    def all_reduce_mean(self, t: torch.Tensor):
+        if self.world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+            t.div_(self.world)
+        return t
+
+    def all_reduce_min(self, t: torch.Tensor):
+        if self.world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=self.group)
+        return t
+
+
+class _MuonUnit:
+    """One shape group: weight slab ``W [n_pad, r, c]`` (replica dtype), gradient slab ``G`` (fp32), owner state for
+    ``k = n_pad / world`` matrices."""
+
+    def __init__(self, group, params, comm, replica_dtype):
+        p0 = params[0]
+        self.group, self.params = group, params
+        self.n, (self.r, self.c) = len(params), p0.shape
+        self.k = -(-self.n // comm.world)
+        self.n_pad = self.k * comm.world
+        dev = p0.device
+        self.W = comm.alloc((self.n_pad, self.r, self.c), replica_dtype, dev)
+        self.G = comm.alloc((self.n_pad, self.r, self.c), torch.float32, dev)
+        own = slice(comm.rank * self.k, (comm.rank + 1) * self.k)
+        full32 = torch.zeros(self.n_pad, self.r, self.c, dtype=torch.float32, device=dev)
+        for i, p in enumerate(params):
+            full32[i].copy_(p.detach())
+        self.master = full32[own].clone()
+        self.W.copy_(full32)
+        del full32
+        for i, p in enumerate(params):
+            p.data = self.W[i]
+            p.main_grad = self.G[i]
+        self.momentum = torch.zeros(self.k, self.r, self.c, dtype=torch.float32, device=dev)
+        self.second = torch.zeros((self.k, self.r, 1) if self.r >= self.c else (self.k, 1, self.c),
+                                  dtype=torch.float32, device=dev)
+        self.own = own
+
+
+class _RowUnit:
+    """One row-sharded AdamW tensor (embedding / head): full replica, fp32 full gradient buffer, owner slice state."""
+
+    def __init__(self, group, p, comm, replica_dtype):
+        self.group, self.p = group, p
+        dev = p.device
+        self.rows = p.shape[0] // comm.world
+        self.W = comm.alloc(tuple(p.shape), replica_dtype, dev)
+        self.G = comm.alloc(tuple(p.shape), torch.float32, dev)
+        self.own = slice(comm.rank * self.rows, (comm.rank + 1) * self.rows)
+        self.master = p.detach()[self.own].float().clone()
+        self.W.copy_(p.detach())
+        p.data = self.W
+        p.main_grad = self.G
+        self.exp_avg = torch.zeros_like(self.master)
+        self.exp_avg_sq = torch.zeros_like(self.master)
+
+
+class LeanDistMuonAdamW(torch.optim.Optimizer):
+    def __init__(self, param_groups, group=None, comm=None, replica_dtype=None, ns_dtype=None, finite_gate=True,
+                 overlap_check=False):
+        super().__init__(param_groups, defaults={})
+        self.comm = comm or TorchComm(group)
+        self.world, self.rank = self.comm.world, self.comm.rank
+        self.finite_gate = finite_gate
+        self.overlap_check = overlap_check
+        self.ns_dtype = ns_dtype
+        self.replica_dtype = replica_dtype
+        self.steps = 0
+        self.bad_steps = 0
+        self.check_mismatches = 0
+        self._build()
+
+    # ------------------------------------------------------------------------------------------------------
+    def _build(self):
+        comm = self.comm
+        self.muon_units, self.row_units, self.local_groups = [], [], []
+        small = []                                        # (param, group)
+        for g in self.param_groups:
+            ps = [p for p in g["params"]]
+            if not ps:
+                continue
+            rd = self.replica_dtype or ps[0].dtype
+            if g.get("moe_local"):
+                self.local_groups.append(g)
+                for p in ps:
+                    p.main_grad = torch.zeros_like(p, dtype=torch.float32)
+            elif g["kind"] == "muon":
+                self.muon_units.append(_MuonUnit(g, ps, comm, rd))
+            else:
+                for p in ps:
+                    if p.numel() >= 1024 and p.dim() >= 2 and p.shape[0] % comm.world == 0:
+                        self.row_units.append(_RowUnit(g, p, comm, self.replica_dtype or p.dtype))
+                    else:
+                        small.append((p, g))
+        # small scalars: one fp32 stack with per-element hyper-parameters
+        n = sum(p.numel() for p, _ in small)
+        dev = small[0][0].device if small else torch.device("cpu")
+        self.S = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.SG = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.S_m, self.S_v = torch.zeros_like(self.S), torch.zeros_like(self.S)
+        self.small = []
+        o = 0
+        for p, g in small:
+            k = p.numel()
+            self.S[o:o + k].copy_(p.detach().reshape(-1))
+            p.data = self.S[o:o + k].view(p.shape)
+            p.main_grad = self.SG[o:o + k].view(p.shape)
+            self.small.append((slice(o, o + k), g))
+            o += k
+        self._local = MuonLocal(self.local_groups, self.ns_dtype)
+
+    def _ns(self, t):
+        if self.ns_dtype is not None:
+            return self.ns_dtype
+        return torch.bfloat16 if t.is_cuda else torch.float32
+
+    # ------------------------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def accumulate(self):
+        """Fold autograd's ``.grad`` into the fp32 communication buffers and drop it.  Kernels that write their weight
+        gradient straight into ``main_grad`` leave ``.grad`` unset and nothing is copied for them."""
+        for g in self.param_groups:
+            for p in g["params"]:
+                if p.grad is not None:
+                    p.main_grad.add_(p.grad)
+                    p.grad = None
+
+    def zero_grad(self, set_to_none: bool = True):
+        for u in self.muon_units:
+            u.G.zero_()
+        for u in self.row_units:
+            u.G.zero_()
+        self.SG.zero_()
+        for g in self.local_groups:
+            for p in g["params"]:
+                p.main_grad.zero_()
+        for g in self.param_groups:
+            for p in g["params"]:
+                p.grad = None
+
+    # ------------------------------------------------------------------------------------------------------
+    def _small_vectors(self):
+        lr, b1, b2, wd = (torch.empty_like(self.S) for _ in range(4))
+        for sl, g in self.small:
+            lr[sl], wd[sl] = g["lr"], g["weight_decay"]
+            b1[sl], b2[sl] = g["betas"]
+        return lr, b1, b2, wd
+
+    @torch.no_grad()
+    def step(self):
+        comm = self.comm
+        self.steps += 1
+        if getattr(comm, "fused", False):
+            return self._step_fused()
+        # 1-3: every reduction first (reference: opt_overlap_rs issues the collectives before any math)
+        row_g = [comm.reduce_scatter_mean(u.G, u.master.numel()).view_as(u.master) for u in self.row_units]
+        muon_g = [comm.reduce_scatter_mean(u.G, u.momentum.numel()).view_as(u.momentum) for u in self.muon_units]
+        comm.all_reduce_mean(self.SG)
+        # 4: finiteness gate
+        if self.finite_gate:
+            sq = self.SG.square().sum()
+            for t in row_g + muon_g:
+                sq = sq + t.square().sum()
+            ok = torch.isfinite(sq).to(torch.float32).reshape(1)
+            comm.all_reduce_min(ok)
+            okb = ok[0] > 0
+            row_g = [torch.where(okb, t, torch.zeros_like(t)) for t in row_g]
+            muon_g = [torch.where(okb, t, torch.zeros_like(t)) for t in muon_g]
+            self.SG.copy_(torch.where(okb, self.SG, torch.zeros_like(self.SG)))
+            self._last_ok = ok
+        # 5: updates on the owners' fp32 masters
+        self._small_step()
+        for u, g in zip(self.row_units, row_g):
+            b1, b2 = u.group["betas"]
+            RF.adamw_update(u.master, g, u.exp_avg, u.exp_avg_sq, step=self.steps, lr=u.group["lr"], beta1=b1,
+                            beta2=b2, eps=u.group["eps"], wd=u.group["weight_decay"])
+            comm.all_gather(u.W, u.master.to(u.W.dtype))
+        for u, g in zip(self.muon_units, muon_g):
+            grp = u.group
+            RF.muon_update(g, u.master, u.momentum, u.second, momentum=grp["momentum"], beta2=grp["beta2"],
+                           lr=grp["lr"], wd=grp["weight_decay"], ns_steps=grp["ns_steps"], ns_dtype=self._ns(u.W))
+            comm.all_gather(u.W, u.master.to(u.W.dtype))
+        # 5b: local experts
+        self._local.step(1.0 / self.world)
+
+    def _small_step(self):
+        if not self.small:
+            return
+        lr, b1, b2, wd = self._small_vectors()
+        g = self.SG
+        self.S.mul_(1 - lr * wd)
+        self.S_m.mul_(b1).add_((1 - b1) * g)
+        self.S_v.mul_(b2).add_((1 - b2) * g * g)
+        c1, c2 = 1 - b1 ** self.steps, 1 - b2 ** self.steps
+        self.S.sub_(lr * (self.S_m / c1) / ((self.S_v / c2).sqrt() + 1e-10))
+
+    def _step_fused(self):
+        """In-kernel collectives (``parallel.symm.PeerComm``): one launch per unit reduces the peers' gradient chunks
+        over NVLink and applies the owner update; one launch publishes the updated shard into every peer's slab."""
+        comm = self.comm
+        comm.pre_step()                                   # all ranks' gradients are complete and visible
+        comm.all_reduce_mean(self.SG)
+        self._small_step()
+        for u in self.row_units:
+            comm.fused_row_adamw(u, self.steps)
+        for u in self.muon_units:
+            comm.fused_muon(u, self.steps, self._ns(u.W))
+        self._local.step(1.0 / self.world)
+        comm.post_step()                                  # every peer's stores into my slabs have landed
+        if self.overlap_check and self.steps == 2:
+            self.check_mismatches += comm.cross_check(self)
+
+    # ------------------------------------------------------------------------------------------------------
+    def _gather_full(self, full, chunk):
+        if self.world == 1:
+            full.view(-1)[:chunk.numel()].copy_(chunk.reshape(-1))
+        else:
+            dist.all_gather_into_tensor(full.view(-1), chunk.reshape(-1).contiguous(),
+                                        group=getattr(self.comm, "group", None))
+
+    def consolidated_state_dict(self):
+        """Owner masters gathered into full fp32 tensors keyed by parameter (for checkpointing in fp32; reference:
+        ``consolidated_state_dict``, round2/source/train.py:13311)."""
+        out = {}
+        for u in self.muon_units:
+            full = torch.empty(u.n_pad, u.r, u.c, dtype=torch.float32, device=u.master.device)
+            self._gather_full(full, u.master)
+            for i, p in enumerate(u.params):
+                out[p] = full[i]
+        for u in self.row_units:
+            full = torch.empty(u.p.shape, dtype=torch.float32, device=u.master.device)
+            self._gather_full(full, u.master)
+            out[u.p] = full
+        return out
+
+    def describe(self) -> str:
+        mu = ", ".join(f"{u.n}x[{u.r},{u.c}] (k={u.k})" for u in self.muon_units)
+        rows = ", ".join(f"[{u.p.shape[0]},{u.p.shape[1]}]/{self.world}" for u in self.row_units)
+        return (f"lean optimizer: world {self.world}; muon slabs: {mu}; row tables: {rows}; scalars: {self.S.numel()}; "
+                f"local expert groups: {len(self.local_groups)}; comm: {type(self.comm).__name__}")
+
+
+class MuonLocal:
+    """Expert groups: the whole gradient forms on this rank; no collective (reference: ``_moe_local_step``)."""
+
+    def __init__(self, groups, ns_dtype=None):
+        self.groups, self.ns_dtype, self.state = groups, ns_dtype, {}
+
+    @torch.no_grad()
+    def step(self, grad_scale: float):
+        for g in self.groups:
+            for p in g["params"]:
+                st = self.state.setdefault(p, {})
+                r, c = p.shape[-2:]
+                if not st:
+                    st["master"] = p.detach().float().clone()
+                    st["momentum"] = torch.zeros_like(st["master"])
+                    st["second"] = torch.zeros((*p.shape[:-2], r, 1) if r >= c else (*p.shape[:-2], 1, c),
+                                               dtype=torch.float32, device=p.device)
+                grad = p.main_grad * grad_scale
+                nd = self.ns_dtype or (torch.bfloat16 if p.is_cuda else torch.float32)
+                RF.muon_update(grad, st["master"], st["momentum"], st["second"], momentum=g["momentum"],
+                               beta2=g["beta2"], lr=g["lr"], wd=g["weight_decay"], ns_steps=g["ns_steps"], ns_dtype=nd)
+                p.copy_(st["master"])

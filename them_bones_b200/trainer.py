@@ -1,0 +1,121 @@
+"""The training engine: model + optimizer + tables + data + one public ``train_step``.
+
+``Trainer.train_step(inputs, targets)`` is the call a user makes per optimizer step (``train.py`` and ``bench.py`` both
+go through it): it copies the step's pinned host windows to the device, runs ``grad_accum`` micro-steps of forward /
+backward / ``optimizer.accumulate()``, applies the schedules, runs the distributed optimizer step and the table update,
+and returns the step's mean loss as a device scalar (reference step loop: round2/source/train.py:22565-23078).
+"""
+from __future__ import annotations
+
+import time
+
+import torch
+import torch.distributed as dist
+
+from . import ops
+from .config import GPTConfig, Hyper, switches
+from .models.gpt import GPT
+from .models.tables import HashedTables
+from .optim import schedules
+from .optim.muon_adamw import setup_optimizer
+from .runtime import Runtime, compute_dtype_for, print0
+
+
+class Trainer:
+    def __init__(self, config: GPTConfig, hyper: Hyper, rt: Runtime, *, device_batch: int | None = None,
+                 total_batch: int | None = None, optimizer_kind: str | None = None, fused_comm: bool | None = None,
+                 horizon_steps: int = 0, budget_seconds: float = 0.0):
+        sw = switches()
+        self.config, self.hyper, self.rt = config, hyper, rt
+        self.dtype = compute_dtype_for(rt.device_type)
+        self.device_batch = device_batch or hyper.device_batch
+        self.total_batch = total_batch or hyper.total_batch
+        tokens_per_micro = self.device_batch * config.sequence_len * rt.world
+        if self.total_batch % tokens_per_micro:
+            raise ValueError(f"total batch {self.total_batch} is not a multiple of {tokens_per_micro} tokens per micro-step")
+        self.grad_accum = self.total_batch // tokens_per_micro
+        self.local_windows = self.device_batch * self.grad_accum
+        self.horizon_steps, self.budget_seconds = horizon_steps, budget_seconds
+        ep_group = dist.group.WORLD if (rt.ddp and config.moe_layers) else None
+        torch.manual_seed(hyper.seed)
+        model = GPT(config, ep_group=ep_group, ep_world=rt.world if config.moe_layers else 1,
+                    ep_rank=rt.rank if config.moe_layers else 0)
+        model.init_weights(hyper.seed)
+        model = model.to(rt.device)
+        model.cast_compute(self.dtype)
+        self.model = model
+        self.comm = None
+        use_fused = sw["FUSED_COMM"] if fused_comm is None else fused_comm
+        if use_fused and rt.device_type == "cuda" and not ops.reference_path():
+            from .parallel import symm
+            self.comm = symm.PeerComm.create(rt)
+        kind = optimizer_kind or sw["OPT"]
+        self.optimizer = setup_optimizer(model, hyper, kind=kind, comm=self.comm, finite_gate=sw["FINITE_GATE"],
+                                         overlap_check=sw["OPT_OVERLAP_CHECK"]) if kind == "lean" else \
+            setup_optimizer(model, hyper, kind=kind)
+        self.tables = None
+        if config.table_orders:
+            self.tables = HashedTables(config.table_orders, config.table_rows, config.n_embd, seed=config.table_seed,
+                                       device=rt.device, dtype=self.dtype, group=dist.group.WORLD if rt.ddp else None,
+                                       world=rt.world, rank=rt.rank, host_state=sw["TABLE_HOST_STATE"])
+            if self.comm is not None and rt.world > 1:
+                self.tables.exchange = self.comm.table_exchange(self.tables)
+            model.attach_tables(self.tables)
+        if self.comm is not None and config.moe_layers and rt.world > 1:
+            self.comm.install_moe(model)
+        self.step_index = 0
+        self.t_start = time.time()
+        self.sched = dict(lrm=1.0, momentum=hyper.muon_momentum, table_lr=hyper.table_lr)
+        self.last_moe_stats = None
+        self._dev_x = self._dev_y = None
+        self.flops_per_token = model.estimate_flops()
+
+    # ------------------------------------------------------------------------------------------------------
+    def progress(self) -> float:
+        if self.budget_seconds > 0:
+            return min(1.0, (time.time() - self.t_start) / self.budget_seconds)
+        if self.horizon_steps > 0:
+            return min(1.0, self.step_index / self.horizon_steps)
+        return 0.0
+
+    def h2d(self, inputs: torch.Tensor, targets: torch.Tensor):
+        """Host windows -> persistent device tensors (non-blocking from pinned memory)."""
+        if self._dev_x is None or self._dev_x.shape != inputs.shape:
+            self._dev_x = torch.empty(inputs.shape, dtype=inputs.dtype, device=self.rt.device)
+            self._dev_y = torch.empty(targets.shape, dtype=targets.dtype, device=self.rt.device)
+        self._dev_x.copy_(inputs, non_blocking=True)
+        self._dev_y.copy_(targets, non_blocking=True)
+        return self._dev_x, self._dev_y
+
+    def train_step(self, inputs: torch.Tensor, targets: torch.Tensor, micro_steps: int | None = None):
+        """One optimizer step on this rank's ``[local_windows, T]`` host (or device) windows."""
+        if inputs.device != self.rt.device:
+            x_all, y_all = self.h2d(inputs, targets)
+        else:
+            x_all, y_all = inputs, targets
+        accum = micro_steps or self.grad_accum
+        db = x_all.shape[0] // self.grad_accum
+        opt = self.optimizer
+        opt.zero_grad()
+        total = None
+        for m in range(accum):
+            x, y = x_all[m * db:(m + 1) * db], y_all[m * db:(m + 1) * db]
+            out = self.model(x, y, loss_div=float(accum))
+            if isinstance(out, tuple):
+                loss, self.last_moe_stats = out
+            else:
+                loss = out
+            loss.backward()
+            opt.accumulate()
+            total = loss.detach() if total is None else total + loss.detach()
+        self.sched = schedules.apply_schedules(opt, self.hyper, self.step_index, self.progress())
+        opt.step()
+        if self.tables is not None:
+            self.tables.step(self.sched["table_lr"])
+        self.step_index += 1
+        return total
+
+    def describe(self) -> str:
+        d = self.optimizer.describe() if hasattr(self.optimizer, "describe") else type(self.optimizer).__name__
+        return (f"trainer: world {self.rt.world}, dtype {self.dtype}, device_batch {self.device_batch}, grad_accum "
+                f"{self.grad_accum}, total_batch {self.total_batch}, flops/token {self.flops_per_token:.3e}; {d}")

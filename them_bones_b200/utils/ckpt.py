@@ -1,0 +1,122 @@
+"""Checkpoint save / load in the reference layout.
+
+``torch.save({"model_state": {name: cpu tensor}, "model_config": {non-default GPTConfig fields}, "meta": {...}})``
+(reference: ``save_checkpoint`` round2/source/train.py:20734-20746, ``save_rescue_checkpoint`` :20749, ``load_for_eval``
+:21031-21126).  Experts are gathered to rank 0 one tensor at a time (``moe_gather_experts`` :20027-20046) and stored as
+``transformer.h.{i}.mlp.w_fc [E,H,d]`` / ``w_proj [E,d,H]``; table shares are stored as extra state keys.  Files are
+written to ``<path>.tmp`` and renamed so a reader never sees a partial file.  Optimizer state is saved only on request
+(``BONES_SAVE_OPT_STATE=1``; the reference never saves it).
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+import torch.distributed as dist
+
+from ..config import GPTConfig, model_config_dict
+
+
+def _is_dist():
+    return dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1
+
+
+def gather_experts(model, group=None) -> dict:
+    """Full ``[E, ...]`` expert tensors on every rank (cold path: library all-gather)."""
+    from ..models.moe import MoeMLP
+    out = {}
+    for i, blk in enumerate(model.transformer.h):
+        if not isinstance(blk.mlp, MoeMLP):
+            continue
+        for name in ("w_fc", "w_proj"):
+            local = getattr(blk.mlp, name).detach()
+            if blk.mlp.ep_world > 1:
+                full = torch.empty(blk.mlp.n_exp, *local.shape[1:], dtype=local.dtype, device=local.device)
+                dist.all_gather_into_tensor(full, local.contiguous(), group=blk.mlp.ep_group)
+            else:
+                full = local
+            out[f"transformer.h.{i}.mlp.{name}"] = full.cpu()
+    return out
+
+
+def model_state(model, optimizer=None, group=None) -> dict:
+    """Name -> CPU tensor.  With a lean optimizer the fp32 masters are what is saved (reference:
+    ``consolidated_state_dict``)."""
+    masters = optimizer.consolidated_state_dict() if hasattr(optimizer, "consolidated_state_dict") else {}
+    state = {}
+    experts = gather_experts(model, group)
+    for name, p in model.named_parameters():
+        if name in experts:
+            state[name] = experts[name]
+        elif p in masters:
+            state[name] = masters[p].detach().cpu().clone()
+        else:
+            state[name] = p.detach().cpu().clone()
+    return state
+
+
+def save_checkpoint(path: str, model, meta: dict, optimizer=None, tables=None, rank: int = 0, state: dict | None = None):
+    """Collective when the model is sharded: every rank must call it; only rank 0 writes."""
+    state = state if state is not None else model_state(model, optimizer)
+    extra = {}
+    if tables is not None:
+        share = tables.state_for_checkpoint()
+        if _is_dist():
+            parts = [None] * dist.get_world_size()
+            dist.all_gather_object(parts, share)
+            for k in share:
+                full = torch.empty(tables.rows, *share[k].shape[1:], dtype=share[k].dtype)
+                for r, part in enumerate(parts):
+                    full[r::len(parts)] = part[k]
+                extra[k] = full
+        else:
+            extra = share
+    if rank != 0:
+        return
+    payload = {"model_state": {**state, **extra}, "model_config": model_config_dict(model.config), "meta": meta}
+    if optimizer is not None and meta.get("save_opt_state"):
+        payload["optimizer_state"] = optimizer.state_dict()
+    tmp = path + ".tmp"
+    os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
+    torch.save(payload, tmp)
+    os.replace(tmp, path)
+
+
+def load_for_eval(path: str, device="cpu", dtype=None):
+    """Rebuild the model from a checkpoint with no environment: ``GPTConfig(**model_config)``, strict load of the
+    dense state, experts and tables attached separately, eval mode.  Every rank is an independent full replica (all
+    experts local)."""
+    from ..models.gpt import GPT
+    from ..models.tables import HashedTables
+    ckpt = torch.load(path, map_location="cpu", weights_only=True, mmap=True)
+    config = GPTConfig(**ckpt["model_config"])
+    state = dict(ckpt["model_state"])
+    device = torch.device(device)
+    model = GPT(config)
+    table_state = {k: state.pop(k) for k in list(state) if k.startswith("table_") and not k.startswith("table_lambda")}
+    model.load_state_dict(state, strict=True)
+    dtype = dtype or (torch.bfloat16 if device.type == "cuda" else torch.float32)
+    model = model.to(device)
+    model.cast_compute(dtype)
+    if config.table_orders:
+        tables = HashedTables(config.table_orders, config.table_rows, config.n_embd, seed=config.table_seed,
+                              device=device, dtype=dtype)
+        tables.load_share(table_state)
+        model.attach_tables(tables)
+    model.eval()
+    return model, ckpt.get("meta", {})
+
+
+class RescueCopy:
+    """Host copy of the weights refreshed every ``every`` steps once ``progress >= start`` and written out when the loss
+    goes bad (reference: round2/source/train.py:22535-22558, 23060-23078)."""
+
+    def __init__(self, start: float, every: int):
+        self.start, self.every = start, every
+        self.state, self.step = None, -1
+
+    def maybe_refresh(self, step: int, progress: float, model, optimizer=None):
+        if progress >= self.start and (self.state is None or step - self.step >= self.every):
+            self.state, self.step = model_state(model, optimizer), step
+            return True
+        return False
