@@ -1,0 +1,426 @@
+// Bandwidth-bound fused blocks: parameter-free RMSNorm, residual mix + norm, embedding gather / scatter-add, softcap
+// cross-entropy with in-place logit gradients, row gathers for the MoE slot buffer.
+//
+// Row kernels use one warp per row with 16-byte vector accesses and keep the row in registers between the reduction and
+// the write, so every tensor is read once and written once.  Reductions for scalar-gain gradients are summed per block
+// and added with one atomic per block.
+//
+// Reference counterparts: block head `x' = l1*x + l2*x0; xn = rms(x')` (round1/source/train.py:5257-5301), rms pair
+// (:5378-5410), residual-mix backward with gain partial sums (round2/source/kernels/nki_resmix.py), embedding backward
+// (round2/source/train.py:5606-5658, there a one-hot contraction), chunked loss head (round2/source/train.py:5238-5297).
+#include "common.cuh"
+
+namespace bones {
+
+constexpr float kRmsEps = 1.1920928955078125e-07f;   // 2^-23
+constexpr int kMaxVec = 8;                           // up to 8 x (32 lanes x 8 bf16) = 2048 columns per row
+
+struct RowRegs {
+  float v[kMaxVec][8];
+};
+
+__device__ __forceinline__ void load_row(const __nv_bfloat16* row, int C, int lane, RowRegs& r) {
+#pragma unroll
+  for (int i = 0; i < kMaxVec; ++i) {
+    const int c = (i * 32 + lane) * 8;
+    if (c < C) {
+      const uint4 u = *reinterpret_cast<const uint4*>(row + c);
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float2 f = unpack_bf16(w[t]);
+        r.v[i][2 * t] = f.x;
+        r.v[i][2 * t + 1] = f.y;
+      }
+    } else {
+#pragma unroll
+      for (int t = 0; t < 8; ++t) r.v[i][t] = 0.f;
+    }
+  }
+}
+__device__ __forceinline__ void store_row(__nv_bfloat16* row, int C, int lane, const RowRegs& r) {
+#pragma unroll
+  for (int i = 0; i < kMaxVec; ++i) {
+    const int c = (i * 32 + lane) * 8;
+    if (c < C) {
+      uint4 u;
+      u.x = pack_bf16(r.v[i][0], r.v[i][1]);
+      u.y = pack_bf16(r.v[i][2], r.v[i][3]);
+      u.z = pack_bf16(r.v[i][4], r.v[i][5]);
+      u.w = pack_bf16(r.v[i][6], r.v[i][7]);
+      *reinterpret_cast<uint4*>(row + c) = u;
+    }
+  }
+}
+__device__ __forceinline__ float row_sumsq(const RowRegs& r) {
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < kMaxVec; ++i)
+#pragma unroll
+    for (int t = 0; t < 8; ++t) s += r.v[i][t] * r.v[i][t];
+  return warp_sum(s);
+}
+__device__ __forceinline__ float row_dot(const RowRegs& a, const RowRegs& b) {
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < kMaxVec; ++i)
+#pragma unroll
+    for (int t = 0; t < 8; ++t) s += a.v[i][t] * b.v[i][t];
+  return warp_sum(s);
+}
+
+// y = x * rsqrt(mean(x^2) + eps)
+__global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* x, __nv_bfloat16* y, int M, int C) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= M) return;
+  RowRegs r;
+  load_row(x + (size_t)row * C, C, lane, r);
+  const float rstd = rsqrtf(row_sumsq(r) / C + kRmsEps);
+#pragma unroll
+  for (int i = 0; i < kMaxVec; ++i)
+#pragma unroll
+    for (int t = 0; t < 8; ++t) r.v[i][t] *= rstd;
+  store_row(y + (size_t)row * C, C, lane, r);
+}
+
+// dx = (add ? add : 0) + rstd * (dy - xhat * mean(dy * xhat)),  xhat = x * rstd
+__global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* x, const __nv_bfloat16* dy, const __nv_bfloat16* add, __nv_bfloat16* dx, int M,
+                                   int C) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= M) return;
+  RowRegs rx, rg;
+  load_row(x + (size_t)row * C, C, lane, rx);
+  load_row(dy + (size_t)row * C, C, lane, rg);
+  const float rstd = rsqrtf(row_sumsq(rx) / C + kRmsEps);
+  const float m = row_dot(rx, rg) * rstd * rstd / C;     // mean(dy * xhat) * rstd
+  RowRegs ra;
+  if (add) load_row(add + (size_t)row * C, C, lane, ra);
+#pragma unroll
+  for (int i = 0; i < kMaxVec; ++i)
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+      float g = rstd * (rg.v[i][t] - rx.v[i][t] * m);
+      if (add) g += ra.v[i][t];
+      rg.v[i][t] = g;
+    }
+  store_row(dx + (size_t)row * C, C, lane, rg);
+}
+
+// xm = a*x + b*x0 ; xn = rmsnorm(xm)   (a, b: device scalars)
+__global__ void resid_mix_norm_fwd_kernel(const __nv_bfloat16* x, const __nv_bfloat16* x0, const float* a, const float* b,
+                                          __nv_bfloat16* xm, __nv_bfloat16* xn, int M, int C) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= M) return;
+  const float fa = *a, fb = *b;
+  RowRegs r, r0;
+  load_row(x + (size_t)row * C, C, lane, r);
+  load_row(x0 + (size_t)row * C, C, lane, r0);
+#pragma unroll
+  for (int i = 0; i < kMaxVec; ++i)
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+      // round the mixed stream to bf16 first: the norm sees exactly what is stored
+      r.v[i][t] = __bfloat162float(__float2bfloat16(fa * r.v[i][t] + fb * r0.v[i][t]));
+    }
+  store_row(xm + (size_t)row * C, C, lane, r);
+  const float rstd = rsqrtf(row_sumsq(r) / C + kRmsEps);
+#pragma unroll
+  for (int i = 0; i < kMaxVec; ++i)
+#pragma unroll
+    for (int t = 0; t < 8; ++t) r.v[i][t] *= rstd;
+  store_row(xn + (size_t)row * C, C, lane, r);
+}
+
+// g = dxm + rmsnorm_bwd(xm, dxn);  dx = a*g;  dx0 = b*g;  da += sum(g*x);  db += sum(g*x0)
+__global__ void resid_mix_norm_bwd_kernel(const __nv_bfloat16* x, const __nv_bfloat16* x0, const __nv_bfloat16* xm, const float* a,
+                                          const float* b, const __nv_bfloat16* dxm, const __nv_bfloat16* dxn, __nv_bfloat16* dx,
+                                          __nv_bfloat16* dx0, float* da, float* db, int M, int C) {
+  __shared__ float s_da[32], s_db[32];
+  const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + wid;
+  float pa = 0.f, pb = 0.f;
+  if (row < M) {
+    const float fa = *a, fb = *b;
+    RowRegs rm, rg, rt;
+    load_row(xm + (size_t)row * C, C, lane, rm);
+    load_row(dxn + (size_t)row * C, C, lane, rg);
+    const float rstd = rsqrtf(row_sumsq(rm) / C + kRmsEps);
+    const float m = row_dot(rm, rg) * rstd * rstd / C;
+    load_row(dxm + (size_t)row * C, C, lane, rt);
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i)
+#pragma unroll
+      for (int t = 0; t < 8; ++t) rg.v[i][t] = rt.v[i][t] + rstd * (rg.v[i][t] - rm.v[i][t] * m);
+    load_row(x + (size_t)row * C, C, lane, rt);
+    pa = row_dot(rg, rt);
+    load_row(x0 + (size_t)row * C, C, lane, rt);
+    pb = row_dot(rg, rt);
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i)
+#pragma unroll
+      for (int t = 0; t < 8; ++t) rt.v[i][t] = fb * rg.v[i][t];
+    store_row(dx0 + (size_t)row * C, C, lane, rt);
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i)
+#pragma unroll
+      for (int t = 0; t < 8; ++t) rg.v[i][t] *= fa;
+    store_row(dx + (size_t)row * C, C, lane, rg);
+  }
+  if (lane == 0) { s_da[wid] = pa; s_db[wid] = pb; }
+  __syncthreads();
+  if (wid == 0) {
+    const int nw = blockDim.x >> 5;
+    float va = lane < nw ? s_da[lane] : 0.f, vb = lane < nw ? s_db[lane] : 0.f;
+    va = warp_sum(va);
+    vb = warp_sum(vb);
+    if (lane == 0) { atomicAdd(da, va); atomicAdd(db, vb); }
+  }
+}
+
+// out[i] = table[idx[i]] (bf16 rows); idx == n_rows (the pad id) gives a zero row
+template <typename IdxT>
+__global__ void gather_rows_kernel(const __nv_bfloat16* table, const IdxT* idx, __nv_bfloat16* out, int n, int C, long long n_rows) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= n) return;
+  const long long src = (long long)idx[row];
+  const bool valid = src >= 0 && src < n_rows;
+  for (int c = lane * 8; c < C; c += 256) {
+    uint4 u = make_uint4(0, 0, 0, 0);
+    if (valid) u = *reinterpret_cast<const uint4*>(table + (size_t)src * C + c);
+    *reinterpret_cast<uint4*>(out + (size_t)row * C + c) = u;
+  }
+}
+
+// grad[idx[i]] += dy[i]  (fp32 accumulation buffer, one vector atomic per 4 columns)
+template <typename IdxT>
+__global__ void scatter_add_rows_kernel(const __nv_bfloat16* dy, const IdxT* idx, float* grad, int n, int C, long long n_rows) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= n) return;
+  const long long dst = (long long)idx[row];
+  if (dst < 0 || dst >= n_rows) return;
+  for (int c = lane * 8; c < C; c += 256) {
+    const uint4 u = *reinterpret_cast<const uint4*>(dy + (size_t)row * C + c);
+    const float2 f0 = unpack_bf16(u.x), f1 = unpack_bf16(u.y), f2 = unpack_bf16(u.z), f3 = unpack_bf16(u.w);
+    float4* g = reinterpret_cast<float4*>(grad + (size_t)dst * C + c);
+    atomicAdd(g, make_float4(f0.x, f0.y, f1.x, f1.y));
+    atomicAdd(g + 1, make_float4(f2.x, f2.y, f3.x, f3.y));
+  }
+}
+
+// out[n] = sum_k gates[n,k] * ys[slot[n,k]]   (slot == S: dropped)
+__global__ void moe_combine_kernel(const __nv_bfloat16* ys, const long long* slot, const float* gates, __nv_bfloat16* out, int n, int C,
+                                   int topk, long long S) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= n) return;
+  for (int c = lane * 8; c < C; c += 256) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int k = 0; k < topk; ++k) {
+      const long long s = slot[(size_t)row * topk + k];
+      if (s < 0 || s >= S) continue;
+      const float g = gates[(size_t)row * topk + k];
+      const uint4 u = *reinterpret_cast<const uint4*>(ys + (size_t)s * C + c);
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float2 f = unpack_bf16(w[t]);
+        acc[2 * t] += g * f.x;
+        acc[2 * t + 1] += g * f.y;
+      }
+    }
+    uint4 o;
+    o.x = pack_bf16(acc[0], acc[1]); o.y = pack_bf16(acc[2], acc[3]);
+    o.z = pack_bf16(acc[4], acc[5]); o.w = pack_bf16(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(out + (size_t)row * C + c) = o;
+  }
+}
+
+// Softcap cross-entropy over full rows of bf16 logits [M, ldl] (first V columns valid), one CTA per row.
+//   z = cap * tanh(l / cap);  lse = log sum exp z;  nll = lse - z[target]
+// Outputs: nll[row] (0 where target < 0).  With `dlogits` (may alias logits) the gradient of
+//   sum_rows w_row * nll_row,   w_row = row_w ? row_w[row] : 1/max(1, *n_valid) / loss_div
+// is written in place: d l = w * (softmax(z) - onehot) * (1 - tanh^2).  Bounded logits (|z| <= cap) make a max pass
+// unnecessary: exp(z - cap) never overflows.
+__global__ void softcap_ce_kernel(const __nv_bfloat16* logits, long long ldl, const long long* targets, int V, float cap, float* nll,
+                                  __nv_bfloat16* dlogits, const float* row_w, const float* n_valid, float inv_loss_div, int M) {
+  const int row = blockIdx.x;
+  if (row >= M) return;
+  const __nv_bfloat16* l = logits + (size_t)row * ldl;
+  const long long tgt = targets[row];
+  const float inv_cap = 1.0f / cap;
+  __shared__ float red[32];
+  __shared__ float s_total;
+  float s = 0.f;
+  for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) {
+    const uint4 u = *reinterpret_cast<const uint4*>(l + c);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const float2 f = unpack_bf16(w[t]);
+      s += __expf(cap * tanhf(f.x * inv_cap) - cap) + __expf(cap * tanhf(f.y * inv_cap) - cap);
+    }
+  }
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    v = warp_sum(v);
+    if (threadIdx.x == 0) s_total = v;
+  }
+  __syncthreads();
+  const float lse = logf(s_total) + cap;
+  const bool valid = tgt >= 0 && tgt < V;
+  if (threadIdx.x == 0) {
+    float out = 0.f;
+    if (valid) out = lse - cap * tanhf(__bfloat162float(l[tgt]) * inv_cap);
+    nll[row] = out;
+  }
+  if (!dlogits) return;
+  float w = 0.f;
+  if (valid) w = row_w ? row_w[row] : inv_loss_div / fmaxf(1.0f, *n_valid);
+  __nv_bfloat16* d = dlogits + (size_t)row * ldl;
+  for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) {
+    const uint4 u = *reinterpret_cast<const uint4*>(l + c);
+    const uint32_t wd[4] = {u.x, u.y, u.z, u.w};
+    float g[8];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const float2 f = unpack_bf16(wd[t]);
+      const float t0 = tanhf(f.x * inv_cap), t1 = tanhf(f.y * inv_cap);
+      float p0 = __expf(cap * t0 - lse), p1 = __expf(cap * t1 - lse);
+      if (c + 2 * t == tgt) p0 -= 1.0f;
+      if (c + 2 * t + 1 == tgt) p1 -= 1.0f;
+      g[2 * t] = w * p0 * (1.0f - t0 * t0);
+      g[2 * t + 1] = w * p1 * (1.0f - t1 * t1);
+    }
+    uint4 o;
+    o.x = pack_bf16(g[0], g[1]); o.y = pack_bf16(g[2], g[3]); o.z = pack_bf16(g[4], g[5]); o.w = pack_bf16(g[6], g[7]);
+    *reinterpret_cast<uint4*>(d + c) = o;
+  }
+  // padded vocabulary columns carry no gradient
+  for (int c = V + threadIdx.x; c < ldl; c += blockDim.x) d[c] = __float2bfloat16(0.f);
+}
+
+// y = cap * tanh(x / cap) in fp32 from bf16 logits, first V of ldl columns
+__global__ void softcap_logits_kernel(const __nv_bfloat16* logits, long long ldl, float* out, int V, float cap, long long total) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const long long r = i / V;
+  const int c = (int)(i - r * V);
+  out[i] = cap * tanhf(__bfloat162float(logits[r * ldl + c]) / cap);
+}
+
+// fused AdamW on fp32 master + moments with a low-precision replica write (decoupled decay, bias correction)
+__global__ void adamw_kernel(float* p, const float* g, float* m, float* v, __nv_bfloat16* replica, long long n, float lr, float b1,
+                             float b2, float eps, float wd, float c1, float c2, float gscale, const float* ok) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float gi = g[i] * gscale;
+  if (ok && *ok <= 0.f) gi = 0.f;
+  float pi = p[i] * (1.0f - lr * wd);
+  const float mi = m[i] + (1.0f - b1) * (gi - m[i]);
+  const float vi = v[i] + (1.0f - b2) * (gi * gi - v[i]);
+  pi -= lr * (mi / c1) / (sqrtf(vi / c2) + eps);
+  p[i] = pi; m[i] = mi; v[i] = vi;
+  if (replica) replica[i] = __float2bfloat16(pi);
+}
+
+// sparse Adam on touched table rows: table[rows[i]] (bf16) updated from g[i], m[i], v[i] (fp32, compacted)
+__global__ void sparse_adam_kernel(__nv_bfloat16* table, const long long* rows, const float* g, float* m, float* v, int n, int C, float lr,
+                                   float b1, float b2, float eps, float decay, float c1, float c2) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= n) return;
+  __nv_bfloat16* w = table + (size_t)rows[row] * C;
+  for (int c = lane; c < C; c += 32) {
+    const size_t i = (size_t)row * C + c;
+    const float gi = g[i];
+    const float mi = m[i] + (1.0f - b1) * (gi - m[i]);
+    const float vi = v[i] + (1.0f - b2) * (gi * gi - v[i]);
+    m[i] = mi; v[i] = vi;
+    const float wi = __bfloat162float(w[c]) * (1.0f - lr * decay) - lr * (mi / c1) / (sqrtf(vi / c2) + eps);
+    w[c] = __float2bfloat16(wi);
+  }
+}
+
+}  // namespace bones
+
+extern "C" {
+using namespace bones;
+#define ROWS_PER_BLOCK 8
+#define ROW_GRID(M) dim3(((M) + ROWS_PER_BLOCK - 1) / ROWS_PER_BLOCK), dim3(ROWS_PER_BLOCK * 32)
+
+int bones_rmsnorm_fwd(const void* x, void* y, int M, int C, void* stream) {
+  if (C % 8 || C > kMaxVec * 256) return -2;
+  rmsnorm_fwd_kernel<<<ROW_GRID(M), 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, M, C);
+  return (int)cudaGetLastError();
+}
+int bones_rmsnorm_bwd(const void* x, const void* dy, const void* add, void* dx, int M, int C, void* stream) {
+  if (C % 8 || C > kMaxVec * 256) return -2;
+  rmsnorm_bwd_kernel<<<ROW_GRID(M), 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)add,
+                                                             (__nv_bfloat16*)dx, M, C);
+  return (int)cudaGetLastError();
+}
+int bones_resid_mix_norm_fwd(const void* x, const void* x0, const float* a, const float* b, void* xm, void* xn, int M, int C, void* stream) {
+  if (C % 8 || C > kMaxVec * 256) return -2;
+  resid_mix_norm_fwd_kernel<<<ROW_GRID(M), 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)x0, a, b,
+                                                                    (__nv_bfloat16*)xm, (__nv_bfloat16*)xn, M, C);
+  return (int)cudaGetLastError();
+}
+int bones_resid_mix_norm_bwd(const void* x, const void* x0, const void* xm, const float* a, const float* b, const void* dxm, const void* dxn,
+                             void* dx, void* dx0, float* da, float* db, int M, int C, void* stream) {
+  if (C % 8 || C > kMaxVec * 256) return -2;
+  resid_mix_norm_bwd_kernel<<<ROW_GRID(M), 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)x0, (const __nv_bfloat16*)xm, a, b, (const __nv_bfloat16*)dxm, (const __nv_bfloat16*)dxn,
+      (__nv_bfloat16*)dx, (__nv_bfloat16*)dx0, da, db, M, C);
+  return (int)cudaGetLastError();
+}
+int bones_gather_rows(const void* table, const void* idx, int idx_is_64, void* out, int n, int C, long long n_rows, void* stream) {
+  if (C % 8) return -2;
+  if (idx_is_64)
+    gather_rows_kernel<long long><<<ROW_GRID(n), 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)table, (const long long*)idx,
+                                                                          (__nv_bfloat16*)out, n, C, n_rows);
+  else
+    gather_rows_kernel<int><<<ROW_GRID(n), 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)table, (const int*)idx, (__nv_bfloat16*)out, n, C,
+                                                                    n_rows);
+  return (int)cudaGetLastError();
+}
+int bones_scatter_add_rows(const void* dy, const void* idx, int idx_is_64, float* grad, int n, int C, long long n_rows, void* stream) {
+  if (C % 8) return -2;
+  if (idx_is_64)
+    scatter_add_rows_kernel<long long><<<ROW_GRID(n), 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)dy, (const long long*)idx, grad, n, C,
+                                                                               n_rows);
+  else
+    scatter_add_rows_kernel<int><<<ROW_GRID(n), 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)dy, (const int*)idx, grad, n, C, n_rows);
+  return (int)cudaGetLastError();
+}
+int bones_moe_combine(const void* ys, const long long* slot, const float* gates, void* out, int n, int C, int topk, long long S, void* stream) {
+  if (C % 8) return -2;
+  moe_combine_kernel<<<ROW_GRID(n), 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)ys, slot, gates, (__nv_bfloat16*)out, n, C, topk, S);
+  return (int)cudaGetLastError();
+}
+int bones_softcap_ce(const void* logits, long long ldl, const long long* targets, int V, float cap, float* nll, void* dlogits,
+                     const float* row_w, const float* n_valid, float inv_loss_div, int M, void* stream) {
+  if (V % 8 || ldl % 8) return -2;
+  softcap_ce_kernel<<<M, 512, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, ldl, targets, V, cap, nll, (__nv_bfloat16*)dlogits,
+                                                        row_w, n_valid, inv_loss_div, M);
+  return (int)cudaGetLastError();
+}
+int bones_softcap_logits(const void* logits, long long ldl, float* out, int V, float cap, long long rows, void* stream) {
+  const long long total = rows * V;
+  softcap_logits_kernel<<<(unsigned)((total + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, ldl, out, V, cap, total);
+  return (int)cudaGetLastError();
+}
+int bones_adamw(float* p, const float* g, float* m, float* v, void* replica, long long n, float lr, float b1, float b2, float eps, float wd,
+                int step, float gscale, const float* ok, void* stream) {
+  const float c1 = 1.0f - powf(b1, (float)step), c2 = 1.0f - powf(b2, (float)step);
+  adamw_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(p, g, m, v, (__nv_bfloat16*)replica, n, lr, b1, b2, eps, wd, c1, c2,
+                                                                            gscale, ok);
+  return (int)cudaGetLastError();
+}
+int bones_sparse_adam(void* table, const long long* rows, const float* g, float* m, float* v, int n, int C, float lr, float b1, float b2,
+                      float eps, float decay, int step, void* stream) {
+  const float c1 = 1.0f - powf(b1, (float)step), c2 = 1.0f - powf(b2, (float)step);
+  sparse_adam_kernel<<<ROW_GRID(n), 0, (cudaStream_t)stream>>>((__nv_bfloat16*)table, rows, g, m, v, n, C, lr, b1, b2, eps, decay, c1, c2);
+  return (int)cudaGetLastError();
+}
+}  // extern "C"

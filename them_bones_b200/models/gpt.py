@@ -243,11 +243,9 @@ class GPT(nn.Module):
         if targets is None:
             return ops.lmhead_logits(x, self.lm_head.weight, cfg.vocab_size, cfg.softcap)
         loss = ops.lmhead_loss(x, self.lm_head.weight, targets, cfg.vocab_size, cfg.softcap,
-                               reduction=loss_reduction, row_weights=row_weights)
-        if loss_reduction != "mean":
+                               reduction=loss_reduction, row_weights=row_weights, loss_div=loss_div)
+        if loss_reduction != "mean" or moe_aux is None:
             return loss
-        if moe_aux is None:
-            return loss / loss_div if loss_div != 1.0 else loss
         aux = torch.stack([a[0] for a in moe_aux]).sum()
         stats = torch.stack([a[1] for a in moe_aux])
-        return (loss + aux) / loss_div, stats.detach()
+        return loss + aux / loss_div, stats.detach()

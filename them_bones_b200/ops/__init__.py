@@ -143,11 +143,13 @@ def lmhead_logits(x, w, vocab, cap):
     return RF.softcap_logits(F.linear(x, w.to(x.dtype))[..., :vocab], cap)
 
 
-def lmhead_loss(x, w, targets, vocab, cap, reduction="mean", row_weights=None):
-    """Fused head: GEMM + softcap + log-sum-exp + target gather; logits never reach HBM on the native path."""
+def lmhead_loss(x, w, targets, vocab, cap, reduction="mean", row_weights=None, loss_div=1.0):
+    """Loss head: GEMM + softcap + log-sum-exp + target gather in row blocks; the full ``[M, V]`` logits never exist
+    on the native path.  ``"mean"`` is divided by ``loss_div`` (gradient accumulation folded into the graph)."""
     if native(x):
-        return _cuda().lmhead_loss(x, w, targets, vocab, cap, reduction, row_weights)
-    return RF.softcap_cross_entropy(x, w.to(x.dtype), targets, vocab, cap, row_weights, reduction)
+        return _cuda().lmhead_loss(x, w, targets, vocab, cap, reduction, row_weights, loss_div)
+    out = RF.softcap_cross_entropy(x, w.to(x.dtype), targets, vocab, cap, row_weights, reduction)
+    return out / loss_div if (reduction == "mean" and loss_div != 1.0) else out
 
 
 # -- MoE ---------------------------------------------------------------------------------------------------------

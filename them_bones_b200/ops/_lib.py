@@ -1,0 +1,76 @@
+"""ctypes binding of the native library ``them_bones_b200/lib/libbones_b200.so``.
+
+The library is plain C ABI: every entry point takes raw device pointers, sizes and the CUDA stream, launches
+asynchronously and returns 0 or an error code.  It is built in-tree by ``csrc/build.py`` (nvcc, sm_100a) and is
+required on a GPU: a missing or unloadable library raises here rather than letting a GPU run continue on a fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+_LIB = None
+_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib", "libbones_b200.so")
+
+
+def lib_path() -> str:
+    return _PATH
+
+
+def load():
+    global _LIB
+    if _LIB is None:
+        if not os.path.exists(_PATH):
+            raise RuntimeError(f"native library missing: {_PATH}; run `python -m them_bones_b200.csrc.build` "
+                               "(or __graft_entry__.build()) first")
+        _LIB = ctypes.CDLL(_PATH)
+    return _LIB
+
+
+def available() -> bool:
+    try:
+        load()
+        return True
+    except (RuntimeError, OSError):
+        return False
+
+
+def ptr(t):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+_I, _L, _F = ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+
+
+LAUNCHES = [0]        # native kernel launches issued by this process (each entry point launches one kernel)
+
+
+def call(name: str, *args):
+    LAUNCHES[0] += 1
+    rc = getattr(load(), name)(*args)
+    if rc != 0:
+        raise RuntimeError(f"{name} failed with code {rc}")
+
+
+def check_error_word():
+    """Raises if any kernel on the current device gave up on a bounded wait since the last check.  Synchronises."""
+    rc = load().bones_error_read_clear()
+    if rc != 0:
+        raise RuntimeError(f"a native kernel reported error code {rc} (bounded wait expired or bad argument)")
+
+
+EPI_BF16, EPI_BF16_RES, EPI_RELU2, EPI_ACC_F32, EPI_MUL_2SQRT, EPI_F32, EPI_F32_RES = range(7)
+
+
+def gemm(a, b, d, *, m, n, k, lda, ldb, ldd, a_major=0, b_major=0, epi=EPI_BF16, r=None, ldr=0, alpha=1.0, beta=1.0,
+         batch=1, stride_a=0, stride_b=0, stride_d=0, stride_r=0, force_bn=0):
+    """``d = epilogue(alpha * a @ b^T, r)``; see csrc/gemm_bf16.cu for operand layouts."""
+    call("bones_gemm_bf16", ptr(a), ptr(b), ptr(d), ptr(r), _I(m), _I(n), _I(k), _I(batch), _L(lda), _L(ldb), _L(ldd),
+         _L(ldr), _L(stride_a), _L(stride_b), _L(stride_d), _L(stride_r), _I(a_major), _I(b_major), _I(epi), _F(alpha),
+         _F(beta), _I(force_bn), stream())
