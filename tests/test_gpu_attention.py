@@ -1,0 +1,66 @@
+"""tcgen05 flash attention (RoPE + QK-norm + causal + document reset + band) against the fp32 PyTorch statement."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return float((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12))
+
+
+def _inputs(b, t, h, d, seed=0, docs=True):
+    from them_bones_b200.ref import functional as RF
+    torch.manual_seed(seed)
+    qkv = torch.randn(b, t, 3 * h * d, device="cuda", dtype=torch.bfloat16)
+    cos, sin = RF.rotary_tables(t, d, 10000.0, device="cuda")
+    cos, sin = cos.bfloat16().float(), sin.bfloat16().float()
+    ds = None
+    if docs:
+        idx = torch.randint(1, 100, (b, t), device="cuda")
+        idx[:, 0] = 0
+        idx[0, t // 3] = 0
+        idx[-1, t - 5] = 0
+        idx[-1, 130] = 0
+        ds = RF.doc_start_positions(idx, 0)
+    return qkv, cos, sin, ds
+
+
+@pytest.mark.parametrize("b,t,h,window,docs", [(1, 128, 1, 0, False), (2, 512, 2, 0, True), (1, 1024, 3, 256, True),
+                                               (2, 2048, 2, 0, True)])
+def test_attention_forward(b, t, h, window, docs):
+    from them_bones_b200.ops import _lib as L
+    from them_bones_b200.ops import attention_native as AN
+    from them_bones_b200.ref import functional as RF
+    d = 128
+    qkv, cos, sin, ds = _inputs(b, t, h, d, docs=docs)
+    scale = 1.0 / math.sqrt(d)
+    with torch.no_grad():
+        y = AN.attention(qkv, cos, sin, h, d, scale, ds, window)
+        ref = RF.attention(qkv.float(), cos, sin, h, d, scale, ds, window)
+    torch.cuda.synchronize()
+    L.check_error_word()
+    assert torch.isfinite(y).all()
+    assert _rel(y, ref) < 2e-2, _rel(y, ref)
+
+
+def test_attention_backward():
+    from them_bones_b200.ops import _lib as L
+    from them_bones_b200.ops import attention_native as AN
+    from them_bones_b200.ref import functional as RF
+    b, t, h, d = 2, 512, 2, 128
+    qkv, cos, sin, ds = _inputs(b, t, h, d, seed=3)
+    scale = 0.11
+    g = torch.randn(b, t, h * d, device="cuda", dtype=torch.bfloat16)
+    x = qkv.clone().requires_grad_(True)
+    y = AN.attention(x, cos, sin, h, d, scale, ds, 256)
+    y.backward(g)
+    xr = qkv.float().requires_grad_(True)
+    yr = RF.attention(xr, cos, sin, h, d, scale, ds, 256)
+    yr.backward(g.float())
+    torch.cuda.synchronize()
+    L.check_error_word()
+    assert _rel(y, yr) < 2e-2
+    assert _rel(x.grad, xr.grad) < 4e-2, _rel(x.grad, xr.grad)

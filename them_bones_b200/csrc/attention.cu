@@ -1,0 +1,400 @@
+// Causal flash attention for the decoder, forward pass, on tcgen05 tensor cores with TMEM accumulators and TMA loads,
+// plus the RoPE + QK-RMSNorm pre/post passes.
+//
+// Semantics (reference: fused RoPE + QK-norm + causal attention, round2/source/kernels/nki_attn_bandpro.py:686-978; eager
+// form round2/source/train.py:10209-10252): q and k are rotated (rotate-half RoPE), RMS-normalised per head, and
+// attention is causal softmax(scale * q k^T) v.  Added here: keys are limited to the query's document
+// (`doc_start[b, t]` = position of the most recent BOS) and, for banded layers, to the query's 128-token tile and the
+// `window_tiles - 1` tiles before it (the reference's tile band, round2/source/train.py:4740-4745).
+//
+// Because q and k are RMS-normalised, |q.k| <= head_dim, so the softmax uses the fixed shift `scale * head_dim` instead
+// of a running maximum (the reference kernels do the same): P = exp(scale*s - scale*D) never overflows and no rescale of
+// the output accumulator is ever needed.  The row sum is kept in registers and `lse = log(sum) + scale*D` is saved.
+//
+// One CTA per (128-query tile, head, batch).  Warp 0: TMA producer (Q once, K/V tiles through a 2-stage ring).  Warp 1:
+// tcgen05.mma issuer: S = Q K^T into one of two TMEM buffers, then O += P V with P read from shared memory.  Warps 2-5:
+// one query row per thread: tcgen05.ld the scores, mask, exponentiate, write P (bf16) into 128-byte-swizzled shared
+// memory for the second MMA; at the end divide O by the row sum and store.
+#include "common.cuh"
+
+namespace bones {
+
+constexpr float kQkEps = 1.1920928955078125e-07f;   // 2^-23
+
+// ---------------------------------------------------------------------------------------------------------------
+// RoPE + QK-norm pre-pass: qkv [M, 3A] -> qk [M, 2A]  (A = H * D; q-hat then k-hat).  One warp per (row, head, q|k).
+// ---------------------------------------------------------------------------------------------------------------
+template <int D>
+__global__ void rope_qknorm_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ cosT,
+                                       const float* __restrict__ sinT, __nv_bfloat16* __restrict__ qk, long long M, int T, int H) {
+  constexpr int HALF = D / 2, PER = HALF / 32;
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (w >= M * H * 2) return;
+  const int which = (int)(w % 2), h = (int)((w / 2) % H);
+  const long long row = w / (2 * H);
+  const int t = (int)(row % T);
+  const long long A = (long long)H * D;
+  const __nv_bfloat16* src = qkv + row * 3 * A + which * A + (long long)h * D;
+  __nv_bfloat16* dst = qk + row * 2 * A + which * A + (long long)h * D;
+  float y1[PER], y2[PER], ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < PER; ++e) {
+    const int i = lane * PER + e;
+    const float x1 = __bfloat162float(src[i]), x2 = __bfloat162float(src[HALF + i]);
+    const float c = cosT[(long long)t * HALF + i], s = sinT[(long long)t * HALF + i];
+    y1[e] = x1 * c + x2 * s;
+    y2[e] = -x1 * s + x2 * c;
+    ss += y1[e] * y1[e] + y2[e] * y2[e];
+  }
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / D + kQkEps);
+#pragma unroll
+  for (int e = 0; e < PER; ++e) {
+    const int i = lane * PER + e;
+    dst[i] = __float2bfloat16(y1[e] * r);
+    dst[HALF + i] = __float2bfloat16(y2[e] * r);
+  }
+}
+
+// Backward of the pre-pass: dq-hat/dk-hat (fp32 [M, 2A]) + dv (bf16 [M, A]) -> dqkv (bf16 [M, 3A]).
+// u = rope(x), r = rsqrt(mean(u^2)+eps), xhat = u r;  du = r (dxhat - xhat mean(dxhat xhat));  dx = rope^T(du).
+template <int D>
+__global__ void rope_qknorm_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ cosT,
+                                       const float* __restrict__ sinT, const float* __restrict__ dqk,
+                                       const __nv_bfloat16* __restrict__ dv, __nv_bfloat16* __restrict__ dqkv, long long M, int T,
+                                       int H) {
+  constexpr int HALF = D / 2, PER = HALF / 32;
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (w >= M * H * 3) return;
+  const int which = (int)(w % 3), h = (int)((w / 3) % H);
+  const long long row = w / (3 * H);
+  const long long A = (long long)H * D;
+  __nv_bfloat16* out = dqkv + row * 3 * A + which * A + (long long)h * D;
+  if (which == 2) {   // values pass straight through
+    const __nv_bfloat16* g = dv + row * A + (long long)h * D;
+    for (int i = lane; i < D; i += 32) out[i] = g[i];
+    return;
+  }
+  const int t = (int)(row % T);
+  const __nv_bfloat16* src = qkv + row * 3 * A + which * A + (long long)h * D;
+  const float* g = dqk + row * 2 * A + which * A + (long long)h * D;
+  float y1[PER], y2[PER], g1[PER], g2[PER], cs[PER], sn[PER], ss = 0.f, dot = 0.f;
+#pragma unroll
+  for (int e = 0; e < PER; ++e) {
+    const int i = lane * PER + e;
+    const float x1 = __bfloat162float(src[i]), x2 = __bfloat162float(src[HALF + i]);
+    cs[e] = cosT[(long long)t * HALF + i];
+    sn[e] = sinT[(long long)t * HALF + i];
+    y1[e] = x1 * cs[e] + x2 * sn[e];
+    y2[e] = -x1 * sn[e] + x2 * cs[e];
+    g1[e] = g[i];
+    g2[e] = g[HALF + i];
+    ss += y1[e] * y1[e] + y2[e] * y2[e];
+    dot += y1[e] * g1[e] + y2[e] * g2[e];
+  }
+  ss = warp_sum(ss);
+  dot = warp_sum(dot);
+  const float r = rsqrtf(ss / D + kQkEps);
+  const float m = dot * r * r / D;     // mean(dxhat * xhat) * r, with xhat = u r
+#pragma unroll
+  for (int e = 0; e < PER; ++e) {
+    const int i = lane * PER + e;
+    const float du1 = r * (g1[e] - y1[e] * m), du2 = r * (g2[e] - y2[e] * m);
+    out[i] = __float2bfloat16(du1 * cs[e] - du2 * sn[e]);
+    out[HALF + i] = __float2bfloat16(du1 * sn[e] + du2 * cs[e]);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// forward attention, head_dim 128
+// ---------------------------------------------------------------------------------------------------------------
+struct AttnParams {
+  int B, T, H;
+  float c1;          // scale * log2(e)
+  float c2;          // scale * D * log2(e)   (fixed softmax shift, in base-2 units)
+  float shift_ln;    // scale * D
+  int window_tiles;  // 0: full causal
+  const int* doc_start;
+  __nv_bfloat16* y;  // [B*T, H*128]
+  float* lse;        // [B, H, T]
+  int* err;
+};
+
+constexpr int AT = 128;                    // tile edge (queries and keys)
+constexpr int AD = 128;                    // head dim
+constexpr uint32_t TILE_BYTES = AT * AD * 2;   // 32 KB: two 128-byte-swizzled atoms of [128 rows][64 cols]
+constexpr uint32_t ATOM_BYTES = TILE_BYTES / 2;
+
+__device__ __forceinline__ int attn_first_tile(const AttnParams& p, int b, int qt) {
+  int lo = 0;
+  if (p.doc_start) lo = p.doc_start[(long long)b * p.T + qt * AT] / AT;
+  if (p.window_tiles > 0) lo = max(lo, qt - p.window_tiles + 1);
+  return lo;
+}
+
+__global__ void __launch_bounds__(192, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* gen = smem_raw + (base - raw);
+  const uint32_t sQ = base;
+  auto sK = [&](int s) { return base + TILE_BYTES * (1 + 2 * s); };
+  auto sV = [&](int s) { return base + TILE_BYTES * (2 + 2 * s); };
+  auto sP = [&](int s) { return base + TILE_BYTES * (5 + s); };
+  const uint32_t bars = base + TILE_BYTES * 7;
+  const uint32_t q_full = bars;
+  auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
+  auto s_full = [&](int s) { return bars + 8u * (3 + s); };
+  auto p_full = [&](int s) { return bars + 8u * (5 + s); };
+  auto pv_done = [&](int s) { return bars + 8u * (7 + s); };
+  const uint32_t o_full = bars + 8u * 9;
+  const uint32_t tmem_slot = bars + 8u * 10;
+  volatile uint32_t* tmem_slot_g = reinterpret_cast<volatile uint32_t*>(gen + TILE_BYTES * 7 + 80);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + TILE_BYTES * 7 + 88);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;   // heaviest (latest) query tiles first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int A = p.H * AD;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(kv_full(s), 1);
+      mbar_init(s_full(s), 1);
+      mbar_init(p_full(s), 4);
+      mbar_init(pv_done(s), 1);
+    }
+    mbar_init(o_full, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tm_qk);
+    tma_prefetch_desc(&tm_v);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot_g;
+  const uint32_t tS[2] = {tmem, tmem + 128};
+  const uint32_t tO = tmem + 256;
+
+  const int kt0 = attn_first_tile(p, b, qt);
+  const int n = qt - kt0 + 1;
+  const int row0 = b * p.T;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(q_full, TILE_BYTES);
+      tma_load_2d(sQ, &tm_qk, q_full, h * AD, row0 + qt * AT);
+      tma_load_2d(sQ + ATOM_BYTES, &tm_qk, q_full, h * AD + 64, row0 + qt * AT);
+      for (int j = 0; j < n; ++j) {
+        const int s = j & 1;
+        if (j >= 2 && !mbar_wait(pv_done(s), ((j - 2) >> 1) & 1, abort_flag, p.err, ERR_WAIT_EMPTY)) break;
+        mbar_arrive_expect_tx(kv_full(s), 2 * TILE_BYTES);
+        const int r = row0 + (kt0 + j) * AT;
+        tma_load_2d(sK(s), &tm_qk, kv_full(s), A + h * AD, r);
+        tma_load_2d(sK(s) + ATOM_BYTES, &tm_qk, kv_full(s), A + h * AD + 64, r);
+        tma_load_2d(sV(s), &tm_v, kv_full(s), 2 * A + h * AD, r);
+        tma_load_2d(sV(s) + ATOM_BYTES, &tm_v, kv_full(s), 2 * A + h * AD + 64, r);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = umma_idesc_f16(128, 128, 1, 0, 0);   // Q (K-major) x K (K-major)
+      const uint32_t idesc_o = umma_idesc_f16(128, 128, 1, 0, 1);   // P (K-major) x V (MN-major)
+      auto issue_pv = [&](int j) -> bool {
+        const int s = j & 1;
+        if (!mbar_wait(p_full(s), (j >> 1) & 1, abort_flag, p.err, ERR_WAIT_AUX)) return false;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint64_t ad = umma_smem_desc(sP(s) + (k >> 2) * ATOM_BYTES + (k & 3) * 32, 0, 1024, kLayoutSw128);
+          const uint64_t bd = umma_smem_desc(sV(s) + k * 2048, ATOM_BYTES, 1024, kLayoutSw128);
+          umma_f16(tO, ad, bd, idesc_o, (j | k) ? 1u : 0u);
+        }
+        tc_commit(pv_done(s));
+        return true;
+      };
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.err, ERR_WAIT_FULL);
+      for (int j = 0; j < n && ok; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait(kv_full(s), (j >> 1) & 1, abort_flag, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = (k >> 2) * ATOM_BYTES + (k & 3) * 32;
+          umma_f16(tS[s], umma_smem_desc(sQ + off, 0, 1024, kLayoutSw128), umma_smem_desc(sK(s) + off, 0, 1024, kLayoutSw128),
+                   idesc_s, k ? 1u : 0u);
+        }
+        tc_commit(s_full(s));
+        if (j >= 1) ok = issue_pv(j - 1);
+      }
+      if (ok) ok = issue_pv(n - 1);
+      if (ok) tc_commit(o_full);
+    }
+  } else {
+    const int q = warp & 3;
+    const int r = q * 32 + lane;            // row within the tile == TMEM lane
+    const int qpos = qt * AT + r;
+    int lo = 0;
+    if (p.doc_start) lo = p.doc_start[(long long)b * p.T + qpos];
+    float l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n; ++j) {
+      const int s = j & 1;
+      bool got = mbar_wait(s_full(s), (j >> 1) & 1, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
+      if (got && j >= 2) got = mbar_wait(pv_done(s), ((j - 2) >> 1) & 1, abort_flag, p.err, ERR_WAIT_EMPTY);
+      if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+      tc_fence_after();
+      const int k0 = (kt0 + j) * AT;
+      const bool need_mask = (k0 + AT - 1 > qt * AT) || (k0 < lo);   // diagonal tile or document boundary inside
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        __syncwarp();
+        BONES_TMEM_LD32(tS[s] + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
+        tmem_ld_wait();
+        float pr[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float e = exp2f(__uint_as_float(v[i]) * p.c1 - p.c2);
+          if (need_mask) {
+            const int kpos = k0 + c * 32 + i;
+            if (kpos > qpos || kpos < lo) e = 0.f;
+          }
+          // the row sum must match what the second GEMM sees: sum the bf16-rounded probabilities
+          const float eb = __bfloat162float(__float2bfloat16(e));
+          pr[i] = eb;
+          l += eb;
+        }
+        const uint32_t prow = sP(s) + (uint32_t)(c >> 1) * ATOM_BYTES + (uint32_t)r * 128u;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const uint32_t chunk = (uint32_t)((c & 1) * 4 + g) ^ (uint32_t)(r & 7);
+          const uint32_t w0 = pack_bf16(pr[g * 8 + 0], pr[g * 8 + 1]), w1 = pack_bf16(pr[g * 8 + 2], pr[g * 8 + 3]);
+          const uint32_t w2 = pack_bf16(pr[g * 8 + 4], pr[g * 8 + 5]), w3 = pack_bf16(pr[g * 8 + 6], pr[g * 8 + 7]);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + chunk * 16u), "r"(w0), "r"(w1), "r"(w2), "r"(w3)
+                       : "memory");
+        }
+      }
+      fence_proxy_async_smem();    // generic-proxy stores to shared memory -> visible to the tensor core (async proxy)
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full(s));
+    }
+    if (ok) {
+      const bool got = mbar_wait(o_full, 0, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
+      if (__all_sync(0xffffffffu, got)) {
+        tc_fence_after();
+        const float inv = 1.0f / l;
+        __nv_bfloat16* yrow = p.y + ((long long)(row0 + qpos)) * A + (long long)h * AD;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          __syncwarp();
+          BONES_TMEM_LD32(tO + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 u;
+            u.x = pack_bf16(__uint_as_float(v[g * 8 + 0]) * inv, __uint_as_float(v[g * 8 + 1]) * inv);
+            u.y = pack_bf16(__uint_as_float(v[g * 8 + 2]) * inv, __uint_as_float(v[g * 8 + 3]) * inv);
+            u.z = pack_bf16(__uint_as_float(v[g * 8 + 4]) * inv, __uint_as_float(v[g * 8 + 5]) * inv);
+            u.w = pack_bf16(__uint_as_float(v[g * 8 + 6]) * inv, __uint_as_float(v[g * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(yrow + c * 32 + g * 8) = u;
+          }
+        }
+        p.lse[((long long)b * p.H + h) * p.T + qpos] = logf(l) + p.shift_ln;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+static int tmap_rows_2d(CUtensorMap* out, const void* ptr, long long rows, long long cols) {
+  uint64_t dims[2] = {(uint64_t)cols, (uint64_t)rows};
+  uint64_t strides[1] = {(uint64_t)cols * 2};
+  uint32_t box[2] = {64, 128};
+  return make_tmap(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ptr, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+}  // namespace bones
+
+extern "C" {
+using namespace bones;
+
+int bones_rope_qknorm_fwd(const void* qkv, const float* cosT, const float* sinT, void* qk, long long M, int T, int H, int D, void* stream) {
+  const long long warps = M * H * 2;
+  const unsigned grid = (unsigned)((warps + 7) / 8);
+  if (D == 128)
+    rope_qknorm_fwd_kernel<128><<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)qkv, cosT, sinT, (__nv_bfloat16*)qk, M, T, H);
+  else if (D == 64)
+    rope_qknorm_fwd_kernel<64><<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)qkv, cosT, sinT, (__nv_bfloat16*)qk, M, T, H);
+  else
+    return -2;
+  return (int)cudaGetLastError();
+}
+
+int bones_rope_qknorm_bwd(const void* qkv, const float* cosT, const float* sinT, const float* dqk, const void* dv, void* dqkv, long long M,
+                          int T, int H, int D, void* stream) {
+  const long long warps = M * H * 3;
+  const unsigned grid = (unsigned)((warps + 7) / 8);
+  if (D == 128)
+    rope_qknorm_bwd_kernel<128><<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)qkv, cosT, sinT, dqk, (const __nv_bfloat16*)dv,
+                                                                     (__nv_bfloat16*)dqkv, M, T, H);
+  else if (D == 64)
+    rope_qknorm_bwd_kernel<64><<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)qkv, cosT, sinT, dqk, (const __nv_bfloat16*)dv,
+                                                                    (__nv_bfloat16*)dqkv, M, T, H);
+  else
+    return -2;
+  return (int)cudaGetLastError();
+}
+
+// qk: [B*T, 2*H*128] (rotated, normalised q and k); qkv: [B*T, 3*H*128] (values read in place); y: [B*T, H*128]; lse: [B,H,T]
+int bones_attn_fwd(const void* qk, const void* qkv, void* y, float* lse, const int* doc_start, int B, int T, int H, float scale,
+                   int window_tiles, void* stream) {
+  if (T % AT) return -2;
+  CUtensorMap tq, tv;
+  const long long M = (long long)B * T, A = (long long)H * AD;
+  int rc = tmap_rows_2d(&tq, qk, M, 2 * A);
+  if (rc) return rc;
+  rc = tmap_rows_2d(&tv, qkv, M, 3 * A);
+  if (rc) return rc;
+  AttnParams p;
+  p.B = B; p.T = T; p.H = H;
+  p.c1 = scale * 1.4426950408889634f;
+  p.c2 = scale * AD * 1.4426950408889634f;
+  p.shift_ln = scale * AD;
+  p.window_tiles = window_tiles;
+  p.doc_start = doc_start;
+  p.y = (__nv_bfloat16*)y;
+  p.lse = lse;
+  p.err = error_word();
+  constexpr size_t smem = (size_t)TILE_BYTES * 7 + 128 + 1024;
+  static bool attr_done = false;
+  if (!attr_done) {
+    BONES_CHECK(cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr_done = true;
+  }
+  dim3 grid(T / AT, H, B);
+  attn_fwd_kernel<<<grid, 192, smem, (cudaStream_t)stream>>>(tq, tv, p);
+  return (int)cudaGetLastError();
+}
+}  // extern "C"

@@ -1,0 +1,73 @@
+"""Autograd wrapper of the sm_100a attention kernels (``csrc/attention.cu``, ``csrc/attention_bwd.cu``).
+
+Forward: RoPE + QK-norm pre-pass into a ``[B*T, 2*H*D]`` buffer, then the tcgen05 flash-attention kernel reading the
+values in place from the packed ``qkv``.  Saved for backward: ``qkv``, the rotated/normalised ``qk``, the output and
+``lse``.  Backward: ``delta = rowsum(dO * O)``, the tcgen05 backward kernel (dQ-hat accumulated in fp32 by vector
+atomics, dK-hat / dV per key tile), then the pre-pass backward that applies the norm Jacobian and the inverse rotation
+and writes one packed ``[B, T, 3*H*D]`` gradient (reference: the fused backward emits one packed gradient,
+round2/source/kernels/nki_attn_bandpro.py:1-134).
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib as L
+
+_I, _L, _F = ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+HAVE_BWD = False
+
+
+def applies(qkv, n_head, head_dim) -> bool:
+    return qkv.dtype == torch.bfloat16 and head_dim == 128 and qkv.shape[1] % 128 == 0
+
+
+def rope_qknorm(qkv2, cos, sin, t, n_head, head_dim):
+    m = qkv2.shape[0]
+    qk = torch.empty(m, 2 * n_head * head_dim, dtype=qkv2.dtype, device=qkv2.device)
+    L.call("bones_rope_qknorm_fwd", L.ptr(qkv2), L.ptr(cos), L.ptr(sin), L.ptr(qk), _L(m), _I(t), _I(n_head), _I(head_dim),
+           L.stream())
+    return qk
+
+
+def attn_forward(qk, qkv2, doc_start, b, t, n_head, scale, window):
+    y = torch.empty(b * t, n_head * 128, dtype=qkv2.dtype, device=qkv2.device)
+    lse = torch.empty(b, n_head, t, dtype=torch.float32, device=qkv2.device)
+    L.call("bones_attn_fwd", L.ptr(qk), L.ptr(qkv2), L.ptr(y), L.ptr(lse), L.ptr(doc_start), _I(b), _I(t), _I(n_head), _F(scale),
+           _I(window // 128), L.stream())
+    return y, lse
+
+
+class _AttnFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, n_head, head_dim, scale, doc_start, window):
+        b, t, _ = qkv.shape
+        qkv2 = (qkv if qkv.is_contiguous() else qkv.contiguous()).view(b * t, -1)
+        cos, sin = cos.float().contiguous(), sin.float().contiguous()
+        ds = doc_start.to(torch.int32).contiguous() if doc_start is not None else None
+        qk = rope_qknorm(qkv2, cos, sin, t, n_head, head_dim)
+        y, lse = attn_forward(qk, qkv2, ds, b, t, n_head, scale, window)
+        ctx.save_for_backward(qkv2, qk, y, lse, cos, sin, ds)
+        ctx.meta = (b, t, n_head, head_dim, scale, window)
+        return y.view(b, t, n_head * head_dim)
+
+    @staticmethod
+    def backward(ctx, dy):
+        qkv2, qk, y, lse, cos, sin, ds = ctx.saved_tensors
+        b, t, n_head, head_dim, scale, window = ctx.meta
+        if HAVE_BWD:
+            from . import attention_bwd as AB
+            dqkv = AB.backward(dy, qkv2, qk, y, lse, cos, sin, ds, b, t, n_head, head_dim, scale, window)
+            return dqkv.view(b, t, -1), None, None, None, None, None, None, None
+        # interim route: differentiate the library path on the saved inputs
+        from . import _sdpa_attention
+        with torch.enable_grad():
+            x = qkv2.view(b, t, -1).detach().requires_grad_(True)
+            out = _sdpa_attention(x, cos, sin, n_head, head_dim, scale, ds, window)
+            (dqkv,) = torch.autograd.grad(out, x, dy)
+        return dqkv, None, None, None, None, None, None, None
+
+
+def attention(qkv, cos, sin, n_head, head_dim, scale, doc_start, window):
+    return _AttnFn.apply(qkv, cos, sin, n_head, head_dim, scale, doc_start, window)

@@ -257,7 +257,7 @@ def embedding(idx, weight, dtype):
 
 # -- attention -------------------------------------------------------------------------------------------------------
 def attention(qkv, cos, sin, n_head, head_dim, scale, doc_start, window):
-    from . import attention as A
+    from . import attn_dispatch as A
     return A.attention(qkv, cos, sin, n_head, head_dim, scale, doc_start, window)
 
 

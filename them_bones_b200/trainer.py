@@ -46,7 +46,7 @@ class Trainer:
         self.model = model
         self.comm = None
         use_fused = sw["FUSED_COMM"] if fused_comm is None else fused_comm
-        if use_fused and rt.device_type == "cuda" and not ops.reference_path():
+        if use_fused and rt.device_type == "cuda" and rt.world > 1 and not ops.reference_path():
             from .parallel import symm
             self.comm = symm.PeerComm.create(rt)
         kind = optimizer_kind or sw["OPT"]
