@@ -1,0 +1,208 @@
+"""CPU tests: configuration, synthetic data, schedules, optimizer math, MXFP8 emulation, control utilities."""
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from them_bones_b200 import config as C
+from them_bones_b200.data import synth
+from them_bones_b200.optim import schedules as S
+from them_bones_b200.ref import functional as RF
+
+
+def test_env_parsing_and_refusals(monkeypatch):
+    monkeypatch.setenv("BONES_UNET", "1")
+    monkeypatch.setenv("BONES_MLP", "mxfp8")
+    s = C.switches(refresh=True)
+    assert s["UNET"] is True and s["MLP"] == "mxfp8"
+    monkeypatch.setenv("BONES_UNET", "yes")
+    with pytest.raises(ValueError):
+        C.switches(refresh=True)
+    monkeypatch.setenv("BONES_UNET", "0")
+    monkeypatch.setenv("BONES_SHED", "1")
+    monkeypatch.setenv("BONES_MOE", "1")
+    with pytest.raises(ValueError):
+        C.switches(refresh=True)
+    monkeypatch.delenv("BONES_SHED")
+    monkeypatch.delenv("BONES_MOE")
+    monkeypatch.delenv("BONES_MLP")
+    C.switches(refresh=True)
+
+
+def test_recipe_file_and_config_roundtrip(tmp_path, monkeypatch):
+    p = tmp_path / "r.env"
+    p.write_text("# comment\nexport BONES_DOC_MASK=1\nBONES_ATTN_WINDOW=256  # trailing\n")
+    monkeypatch.delenv("BONES_DOC_MASK", raising=False)
+    monkeypatch.delenv("BONES_ATTN_WINDOW", raising=False)
+    got = C.load_recipe(str(p))
+    assert got == {"BONES_DOC_MASK": "1", "BONES_ATTN_WINDOW": "256"}
+    C.switches(refresh=True)
+    cfg = C.build_config(8, 256, 2, 512, 8192, head_dim=128)
+    assert cfg.doc_mask and cfg.attn_window == 256 and cfg.attn_long == (3, 7)
+    d = C.model_config_dict(cfg)
+    assert "unet" not in d and d["attn_window"] == 256
+    assert C.GPTConfig(**d) == cfg
+    for k in got:
+        monkeypatch.delenv(k)
+    C.switches(refresh=True)
+
+
+def test_moe_capacity_and_layer_parsing():
+    assert C.moe_capacity_for(1.25, 2048, 1, 64) == 40
+    assert C.moe_capacity_for(1.25, 2048, 2, 16) == 320
+    assert C.parse_layers("2:", 6) == (2, 3, 4, 5)
+    assert C.parse_layers("1,3", 6) == (1, 3)
+    with pytest.raises(ValueError):
+        C.parse_layers("9", 6)
+
+
+def test_zipf_stream_is_deterministic_and_skewed():
+    a = synth.ZipfDocs(8192, 1.1, (16, 64), seed=3).tokens(20000)
+    b = synth.ZipfDocs(8192, 1.1, (16, 64), seed=3).tokens(20000)
+    assert (a == b).all() and a.min() >= 1 and a.max() < 8192
+    counts = np.bincount(a, minlength=8192)
+    assert counts[1] > counts[10] > counts[1000]
+    ratio = counts[1] / max(1, counts[2])
+    assert 1.5 < ratio < 3.0                      # 2**1.1 = 2.14
+
+
+def test_packed_rows_windows_and_bos_mask():
+    ld = synth.SynthLoader(8192, 256, 8, seed=1, doc_len=(64, 512))
+    x, y = ld.next_step()
+    assert x.shape == (8, 256) and y.shape == (8, 256) and x.dtype == torch.int32 and y.dtype == torch.int64
+    flat_x, flat_y = x.reshape(-1), y.reshape(-1)
+    assert flat_x[0] == 0                                                  # a row starts with a document
+    nxt = flat_x[1:].long()
+    assert ((flat_y[:-1] == nxt) | ((nxt == 0) & (flat_y[:-1] == -1))).all()  # shifted by one, BOS targets masked
+    assert (flat_y != 0).all()
+    ld.set_seq_len(128)
+    x2, _ = ld.next_step()
+    assert x2.shape == (16, 128)
+
+
+def test_prefetcher_surfaces_worker_exception():
+    def boom():
+        raise RuntimeError("worker died")
+    p = synth.Prefetcher(boom)
+    p.start()
+    with pytest.raises(RuntimeError, match="worker died"):
+        p.finish()
+
+
+def test_schedules():
+    assert S.lr_multiplier(0.0, 0, 40, 0.85, 0.01) == pytest.approx(1 / 40)
+    assert S.lr_multiplier(0.1, 100, 40, 0.85, 0.01) == 1.0
+    assert S.lr_multiplier(1.0, 1000, 40, 0.85, 0.01) == pytest.approx(0.01)
+    mid = S.lr_multiplier(0.575, 1000, 40, 0.85, 0.01)
+    assert 0.01 < mid < 1.0
+    assert S.muon_momentum(0, 0.0, 0.65) == pytest.approx(0.85)
+    assert S.muon_momentum(300, 0.1, 0.65) == pytest.approx(0.97)
+    assert S.muon_momentum(5000, 1.0, 0.65) == pytest.approx(0.90)
+    assert S.grad_accum_for_step(0.1, 8, 0.3) == 4 and S.grad_accum_for_step(0.5, 8, 0.3) == 8
+
+
+def test_newton_schulz_orthogonalises():
+    torch.manual_seed(0)
+    for shape in ((2, 64, 32), (2, 32, 64)):
+        x = torch.randn(*shape)
+        x = x / (x.norm(dim=(-2, -1), keepdim=True) * 1.01 + 1e-6)
+        y = RF.newton_schulz(x, 5)
+        s = torch.linalg.svdvals(y)
+        assert s.max() < 1.3 and s.min() > 0.5
+
+
+def test_muon_update_matches_manual_reference():
+    torch.manual_seed(1)
+    n, r, c = 3, 48, 32
+    g = torch.randn(n, r, c)
+    w0 = torch.randn(n, r, c)
+    w, mom, sec = w0.clone(), torch.zeros(n, r, c), torch.zeros(n, r, 1)
+    RF.muon_update(g.clone(), w, mom, sec, momentum=0.95, beta2=0.9, lr=0.02, wd=0.05)
+    # manual restatement of the same formulae
+    m = 0.05 * g
+    gg = g + 0.95 * (m - g)
+    x = gg / (gg.norm(dim=(-2, -1), keepdim=True) * 1.01 + 1e-6)
+    x = RF.newton_schulz(x, 5)
+    v_mean = x.square().mean(-1, keepdim=True)
+    v_norm = (v_mean.sum((-2, -1), keepdim=True) * c).sqrt()
+    second = 0.1 * v_mean
+    step = second.clamp_min(1e-10).rsqrt()
+    v_new = ((v_mean * c) * step.square()).sum((-2, -1), keepdim=True).sqrt()
+    upd = x * (step * (v_norm / v_new.clamp_min(1e-10)))
+    lr = 0.02 * math.sqrt(r / c)
+    ref = w0 - (lr * upd + lr * 0.05 * w0 * ((upd * w0) >= 0))
+    assert torch.allclose(w, ref, atol=1e-6)
+    assert torch.allclose(mom, m) and torch.allclose(sec, second)
+
+
+def test_adamw_update_matches_torch():
+    torch.manual_seed(2)
+    p = torch.randn(10, 7)
+    ref = p.clone().requires_grad_(True)
+    opt = torch.optim.AdamW([ref], lr=0.01, betas=(0.8, 0.95), eps=1e-10, weight_decay=0.1)
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    for step in range(1, 4):
+        g = torch.randn(10, 7)
+        ref.grad = g.clone()
+        opt.step()
+        RF.adamw_update(p, g, m, v, step=step, lr=0.01, beta1=0.8, beta2=0.95, eps=1e-10, wd=0.1)
+    assert torch.allclose(p, ref.detach(), atol=1e-5)
+
+
+def test_mx_quantisation_properties():
+    torch.manual_seed(3)
+    x = torch.randn(8, 128) * torch.logspace(-6, 3, 8)[:, None]
+    q, e = RF.mx_quantize(x, -1)
+    assert q.dtype == torch.float8_e4m3fn and e.shape == (8, 4) and e.dtype == torch.uint8
+    back = RF.mx_dequantize(q, e, -1)
+    blk = x.view(8, 4, 32)
+    amax = blk.abs().amax(-1)
+    scale = torch.exp2(e.float() - 127)
+    assert (amax / scale <= 448.0 + 1e-3).all()                    # nothing saturates
+    assert (amax / scale > 448.0 / 2 - 1e-3).all()                 # and the scale is the tightest power of two
+    assert ((back - x).abs() <= blk.abs().amax(-1, keepdim=True).expand(8, 4, 32).reshape(8, 128) * 2 ** -3).all()
+    z = torch.zeros(1, 32)
+    qz, ez = RF.mx_quantize(z)
+    assert (RF.mx_dequantize(qz, ez) == 0).all()
+    col = RF.mx_qdq(x.T.contiguous(), 0)                           # quantise along the other axis
+    assert torch.allclose(col.T, RF.mx_qdq(x, -1))
+
+
+def test_mx_linear_close_to_fp32():
+    torch.manual_seed(4)
+    x, w = torch.randn(64, 256), torch.randn(96, 256) * 0.05
+    rel = (RF.mx_linear(x, w) - x @ w.T).norm() / (x @ w.T).norm()
+    assert rel < 0.05
+
+
+def test_doc_start_and_attention_mask():
+    idx = torch.tensor([[0, 5, 6, 0, 7, 8, 9, 0]])
+    ds = RF.doc_start_positions(idx, 0)
+    assert ds.tolist() == [[0, 0, 0, 3, 3, 3, 3, 7]]
+    m = RF.attention_mask(8, "cpu", ds)[0, 0]
+    assert m[2].tolist() == [True, True, True, False, False, False, False, False]
+    assert m[5].tolist() == [False, False, False, True, True, True, False, False]
+    band = RF.attention_mask(512, "cpu", None, window=256)[0, 0]
+    assert band[511, 255] == False and band[511, 256] == True and band[300, 128] == True and band[300, 127] == False  # noqa: E712
+
+
+def test_stop_rule_shed_plan_and_control():
+    from them_bones_b200.runtime import Runtime
+    from them_bones_b200.utils.control import AsyncBoundary, StepControl, StopRule
+    from them_bones_b200.utils.shed import shed_plan
+    sr = StopRule(100.0, reserve_s=5.0)
+    for dt in (1.0, 1.2, 3.0):
+        sr.observe(dt)
+    assert not sr.should_stop(90.0) and sr.should_stop(92.5)
+    counts, total = shed_plan([10, 10, 10, 20, 10, 10, 10, 10], 4)
+    assert counts == [4, 4, 4, 3, 4, 4, 4, 4] and total == 31
+    assert shed_plan([10] * 8, 4)[0] == [4] * 8
+    rt = Runtime(False, 0, 0, 1, torch.device("cpu"), "cpu")
+    sc = StepControl(rt, 100.0)
+    assert sc.decide(float("nan"), False)[0] and sc.decide(101.0, False)[0] and not sc.decide(5.0, False)[0]
+    assert sc.decide(5.0, True)[1]
+    ab = AsyncBoundary("cpu", sync_every=3)
+    ab.submit(4, torch.tensor(2.5))
+    assert ab.collect() == (4, 2.5) and ab.must_sync(6) and not ab.must_sync(7)

@@ -16,7 +16,7 @@ import torch
 from . import _lib as L
 
 _I, _L, _F = ctypes.c_int, ctypes.c_longlong, ctypes.c_float
-HAVE_BWD = False
+HAVE_BWD = True
 
 
 def applies(qkv, n_head, head_dim) -> bool:
