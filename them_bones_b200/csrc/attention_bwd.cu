@@ -373,3 +373,82 @@ int bones_attn_bwd(const void* qk, const void* qkv, const void* dy, const float*
   return (int)cudaGetLastError();
 }
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------------------
+// Allocation-free variant of the attention backward (declared in bones_noalloc.h).
+// ---------------------------------------------------------------------------------------------------------------
+namespace bones {
+// delta = rowsum(dO * O) is the one piece of scratch the backward needs besides its inputs and outputs.  It lives here, in
+// a fixed array every GPU that loads this library keeps until the process exits (4 MiB), instead of coming from
+// cudaMalloc or a framework allocator.
+constexpr long long kNoAllocMaxRows = 1ll << 20;        // B * H * T
+static __device__ __align__(256) float g_noalloc_delta[kNoAllocMaxRows];
+static __device__ __align__(256) int g_noalloc_err[64];
+
+struct NoAllocDevice {
+  float* delta = nullptr;   // device addresses resolved from the symbols above (the symbol names are host stand-ins)
+  int* err = nullptr;
+  bool ready = false;
+};
+static NoAllocDevice g_noalloc_dev[64];
+}  // namespace bones
+
+extern "C" {
+using namespace bones;
+
+const char* bones_attn_bwd_noalloc_strerror(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case -2: return "sequence length must be a multiple of 128";
+    case -10: return "B*H*T exceeds the built-in scratch (1048576 rows): split the batch or use bones_attn_bwd";
+    case -11: return "could not resolve the scratch symbol on this device (cudaGetSymbolAddress failed)";
+    case -12: return "unsupported device ordinal (>= 64)";
+    default: return code > 0 ? "CUDA runtime error (the value is the cudaError_t)" : "tensor-map encoding failed";
+  }
+}
+
+int bones_attn_bwd_noalloc(const void* qk, const void* qkv, const void* dy, const void* y, const float* lse, float* dqk, void* dv,
+                           const int* doc_start, int B, int T, int H, float scale, int window_tiles, void* stream) {
+  if (T % BT) return -2;
+  const long long M = (long long)B * T, A = (long long)H * BD;
+  if (M * H > kNoAllocMaxRows) return -10;
+  int dev = 0;
+  BONES_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return -12;
+  constexpr size_t smem = (size_t)BTILE * 7 + 160 + 1024;
+  NoAllocDevice& nd = g_noalloc_dev[dev];
+  if (!nd.ready) {
+    // once per device, with that device current: turn the symbols into device addresses
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_delta) != cudaSuccess || !p) return -11;
+    nd.delta = static_cast<float*>(p);
+    if (cudaGetSymbolAddress(&p, g_noalloc_err) != cudaSuccess || !p) return -11;
+    nd.err = static_cast<int*>(p);
+    BONES_CHECK(cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    nd.ready = true;
+  }
+  CUtensorMap tq, tv, td;
+  int rc = tmap_rows_2d_b(&tq, qk, M, 2 * A);
+  if (rc) return rc;
+  rc = tmap_rows_2d_b(&tv, qkv, M, 3 * A);
+  if (rc) return rc;
+  rc = tmap_rows_2d_b(&td, dy, M, A);
+  if (rc) return rc;
+  cudaStream_t s = (cudaStream_t)stream;
+  const long long warps = M * H;
+  attn_delta_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, s>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)y, nd.delta, M, T, H);
+  BONES_CHECK(cudaGetLastError());
+  BONES_CHECK(cudaMemset2DAsync(dqk, (size_t)(2 * A) * 4, 0, (size_t)A * 4, (size_t)M, s));
+  AttnBwdParams p;
+  p.B = B; p.T = T; p.H = H;
+  p.c1 = scale * 1.4426950408889634f;
+  p.scale = scale;
+  p.window_tiles = window_tiles;
+  p.doc_start = doc_start;
+  p.lse = lse; p.delta = nd.delta; p.dqk = dqk; p.dv = (__nv_bfloat16*)dv;
+  p.err = nd.err;
+  dim3 grid(T / BT, H, B);
+  attn_bwd_kernel<<<grid, 320, smem, s>>>(tq, tv, td, p);
+  return (int)cudaGetLastError();
+}
+}  // extern "C"
