@@ -1,7 +1,112 @@
-"""Reference arm of ``bench.py --impl reference``."""
+"""Reference arm of ``bench.py --impl reference``.
+
+Runs the *unmodified* reference training program (``baseline/_ref/round2/source/train.py``, a byte-for-byte copy of the
+reference tree; the reference has no packaging, so ``pip install`` cannot produce it and the tree is copied instead)
+through its own entry point ``main()`` and its stock code path, at the benchmark's geometry given by its own CLI flags:
+``--depth 20 --aspect-ratio 64 --head-dim 128 --seq-len 2048 --total-batch-size 524288`` (20 layers x 1280, 10 heads x
+128, vocabulary 65536 from the kit constant).  The only thing supplied from outside is the competition kit module
+``prepare`` the reference imports but does not ship (``baseline/prepare.py``: synthetic Zipf data, timers).  Off Trainium
+every NKI kernel module of the reference reports itself unavailable and the program takes its plain PyTorch route: SDPA
+attention, cuBLAS linears, ``F.cross_entropy``, its lean Muon+AdamW optimizer over NCCL, under ``torch.compile`` as
+its defaults say.  None of this repository's models, kernels or optimizer run in that process.
+
+Each rank launched by ``torch.distributed.run`` starts one reference process with the same rendezvous environment.
+Step times come from the kit hook ``record_step_boundary`` that the reference calls after its own ``synchronize()``.
+"""
+from __future__ import annotations
+
 import json
+import os
+import subprocess
+import sys
+import tempfile
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REF_TRAIN = os.path.join(HERE, "_ref", "round2", "source", "train.py")
+PUBLISHED_TOK_S = 340000.0
+
+
+def _unavailable(why: str):
+    if int(os.environ.get("RANK", 0)) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
+    return 0
+
+
+def _run(args, compile_on: bool, workdir: str, stamps: str, device_batch: int):
+    env = dict(os.environ)
+    env["PYTHONPATH"] = HERE + os.pathsep + env.get("PYTHONPATH", "")
+    env["BONES_REF_VOCAB"] = "65536"
+    env["BONES_REF_STAMPS"] = stamps
+    env["R2_ATTN_V8"] = "1"          # the default attention module file is not part of the reference repository; this
+    #                                  switch names one that is (it declares itself unavailable off Trainium)
+    env["NEURON_COMPETITION_R2_COMPILE"] = "1" if compile_on else "0"
+    env.setdefault("MASTER_ADDR", "127.0.0.1")
+    cmd = [sys.executable, REF_TRAIN, "--depth", "20", "--aspect-ratio", "64", "--head-dim", "128", "--seq-len", "2048",
+           "--device-batch-size", str(device_batch), "--total-batch-size", str(args.total_batch), "--num-steps",
+           str(args.warmup + args.steps), "--out-dir", os.path.join(workdir, "out")]
+    log = os.path.join(workdir, f"ref_rank{os.environ.get('RANK', 0)}.log")
+    with open(log, "w") as fh:
+        rc = subprocess.run(cmd, env=env, cwd=workdir, stdout=fh, stderr=subprocess.STDOUT,
+                            timeout=int(os.environ.get("BONES_REF_TIMEOUT", 2400))).returncode
+    return rc, log
 
 
 def main(args):
-    print(json.dumps({"impl": "reference", "unavailable": "reference install not attempted yet"}), flush=True)
+    if not os.path.exists(REF_TRAIN):
+        return _unavailable("baseline/_ref is missing (the reference tree has no setup.py/pyproject; copy it there)")
+    import torch
+    if not torch.cuda.is_available():
+        return _unavailable("no CUDA device")
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if world != args.gpus:
+        return _unavailable(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    workdir = os.environ.get("BONES_REF_WORKDIR") or tempfile.mkdtemp(prefix="bones_ref_")
+    os.makedirs(workdir, exist_ok=True)
+    stamps = os.path.join(workdir, "stamps.json")
+    device_batch = int(os.environ.get("BONES_REF_DEVICE_BATCH", 8))
+    tried = []
+    for compile_on in ((True, False) if os.environ.get("BONES_REF_COMPILE", "1") != "0" else (False,)):
+        try:
+            rc, log = _run(args, compile_on, workdir, stamps, device_batch)
+        except subprocess.TimeoutExpired:
+            rc, log = -9, "(timeout)"
+        tried.append((compile_on, rc))
+        if rc == 0 and (rank != 0 or os.path.exists(stamps)):
+            break
+        if world > 1:
+            break                                   # ranks cannot agree on a retry without a rendezvous of their own
+    else:
+        tail = ""
+        try:
+            tail = open(log).read()[-400:].replace("\n", " | ")
+        except OSError:
+            pass
+        return _unavailable(f"reference run failed {tried}: {tail}")
+    if rank != 0:
+        return 0
+    if not os.path.exists(stamps):
+        return _unavailable(f"reference run left no step stamps {tried}")
+    st = json.load(open(stamps))
+    w, k = args.warmup, args.steps
+    if len(st) < w + k or w < 1:
+        return _unavailable(f"reference recorded {len(st)} steps, wanted {w + k}")
+    ms = (st[w + k - 1][1] - st[w - 1][1]) * 1e3
+    tokens = k * args.total_batch
+    value = tokens / (ms / 1e3)
+    local_tokens = args.total_batch // world
+    out = {
+        "impl": "reference", "metric": "train tokens/sec (device-timed, max over ranks)", "value": value, "unit": "tokens/s",
+        "n_gpus": world, "steps": k, "warmup": w, "ms_per_step": ms / k, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": value / PUBLISHED_TOK_S, "dtype": "bf16",
+        "data": "synthetic Zipf(1.1) tokens, documents 128-2048, random-init weights (kit shim baseline/prepare.py)",
+        "config": {"model": "round1-dense 20Lx1280 10hx128 relu2-mlp x4 vocab65536 (reference round2/source/train.py flags)",
+                   "global_batch": args.total_batch, "seq_len": 2048, "parallelism": f"dp{world}",
+                   "device_batch": device_batch, "torch_compile": tried[-1][0],
+                   "timing": "wall clock between the reference's own post-synchronize step boundaries on rank 0"},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": local_tokens * 8, "d2h_bytes_per_step": 4,
+                "note": "the reference's loop always includes its loader's host-to-device copies and its loss read"},
+        "gpu_launches": None,
+    }
+    print(json.dumps(out), flush=True)
     return 0

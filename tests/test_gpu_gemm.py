@@ -71,3 +71,18 @@ def test_gemm_epilogues_and_batch():
     torch.cuda.synchronize()
     L.check_error_word()
     assert _rel(of, acc) < 1e-4
+
+
+@pytest.mark.parametrize("splits", [0, 1, 4])
+def test_wgrad_split_k(splits):
+    """Weight-gradient GEMM (contraction over many rows, few output tiles) with split-K partial sums added atomically."""
+    L = _lib()
+    torch.manual_seed(5)
+    m, n, k = 8192, 384, 256
+    dy = torch.randn(m, n, device="cuda", dtype=torch.bfloat16)
+    x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    g = torch.full((n, k), -1.0, device="cuda", dtype=torch.float32)
+    L.gemm(dy, x, g, m=n, n=k, k=m, lda=n, ldb=k, ldd=k, a_major=1, b_major=1, epi=L.EPI_ACC_F32, splits=splits)
+    torch.cuda.synchronize()
+    L.check_error_word()
+    assert _rel(g, -1.0 + dy.float().T @ x.float()) < 2e-3

@@ -38,22 +38,39 @@ __global__ void rope_qknorm_fwd_kernel(const __nv_bfloat16* __restrict__ qkv, co
   const __nv_bfloat16* src = qkv + row * 3 * A + which * A + (long long)h * D;
   __nv_bfloat16* dst = qk + row * 2 * A + which * A + (long long)h * D;
   float y1[PER], y2[PER], ss = 0.f;
+  float x1[PER], x2[PER], cs[PER], sn[PER];
+  if constexpr (PER == 2) {   // 4-byte / 8-byte vector accesses: a warp reads 128 contiguous bytes per half
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + 2 * lane));
+    const float2 c2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + HALF + 2 * lane));
+    const float2 cc = *reinterpret_cast<const float2*>(cosT + (long long)t * HALF + 2 * lane);
+    const float2 sc = *reinterpret_cast<const float2*>(sinT + (long long)t * HALF + 2 * lane);
+    x1[0] = a.x; x1[1] = a.y; x2[0] = c2.x; x2[1] = c2.y; cs[0] = cc.x; cs[1] = cc.y; sn[0] = sc.x; sn[1] = sc.y;
+  } else {
+#pragma unroll
+    for (int e = 0; e < PER; ++e) {
+      const int i = lane * PER + e;
+      x1[e] = __bfloat162float(src[i]); x2[e] = __bfloat162float(src[HALF + i]);
+      cs[e] = cosT[(long long)t * HALF + i]; sn[e] = sinT[(long long)t * HALF + i];
+    }
+  }
 #pragma unroll
   for (int e = 0; e < PER; ++e) {
-    const int i = lane * PER + e;
-    const float x1 = __bfloat162float(src[i]), x2 = __bfloat162float(src[HALF + i]);
-    const float c = cosT[(long long)t * HALF + i], s = sinT[(long long)t * HALF + i];
-    y1[e] = x1 * c + x2 * s;
-    y2[e] = -x1 * s + x2 * c;
+    y1[e] = x1[e] * cs[e] + x2[e] * sn[e];
+    y2[e] = -x1[e] * sn[e] + x2[e] * cs[e];
     ss += y1[e] * y1[e] + y2[e] * y2[e];
   }
   ss = warp_sum(ss);
   const float r = rsqrtf(ss / D + kQkEps);
+  if constexpr (PER == 2) {
+    *reinterpret_cast<__nv_bfloat162*>(dst + 2 * lane) = __floats2bfloat162_rn(y1[0] * r, y1[1] * r);
+    *reinterpret_cast<__nv_bfloat162*>(dst + HALF + 2 * lane) = __floats2bfloat162_rn(y2[0] * r, y2[1] * r);
+  } else {
 #pragma unroll
-  for (int e = 0; e < PER; ++e) {
-    const int i = lane * PER + e;
-    dst[i] = __float2bfloat16(y1[e] * r);
-    dst[HALF + i] = __float2bfloat16(y2[e] * r);
+    for (int e = 0; e < PER; ++e) {
+      const int i = lane * PER + e;
+      dst[i] = __float2bfloat16(y1[e] * r);
+      dst[HALF + i] = __float2bfloat16(y2[e] * r);
+    }
   }
 }
 
@@ -74,23 +91,39 @@ __global__ void rope_qknorm_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, co
   __nv_bfloat16* out = dqkv + row * 3 * A + which * A + (long long)h * D;
   if (which == 2) {   // values pass straight through
     const __nv_bfloat16* g = dv + row * A + (long long)h * D;
-    for (int i = lane; i < D; i += 32) out[i] = g[i];
+    if constexpr (D == 128) {
+      *reinterpret_cast<uint2*>(out + 4 * lane) = *reinterpret_cast<const uint2*>(g + 4 * lane);
+    } else {
+      for (int i = lane; i < D; i += 32) out[i] = g[i];
+    }
     return;
   }
   const int t = (int)(row % T);
   const __nv_bfloat16* src = qkv + row * 3 * A + which * A + (long long)h * D;
   const float* g = dqk + row * 2 * A + which * A + (long long)h * D;
-  float y1[PER], y2[PER], g1[PER], g2[PER], cs[PER], sn[PER], ss = 0.f, dot = 0.f;
+  float y1[PER], y2[PER], g1[PER], g2[PER], cs[PER], sn[PER], x1[PER], x2[PER], ss = 0.f, dot = 0.f;
+  if constexpr (PER == 2) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + 2 * lane));
+    const float2 c2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + HALF + 2 * lane));
+    const float2 cc = *reinterpret_cast<const float2*>(cosT + (long long)t * HALF + 2 * lane);
+    const float2 sc = *reinterpret_cast<const float2*>(sinT + (long long)t * HALF + 2 * lane);
+    const float2 ga = *reinterpret_cast<const float2*>(g + 2 * lane);
+    const float2 gb = *reinterpret_cast<const float2*>(g + HALF + 2 * lane);
+    x1[0] = a.x; x1[1] = a.y; x2[0] = c2.x; x2[1] = c2.y; cs[0] = cc.x; cs[1] = cc.y; sn[0] = sc.x; sn[1] = sc.y;
+    g1[0] = ga.x; g1[1] = ga.y; g2[0] = gb.x; g2[1] = gb.y;
+  } else {
+#pragma unroll
+    for (int e = 0; e < PER; ++e) {
+      const int i = lane * PER + e;
+      x1[e] = __bfloat162float(src[i]); x2[e] = __bfloat162float(src[HALF + i]);
+      cs[e] = cosT[(long long)t * HALF + i]; sn[e] = sinT[(long long)t * HALF + i];
+      g1[e] = g[i]; g2[e] = g[HALF + i];
+    }
+  }
 #pragma unroll
   for (int e = 0; e < PER; ++e) {
-    const int i = lane * PER + e;
-    const float x1 = __bfloat162float(src[i]), x2 = __bfloat162float(src[HALF + i]);
-    cs[e] = cosT[(long long)t * HALF + i];
-    sn[e] = sinT[(long long)t * HALF + i];
-    y1[e] = x1 * cs[e] + x2 * sn[e];
-    y2[e] = -x1 * sn[e] + x2 * cs[e];
-    g1[e] = g[i];
-    g2[e] = g[HALF + i];
+    y1[e] = x1[e] * cs[e] + x2[e] * sn[e];
+    y2[e] = -x1[e] * sn[e] + x2[e] * cs[e];
     ss += y1[e] * y1[e] + y2[e] * y2[e];
     dot += y1[e] * g1[e] + y2[e] * g2[e];
   }
@@ -98,12 +131,23 @@ __global__ void rope_qknorm_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, co
   dot = warp_sum(dot);
   const float r = rsqrtf(ss / D + kQkEps);
   const float m = dot * r * r / D;     // mean(dxhat * xhat) * r, with xhat = u r
+  float o1[PER], o2[PER];
 #pragma unroll
   for (int e = 0; e < PER; ++e) {
-    const int i = lane * PER + e;
     const float du1 = r * (g1[e] - y1[e] * m), du2 = r * (g2[e] - y2[e] * m);
-    out[i] = __float2bfloat16(du1 * cs[e] - du2 * sn[e]);
-    out[HALF + i] = __float2bfloat16(du1 * sn[e] + du2 * cs[e]);
+    o1[e] = du1 * cs[e] - du2 * sn[e];
+    o2[e] = du1 * sn[e] + du2 * cs[e];
+  }
+  if constexpr (PER == 2) {
+    *reinterpret_cast<__nv_bfloat162*>(out + 2 * lane) = __floats2bfloat162_rn(o1[0], o1[1]);
+    *reinterpret_cast<__nv_bfloat162*>(out + HALF + 2 * lane) = __floats2bfloat162_rn(o2[0], o2[1]);
+  } else {
+#pragma unroll
+    for (int e = 0; e < PER; ++e) {
+      const int i = lane * PER + e;
+      out[i] = __float2bfloat16(o1[e]);
+      out[HALF + i] = __float2bfloat16(o2[e]);
+    }
   }
 }
 

@@ -40,6 +40,7 @@ struct GemmParams {
   long long ldr, strideR;
   int* err;
   int tiles_m, tiles_n;
+  int splits;          // split-K factor (> 1 only with EPI_ACC_F32: partial tiles are added with vector atomics)
 };
 
 constexpr int BM = 128;
@@ -105,7 +106,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   tc_fence_after();
   const uint32_t tmem = *tmem_slot_g;
 
-  const int total = p.batch * p.tiles_m * p.tiles_n;
+  const int total = p.batch * p.tiles_m * p.tiles_n * p.splits;
   const int KB = (p.K + BK - 1) / BK;
 
   if (warp == 0) {
@@ -115,8 +116,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       bool ok = true;
       for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
         int b, mb, nb;
-        decode_tile(tile, p.tiles_m, p.tiles_n, b, mb, nb);
-        for (int kb = 0; kb < KB; ++kb) {
+        const int sp = tile % p.splits;
+        decode_tile(tile / p.splits, p.tiles_m, p.tiles_n, b, mb, nb);
+        const int kb0 = (int)((long long)KB * sp / p.splits), kb1 = (int)((long long)KB * (sp + 1) / p.splits);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(empty(stage), phase ^ 1u, abort_flag, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
           mbar_arrive_expect_tx(full(stage), STAGE_BYTES);
           const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_BYTES;
@@ -149,7 +152,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         if (!mbar_wait(tempty(acc), acc_phase ^ 1u, abort_flag, p.err, ERR_WAIT_TMEM_EMPTY)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem + acc * BN;
-        for (int kb = 0; kb < KB; ++kb) {
+        const int sp = tile % p.splits;
+        const int kb0 = (int)((long long)KB * sp / p.splits), kb1 = (int)((long long)KB * (sp + 1) / p.splits);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(full(stage), phase, abort_flag, p.err, ERR_WAIT_FULL)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_BYTES;
@@ -157,7 +162,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           const uint64_t bdesc = umma_smem_desc(sb, b_lbo, 1024, kLayoutSw128);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)
-            umma_f16(d_tmem, adesc + (uint64_t)(k * a_step), bdesc + (uint64_t)(k * b_step), idesc, (kb | k) ? 1u : 0u);
+            umma_f16(d_tmem, adesc + (uint64_t)(k * a_step), bdesc + (uint64_t)(k * b_step), idesc, ((kb - kb0) | k) ? 1u : 0u);
           tc_commit(empty(stage));
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -173,7 +178,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     uint32_t acc_phase = 0;
     for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
       int b, mb, nb;
-      decode_tile(tile, p.tiles_m, p.tiles_n, b, mb, nb);
+      decode_tile(tile / p.splits, p.tiles_m, p.tiles_n, b, mb, nb);
       const bool got = mbar_wait(tfull(acc), acc_phase, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
       if (!__all_sync(0xffffffffu, got)) break;   // warp-uniform: the TMEM loads below need the whole warp
       tc_fence_after();
@@ -248,6 +253,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
             for (int j = 0; j < 8; ++j) {
               float4 o = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
               if (p.epi == EPI_ACC_F32) {
+                if (p.splits > 1) {
+                  atomicAdd(reinterpret_cast<float4*>(D + 4 * j), o);
+                  continue;
+                }
                 const float4 d = *reinterpret_cast<const float4*>(D + 4 * j);
                 o.x += d.x; o.y += d.y; o.z += d.z; o.w += d.w;
               } else if (p.epi == EPI_F32_RES) {
@@ -259,6 +268,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           } else {
             for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
               float x = v[j];
+              if (p.epi == EPI_ACC_F32 && p.splits > 1) { atomicAdd(D + j, x); continue; }
               if (p.epi == EPI_ACC_F32) x += D[j];
               else if (p.epi == EPI_F32_RES) x += p.beta * R[j];
               D[j] = x;
@@ -301,7 +311,24 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams 
   BONES_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   p.tiles_m = (p.M + BM - 1) / BM;
   p.tiles_n = (p.N + BN - 1) / BN;
-  const int total = p.batch * p.tiles_m * p.tiles_n;
+  const int base_tiles = p.batch * p.tiles_m * p.tiles_n;
+  const int KB = (p.K + BK - 1) / BK;
+  if (p.splits <= 0) {
+    // split-K only pays for fp32-accumulating outputs (weight gradients: few output tiles, very long K)
+    p.splits = 1;
+    if (p.epi == EPI_ACC_F32 && base_tiles < 4 * sms && KB >= 32) {
+      long long best = -1;
+      const int cand[] = {1, 2, 3, 4, 6, 8, 12, 16};
+      for (int c : cand) {
+        if (c > KB / 8) break;
+        const long long waves = ((long long)base_tiles * c + sms - 1) / sms;
+        const long long cost = waves * (((long long)KB + c - 1) / c + 6) + (c > 1 ? 2 * c : 0);   // +6: tile prologue/epilogue, 2c: atomics
+        if (best < 0 || cost < best) { best = cost; p.splits = c; }
+      }
+    }
+  }
+  if (p.splits > 1 && p.epi != EPI_ACC_F32) p.splits = 1;
+  const int total = base_tiles * p.splits;
   const int grid = total < sms ? total : sms;
   gemm_bf16_kernel<BN, STAGES><<<grid, 192, smem, stream>>>(ta, tb, p);
   return (int)cudaGetLastError();
@@ -333,7 +360,7 @@ extern "C" {
 // Returns 0 on success, a CUDA error code (> 0) or a negative descriptor-encoding error.
 int bones_gemm_bf16(const void* A, const void* B, void* D, const void* R, int M, int N, int K, int batch, long long lda,
                     long long ldb, long long ldd, long long ldr, long long strideA, long long strideB, long long strideD,
-                    long long strideR, int a_major, int b_major, int epi, float alpha, float beta, int force_bn, void* stream) {
+                    long long strideR, int a_major, int b_major, int epi, float alpha, float beta, int force_bn, int splits, void* stream) {
   using namespace bones;
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 0;
   if ((lda % 8) || (ldb % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || ((uintptr_t)D & 15)) return -2;
@@ -347,6 +374,7 @@ int bones_gemm_bf16(const void* A, const void* B, void* D, const void* R, int M,
   p.D = D; p.ldd = ldd; p.strideD = strideD;
   p.R = R ? R : D; p.ldr = R ? ldr : ldd; p.strideR = R ? strideR : strideD;
   p.err = error_word();
+  p.splits = splits;
   CUtensorMap ta, tb;
   int rc = operand_tmap(&ta, A, a_major, M, K, lda, strideA, batch, BM);
   if (rc) return rc;

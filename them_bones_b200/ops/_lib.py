@@ -69,8 +69,8 @@ EPI_BF16, EPI_BF16_RES, EPI_RELU2, EPI_ACC_F32, EPI_MUL_2SQRT, EPI_F32, EPI_F32_
 
 
 def gemm(a, b, d, *, m, n, k, lda, ldb, ldd, a_major=0, b_major=0, epi=EPI_BF16, r=None, ldr=0, alpha=1.0, beta=1.0,
-         batch=1, stride_a=0, stride_b=0, stride_d=0, stride_r=0, force_bn=0):
+         batch=1, stride_a=0, stride_b=0, stride_d=0, stride_r=0, force_bn=0, splits=0):
     """``d = epilogue(alpha * a @ b^T, r)``; see csrc/gemm_bf16.cu for operand layouts."""
     call("bones_gemm_bf16", ptr(a), ptr(b), ptr(d), ptr(r), _I(m), _I(n), _I(k), _I(batch), _L(lda), _L(ldb), _L(ldd),
          _L(ldr), _L(stride_a), _L(stride_b), _L(stride_d), _L(stride_r), _I(a_major), _I(b_major), _I(epi), _F(alpha),
-         _F(beta), _I(force_bn), stream())
+         _F(beta), _I(force_bn), _I(splits), stream())

@@ -153,7 +153,7 @@ class LeanDistMuonAdamW(torch.optim.Optimizer):
         n = sum(p.numel() for p, _ in small)
         dev = small[0][0].device if small else torch.device("cpu")
         self.S = torch.zeros(n, dtype=torch.float32, device=dev)
-        self.SG = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.SG = comm.alloc((max(n, 1),), torch.float32, dev)[:n]      # peers read it in the fused scalar all-reduce
         self.S_m, self.S_v = torch.zeros_like(self.S), torch.zeros_like(self.S)
         self.small = []
         o = 0
@@ -170,6 +170,15 @@ class LeanDistMuonAdamW(torch.optim.Optimizer):
         if self.ns_dtype is not None:
             return self.ns_dtype
         return torch.bfloat16 if t.is_cuda else torch.float32
+
+    @staticmethod
+    def _ns_fn(t):
+        """The tcgen05 Newton-Schulz on a GPU (unless the plain-PyTorch path is forced), else None."""
+        from .. import ops
+        if t.is_cuda and not ops.reference_path() and t.shape[-1] % 8 == 0 and t.shape[-2] % 8 == 0:
+            from ..ops import muon_native
+            return muon_native.newton_schulz
+        return None
 
     # ------------------------------------------------------------------------------------------------------
     @torch.no_grad()
@@ -235,16 +244,17 @@ class LeanDistMuonAdamW(torch.optim.Optimizer):
         for u, g in zip(self.muon_units, muon_g):
             grp = u.group
             RF.muon_update(g, u.master, u.momentum, u.second, momentum=grp["momentum"], beta2=grp["beta2"],
-                           lr=grp["lr"], wd=grp["weight_decay"], ns_steps=grp["ns_steps"], ns_dtype=self._ns(u.W))
+                           lr=grp["lr"], wd=grp["weight_decay"], ns_steps=grp["ns_steps"], ns_dtype=self._ns(u.W),
+                           ns_fn=self._ns_fn(u.W))
             comm.all_gather(u.W, u.master.to(u.W.dtype))
         # 5b: local experts
         self._local.step(1.0 / self.world)
 
-    def _small_step(self):
+    def _small_step(self, g=None):
         if not self.small:
             return
         lr, b1, b2, wd = self._small_vectors()
-        g = self.SG
+        g = self.SG if g is None else g
         self.S.mul_(1 - lr * wd)
         self.S_m.mul_(b1).add_((1 - b1) * g)
         self.S_v.mul_(b2).add_((1 - b2) * g * g)
@@ -256,8 +266,7 @@ class LeanDistMuonAdamW(torch.optim.Optimizer):
         over NVLink and applies the owner update; one launch publishes the updated shard into every peer's slab."""
         comm = self.comm
         comm.pre_step()                                   # all ranks' gradients are complete and visible
-        comm.all_reduce_mean(self.SG)
-        self._small_step()
+        self._small_step(comm.all_reduce_mean(self.SG))
         for u in self.row_units:
             comm.fused_row_adamw(u, self.steps)
         for u in self.muon_units:

@@ -211,7 +211,8 @@ def newton_schulz(x: torch.Tensor, steps: int = 5) -> torch.Tensor:
     return x
 
 
-def muon_update(g, w, momentum_buffer, second, *, momentum, beta2, lr, wd, ns_steps=5, ns_dtype=torch.float32):
+def muon_update(g, w, momentum_buffer, second, *, momentum, beta2, lr, wd, ns_steps=5, ns_dtype=torch.float32,
+                ns_fn=None):
     """One Muon step on stacks ``[n, r, c]`` (in place on ``w``, ``momentum_buffer``, ``second``): momentum lerp,
     Nesterov, Frobenius normalisation, Polar-Express NS, NorMuon second-moment rescale that keeps the Frobenius norm,
     cautious weight decay, ``lr * sqrt(max(1, r/c))`` (reference: round2/source/train.py:11868-11905)."""
@@ -221,7 +222,7 @@ def muon_update(g, w, momentum_buffer, second, *, momentum, beta2, lr, wd, ns_st
     g = g.lerp(momentum_buffer, momentum)
     x = g.to(ns_dtype)
     x = x / (x.norm(dim=(-2, -1), keepdim=True) * 1.01 + 1e-6)
-    g = newton_schulz(x, ns_steps)
+    g = (ns_fn or newton_schulz)(x.contiguous() if ns_fn else x, ns_steps)
     red_dim = -1 if r >= c else -2
     v_mean = g.float().square().mean(dim=red_dim, keepdim=True)
     n_red = g.size(red_dim)
