@@ -86,3 +86,47 @@ def test_wgrad_split_k(splits):
     torch.cuda.synchronize()
     L.check_error_word()
     assert _rel(g, -1.0 + dy.float().T @ x.float()) < 2e-3
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (512, 768, 320), (1000, 520, 200), (2048, 1280, 1280)])
+def test_pair_gemm_nt(m, n, k):
+    """CTA-pair (cta_group::2) kernel: K-major operands, ragged edges."""
+    L = _lib()
+    torch.manual_seed(7)
+    x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(n, k, device="cuda", dtype=torch.bfloat16)
+    out = torch.zeros(m, n, device="cuda", dtype=torch.bfloat16)
+    L.gemm(x, w, out, m=m, n=n, k=k, lda=k, ldb=k, ldd=n, pair=True)
+    torch.cuda.synchronize()
+    L.check_error_word()
+    assert _rel(out, x.float() @ w.float().T) < 6e-3
+
+
+def test_pair_gemm_layouts_epilogues_batch():
+    L = _lib()
+    torch.manual_seed(8)
+    m, n, k = 512, 384, 640
+    dy = torch.randn(m, n, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(n, k, device="cuda", dtype=torch.bfloat16)
+    x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    dx = torch.empty(m, k, device="cuda", dtype=torch.bfloat16)
+    L.gemm(dy, w, dx, m=m, n=k, k=n, lda=n, ldb=k, ldd=k, b_major=1, pair=True)
+    g = torch.full((n, k), 0.25, device="cuda", dtype=torch.float32)
+    L.gemm(dy, x, g, m=n, n=k, k=m, lda=n, ldb=k, ldd=k, a_major=1, b_major=1, epi=L.EPI_ACC_F32, pair=True)
+    g2 = torch.full((n, k), 0.25, device="cuda", dtype=torch.float32)
+    L.gemm(dy, x, g2, m=n, n=k, k=m, lda=n, ldb=k, ldd=k, a_major=1, b_major=1, epi=L.EPI_ACC_F32, splits=2, pair=True)
+    torch.cuda.synchronize()
+    L.check_error_word()
+    assert _rel(dx, dy.float() @ w.float()) < 6e-3
+    assert _rel(g, 0.25 + dy.float().T @ x.float()) < 2e-3 and _rel(g2, 0.25 + dy.float().T @ x.float()) < 2e-3
+    b = 3
+    xb = torch.randn(b, 256, 320, device="cuda", dtype=torch.bfloat16)
+    wb = torch.randn(b, 512, 320, device="cuda", dtype=torch.bfloat16) * 0.1
+    rb = torch.randn(b, 256, 512, device="cuda", dtype=torch.bfloat16)
+    o = torch.empty(b, 256, 512, device="cuda", dtype=torch.bfloat16)
+    L.gemm(xb, wb, o, m=256, n=512, k=320, lda=320, ldb=320, ldd=512, batch=b, stride_a=256 * 320, stride_b=512 * 320,
+           stride_d=256 * 512, epi=L.EPI_BF16_RES, r=rb, ldr=512, stride_r=256 * 512, alpha=0.5, beta=2.0, pair=True)
+    torch.cuda.synchronize()
+    L.check_error_word()
+    acc = torch.einsum("bmk,bnk->bmn", xb.float(), wb.float())
+    assert _rel(o, 0.5 * acc + 2.0 * rb.float()) < 6e-3
