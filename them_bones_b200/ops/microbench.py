@@ -1,0 +1,135 @@
+"""Kernel micro-benchmarks with roofline fractions.
+
+    python -m them_bones_b200.ops.microbench gemm --m 8192 --n 8192 --k 8192 [--pair 1] [--layout nt|nn|tn]
+    python -m them_bones_b200.ops.microbench attn_fwd --b 4 --t 2048 --h 10
+    python -m them_bones_b200.ops.microbench attn_bwd --b 4 --t 2048 --h 10
+    python -m them_bones_b200.ops.microbench norm --rows 65536 --cols 1280
+    python -m them_bones_b200.ops.microbench ce --rows 4096 --vocab 65536
+
+Timing: CUDA events on the launching stream, ``--warmup`` untimed iterations, an L2 flush (a 256 MiB write) between
+timed iterations, mean over ``--iters``.  Fractions are against the measured peaks in ``MEASURED_PEAKS.json`` at the
+repository root when present (copy bandwidth, cuBLAS bf16 burst), else 6650 GB/s and 1590 TFLOP/s.  ``--iters 1
+--warmup 0 --no-flush`` gives a launch list short enough to run under a profiler.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+
+import torch
+
+from . import _lib as L
+
+
+def peaks():
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    try:
+        d = json.load(open(os.path.join(root, "MEASURED_PEAKS.json")))
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    except (OSError, KeyError, ValueError):
+        return 6650.0, 1590.0, "fallback"
+
+
+def timeit(fn, iters, warmup, flush):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    total = 0.0
+    for _ in range(iters):
+        if buf is not None:
+            buf.zero_()
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    L.check_error_word()
+    return total / iters
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemm", "attn_fwd", "attn_bwd", "norm", "ce"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--pair", type=int, default=1)
+    ap.add_argument("--layout", default="nt")
+    ap.add_argument("--b", type=int, default=4)
+    ap.add_argument("--t", type=int, default=2048)
+    ap.add_argument("--h", type=int, default=10)
+    ap.add_argument("--rows", type=int, default=65536)
+    ap.add_argument("--cols", type=int, default=1280)
+    ap.add_argument("--vocab", type=int, default=65536)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--no-flush", action="store_true")
+    a = ap.parse_args()
+    hbm, tf, src = peaks()
+    bf = torch.bfloat16
+    out = {"what": a.what, "peaks": src}
+    torch.manual_seed(0)
+    if a.what == "gemm":
+        m, n, k = a.m, a.n, a.k
+        if a.layout == "nt":
+            x, w, d = torch.randn(m, k, device="cuda", dtype=bf), torch.randn(n, k, device="cuda", dtype=bf), torch.empty(m, n, device="cuda", dtype=bf)
+            fn = lambda: L.gemm(x, w, d, m=m, n=n, k=k, lda=k, ldb=k, ldd=n, pair=bool(a.pair))  # noqa: E731
+        elif a.layout == "nn":
+            x, w, d = torch.randn(m, k, device="cuda", dtype=bf), torch.randn(k, n, device="cuda", dtype=bf), torch.empty(m, n, device="cuda", dtype=bf)
+            fn = lambda: L.gemm(x, w, d, m=m, n=n, k=k, lda=k, ldb=n, ldd=n, b_major=1, pair=bool(a.pair))  # noqa: E731
+        else:
+            x, w, d = torch.randn(k, m, device="cuda", dtype=bf), torch.randn(k, n, device="cuda", dtype=bf), torch.zeros(m, n, device="cuda")
+            fn = lambda: L.gemm(x, w, d, m=m, n=n, k=k, lda=m, ldb=n, ldd=n, a_major=1, b_major=1, epi=L.EPI_ACC_F32, pair=bool(a.pair))  # noqa: E731
+        ms = timeit(fn, a.iters, a.warmup, not a.no_flush)
+        fl = 2.0 * m * n * k
+        out.update(shape=[m, n, k], layout=a.layout, pair=a.pair, ms=ms, tflops=fl / ms / 1e9, frac_of_bf16_peak=fl / ms / 1e9 / tf)
+    elif a.what in ("attn_fwd", "attn_bwd"):
+        from . import attention_bwd as AB
+        from . import attention_native as AN
+        from ..ref import functional as RF
+        b, t, h, d = a.b, a.t, a.h, 128
+        qkv = torch.randn(b * t, 3 * h * d, device="cuda", dtype=bf)
+        cos, sin = RF.rotary_tables(t, d, 10000.0, device="cuda")
+        scale = 1.0 / math.sqrt(d)
+        qk = AN.rope_qknorm(qkv, cos, sin, t, h, d)
+        y, lse = AN.attn_forward(qk, qkv, None, b, t, h, scale, 0)
+        fl = 4.0 * b * h * t * t * d / 2                      # causal: half the square
+        if a.what == "attn_fwd":
+            ms = timeit(lambda: AN.attn_forward(qk, qkv, None, b, t, h, scale, 0), a.iters, a.warmup, not a.no_flush)
+        else:
+            dy = torch.randn(b * t, h * d, device="cuda", dtype=bf)
+            ms = timeit(lambda: AB.backward(dy, qkv, qk, y, lse, cos, sin, None, b, t, h, d, scale, 0), a.iters, a.warmup,
+                        not a.no_flush)
+            fl *= 2.5
+        out.update(shape=[b, t, h, d], ms=ms, tflops=fl / ms / 1e9, frac_of_bf16_peak=fl / ms / 1e9 / tf)
+    elif a.what == "norm":
+        from . import cuda as C
+        x = torch.randn(a.rows, a.cols, device="cuda", dtype=bf)
+        x0 = torch.randn_like(x)
+        one, small = torch.ones(1, device="cuda"), torch.full((1,), 0.05, device="cuda")
+        with torch.no_grad():
+            ms = timeit(lambda: C.resid_mix_norm(x, x0, one, small), a.iters, a.warmup, not a.no_flush)
+        by = 4.0 * x.numel() * 2                                # two reads, two writes
+        out.update(shape=[a.rows, a.cols], ms=ms, gbs=by / ms / 1e6, frac_of_hbm_peak=by / ms / 1e6 / hbm)
+    else:
+        import ctypes
+        rows, v = a.rows, a.vocab
+        lg = torch.randn(rows, v, device="cuda", dtype=bf)
+        tg = torch.randint(0, v, (rows,), device="cuda")
+        nll = torch.empty(rows, device="cuda")
+        nv = torch.full((1,), float(rows), device="cuda")
+        fn = lambda: L.call("bones_softcap_ce", L.ptr(lg), ctypes.c_longlong(v), L.ptr(tg), ctypes.c_int(v),  # noqa: E731
+                            ctypes.c_float(15.0), L.ptr(nll), L.ptr(lg), L.ptr(None), L.ptr(nv), ctypes.c_float(1.0),
+                            ctypes.c_int(rows), L.stream())
+        ms = timeit(fn, a.iters, a.warmup, not a.no_flush)
+        by = 3.0 * lg.numel() * 2                               # read twice, write once
+        out.update(shape=[rows, v], ms=ms, gbs=by / ms / 1e6, frac_of_hbm_peak=by / ms / 1e6 / hbm)
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()
