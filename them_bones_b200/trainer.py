@@ -110,6 +110,9 @@ class Trainer:
             total = loss.detach() if total is None else total + loss.detach()
         self.sched = schedules.apply_schedules(opt, self.hyper, self.step_index, self.progress())
         opt.step()
+        if self.config.mlp_precision == "mxfp8" and self.rt.device_type == "cuda":
+            from .ops import mxfp8
+            mxfp8.weights_updated()          # quantised weight copies are refreshed lazily on their next use
         if self.tables is not None:
             self.tables.step(self.sched["table_lr"])
         self.step_index += 1
