@@ -178,7 +178,7 @@ __device__ __forceinline__ int attn_first_tile(const AttnParams& p, int b, int q
   return lo;
 }
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -209,7 +209,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
     for (int s = 0; s < 2; ++s) {
       mbar_init(kv_full(s), 1);
       mbar_init(s_full(s), 1);
-      mbar_init(p_full(s), 4);
+      mbar_init(p_full(s), 8);
       mbar_init(pv_done(s), 1);
     }
     mbar_init(o_full, 1);
@@ -285,9 +285,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
       if (ok) tc_commit(o_full);
     }
   } else {
-    const int q = warp & 3;
+    // Softmax: eight warps, two per 32-lane TMEM quadrant; each thread owns one query row and 64 of the tile's 128 keys.
+    const int q = warp & 3, half = (warp - 2) >> 2;
     const int r = q * 32 + lane;            // row within the tile == TMEM lane
+    const int c0 = half * 64;
     const int qpos = qt * AT + r;
+    const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
     int lo = 0;
     if (p.doc_start) lo = p.doc_start[(long long)b * p.T + qpos];
     float l = 0.f;
@@ -298,33 +301,36 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
       if (got && j >= 2) got = mbar_wait(pv_done(s), ((j - 2) >> 1) & 1, abort_flag, p.err, ERR_WAIT_EMPTY);
       if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
       tc_fence_after();
-      const int k0 = (kt0 + j) * AT;
-      const bool need_mask = (k0 + AT - 1 > qt * AT) || (k0 < lo);   // diagonal tile or document boundary inside
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      const int k0 = (kt0 + j) * AT + c0;
+      // warp-uniform: does any row of this warp need the element mask for these 64 keys (diagonal or document start)?
+      const bool need_mask = __any_sync(0xffffffffu, (k0 + 63 > qpos) || (k0 < lo));
+      const uint32_t prow = sP(s) + (uint32_t)half * ATOM_BYTES + (uint32_t)r * 128u;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
         uint32_t v[32];
         __syncwarp();
-        BONES_TMEM_LD32(tS[s] + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
+        BONES_TMEM_LD32(tS[s] + lane_addr + (uint32_t)(c0 + c * 32), v);
         tmem_ld_wait();
-        float pr[32];
+        float e[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float e = exp2f(__uint_as_float(v[i]) * p.c1 - p.c2);
-          if (need_mask) {
-            const int kpos = k0 + c * 32 + i;
-            if (kpos > qpos || kpos < lo) e = 0.f;
-          }
-          // the row sum must match what the second GEMM sees: sum the bf16-rounded probabilities
-          const float eb = __bfloat162float(__float2bfloat16(e));
-          pr[i] = eb;
-          l += eb;
+          const float x = fmaf(__uint_as_float(v[i]), p.c1, -p.c2);
+          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e[i]) : "f"(x));
         }
-        const uint32_t prow = sP(s) + (uint32_t)(c >> 1) * ATOM_BYTES + (uint32_t)r * 128u;
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int kpos = k0 + c * 32 + i;
+            if (kpos > qpos || kpos < lo) e[i] = 0.f;
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) l += e[i];
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          const uint32_t chunk = (uint32_t)((c & 1) * 4 + g) ^ (uint32_t)(r & 7);
-          const uint32_t w0 = pack_bf16(pr[g * 8 + 0], pr[g * 8 + 1]), w1 = pack_bf16(pr[g * 8 + 2], pr[g * 8 + 3]);
-          const uint32_t w2 = pack_bf16(pr[g * 8 + 4], pr[g * 8 + 5]), w3 = pack_bf16(pr[g * 8 + 6], pr[g * 8 + 7]);
+          const uint32_t chunk = (uint32_t)(c * 4 + g) ^ (uint32_t)(r & 7);
+          const uint32_t w0 = pack_bf16(e[g * 8 + 0], e[g * 8 + 1]), w1 = pack_bf16(e[g * 8 + 2], e[g * 8 + 3]);
+          const uint32_t w2 = pack_bf16(e[g * 8 + 4], e[g * 8 + 5]), w3 = pack_bf16(e[g * 8 + 6], e[g * 8 + 7]);
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + chunk * 16u), "r"(w0), "r"(w1), "r"(w2), "r"(w3)
                        : "memory");
         }
@@ -334,17 +340,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full(s));
     }
+    // the two threads of a row exchange their partial row sums through shared memory (the Q tile is dead by now only
+    // after the last S MMA, so a dedicated 1 KB scratch after the barriers is used)
+    float* lsum = reinterpret_cast<float*>(gen + TILE_BYTES * 7 + 128);
+    lsum[half * AT + r] = l;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    l += lsum[(half ^ 1) * AT + r];
     if (ok) {
       const bool got = mbar_wait(o_full, 0, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
       if (__all_sync(0xffffffffu, got)) {
         tc_fence_after();
         const float inv = 1.0f / l;
-        __nv_bfloat16* yrow = p.y + ((long long)(row0 + qpos)) * A + (long long)h * AD;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        __nv_bfloat16* yrow = p.y + ((long long)(row0 + qpos)) * A + (long long)h * AD + c0;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
           uint32_t v[32];
           __syncwarp();
-          BONES_TMEM_LD32(tO + ((uint32_t)(q * 32) << 16) + (uint32_t)(c * 32), v);
+          BONES_TMEM_LD32(tO + lane_addr + (uint32_t)(c0 + c * 32), v);
           tmem_ld_wait();
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
@@ -356,7 +368,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
             *reinterpret_cast<uint4*>(yrow + c * 32 + g * 8) = u;
           }
         }
-        p.lse[((long long)b * p.H + h) * p.T + qpos] = logf(l) + p.shift_ln;
+        if (half == 0) p.lse[((long long)b * p.H + h) * p.T + qpos] = logf(l) + p.shift_ln;
       }
     }
   }
@@ -431,14 +443,14 @@ int bones_attn_fwd(const void* qk, const void* qkv, void* y, float* lse, const i
   p.y = (__nv_bfloat16*)y;
   p.lse = lse;
   p.err = error_word();
-  constexpr size_t smem = (size_t)TILE_BYTES * 7 + 128 + 1024;
+  constexpr size_t smem = (size_t)TILE_BYTES * 7 + 128 + 1024 + 1024;   // tiles, barriers, row-sum scratch, alignment slack
   static bool attr_done = false;
   if (!attr_done) {
     BONES_CHECK(cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attr_done = true;
   }
   dim3 grid(T / AT, H, B);
-  attn_fwd_kernel<<<grid, 192, smem, (cudaStream_t)stream>>>(tq, tv, p);
+  attn_fwd_kernel<<<grid, 320, smem, (cudaStream_t)stream>>>(tq, tv, p);
   return (int)cudaGetLastError();
 }
 }  // extern "C"

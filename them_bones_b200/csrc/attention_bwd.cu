@@ -187,17 +187,31 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
     const int c0 = half * 64;
     const float log2e = 1.4426950408889634f;
     bool ok = true;
+    // per-row statistics of the next query tile are fetched one iteration ahead so their latency hides behind the MMAs
+    float nx_lse2 = 0.f, nx_dlt = 0.f;
+    int nx_lo = 0;
+    if (n > 0) {
+      const int qpos0 = kt * BT + r;
+      const long long st0 = ((long long)b * p.H + h) * p.T + qpos0;
+      nx_lse2 = p.lse[st0] * log2e;
+      nx_dlt = p.delta[st0];
+      if (p.doc_start) nx_lo = p.doc_start[(long long)b * p.T + qpos0];
+    }
     for (int i = 0; i < n && ok; ++i) {
       const uint32_t ph = (uint32_t)(i & 1);
       const int qt = kt + i;
       const int qpos = qt * BT + r;
-      const long long stat = ((long long)b * p.H + h) * p.T + qpos;
-      const float lse2 = p.lse[stat] * log2e;
-      const float dlt = p.delta[stat];
-      int lo = 0;
-      if (p.doc_start) lo = p.doc_start[(long long)b * p.T + qpos];
+      const float lse2 = nx_lse2, dlt = nx_dlt;
+      const int lo = nx_lo;
+      if (i + 1 < n) {
+        const int qn = qpos + BT;
+        const long long stn = ((long long)b * p.H + h) * p.T + qn;
+        nx_lse2 = p.lse[stn] * log2e;
+        nx_dlt = p.delta[stn];
+        if (p.doc_start) nx_lo = p.doc_start[(long long)b * p.T + qn];
+      }
       const int k0 = kt * BT;
-      const bool need_mask = (i == 0) || (k0 < lo);
+      const bool need_mask = __any_sync(0xffffffffu, (i == 0) || (k0 + c0 < lo));
       float pr[64];
       // ---- P ----
       bool got = mbar_wait(bar(B_SFULL), ph, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
@@ -211,7 +225,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
-          float e = exp2f(__uint_as_float(v[j]) * p.c1 - lse2);
+          float e;
+          const float xx = fmaf(__uint_as_float(v[j]), p.c1, -lse2);
+          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(xx));
           if (need_mask) {
             const int kpos = k0 + c0 + c * 32 + j;
             if (kpos > qpos || kpos < lo) e = 0.f;
