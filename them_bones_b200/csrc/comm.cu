@@ -204,6 +204,27 @@ __global__ void peer_all_to_all_kernel(const uint4* __restrict__ src, PeerPtrs d
   reinterpret_cast<uint4*>(dst.p[d])[(long long)rank * chunk16 + j] = src[i];
 }
 
+// MoE dispatch fused with the expert-parallel exchange: slot s of the [E, b, C] slot buffer belongs to rank
+// d = s / rows_per_dest; its token row h[tok[s]] (or zeros for an empty slot) is stored straight into rank d's receive
+// buffer at [source rank][s % rows_per_dest]: the permute and the all-to-all are one pass over NVLink, and no local slot
+// buffer exists.  One warp per slot.
+__global__ void peer_dispatch_rows_kernel(const __nv_bfloat16* __restrict__ h, const long long* __restrict__ tok, PeerPtrs dst,
+                                          long long rows_per_dest, long long n_slots, long long n_tokens, int C, int rank) {
+  const long long s = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (s >= n_slots) return;
+  const int d = (int)(s / rows_per_dest);
+  const long long j = s - (long long)d * rows_per_dest;
+  const long long t = tok[s];
+  const bool valid = t >= 0 && t < n_tokens;
+  __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(dst.p[d]) + ((long long)rank * rows_per_dest + j) * C;
+  for (int c = lane * 8; c < C; c += 256) {
+    uint4 u = make_uint4(0, 0, 0, 0);
+    if (valid) u = *reinterpret_cast<const uint4*>(h + t * C + c);
+    *reinterpret_cast<uint4*>(out + c) = u;
+  }
+}
+
 static PeerPtrs make_ptrs(void* const* ptrs, int world) {
   PeerPtrs p;
   for (int i = 0; i < kMaxPeers; ++i) p.p[i] = i < world ? ptrs[i] : nullptr;
@@ -261,6 +282,14 @@ int bones_peer_publish(const float* src, void* const* w_ptrs, long long off, lon
 int bones_peer_gather_rows(void* const* table_ptrs, const long long* ids, void* out, int n, int C, int world, void* stream) {
   if (world > kMaxPeers || (C % 8)) return -2;
   peer_gather_rows_kernel<<<(n + 7) / 8, 256, 0, (cudaStream_t)stream>>>(make_ptrs(table_ptrs, world), ids, (__nv_bfloat16*)out, n, C, world);
+  return (int)cudaGetLastError();
+}
+
+int bones_peer_dispatch_rows(const void* h, const long long* tok, void* const* dst_ptrs, long long rows_per_dest, long long n_slots,
+                             long long n_tokens, int C, int rank, int world, void* stream) {
+  if (world > kMaxPeers || (C % 8)) return -2;
+  peer_dispatch_rows_kernel<<<(unsigned)((n_slots + 7) / 8), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)h, tok, make_ptrs(dst_ptrs, world),
+                                                                                           rows_per_dest, n_slots, n_tokens, C, rank);
   return (int)cudaGetLastError();
 }
 

@@ -172,6 +172,11 @@ def moe_combine(ys, slot, gates):
     return out
 
 
+def moe_dispatch_exchange(h, tok, group, world, n_exp):
+    from ..parallel import moe_a2a
+    return moe_a2a.dispatch_exchange(h, tok, group, world, n_exp)
+
+
 def moe_exchange(xs, group, world, n_exp, forward=True):
     from ..parallel import moe_a2a
     return moe_a2a.exchange(xs, group, world, n_exp, forward)

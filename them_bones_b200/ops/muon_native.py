@@ -19,6 +19,9 @@ def newton_schulz(x: torch.Tensor, steps: int = 5) -> torch.Tensor:
     """``x [k, r, c]`` bf16, Frobenius-normalised.  Returns the orthogonalised stack (bf16, new tensor)."""
     assert x.dtype == torch.bfloat16 and x.is_contiguous()
     k, r, c = x.shape
+    if r % 8 or c % 8:       # tiny matrices (a 16 x d router): not worth a tensor-core tile, and below the TMA alignment
+        from ..ref.functional import newton_schulz as ns_ref
+        return ns_ref(x, steps)
     tall = r > c
     n = c if tall else r
     g = torch.empty(k, n, n, dtype=torch.bfloat16, device=x.device)

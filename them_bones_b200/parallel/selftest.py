@@ -86,6 +86,28 @@ def main():
         print(f"peer a2a equals NCCL all_to_all: {a2a_ok}; max abs diff {float((got.float() - ref.float()).abs().max()):.3e}")
     if not a2a_ok:
         ok = False
+    # MoE (expert parallel, fused dispatch + peer all-to-all) and hashed tables (peer row gather) against NCCL
+    from them_bones_b200.parallel import moe_a2a
+    mcfg = GPTConfig(sequence_len=256, vocab_size=4096, n_layer=2, n_head=2, n_embd=256, head_dim=128, doc_mask=True,
+                     moe_layers=(1,), moe_experts=2 * w, moe_topk=2, moe_capacity=64, moe_hidden=256,
+                     table_orders=(2, 3), table_rows=1 << 14)
+    mres = {}
+    for name, fused in (("nccl", False), ("fused", True)):
+        moe_a2a.install_fused(None)
+        tr2 = Trainer(mcfg, hy, rt, fused_comm=fused, horizon_steps=10)
+        ld = SynthLoader(mcfg.vocab_size, 256, tr2.local_windows, rank=rt.rank, seed=5, doc_len=(32, 256), pin=True)
+        ls = []
+        for _ in range(3):
+            x, y = ld.next_step()
+            ls.append(float(tr2.train_step(x, y)))
+        torch.cuda.synchronize()
+        L.check_error_word()
+        mres[name] = ls
+    moe_ok = all(abs(a - b) <= 2e-2 * abs(a) for a, b in zip(mres["nccl"], mres["fused"]))
+    if rt.rank == 0:
+        print(f"moe+tables losses nccl {mres['nccl']} fused {mres['fused']} ok {moe_ok}")
+    if not moe_ok:
+        ok = False
     flag = torch.tensor([int(ok)], device=rt.device)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     L.check_error_word()

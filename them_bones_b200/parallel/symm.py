@@ -182,6 +182,38 @@ class PeerMoeExchange:
     def exchange(self, xs, world, m, forward):
         return _PeerA2A.apply(xs, self, world, m, forward)
 
+    def dispatch(self, h, tok, world, m):
+        """Permute + exchange in one kernel: token rows go straight into the owning rank's expert buffer."""
+        return _PeerDispatch.apply(h, tok, self, world, m)
+
+
+class _PeerDispatch(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, h, tok, ex, world, m):
+        comm = ex.comm
+        h = h.contiguous()
+        n_slots, d = tok.numel(), h.shape[1]
+        recv = ex._recv(n_slots * d, h.dtype, "disp")
+        comm.barrier()
+        L.call("bones_peer_dispatch_rows", L.ptr(h), L.ptr(tok), comm.peers(recv), _L(n_slots // world), _L(n_slots),
+               _L(h.shape[0]), _I(d), _I(comm.rank), _I(world), L.stream())
+        comm.barrier()
+        comm.launches += 1
+        ctx.save_for_backward(tok)
+        ctx.ex, ctx.world, ctx.m, ctx.n = ex, world, m, h.shape[0]
+        ys = recv.view(n_slots, d).clone()                                  # [W(src), m, bC, d]
+        return ys.view(world, m, -1, d).transpose(0, 1).reshape(-1, d)      # [m, W*bC, d]
+
+    @staticmethod
+    def backward(ctx, g):
+        (tok,) = ctx.saved_tensors
+        ex, world, m, d = ctx.ex, ctx.world, ctx.m, g.shape[-1]
+        back = g.reshape(m, world, -1, d).transpose(0, 1).reshape(-1, d)
+        dxs = ex._a2a(back, "gdisp")                                        # gradients of my slots
+        dh = torch.zeros(ctx.n + 1, d, dtype=torch.float32, device=g.device)
+        dh.index_add_(0, tok, dxs.float())
+        return dh[:ctx.n].to(g.dtype), None, None, None, None
+
 
 class _PeerA2A(torch.autograd.Function):
     @staticmethod
