@@ -100,3 +100,20 @@ def test_logits_and_eval_loss_match():
         ops.set_reference_path(False)
         b, lb = model(x), model(x, y, loss_reduction="none")
     assert _rel(b, a) < 2e-2 and _rel(lb, la) < 2e-2
+
+
+def test_bounded_peer_wait_expires_with_an_error_code():
+    """A peer flag that nothing ever sets: the barrier kernel gives up after its (short) limit, records the error code in
+    the host-visible word and returns; the context stays usable."""
+    import ctypes
+    from them_bones_b200.ops import _lib as L
+    flags = torch.zeros(64, dtype=torch.int32, device="cuda")
+    ptrs = (ctypes.c_void_p * 2)(ctypes.c_void_p(flags.data_ptr()), ctypes.c_void_p(flags.data_ptr()))
+    # "rank 0 of 2": it publishes slot 0 itself, but slot 1 would have to come from the absent peer
+    L.call("bones_peer_barrier", ptrs, ctypes.c_int(0), ctypes.c_int(2), ctypes.c_int(1), ctypes.c_double(0.2), L.stream())
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="error code 5"):
+        L.check_error_word()
+    L.check_error_word()                                   # cleared: the next check passes
+    x = torch.ones(8, device="cuda")
+    assert float(x.sum()) == 8.0                           # the CUDA context is intact

@@ -151,6 +151,125 @@ __global__ void rope_qknorm_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, co
   }
 }
 
+// head_dim 128 fast paths: eight lanes per head vector (16-byte accesses: elements [8 l, 8 l + 8) of the first half and
+// their rotate-half partners in the second half), four head vectors per warp, reductions over the 8-lane group.
+__device__ __forceinline__ void ld8_bf16(const __nv_bfloat16* p, float* f) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const float2 v = unpack_bf16(w[t]);
+    f[2 * t] = v.x;
+    f[2 * t + 1] = v.y;
+  }
+}
+__device__ __forceinline__ void st8_bf16(__nv_bfloat16* p, const float* f) {
+  uint4 u;
+  u.x = pack_bf16(f[0], f[1]); u.y = pack_bf16(f[2], f[3]); u.z = pack_bf16(f[4], f[5]); u.w = pack_bf16(f[6], f[7]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+__device__ __forceinline__ void ld8_f32(const float* p, float* f) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+__device__ __forceinline__ float group8_sum(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  v += __shfl_xor_sync(0xffffffffu, v, 2);
+  v += __shfl_xor_sync(0xffffffffu, v, 4);
+  return v;
+}
+
+__global__ void rope_qknorm_fwd128_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ cosT,
+                                          const float* __restrict__ sinT, __nv_bfloat16* __restrict__ qk, long long M, int T, int H) {
+  const long long item = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 3;     // (row, q|k, head)
+  const int l8 = threadIdx.x & 7;
+  const long long total = M * 2 * H;
+  const bool live = item < total;
+  const long long it = live ? item : total - 1;
+  const int h = (int)(it % H), which = (int)((it / H) % 2);
+  const long long row = it / (2 * H);
+  const int t = (int)(row % T);
+  const long long A = (long long)H * 128;
+  const __nv_bfloat16* src = qkv + row * 3 * A + which * A + (long long)h * 128 + l8 * 8;
+  float x1[8], x2[8], cs[8], sn[8], y1[8], y2[8];
+  ld8_bf16(src, x1);
+  ld8_bf16(src + 64, x2);
+  ld8_f32(cosT + (long long)t * 64 + l8 * 8, cs);
+  ld8_f32(sinT + (long long)t * 64 + l8 * 8, sn);
+  float ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    y1[e] = x1[e] * cs[e] + x2[e] * sn[e];
+    y2[e] = -x1[e] * sn[e] + x2[e] * cs[e];
+    ss += y1[e] * y1[e] + y2[e] * y2[e];
+  }
+  ss = group8_sum(ss);
+  const float r = rsqrtf(ss * (1.0f / 128.0f) + kQkEps);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) { y1[e] *= r; y2[e] *= r; }
+  if (live) {
+    __nv_bfloat16* dst = qk + row * 2 * A + which * A + (long long)h * 128 + l8 * 8;
+    st8_bf16(dst, y1);
+    st8_bf16(dst + 64, y2);
+  }
+}
+
+__global__ void rope_qknorm_bwd128_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ cosT,
+                                          const float* __restrict__ sinT, const float* __restrict__ dqk,
+                                          const __nv_bfloat16* __restrict__ dv, __nv_bfloat16* __restrict__ dqkv, long long M, int T,
+                                          int H) {
+  const long long item = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 3;     // (row, q|k|v, head)
+  const int l8 = threadIdx.x & 7;
+  const long long total = M * 3 * H;
+  const bool live = item < total;
+  const long long it = live ? item : total - 1;
+  const int h = (int)(it % H), which = (int)((it / H) % 3);
+  const long long row = it / (3 * H);
+  const long long A = (long long)H * 128;
+  __nv_bfloat16* out = dqkv + row * 3 * A + which * A + (long long)h * 128 + l8 * 8;
+  // `which` is uniform over each 8-lane group but may differ inside a warp; the shuffles below are executed by all lanes
+  const int t = (int)(row % T);
+  const bool is_v = which == 2;
+  const int wq = is_v ? 0 : which;
+  const __nv_bfloat16* src = qkv + row * 3 * A + wq * A + (long long)h * 128 + l8 * 8;
+  const float* g = dqk + row * 2 * A + wq * A + (long long)h * 128 + l8 * 8;
+  float x1[8], x2[8], cs[8], sn[8], g1[8], g2[8], y1[8], y2[8];
+  ld8_bf16(src, x1);
+  ld8_bf16(src + 64, x2);
+  ld8_f32(cosT + (long long)t * 64 + l8 * 8, cs);
+  ld8_f32(sinT + (long long)t * 64 + l8 * 8, sn);
+  ld8_f32(g, g1);
+  ld8_f32(g + 64, g2);
+  float ss = 0.f, dot = 0.f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    y1[e] = x1[e] * cs[e] + x2[e] * sn[e];
+    y2[e] = -x1[e] * sn[e] + x2[e] * cs[e];
+    ss += y1[e] * y1[e] + y2[e] * y2[e];
+    dot += y1[e] * g1[e] + y2[e] * g2[e];
+  }
+  ss = group8_sum(ss);
+  dot = group8_sum(dot);
+  const float r = rsqrtf(ss * (1.0f / 128.0f) + kQkEps);
+  const float m = dot * r * r * (1.0f / 128.0f);
+  float o1[8], o2[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float du1 = r * (g1[e] - y1[e] * m), du2 = r * (g2[e] - y2[e] * m);
+    o1[e] = du1 * cs[e] - du2 * sn[e];
+    o2[e] = du1 * sn[e] + du2 * cs[e];
+  }
+  if (!live) return;
+  if (is_v) {
+    const __nv_bfloat16* gv = dv + row * A + (long long)h * 128 + l8 * 8;
+    *reinterpret_cast<uint4*>(out) = *reinterpret_cast<const uint4*>(gv);
+    *reinterpret_cast<uint4*>(out + 64) = *reinterpret_cast<const uint4*>(gv + 64);
+  } else {
+    st8_bf16(out, o1);
+    st8_bf16(out + 64, o2);
+  }
+}
+
 // ---------------------------------------------------------------------------------------------------------------
 // forward attention, head_dim 128
 // ---------------------------------------------------------------------------------------------------------------
@@ -399,8 +518,11 @@ using namespace bones;
 int bones_rope_qknorm_fwd(const void* qkv, const float* cosT, const float* sinT, void* qk, long long M, int T, int H, int D, void* stream) {
   const long long warps = M * H * 2;
   const unsigned grid = (unsigned)((warps + 7) / 8);
-  if (D == 128)
-    rope_qknorm_fwd_kernel<128><<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)qkv, cosT, sinT, (__nv_bfloat16*)qk, M, T, H);
+  if (D == 128) {
+    const long long threads = M * 2 * H * 8;
+    rope_qknorm_fwd128_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)qkv, cosT, sinT,
+                                                                                                   (__nv_bfloat16*)qk, M, T, H);
+  }
   else if (D == 64)
     rope_qknorm_fwd_kernel<64><<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)qkv, cosT, sinT, (__nv_bfloat16*)qk, M, T, H);
   else
@@ -412,9 +534,11 @@ int bones_rope_qknorm_bwd(const void* qkv, const float* cosT, const float* sinT,
                           int T, int H, int D, void* stream) {
   const long long warps = M * H * 3;
   const unsigned grid = (unsigned)((warps + 7) / 8);
-  if (D == 128)
-    rope_qknorm_bwd_kernel<128><<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)qkv, cosT, sinT, dqk, (const __nv_bfloat16*)dv,
-                                                                     (__nv_bfloat16*)dqkv, M, T, H);
+  if (D == 128) {
+    const long long threads = M * 3 * H * 8;
+    rope_qknorm_bwd128_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)qkv, cosT, sinT, dqk, (const __nv_bfloat16*)dv, (__nv_bfloat16*)dqkv, M, T, H);
+  }
   else if (D == 64)
     rope_qknorm_bwd_kernel<64><<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)qkv, cosT, sinT, dqk, (const __nv_bfloat16*)dv,
                                                                     (__nv_bfloat16*)dqkv, M, T, H);

@@ -84,6 +84,9 @@ __global__ void rs_muon_prep_kernel(PeerPtrs G, long long off, long long n, int 
     }
     s.x *= scale; s.y *= scale; s.z *= scale; s.w *= scale;
     lg = s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
+    // finiteness gate: a non-finite reduced gradient contributes nothing to the update (lg still records it)
+    if (!isfinite(lg)) s = make_float4(isfinite(s.x) ? s.x : 0.f, isfinite(s.y) ? s.y : 0.f, isfinite(s.z) ? s.z : 0.f,
+                                       isfinite(s.w) ? s.w : 0.f);
     float4 m = *reinterpret_cast<float4*>(mom + i4);
     m.x += (1.f - mu) * (s.x - m.x); m.y += (1.f - mu) * (s.y - m.y);
     m.z += (1.f - mu) * (s.z - m.z); m.w += (1.f - mu) * (s.w - m.w);
@@ -149,6 +152,7 @@ __global__ void rs_adamw_publish_kernel(PeerPtrs G, PeerPtrs Wt, long long off, 
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
       lg += g[t] * g[t];
+      if (!isfinite(g[t])) g[t] = 0.f;       // finiteness gate (lg keeps the evidence)
       pp[t] *= 1.0f - lr * wd;
       aa[t] += (1.0f - b1) * (g[t] - aa[t]);
       bb[t] += (1.0f - b2) * (g[t] * g[t] - bb[t]);
@@ -163,7 +167,7 @@ __global__ void rs_adamw_publish_kernel(PeerPtrs G, PeerPtrs Wt, long long off, 
     for (int r = 0; r < world; ++r) *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(Wt.p[r]) + off + i4) = o;
   }
   lg = warp_sum(lg);
-  if ((threadIdx.x & 31) == 0 && lg != 0.f) atomicAdd(gsq, lg);
+  if ((threadIdx.x & 31) == 0 && !(lg == 0.f)) atomicAdd(gsq, lg);
 }
 
 // Publish: bf16(src[i]) stored into every rank's weight slab at off + i (src fp32 master of the owned chunk).

@@ -273,6 +273,8 @@ class LeanDistMuonAdamW(torch.optim.Optimizer):
             comm.fused_muon(u, self.steps, self._ns(u.W))
         self._local.step(1.0 / self.world)
         comm.post_step()                                  # every peer's stores into my slabs have landed
+        self._gsq_history = getattr(self, "_gsq_history", [])
+        self._gsq_history.append(comm.gsq.clone())        # read lazily: no host synchronisation in the step
         if self.overlap_check and self.steps == 2:
             self.check_mismatches += comm.cross_check(self)
 
@@ -298,6 +300,15 @@ class LeanDistMuonAdamW(torch.optim.Optimizer):
             self._gather_full(full, u.master)
             out[u.p] = full
         return out
+
+    def count_bad_steps(self) -> int:
+        """Steps whose reduced gradient held a non-finite value (the fused kernels zeroed those entries).  Synchronises;
+        call at a step boundary that synchronises anyway."""
+        hist = getattr(self, "_gsq_history", [])
+        if hist:
+            self.bad_steps += int((~torch.isfinite(torch.stack(hist))).sum())
+            self._gsq_history = []
+        return self.bad_steps
 
     def describe(self) -> str:
         mu = ", ".join(f"{u.n}x[{u.r},{u.c}] (k={u.k})" for u in self.muon_units)
