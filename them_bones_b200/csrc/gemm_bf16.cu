@@ -40,6 +40,7 @@ struct GemmParams {
   long long ldr, strideR;
   int* err;
   int tiles_m, tiles_n;
+  int wide;            // rows are 32-byte aligned: use 256-bit global accesses in the epilogue
   int splits;          // split-K factor (> 1 only with EPI_ACC_F32: partial tiles are added with vector atomics)
 };
 
@@ -204,9 +205,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
           const __nv_bfloat16* R = reinterpret_cast<const __nv_bfloat16*>(p.R) + rrow + col0;
           if (fullc) {
             if (p.epi == EPI_BF16_RES || p.epi == EPI_MUL_2SQRT) {
+              uint4 rr[4];
+              if (p.wide) {
+                ld_global_v8(R, rr[0], rr[1]);
+                ld_global_v8(R + 16, rr[2], rr[3]);
+              } else {
+                for (int j = 0; j < 4; ++j) rr[j] = *reinterpret_cast<const uint4*>(R + j * 8);
+              }
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
-                const uint4 u = *reinterpret_cast<const uint4*>(R + j * 8);
+                const uint4 u = rr[j];
                 const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
                 for (int t = 0; t < 4; ++t) {
@@ -227,14 +235,20 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
                 v[j] = t * t;
               }
             }
+            uint4 uu[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              uint4 u;
-              u.x = pack_bf16(v[j * 8 + 0], v[j * 8 + 1]);
-              u.y = pack_bf16(v[j * 8 + 2], v[j * 8 + 3]);
-              u.z = pack_bf16(v[j * 8 + 4], v[j * 8 + 5]);
-              u.w = pack_bf16(v[j * 8 + 6], v[j * 8 + 7]);
-              *reinterpret_cast<uint4*>(D + j * 8) = u;
+              uu[j].x = pack_bf16(v[j * 8 + 0], v[j * 8 + 1]);
+              uu[j].y = pack_bf16(v[j * 8 + 2], v[j * 8 + 3]);
+              uu[j].z = pack_bf16(v[j * 8 + 4], v[j * 8 + 5]);
+              uu[j].w = pack_bf16(v[j * 8 + 6], v[j * 8 + 7]);
+            }
+            if (p.wide) {      // one full 32-byte sector per store
+              st_global_v8(D, uu[0], uu[1]);
+              st_global_v8(D + 16, uu[2], uu[3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(D + j * 8) = uu[j];
             }
           } else {
             for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
@@ -374,6 +388,7 @@ int bones_gemm_bf16(const void* A, const void* B, void* D, const void* R, int M,
   p.D = D; p.ldd = ldd; p.strideD = strideD;
   p.R = R ? R : D; p.ldr = R ? ldr : ldd; p.strideR = R ? strideR : strideD;
   p.err = error_word();
+  p.wide = (!f32out && (ldd % 16 == 0) && (!R || ldr % 16 == 0) && (((uintptr_t)D & 31) == 0) && (!R || ((uintptr_t)R & 31) == 0)) ? 1 : 0;
   p.splits = splits;
   CUtensorMap ta, tb;
   int rc = operand_tmap(&ta, A, a_major, M, K, lda, strideA, batch, BM);

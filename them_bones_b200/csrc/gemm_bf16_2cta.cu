@@ -15,7 +15,7 @@
 //   MMA thread (leader only)    waits `full[s]`, issues the pair MMAs, commits with `.multicast::cluster` so `empty[s]`
 //                               (and at the end of a tile `tmem_full[a]`) fire in both CTAs
 //   epilogue warps (each CTA)   wait their own `tmem_full[a]`, drain their 128 rows, arrive on the leader's
-//                               `tmem_empty[a]` (8 warp arrivals per tile)
+//                               `tmem_empty[a]` (16 warp arrivals per tile)
 #include <cooperative_groups.h>
 
 #include "common.cuh"
@@ -36,6 +36,7 @@ struct Gemm2Params {
   int* err;
   int tiles_m, tiles_n;
   int splits;
+  int wide;            // rows are 32-byte aligned: use 256-bit global accesses in the epilogue
 };
 
 constexpr int PM = 256;      // pair tile M (128 per CTA)
@@ -103,7 +104,7 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
                : "memory");
 }
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const Gemm2Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -129,7 +130,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull(a), 1);       // one multicast commit
-      mbar_init(tempty(a), 8);      // leader: 4 epilogue warps of each CTA
+      mbar_init(tempty(a), 16);     // leader: 8 epilogue warps of each CTA
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -216,21 +217,39 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       }
     }
   } else {
-    const int q = warp & 3;
+    // eight epilogue warps: two per 32-lane TMEM quadrant, each draining four of the tile's eight 32-column chunks
+    const int q = warp & 3, half = (warp - 2) >> 2;
+    const bool need_r = p.epi == E2_BF16_RES || p.epi == E2_MUL_2SQRT;
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int tile = cluster_id; tile < total; tile += n_clusters) {
       int b, mb, nb;
       decode_tile2(tile / p.splits, p.tiles_m, p.tiles_n, b, mb, nb);
-      const bool got = mbar_wait(tfull(acc), acc_phase, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
-      if (!__all_sync(0xffffffffu, got)) break;
-      tc_fence_after();
       const int row = mb * PM + (int)rank * 128 + q * 32 + lane;
       const bool row_ok = row < p.M;
       const long long drow = (long long)b * p.strideD + (long long)row * p.ldd;
       const long long rrow = (long long)b * p.strideR + (long long)row * p.ldr;
-#pragma unroll 1
-      for (int c = 0; c < PN / 32; ++c) {
+      // the residual / auxiliary operand of this thread's four chunks is fetched before the accumulator is awaited, so
+      // its latency hides behind the tile's MMAs
+      uint4 rpre[4][4];
+      const bool pre = need_r && p.wide && row_ok;
+      if (pre) {
+#pragma unroll
+        for (int cc = 0; cc < 4; ++cc) {
+          const int col0 = nb * PN + (half * 4 + cc) * 32;
+          if (col0 + 32 <= p.N) {
+            const __nv_bfloat16* R = reinterpret_cast<const __nv_bfloat16*>(p.R) + rrow + col0;
+            ld_global_v8(R, rpre[cc][0], rpre[cc][1]);
+            ld_global_v8(R + 16, rpre[cc][2], rpre[cc][3]);
+          }
+        }
+      }
+      const bool got = mbar_wait(tfull(acc), acc_phase, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
+      if (!__all_sync(0xffffffffu, got)) break;
+      tc_fence_after();
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        const int c = half * 4 + cc;
         uint32_t r[32];
         const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * PN + c * 32);
         __syncwarp();
@@ -247,9 +266,16 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
             const __nv_bfloat16* R = reinterpret_cast<const __nv_bfloat16*>(p.R) + rrow + col0;
             if (fullc) {
               if (p.epi == E2_BF16_RES || p.epi == E2_MUL_2SQRT) {
+                uint4 rr[4];
+                if (pre) {
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) rr[j] = rpre[cc][j];
+                } else {
+                  for (int j = 0; j < 4; ++j) rr[j] = *reinterpret_cast<const uint4*>(R + j * 8);
+                }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                  const uint4 u = *reinterpret_cast<const uint4*>(R + j * 8);
+                  const uint4 u = rr[j];
                   const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
                   for (int t = 0; t < 4; ++t) {
@@ -270,14 +296,20 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
                   v[j] = t * t;
                 }
               }
+              uint4 uu[4];
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
-                uint4 u;
-                u.x = pack_bf16(v[j * 8 + 0], v[j * 8 + 1]);
-                u.y = pack_bf16(v[j * 8 + 2], v[j * 8 + 3]);
-                u.z = pack_bf16(v[j * 8 + 4], v[j * 8 + 5]);
-                u.w = pack_bf16(v[j * 8 + 6], v[j * 8 + 7]);
-                *reinterpret_cast<uint4*>(D + j * 8) = u;
+                uu[j].x = pack_bf16(v[j * 8 + 0], v[j * 8 + 1]);
+                uu[j].y = pack_bf16(v[j * 8 + 2], v[j * 8 + 3]);
+                uu[j].z = pack_bf16(v[j * 8 + 4], v[j * 8 + 5]);
+                uu[j].w = pack_bf16(v[j * 8 + 6], v[j * 8 + 7]);
+              }
+              if (p.wide) {      // one full 32-byte sector per store
+                st_global_v8(D, uu[0], uu[1]);
+                st_global_v8(D + 16, uu[2], uu[3]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(D + j * 8) = uu[j];
               }
             } else {
               for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
@@ -378,6 +410,7 @@ int bones_gemm_bf16_pair(const void* A, const void* B, void* D, const void* R, i
   p.D = D; p.ldd = ldd; p.strideD = strideD;
   p.R = R ? R : D; p.ldr = R ? ldr : ldd; p.strideR = R ? strideR : strideD;
   p.err = error_word();
+  p.wide = (!f32out && (ldd % 16 == 0) && (!R || ldr % 16 == 0) && (((uintptr_t)D & 31) == 0) && (!R || ((uintptr_t)R & 31) == 0)) ? 1 : 0;
   p.tiles_m = (M + PM - 1) / PM;
   p.tiles_n = (N + PN - 1) / PN;
   CUtensorMap ta, tb;
@@ -414,7 +447,7 @@ int bones_gemm_bf16_pair(const void* A, const void* B, void* D, const void* R, i
   if (p.splits > 1 && epi != E2_ACC_F32) p.splits = 1;
   const int total = base_tiles * p.splits;
   const int clusters = total < pairs ? total : pairs;
-  gemm_bf16_pair_kernel<<<2 * clusters, 192, smem, reinterpret_cast<cudaStream_t>(stream)>>>(ta, tb, p);
+  gemm_bf16_pair_kernel<<<2 * clusters, 320, smem, reinterpret_cast<cudaStream_t>(stream)>>>(ta, tb, p);
   return (int)cudaGetLastError();
 }
 
