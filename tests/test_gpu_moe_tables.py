@@ -88,3 +88,18 @@ def test_native_newton_schulz_matches_reference():
         torch.cuda.synchronize()
         L.check_error_word()
         assert _rel(got, ref) < 5e-2, (shape, _rel(got, ref))
+
+
+def test_native_slotting_matches_reference():
+    from them_bones_b200.ops import cuda as C
+    from them_bones_b200.ref import functional as RF
+    torch.manual_seed(3)
+    for (b, t, e, k, cap) in ((3, 512, 16, 2, 40), (2, 2048, 16, 2, 320), (4, 300, 8, 1, 20)):
+        logits = torch.randn(b * t, e, device="cuda")
+        _, idx, _ = RF.moe_route(logits, k)
+        slot_r, tok_r = RF.moe_slots(idx, b, t, e, cap)
+        slot_n, tok_n = C.moe_slots(idx, b, t, e, cap)
+        torch.cuda.synchronize()
+        assert torch.equal(slot_n, slot_r) and torch.equal(tok_n, tok_r), (b, t, e, k, cap)
+        if cap <= 40:
+            assert (slot_r == e * b * cap).any()                # some assignments were dropped: the cap was exercised

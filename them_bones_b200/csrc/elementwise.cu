@@ -234,6 +234,94 @@ __global__ void moe_combine_kernel(const __nv_bfloat16* ys, const long long* slo
   }
 }
 
+
+// Causal per-sequence capacity slotting (MoE).  One CTA per sequence.  idx [b*t, k] holds each token's expert choices
+// (distinct per token).  The position of an assignment is the number of assignments to the same expert at earlier
+// tokens of the sequence; positions >= cap are dropped.  Outputs: slot [b*t, k] (index into the [E, b, cap] buffer, or
+// E*b*cap when dropped) and tok [E*b*cap] (token in each slot, or b*t when empty).
+// Reference semantics: moe_positions / moe_gather_tables (round2/source/train.py:10555-10636), there as tril matmuls.
+constexpr int kSlotThreads = 256;
+constexpr int kMaxExperts = 64;
+__global__ void moe_slots_kernel(const long long* __restrict__ idx, long long* __restrict__ slot, long long* __restrict__ tok, int b, int t,
+                                 int k, int n_exp, int cap) {
+  __shared__ unsigned short cnt[kMaxExperts][kSlotThreads];
+  const int row = blockIdx.x, tid = threadIdx.x;
+  const int per = (t + kSlotThreads - 1) / kSlotThreads;
+  const int t0 = tid * per, t1 = min(t, t0 + per);
+  const long long n = (long long)b * t, total = (long long)n_exp * b * cap;
+  for (int e = 0; e < n_exp; ++e) cnt[e][tid] = 0;
+  // empty slots of this sequence
+  for (int i = tid; i < n_exp * cap; i += kSlotThreads) {
+    const int e = i / cap, c = i - e * cap;
+    tok[((long long)e * b + row) * cap + c] = n;
+  }
+  for (int tt = t0; tt < t1; ++tt)
+    for (int j = 0; j < k; ++j) cnt[(int)idx[((long long)row * t + tt) * k + j]][tid] += 1;
+  __syncthreads();
+  // exclusive scan over the 256 chunk counts of each expert: one warp per expert at a time
+  const int warp = tid >> 5, lane = tid & 31;
+  for (int e = warp; e < n_exp; e += kSlotThreads / 32) {
+    int v[8], sum = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { v[i] = cnt[e][lane * 8 + i]; sum += v[i]; }
+    int incl = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += y;
+    }
+    int run = incl - sum;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { cnt[e][lane * 8 + i] = (unsigned short)min(run, 65535); run += v[i]; }
+  }
+  __syncthreads();
+  for (int tt = t0; tt < t1; ++tt) {
+    const long long token = (long long)row * t + tt;
+    for (int j = 0; j < k; ++j) {
+      const int e = (int)idx[token * k + j];
+      const int pos = cnt[e][tid];
+      cnt[e][tid] = (unsigned short)min(pos + 1, 65535);
+      long long s = total;
+      if (pos < cap) {
+        s = ((long long)e * b + row) * cap + pos;
+        tok[s] = token;
+      }
+      slot[token * k + j] = s;
+    }
+  }
+}
+
+// Backward of the gate-weighted combine: dys[slot[n,k]] = gates[n,k] * dout[n] (slots are unique; empty slots stay at
+// the zero the caller wrote) and dgates[n,k] = <ys[slot[n,k]], dout[n]>.  One warp per token.
+__global__ void moe_combine_bwd_kernel(const __nv_bfloat16* __restrict__ ys, const long long* __restrict__ slot, const float* __restrict__ gates,
+                                       const __nv_bfloat16* __restrict__ dout, __nv_bfloat16* __restrict__ dys, float* __restrict__ dgates,
+                                       int n, int C, int topk, long long S) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= n) return;
+  for (int kk = 0; kk < topk; ++kk) {
+    const long long s = slot[(size_t)row * topk + kk];
+    float acc = 0.f;
+    if (s >= 0 && s < S) {
+      const float g = gates[(size_t)row * topk + kk];
+      for (int c = lane * 8; c < C; c += 256) {
+        const uint4 uy = *reinterpret_cast<const uint4*>(ys + (size_t)s * C + c);
+        const uint4 ud = *reinterpret_cast<const uint4*>(dout + (size_t)row * C + c);
+        const uint32_t wy[4] = {uy.x, uy.y, uy.z, uy.w}, wd[4] = {ud.x, ud.y, ud.z, ud.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 fy = unpack_bf16(wy[i]), fd = unpack_bf16(wd[i]);
+          acc += fy.x * fd.x + fy.y * fd.y;
+          o[i] = pack_bf16(g * fd.x, g * fd.y);
+        }
+        *reinterpret_cast<uint4*>(dys + (size_t)s * C + c) = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) dgates[(size_t)row * topk + kk] = acc;
+  }
+}
+
 // Softcap cross-entropy over full rows of bf16 logits [M, ldl] (first V columns valid), one CTA per row.
 //   z = cap * tanh(l / cap);  lse = log sum exp z;  nll = lse - z[target]
 // Outputs: nll[row] (0 where target < 0).  With `dlogits` (may alias logits) the gradient of
@@ -396,6 +484,18 @@ int bones_scatter_add_rows(const void* dy, const void* idx, int idx_is_64, float
 int bones_moe_combine(const void* ys, const long long* slot, const float* gates, void* out, int n, int C, int topk, long long S, void* stream) {
   if (C % 8) return -2;
   moe_combine_kernel<<<ROW_GRID(n), 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)ys, slot, gates, (__nv_bfloat16*)out, n, C, topk, S);
+  return (int)cudaGetLastError();
+}
+int bones_moe_slots(const long long* idx, long long* slot, long long* tok, int b, int t, int k, int n_exp, int cap, void* stream) {
+  if (n_exp > kMaxExperts || t > 8 * kSlotThreads * 32) return -2;
+  moe_slots_kernel<<<b, kSlotThreads, 0, (cudaStream_t)stream>>>(idx, slot, tok, b, t, k, n_exp, cap);
+  return (int)cudaGetLastError();
+}
+int bones_moe_combine_bwd(const void* ys, const long long* slot, const float* gates, const void* dout, void* dys, float* dgates, int n, int C,
+                          int topk, long long S, void* stream) {
+  if (C % 8) return -2;
+  moe_combine_bwd_kernel<<<ROW_GRID(n), 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)ys, slot, gates, (const __nv_bfloat16*)dout,
+                                                                 (__nv_bfloat16*)dys, dgates, n, C, topk, S);
   return (int)cudaGetLastError();
 }
 int bones_softcap_ce(const void* logits, long long ldl, const long long* targets, int V, float cap, float* nll, void* dlogits,

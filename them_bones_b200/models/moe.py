@@ -111,9 +111,9 @@ class MoeMLP(nn.Module):
         h = xn.reshape(n, d)
         logits = F.linear(h.float(), self.router.float())
         p, idx, gates = RF.moe_route(logits, self.topk)
-        slot, tok = RF.moe_slots(idx, b, t, self.n_exp, self.cap)
+        slot, tok = ops.moe_slots(idx, b, t, self.n_exp, self.cap)
         # slot gather ([E*b*C, d], empty slots are zero rows) + exchange to the expert owners
-        xs = ops.moe_dispatch_exchange(h, tok, self.ep_group, self.ep_world, self.n_exp)
+        xs = ops.moe_dispatch_exchange(h, tok, self.ep_group, self.ep_world, self.n_exp, slot)
         ys = ops.moe_experts(xs, self.w_fc, self.w_proj, self.precision)   # rows grouped by local expert
         ys = ops.moe_exchange(ys, self.ep_group, self.ep_world, self.n_exp, forward=False)
         out = ops.moe_combine(ys, slot, gates)                            # [n, d]

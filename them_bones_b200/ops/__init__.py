@@ -153,10 +153,17 @@ def lmhead_loss(x, w, targets, vocab, cap, reduction="mean", row_weights=None, l
 
 
 # -- MoE ---------------------------------------------------------------------------------------------------------
-def moe_dispatch(h, tok):
+def moe_slots(idx, b, t, n_exp, cap):
+    """Causal per-sequence capacity slotting: ``(slot [n, k], token_of_slot [E*b*cap])``."""
+    if native(idx):
+        return _cuda().moe_slots(idx, b, t, n_exp, cap)
+    return RF.moe_slots(idx, b, t, n_exp, cap)
+
+
+def moe_dispatch(h, tok, slot=None):
     """Gather token rows into the slot buffer: ``xs[s] = h[tok[s]]`` and zero where ``tok[s] == n``."""
     if native(h):
-        return _cuda().moe_dispatch(h, tok)
+        return _cuda().moe_dispatch(h, tok, slot)
     hp = torch.cat([h, h.new_zeros(1, h.shape[1])])
     return hp.index_select(0, tok)
 
@@ -172,9 +179,9 @@ def moe_combine(ys, slot, gates):
     return out
 
 
-def moe_dispatch_exchange(h, tok, group, world, n_exp):
+def moe_dispatch_exchange(h, tok, group, world, n_exp, slot=None):
     from ..parallel import moe_a2a
-    return moe_a2a.dispatch_exchange(h, tok, group, world, n_exp)
+    return moe_a2a.dispatch_exchange(h, tok, group, world, n_exp, slot)
 
 
 def moe_exchange(xs, group, world, n_exp, forward=True):

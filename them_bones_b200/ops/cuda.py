@@ -334,28 +334,49 @@ def lmhead_logits(x, w, vocab, cap):
 
 
 # -- MoE -------------------------------------------------------------------------------------------------------------
+def moe_slots(idx, b, t, n_exp, cap):
+    """Native capacity slotting: ``idx [b*t, k]`` int64 -> ``(slot [b*t, k], tok [E*b*cap])``."""
+    n, k = idx.shape
+    idx = _c(idx)
+    slot = torch.empty(n, k, dtype=torch.int64, device=idx.device)
+    tok = torch.empty(n_exp * b * cap, dtype=torch.int64, device=idx.device)
+    L.call("bones_moe_slots", L.ptr(idx), L.ptr(slot), L.ptr(tok), _I(b), _I(t), _I(k), _I(n_exp), _I(cap), L.stream())
+    COUNTS["moe_slots"] += 1
+    return slot, tok
+
+
 class _DispatchFn(torch.autograd.Function):
+    """Forward: slot gather.  Backward: every token sums the gradients of its (at most k) slots -- the combine kernel
+    with unit gates -- so both directions are gathers (reference: ``MoeGatherRows``, round2/source/train.py:10637)."""
+
     @staticmethod
-    def forward(ctx, h, tok):
+    def forward(ctx, h, tok, slot):
         out = torch.empty(tok.numel(), h.shape[1], dtype=h.dtype, device=h.device)
         L.call("bones_gather_rows", L.ptr(h), L.ptr(tok), _I(1), L.ptr(out), _I(tok.numel()), _I(h.shape[1]),
                _L(h.shape[0]), L.stream())
-        ctx.save_for_backward(tok)
-        ctx.n = h.shape[0]
+        ctx.save_for_backward(tok, slot if slot is not None else tok)
+        ctx.n, ctx.has_slot = h.shape[0], slot is not None
         COUNTS["moe_dispatch"] += 1
         return out
 
     @staticmethod
     def backward(ctx, dxs):
-        (tok,) = ctx.saved_tensors
+        tok, slot = ctx.saved_tensors
+        dxs = _c(dxs)
+        if ctx.has_slot:
+            ones = torch.ones(slot.shape, dtype=torch.float32, device=dxs.device)
+            dh = torch.empty(ctx.n, dxs.shape[1], dtype=dxs.dtype, device=dxs.device)
+            L.call("bones_moe_combine", L.ptr(dxs), L.ptr(slot), L.ptr(ones), L.ptr(dh), _I(ctx.n), _I(dxs.shape[1]),
+                   _I(slot.shape[1]), _L(dxs.shape[0]), L.stream())
+            return dh, None, None
         g = torch.zeros(ctx.n, dxs.shape[1], dtype=torch.float32, device=dxs.device)
-        L.call("bones_scatter_add_rows", L.ptr(_c(dxs)), L.ptr(tok), _I(1), L.ptr(g), _I(tok.numel()), _I(dxs.shape[1]),
+        L.call("bones_scatter_add_rows", L.ptr(dxs), L.ptr(tok), _I(1), L.ptr(g), _I(tok.numel()), _I(dxs.shape[1]),
                _L(ctx.n), L.stream())
-        return g.to(dxs.dtype), None
+        return g.to(dxs.dtype), None, None
 
 
-def moe_dispatch(h, tok):
-    return _DispatchFn.apply(_c(h), _c(tok))
+def moe_dispatch(h, tok, slot=None):
+    return _DispatchFn.apply(_c(h), _c(tok), _c(slot) if slot is not None else None)
 
 
 class _CombineFn(torch.autograd.Function):
@@ -373,14 +394,12 @@ class _CombineFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dout):
         ys, slot, g32 = ctx.saved_tensors
-        s_total = ys.shape[0]
-        yp = torch.cat([ys, ys.new_zeros(1, ys.shape[1])])
-        dys = torch.zeros(s_total + 1, ys.shape[1], dtype=torch.float32, device=ys.device)
+        dout = _c(dout)
+        dys = torch.zeros_like(ys)
         dg = torch.empty_like(g32)
-        for k in range(slot.shape[1]):
-            dys.index_add_(0, slot[:, k], g32[:, k:k + 1] * dout.float())
-            dg[:, k] = (yp.index_select(0, slot[:, k]).float() * dout.float()).sum(-1)
-        return dys[:s_total].to(ys.dtype), None, dg
+        L.call("bones_moe_combine_bwd", L.ptr(ys), L.ptr(slot), L.ptr(g32), L.ptr(dout), L.ptr(dys), L.ptr(dg), _I(slot.shape[0]),
+               _I(ys.shape[1]), _I(slot.shape[1]), _L(ys.shape[0]), L.stream())
+        return dys, None, dg
 
 
 def moe_combine(ys, slot, gates):

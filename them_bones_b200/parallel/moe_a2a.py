@@ -53,10 +53,10 @@ def exchange(xs: torch.Tensor, group, world: int, n_exp: int, forward: bool) -> 
     return _AllToAll.apply(back, group)
 
 
-def dispatch_exchange(h: torch.Tensor, tok: torch.Tensor, group, world: int, n_exp: int) -> torch.Tensor:
+def dispatch_exchange(h: torch.Tensor, tok: torch.Tensor, group, world: int, n_exp: int, slot=None) -> torch.Tensor:
     """Slot gather + forward exchange.  With the fused transport installed this is one kernel (rows are stored straight
     into the destination rank's expert buffer); otherwise gather then all-to-all."""
     from .. import ops
     if world > 1 and _FUSED is not None and h.is_cuda and hasattr(_FUSED, "dispatch"):
         return _FUSED.dispatch(h, tok, world, n_exp // world)
-    return exchange(ops.moe_dispatch(h, tok), group, world, n_exp, True)
+    return exchange(ops.moe_dispatch(h, tok, slot), group, world, n_exp, True)
