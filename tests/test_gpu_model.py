@@ -117,3 +117,29 @@ def test_bounded_peer_wait_expires_with_an_error_code():
     L.check_error_word()                                   # cleared: the next check passes
     x = torch.ones(8, device="cuda")
     assert float(x.sum()) == 8.0                           # the CUDA context is intact
+
+
+@pytest.mark.parametrize("vocab,ld", [(65536, 65536), (50304, 50432), (8192, 8192)])
+def test_softcap_ce_row_kernel_matches_reference(vocab, ld):
+    """Loss-head kernel at full vocabulary width: per-row loss and the in-place logit gradient against fp32 PyTorch."""
+    from them_bones_b200.ops import _lib as L
+    from them_bones_b200.ops.cuda import _F, _I, _L
+    torch.manual_seed(1)
+    m, cap = 24, 15.0
+    lg = (torch.randn(m, ld, device="cuda") * 6).bfloat16()
+    tg = torch.randint(0, vocab, (m,), device="cuda")
+    tg[3] = -1
+    nll = torch.zeros(m, device="cuda")
+    n_valid = torch.tensor([float((tg >= 0).sum())], device="cuda")
+    lf = lg[:, :vocab].float().requires_grad_()
+    z = cap * torch.tanh(lf / cap)
+    ref_rows = torch.nn.functional.cross_entropy(z, tg, ignore_index=-1, reduction="none")
+    (ref_rows.sum() / n_valid[0]).backward()
+    d = lg.clone()
+    L.call("bones_softcap_ce", L.ptr(d), _L(ld), L.ptr(tg), _I(vocab), _F(cap), L.ptr(nll), L.ptr(d), L.ptr(None), L.ptr(n_valid),
+           _F(1.0), _I(m), L.stream())
+    torch.cuda.synchronize()
+    L.check_error_word()
+    assert float((nll - ref_rows).abs().max()) < 2e-2
+    assert _rel(d[:, :vocab], lf.grad) < 1.5e-2
+    assert float(d[:, vocab:].float().abs().sum()) == 0.0 and float(d[3].float().abs().sum()) == 0.0

@@ -8,6 +8,8 @@
 // Reference counterparts: block head `x' = l1*x + l2*x0; xn = rms(x')` (round1/source/train.py:5257-5301), rms pair
 // (:5378-5410), residual-mix backward with gain partial sums (round2/source/kernels/nki_resmix.py), embedding backward
 // (round2/source/train.py:5606-5658, there a one-hot contraction), chunked loss head (round2/source/train.py:5238-5297).
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 
 namespace bones {
@@ -174,6 +176,134 @@ __global__ void resid_mix_norm_bwd_kernel(const __nv_bfloat16* x, const __nv_bfl
     va = warp_sum(va);
     vb = warp_sum(vb);
     if (lane == 0) { atomicAdd(da, va); atomicAdd(db, vb); }
+  }
+}
+
+// Row kernels for C == NV * 256 that keep every operand packed (one uint4 per 8 columns) and issue all of a row's loads
+// before the first reduction: about half the registers of the generic kernels above, so two blocks fit per SM and
+// enough loads are in flight to keep DRAM busy.
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const float2 a = unpack_bf16(u.x), b = unpack_bf16(u.y), c = unpack_bf16(u.z), d = unpack_bf16(u.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 u;
+  u.x = pack_bf16(f[0], f[1]); u.y = pack_bf16(f[2], f[3]); u.z = pack_bf16(f[4], f[5]); u.w = pack_bf16(f[6], f[7]);
+  return u;
+}
+
+template <int NV>
+__global__ void __launch_bounds__(256, 2)
+rmsnorm_bwd_packed_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ add,
+                          __nv_bfloat16* __restrict__ dx, int M) {
+  constexpr int C = NV * 256;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (row >= M) return;
+  const size_t off = (size_t)row * C + lane * 8;
+  uint4 px[NV], pg[NV], pa[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) px[i] = *reinterpret_cast<const uint4*>(x + off + i * 256);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) pg[i] = *reinterpret_cast<const uint4*>(dy + off + i * 256);
+  if (add) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) pa[i] = *reinterpret_cast<const uint4*>(add + off + i * 256);
+  }
+  float ss = 0.f, dot = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    float fx[8], fg[8];
+    unpack8(px[i], fx);
+    unpack8(pg[i], fg);
+#pragma unroll
+    for (int t = 0; t < 8; ++t) { ss += fx[t] * fx[t]; dot += fx[t] * fg[t]; }
+  }
+  ss = warp_sum(ss);
+  dot = warp_sum(dot);
+  const float rstd = rsqrtf(ss / C + kRmsEps);
+  const float m = dot * rstd * rstd / C;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    float fx[8], fg[8], fa[8];
+    unpack8(px[i], fx);
+    unpack8(pg[i], fg);
+    if (add) unpack8(pa[i], fa);
+#pragma unroll
+    for (int t = 0; t < 8; ++t) {
+      float g = rstd * (fg[t] - fx[t] * m);
+      if (add) g += fa[t];
+      fg[t] = g;
+    }
+    *reinterpret_cast<uint4*>(dx + off + i * 256) = pack8(fg);
+  }
+}
+
+template <int NV>
+__global__ void __launch_bounds__(256, 2)
+resid_mix_norm_bwd_packed_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ x0,
+                                 const __nv_bfloat16* __restrict__ xm, const float* __restrict__ a, const float* __restrict__ b,
+                                 const __nv_bfloat16* __restrict__ dxm, const __nv_bfloat16* __restrict__ dxn,
+                                 __nv_bfloat16* __restrict__ dx, __nv_bfloat16* __restrict__ dx0, float* da, float* db, int M) {
+  constexpr int C = NV * 256;
+  __shared__ float s_da[8], s_db[8];
+  const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + wid;
+  float pa = 0.f, pb = 0.f;
+  if (row < M) {
+    const size_t off = (size_t)row * C + lane * 8;
+    uint4 pm[NV], pn[NV], pt[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) pm[i] = *reinterpret_cast<const uint4*>(xm + off + i * 256);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) pn[i] = *reinterpret_cast<const uint4*>(dxn + off + i * 256);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) pt[i] = *reinterpret_cast<const uint4*>(dxm + off + i * 256);
+    const float fa = *a, fb = *b;
+    float ss = 0.f, dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      float fm[8], fn[8];
+      unpack8(pm[i], fm);
+      unpack8(pn[i], fn);
+#pragma unroll
+      for (int t = 0; t < 8; ++t) { ss += fm[t] * fm[t]; dot += fm[t] * fn[t]; }
+    }
+    ss = warp_sum(ss);
+    dot = warp_sum(dot);
+    const float rstd = rsqrtf(ss / C + kRmsEps);
+    const float m = dot * rstd * rstd / C;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      // x and x0 are only needed from here on: fetched per vector, the other warps of the SM cover their latency
+      const uint4 px = *reinterpret_cast<const uint4*>(x + off + i * 256);
+      const uint4 p0 = *reinterpret_cast<const uint4*>(x0 + off + i * 256);
+      float fm[8], fn[8], ft[8], fx[8], f0[8], o[8];
+      unpack8(pm[i], fm);
+      unpack8(pn[i], fn);
+      unpack8(pt[i], ft);
+      unpack8(px, fx);
+      unpack8(p0, f0);
+#pragma unroll
+      for (int t = 0; t < 8; ++t) {
+        const float g = ft[t] + rstd * (fn[t] - fm[t] * m);
+        pa += g * fx[t];
+        pb += g * f0[t];
+        o[t] = fb * g;
+        fn[t] = fa * g;
+      }
+      *reinterpret_cast<uint4*>(dx0 + off + i * 256) = pack8(o);
+      *reinterpret_cast<uint4*>(dx + off + i * 256) = pack8(fn);
+    }
+    pa = warp_sum(pa);
+    pb = warp_sum(pb);
+  }
+  if (lane == 0) { s_da[wid] = pa; s_db[wid] = pb; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float va = 0.f, vb = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) { va += s_da[w]; vb += s_db[w]; }
+    atomicAdd(da, va);
+    atomicAdd(db, vb);
   }
 }
 
@@ -389,6 +519,88 @@ __global__ void softcap_ce_kernel(const __nv_bfloat16* logits, long long ldl, co
   for (int c = V + threadIdx.x; c < ldl; c += blockDim.x) d[c] = __float2bfloat16(0.f);
 }
 
+// Same contract for V <= 65536 with one 1024-thread block per row: the row is read once, tanh(l / cap) of the thread's 64
+// columns stays in registers as fp16 pairs between the two passes, and the transcendental work is three special-function
+// operations per element (tanh.approx, ex2 for the sum, ex2 for the probability) instead of two libm tanhf and two expf.
+// tanh.approx and fp16 storage both carry about 2^-11 relative error, below the bf16 rounding of the logits themselves.
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__global__ void __launch_bounds__(1024, 1)
+softcap_ce_row_kernel(const __nv_bfloat16* __restrict__ logits, long long ldl, const long long* __restrict__ targets, int V, float cap,
+                      float* __restrict__ nll, __nv_bfloat16* dlogits, const float* __restrict__ row_w, const float* __restrict__ n_valid,
+                      float inv_loss_div, int M) {
+  const int row = blockIdx.x;
+  if (row >= M) return;
+  const __nv_bfloat16* l = logits + (size_t)row * ldl;
+  const long long tgt = targets[row];
+  const float inv_cap = 1.0f / cap, k2 = cap * 1.4426950408889634f;
+  __shared__ float red[32];
+  __shared__ float s_total;
+  uint4 raw[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int c = (i * 1024 + threadIdx.x) * 8;
+    raw[i] = make_uint4(0, 0, 0, 0);
+    if (c < V) raw[i] = *reinterpret_cast<const uint4*>(l + c);
+  }
+  __half2 th[8][4];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int c = (i * 1024 + threadIdx.x) * 8;
+    const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const float2 f = unpack_bf16(w[t]);
+      const float t0 = tanh_fast(f.x * inv_cap), t1 = tanh_fast(f.y * inv_cap);
+      th[i][t] = __floats2half2_rn(t0, t1);
+      if (c < V) s += exp2f(k2 * t0 - k2) + exp2f(k2 * t1 - k2);
+    }
+  }
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = red[threadIdx.x];
+    v = warp_sum(v);
+    if (threadIdx.x == 0) s_total = v;
+  }
+  __syncthreads();
+  const float lse2 = log2f(s_total) + k2;          // log-sum-exp in base-2 units
+  const bool valid = tgt >= 0 && tgt < V;
+  if (threadIdx.x == 0) {
+    float out = 0.f;
+    if (valid) out = lse2 * 0.6931471805599453f - cap * tanh_fast(__bfloat162float(l[tgt]) * inv_cap);
+    nll[row] = out;
+  }
+  if (!dlogits) return;
+  float w = 0.f;
+  if (valid) w = row_w ? row_w[row] : inv_loss_div / fmaxf(1.0f, *n_valid);
+  __nv_bfloat16* d = dlogits + (size_t)row * ldl;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int c = (i * 1024 + threadIdx.x) * 8;
+    if (c >= V) continue;
+    float g[8];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const float2 tt = __half22float2(th[i][t]);
+      float p0 = exp2f(k2 * tt.x - lse2), p1 = exp2f(k2 * tt.y - lse2);
+      if (c + 2 * t == tgt) p0 -= 1.0f;
+      if (c + 2 * t + 1 == tgt) p1 -= 1.0f;
+      g[2 * t] = w * p0 * (1.0f - tt.x * tt.x);
+      g[2 * t + 1] = w * p1 * (1.0f - tt.y * tt.y);
+    }
+    uint4 o;
+    o.x = pack_bf16(g[0], g[1]); o.y = pack_bf16(g[2], g[3]); o.z = pack_bf16(g[4], g[5]); o.w = pack_bf16(g[6], g[7]);
+    *reinterpret_cast<uint4*>(d + c) = o;
+  }
+  for (int c = V + threadIdx.x; c < ldl; c += blockDim.x) d[c] = __float2bfloat16(0.f);
+}
+
 // y = cap * tanh(x / cap) in fp32 from bf16 logits, first V of ldl columns
 __global__ void softcap_logits_kernel(const __nv_bfloat16* logits, long long ldl, float* out, int V, float cap, long long total) {
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -444,6 +656,17 @@ int bones_rmsnorm_fwd(const void* x, void* y, int M, int C, void* stream) {
 }
 int bones_rmsnorm_bwd(const void* x, const void* dy, const void* add, void* dx, int M, int C, void* stream) {
   if (C % 8 || C > kMaxVec * 256) return -2;
+#define BONES_RMS_BWD_CASE(NV)                                                                                                  \
+  case NV:                                                                                                                      \
+    rmsnorm_bwd_packed_kernel<NV><<<ROW_GRID(M), 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy,  \
+                                                                            (const __nv_bfloat16*)add, (__nv_bfloat16*)dx, M);  \
+    return (int)cudaGetLastError();
+  if (C % 256 == 0) {
+    switch (C / 256) {
+      BONES_RMS_BWD_CASE(2) BONES_RMS_BWD_CASE(3) BONES_RMS_BWD_CASE(4) BONES_RMS_BWD_CASE(5) BONES_RMS_BWD_CASE(6)
+      default: break;
+    }
+  }
   rmsnorm_bwd_kernel<<<ROW_GRID(M), 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)add,
                                                              (__nv_bfloat16*)dx, M, C);
   return (int)cudaGetLastError();
@@ -457,6 +680,18 @@ int bones_resid_mix_norm_fwd(const void* x, const void* x0, const float* a, cons
 int bones_resid_mix_norm_bwd(const void* x, const void* x0, const void* xm, const float* a, const float* b, const void* dxm, const void* dxn,
                              void* dx, void* dx0, float* da, float* db, int M, int C, void* stream) {
   if (C % 8 || C > kMaxVec * 256) return -2;
+#define BONES_MIX_BWD_CASE(NV)                                                                                                   \
+  case NV:                                                                                                                       \
+    resid_mix_norm_bwd_packed_kernel<NV><<<ROW_GRID(M), 0, (cudaStream_t)stream>>>(                                              \
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)x0, (const __nv_bfloat16*)xm, a, b, (const __nv_bfloat16*)dxm,            \
+        (const __nv_bfloat16*)dxn, (__nv_bfloat16*)dx, (__nv_bfloat16*)dx0, da, db, M);                                          \
+    return (int)cudaGetLastError();
+  if (C % 256 == 0) {
+    switch (C / 256) {
+      BONES_MIX_BWD_CASE(2) BONES_MIX_BWD_CASE(3) BONES_MIX_BWD_CASE(4) BONES_MIX_BWD_CASE(5) BONES_MIX_BWD_CASE(6)
+      default: break;
+    }
+  }
   resid_mix_norm_bwd_kernel<<<ROW_GRID(M), 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)x, (const __nv_bfloat16*)x0, (const __nv_bfloat16*)xm, a, b, (const __nv_bfloat16*)dxm, (const __nv_bfloat16*)dxn,
       (__nv_bfloat16*)dx, (__nv_bfloat16*)dx0, da, db, M, C);
@@ -501,6 +736,11 @@ int bones_moe_combine_bwd(const void* ys, const long long* slot, const float* ga
 int bones_softcap_ce(const void* logits, long long ldl, const long long* targets, int V, float cap, float* nll, void* dlogits,
                      const float* row_w, const float* n_valid, float inv_loss_div, int M, void* stream) {
   if (V % 8 || ldl % 8) return -2;
+  if (V <= 65536 && V >= 8192) {
+    softcap_ce_row_kernel<<<M, 1024, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, ldl, targets, V, cap, nll,
+                                                                (__nv_bfloat16*)dlogits, row_w, n_valid, inv_loss_div, M);
+    return (int)cudaGetLastError();
+  }
   softcap_ce_kernel<<<M, 512, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, ldl, targets, V, cap, nll, (__nv_bfloat16*)dlogits,
                                                         row_w, n_valid, inv_loss_div, M);
   return (int)cudaGetLastError();

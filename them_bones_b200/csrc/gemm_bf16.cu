@@ -107,7 +107,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   tc_fence_after();
   const uint32_t tmem = *tmem_slot_g;
 
-  const int total = p.batch * p.tiles_m * p.tiles_n * p.splits;
+  // K-split slowest: CTAs running at one time share a K range, so operand slices are reused through L2
+  const int base_tiles = p.batch * p.tiles_m * p.tiles_n;
+  const int total = base_tiles * p.splits;
   const int KB = (p.K + BK - 1) / BK;
 
   if (warp == 0) {
@@ -117,8 +119,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
       bool ok = true;
       for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
         int b, mb, nb;
-        const int sp = tile % p.splits;
-        decode_tile(tile / p.splits, p.tiles_m, p.tiles_n, b, mb, nb);
+        const int sp = tile / base_tiles;
+        decode_tile(tile - sp * base_tiles, p.tiles_m, p.tiles_n, b, mb, nb);
         const int kb0 = (int)((long long)KB * sp / p.splits), kb1 = (int)((long long)KB * (sp + 1) / p.splits);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(empty(stage), phase ^ 1u, abort_flag, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
@@ -153,7 +155,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         if (!mbar_wait(tempty(acc), acc_phase ^ 1u, abort_flag, p.err, ERR_WAIT_TMEM_EMPTY)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem + acc * BN;
-        const int sp = tile % p.splits;
+        const int sp = tile / base_tiles;
         const int kb0 = (int)((long long)KB * sp / p.splits), kb1 = (int)((long long)KB * (sp + 1) / p.splits);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(full(stage), phase, abort_flag, p.err, ERR_WAIT_FULL)) { ok = false; break; }
@@ -179,7 +181,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     uint32_t acc_phase = 0;
     for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
       int b, mb, nb;
-      decode_tile(tile / p.splits, p.tiles_m, p.tiles_n, b, mb, nb);
+      decode_tile(tile % base_tiles, p.tiles_m, p.tiles_n, b, mb, nb);
       const bool got = mbar_wait(tfull(acc), acc_phase, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
       if (!__all_sync(0xffffffffu, got)) break;   // warp-uniform: the TMEM loads below need the whole warp
       tc_fence_after();
@@ -332,8 +334,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams 
     p.splits = 1;
     if (p.epi == EPI_ACC_F32 && base_tiles < 4 * sms && KB >= 32) {
       long long best = -1;
-      const int cand[] = {1, 2, 3, 4, 6, 8, 12, 16};
-      for (int c : cand) {
+      for (int c = 1; c <= 32; ++c) {
         if (c > KB / 8) break;
         const long long waves = ((long long)base_tiles * c + sms - 1) / sms;
         const long long cost = waves * (((long long)KB + c - 1) / c + 6) + (c > 1 ? 2 * c : 0);   // +6: tile prologue/epilogue, 2c: atomics

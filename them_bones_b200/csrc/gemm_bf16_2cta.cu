@@ -147,7 +147,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
   tc_fence_after();
   const uint32_t tmem = *tmem_slot_g;
 
-  const int total = p.batch * p.tiles_m * p.tiles_n * p.splits;
+  // Work units are ordered K-split slowest: the pairs that run at one time work on the same K range of (nearly) all output
+  // tiles, so every operand slice is fetched from DRAM once and shared through L2 by the tiles that need it.
+  const int base_tiles = p.batch * p.tiles_m * p.tiles_n;
+  const int total = base_tiles * p.splits;
   const int KB = (p.K + PK - 1) / PK;
   const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
 
@@ -158,8 +161,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
       bool ok = true;
       for (int tile = cluster_id; tile < total && ok; tile += n_clusters) {
         int b, mb, nb;
-        const int sp = tile % p.splits;
-        decode_tile2(tile / p.splits, p.tiles_m, p.tiles_n, b, mb, nb);
+        const int sp = tile / base_tiles;
+        decode_tile2(tile - sp * base_tiles, p.tiles_m, p.tiles_n, b, mb, nb);
         const int kb0 = (int)((long long)KB * sp / p.splits), kb1 = (int)((long long)KB * (sp + 1) / p.splits);
         const int m0 = mb * PM + (int)rank * 128, n0 = nb * PN + (int)rank * 128;
         for (int kb = kb0; kb < kb1; ++kb) {
@@ -196,7 +199,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         if (!mbar_wait(tempty(acc), acc_phase ^ 1u, abort_flag, p.err, ERR_WAIT_TMEM_EMPTY)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem + acc * PN;
-        const int sp = tile % p.splits;
+        const int sp = tile / base_tiles;
         const int kb0 = (int)((long long)KB * sp / p.splits), kb1 = (int)((long long)KB * (sp + 1) / p.splits);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(full(stage), phase, abort_flag, p.err, ERR_WAIT_FULL)) { ok = false; break; }
@@ -224,7 +227,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
     uint32_t acc_phase = 0;
     for (int tile = cluster_id; tile < total; tile += n_clusters) {
       int b, mb, nb;
-      decode_tile2(tile / p.splits, p.tiles_m, p.tiles_n, b, mb, nb);
+      decode_tile2(tile % base_tiles, p.tiles_m, p.tiles_n, b, mb, nb);
       const int row = mb * PM + (int)rank * 128 + q * 32 + lane;
       const bool row_ok = row < p.M;
       const long long drow = (long long)b * p.strideD + (long long)row * p.ldd;
@@ -435,8 +438,7 @@ int bones_gemm_bf16_pair(const void* A, const void* B, void* D, const void* R, i
     p.splits = 1;
     if (epi == E2_ACC_F32 && base_tiles < 4 * pairs && KB >= 32) {
       long long best = -1;
-      const int cand[] = {1, 2, 3, 4, 6, 8, 12, 16};
-      for (int c : cand) {
+      for (int c = 1; c <= 32; ++c) {
         if (c > KB / 8) break;
         const long long waves = ((long long)base_tiles * c + pairs - 1) / pairs;
         const long long cost = waves * (((long long)KB + c - 1) / c + 6) + (c > 1 ? 2 * c : 0);

@@ -78,7 +78,8 @@ def gemm(a, b, d, *, m, n, k, lda, ldb, ldd, a_major=0, b_major=0, epi=EPI_BF16,
     if pair is None:
         if PAIR_MODE == "auto":
             tiles = -(-m // 256) * -(-n // 256) * batch
-            pair = force_bn == 0 and m >= 256 and n >= 256 and tiles >= 37
+            # few output tiles still fill the pairs when a long K is split (weight gradients)
+            pair = force_bn == 0 and m >= 256 and n >= 256 and (tiles >= 37 or (epi == EPI_ACC_F32 and k >= 8192 * 37 // tiles))
         else:
             pair = PAIR_MODE == "1" and force_bn == 0
     if pair:
