@@ -270,6 +270,55 @@ __global__ void rope_qknorm_bwd128_kernel(const __nv_bfloat16* __restrict__ qkv,
   }
 }
 
+// Same backward for bf16 dq-hat | dk-hat (the two-kernel attention backward writes them in bf16 and puts dV straight into
+// its third of dqkv): only the q and k thirds are produced here.
+__global__ void rope_qknorm_bwd128_bf16_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ cosT,
+                                               const float* __restrict__ sinT, const __nv_bfloat16* __restrict__ dqk,
+                                               __nv_bfloat16* __restrict__ dqkv, long long M, int T, int H) {
+  const long long item = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 3;     // (row, q|k, head)
+  const int l8 = threadIdx.x & 7;
+  const long long total = M * 2 * H;
+  const bool live = item < total;
+  const long long it = live ? item : total - 1;
+  const int h = (int)(it % H), which = (int)((it / H) % 2);
+  const long long row = it / (2 * H);
+  const long long A = (long long)H * 128;
+  const long long col = which * A + (long long)h * 128 + l8 * 8;
+  const __nv_bfloat16* src = qkv + row * 3 * A + col;
+  const __nv_bfloat16* g = dqk + row * 2 * A + col;
+  const int t = (int)(row % T);
+  float x1[8], x2[8], cs[8], sn[8], g1[8], g2[8], y1[8], y2[8];
+  ld8_bf16(src, x1);
+  ld8_bf16(src + 64, x2);
+  ld8_bf16(g, g1);
+  ld8_bf16(g + 64, g2);
+  ld8_f32(cosT + (long long)t * 64 + l8 * 8, cs);
+  ld8_f32(sinT + (long long)t * 64 + l8 * 8, sn);
+  float ss = 0.f, dot = 0.f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    y1[e] = x1[e] * cs[e] + x2[e] * sn[e];
+    y2[e] = -x1[e] * sn[e] + x2[e] * cs[e];
+    ss += y1[e] * y1[e] + y2[e] * y2[e];
+    dot += y1[e] * g1[e] + y2[e] * g2[e];
+  }
+  ss = group8_sum(ss);
+  dot = group8_sum(dot);
+  const float r = rsqrtf(ss * (1.0f / 128.0f) + kQkEps);
+  const float m = dot * r * r * (1.0f / 128.0f);
+  float o1[8], o2[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float du1 = r * (g1[e] - y1[e] * m), du2 = r * (g2[e] - y2[e] * m);
+    o1[e] = du1 * cs[e] - du2 * sn[e];
+    o2[e] = du1 * sn[e] + du2 * cs[e];
+  }
+  if (!live) return;
+  __nv_bfloat16* out = dqkv + row * 3 * A + col;
+  st8_bf16(out, o1);
+  st8_bf16(out + 64, o2);
+}
+
 // ---------------------------------------------------------------------------------------------------------------
 // forward attention, head_dim 128
 // ---------------------------------------------------------------------------------------------------------------
@@ -544,6 +593,15 @@ int bones_rope_qknorm_bwd(const void* qkv, const float* cosT, const float* sinT,
                                                                     (__nv_bfloat16*)dqkv, M, T, H);
   else
     return -2;
+  return (int)cudaGetLastError();
+}
+
+// dqk: bf16 [M, 2*H*128]; writes the q and k thirds of dqkv [M, 3*H*128] (head_dim 128 only)
+int bones_rope_qknorm_bwd_bf16(const void* qkv, const float* cosT, const float* sinT, const void* dqk, void* dqkv, long long M, int T, int H,
+                               void* stream) {
+  const long long threads = M * 2 * H * 8;
+  rope_qknorm_bwd128_bf16_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)qkv, cosT, sinT, (const __nv_bfloat16*)dqk, (__nv_bfloat16*)dqkv, M, T, H);
   return (int)cudaGetLastError();
 }
 

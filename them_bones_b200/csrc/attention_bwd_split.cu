@@ -1,13 +1,18 @@
 // Flash attention backward as two tcgen05 kernels (head_dim 128), the default backward of attention.cu's forward.
 //
-//   dkv kernel   one CTA per 128-key tile walks the query tiles that see it:  S = Qh Kh^T, dP = dO V^T,
-//                P = exp2(S c1 - lse2) masked, dV += P^T dO, dS = P (dP - delta) scale, dK += dS^T Qh.
-//   dq kernel    one CTA per 128-query tile walks its key tiles:  S and dP again, dS, dQ += dS Kh.
-// Recomputing S and dP in the second kernel costs two extra GEMMs per tile pair, but every accumulator (dK, dV, dQ) then
-// lives in TMEM for the whole CTA: no atomics, no per-tile drain, and the MMAs of the next tile pair are issued while
-// the compute warps still work on the current one (in the single-kernel form, attention_bwd.cu, TMEM is full and the
-// five GEMMs serialise with the exponentiation and a dQ drain through fp32 atomics).
-// Operand views, masking, scaling and the saved statistics are those of attention_bwd.cu.
+//   dkv kernel   one CTA per 128-key tile walks the query tiles that see it, in transposed form so that keys are the
+//                TMEM lanes:  S^T = Kh Qh^T,  dP^T = V dO^T,  P^T = exp2(S^T c1 - lse2) masked,  dV += P^T dO,
+//                dS^T = P^T (dP^T - delta) scale,  dK += dS^T Qh.
+//   dq kernel    one CTA per 128-query tile walks its key tiles (queries are the lanes):  S and dP again, dS, dQ += dS Kh.
+//
+// P^T, dS^T and dS never touch shared memory: the compute warps write them back to TMEM as packed bf16 pairs over the
+// columns of the fp32 tile they were computed from, and the next MMA takes its A operand from TMEM.  Every accumulator
+// (dK, dV, dQ) lives in TMEM for the whole CTA: no atomics, no per-tile drain, deterministic results.  Recomputing S and
+// dP in the second kernel costs two extra GEMMs per tile pair; in the single-kernel form (attention_bwd.cu) TMEM is full
+// and the five GEMMs serialise with the exponentiation and a dQ drain through fp32 atomics.
+// Outputs are bf16: dq-hat | dk-hat as [B*T, 2A] for the RoPE / QK-norm backward, dV straight into its third of dqkv.
+// Operand views, masking and scaling are those of attention_bwd.cu; the saved log-sum-exp is consumed through a
+// pre-pass that also computes delta = rowsum(dO * O).
 #include "common.cuh"
 
 namespace bones {
@@ -15,16 +20,17 @@ namespace bones {
 constexpr int ST = 128;
 constexpr uint32_t STILE = ST * 128 * 2;   // 32 KB: two 128-byte-swizzled atoms of [128 rows][64 cols]
 constexpr uint32_t SATOM = STILE / 2;
+constexpr float kLog2e = 1.4426950408889634f;
 
 struct SplitParams {
   int B, T, H;
   float c1, scale;
   int window_tiles;
   const int* doc_start;
-  const float* lse;
-  const float* delta;
-  float* dqk;          // [B*T, 2A] fp32: dq-hat | dk-hat
-  __nv_bfloat16* dv;   // [B*T, A]
+  const float2* stats;   // [B, H, T]: (-lse * log2(e), delta)
+  __nv_bfloat16* dqk;    // [B*T, 2A]: dq-hat | dk-hat
+  __nv_bfloat16* dv;     // rows of dv_ld elements
+  long long dv_ld;
   int* err;
 };
 
@@ -40,21 +46,71 @@ __device__ __forceinline__ uint64_t sdesc_k(uint32_t tile, int k) {   // K-major
 __device__ __forceinline__ uint64_t sdesc_mn(uint32_t tile, int k) {  // MN-major view of the same bytes
   return umma_smem_desc(tile + k * 2048, SATOM, 1024, kLayoutSw128);
 }
-__device__ __forceinline__ void store_row64_sw128(uint32_t tile, int half, int r, const float* v) {
-  const uint32_t prow = tile + (uint32_t)half * SATOM + (uint32_t)r * 128u;
+// TMEM column of UMMA_K step k of a packed bf16 A operand: each of the two compute warps of a lane quadrant packs its
+// 64 fp32 columns (c0 = 0 or 64) into the first 32 columns of its own range
+__device__ __forceinline__ uint32_t packed_col(int k) { return (uint32_t)((k & 3) * 8 + (k >> 2) * 64); }
+
+__device__ __forceinline__ float ex2_fast(float x) {
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x));
+  return e;
+}
+// 64 fp32 values -> 32 packed bf16 pairs -> 32 TMEM columns starting at taddr
+__device__ __forceinline__ void store_packed64(uint32_t taddr, const float* v) {
+  uint32_t pk[32];
 #pragma unroll
-  for (int g = 0; g < 8; ++g) {
-    const uint32_t chunk = (uint32_t)g ^ (uint32_t)(r & 7);
-    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + chunk * 16u), "r"(pack_bf16(v[g * 8 + 0], v[g * 8 + 1])),
-                 "r"(pack_bf16(v[g * 8 + 2], v[g * 8 + 3])), "r"(pack_bf16(v[g * 8 + 4], v[g * 8 + 5])),
-                 "r"(pack_bf16(v[g * 8 + 6], v[g * 8 + 7]))
-                 : "memory");
+  for (int j = 0; j < 32; ++j) pk[j] = pack_bf16(v[2 * j], v[2 * j + 1]);
+  BONES_TMEM_ST32(taddr, pk);
+  tmem_st_wait();
+}
+// 64 accumulator columns of this thread's row -> 64 bf16 in global memory (four 32-byte sectors)
+__device__ __forceinline__ void drain_row64(uint32_t taddr, __nv_bfloat16* dst) {
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    uint32_t v[32];
+    __syncwarp();
+    BONES_TMEM_LD32(taddr + (uint32_t)(c * 32), v);
+    tmem_ld_wait();
+    uint4 u[4];
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      u[g].x = pack_bf16(__uint_as_float(v[g * 8 + 0]), __uint_as_float(v[g * 8 + 1]));
+      u[g].y = pack_bf16(__uint_as_float(v[g * 8 + 2]), __uint_as_float(v[g * 8 + 3]));
+      u[g].z = pack_bf16(__uint_as_float(v[g * 8 + 4]), __uint_as_float(v[g * 8 + 5]));
+      u[g].w = pack_bf16(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7]));
+    }
+    st_global_v8(dst + c * 32, u[0], u[1]);
+    st_global_v8(dst + c * 32 + 16, u[2], u[3]);
+  }
+}
+
+// stats[b,h,t] = (-lse * log2(e), sum_d dO * O)
+__global__ void attn_bwd_stats_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ y,
+                                      const float* __restrict__ lse, float2* __restrict__ stats, long long M, int T, int H) {
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (w >= M * H) return;
+  const int h = (int)(w % H);
+  const long long row = w / H;
+  const long long off = row * H * 128 + (long long)h * 128 + lane * 4;
+  const uint2 a = *reinterpret_cast<const uint2*>(dy + off), c = *reinterpret_cast<const uint2*>(y + off);
+  const float2 a0 = unpack_bf16(a.x), a1 = unpack_bf16(a.y), c0 = unpack_bf16(c.x), c1 = unpack_bf16(c.y);
+  float s = a0.x * c0.x + a0.y * c0.y + a1.x * c1.x + a1.y * c1.y;
+  s = warp_sum(s);
+  if (lane == 0) {
+    const long long b = row / T, t = row % T;
+    const long long i = (b * H + h) * T + t;
+    stats[i] = make_float2(-lse[i] * kLog2e, s);
   }
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// dK / dV
+// dK / dV  (transposed: TMEM lanes are keys, columns are queries)
 // ---------------------------------------------------------------------------------------------------------------
+constexpr uint32_t DKV_STAT = STILE * 6;            // two stages of 128 x (float2 stats) then two of 128 x int doc starts
+constexpr uint32_t DKV_LO = DKV_STAT + 2 * 1024;
+constexpr uint32_t DKV_BARS = DKV_LO + 2 * 512;
+
 __global__ void __launch_bounds__(320, 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant__ CUtensorMap tm_v,
                     const __grid_constant__ CUtensorMap tm_dy, const SplitParams p) {
@@ -65,13 +121,12 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
   const uint32_t sK = base, sV = base + STILE;
   auto sQ = [&](int s) { return base + STILE * (2 + 2 * s); };
   auto sdO = [&](int s) { return base + STILE * (3 + 2 * s); };
-  const uint32_t sPB = base + STILE * 6;
-  const uint32_t bars = base + STILE * 7;
-  enum { B_KV = 0, B_QDO0, B_QDO1, B_FREE0, B_FREE1, B_SFULL, B_DPFULL, B_PREADY, B_DVDONE, B_DSREADY, B_DKDONE, B_COUNT };
+  const uint32_t bars = base + DKV_BARS;
+  enum { B_KV = 0, B_QDO0, B_QDO1, B_FREE0, B_FREE1, B_SFULL, B_DPFULL, B_PREADY, B_DSREADY, B_DONE, B_COUNT };
   auto bar = [&](int i) { return bars + 8u * i; };
   const uint32_t tmem_slot = bars + 8u * B_COUNT;
-  volatile uint32_t* tmem_slot_g = reinterpret_cast<volatile uint32_t*>(gen + STILE * 7 + 8 * B_COUNT);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + STILE * 7 + 8 * B_COUNT + 8);
+  volatile uint32_t* tmem_slot_g = reinterpret_cast<volatile uint32_t*>(gen + DKV_BARS + 8 * B_COUNT);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + DKV_BARS + 8 * B_COUNT + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
@@ -87,9 +142,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
     mbar_init(bar(B_SFULL), 1);
     mbar_init(bar(B_DPFULL), 1);
     mbar_init(bar(B_PREADY), 8);
-    mbar_init(bar(B_DVDONE), 1);
     mbar_init(bar(B_DSREADY), 8);
-    mbar_init(bar(B_DKDONE), 1);
+    mbar_init(bar(B_DONE), 1);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tm_qk);
@@ -121,180 +175,143 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
       tma_load_2d(sK + SATOM, &tm_qk, bar(B_KV), A + h * 128 + 64, row0 + kt * ST);
       tma_load_2d(sV, &tm_v, bar(B_KV), 2 * A + h * 128, row0 + kt * ST);
       tma_load_2d(sV + SATOM, &tm_v, bar(B_KV), 2 * A + h * 128 + 64, row0 + kt * ST);
+      const float2* stat_row = p.stats + ((long long)b * p.H + h) * p.T;
       for (int i = 0; i < n; ++i) {
         const int s = i & 1;
         if (i >= 2 && !mbar_wait(bar(B_FREE0 + s), ((i - 2) >> 1) & 1, abort_flag, p.err, ERR_WAIT_EMPTY)) break;
-        mbar_arrive_expect_tx(bar(B_QDO0 + s), 2 * STILE);
+        mbar_arrive_expect_tx(bar(B_QDO0 + s), 2 * STILE + 1024 + (p.doc_start ? 512u : 0u));
         const int r = row0 + (kt + i) * ST;
         tma_load_2d(sQ(s), &tm_qk, bar(B_QDO0 + s), h * 128, r);
         tma_load_2d(sQ(s) + SATOM, &tm_qk, bar(B_QDO0 + s), h * 128 + 64, r);
         tma_load_2d(sdO(s), &tm_dy, bar(B_QDO0 + s), h * 128, r);
         tma_load_2d(sdO(s) + SATOM, &tm_dy, bar(B_QDO0 + s), h * 128 + 64, r);
+        bulk_load(base + DKV_STAT + s * 1024, stat_row + (kt + i) * ST, 1024, bar(B_QDO0 + s));
+        if (p.doc_start) bulk_load(base + DKV_LO + s * 512, p.doc_start + r, 512, bar(B_QDO0 + s));
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t id_kk = umma_idesc_f16(128, 128, 1, 0, 0);
-      const uint32_t id_mm = umma_idesc_f16(128, 128, 1, 1, 1);
+      const uint32_t id_km = umma_idesc_f16(128, 128, 1, 0, 1);
       bool ok = mbar_wait(bar(B_KV), 0, abort_flag, p.err, ERR_WAIT_FULL);
-      // S(0), dP(0)
-      if (ok && n > 0) {
-        ok = mbar_wait(bar(B_QDO0), 0, abort_flag, p.err, ERR_WAIT_FULL);
-        if (ok) {
-          tc_fence_after();
+      if (ok) ok = mbar_wait(bar(B_QDO0), 0, abort_flag, p.err, ERR_WAIT_FULL);
+      if (ok) {
+        tc_fence_after();
 #pragma unroll
-          for (int k = 0; k < 8; ++k) umma_f16(tS, sdesc_k(sQ(0), k), sdesc_k(sK, k), id_kk, k ? 1u : 0u);
-          tc_commit(bar(B_SFULL));
+        for (int k = 0; k < 8; ++k) umma_f16(tS, sdesc_k(sK, k), sdesc_k(sQ(0), k), id_kk, k ? 1u : 0u);
+        tc_commit(bar(B_SFULL));
 #pragma unroll
-          for (int k = 0; k < 8; ++k) umma_f16(tdP, sdesc_k(sdO(0), k), sdesc_k(sV, k), id_kk, k ? 1u : 0u);
-          tc_commit(bar(B_DPFULL));
-        }
+        for (int k = 0; k < 8; ++k) umma_f16(tdP, sdesc_k(sV, k), sdesc_k(sdO(0), k), id_kk, k ? 1u : 0u);
+        tc_commit(bar(B_DPFULL));
       }
       for (int i = 0; i < n && ok; ++i) {
         const int s = i & 1;
         const uint32_t ph = (uint32_t)(i & 1);
         const bool more = i + 1 < n;
-        // P(i) is in shared memory (and S(i) has been read): dV += P^T dO, then S(i+1) behind it
+        // P^T(i) sits packed in the S^T columns: dV += P^T dO, then S^T(i+1) behind it (same pipe, in order)
         if (!mbar_wait(bar(B_PREADY), ph, abort_flag, p.err, ERR_WAIT_AUX)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < 8; ++k) umma_f16(tdV, sdesc_mn(sPB, k), sdesc_mn(sdO(s), k), id_mm, (i | k) ? 1u : 0u);
-        tc_commit(bar(B_DVDONE));
+        for (int k = 0; k < 8; ++k) umma_f16_ts(tdV, tS + packed_col(k), sdesc_mn(sdO(s), k), id_km, (i | k) ? 1u : 0u);
         if (more) {
           if (!mbar_wait(bar(B_QDO0 + (s ^ 1)), ((i + 1) >> 1) & 1, abort_flag, p.err, ERR_WAIT_FULL)) { ok = false; break; }
           tc_fence_after();
 #pragma unroll
-          for (int k = 0; k < 8; ++k) umma_f16(tS, sdesc_k(sQ(s ^ 1), k), sdesc_k(sK, k), id_kk, k ? 1u : 0u);
+          for (int k = 0; k < 8; ++k) umma_f16(tS, sdesc_k(sK, k), sdesc_k(sQ(s ^ 1), k), id_kk, k ? 1u : 0u);
           tc_commit(bar(B_SFULL));
         }
-        // dS(i) is in shared memory (and dP(i) has been read): dK += dS^T Qh, then dP(i+1) behind it
+        // dS^T(i) sits packed in the dP^T columns: dK += dS^T Qh, then dP^T(i+1) behind it
         if (!mbar_wait(bar(B_DSREADY), ph, abort_flag, p.err, ERR_WAIT_AUX)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < 8; ++k) umma_f16(tdK, sdesc_mn(sPB, k), sdesc_mn(sQ(s), k), id_mm, (i | k) ? 1u : 0u);
-        tc_commit(bar(B_DKDONE));
+        for (int k = 0; k < 8; ++k) umma_f16_ts(tdK, tdP + packed_col(k), sdesc_mn(sQ(s), k), id_km, (i | k) ? 1u : 0u);
         tc_commit(bar(B_FREE0 + s));
         if (more) {
 #pragma unroll
-          for (int k = 0; k < 8; ++k) umma_f16(tdP, sdesc_k(sdO(s ^ 1), k), sdesc_k(sV, k), id_kk, k ? 1u : 0u);
+          for (int k = 0; k < 8; ++k) umma_f16(tdP, sdesc_k(sV, k), sdesc_k(sdO(s ^ 1), k), id_kk, k ? 1u : 0u);
           tc_commit(bar(B_DPFULL));
+        } else {
+          tc_commit(bar(B_DONE));
         }
       }
     }
   } else {
     const int q = warp & 3, half = (warp - 2) >> 2;
-    const int r = q * 32 + lane;
+    const int r = q * 32 + lane;                       // key row of this thread
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-    const int c0 = half * 64;
-    const float log2e = 1.4426950408889634f;
+    const int c0 = half * 64;                          // first query column of this thread
+    const int k0 = kt * ST, kpos = k0 + r;
     bool ok = true;
-    float nx_lse2 = 0.f, nx_dlt = 0.f;
-    int nx_lo = 0;
-    if (n > 0) {
-      const int qpos0 = kt * ST + r;
-      const long long st0 = ((long long)b * p.H + h) * p.T + qpos0;
-      nx_lse2 = p.lse[st0] * log2e;
-      nx_dlt = p.delta[st0];
-      if (p.doc_start) nx_lo = p.doc_start[(long long)b * p.T + qpos0];
-    }
     for (int i = 0; i < n && ok; ++i) {
+      const int s = i & 1;
       const uint32_t ph = (uint32_t)(i & 1);
-      const int qpos = (kt + i) * ST + r;
-      const float lse2 = nx_lse2, dlt = nx_dlt;
-      const int lo = nx_lo;
-      if (i + 1 < n) {
-        const int qn = qpos + ST;
-        const long long stn = ((long long)b * p.H + h) * p.T + qn;
-        nx_lse2 = p.lse[stn] * log2e;
-        nx_dlt = p.delta[stn];
-        if (p.doc_start) nx_lo = p.doc_start[(long long)b * p.T + qn];
-      }
-      const int k0 = kt * ST;
-      const bool need_mask = __any_sync(0xffffffffu, (i == 0) || (k0 + c0 < lo));
+      bool got = mbar_wait(bar(B_QDO0 + s), (i >> 1) & 1, abort_flag, p.err, ERR_WAIT_FULL);   // this tile's statistics
+      if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+      const float4* st4 = reinterpret_cast<const float4*>(gen + DKV_STAT + s * 1024) + c0 / 2;   // two queries per float4
+      const int* slo = reinterpret_cast<const int*>(gen + DKV_LO + s * 512);
+      const bool need_doc = p.doc_start && slo[ST - 1] > k0;
       float pr[64];
-      bool got = mbar_wait(bar(B_SFULL), ph, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
+      got = mbar_wait(bar(B_SFULL), ph, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
       if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
       tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t v[32];
+      {
+        uint32_t v0[32], v1[32];
         __syncwarp();
-        BONES_TMEM_LD32(tS + lane_addr + (uint32_t)(c0 + c * 32), v);
+        BONES_TMEM_LD32(tS + lane_addr + (uint32_t)c0, v0);
+        BONES_TMEM_LD32(tS + lane_addr + (uint32_t)(c0 + 32), v1);
         tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float xx = fmaf(__uint_as_float(v[j]), p.c1, -lse2);
-          float e;
-          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(xx));
-          pr[c * 32 + j] = e;
+        for (int j = 0; j < 16; ++j) {
+          const float4 a = st4[j], c = st4[16 + j];
+          pr[2 * j] = ex2_fast(fmaf(__uint_as_float(v0[2 * j]), p.c1, a.x));
+          pr[2 * j + 1] = ex2_fast(fmaf(__uint_as_float(v0[2 * j + 1]), p.c1, a.z));
+          pr[32 + 2 * j] = ex2_fast(fmaf(__uint_as_float(v1[2 * j]), p.c1, c.x));
+          pr[32 + 2 * j + 1] = ex2_fast(fmaf(__uint_as_float(v1[2 * j + 1]), p.c1, c.z));
         }
       }
-      if (need_mask) {
+      if (i == 0) {                                    // diagonal tile: a key sees only queries at or after it
 #pragma unroll
-        for (int j = 0; j < 64; ++j) {
-          const int kpos = k0 + c0 + j;
-          if (kpos > qpos || kpos < lo) pr[j] = 0.f;
-        }
+        for (int j = 0; j < 64; ++j)
+          if (r > c0 + j) pr[j] = 0.f;
       }
+      if (need_doc) {                                  // a query sees only keys of its own document
+#pragma unroll
+        for (int j = 0; j < 64; ++j)
+          if (kpos < slo[c0 + j]) pr[j] = 0.f;
+      }
+      store_packed64(tS + lane_addr + (uint32_t)c0, pr);
       tc_fence_before();
-      if (i >= 1) {   // dS(i-1) must have been consumed by dK's MMAs before P(i) overwrites the buffer
-        got = mbar_wait(bar(B_DKDONE), (uint32_t)((i - 1) & 1), abort_flag, p.err, ERR_WAIT_AUX);
-        if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
-      }
-      store_row64_sw128(sPB, half, r, pr);
-      fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_PREADY));
       got = mbar_wait(bar(B_DPFULL), ph, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
       if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
       tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t v[32];
+      {
+        uint32_t v0[32], v1[32];
         __syncwarp();
-        BONES_TMEM_LD32(tdP + lane_addr + (uint32_t)(c0 + c * 32), v);
+        BONES_TMEM_LD32(tdP + lane_addr + (uint32_t)c0, v0);
+        BONES_TMEM_LD32(tdP + lane_addr + (uint32_t)(c0 + 32), v1);
         tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) pr[c * 32 + j] = pr[c * 32 + j] * (__uint_as_float(v[j]) - dlt) * p.scale;
+        for (int j = 0; j < 16; ++j) {
+          const float4 a = st4[j], c = st4[16 + j];
+          pr[2 * j] *= (__uint_as_float(v0[2 * j]) - a.y) * p.scale;
+          pr[2 * j + 1] *= (__uint_as_float(v0[2 * j + 1]) - a.w) * p.scale;
+          pr[32 + 2 * j] *= (__uint_as_float(v1[2 * j]) - c.y) * p.scale;
+          pr[32 + 2 * j + 1] *= (__uint_as_float(v1[2 * j + 1]) - c.w) * p.scale;
+        }
       }
+      store_packed64(tdP + lane_addr + (uint32_t)c0, pr);
       tc_fence_before();
-      got = mbar_wait(bar(B_DVDONE), ph, abort_flag, p.err, ERR_WAIT_AUX);
-      if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
-      store_row64_sw128(sPB, half, r, pr);
-      fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_DSREADY));
     }
     if (ok && n > 0) {
-      const bool got = mbar_wait(bar(B_DKDONE), (uint32_t)((n - 1) & 1), abort_flag, p.err, ERR_WAIT_TMEM_FULL);
+      const bool got = mbar_wait(bar(B_DONE), 0, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
       if (__all_sync(0xffffffffu, got)) {
         tc_fence_after();
-        const int kpos = kt * ST + r;
-        float* dk = p.dqk + ((long long)(row0 + kpos)) * 2 * A + A + (long long)h * 128 + c0;
-        __nv_bfloat16* dv = p.dv + ((long long)(row0 + kpos)) * A + (long long)h * 128 + c0;
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t v[32];
-          __syncwarp();
-          BONES_TMEM_LD32(tdK + lane_addr + (uint32_t)(c0 + c * 32), v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int g = 0; g < 8; ++g)
-            *reinterpret_cast<float4*>(dk + c * 32 + g * 4) = make_float4(__uint_as_float(v[g * 4]), __uint_as_float(v[g * 4 + 1]),
-                                                                          __uint_as_float(v[g * 4 + 2]), __uint_as_float(v[g * 4 + 3]));
-          __syncwarp();
-          BONES_TMEM_LD32(tdV + lane_addr + (uint32_t)(c0 + c * 32), v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 u;
-            u.x = pack_bf16(__uint_as_float(v[g * 8 + 0]), __uint_as_float(v[g * 8 + 1]));
-            u.y = pack_bf16(__uint_as_float(v[g * 8 + 2]), __uint_as_float(v[g * 8 + 3]));
-            u.z = pack_bf16(__uint_as_float(v[g * 8 + 4]), __uint_as_float(v[g * 8 + 5]));
-            u.w = pack_bf16(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7]));
-            *reinterpret_cast<uint4*>(dv + c * 32 + g * 8) = u;
-          }
-        }
+        drain_row64(tdK + lane_addr + (uint32_t)c0, p.dqk + ((long long)(row0 + kpos)) * 2 * A + A + (long long)h * 128 + c0);
+        drain_row64(tdV + lane_addr + (uint32_t)c0, p.dv + ((long long)(row0 + kpos)) * p.dv_ld + (long long)h * 128 + c0);
       }
     }
   }
@@ -311,8 +328,11 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// dQ
+// dQ  (TMEM lanes are queries, columns are keys; dP double-buffered so the MMAs of tile j+1 run under the
+//      exponentiation of tile j)
 // ---------------------------------------------------------------------------------------------------------------
+constexpr uint32_t DQ_BARS = STILE * 6;
+
 __global__ void __launch_bounds__(320, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant__ CUtensorMap tm_v,
                    const __grid_constant__ CUtensorMap tm_dy, const SplitParams p) {
@@ -323,16 +343,15 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_const
   const uint32_t sQ = base, sdO = base + STILE;
   auto sK = [&](int s) { return base + STILE * (2 + 2 * s); };
   auto sV = [&](int s) { return base + STILE * (3 + 2 * s); };
-  const uint32_t sDS = base + STILE * 6;
-  const uint32_t bars = base + STILE * 7;
-  enum { B_QDO = 0, B_KV0, B_KV1, B_FREE0, B_FREE1, B_SDP0, B_SDP1, B_DSREADY, B_DQDONE, B_COUNT };
+  const uint32_t bars = base + DQ_BARS;
+  enum { B_QDO = 0, B_KV0, B_KV1, B_FREE0, B_FREE1, B_SFULL, B_SFREE, B_DPFULL0, B_DPFULL1, B_DSREADY, B_DONE, B_COUNT };
   auto bar = [&](int i) { return bars + 8u * i; };
   const uint32_t tmem_slot = bars + 8u * B_COUNT;
-  volatile uint32_t* tmem_slot_g = reinterpret_cast<volatile uint32_t*>(gen + STILE * 7 + 8 * B_COUNT);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + STILE * 7 + 8 * B_COUNT + 8);
+  volatile uint32_t* tmem_slot_g = reinterpret_cast<volatile uint32_t*>(gen + DQ_BARS + 8 * B_COUNT);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + DQ_BARS + 8 * B_COUNT + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x, h = blockIdx.y, b = blockIdx.z;   // longest rows first
   const int A = p.H * 128;
 
   if (threadIdx.x == 0) {
@@ -340,10 +359,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_const
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar(B_KV0 + s), 1);
       mbar_init(bar(B_FREE0 + s), 1);
-      mbar_init(bar(B_SDP0 + s), 1);
+      mbar_init(bar(B_DPFULL0 + s), 1);
     }
+    mbar_init(bar(B_SFULL), 1);
+    mbar_init(bar(B_SFREE), 8);
     mbar_init(bar(B_DSREADY), 8);
-    mbar_init(bar(B_DQDONE), 1);
+    mbar_init(bar(B_DONE), 1);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tm_qk);
@@ -359,10 +380,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot_g;
-  // S and dP are double-buffered as pairs: buffer s holds S at +0 and dP at +128 of its 256 columns?  No: dQ needs 128
-  // columns too, so S is double-buffered (0, 128), dP single (256), dQ (384).
-  const uint32_t tS[2] = {tmem, tmem + 128};
-  const uint32_t tdP = tmem + 256, tdQ = tmem + 384;
+  const uint32_t tS = tmem, tdQ = tmem + 384;
+  const uint32_t tdP[2] = {tmem + 128, tmem + 256};
 
   const int kt0 = split_first_tile(p, b, qt);
   const int n = qt - kt0 + 1;
@@ -392,34 +411,38 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_const
       const uint32_t id_kk = umma_idesc_f16(128, 128, 1, 0, 0);
       const uint32_t id_km = umma_idesc_f16(128, 128, 1, 0, 1);
       bool ok = mbar_wait(bar(B_QDO), 0, abort_flag, p.err, ERR_WAIT_FULL);
+      if (ok) ok = mbar_wait(bar(B_KV0), 0, abort_flag, p.err, ERR_WAIT_FULL);
+      if (ok) {
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_f16(tS, sdesc_k(sQ, k), sdesc_k(sK(0), k), id_kk, k ? 1u : 0u);
+        tc_commit(bar(B_SFULL));
+#pragma unroll
+        for (int k = 0; k < 8; ++k) umma_f16(tdP[0], sdesc_k(sdO, k), sdesc_k(sV(0), k), id_kk, k ? 1u : 0u);
+        tc_commit(bar(B_DPFULL0));
+      }
       for (int j = 0; j < n && ok; ++j) {
         const int s = j & 1;
-        if (!mbar_wait(bar(B_KV0 + s), (j >> 1) & 1, abort_flag, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+        if (j + 1 < n) {
+          // S(j+1) as soon as the compute warps hold S(j) in registers; dP(j+1) into the other dP buffer, whose packed
+          // dS(j-1) the dQ MMAs of tile j-1 (issued earlier, same pipe) have read by then
+          if (!mbar_wait(bar(B_KV0 + (s ^ 1)), ((j + 1) >> 1) & 1, abort_flag, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+          if (!mbar_wait(bar(B_SFREE), (uint32_t)(j & 1), abort_flag, p.err, ERR_WAIT_AUX)) { ok = false; break; }
+          tc_fence_after();
+#pragma unroll
+          for (int k = 0; k < 8; ++k) umma_f16(tS, sdesc_k(sQ, k), sdesc_k(sK(s ^ 1), k), id_kk, k ? 1u : 0u);
+          tc_commit(bar(B_SFULL));
+#pragma unroll
+          for (int k = 0; k < 8; ++k) umma_f16(tdP[s ^ 1], sdesc_k(sdO, k), sdesc_k(sV(s ^ 1), k), id_kk, k ? 1u : 0u);
+          tc_commit(bar(B_DPFULL0 + (s ^ 1)));
+        }
+        // dS(j) sits packed in the dP(j) columns: dQ += dS Kh(j), which also frees that K/V stage
+        if (!mbar_wait(bar(B_DSREADY), (uint32_t)(j & 1), abort_flag, p.err, ERR_WAIT_AUX)) { ok = false; break; }
         tc_fence_after();
-        // S(j): its buffer was last read for tile j-2, whose dS has long been published
 #pragma unroll
-        for (int k = 0; k < 8; ++k) umma_f16(tS[s], sdesc_k(sQ, k), sdesc_k(sK(s), k), id_kk, k ? 1u : 0u);
-        if (j >= 1) {
-          // dS(j-1) is in shared memory and dP(j-1) has been read: dQ += dS Kh(j-1), which also frees that K/V stage
-          if (!mbar_wait(bar(B_DSREADY), (uint32_t)((j - 1) & 1), abort_flag, p.err, ERR_WAIT_AUX)) { ok = false; break; }
-          tc_fence_after();
-#pragma unroll
-          for (int k = 0; k < 8; ++k) umma_f16(tdQ, sdesc_k(sDS, k), sdesc_mn(sK(s ^ 1), k), id_km, ((j - 1) | k) ? 1u : 0u);
-          tc_commit(bar(B_DQDONE));
-          tc_commit(bar(B_FREE0 + (s ^ 1)));
-        }
-#pragma unroll
-        for (int k = 0; k < 8; ++k) umma_f16(tdP, sdesc_k(sdO, k), sdesc_k(sV(s), k), id_kk, k ? 1u : 0u);
-        tc_commit(bar(B_SDP0 + s));
-      }
-      if (ok && n > 0) {
-        const int s = (n - 1) & 1;
-        if (mbar_wait(bar(B_DSREADY), (uint32_t)((n - 1) & 1), abort_flag, p.err, ERR_WAIT_AUX)) {
-          tc_fence_after();
-#pragma unroll
-          for (int k = 0; k < 8; ++k) umma_f16(tdQ, sdesc_k(sDS, k), sdesc_mn(sK(s), k), id_km, ((n - 1) | k) ? 1u : 0u);
-          tc_commit(bar(B_DQDONE));
-        }
+        for (int k = 0; k < 8; ++k) umma_f16_ts(tdQ, tdP[s] + packed_col(k), sdesc_mn(sK(s), k), id_km, (j | k) ? 1u : 0u);
+        tc_commit(bar(B_FREE0 + s));
+        if (j + 1 == n) tc_commit(bar(B_DONE));
       }
     }
   } else {
@@ -428,68 +451,65 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_const
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
     const int c0 = half * 64;
     const int qpos = qt * ST + r;
-    const long long stat = ((long long)b * p.H + h) * p.T + qpos;
-    const float lse2 = p.lse[stat] * 1.4426950408889634f;
-    const float dlt = p.delta[stat];
+    const float2 st = p.stats[((long long)b * p.H + h) * p.T + qpos];
     int lo = 0;
     if (p.doc_start) lo = p.doc_start[(long long)b * p.T + qpos];
     bool ok = true;
     for (int j = 0; j < n && ok; ++j) {
       const int s = j & 1;
-      bool got = mbar_wait(bar(B_SDP0 + s), (j >> 1) & 1, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
+      bool got = mbar_wait(bar(B_SFULL), (uint32_t)(j & 1), abort_flag, p.err, ERR_WAIT_TMEM_FULL);
       if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
       tc_fence_after();
       const int k0 = (kt0 + j) * ST + c0;
       const bool need_mask = __any_sync(0xffffffffu, (k0 + 63 > qpos) || (k0 < lo));
       float pr[64];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t v[32], w[32];
+      {
+        uint32_t v0[32], v1[32];
         __syncwarp();
-        BONES_TMEM_LD32(tS[s] + lane_addr + (uint32_t)(c0 + c * 32), v);
-        BONES_TMEM_LD32(tdP + lane_addr + (uint32_t)(c0 + c * 32), w);
+        BONES_TMEM_LD32(tS + lane_addr + (uint32_t)c0, v0);
+        BONES_TMEM_LD32(tS + lane_addr + (uint32_t)(c0 + 32), v1);
         tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(B_SFREE));
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const float xx = fmaf(__uint_as_float(v[i]), p.c1, -lse2);
-          float e;
-          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(xx));
-          pr[c * 32 + i] = e * (__uint_as_float(w[i]) - dlt) * p.scale;
+          pr[i] = ex2_fast(fmaf(__uint_as_float(v0[i]), p.c1, st.x));
+          pr[32 + i] = ex2_fast(fmaf(__uint_as_float(v1[i]), p.c1, st.x));
         }
       }
       if (need_mask) {
 #pragma unroll
         for (int i = 0; i < 64; ++i) {
-          const int kpos = k0 + i;
-          if (kpos > qpos || kpos < lo) pr[i] = 0.f;
+          const int kp = k0 + i;
+          if (kp > qpos || kp < lo) pr[i] = 0.f;
         }
       }
-      tc_fence_before();
-      if (j >= 1) {   // the dQ MMAs of tile j-1 must be done reading the dS buffer
-        got = mbar_wait(bar(B_DQDONE), (uint32_t)((j - 1) & 1), abort_flag, p.err, ERR_WAIT_AUX);
-        if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+      got = mbar_wait(bar(B_DPFULL0 + s), (uint32_t)((j >> 1) & 1), abort_flag, p.err, ERR_WAIT_TMEM_FULL);
+      if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+      tc_fence_after();
+      {
+        uint32_t v0[32], v1[32];
+        __syncwarp();
+        BONES_TMEM_LD32(tdP[s] + lane_addr + (uint32_t)c0, v0);
+        BONES_TMEM_LD32(tdP[s] + lane_addr + (uint32_t)(c0 + 32), v1);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          pr[i] *= (__uint_as_float(v0[i]) - st.y) * p.scale;
+          pr[32 + i] *= (__uint_as_float(v1[i]) - st.y) * p.scale;
+        }
       }
-      store_row64_sw128(sDS, half, r, pr);
-      fence_proxy_async_smem();
+      store_packed64(tdP[s] + lane_addr + (uint32_t)c0, pr);
+      tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_DSREADY));
     }
     if (ok && n > 0) {
-      const bool got = mbar_wait(bar(B_DQDONE), (uint32_t)((n - 1) & 1), abort_flag, p.err, ERR_WAIT_TMEM_FULL);
+      const bool got = mbar_wait(bar(B_DONE), 0, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
       if (__all_sync(0xffffffffu, got)) {
         tc_fence_after();
-        float* dq = p.dqk + ((long long)(row0 + qpos)) * 2 * A + (long long)h * 128 + c0;
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t v[32];
-          __syncwarp();
-          BONES_TMEM_LD32(tdQ + lane_addr + (uint32_t)(c0 + c * 32), v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int g = 0; g < 8; ++g)
-            *reinterpret_cast<float4*>(dq + c * 32 + g * 4) = make_float4(__uint_as_float(v[g * 4]), __uint_as_float(v[g * 4 + 1]),
-                                                                          __uint_as_float(v[g * 4 + 2]), __uint_as_float(v[g * 4 + 3]));
-        }
+        drain_row64(tdQ + lane_addr + (uint32_t)c0, p.dqk + ((long long)(row0 + qpos)) * 2 * A + (long long)h * 128 + c0);
       }
     }
   }
@@ -517,10 +537,22 @@ static int tmap_rows_2d_s(CUtensorMap* out, const void* ptr, long long rows, lon
 extern "C" {
 using namespace bones;
 
-// Same contract as bones_attn_bwd (attention_bwd.cu); dqk needs no zeroing: both halves are overwritten.
-int bones_attn_bwd_split(const void* qk, const void* qkv, const void* dy, const float* lse, const float* delta, float* dqk, void* dv,
+// stats: [B, H, T] float2 scratch filled by the pre-pass
+int bones_attn_bwd_stats(const void* dy, const void* y, const float* lse, void* stats, long long M, int T, int H, void* stream) {
+  const long long warps = M * H;
+  attn_bwd_stats_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)y,
+                                                                                       lse, (float2*)stats, M, T, H);
+  return (int)cudaGetLastError();
+}
+
+// qk: [B*T, 2A] rotated, normalised q | k;  qkv: [B*T, 3A] (values read in place);  dy: [B*T, A];  stats from the pre-pass.
+// Outputs (bf16, every element overwritten): dqk [B*T, 2A];  dv rows of dv_ld elements (e.g. the last third of dqkv).
+int bones_attn_bwd_split(const void* qk, const void* qkv, const void* dy, const void* stats, void* dqk, void* dv, long long dv_ld,
                          const int* doc_start, int B, int T, int H, float scale, int window_tiles, void* stream) {
   if (T % ST) return -2;
+  if ((dv_ld % 16) || ((uintptr_t)dv & 31) || ((uintptr_t)dqk & 31) || ((uintptr_t)stats & 15) ||
+      (doc_start && ((uintptr_t)doc_start & 15)))
+    return -3;
   const long long M = (long long)B * T, A = (long long)H * 128;
   CUtensorMap tq, tv, td;
   int rc = tmap_rows_2d_s(&tq, qk, M, 2 * A);
@@ -531,24 +563,28 @@ int bones_attn_bwd_split(const void* qk, const void* qkv, const void* dy, const 
   if (rc) return rc;
   SplitParams p;
   p.B = B; p.T = T; p.H = H;
-  p.c1 = scale * 1.4426950408889634f;
+  p.c1 = scale * kLog2e;
   p.scale = scale;
   p.window_tiles = window_tiles;
   p.doc_start = doc_start;
-  p.lse = lse; p.delta = delta; p.dqk = dqk; p.dv = (__nv_bfloat16*)dv;
+  p.stats = (const float2*)stats;
+  p.dqk = (__nv_bfloat16*)dqk;
+  p.dv = (__nv_bfloat16*)dv;
+  p.dv_ld = dv_ld;
   p.err = error_word();
-  constexpr size_t smem = (size_t)STILE * 7 + 160 + 1024;
+  constexpr size_t smem_dkv = (size_t)DKV_BARS + 160 + 1024;
+  constexpr size_t smem_dq = (size_t)DQ_BARS + 160 + 1024;
   static bool attr_done = false;
   if (!attr_done) {
-    BONES_CHECK(cudaFuncSetAttribute(attn_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    BONES_CHECK(cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    BONES_CHECK(cudaFuncSetAttribute(attn_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dkv));
+    BONES_CHECK(cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dq));
     attr_done = true;
   }
   dim3 grid(T / ST, H, B);
   cudaStream_t s = (cudaStream_t)stream;
-  attn_bwd_dkv_kernel<<<grid, 320, smem, s>>>(tq, tv, td, p);
+  attn_bwd_dkv_kernel<<<grid, 320, smem_dkv, s>>>(tq, tv, td, p);
   BONES_CHECK(cudaGetLastError());
-  attn_bwd_dq_kernel<<<grid, 320, smem, s>>>(tq, tv, td, p);
+  attn_bwd_dq_kernel<<<grid, 320, smem_dq, s>>>(tq, tv, td, p);
   return (int)cudaGetLastError();
 }
 }  // extern "C"
