@@ -355,17 +355,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
   const uint32_t sQ = base;
   auto sK = [&](int s) { return base + TILE_BYTES * (1 + 2 * s); };
   auto sV = [&](int s) { return base + TILE_BYTES * (2 + 2 * s); };
-  auto sP = [&](int s) { return base + TILE_BYTES * (5 + s); };
   const uint32_t bars = base + TILE_BYTES * 7;
   const uint32_t q_full = bars;
-  auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
-  auto s_full = [&](int s) { return bars + 8u * (3 + s); };
-  auto p_full = [&](int s) { return bars + 8u * (5 + s); };
-  auto pv_done = [&](int s) { return bars + 8u * (7 + s); };
-  const uint32_t o_full = bars + 8u * 9;
-  const uint32_t tmem_slot = bars + 8u * 10;
-  volatile uint32_t* tmem_slot_g = reinterpret_cast<volatile uint32_t*>(gen + TILE_BYTES * 7 + 80);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + TILE_BYTES * 7 + 88);
+  auto kv_full = [&](int s) { return bars + 8u * (1 + s); };      // three K/V stages
+  auto kv_free = [&](int s) { return bars + 8u * (4 + s); };
+  auto s_full = [&](int s) { return bars + 8u * (7 + s); };       // two S buffers
+  auto p_full = [&](int s) { return bars + 8u * (9 + s); };
+  const uint32_t o_full = bars + 8u * 11;
+  const uint32_t tmem_slot = bars + 8u * 12;
+  volatile uint32_t* tmem_slot_g = reinterpret_cast<volatile uint32_t*>(gen + TILE_BYTES * 7 + 96);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + TILE_BYTES * 7 + 104);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;   // heaviest (latest) query tiles first
@@ -374,11 +373,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < 3; ++s) {
       mbar_init(kv_full(s), 1);
+      mbar_init(kv_free(s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
       mbar_init(s_full(s), 1);
       mbar_init(p_full(s), 8);
-      mbar_init(pv_done(s), 1);
     }
     mbar_init(o_full, 1);
     *abort_flag = 0;
@@ -408,8 +409,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
       tma_load_2d(sQ, &tm_qk, q_full, h * AD, row0 + qt * AT);
       tma_load_2d(sQ + ATOM_BYTES, &tm_qk, q_full, h * AD + 64, row0 + qt * AT);
       for (int j = 0; j < n; ++j) {
-        const int s = j & 1;
-        if (j >= 2 && !mbar_wait(pv_done(s), ((j - 2) >> 1) & 1, abort_flag, p.err, ERR_WAIT_EMPTY)) break;
+        const int s = j % 3;
+        if (j >= 3 && !mbar_wait(kv_free(s), (uint32_t)(((j - 3) / 3) & 1), abort_flag, p.err, ERR_WAIT_EMPTY)) break;
         mbar_arrive_expect_tx(kv_full(s), 2 * TILE_BYTES);
         const int r = row0 + (kt0 + j) * AT;
         tma_load_2d(sK(s), &tm_qk, kv_full(s), A + h * AD, r);
@@ -422,28 +423,30 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
     if (lane == 0) {
       const uint32_t idesc_s = umma_idesc_f16(128, 128, 1, 0, 0);   // Q (K-major) x K (K-major)
       const uint32_t idesc_o = umma_idesc_f16(128, 128, 1, 0, 1);   // P (K-major) x V (MN-major)
+      // P(j) sits in TMEM as packed bf16 pairs over the S(j) columns it was computed from (each softmax warp packs its
+      // 64 columns into the first 32 of its own range) and is the A operand of O += P V straight from there
       auto issue_pv = [&](int j) -> bool {
-        const int s = j & 1;
+        const int s = j & 1, st = j % 3;
         if (!mbar_wait(p_full(s), (j >> 1) & 1, abort_flag, p.err, ERR_WAIT_AUX)) return false;
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          const uint64_t ad = umma_smem_desc(sP(s) + (k >> 2) * ATOM_BYTES + (k & 3) * 32, 0, 1024, kLayoutSw128);
-          const uint64_t bd = umma_smem_desc(sV(s) + k * 2048, ATOM_BYTES, 1024, kLayoutSw128);
-          umma_f16(tO, ad, bd, idesc_o, (j | k) ? 1u : 0u);
+          const uint64_t bd = umma_smem_desc(sV(st) + k * 2048, ATOM_BYTES, 1024, kLayoutSw128);
+          umma_f16_ts(tO, tS[s] + (uint32_t)((k & 3) * 8 + (k >> 2) * 64), bd, idesc_o, (j | k) ? 1u : 0u);
         }
-        tc_commit(pv_done(s));
+        tc_commit(kv_free(st));
         return true;
       };
       bool ok = mbar_wait(q_full, 0, abort_flag, p.err, ERR_WAIT_FULL);
       for (int j = 0; j < n && ok; ++j) {
-        const int s = j & 1;
-        if (!mbar_wait(kv_full(s), (j >> 1) & 1, abort_flag, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+        const int s = j & 1, st = j % 3;
+        if (!mbar_wait(kv_full(st), (uint32_t)((j / 3) & 1), abort_flag, p.err, ERR_WAIT_FULL)) { ok = false; break; }
         tc_fence_after();
+        // S(j) overwrites the buffer that held P(j-2): its O MMAs were issued earlier on the same (in-order) pipe
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t off = (k >> 2) * ATOM_BYTES + (k & 3) * 32;
-          umma_f16(tS[s], umma_smem_desc(sQ + off, 0, 1024, kLayoutSw128), umma_smem_desc(sK(s) + off, 0, 1024, kLayoutSw128),
+          umma_f16(tS[s], umma_smem_desc(sQ + off, 0, 1024, kLayoutSw128), umma_smem_desc(sK(st) + off, 0, 1024, kLayoutSw128),
                    idesc_s, k ? 1u : 0u);
         }
         tc_commit(s_full(s));
@@ -465,24 +468,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
     bool ok = true;
     for (int j = 0; j < n; ++j) {
       const int s = j & 1;
-      bool got = mbar_wait(s_full(s), (j >> 1) & 1, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
-      if (got && j >= 2) got = mbar_wait(pv_done(s), ((j - 2) >> 1) & 1, abort_flag, p.err, ERR_WAIT_EMPTY);
+      const bool got = mbar_wait(s_full(s), (j >> 1) & 1, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
       if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
       tc_fence_after();
       const int k0 = (kt0 + j) * AT + c0;
       // warp-uniform: does any row of this warp need the element mask for these 64 keys (diagonal or document start)?
       const bool need_mask = __any_sync(0xffffffffu, (k0 + 63 > qpos) || (k0 < lo));
-      const uint32_t prow = sP(s) + (uint32_t)half * ATOM_BYTES + (uint32_t)r * 128u;
+      uint32_t v0[32], v1[32], pk[32];
+      __syncwarp();
+      BONES_TMEM_LD32(tS[s] + lane_addr + (uint32_t)c0, v0);
+      BONES_TMEM_LD32(tS[s] + lane_addr + (uint32_t)(c0 + 32), v1);
+      tmem_ld_wait();
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        uint32_t v[32];
-        __syncwarp();
-        BONES_TMEM_LD32(tS[s] + lane_addr + (uint32_t)(c0 + c * 32), v);
-        tmem_ld_wait();
         float e[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const float x = fmaf(__uint_as_float(v[i]), p.c1, -p.c2);
+          const float x = fmaf(__uint_as_float(c ? v1[i] : v0[i]), p.c1, -p.c2);
           asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e[i]) : "f"(x));
         }
         if (need_mask) {
@@ -495,15 +497,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
 #pragma unroll
         for (int i = 0; i < 32; ++i) l += e[i];
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const uint32_t chunk = (uint32_t)(c * 4 + g) ^ (uint32_t)(r & 7);
-          const uint32_t w0 = pack_bf16(e[g * 8 + 0], e[g * 8 + 1]), w1 = pack_bf16(e[g * 8 + 2], e[g * 8 + 3]);
-          const uint32_t w2 = pack_bf16(e[g * 8 + 4], e[g * 8 + 5]), w3 = pack_bf16(e[g * 8 + 6], e[g * 8 + 7]);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(prow + chunk * 16u), "r"(w0), "r"(w1), "r"(w2), "r"(w3)
-                       : "memory");
-        }
+        for (int i = 0; i < 16; ++i) pk[c * 16 + i] = pack_bf16(e[2 * i], e[2 * i + 1]);
       }
-      fence_proxy_async_smem();    // generic-proxy stores to shared memory -> visible to the tensor core (async proxy)
+      BONES_TMEM_ST32(tS[s] + lane_addr + (uint32_t)c0, pk);
+      tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full(s));
@@ -526,15 +523,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
           __syncwarp();
           BONES_TMEM_LD32(tO + lane_addr + (uint32_t)(c0 + c * 32), v);
           tmem_ld_wait();
+          uint4 u[4];
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
-            uint4 u;
-            u.x = pack_bf16(__uint_as_float(v[g * 8 + 0]) * inv, __uint_as_float(v[g * 8 + 1]) * inv);
-            u.y = pack_bf16(__uint_as_float(v[g * 8 + 2]) * inv, __uint_as_float(v[g * 8 + 3]) * inv);
-            u.z = pack_bf16(__uint_as_float(v[g * 8 + 4]) * inv, __uint_as_float(v[g * 8 + 5]) * inv);
-            u.w = pack_bf16(__uint_as_float(v[g * 8 + 6]) * inv, __uint_as_float(v[g * 8 + 7]) * inv);
-            *reinterpret_cast<uint4*>(yrow + c * 32 + g * 8) = u;
+            u[g].x = pack_bf16(__uint_as_float(v[g * 8 + 0]) * inv, __uint_as_float(v[g * 8 + 1]) * inv);
+            u[g].y = pack_bf16(__uint_as_float(v[g * 8 + 2]) * inv, __uint_as_float(v[g * 8 + 3]) * inv);
+            u[g].z = pack_bf16(__uint_as_float(v[g * 8 + 4]) * inv, __uint_as_float(v[g * 8 + 5]) * inv);
+            u[g].w = pack_bf16(__uint_as_float(v[g * 8 + 6]) * inv, __uint_as_float(v[g * 8 + 7]) * inv);
           }
+          st_global_v8(yrow + c * 32, u[0], u[1]);       // one full 32-byte sector per store
+          st_global_v8(yrow + c * 32 + 16, u[2], u[3]);
         }
         if (half == 0) p.lse[((long long)b * p.H + h) * p.T + qpos] = logf(l) + p.shift_ln;
       }
