@@ -16,6 +16,7 @@
 // Replaces the reference's bf16 GEMM primitives (round1/source/train.py:926-1052) and fused ReLU^2 MLP GEMMs
 // (round2/source/kernels/nki_mlp_fused.py) with one tcgen05 kernel.
 #include "common.cuh"
+#include "gemm_epilogue.cuh"
 
 namespace bones {
 
@@ -177,6 +178,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
     }
   } else {
     const int q = warp & 3;
+    const bool f32out = p.epi == EPI_ACC_F32 || p.epi == EPI_F32 || p.epi == EPI_F32_RES;
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
@@ -198,99 +200,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         tmem_ld_wait();
         const int col0 = nb * BN + c * 32;
         if (row_ok && col0 < p.N) {
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * p.alpha;
-        const bool fullc = col0 + 32 <= p.N;
-        if (p.epi == EPI_BF16 || p.epi == EPI_BF16_RES || p.epi == EPI_RELU2 || p.epi == EPI_MUL_2SQRT) {
-          __nv_bfloat16* D = reinterpret_cast<__nv_bfloat16*>(p.D) + drow + col0;
-          const __nv_bfloat16* R = reinterpret_cast<const __nv_bfloat16*>(p.R) + rrow + col0;
-          if (fullc) {
-            if (p.epi == EPI_BF16_RES || p.epi == EPI_MUL_2SQRT) {
-              uint4 rr[4];
-              if (p.wide) {
-                ld_global_v8(R, rr[0], rr[1]);
-                ld_global_v8(R + 16, rr[2], rr[3]);
-              } else {
-                for (int j = 0; j < 4; ++j) rr[j] = *reinterpret_cast<const uint4*>(R + j * 8);
-              }
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const uint4 u = rr[j];
-                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                  const float2 f = unpack_bf16(w[t]);
-                  if (p.epi == EPI_BF16_RES) {
-                    v[j * 8 + 2 * t] += p.beta * f.x;
-                    v[j * 8 + 2 * t + 1] += p.beta * f.y;
-                  } else {
-                    v[j * 8 + 2 * t] *= 2.0f * sqrtf(f.x);
-                    v[j * 8 + 2 * t + 1] *= 2.0f * sqrtf(f.y);
-                  }
-                }
-              }
-            } else if (p.epi == EPI_RELU2) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                const float t = fmaxf(v[j], 0.0f);
-                v[j] = t * t;
-              }
-            }
-            uint4 uu[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              uu[j].x = pack_bf16(v[j * 8 + 0], v[j * 8 + 1]);
-              uu[j].y = pack_bf16(v[j * 8 + 2], v[j * 8 + 3]);
-              uu[j].z = pack_bf16(v[j * 8 + 4], v[j * 8 + 5]);
-              uu[j].w = pack_bf16(v[j * 8 + 6], v[j * 8 + 7]);
-            }
-            if (p.wide) {      // one full 32-byte sector per store
-              st_global_v8(D, uu[0], uu[1]);
-              st_global_v8(D + 16, uu[2], uu[3]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(D + j * 8) = uu[j];
-            }
-          } else {
-            for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
-              float x = v[j];
-              if (p.epi == EPI_BF16_RES) x += p.beta * __bfloat162float(R[j]);
-              else if (p.epi == EPI_MUL_2SQRT) x *= 2.0f * sqrtf(__bfloat162float(R[j]));
-              else if (p.epi == EPI_RELU2) { x = fmaxf(x, 0.0f); x = x * x; }
-              D[j] = __float2bfloat16(x);
-            }
-          }
-        } else {
-          float* D = reinterpret_cast<float*>(p.D) + drow + col0;
-          const float* R = reinterpret_cast<const float*>(p.R) + rrow + col0;
-          if (fullc) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              float4 o = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-              if (p.epi == EPI_ACC_F32) {
-                if (p.splits > 1) {
-                  atomicAdd(reinterpret_cast<float4*>(D + 4 * j), o);
-                  continue;
-                }
-                const float4 d = *reinterpret_cast<const float4*>(D + 4 * j);
-                o.x += d.x; o.y += d.y; o.z += d.z; o.w += d.w;
-              } else if (p.epi == EPI_F32_RES) {
-                const float4 d = *reinterpret_cast<const float4*>(R + 4 * j);
-                o.x += p.beta * d.x; o.y += p.beta * d.y; o.z += p.beta * d.z; o.w += p.beta * d.w;
-              }
-              *reinterpret_cast<float4*>(D + 4 * j) = o;
-            }
-          } else {
-            for (int j = 0; j < 32 && col0 + j < p.N; ++j) {
-              float x = v[j];
-              if (p.epi == EPI_ACC_F32 && p.splits > 1) { atomicAdd(D + j, x); continue; }
-              if (p.epi == EPI_ACC_F32) x += D[j];
-              else if (p.epi == EPI_F32_RES) x += p.beta * R[j];
-              D[j] = x;
-            }
-          }
-        }
+          const size_t esz = f32out ? 4 : 2;
+          const uint4 none[4] = {};
+          gemm_store_chunk(r, p.epi, p.alpha, p.beta, p.wide != 0, p.splits > 1, reinterpret_cast<uint8_t*>(p.D) + (drow + col0) * esz,
+                           reinterpret_cast<const uint8_t*>(p.R) + (rrow + col0) * esz, false, none, min(32, p.N - col0));
         }
       }
       tc_fence_before();
@@ -389,7 +302,9 @@ int bones_gemm_bf16(const void* A, const void* B, void* D, const void* R, int M,
   p.D = D; p.ldd = ldd; p.strideD = strideD;
   p.R = R ? R : D; p.ldr = R ? ldr : ldd; p.strideR = R ? strideR : strideD;
   p.err = error_word();
-  p.wide = (!f32out && (ldd % 16 == 0) && (!R || ldr % 16 == 0) && (((uintptr_t)D & 31) == 0) && (!R || ((uintptr_t)R & 31) == 0)) ? 1 : 0;
+  const long long wal = f32out ? 8 : 16;     // elements per 32 bytes
+  p.wide = ((ldd % wal == 0) && (strideD % wal == 0) && (!R || (ldr % wal == 0 && strideR % wal == 0)) && (((uintptr_t)D & 31) == 0) &&
+            (!R || ((uintptr_t)R & 31) == 0)) ? 1 : 0;
   p.splits = splits;
   CUtensorMap ta, tb;
   int rc = operand_tmap(&ta, A, a_major, M, K, lda, strideA, batch, BM);

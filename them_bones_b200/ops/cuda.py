@@ -61,6 +61,16 @@ def mm_nn(x, w, out=None, epi=L.EPI_BF16, r=None, alpha=1.0, beta=1.0):
     return out
 
 
+def mm_nn_acc(x, w, out32):
+    """``out32 [M,K] (fp32) += x[M,N] @ w[N,K]``: the fp32 accumulate form lets a long contraction over few output tiles be
+    split across the SMs (split-K with vector atomics)"""
+    m, n = x.shape
+    k = w.shape[1]
+    L.gemm(x, w, out32, m=m, n=k, k=n, lda=x.stride(0), ldb=w.stride(0), ldd=out32.stride(0), b_major=1, epi=L.EPI_ACC_F32)
+    COUNTS["gemm"] += 1
+    return out32
+
+
 def mm_tn_acc(dy, x, grad, alpha=1.0):
     """``grad [N,K] (fp32) += alpha * dy[M,N]^T @ x[M,K]`` (both operands MN-major: contraction over rows)"""
     m, n = dy.shape
@@ -280,7 +290,8 @@ class _LmHeadLossFn(torch.autograd.Function):
         tg = _c(targets).view(-1).to(torch.int64)
         nll = torch.empty(m, dtype=torch.float32, device=x.device)
         n_valid = (tg >= 0).sum().float().reshape(1)
-        dx = torch.empty_like(x2) if want_grad else None
+        # dX contracts over the whole vocabulary into few output tiles: accumulated in fp32 so the contraction can be split
+        dx32 = torch.zeros(x2.shape, dtype=torch.float32, device=x.device) if want_grad else None
         rw = _c(row_weights).view(-1).float() if row_weights is not None else None
         vp = w.shape[0]
         grad_w = getattr(w, "main_grad", None)
@@ -296,9 +307,10 @@ class _LmHeadLossFn(torch.autograd.Function):
                    L.ptr(lg if want_grad else None), L.ptr(rw[r0:r1] if rw is not None else None), L.ptr(n_valid),
                    _F(1.0 / loss_div), _I(r1 - r0), L.stream())
             if want_grad:
-                mm_nn(lg, w, out=dx[r0:r1])
+                mm_nn_acc(lg, w, dx32[r0:r1])
                 mm_tn_acc(lg, x2[r0:r1], grad_w)
         COUNTS["lmhead_loss"] += 1
+        dx = dx32.to(x2.dtype) if want_grad else None
         ctx.dx, ctx.shp, ctx.own_gw, ctx.wdtype = dx, shp, own_gw, w.dtype
         if rw is not None:
             loss = (nll * rw).sum()
