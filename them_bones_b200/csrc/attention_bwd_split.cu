@@ -84,20 +84,27 @@ __device__ __forceinline__ void drain_row64(uint32_t taddr, __nv_bfloat16* dst) 
   }
 }
 
-// stats[b,h,t] = (-lse * log2(e), sum_d dO * O)
+// stats[b,h,t] = (-lse * log2(e), sum_d dO * O); sixteen lanes per (row, head), 16 bytes of each operand per lane
 __global__ void attn_bwd_stats_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ y,
                                       const float* __restrict__ lse, float2* __restrict__ stats, long long M, int T, int H) {
-  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (w >= M * H) return;
-  const int h = (int)(w % H);
-  const long long row = w / H;
-  const long long off = row * H * 128 + (long long)h * 128 + lane * 4;
-  const uint2 a = *reinterpret_cast<const uint2*>(dy + off), c = *reinterpret_cast<const uint2*>(y + off);
-  const float2 a0 = unpack_bf16(a.x), a1 = unpack_bf16(a.y), c0 = unpack_bf16(c.x), c1 = unpack_bf16(c.y);
-  float s = a0.x * c0.x + a0.y * c0.y + a1.x * c1.x + a1.y * c1.y;
-  s = warp_sum(s);
-  if (lane == 0) {
+  const long long item = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 4;
+  const int l16 = threadIdx.x & 15;
+  const long long total = M * H;
+  const long long it = item < total ? item : total - 1;      // every lane takes part in the shuffles
+  const int h = (int)(it % H);
+  const long long row = it / H;
+  const long long off = it * 128 + l16 * 8;                  // == row * H * 128 + h * 128 + ...
+  const uint4 a = *reinterpret_cast<const uint4*>(dy + off), c = *reinterpret_cast<const uint4*>(y + off);
+  const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, cw[4] = {c.x, c.y, c.z, c.w};
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 fa = unpack_bf16(aw[i]), fc = unpack_bf16(cw[i]);
+    s += fa.x * fc.x + fa.y * fc.y;
+  }
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (l16 == 0 && item < total) {
     const long long b = row / T, t = row % T;
     const long long i = (b * H + h) * T + t;
     stats[i] = make_float2(-lse[i] * kLog2e, s);
@@ -539,8 +546,8 @@ using namespace bones;
 
 // stats: [B, H, T] float2 scratch filled by the pre-pass
 int bones_attn_bwd_stats(const void* dy, const void* y, const float* lse, void* stats, long long M, int T, int H, void* stream) {
-  const long long warps = M * H;
-  attn_bwd_stats_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)y,
+  const long long threads = M * H * 16;
+  attn_bwd_stats_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)y,
                                                                                        lse, (float2*)stats, M, T, H);
   return (int)cudaGetLastError();
 }

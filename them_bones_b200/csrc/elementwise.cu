@@ -136,7 +136,7 @@ __global__ void resid_mix_norm_fwd_kernel(const __nv_bfloat16* x, const __nv_bfl
 // g = dxm + rmsnorm_bwd(xm, dxn);  dx = a*g;  dx0 = b*g;  da += sum(g*x);  db += sum(g*x0)
 __global__ void resid_mix_norm_bwd_kernel(const __nv_bfloat16* x, const __nv_bfloat16* x0, const __nv_bfloat16* xm, const float* a,
                                           const float* b, const __nv_bfloat16* dxm, const __nv_bfloat16* dxn, __nv_bfloat16* dx,
-                                          __nv_bfloat16* dx0, float* da, float* db, int M, int C) {
+                                          __nv_bfloat16* dx0, float* da, float* db, int M, int C, int acc_x0) {
   __shared__ float s_da[32], s_db[32];
   const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x * (blockDim.x >> 5) + wid;
@@ -161,6 +161,14 @@ __global__ void resid_mix_norm_bwd_kernel(const __nv_bfloat16* x, const __nv_bfl
     for (int i = 0; i < kMaxVec; ++i)
 #pragma unroll
       for (int t = 0; t < 8; ++t) rt.v[i][t] = fb * rg.v[i][t];
+    if (acc_x0) {                       // dx0 accumulates the contributions of all blocks that read x0
+      RowRegs ro;
+      load_row(dx0 + (size_t)row * C, C, lane, ro);
+#pragma unroll
+      for (int i = 0; i < kMaxVec; ++i)
+#pragma unroll
+        for (int t = 0; t < 8; ++t) rt.v[i][t] += ro.v[i][t];
+    }
     store_row(dx0 + (size_t)row * C, C, lane, rt);
 #pragma unroll
     for (int i = 0; i < kMaxVec; ++i)
@@ -243,7 +251,7 @@ __global__ void __launch_bounds__(256, 2)
 resid_mix_norm_bwd_packed_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ x0,
                                  const __nv_bfloat16* __restrict__ xm, const float* __restrict__ a, const float* __restrict__ b,
                                  const __nv_bfloat16* __restrict__ dxm, const __nv_bfloat16* __restrict__ dxn,
-                                 __nv_bfloat16* __restrict__ dx, __nv_bfloat16* __restrict__ dx0, float* da, float* db, int M) {
+                                 __nv_bfloat16* __restrict__ dx, __nv_bfloat16* dx0, float* da, float* db, int M, int acc_x0) {
   constexpr int C = NV * 256;
   __shared__ float s_da[8], s_db[8];
   const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -290,6 +298,12 @@ resid_mix_norm_bwd_packed_kernel(const __nv_bfloat16* __restrict__ x, const __nv
         pb += g * f0[t];
         o[t] = fb * g;
         fn[t] = fa * g;
+      }
+      if (acc_x0) {                     // dx0 accumulates the contributions of all blocks that read x0
+        float old[8];
+        unpack8(*reinterpret_cast<const uint4*>(dx0 + off + i * 256), old);
+#pragma unroll
+        for (int t = 0; t < 8; ++t) o[t] += old[t];
       }
       *reinterpret_cast<uint4*>(dx0 + off + i * 256) = pack8(o);
       *reinterpret_cast<uint4*>(dx + off + i * 256) = pack8(fn);
@@ -678,13 +692,13 @@ int bones_resid_mix_norm_fwd(const void* x, const void* x0, const float* a, cons
   return (int)cudaGetLastError();
 }
 int bones_resid_mix_norm_bwd(const void* x, const void* x0, const void* xm, const float* a, const float* b, const void* dxm, const void* dxn,
-                             void* dx, void* dx0, float* da, float* db, int M, int C, void* stream) {
+                             void* dx, void* dx0, float* da, float* db, int M, int C, int acc_x0, void* stream) {
   if (C % 8 || C > kMaxVec * 256) return -2;
 #define BONES_MIX_BWD_CASE(NV)                                                                                                   \
   case NV:                                                                                                                       \
     resid_mix_norm_bwd_packed_kernel<NV><<<ROW_GRID(M), 0, (cudaStream_t)stream>>>(                                              \
         (const __nv_bfloat16*)x, (const __nv_bfloat16*)x0, (const __nv_bfloat16*)xm, a, b, (const __nv_bfloat16*)dxm,            \
-        (const __nv_bfloat16*)dxn, (__nv_bfloat16*)dx, (__nv_bfloat16*)dx0, da, db, M);                                          \
+        (const __nv_bfloat16*)dxn, (__nv_bfloat16*)dx, (__nv_bfloat16*)dx0, da, db, M, acc_x0);                                  \
     return (int)cudaGetLastError();
   if (C % 256 == 0) {
     switch (C / 256) {
@@ -694,7 +708,7 @@ int bones_resid_mix_norm_bwd(const void* x, const void* x0, const void* xm, cons
   }
   resid_mix_norm_bwd_kernel<<<ROW_GRID(M), 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)x, (const __nv_bfloat16*)x0, (const __nv_bfloat16*)xm, a, b, (const __nv_bfloat16*)dxm, (const __nv_bfloat16*)dxn,
-      (__nv_bfloat16*)dx, (__nv_bfloat16*)dx0, da, db, M, C);
+      (__nv_bfloat16*)dx, (__nv_bfloat16*)dx0, da, db, M, C, acc_x0);
   return (int)cudaGetLastError();
 }
 int bones_gather_rows(const void* table, const void* idx, int idx_is_64, void* out, int n, int C, long long n_rows, void* stream) {

@@ -86,10 +86,10 @@ class Block(nn.Module):
         self.x0_lambda = nn.Parameter(torch.zeros(1))
         self.ve_lambda = nn.Parameter(torch.zeros(1)) if has_ve else None
 
-    def forward(self, x, x0, cos, sin, doc_start, ve=None, moe_aux=None):
-        x, xn = ops.resid_mix_norm(x, x0, self.resid_lambda, self.x0_lambda)
+    def forward(self, x, x0, cos, sin, doc_start, ve=None, moe_aux=None, x0_acc=None):
+        x, xn = ops.resid_mix_norm(x, x0, self.resid_lambda, self.x0_lambda, x0_acc)
         x = self.attn(xn, cos, sin, doc_start, ve, self.ve_lambda, residual=x)
-        xn = ops.rms_norm(x)
+        x, xn = ops.norm_split(x)
         if isinstance(self.mlp, MoeMLP):
             return self.mlp(xn, residual=x, moe_aux=moe_aux)
         return self.mlp(xn, residual=x)
@@ -218,6 +218,7 @@ class GPT(nn.Module):
         cos, sin = self.cos[:t], self.sin[:t]
         x = ops.rms_norm(self.embed(idx, doc_start, table_rows))
         x0 = x
+        x0_acc = ops.x0_accumulator(x)
         skips = []
         n_layer, n_skip = cfg.n_layer, self.n_skip
         for i, blk in enumerate(self.transformer.h):
@@ -227,7 +228,7 @@ class GPT(nn.Module):
             ve = None
             if self.value_embeds is not None and str(i) in self.value_embeds:
                 ve = ops.embedding(idx, self.value_embeds[str(i)].weight, x.dtype)
-            x = blk(x, x0, cos, sin, doc_start, ve, moe_aux)
+            x = blk(x, x0, cos, sin, doc_start, ve, moe_aux, x0_acc)
             if n_skip and i < n_skip:
                 skips.append(x)
         return ops.rms_norm(x)

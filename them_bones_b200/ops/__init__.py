@@ -55,10 +55,22 @@ def rms_norm(x):
     return RF.rms_norm(x)
 
 
-def resid_mix_norm(x, x0, a, b):
+def norm_split(x):
+    """``(x, rms_norm(x))`` for ``x + f(norm(x))``: natively the pass-through gradient is added inside the norm backward."""
+    if native(x):
+        return _cuda().norm_split(x)
+    return x, RF.rms_norm(x)
+
+
+def x0_accumulator(x):
+    """Per-forward accumulator for the gradient of the shared ``x0`` operand of ``resid_mix_norm`` (native path only)."""
+    return _cuda().X0Accum() if native(x) and torch.is_grad_enabled() else None
+
+
+def resid_mix_norm(x, x0, a, b, acc=None):
     """``x' = a*x + b*x0`` and ``rms_norm(x')`` in one pass."""
     if native(x):
-        return _cuda().resid_mix_norm(x, x0, a, b)
+        return _cuda().resid_mix_norm(x, x0, a, b, acc)
     xm = RF.resid_mix(x, x0, a, b)
     return xm, RF.rms_norm(xm)
 

@@ -198,9 +198,53 @@ def rms_norm(x):
     return _RmsNormFn.apply(x)
 
 
+class _NormSplitFn(torch.autograd.Function):
+    """``x -> (x, rms_norm(x))`` for the ``x + f(norm(x))`` pattern: the backward adds the gradient of the pass-through
+    copy inside the norm-backward kernel instead of leaving a separate accumulation to autograd."""
+
+    @staticmethod
+    def forward(ctx, x):
+        x2 = _c(x).view(-1, x.shape[-1])
+        y = torch.empty_like(x2)
+        L.call("bones_rmsnorm_fwd", L.ptr(x2), L.ptr(y), _I(x2.shape[0]), _I(x2.shape[1]), L.stream())
+        ctx.save_for_backward(x2)
+        COUNTS["rmsnorm"] += 1
+        return x.view(x.shape), y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dx_pass, dy):
+        (x2,) = ctx.saved_tensors
+        if dy is None:
+            return dx_pass
+        dy2 = _c(dy).view(x2.shape)
+        add = _c(dx_pass).view(x2.shape) if dx_pass is not None else None
+        dx = torch.empty_like(x2)
+        L.call("bones_rmsnorm_bwd", L.ptr(x2), L.ptr(dy2), L.ptr(add), L.ptr(dx), _I(x2.shape[0]), _I(x2.shape[1]), L.stream())
+        return dx.view(dy.shape)
+
+
+def norm_split(x):
+    if x.dtype != BF16:
+        from ..ref import functional as RF
+        return x, RF.rms_norm(x)
+    return _NormSplitFn.apply(x)
+
+
+class X0Accum:
+    """Shared by the blocks of one forward pass: their backward passes add the gradient of the common ``x0`` operand into
+    one buffer inside the kernel, and the first block (the last to run backward) hands the sum to autograd."""
+
+    def __init__(self):
+        self.pending = 0
+        self.buf = None
+
+
 class _ResidMixNormFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, x0, a, b):
+    def forward(ctx, x, x0, a, b, acc=None):
+        ctx.acc = acc
+        if acc is not None:
+            acc.pending += 1
         x2, x02 = _c(x).view(-1, x.shape[-1]), _c(x0).view(-1, x.shape[-1])
         xm, xn = torch.empty_like(x2), torch.empty_like(x2)
         af, bf = a.detach().float().reshape(1), b.detach().float().reshape(1)
@@ -219,16 +263,25 @@ class _ResidMixNormFn(torch.autograd.Function):
         if dxn is None:
             dxn = torch.zeros_like(xm)
         dxm2, dxn2 = _c(dxm).view(x2.shape), _c(dxn).view(x2.shape)
-        dx, dx0 = torch.empty_like(x2), torch.empty_like(x2)
+        acc = ctx.acc
+        dx = torch.empty_like(x2)
+        accumulate = acc is not None and acc.buf is not None
+        dx0 = acc.buf if accumulate else torch.empty_like(x2)
         dab = torch.zeros(2, dtype=torch.float32, device=x2.device)
         L.call("bones_resid_mix_norm_bwd", L.ptr(x2), L.ptr(x02), L.ptr(xm), L.ptr(af), L.ptr(bf), L.ptr(dxm2),
                L.ptr(dxn2), L.ptr(dx), L.ptr(dx0), L.ptr(dab[0:1]), L.ptr(dab[1:2]), _I(x2.shape[0]), _I(x2.shape[1]),
-               L.stream())
-        return dx.view(ctx.shape), dx0.view(ctx.shape), dab[0:1], dab[1:2]
+               _I(int(accumulate)), L.stream())
+        if acc is not None:
+            acc.buf = dx0
+            acc.pending -= 1
+            if acc.pending > 0:
+                return dx.view(ctx.shape), None, dab[0:1], dab[1:2], None
+            acc.buf = None
+        return dx.view(ctx.shape), dx0.view(ctx.shape), dab[0:1], dab[1:2], None
 
 
-def resid_mix_norm(x, x0, a, b):
-    return _ResidMixNormFn.apply(x, x0, a, b)
+def resid_mix_norm(x, x0, a, b, acc=None):
+    return _ResidMixNormFn.apply(x, x0, a, b, acc)
 
 
 # -- embedding -------------------------------------------------------------------------------------------------------
