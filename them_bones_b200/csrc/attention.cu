@@ -346,42 +346,76 @@ __device__ __forceinline__ int attn_first_tile(const AttnParams& p, int b, int q
   return lo;
 }
 
+// Persistent forward: one CTA per SM walks (query tile, head, batch) items.  Consecutive items are the query tiles of one
+// (head, batch), so the CTAs that run at one time share their K/V tiles through L2 (dealing the heaviest tiles of all
+// heads first made every CTA stream its own K/V from DRAM at once); the tile order is rotated from one (head, batch) to
+// the next so that every CTA sees a mix of lengths.  All barrier phases run on across items: the producer loads the next
+// item's Q and K/V while the current item computes, the MMA thread issues the next item's first S tiles while the softmax
+// warps finish the current one, and the output accumulator is double-buffered in TMEM so the drain of item i happens
+// after the first softmax tile of item i+1.
+//   TMEM: S/P buffers at columns 0 and 128 (by running tile count), O buffers at 256 and 384 (by item parity).
+//   smem: Q x 2 (item parity), K x 2 and V x 3 stages (running tile count): a K stage is free again once its S tile is
+//   done, a V stage only after its O MMAs, so K and V rings of different depth keep the loads a full tile ahead.
+struct FwdItem {
+  int qt, h, b, kt0, n;
+};
+__device__ __forceinline__ FwdItem fwd_item(const AttnParams& p, int w, int n_tiles) {
+  FwdItem it;
+  const int grp = w / n_tiles;
+  it.qt = n_tiles - 1 - (w % n_tiles + grp) % n_tiles;
+  it.h = grp % p.H;
+  it.b = grp / p.H;
+  it.kt0 = attn_first_tile(p, it.b, it.qt);
+  it.n = it.qt - it.kt0 + 1;
+  return it;
+}
+
 __global__ void __launch_bounds__(320, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - raw);
-  const uint32_t sQ = base;
-  auto sK = [&](int s) { return base + TILE_BYTES * (1 + 2 * s); };
-  auto sV = [&](int s) { return base + TILE_BYTES * (2 + 2 * s); };
-  const uint32_t bars = base + TILE_BYTES * 7;
-  const uint32_t q_full = bars;
-  auto kv_full = [&](int s) { return bars + 8u * (1 + s); };      // three K/V stages
-  auto kv_free = [&](int s) { return bars + 8u * (4 + s); };
-  auto s_full = [&](int s) { return bars + 8u * (7 + s); };       // two S buffers
-  auto p_full = [&](int s) { return bars + 8u * (9 + s); };
-  const uint32_t o_full = bars + 8u * 11;
-  const uint32_t tmem_slot = bars + 8u * 12;
-  volatile uint32_t* tmem_slot_g = reinterpret_cast<volatile uint32_t*>(gen + TILE_BYTES * 7 + 96);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + TILE_BYTES * 7 + 104);
+  auto sQ = [&](int s) { return base + TILE_BYTES * s; };
+  auto sK = [&](int s) { return base + TILE_BYTES * (2 + s); };
+  auto sV = [&](int s) { return base + TILE_BYTES * (4 + s); };
+  constexpr uint32_t kBars = TILE_BYTES * 7;
+  const uint32_t bars = base + kBars;
+  auto q_full = [&](int s) { return bars + 8u * (0 + s); };
+  auto q_free = [&](int s) { return bars + 8u * (2 + s); };
+  auto k_full = [&](int s) { return bars + 8u * (4 + s); };
+  auto k_free = [&](int s) { return bars + 8u * (6 + s); };
+  auto v_full = [&](int s) { return bars + 8u * (8 + s); };
+  auto v_free = [&](int s) { return bars + 8u * (11 + s); };
+  auto s_full = [&](int s) { return bars + 8u * (14 + s); };
+  auto p_full = [&](int s) { return bars + 8u * (16 + s); };
+  auto o_full = [&](int s) { return bars + 8u * (18 + s); };
+  auto o_free = [&](int s) { return bars + 8u * (20 + s); };
+  const uint32_t tmem_slot = bars + 8u * 22;
+  volatile uint32_t* tmem_slot_g = reinterpret_cast<volatile uint32_t*>(gen + kBars + 176);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + kBars + 184);
+  float* lsum = reinterpret_cast<float*>(gen + kBars + 256);           // [2 halves][128 rows]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x;   // heaviest (latest) query tiles first
-  const int h = blockIdx.y, b = blockIdx.z;
   const int A = p.H * AD;
+  const int n_tiles = p.T / AT;
+  const int total = n_tiles * p.H * p.B;
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
-    for (int s = 0; s < 3; ++s) {
-      mbar_init(kv_full(s), 1);
-      mbar_init(kv_free(s), 1);
-    }
     for (int s = 0; s < 2; ++s) {
+      mbar_init(q_full(s), 1);
+      mbar_init(q_free(s), 1);
+      mbar_init(k_full(s), 1);
+      mbar_init(k_free(s), 1);
       mbar_init(s_full(s), 1);
       mbar_init(p_full(s), 8);
+      mbar_init(o_full(s), 1);
+      mbar_init(o_free(s), 8);
     }
-    mbar_init(o_full, 1);
+    for (int s = 0; s < 3; ++s) {
+      mbar_init(v_full(s), 1);
+      mbar_init(v_free(s), 1);
+    }
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tm_qk);
@@ -396,147 +430,185 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot_g;
-  const uint32_t tS[2] = {tmem, tmem + 128};
-  const uint32_t tO = tmem + 256;
-
-  const int kt0 = attn_first_tile(p, b, qt);
-  const int n = qt - kt0 + 1;
-  const int row0 = b * p.T;
+  auto tS = [&](int s) { return tmem + (uint32_t)s * 128u; };
+  auto tO = [&](int s) { return tmem + 256u + (uint32_t)s * 128u; };
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_arrive_expect_tx(q_full, TILE_BYTES);
-      tma_load_2d(sQ, &tm_qk, q_full, h * AD, row0 + qt * AT);
-      tma_load_2d(sQ + ATOM_BYTES, &tm_qk, q_full, h * AD + 64, row0 + qt * AT);
-      for (int j = 0; j < n; ++j) {
-        const int s = j % 3;
-        if (j >= 3 && !mbar_wait(kv_free(s), (uint32_t)(((j - 3) / 3) & 1), abort_flag, p.err, ERR_WAIT_EMPTY)) break;
-        mbar_arrive_expect_tx(kv_full(s), 2 * TILE_BYTES);
-        const int r = row0 + (kt0 + j) * AT;
-        tma_load_2d(sK(s), &tm_qk, kv_full(s), A + h * AD, r);
-        tma_load_2d(sK(s) + ATOM_BYTES, &tm_qk, kv_full(s), A + h * AD + 64, r);
-        tma_load_2d(sV(s), &tm_v, kv_full(s), 2 * A + h * AD, r);
-        tma_load_2d(sV(s) + ATOM_BYTES, &tm_v, kv_full(s), 2 * A + h * AD + 64, r);
+      int g = 0, it = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total && ok; w += gridDim.x, ++it) {
+        const FwdItem im = fwd_item(p, w, n_tiles);
+        const int qb = it & 1, row0 = im.b * p.T;
+        if (it >= 2 && !mbar_wait(q_free(qb), (uint32_t)(((it - 2) >> 1) & 1), abort_flag, p.err, ERR_WAIT_EMPTY)) break;
+        mbar_arrive_expect_tx(q_full(qb), TILE_BYTES);
+        tma_load_2d(sQ(qb), &tm_qk, q_full(qb), im.h * AD, row0 + im.qt * AT);
+        tma_load_2d(sQ(qb) + ATOM_BYTES, &tm_qk, q_full(qb), im.h * AD + 64, row0 + im.qt * AT);
+        for (int j = 0; j < im.n; ++j, ++g) {
+          const int ks = g & 1, vs = g % 3;
+          const int r = row0 + (im.kt0 + j) * AT;
+          if (g >= 2 && !mbar_wait(k_free(ks), (uint32_t)(((g - 2) >> 1) & 1), abort_flag, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+          mbar_arrive_expect_tx(k_full(ks), TILE_BYTES);
+          tma_load_2d(sK(ks), &tm_qk, k_full(ks), A + im.h * AD, r);
+          tma_load_2d(sK(ks) + ATOM_BYTES, &tm_qk, k_full(ks), A + im.h * AD + 64, r);
+          if (g >= 3 && !mbar_wait(v_free(vs), (uint32_t)(((g - 3) / 3) & 1), abort_flag, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+          mbar_arrive_expect_tx(v_full(vs), TILE_BYTES);
+          tma_load_2d(sV(vs), &tm_v, v_full(vs), 2 * A + im.h * AD, r);
+          tma_load_2d(sV(vs) + ATOM_BYTES, &tm_v, v_full(vs), 2 * A + im.h * AD + 64, r);
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t idesc_s = umma_idesc_f16(128, 128, 1, 0, 0);   // Q (K-major) x K (K-major)
-      const uint32_t idesc_o = umma_idesc_f16(128, 128, 1, 0, 1);   // P (K-major) x V (MN-major)
-      // P(j) sits in TMEM as packed bf16 pairs over the S(j) columns it was computed from (each softmax warp packs its
-      // 64 columns into the first 32 of its own range) and is the A operand of O += P V straight from there
-      auto issue_pv = [&](int j) -> bool {
-        const int s = j & 1, st = j % 3;
-        if (!mbar_wait(p_full(s), (j >> 1) & 1, abort_flag, p.err, ERR_WAIT_AUX)) return false;
+      const uint32_t idesc_o = umma_idesc_f16(128, 128, 1, 0, 1);   // P (TMEM) x V (MN-major)
+      // the O += P V step of a tile is issued one tile late, behind the next tile's S, so the softmax of tile g runs
+      // under the S MMAs of tile g+1.  P(g) sits in TMEM as packed bf16 pairs over the S(g) columns it was computed
+      // from (each softmax warp packs its 64 columns into the first 32 of its own range).
+      int pg = -1, p_item = 0;
+      bool p_first = false, p_last = false;
+      auto issue_pv = [&]() -> bool {
+        const int sb = pg & 1, ob = p_item & 1, vs = pg % 3;
+        if (!mbar_wait(v_full(vs), (uint32_t)((pg / 3) & 1), abort_flag, p.err, ERR_WAIT_FULL)) return false;
+        if (!mbar_wait(p_full(sb), (uint32_t)((pg >> 1) & 1), abort_flag, p.err, ERR_WAIT_AUX)) return false;
+        if (p_first && p_item >= 2 &&
+            !mbar_wait(o_free(ob), (uint32_t)(((p_item - 2) >> 1) & 1), abort_flag, p.err, ERR_WAIT_TMEM_EMPTY))
+          return false;
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          const uint64_t bd = umma_smem_desc(sV(st) + k * 2048, ATOM_BYTES, 1024, kLayoutSw128);
-          umma_f16_ts(tO, tS[s] + (uint32_t)((k & 3) * 8 + (k >> 2) * 64), bd, idesc_o, (j | k) ? 1u : 0u);
+          const uint64_t bd = umma_smem_desc(sV(vs) + k * 2048, ATOM_BYTES, 1024, kLayoutSw128);
+          umma_f16_ts(tO(ob), tS(sb) + (uint32_t)((k & 3) * 8 + (k >> 2) * 64), bd, idesc_o, (p_first && k == 0) ? 0u : 1u);
         }
-        tc_commit(kv_free(st));
+        tc_commit(v_free(vs));
+        if (p_last) tc_commit(o_full(ob));
         return true;
       };
-      bool ok = mbar_wait(q_full, 0, abort_flag, p.err, ERR_WAIT_FULL);
-      for (int j = 0; j < n && ok; ++j) {
-        const int s = j & 1, st = j % 3;
-        if (!mbar_wait(kv_full(st), (uint32_t)((j / 3) & 1), abort_flag, p.err, ERR_WAIT_FULL)) { ok = false; break; }
-        tc_fence_after();
-        // S(j) overwrites the buffer that held P(j-2): its O MMAs were issued earlier on the same (in-order) pipe
+      int g = 0, it = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total && ok; w += gridDim.x, ++it) {
+        const FwdItem im = fwd_item(p, w, n_tiles);
+        const int qb = it & 1;
+        if (!mbar_wait(q_full(qb), (uint32_t)((it >> 1) & 1), abort_flag, p.err, ERR_WAIT_FULL)) break;
+        for (int j = 0; j < im.n; ++j, ++g) {
+          const int sb = g & 1;
+          if (!mbar_wait(k_full(sb), (uint32_t)((g >> 1) & 1), abort_flag, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          // S(g) overwrites the buffer that held P(g-2): its O MMAs were issued earlier on the same (in-order) pipe
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t off = (k >> 2) * ATOM_BYTES + (k & 3) * 32;
-          umma_f16(tS[s], umma_smem_desc(sQ + off, 0, 1024, kLayoutSw128), umma_smem_desc(sK(st) + off, 0, 1024, kLayoutSw128),
-                   idesc_s, k ? 1u : 0u);
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t off = (k >> 2) * ATOM_BYTES + (k & 3) * 32;
+            umma_f16(tS(sb), umma_smem_desc(sQ(qb) + off, 0, 1024, kLayoutSw128), umma_smem_desc(sK(sb) + off, 0, 1024, kLayoutSw128),
+                     idesc_s, k ? 1u : 0u);
+          }
+          tc_commit(s_full(sb));
+          tc_commit(k_free(sb));
+          if (j == im.n - 1) tc_commit(q_free(qb));
+          if (pg >= 0 && !issue_pv()) { ok = false; break; }
+          pg = g; p_item = it; p_first = j == 0; p_last = j == im.n - 1;
         }
-        tc_commit(s_full(s));
-        if (j >= 1) ok = issue_pv(j - 1);
       }
-      if (ok) ok = issue_pv(n - 1);
-      if (ok) tc_commit(o_full);
+      if (ok && pg >= 0) issue_pv();
     }
   } else {
     // Softmax: eight warps, two per 32-lane TMEM quadrant; each thread owns one query row and 64 of the tile's 128 keys.
     const int q = warp & 3, half = (warp - 2) >> 2;
     const int r = q * 32 + lane;            // row within the tile == TMEM lane
     const int c0 = half * 64;
-    const int qpos = qt * AT + r;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-    int lo = 0;
-    if (p.doc_start) lo = p.doc_start[(long long)b * p.T + qpos];
-    float l = 0.f;
-    bool ok = true;
-    for (int j = 0; j < n; ++j) {
-      const int s = j & 1;
-      const bool got = mbar_wait(s_full(s), (j >> 1) & 1, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
-      if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+    // the drain of an item's output is deferred until the first tile of the next item has been exponentiated
+    bool pend = false, ok = true;
+    int pend_it = 0;
+    float pend_inv = 0.f;
+    __nv_bfloat16* pend_y = nullptr;
+    auto drain = [&]() -> bool {
+      const int ob = pend_it & 1;
+      const bool got = mbar_wait(o_full(ob), (uint32_t)((pend_it >> 1) & 1), abort_flag, p.err, ERR_WAIT_TMEM_FULL);
+      if (!__all_sync(0xffffffffu, got)) return false;
       tc_fence_after();
-      const int k0 = (kt0 + j) * AT + c0;
-      // warp-uniform: does any row of this warp need the element mask for these 64 keys (diagonal or document start)?
-      const bool need_mask = __any_sync(0xffffffffu, (k0 + 63 > qpos) || (k0 < lo));
-      uint32_t v0[32], v1[32], pk[32];
-      __syncwarp();
-      BONES_TMEM_LD32(tS[s] + lane_addr + (uint32_t)c0, v0);
-      BONES_TMEM_LD32(tS[s] + lane_addr + (uint32_t)(c0 + 32), v1);
-      tmem_ld_wait();
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        float e[32];
+        uint32_t v[32];
+        __syncwarp();
+        BONES_TMEM_LD32(tO(ob) + lane_addr + (uint32_t)(c0 + c * 32), v);
+        tmem_ld_wait();
+        uint4 u[4];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float x = fmaf(__uint_as_float(c ? v1[i] : v0[i]), p.c1, -p.c2);
-          asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e[i]) : "f"(x));
+        for (int gq = 0; gq < 4; ++gq) {
+          u[gq].x = pack_bf16(__uint_as_float(v[gq * 8 + 0]) * pend_inv, __uint_as_float(v[gq * 8 + 1]) * pend_inv);
+          u[gq].y = pack_bf16(__uint_as_float(v[gq * 8 + 2]) * pend_inv, __uint_as_float(v[gq * 8 + 3]) * pend_inv);
+          u[gq].z = pack_bf16(__uint_as_float(v[gq * 8 + 4]) * pend_inv, __uint_as_float(v[gq * 8 + 5]) * pend_inv);
+          u[gq].w = pack_bf16(__uint_as_float(v[gq * 8 + 6]) * pend_inv, __uint_as_float(v[gq * 8 + 7]) * pend_inv);
         }
-        if (need_mask) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int kpos = k0 + c * 32 + i;
-            if (kpos > qpos || kpos < lo) e[i] = 0.f;
-          }
-        }
-#pragma unroll
-        for (int i = 0; i < 32; ++i) l += e[i];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) pk[c * 16 + i] = pack_bf16(e[2 * i], e[2 * i + 1]);
+        st_global_v8(pend_y + c * 32, u[0], u[1]);       // one full 32-byte sector per store
+        st_global_v8(pend_y + c * 32 + 16, u[2], u[3]);
       }
-      BONES_TMEM_ST32(tS[s] + lane_addr + (uint32_t)c0, pk);
-      tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full(s));
-    }
-    // the two threads of a row exchange their partial row sums through shared memory (the Q tile is dead by now only
-    // after the last S MMA, so a dedicated 1 KB scratch after the barriers is used)
-    float* lsum = reinterpret_cast<float*>(gen + TILE_BYTES * 7 + 128);
-    lsum[half * AT + r] = l;
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-    l += lsum[(half ^ 1) * AT + r];
-    if (ok) {
-      const bool got = mbar_wait(o_full, 0, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
-      if (__all_sync(0xffffffffu, got)) {
+      if (lane == 0) mbar_arrive(o_free(ob));
+      pend = false;
+      return true;
+    };
+    int g = 0, it = 0;
+    for (int w = blockIdx.x; w < total && ok; w += gridDim.x, ++it) {
+      const FwdItem im = fwd_item(p, w, n_tiles);
+      const int qpos = im.qt * AT + r, row0 = im.b * p.T;
+      int lo = 0;
+      if (p.doc_start) lo = p.doc_start[(long long)im.b * p.T + qpos];
+      float l = 0.f;
+      for (int j = 0; j < im.n; ++j, ++g) {
+        const int sb = g & 1;
+        const bool got = mbar_wait(s_full(sb), (uint32_t)((g >> 1) & 1), abort_flag, p.err, ERR_WAIT_TMEM_FULL);
+        if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
         tc_fence_after();
-        const float inv = 1.0f / l;
-        __nv_bfloat16* yrow = p.y + ((long long)(row0 + qpos)) * A + (long long)h * AD + c0;
+        const int k0 = (im.kt0 + j) * AT + c0;
+        // warp-uniform: does any row of this warp need the element mask for these 64 keys (diagonal or document start)?
+        const bool need_mask = __any_sync(0xffffffffu, (k0 + 63 > qpos) || (k0 < lo));
+        uint32_t v0[32], v1[32], pk[32];
+        __syncwarp();
+        BONES_TMEM_LD32(tS(sb) + lane_addr + (uint32_t)c0, v0);
+        BONES_TMEM_LD32(tS(sb) + lane_addr + (uint32_t)(c0 + 32), v1);
+        tmem_ld_wait();
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
-          uint32_t v[32];
-          __syncwarp();
-          BONES_TMEM_LD32(tO + lane_addr + (uint32_t)(c0 + c * 32), v);
-          tmem_ld_wait();
-          uint4 u[4];
+          float e[32];
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            u[g].x = pack_bf16(__uint_as_float(v[g * 8 + 0]) * inv, __uint_as_float(v[g * 8 + 1]) * inv);
-            u[g].y = pack_bf16(__uint_as_float(v[g * 8 + 2]) * inv, __uint_as_float(v[g * 8 + 3]) * inv);
-            u[g].z = pack_bf16(__uint_as_float(v[g * 8 + 4]) * inv, __uint_as_float(v[g * 8 + 5]) * inv);
-            u[g].w = pack_bf16(__uint_as_float(v[g * 8 + 6]) * inv, __uint_as_float(v[g * 8 + 7]) * inv);
+          for (int i = 0; i < 32; ++i) {
+            const float x = fmaf(__uint_as_float(c ? v1[i] : v0[i]), p.c1, -p.c2);
+            asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e[i]) : "f"(x));
           }
-          st_global_v8(yrow + c * 32, u[0], u[1]);       // one full 32-byte sector per store
-          st_global_v8(yrow + c * 32 + 16, u[2], u[3]);
+          if (need_mask) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int kpos = k0 + c * 32 + i;
+              if (kpos > qpos || kpos < lo) e[i] = 0.f;
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) l += e[i];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) pk[c * 16 + i] = pack_bf16(e[2 * i], e[2 * i + 1]);
         }
-        if (half == 0) p.lse[((long long)b * p.H + h) * p.T + qpos] = logf(l) + p.shift_ln;
+        BONES_TMEM_ST32(tS(sb) + lane_addr + (uint32_t)c0, pk);
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_full(sb));
+        if (pend && !drain()) { ok = false; break; }
       }
+      if (!ok) break;
+      // the two threads of a row exchange their partial row sums through shared memory
+      lsum[half * AT + r] = l;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      l += lsum[(half ^ 1) * AT + r];
+      asm volatile("bar.sync 1, 256;" ::: "memory");      // nobody rewrites the scratch before everybody has read it
+      if (half == 0) p.lse[((long long)im.b * p.H + im.h) * p.T + qpos] = logf(l) + p.shift_ln;
+      pend = true;
+      pend_it = it;
+      pend_inv = 1.0f / l;
+      pend_y = p.y + ((long long)(row0 + qpos)) * A + (long long)im.h * AD + c0;
     }
+    if (ok && pend) drain();
   }
 
   tc_fence_before();
@@ -623,13 +695,17 @@ int bones_attn_fwd(const void* qk, const void* qkv, void* y, float* lse, const i
   p.y = (__nv_bfloat16*)y;
   p.lse = lse;
   p.err = error_word();
-  constexpr size_t smem = (size_t)TILE_BYTES * 7 + 128 + 1024 + 1024;   // tiles, barriers, row-sum scratch, alignment slack
+  constexpr size_t smem = (size_t)TILE_BYTES * 7 + 256 + 1024 + 1024;   // tiles, barriers, row-sum scratch, alignment slack
   static bool attr_done = false;
   if (!attr_done) {
     BONES_CHECK(cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attr_done = true;
   }
-  dim3 grid(T / AT, H, B);
+  int dev = 0, sms = 0;
+  BONES_CHECK(cudaGetDevice(&dev));
+  BONES_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const long long items = (long long)(T / AT) * H * B;
+  const unsigned grid = (unsigned)(items < sms ? items : sms);       // persistent: one CTA per SM
   attn_fwd_kernel<<<grid, 320, smem, (cudaStream_t)stream>>>(tq, tv, p);
   return (int)cudaGetLastError();
 }

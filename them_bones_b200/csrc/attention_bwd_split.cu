@@ -388,7 +388,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_const
   tc_fence_after();
   const uint32_t tmem = *tmem_slot_g;
   const uint32_t tS = tmem, tdQ = tmem + 384;
-  const uint32_t tdP[2] = {tmem + 128, tmem + 256};
+  auto tdP = [&](int s) { return tmem + 128u + (uint32_t)s * 128u; };
 
   const int kt0 = split_first_tile(p, b, qt);
   const int n = qt - kt0 + 1;
@@ -425,7 +425,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_const
         for (int k = 0; k < 8; ++k) umma_f16(tS, sdesc_k(sQ, k), sdesc_k(sK(0), k), id_kk, k ? 1u : 0u);
         tc_commit(bar(B_SFULL));
 #pragma unroll
-        for (int k = 0; k < 8; ++k) umma_f16(tdP[0], sdesc_k(sdO, k), sdesc_k(sV(0), k), id_kk, k ? 1u : 0u);
+        for (int k = 0; k < 8; ++k) umma_f16(tdP(0), sdesc_k(sdO, k), sdesc_k(sV(0), k), id_kk, k ? 1u : 0u);
         tc_commit(bar(B_DPFULL0));
       }
       for (int j = 0; j < n && ok; ++j) {
@@ -440,14 +440,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_const
           for (int k = 0; k < 8; ++k) umma_f16(tS, sdesc_k(sQ, k), sdesc_k(sK(s ^ 1), k), id_kk, k ? 1u : 0u);
           tc_commit(bar(B_SFULL));
 #pragma unroll
-          for (int k = 0; k < 8; ++k) umma_f16(tdP[s ^ 1], sdesc_k(sdO, k), sdesc_k(sV(s ^ 1), k), id_kk, k ? 1u : 0u);
+          for (int k = 0; k < 8; ++k) umma_f16(tdP(s ^ 1), sdesc_k(sdO, k), sdesc_k(sV(s ^ 1), k), id_kk, k ? 1u : 0u);
           tc_commit(bar(B_DPFULL0 + (s ^ 1)));
         }
         // dS(j) sits packed in the dP(j) columns: dQ += dS Kh(j), which also frees that K/V stage
         if (!mbar_wait(bar(B_DSREADY), (uint32_t)(j & 1), abort_flag, p.err, ERR_WAIT_AUX)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < 8; ++k) umma_f16_ts(tdQ, tdP[s] + packed_col(k), sdesc_mn(sK(s), k), id_km, (j | k) ? 1u : 0u);
+        for (int k = 0; k < 8; ++k) umma_f16_ts(tdQ, tdP(s) + packed_col(k), sdesc_mn(sK(s), k), id_km, (j | k) ? 1u : 0u);
         tc_commit(bar(B_FREE0 + s));
         if (j + 1 == n) tc_commit(bar(B_DONE));
       }
@@ -498,8 +498,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_const
       {
         uint32_t v0[32], v1[32];
         __syncwarp();
-        BONES_TMEM_LD32(tdP[s] + lane_addr + (uint32_t)c0, v0);
-        BONES_TMEM_LD32(tdP[s] + lane_addr + (uint32_t)(c0 + 32), v1);
+        BONES_TMEM_LD32(tdP(s) + lane_addr + (uint32_t)c0, v0);
+        BONES_TMEM_LD32(tdP(s) + lane_addr + (uint32_t)(c0 + 32), v1);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
@@ -507,7 +507,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_const
           pr[32 + i] *= (__uint_as_float(v1[i]) - st.y) * p.scale;
         }
       }
-      store_packed64(tdP[s] + lane_addr + (uint32_t)c0, pr);
+      store_packed64(tdP(s) + lane_addr + (uint32_t)c0, pr);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_DSREADY));
