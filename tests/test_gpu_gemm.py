@@ -130,3 +130,20 @@ def test_pair_gemm_layouts_epilogues_batch():
     L.check_error_word()
     acc = torch.einsum("bmk,bnk->bmn", xb.float(), wb.float())
     assert _rel(o, 0.5 * acc + 2.0 * rb.float()) < 6e-3
+
+
+@pytest.mark.parametrize("pair", [False, True])
+def test_gemm_softcap_epilogue(pair):
+    """Logit soft-capping fused into the GEMM epilogue: ``cap * tanh(x @ w.T / cap)`` in bf16."""
+    from them_bones_b200.ops import _lib as L
+    torch.manual_seed(2)
+    m, n, k, cap = 512, 1000, 256, 15.0
+    x = torch.randn(m, k, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(n, k, device="cuda", dtype=torch.bfloat16)
+    out = torch.zeros(m, 1008, device="cuda", dtype=torch.bfloat16)
+    L.gemm(x, w, out, m=m, n=n, k=k, lda=k, ldb=k, ldd=1008, epi=L.EPI_SOFTCAP, alpha=1.0 / cap, beta=cap, pair=pair)
+    torch.cuda.synchronize()
+    L.check_error_word()
+    ref = cap * torch.tanh(x.float() @ w.float().T / cap)
+    assert float((out[:, :n].float() - ref).abs().max()) < 0.08
+    assert float(out[:, n:].float().abs().sum()) == 0.0

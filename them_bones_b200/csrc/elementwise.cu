@@ -473,7 +473,7 @@ __global__ void moe_combine_bwd_kernel(const __nv_bfloat16* __restrict__ ys, con
 // is written in place: d l = w * (softmax(z) - onehot) * (1 - tanh^2).  Bounded logits (|z| <= cap) make a max pass
 // unnecessary: exp(z - cap) never overflows.
 __global__ void softcap_ce_kernel(const __nv_bfloat16* logits, long long ldl, const long long* targets, int V, float cap, float* nll,
-                                  __nv_bfloat16* dlogits, const float* row_w, const float* n_valid, float inv_loss_div, int M) {
+                                  __nv_bfloat16* dlogits, const float* row_w, const float* n_valid, float inv_loss_div, int M, int capped) {
   const int row = blockIdx.x;
   if (row >= M) return;
   const __nv_bfloat16* l = logits + (size_t)row * ldl;
@@ -488,7 +488,8 @@ __global__ void softcap_ce_kernel(const __nv_bfloat16* logits, long long ldl, co
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
       const float2 f = unpack_bf16(w[t]);
-      s += __expf(cap * tanhf(f.x * inv_cap) - cap) + __expf(cap * tanhf(f.y * inv_cap) - cap);
+      const float t0 = capped ? f.x * inv_cap : tanhf(f.x * inv_cap), t1 = capped ? f.y * inv_cap : tanhf(f.y * inv_cap);
+      s += __expf(cap * t0 - cap) + __expf(cap * t1 - cap);
     }
   }
   s = warp_sum(s);
@@ -504,7 +505,7 @@ __global__ void softcap_ce_kernel(const __nv_bfloat16* logits, long long ldl, co
   const bool valid = tgt >= 0 && tgt < V;
   if (threadIdx.x == 0) {
     float out = 0.f;
-    if (valid) out = lse - cap * tanhf(__bfloat162float(l[tgt]) * inv_cap);
+    if (valid) out = lse - (capped ? __bfloat162float(l[tgt]) : cap * tanhf(__bfloat162float(l[tgt]) * inv_cap));
     nll[row] = out;
   }
   if (!dlogits) return;
@@ -518,7 +519,7 @@ __global__ void softcap_ce_kernel(const __nv_bfloat16* logits, long long ldl, co
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
       const float2 f = unpack_bf16(wd[t]);
-      const float t0 = tanhf(f.x * inv_cap), t1 = tanhf(f.y * inv_cap);
+      const float t0 = capped ? f.x * inv_cap : tanhf(f.x * inv_cap), t1 = capped ? f.y * inv_cap : tanhf(f.y * inv_cap);
       float p0 = __expf(cap * t0 - lse), p1 = __expf(cap * t1 - lse);
       if (c + 2 * t == tgt) p0 -= 1.0f;
       if (c + 2 * t + 1 == tgt) p1 -= 1.0f;
@@ -545,7 +546,7 @@ __device__ __forceinline__ float tanh_fast(float x) {
 __global__ void __launch_bounds__(1024, 1)
 softcap_ce_row_kernel(const __nv_bfloat16* __restrict__ logits, long long ldl, const long long* __restrict__ targets, int V, float cap,
                       float* __restrict__ nll, __nv_bfloat16* dlogits, const float* __restrict__ row_w, const float* __restrict__ n_valid,
-                      float inv_loss_div, int M) {
+                      float inv_loss_div, int M, int capped) {
   const int row = blockIdx.x;
   if (row >= M) return;
   const __nv_bfloat16* l = logits + (size_t)row * ldl;
@@ -569,7 +570,8 @@ softcap_ce_row_kernel(const __nv_bfloat16* __restrict__ logits, long long ldl, c
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
       const float2 f = unpack_bf16(w[t]);
-      const float t0 = tanh_fast(f.x * inv_cap), t1 = tanh_fast(f.y * inv_cap);
+      // `capped`: the GEMM epilogue already applied cap * tanh(. / cap), only the scaling is left
+      const float t0 = capped ? f.x * inv_cap : tanh_fast(f.x * inv_cap), t1 = capped ? f.y * inv_cap : tanh_fast(f.y * inv_cap);
       th[i][t] = __floats2half2_rn(t0, t1);
       if (c < V) s += exp2f(k2 * t0 - k2) + exp2f(k2 * t1 - k2);
     }
@@ -587,7 +589,7 @@ softcap_ce_row_kernel(const __nv_bfloat16* __restrict__ logits, long long ldl, c
   const bool valid = tgt >= 0 && tgt < V;
   if (threadIdx.x == 0) {
     float out = 0.f;
-    if (valid) out = lse2 * 0.6931471805599453f - cap * tanh_fast(__bfloat162float(l[tgt]) * inv_cap);
+    if (valid) out = lse2 * 0.6931471805599453f - (capped ? __bfloat162float(l[tgt]) : cap * tanh_fast(__bfloat162float(l[tgt]) * inv_cap));
     nll[row] = out;
   }
   if (!dlogits) return;
@@ -748,15 +750,15 @@ int bones_moe_combine_bwd(const void* ys, const long long* slot, const float* ga
   return (int)cudaGetLastError();
 }
 int bones_softcap_ce(const void* logits, long long ldl, const long long* targets, int V, float cap, float* nll, void* dlogits,
-                     const float* row_w, const float* n_valid, float inv_loss_div, int M, void* stream) {
+                     const float* row_w, const float* n_valid, float inv_loss_div, int M, int capped, void* stream) {
   if (V % 8 || ldl % 8) return -2;
   if (V <= 65536 && V >= 8192) {
     softcap_ce_row_kernel<<<M, 1024, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, ldl, targets, V, cap, nll,
-                                                                (__nv_bfloat16*)dlogits, row_w, n_valid, inv_loss_div, M);
+                                                                (__nv_bfloat16*)dlogits, row_w, n_valid, inv_loss_div, M, capped);
     return (int)cudaGetLastError();
   }
   softcap_ce_kernel<<<M, 512, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, ldl, targets, V, cap, nll, (__nv_bfloat16*)dlogits,
-                                                        row_w, n_valid, inv_loss_div, M);
+                                                        row_w, n_valid, inv_loss_div, M, capped);
   return (int)cudaGetLastError();
 }
 int bones_softcap_logits(const void* logits, long long ldl, float* out, int V, float cap, long long rows, void* stream) {

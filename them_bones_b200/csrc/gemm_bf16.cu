@@ -28,6 +28,7 @@ enum Epi : int {
   EPI_MUL_2SQRT = 4,   // D(bf16) = alpha*acc * 2*sqrt(R(bf16))
   EPI_F32 = 5,         // D(f32)  = alpha*acc
   EPI_F32_RES = 6,     // D(f32)  = alpha*acc + beta*R(f32)
+  EPI_SOFTCAP = 7,     // D(bf16) = beta * tanh(alpha*acc)
 };
 
 struct GemmParams {

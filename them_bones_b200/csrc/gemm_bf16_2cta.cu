@@ -23,7 +23,7 @@
 
 namespace bones {
 
-enum Epi2 : int { E2_BF16 = 0, E2_BF16_RES = 1, E2_RELU2 = 2, E2_ACC_F32 = 3, E2_MUL_2SQRT = 4, E2_F32 = 5, E2_F32_RES = 6 };
+enum Epi2 : int { E2_BF16 = 0, E2_BF16_RES = 1, E2_RELU2 = 2, E2_ACC_F32 = 3, E2_MUL_2SQRT = 4, E2_F32 = 5, E2_F32_RES = 6, E2_SOFTCAP = 7 };
 
 struct Gemm2Params {
   int M, N, K, batch;

@@ -6,8 +6,14 @@
 
 namespace bones {
 
-enum GemmEpi : int { GE_BF16 = 0, GE_BF16_RES = 1, GE_RELU2 = 2, GE_ACC_F32 = 3, GE_MUL_2SQRT = 4, GE_F32 = 5, GE_F32_RES = 6 };
+enum GemmEpi : int { GE_BF16 = 0, GE_BF16_RES = 1, GE_RELU2 = 2, GE_ACC_F32 = 3, GE_MUL_2SQRT = 4, GE_F32 = 5, GE_F32_RES = 6,
+                     GE_SOFTCAP = 7 };   // D(bf16) = beta * tanh(alpha * acc): logit soft-capping with alpha = 1 / cap, beta = cap
 
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float sqrt_fast(float x) {
   float y;
   asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -26,7 +32,7 @@ __device__ __forceinline__ void gemm_store_chunk(const uint32_t (&acc)[32], int 
 #pragma unroll
   for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(acc[j]) * alpha;
   const bool full = ncols >= 32;
-  if (epi == GE_BF16 || epi == GE_BF16_RES || epi == GE_RELU2 || epi == GE_MUL_2SQRT) {
+  if (epi == GE_BF16 || epi == GE_BF16_RES || epi == GE_RELU2 || epi == GE_MUL_2SQRT || epi == GE_SOFTCAP) {
     __nv_bfloat16* D = reinterpret_cast<__nv_bfloat16*>(Dv);
     const __nv_bfloat16* R = reinterpret_cast<const __nv_bfloat16*>(Rv);
     if (epi == GE_BF16_RES || epi == GE_MUL_2SQRT) {
@@ -66,6 +72,9 @@ __device__ __forceinline__ void gemm_store_chunk(const uint32_t (&acc)[32], int 
         const float t = fmaxf(v[j], 0.0f);
         v[j] = t * t;
       }
+    } else if (epi == GE_SOFTCAP) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = beta * tanh_approx(v[j]);
     }
     if (full) {
       uint4 uu[4];

@@ -65,7 +65,7 @@ def check_error_word():
         raise RuntimeError(f"a native kernel reported error code {rc} (bounded wait expired or bad argument)")
 
 
-EPI_BF16, EPI_BF16_RES, EPI_RELU2, EPI_ACC_F32, EPI_MUL_2SQRT, EPI_F32, EPI_F32_RES = range(7)
+EPI_BF16, EPI_BF16_RES, EPI_RELU2, EPI_ACC_F32, EPI_MUL_2SQRT, EPI_F32, EPI_F32_RES, EPI_SOFTCAP = range(8)
 
 
 PAIR_MODE = os.environ.get("BONES_GEMM_PAIR", "auto")      # auto | 0 | 1

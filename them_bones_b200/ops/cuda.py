@@ -355,10 +355,11 @@ class _LmHeadLossFn(torch.autograd.Function):
         for r0 in range(0, m, LOSS_ROWS):
             r1 = min(m, r0 + LOSS_ROWS)
             lg = buf[:r1 - r0]
-            mm_nt(x2[r0:r1], w, out=lg)
+            # the logits GEMM soft-caps in its epilogue (cap * tanh(. / cap)); the loss kernel then only exponentiates
+            mm_nt(x2[r0:r1], w, out=lg, epi=L.EPI_SOFTCAP, alpha=1.0 / cap, beta=cap)
             L.call("bones_softcap_ce", L.ptr(lg), _L(vp), L.ptr(tg[r0:r1]), _I(vocab), _F(cap), L.ptr(nll[r0:r1]),
                    L.ptr(lg if want_grad else None), L.ptr(rw[r0:r1] if rw is not None else None), L.ptr(n_valid),
-                   _F(1.0 / loss_div), _I(r1 - r0), L.stream())
+                   _F(1.0 / loss_div), _I(r1 - r0), _I(1), L.stream())
             if want_grad:
                 mm_nn_acc(lg, w, dx32[r0:r1])
                 mm_tn_acc(lg, x2[r0:r1], grad_w)
