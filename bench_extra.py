@@ -121,7 +121,7 @@ def main():
                               "decode_tokens_per_s": rt.world * a.decode_batch * a.new_tokens / (ms_dec / 1e3),
                               "decode_batch": a.decode_batch, "new_tokens": a.new_tokens, "ms_score": ms_score, "ms_decode": ms_dec,
                               "config": {"model": f"dense {a.depth}Lx1280 replica per rank", "kv_cache": True,
-                                         "scoring_path": "native kernels", "decode_path": "PyTorch with KV cache"},
+                                         "scoring_path": "native kernels", "decode_path": "native kernels in a CUDA graph, KV cache"},
                               "sample": out[0, -4:].tolist(), "mean_score": float(s.mean())}), flush=True)
     if rt.ddp:
         dist.barrier()

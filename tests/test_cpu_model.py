@@ -218,3 +218,62 @@ def test_tables_zero_init_is_identity_then_learns():
     assert float(tr1.tables.shards[0].abs().sum()) > 0       # rows moved
     state = tr1.tables.state_for_checkpoint(quantize=True)
     assert state["table_2"].dtype == torch.int8 and state["table_2_scale"].dtype == torch.bfloat16
+
+
+def test_attention_free_blocks_with_shift_mixer():
+    """Round-1 style stack: attention only in some blocks, the others add a learned multiple of the one-token shift."""
+    from them_bones_b200.utils.evalbpb import causality_check
+    cfg = tiny_cfg(n_layer=4, attn_layers=(0, 2), mixer="shift1", mlp_ratio=6)
+    assert model_config_dict(cfg)["attn_layers"] == [0, 2] and GPTConfig(**model_config_dict(cfg)) == cfg
+    tr, losses = run_steps(cfg, "lean", steps=8)
+    assert losses[-1] < losses[0]
+    names = dict(tr.model.named_parameters())
+    assert "transformer.h.1.mix_lambda" in names and "transformer.h.1.attn.c_q.weight" not in names
+    assert "transformer.h.0.attn.c_q.weight" in names and "transformer.h.0.mix_lambda" not in names
+    assert names["transformer.h.1.mlp.c_fc.weight"].shape == (6 * 256, 256)
+    assert float(names["transformer.h.1.mix_lambda"].abs().sum()) > 0          # the mixer gain was trained
+    x = torch.arange(12.0).view(1, 4, 3)
+    assert torch.equal(RF.shift1(x)[0, 1:], x[0, :-1]) and float(RF.shift1(x)[0, 0].abs().sum()) == 0
+    assert causality_check(tr.model, 8192, 2, 64, "cpu")["passed"]
+
+
+def test_multi_token_prediction_targets_and_schedule():
+    from them_bones_b200.optim.schedules import mtp_weights
+    # the reference's two-target schedule: t+3 fades over the first quarter, t+2 over the second
+    assert mtp_weights(0.0, 2) == (0.5, 0.25)
+    assert mtp_weights(0.125, 2) == pytest.approx((0.5, 0.125))
+    assert mtp_weights(0.375, 2) == pytest.approx((0.25, 0.0))
+    assert mtp_weights(0.5, 2) == (0.0, 0.0) and mtp_weights(0.9, 2) == (0.0, 0.0)
+    torch.manual_seed(0)
+    cfg = tiny_cfg(n_layer=2, mtp_offsets=(2, 3))
+    model = GPT(cfg)
+    model.init_weights()
+    with torch.no_grad():
+        model.lm_head.weight.normal_(0, 0.05)
+    model.train()
+    x = torch.randint(1, 8192, (2, 64))
+    x[:, 0] = 0
+    x[0, 40] = 0
+    y = torch.roll(x, -1, 1)
+    y[:, -1] = -1
+    y[y == 0] = -1                                             # targets that are a document start are not predicted
+    model.set_mtp_weights((0.0, 0.0))
+    base = float(model(x, y))
+    model.set_mtp_weights((0.5, 0.25))
+    terms = model.mtp_terms(y)
+    assert len(terms) == 2
+    t2, w2 = terms[0]
+    assert torch.equal(t2[0, :10], y[0, 1:11]) and int(t2[0, -1]) == -1
+    assert float(w2[0, 38]) == 0.0 and float(w2[0, 39]) == 0.0    # y[0, 39] is masked: nothing is predicted across it
+    assert float(w2[0, 10]) > 0
+    with torch.no_grad():
+        h = model.trunk(x)
+        manual = base
+        for tk, wk in terms:
+            manual += float(RF.softcap_cross_entropy(h, model.lm_head.weight, tk, cfg.vocab_size, cfg.softcap, wk))
+    full = model(x, y)
+    assert float(full) == pytest.approx(manual, rel=1e-5) and float(full) > base
+    full.backward()
+    assert model.lm_head.weight.grad is not None
+    model.eval()
+    assert float(model(x, y)) == pytest.approx(base, rel=1e-6)   # evaluation is next-token only

@@ -79,6 +79,9 @@ class GPTConfig:
     value_embeds: int = 0          # number of value-embedding tables on alternating last layers
     attn_window: int = 0           # sliding window in tokens (multiple of 128) on the layers not in attn_long
     attn_long: tuple = ()          # layers that keep full causal attention when attn_window > 0
+    attn_layers: tuple = ()        # blocks that have attention (empty: all); the others are MLP-only
+    mixer: str = "off"             # "shift1": attention-free blocks add mix_lambda * (x shifted by one token)
+    mtp_offsets: tuple = ()        # extra next-token targets, e.g. (2, 3): predict t+2 and t+3 from position t
     mlp_precision: str = "bf16"    # "bf16" | "mxfp8": block-scaled MLP / expert GEMMs
     moe_layers: tuple = ()
     moe_experts: int = 0
@@ -93,12 +96,16 @@ class GPTConfig:
     table_seed: int = 0
 
     def __post_init__(self):
-        for name in ("attn_long", "moe_layers", "table_orders"):
+        for name in ("attn_long", "moe_layers", "table_orders", "attn_layers", "mtp_offsets"):
             setattr(self, name, tuple(int(v) for v in getattr(self, name)))
         if self.head_dim == 0:
             self.head_dim = self.n_embd // self.n_head
         if self.attn_window and self.attn_window % 128:
             raise ValueError("attn_window must be a multiple of the 128-token attention tile")
+        if self.mixer not in ("off", "shift1"):
+            raise ValueError(f"mixer={self.mixer!r}: expected 'off' or 'shift1'")
+        if any(o < 2 for o in self.mtp_offsets):
+            raise ValueError("mtp_offsets are distances beyond the next token: each must be >= 2")
         if self.mlp_precision not in ("bf16", "mxfp8"):
             raise ValueError(f"mlp_precision={self.mlp_precision!r}")
         if self.moe_layers:
@@ -204,6 +211,8 @@ def switches(refresh: bool = False) -> dict:
         UNET=e("UNET", False, bool), VE=e("VE", 0, int), QK_SCALE=e("QK_SCALE", 0.0, float),
         ROPE_BASE=e("ROPE_BASE", 100000.0, float), DOC_MASK=e("DOC_MASK", False, bool),
         ATTN_WINDOW=e("ATTN_WINDOW", 0, int), ATTN_LONG=e("ATTN_LONG", "", str),
+        ATTN_LAYERS=e("ATTN_LAYERS", "", str), MIXER=e("MIXER", "off", str), MLP_RATIO=e("MLP_RATIO", 4, int),
+        MTP=e("MTP", "", str), MTP_WEIGHT=e("MTP_WEIGHT", 0.5, float), MTP_ANNEAL=e("MTP_ANNEAL", 0.5, float),
         MLP=e("MLP", "bf16", str),
         MOE=e("MOE", False, bool), MOE_LAYERS=e("MOE_LAYERS", "", str), MOE_EXPERTS=e("MOE_EXPERTS", 16, int),
         MOE_TOPK=e("MOE_TOPK", 2, int), MOE_HIDDEN=e("MOE_HIDDEN", 0, int), MOE_SHARED=e("MOE_SHARED", 0, int),
@@ -252,7 +261,12 @@ def build_config(depth: int, n_embd: int, n_head: int, seq_len: int, vocab: int,
     h = hyper or Hyper.from_env()
     kw = dict(sequence_len=seq_len, vocab_size=vocab, n_layer=depth, n_head=n_head, n_embd=n_embd, head_dim=head_dim,
               rope_base=s["ROPE_BASE"], qk_scale=s["QK_SCALE"], bos_id=bos_id, doc_mask=s["DOC_MASK"], unet=s["UNET"],
-              value_embeds=s["VE"], attn_window=s["ATTN_WINDOW"], mlp_precision=s["MLP"])
+              value_embeds=s["VE"], attn_window=s["ATTN_WINDOW"], mlp_precision=s["MLP"], mlp_ratio=s["MLP_RATIO"],
+              mixer=s["MIXER"])
+    if s["ATTN_LAYERS"]:
+        kw["attn_layers"] = parse_layers(s["ATTN_LAYERS"], depth)
+    if s["MTP"]:
+        kw["mtp_offsets"] = tuple(int(v) for v in s["MTP"].split(",") if v.strip())
     if s["ATTN_WINDOW"]:
         kw["attn_long"] = (parse_layers(s["ATTN_LONG"], depth) if s["ATTN_LONG"]
                            else tuple(i for i in range(depth) if i % 4 == 3 or i == depth - 1))

@@ -466,6 +466,14 @@ __global__ void moe_combine_bwd_kernel(const __nv_bfloat16* __restrict__ ys, con
   }
 }
 
+// Up to two auxiliary targets per row (multi-token prediction: the tokens two and three positions ahead) share the
+// row's soft-max: nll_aux = sum_k w_k * (lse - z[target_k]) and the logit gradient gains w_k * (p - onehot_k).
+struct AuxTargets {
+  const long long* tg[2];
+  const float* w[2];        // absolute row weights (0 where the auxiliary target does not apply)
+  float* nll_aux;           // [M], written when any auxiliary target is given
+};
+
 // Softcap cross-entropy over full rows of bf16 logits [M, ldl] (first V columns valid), one CTA per row.
 //   z = cap * tanh(l / cap);  lse = log sum exp z;  nll = lse - z[target]
 // Outputs: nll[row] (0 where target < 0).  With `dlogits` (may alias logits) the gradient of
@@ -473,7 +481,8 @@ __global__ void moe_combine_bwd_kernel(const __nv_bfloat16* __restrict__ ys, con
 // is written in place: d l = w * (softmax(z) - onehot) * (1 - tanh^2).  Bounded logits (|z| <= cap) make a max pass
 // unnecessary: exp(z - cap) never overflows.
 __global__ void softcap_ce_kernel(const __nv_bfloat16* logits, long long ldl, const long long* targets, int V, float cap, float* nll,
-                                  __nv_bfloat16* dlogits, const float* row_w, const float* n_valid, float inv_loss_div, int M, int capped) {
+                                  __nv_bfloat16* dlogits, const float* row_w, const float* n_valid, float inv_loss_div, int M, int capped,
+                                  AuxTargets aux) {
   const int row = blockIdx.x;
   if (row >= M) return;
   const __nv_bfloat16* l = logits + (size_t)row * ldl;
@@ -508,9 +517,20 @@ __global__ void softcap_ce_kernel(const __nv_bfloat16* logits, long long ldl, co
     if (valid) out = lse - (capped ? __bfloat162float(l[tgt]) : cap * tanhf(__bfloat162float(l[tgt]) * inv_cap));
     nll[row] = out;
   }
+  long long t2 = -1, t3 = -1;
+  float a2 = 0.f, a3 = 0.f;
+  if (aux.tg[0]) { t2 = aux.tg[0][row]; a2 = (t2 >= 0 && t2 < V) ? aux.w[0][row] : 0.f; }
+  if (aux.tg[1]) { t3 = aux.tg[1][row]; a3 = (t3 >= 0 && t3 < V) ? aux.w[1][row] : 0.f; }
+  if (threadIdx.x == 0 && aux.nll_aux) {
+    float out = 0.f;
+    if (a2 != 0.f) out += a2 * (lse - (capped ? __bfloat162float(l[t2]) : cap * tanhf(__bfloat162float(l[t2]) * inv_cap)));
+    if (a3 != 0.f) out += a3 * (lse - (capped ? __bfloat162float(l[t3]) : cap * tanhf(__bfloat162float(l[t3]) * inv_cap)));
+    aux.nll_aux[row] = out;
+  }
   if (!dlogits) return;
   float w = 0.f;
   if (valid) w = row_w ? row_w[row] : inv_loss_div / fmaxf(1.0f, *n_valid);
+  const float wsum = w + a2 + a3;
   __nv_bfloat16* d = dlogits + (size_t)row * ldl;
   for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) {
     const uint4 u = *reinterpret_cast<const uint4*>(l + c);
@@ -520,11 +540,16 @@ __global__ void softcap_ce_kernel(const __nv_bfloat16* logits, long long ldl, co
     for (int t = 0; t < 4; ++t) {
       const float2 f = unpack_bf16(wd[t]);
       const float t0 = capped ? f.x * inv_cap : tanhf(f.x * inv_cap), t1 = capped ? f.y * inv_cap : tanhf(f.y * inv_cap);
-      float p0 = __expf(cap * t0 - lse), p1 = __expf(cap * t1 - lse);
-      if (c + 2 * t == tgt) p0 -= 1.0f;
-      if (c + 2 * t + 1 == tgt) p1 -= 1.0f;
-      g[2 * t] = w * p0 * (1.0f - t0 * t0);
-      g[2 * t + 1] = w * p1 * (1.0f - t1 * t1);
+      float p0 = wsum * __expf(cap * t0 - lse), p1 = wsum * __expf(cap * t1 - lse);
+      const int c0i = c + 2 * t, c1i = c0i + 1;
+      if (c0i == tgt) p0 -= w;
+      if (c1i == tgt) p1 -= w;
+      if (c0i == t2) p0 -= a2;
+      if (c1i == t2) p1 -= a2;
+      if (c0i == t3) p0 -= a3;
+      if (c1i == t3) p1 -= a3;
+      g[2 * t] = p0 * (1.0f - t0 * t0);
+      g[2 * t + 1] = p1 * (1.0f - t1 * t1);
     }
     uint4 o;
     o.x = pack_bf16(g[0], g[1]); o.y = pack_bf16(g[2], g[3]); o.z = pack_bf16(g[4], g[5]); o.w = pack_bf16(g[6], g[7]);
@@ -546,7 +571,7 @@ __device__ __forceinline__ float tanh_fast(float x) {
 __global__ void __launch_bounds__(1024, 1)
 softcap_ce_row_kernel(const __nv_bfloat16* __restrict__ logits, long long ldl, const long long* __restrict__ targets, int V, float cap,
                       float* __restrict__ nll, __nv_bfloat16* dlogits, const float* __restrict__ row_w, const float* __restrict__ n_valid,
-                      float inv_loss_div, int M, int capped) {
+                      float inv_loss_div, int M, int capped, AuxTargets aux) {
   const int row = blockIdx.x;
   if (row >= M) return;
   const __nv_bfloat16* l = logits + (size_t)row * ldl;
@@ -592,9 +617,21 @@ softcap_ce_row_kernel(const __nv_bfloat16* __restrict__ logits, long long ldl, c
     if (valid) out = lse2 * 0.6931471805599453f - (capped ? __bfloat162float(l[tgt]) : cap * tanh_fast(__bfloat162float(l[tgt]) * inv_cap));
     nll[row] = out;
   }
+  long long t2 = -1, t3 = -1;
+  float a2 = 0.f, a3 = 0.f;
+  if (aux.tg[0]) { t2 = aux.tg[0][row]; a2 = (t2 >= 0 && t2 < V) ? aux.w[0][row] : 0.f; }
+  if (aux.tg[1]) { t3 = aux.tg[1][row]; a3 = (t3 >= 0 && t3 < V) ? aux.w[1][row] : 0.f; }
+  if (threadIdx.x == 0 && aux.nll_aux) {
+    const float lse = lse2 * 0.6931471805599453f;
+    float out = 0.f;
+    if (a2 != 0.f) out += a2 * (lse - (capped ? __bfloat162float(l[t2]) : cap * tanh_fast(__bfloat162float(l[t2]) * inv_cap)));
+    if (a3 != 0.f) out += a3 * (lse - (capped ? __bfloat162float(l[t3]) : cap * tanh_fast(__bfloat162float(l[t3]) * inv_cap)));
+    aux.nll_aux[row] = out;
+  }
   if (!dlogits) return;
   float w = 0.f;
   if (valid) w = row_w ? row_w[row] : inv_loss_div / fmaxf(1.0f, *n_valid);
+  const float wsum = w + a2 + a3;
   __nv_bfloat16* d = dlogits + (size_t)row * ldl;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
@@ -604,11 +641,16 @@ softcap_ce_row_kernel(const __nv_bfloat16* __restrict__ logits, long long ldl, c
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
       const float2 tt = __half22float2(th[i][t]);
-      float p0 = exp2f(k2 * tt.x - lse2), p1 = exp2f(k2 * tt.y - lse2);
-      if (c + 2 * t == tgt) p0 -= 1.0f;
-      if (c + 2 * t + 1 == tgt) p1 -= 1.0f;
-      g[2 * t] = w * p0 * (1.0f - tt.x * tt.x);
-      g[2 * t + 1] = w * p1 * (1.0f - tt.y * tt.y);
+      float p0 = wsum * exp2f(k2 * tt.x - lse2), p1 = wsum * exp2f(k2 * tt.y - lse2);
+      const int c0i = c + 2 * t, c1i = c0i + 1;
+      if (c0i == tgt) p0 -= w;
+      if (c1i == tgt) p1 -= w;
+      if (c0i == t2) p0 -= a2;
+      if (c1i == t2) p1 -= a2;
+      if (c0i == t3) p0 -= a3;
+      if (c1i == t3) p1 -= a3;
+      g[2 * t] = p0 * (1.0f - tt.x * tt.x);
+      g[2 * t + 1] = p1 * (1.0f - tt.y * tt.y);
     }
     uint4 o;
     o.x = pack_bf16(g[0], g[1]); o.y = pack_bf16(g[2], g[3]); o.z = pack_bf16(g[4], g[5]); o.w = pack_bf16(g[6], g[7]);
@@ -750,15 +792,18 @@ int bones_moe_combine_bwd(const void* ys, const long long* slot, const float* ga
   return (int)cudaGetLastError();
 }
 int bones_softcap_ce(const void* logits, long long ldl, const long long* targets, int V, float cap, float* nll, void* dlogits,
-                     const float* row_w, const float* n_valid, float inv_loss_div, int M, int capped, void* stream) {
+                     const float* row_w, const float* n_valid, float inv_loss_div, int M, int capped, const long long* tg2, const float* w2,
+                     const long long* tg3, const float* w3, float* nll_aux, void* stream) {
   if (V % 8 || ldl % 8) return -2;
+  AuxTargets aux;
+  aux.tg[0] = tg2; aux.w[0] = w2; aux.tg[1] = tg3; aux.w[1] = w3; aux.nll_aux = nll_aux;
   if (V <= 65536 && V >= 8192) {
     softcap_ce_row_kernel<<<M, 1024, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, ldl, targets, V, cap, nll,
-                                                                (__nv_bfloat16*)dlogits, row_w, n_valid, inv_loss_div, M, capped);
+                                                                (__nv_bfloat16*)dlogits, row_w, n_valid, inv_loss_div, M, capped, aux);
     return (int)cudaGetLastError();
   }
   softcap_ce_kernel<<<M, 512, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, ldl, targets, V, cap, nll, (__nv_bfloat16*)dlogits,
-                                                        row_w, n_valid, inv_loss_div, M, capped);
+                                                        row_w, n_valid, inv_loss_div, M, capped, aux);
   return (int)cudaGetLastError();
 }
 int bones_softcap_logits(const void* logits, long long ldl, float* out, int V, float cap, long long rows, void* stream) {

@@ -80,16 +80,24 @@ class MLP(nn.Module):
 class Block(nn.Module):
     def __init__(self, config: GPTConfig, layer: int, has_ve: bool):
         super().__init__()
-        self.attn = CausalSelfAttention(config, layer)
+        # an attention-free block keeps only the MLP; with the "shift1" mixer it first adds a learned multiple of the
+        # stream shifted by one token (reference: round1/source/train.py:300-304, 8808-8868)
+        has_attn = not config.attn_layers or layer in config.attn_layers
+        self.attn = CausalSelfAttention(config, layer) if has_attn else None
         self.mlp = MoeMLP(config, layer) if layer in config.moe_layers else MLP(config)
         self.resid_lambda = nn.Parameter(torch.ones(1))
         self.x0_lambda = nn.Parameter(torch.zeros(1))
-        self.ve_lambda = nn.Parameter(torch.zeros(1)) if has_ve else None
+        self.ve_lambda = nn.Parameter(torch.zeros(1)) if (has_ve and has_attn) else None
+        self.mix_lambda = nn.Parameter(torch.zeros(1)) if (not has_attn and config.mixer == "shift1") else None
 
     def forward(self, x, x0, cos, sin, doc_start, ve=None, moe_aux=None, x0_acc=None):
         x, xn = ops.resid_mix_norm(x, x0, self.resid_lambda, self.x0_lambda, x0_acc)
-        x = self.attn(xn, cos, sin, doc_start, ve, self.ve_lambda, residual=x)
-        x, xn = ops.norm_split(x)
+        if self.attn is not None:
+            x = self.attn(xn, cos, sin, doc_start, ve, self.ve_lambda, residual=x)
+            x, xn = ops.norm_split(x)
+        elif self.mix_lambda is not None:
+            x = x + self.mix_lambda.to(x.dtype) * RF.shift1(x)
+            x, xn = ops.norm_split(x)
         if isinstance(self.mlp, MoeMLP):
             return self.mlp(xn, residual=x, moe_aux=moe_aux)
         return self.mlp(xn, residual=x)
@@ -127,9 +135,10 @@ class GPT(nn.Module):
         nn.init.normal_(self.lm_head.weight, mean=0.0, std=0.001)
         s = math.sqrt(3.0) * cfg.n_embd ** -0.5
         for blk in self.transformer.h:
-            for lin in (blk.attn.c_q, blk.attn.c_k, blk.attn.c_v):
-                nn.init.uniform_(lin.weight, -s, s)
-            nn.init.zeros_(blk.attn.c_proj.weight)
+            if blk.attn is not None:
+                for lin in (blk.attn.c_q, blk.attn.c_k, blk.attn.c_v):
+                    nn.init.uniform_(lin.weight, -s, s)
+                nn.init.zeros_(blk.attn.c_proj.weight)
             if isinstance(blk.mlp, MoeMLP):
                 blk.mlp.init_stream(s)
             else:
@@ -174,7 +183,8 @@ class GPT(nn.Module):
         cfg = self.config
         active = 0
         for blk in self.transformer.h:
-            active += sum(p.numel() for p in blk.attn.parameters())
+            if blk.attn is not None:
+                active += sum(p.numel() for p in blk.attn.parameters())
             if isinstance(blk.mlp, MoeMLP):
                 active += blk.mlp.active_params()
             else:
@@ -182,6 +192,8 @@ class GPT(nn.Module):
         active += self.lm_head.weight.numel()
         attn = 0
         for blk in self.transformer.h:
+            if blk.attn is None:
+                continue
             span = min(blk.attn.window or cfg.sequence_len, cfg.sequence_len)
             attn += 12 * cfg.n_head * cfg.head_dim * span / 2       # causal: half the span on average
         return 6 * active + attn
@@ -196,6 +208,7 @@ class GPT(nn.Module):
         if self.table_lambda is not None:
             out.append(self.table_lambda)
         out.extend(blk.ve_lambda for blk in self.transformer.h if blk.ve_lambda is not None)
+        out.extend(blk.mix_lambda for blk in self.transformer.h if blk.mix_lambda is not None)
         return out
 
     # ---------------------------------------------------------------------------------------------------------
@@ -204,6 +217,33 @@ class GPT(nn.Module):
         if self.tables is not None:
             x = self.tables.add_lookup(x, idx, doc_start, self.table_lambda, rows=table_rows)
         return x
+
+    def set_mtp_weights(self, weights) -> None:
+        """Per-step weights of the extra targets in ``config.mtp_offsets`` (all zero: next-token loss only)."""
+        self.mtp_weights = tuple(float(w) for w in weights)
+
+    def mtp_terms(self, targets, loss_div: float = 1.0):
+        """``(targets_k, row_weights_k)`` for every live extra target: position t also predicts the token ``offset``
+        places ahead, unless a masked target (document start) lies on the way or the window ends first.  Weights carry
+        the schedule weight, the mean over valid next-token targets and ``loss_div`` (reference: ``mtp_terms``,
+        round1/source/train.py:5053-5064, there without the document check)."""
+        offs, ws = self.config.mtp_offsets, getattr(self, "mtp_weights", ())
+        live = [(o, w) for o, w in zip(offs, ws) if w > 0][:2]
+        if not live:
+            return None
+        b, t = targets.shape
+        n_valid = (targets >= 0).sum().clamp_min(1).float()
+        out = []
+        for o, w in live:
+            j = o - 1
+            tk = torch.full_like(targets, -1)
+            tk[:, :t - j] = targets[:, j:]
+            ok = tk >= 0
+            for s in range(j):                                   # every target between t and t+offset must be real
+                ok[:, :t - s] &= targets[:, s:] >= 0
+            tk = torch.where(ok, tk, torch.full_like(tk, -1))
+            out.append((tk, ok.float() * (w / loss_div) / n_valid))
+        return out
 
     def cos_dtype(self):
         return self.lm_head.weight.dtype
@@ -243,8 +283,9 @@ class GPT(nn.Module):
         x = self.trunk(idx, doc_start, moe_aux, table_rows)
         if targets is None:
             return ops.lmhead_logits(x, self.lm_head.weight, cfg.vocab_size, cfg.softcap)
+        aux = self.mtp_terms(targets, loss_div) if (loss_reduction == "mean" and self.training) else None
         loss = ops.lmhead_loss(x, self.lm_head.weight, targets, cfg.vocab_size, cfg.softcap,
-                               reduction=loss_reduction, row_weights=row_weights, loss_div=loss_div)
+                               reduction=loss_reduction, row_weights=row_weights, loss_div=loss_div, aux=aux)
         if loss_reduction != "mean" or moe_aux is None:
             return loss
         aux = torch.stack([a[0] for a in moe_aux]).sum()

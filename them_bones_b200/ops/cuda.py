@@ -336,7 +336,8 @@ class _LmHeadLossFn(torch.autograd.Function):
     ``loss_scaled`` :11712)."""
 
     @staticmethod
-    def forward(ctx, x, w, targets, vocab, cap, loss_div, row_weights, want_grad):
+    def forward(ctx, x, w, targets, vocab, cap, loss_div, row_weights, want_grad, aux=None):
+        # aux: up to two (targets, absolute row weights) pairs that share the row's soft-max (multi-token prediction)
         shp = x.shape
         x2 = _c(x).view(-1, shp[-1])
         m = x2.shape[0]
@@ -352,6 +353,15 @@ class _LmHeadLossFn(torch.autograd.Function):
         if want_grad and grad_w is None:
             own_gw = grad_w = torch.zeros(w.shape, dtype=torch.float32, device=w.device)
         buf = torch.empty(min(LOSS_ROWS, m), vp, dtype=BF16, device=x.device)
+        aux = [(_c(t).view(-1).to(torch.int64), _c(wk).view(-1).float()) for t, wk in (aux or [])][:2]
+        nll_aux = torch.zeros(m, dtype=torch.float32, device=x.device) if aux else None
+
+        def aux_ptrs(r0, r1):
+            out = []
+            for k in range(2):
+                out += [L.ptr(aux[k][0][r0:r1]), L.ptr(aux[k][1][r0:r1])] if k < len(aux) else [L.ptr(None), L.ptr(None)]
+            return out + [L.ptr(nll_aux[r0:r1] if aux else None)]
+
         for r0 in range(0, m, LOSS_ROWS):
             r1 = min(m, r0 + LOSS_ROWS)
             lg = buf[:r1 - r0]
@@ -359,7 +369,7 @@ class _LmHeadLossFn(torch.autograd.Function):
             mm_nt(x2[r0:r1], w, out=lg, epi=L.EPI_SOFTCAP, alpha=1.0 / cap, beta=cap)
             L.call("bones_softcap_ce", L.ptr(lg), _L(vp), L.ptr(tg[r0:r1]), _I(vocab), _F(cap), L.ptr(nll[r0:r1]),
                    L.ptr(lg if want_grad else None), L.ptr(rw[r0:r1] if rw is not None else None), L.ptr(n_valid),
-                   _F(1.0 / loss_div), _I(r1 - r0), _I(1), L.stream())
+                   _F(1.0 / loss_div), _I(r1 - r0), _I(1), *aux_ptrs(r0, r1), L.stream())
             if want_grad:
                 mm_nn_acc(lg, w, dx32[r0:r1])
                 mm_tn_acc(lg, x2[r0:r1], grad_w)
@@ -370,6 +380,8 @@ class _LmHeadLossFn(torch.autograd.Function):
             loss = (nll * rw).sum()
         else:
             loss = nll.sum() / n_valid.clamp_min(1.0)[0] / loss_div
+        if aux:
+            loss = loss + nll_aux.sum()
         ctx.mark_non_differentiable(nll)
         return loss, nll
 
@@ -377,12 +389,12 @@ class _LmHeadLossFn(torch.autograd.Function):
     def backward(ctx, dloss, _dnll):
         dx = ctx.dx.view(ctx.shp) * dloss.to(ctx.dx.dtype)
         gw = ctx.own_gw.to(ctx.wdtype) * dloss.to(ctx.wdtype) if ctx.own_gw is not None else None
-        return dx, gw, None, None, None, None, None, None
+        return dx, gw, None, None, None, None, None, None, None
 
 
-def lmhead_loss(x, w, targets, vocab, cap, reduction="mean", row_weights=None, loss_div=1.0):
+def lmhead_loss(x, w, targets, vocab, cap, reduction="mean", row_weights=None, loss_div=1.0, aux=None):
     want_grad = torch.is_grad_enabled() and (x.requires_grad or w.requires_grad) and reduction == "mean"
-    loss, nll = _LmHeadLossFn.apply(x, w, targets, vocab, cap, float(loss_div), row_weights, want_grad)
+    loss, nll = _LmHeadLossFn.apply(x, w, targets, vocab, cap, float(loss_div), row_weights, want_grad, aux)
     if reduction == "mean":
         return loss
     if reduction == "sum":

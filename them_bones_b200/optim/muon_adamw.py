@@ -209,7 +209,8 @@ def build_param_groups(model, hyper):
     for blk in model.transformer.h:
         resid.append(blk.resid_lambda)
         scalar.append(blk.x0_lambda)
-        matrix.extend(blk.attn.parameters())
+        if blk.attn is not None:
+            matrix.extend(blk.attn.parameters())
         matrix.extend(blk.mlp.trunk_parameters() if isinstance(blk.mlp, MoeMLP) else blk.mlp.parameters())
     scalar.extend(model.arch_gain_params())
     emb = list(model.transformer.wte.parameters())

@@ -36,6 +36,28 @@ def grad_accum_for_step(progress: float, accum: int, half_until: float = 0.0) ->
     return accum
 
 
+def mtp_weights(progress: float, n_targets: int, base: float = 0.5, anneal: float = 0.5) -> tuple:
+    """Weights of the extra multi-token-prediction targets at clock fraction ``progress``.  Target k (k = 0 is t+2)
+    starts at ``base / 2**k``; the annealing window ``[0, anneal]`` is split into ``n_targets`` equal phases and target k
+    falls linearly to zero during phase ``n_targets - 1 - k``, so the farthest target goes first and from ``anneal`` on
+    only the next-token loss is left.  With two targets, base 0.5 and anneal 0.5 this is the reference's schedule
+    (``mtp_set``, round1/source/train.py:5042-5051): t+3 0.25 -> 0 over [0, 1/4), t+2 0.5 flat then -> 0 over [1/4, 1/2)."""
+    if n_targets <= 0:
+        return ()
+    width = anneal / n_targets
+    out = []
+    for k in range(n_targets):
+        start = width * (n_targets - 1 - k)
+        w0 = base / (2 ** k)
+        if width <= 0 or progress >= start + width:
+            out.append(0.0)
+        elif progress <= start:
+            out.append(w0)
+        else:
+            out.append(w0 * (1.0 - (progress - start) / width))
+    return tuple(out)
+
+
 def apply_schedules(optimizer, hyper, step: int, progress: float, tables=None):
     lrm = lr_multiplier(progress, step, hyper.warmup_steps, hyper.warmdown_frac, hyper.final_lr_frac)
     lrm_rows = lr_multiplier(progress, step, hyper.warmup_steps, hyper.rows_warmdown_frac, hyper.rows_final_lr_frac)

@@ -26,6 +26,12 @@ def rms_norm(x: torch.Tensor, eps: float = RMS_EPS) -> torch.Tensor:
     return (xf * torch.rsqrt(xf.square().mean(-1, keepdim=True) + eps)).to(x.dtype)
 
 
+def shift1(x: torch.Tensor) -> torch.Tensor:
+    """Causal one-token shift over the sequence dim of ``[B, T, C]``: row t is input row t-1, row 0 is zeros
+    (reference: round1/source/train.py:300-304)."""
+    return torch.cat((x.new_zeros(x.shape[0], 1, x.shape[2]), x[:, :-1, :]), dim=1)
+
+
 def resid_mix(x, x0, a, b):
     """``x = a * x + b * x0`` with scalar gains."""
     return (a.float() * x.float() + b.float() * x0.float()).to(x.dtype)

@@ -94,6 +94,10 @@ class Trainer:
         else:
             x_all, y_all = inputs, targets
         accum = micro_steps or self.grad_accum
+        if self.config.mtp_offsets:
+            sw = switches()
+            self.model.set_mtp_weights(schedules.mtp_weights(self.progress(), len(self.config.mtp_offsets),
+                                                              sw["MTP_WEIGHT"], sw["MTP_ANNEAL"]))
         db = x_all.shape[0] // self.grad_accum
         opt = self.optimizer
         opt.zero_grad()

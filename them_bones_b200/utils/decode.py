@@ -15,6 +15,11 @@ from ..models.moe import MoeMLP
 from ..ref import functional as RF
 
 
+def L_check():
+    from ..ops import _lib as L
+    L.check_error_word()
+
+
 class KVCache:
     def __init__(self, model, batch: int, max_len: int):
         cfg = model.config
@@ -105,15 +110,114 @@ def _rope_at(x, cos, sin):
     return torch.cat([x1 * c + x2 * s, -x1 * s + x2 * c], -1).to(x.dtype)
 
 
+class NativeDecoder:
+    """One decode step as a CUDA graph over the native kernels: embedding, fused norms, tcgen05 GEMMs, the two decode
+    kernels (``csrc/decode.cu``: RoPE + QK-norm + cache append, cached attention), soft-capped logits, arg-max.  The
+    position, the per-sequence document starts, the current tokens and the output buffer live on the device and are
+    advanced inside the graph, so generating ``n`` tokens is ``n`` graph replays with no host synchronisation.
+    Eligible: dense bf16 models on CUDA whose blocks all have attention with head_dim 128 (no MoE, no hashed tables)."""
+
+    @staticmethod
+    def eligible(model) -> bool:
+        cfg = model.config
+        w = model.lm_head.weight
+        return (w.is_cuda and w.dtype == torch.bfloat16 and cfg.head_dim == 128 and model.tables is None
+                and not ops.reference_path() and all(blk.attn is not None and not isinstance(blk.mlp, MoeMLP)
+                                                     for blk in model.transformer.h))
+
+    def __init__(self, model, cache: KVCache, first_tokens: torch.Tensor, out: torch.Tensor):
+        self.model, self.cache, self.out = model, cache, out
+        dev = first_tokens.device
+        self.tok = first_tokens.clone().to(torch.int64)
+        self.pos = torch.tensor([cache.len], dtype=torch.int32, device=dev)
+        self.graph = None
+        cfg = model.config
+        b, a = self.tok.shape[0], cfg.n_head * cfg.head_dim
+        self.qbuf = torch.empty(b, a, dtype=torch.bfloat16, device=dev)
+        self.y = torch.empty(b, a, dtype=torch.bfloat16, device=dev)
+
+    def _step(self):
+        from ..ops import _lib as L
+        from ..ops import cuda as C
+        model, cache, cfg = self.model, self.cache, self.model.config
+        tok, pos = self.tok, self.pos
+        b, tmax = tok.shape[0], cache.k.shape[2]
+        if cfg.doc_mask:
+            cache.doc_start.copy_(torch.where(tok == cfg.bos_id, pos.expand(b), cache.doc_start))
+        x = ops.rms_norm(ops.embedding(tok, model.transformer.wte.weight, torch.bfloat16))
+        x0 = x
+        skips = []
+        n_layer, n_skip = cfg.n_layer, model.n_skip
+        for i, blk in enumerate(model.transformer.h):
+            if n_skip and i >= n_layer - n_skip:
+                x = x + model.skip_lambda[i - (n_layer - n_skip)].to(x.dtype) * skips.pop()
+            x, xn = ops.resid_mix_norm(x, x0, blk.resid_lambda, blk.x0_lambda)
+            at = blk.attn
+            qkv = ops.linear_qkv(xn, at.c_q.weight, at.c_k.weight, at.c_v.weight)
+            ve = lam = None
+            if model.value_embeds is not None and str(i) in model.value_embeds:
+                ve = ops.embedding(tok, model.value_embeds[str(i)].weight, torch.bfloat16)
+                lam = blk.ve_lambda.detach().float()
+            L.call("bones_decode_qkv", L.ptr(qkv), L.ptr(model.cos), L.ptr(model.sin), L.ptr(ve), L.ptr(lam), L.ptr(self.qbuf),
+                   L.ptr(cache.k[i]), L.ptr(cache.v[i]), L.ptr(pos), C._I(b), C._I(at.n_head), C._I(tmax), L.stream())
+            L.call("bones_decode_attn", L.ptr(self.qbuf), L.ptr(cache.k[i]), L.ptr(cache.v[i]), L.ptr(pos),
+                   L.ptr(cache.doc_start if cfg.doc_mask else None), L.ptr(self.y), C._I(b), C._I(at.n_head), C._I(tmax),
+                   C._F(at.scale), C._I(at.window // 128), L.stream())
+            x = ops.linear(self.y, at.c_proj.weight, residual=x)
+            x, xn = ops.norm_split(x)
+            x = blk.mlp(xn, residual=x)
+            if n_skip and i < n_skip:
+                skips.append(x)
+        xn = ops.rms_norm(x)
+        logits = C.mm_nt(xn, model.lm_head.weight, epi=L.EPI_SOFTCAP, alpha=1.0 / cfg.softcap, beta=cfg.softcap)
+        self.last_logits = logits                                          # [B, padded vocab] bf16, soft-capped
+        nxt = logits[:, :cfg.vocab_size].float().argmax(-1)
+        pos.add_(1)
+        self.out.index_copy_(1, pos.to(torch.int64), nxt[:, None])       # token at position pos (after the increment)
+        tok.copy_(nxt)
+
+    @torch.no_grad()
+    def run(self, n_steps: int):
+        """``n_steps`` decode steps; the first one runs eagerly (it also warms every kernel up), the rest replay the graph."""
+        if n_steps <= 0:
+            return
+        self._step()
+        if n_steps == 1:
+            return
+        if self.graph is None:
+            torch.cuda.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(self.graph, stream=side):
+                    self._step()
+            torch.cuda.current_stream().wait_stream(side)       # capturing does not execute the step
+        for _ in range(n_steps - 1):
+            self.graph.replay()
+
+
 @torch.no_grad()
 def greedy_decode(model, prompts: torch.Tensor, n_new: int) -> torch.Tensor:
     """``prompts [B, P]`` -> ``[B, P + n_new]`` by arg-max decoding."""
     b, p = prompts.shape
     if p + n_new > model.config.sequence_len:
         raise ValueError("prompt + new tokens exceed the model's sequence length")
-    if model.tables is not None:
-        return greedy_decode_full(model, prompts, n_new)
+    if model.tables is not None or any(blk.attn is None for blk in model.transformer.h):
+        return greedy_decode_full(model, prompts, n_new)          # tables and attention-free blocks: cache-free route
     cache = KVCache(model, b, p + n_new)
+    if NativeDecoder.eligible(model) and n_new >= 1:
+        # prefill on the cached PyTorch route, then one CUDA-graph replay per generated token
+        logits = _forward_cached(model, prompts, cache)
+        out = torch.zeros(b, p + n_new, dtype=torch.int64, device=prompts.device)
+        out[:, :p] = prompts
+        first = logits.argmax(-1)
+        out[:, p] = first
+        if n_new > 1:
+            dec = NativeDecoder(model, cache, first, out)
+            dec.run(n_new - 1)
+            L_check()
+        return out
     out = [prompts]
     logits = _forward_cached(model, prompts, cache)
     for _ in range(n_new):
