@@ -194,15 +194,13 @@ def test_native_decode_step_matches_cached_pytorch_route():
             tok = ref.argmax(-1)
         torch.cuda.synchronize()
         L.check_error_word()
-        # whole decode: graph replay reproduces eager stepping of the same kernels
+        # whole decode (stepwise prefill + decode as graph replays) reproduces eager stepping of the same kernels
         full = D.greedy_decode(model, prompts, n_new)
         cc = D.KVCache(model, b, p + n_new)
-        lc = D._forward_cached(model, prompts, cc)
         out2 = torch.zeros_like(full)
         out2[:, :p] = prompts
-        out2[:, p] = lc.argmax(-1)
-        dec2 = D.NativeDecoder(model, cc, out2[:, p].clone(), out2)
-        for _ in range(n_new - 1):
+        dec2 = D.NativeDecoder(model, cc, prompts[:, 0], out2, prompt_len=p)
+        for _ in range(p + n_new - 1):
             dec2._step()
         torch.cuda.synchronize()
     assert torch.equal(full, out2)

@@ -125,9 +125,11 @@ class NativeDecoder:
                 and not ops.reference_path() and all(blk.attn is not None and not isinstance(blk.mlp, MoeMLP)
                                                      for blk in model.transformer.h))
 
-    def __init__(self, model, cache: KVCache, first_tokens: torch.Tensor, out: torch.Tensor):
+    def __init__(self, model, cache: KVCache, first_tokens: torch.Tensor, out: torch.Tensor, prompt_len: int = 0):
+        # positions below ``prompt_len`` are teacher-forced from ``out`` (stepwise prefill through the same graph)
         self.model, self.cache, self.out = model, cache, out
         dev = first_tokens.device
+        self.prompt_len = torch.tensor([prompt_len], dtype=torch.int32, device=dev)
         self.tok = first_tokens.clone().to(torch.int64)
         self.pos = torch.tensor([cache.len], dtype=torch.int32, device=dev)
         self.graph = None
@@ -173,7 +175,10 @@ class NativeDecoder:
         self.last_logits = logits                                          # [B, padded vocab] bf16, soft-capped
         nxt = logits[:, :cfg.vocab_size].float().argmax(-1)
         pos.add_(1)
-        self.out.index_copy_(1, pos.to(torch.int64), nxt[:, None])       # token at position pos (after the increment)
+        at = pos.to(torch.int64)
+        forced = self.out.index_select(1, at)[:, 0]
+        nxt = torch.where((pos < self.prompt_len).expand_as(nxt), forced, nxt)
+        self.out.index_copy_(1, at, nxt[:, None])                         # token at position pos (after the increment)
         tok.copy_(nxt)
 
     @torch.no_grad()
@@ -207,16 +212,21 @@ def greedy_decode(model, prompts: torch.Tensor, n_new: int) -> torch.Tensor:
         return greedy_decode_full(model, prompts, n_new)          # tables and attention-free blocks: cache-free route
     cache = KVCache(model, b, p + n_new)
     if NativeDecoder.eligible(model) and n_new >= 1:
-        # prefill on the cached PyTorch route, then one CUDA-graph replay per generated token
-        logits = _forward_cached(model, prompts, cache)
         out = torch.zeros(b, p + n_new, dtype=torch.int64, device=prompts.device)
         out[:, :p] = prompts
-        first = logits.argmax(-1)
-        out[:, p] = first
-        if n_new > 1:
-            dec = NativeDecoder(model, cache, first, out)
-            dec.run(n_new - 1)
-            L_check()
+        if p <= 512:
+            # short prompts are pre-filled token by token through the same graph (teacher-forced), then decoded
+            dec = NativeDecoder(model, cache, prompts[:, 0], out, prompt_len=p)
+            dec.run(p + n_new - 1)
+        else:
+            # long prompts: prefill on the cached PyTorch route, then one graph replay per generated token
+            logits = _forward_cached(model, prompts, cache)
+            first = logits.argmax(-1)
+            out[:, p] = first
+            if n_new > 1:
+                dec = NativeDecoder(model, cache, first, out)
+                dec.run(n_new - 1)
+        L_check()
         return out
     out = [prompts]
     logits = _forward_cached(model, prompts, cache)
