@@ -206,3 +206,38 @@ def test_stop_rule_shed_plan_and_control():
     ab = AsyncBoundary("cpu", sync_every=3)
     ab.submit(4, torch.tensor(2.5))
     assert ab.collect() == (4, 2.5) and ab.must_sync(6) and not ab.must_sync(7)
+
+
+def test_document_selection_rule():
+    """Token-id selection rules: length band, typicality band after warm-up, duplicate prefix, start phase."""
+    import numpy as np
+
+    from them_bones_b200.data.select import DocRule
+    from them_bones_b200.data.synth import PackedRows, SynthLoader, ZipfDocs
+    src = ZipfDocs(4096, doc_len=(16, 300), seed=3)
+    rule = DocRule.parse("len:32-256,band:0.1-0.9,warm:64,dedup:8,from:0.5", 4096)
+    docs = src.docs(200)
+    rule.phase = 0.0
+    assert all(rule.decide(docs))                                     # before the start phase nothing is dropped
+    rule.phase = 0.6
+    docs = src.docs(400)
+    weird = np.concatenate([[0], 4000 + (np.arange(100) % 90)]).astype(np.int32)   # rare ids only: far from typical
+    docs.append(weird)
+    keep = rule.decide(docs)
+    lens = np.array([len(d) - 1 for d in docs])
+    assert not any(k for k, n in zip(keep, lens) if n < 32 or n > 256)
+    assert keep[-1] is False
+    c = rule.count
+    assert c["drop_length"][1] > 0 and c["drop_band"][1] > 0
+    assert int(c["docs_read"].sum()) == 601 and "kept" in rule.line()
+    dd = DocRule.parse("dedup:8", 4096)
+    dd.phase = 1.0
+    assert dd.decide([docs[5], docs[6], docs[5].copy()]) == [True, True, False] and dd.count["drop_dup"][1] == 1
+    frac = c["docs_kept"][1] / c["docs_read"][1]
+    assert 0.4 < frac < 0.9                                           # the band keeps about 80 % of the in-range documents
+    # the packer only sees accepted documents and still fills its rows
+    ld = SynthLoader(4096, 128, 4, seed=1, doc_len=(16, 300), rule=DocRule.parse("len:64-300", 4096))
+    ld.rule.phase = 1.0
+    x, y = ld.next_step()
+    assert x.shape == (4, 128) and ld.rule.count["drop_length"][1] > 0
+    assert isinstance(ld.rows, PackedRows) and ld.rows.rule is ld.rule

@@ -219,6 +219,7 @@ def switches(refresh: bool = False) -> dict:
         MOE_AUX=e("MOE_AUX", 0.01, float), MOE_ZLOSS=e("MOE_ZLOSS", 0.0, float),
         TABLES=e("TABLES", "", str), TABLE_ROWS=e("TABLE_ROWS", 0, int), TABLE_SEED=e("TABLE_SEED", 0, int),
         TABLE_STALE=e("TABLE_STALE", False, bool), TABLE_HOST_STATE=e("TABLE_HOST_STATE", True, bool),
+        DATA_RULE=e("DATA_RULE", "", str),           # e.g. "len:64-4096,band:0.05-0.95,dedup:32,from:0.1"
         # kernels / system
         KERNELS=e("KERNELS", "auto", str),           # auto: CUDA kernels on a GPU, torch oracle on CPU | ref
         FUSED_COMM=e("FUSED_COMM", True, bool),      # in-kernel NVLink collectives (False: NCCL baseline path)

@@ -49,13 +49,17 @@ class ZipfDocs:
 class PackedRows:
     """Best-fit packer: yields int32 rows of ``row_len + 1`` tokens."""
 
-    def __init__(self, source: ZipfDocs, row_len: int, buffer_docs: int = 512):
+    def __init__(self, source: ZipfDocs, row_len: int, buffer_docs: int = 512, rule=None):
         self.src, self.row_len, self.buffer_docs = source, row_len, buffer_docs
         self.buf: list = []
+        self.rule = rule                     # data.select.DocRule: documents it rejects never enter the buffer
 
     def _refill(self):
-        if len(self.buf) < self.buffer_docs:
-            self.buf.extend(self.src.docs(self.buffer_docs))
+        while len(self.buf) < self.buffer_docs:
+            docs = self.src.docs(self.buffer_docs)
+            if self.rule is not None:
+                docs = [d for d, keep in zip(docs, self.rule.decide(docs)) if keep]
+            self.buf.extend(docs)
 
     def next_row(self) -> np.ndarray:
         need = self.row_len + 1
@@ -94,10 +98,11 @@ class SynthLoader:
     ``inputs [local_windows, T] int32`` and ``targets [local_windows, T] int64``."""
 
     def __init__(self, vocab: int, seq_len: int, local_windows: int, *, rank: int = 0, seed: int = 0,
-                 doc_len=(128, 2048), zipf_s: float = 1.1, bos_id: int = 0, pin: bool = False):
+                 doc_len=(128, 2048), zipf_s: float = 1.1, bos_id: int = 0, pin: bool = False, rule=None):
         self.seq_len, self.local_windows, self.bos_id = seq_len, local_windows, bos_id
         self.docs = ZipfDocs(vocab, zipf_s, doc_len, seed=seed * 1000003 + rank, bos_id=bos_id)
-        self.rows = PackedRows(self.docs, seq_len * local_windows)
+        self.rule = rule
+        self.rows = PackedRows(self.docs, seq_len * local_windows, rule=rule)
         self.pin = pin and torch.cuda.is_available()
         self.epoch = 0
 

@@ -73,8 +73,11 @@ def main(argv=None):
     n_params = tr.model.num_scaling_params()
     print0(f"parameters {n_params:,}; flops/token {tr.flops_per_token:.4e}")
     lo, hi = (int(v) for v in args.doc_len.split(","))
+    from them_bones_b200.data.select import DocRule
+    rule = DocRule.parse(sw["DATA_RULE"], cfg.vocab_size, cfg.bos_id)
     loader = SynthLoader(cfg.vocab_size, cfg.sequence_len, tr.local_windows, rank=rt.rank, seed=hyper.seed,
-                         doc_len=(lo, min(hi, cfg.sequence_len * 4)), bos_id=cfg.bos_id, pin=rt.device_type == "cuda")
+                         doc_len=(lo, min(hi, cfg.sequence_len * 4)), bos_id=cfg.bos_id, pin=rt.device_type == "cuda",
+                         rule=rule)
     if args.compile_only:
         x = torch.zeros(tr.local_windows, cfg.sequence_len, dtype=torch.int32)
         y = torch.zeros(tr.local_windows, cfg.sequence_len, dtype=torch.int64)
@@ -109,6 +112,8 @@ def main(argv=None):
             if loader.seq_len != want:
                 loader.set_seq_len(want)
                 print0(f"step {step}: window length -> {want}")
+        if rule is not None:
+            rule.phase = tr.progress()
         x, y = prefetch.finish() if prefetch else fetch()
         if prefetch:
             prefetch.start()
