@@ -112,24 +112,31 @@ __global__ void attn_bwd_stats_kernel(const __nv_bfloat16* __restrict__ dy, cons
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// dK / dV  (transposed: TMEM lanes are keys, columns are queries)
+// dK / dV  (transposed: TMEM lanes are keys, columns are queries).  A Q tile lives from S^T(i) (issued during tile
+//          i-1) to dK(i), so Q has a ring of three; dO (with the tile's statistics) is first needed a tile later and
+//          has a ring of two.
 // ---------------------------------------------------------------------------------------------------------------
-constexpr uint32_t DKV_STAT = STILE * 6;            // two stages of 128 x (float2 stats) then two of 128 x int doc starts
-constexpr uint32_t DKV_LO = DKV_STAT + 2 * 1024;
-constexpr uint32_t DKV_BARS = DKV_LO + 2 * 512;
+constexpr uint32_t DKV_STAT = STILE * 7;            // two stages of 128 x (float2 stats), travelling with dO
+constexpr uint32_t DKV_BARS = DKV_STAT + 2 * 1024;
+constexpr uint32_t DKV_SLACK = 512;                 // room for aligning the tiles to 1024 bytes
 
 __global__ void __launch_bounds__(320, 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant__ CUtensorMap tm_v,
                     const __grid_constant__ CUtensorMap tm_dy, const SplitParams p) {
-  extern __shared__ uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
+  if (base - raw > DKV_SLACK) {                       // the seven tiles would not fit behind the alignment gap
+    if (threadIdx.x == 0) atomicCAS(p.err, 0, ERR_WAIT_AUX);
+    return;
+  }
   uint8_t* gen = smem_raw + (base - raw);
   const uint32_t sK = base, sV = base + STILE;
-  auto sQ = [&](int s) { return base + STILE * (2 + 2 * s); };
-  auto sdO = [&](int s) { return base + STILE * (3 + 2 * s); };
+  auto sQ = [&](int s) { return base + STILE * (2 + s); };       // three stages
+  auto sdO = [&](int s) { return base + STILE * (5 + s); };      // two stages
   const uint32_t bars = base + DKV_BARS;
-  enum { B_KV = 0, B_QDO0, B_QDO1, B_FREE0, B_FREE1, B_SFULL, B_DPFULL, B_PREADY, B_DSREADY, B_DONE, B_COUNT };
+  enum { B_KV = 0, B_Q0, B_Q1, B_Q2, B_QFREE0, B_QFREE1, B_QFREE2, B_DO0, B_DO1, B_DOFREE0, B_DOFREE1, B_SFULL, B_DPFULL, B_PREADY,
+         B_DSREADY, B_DONE, B_COUNT };
   auto bar = [&](int i) { return bars + 8u * i; };
   const uint32_t tmem_slot = bars + 8u * B_COUNT;
   volatile uint32_t* tmem_slot_g = reinterpret_cast<volatile uint32_t*>(gen + DKV_BARS + 8 * B_COUNT);
@@ -142,10 +149,14 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
 
   if (threadIdx.x == 0) {
     mbar_init(bar(B_KV), 1);
-    mbar_init(bar(B_QDO0), 1);
-    mbar_init(bar(B_QDO1), 1);
-    mbar_init(bar(B_FREE0), 1);
-    mbar_init(bar(B_FREE1), 1);
+    for (int s = 0; s < 3; ++s) {
+      mbar_init(bar(B_Q0 + s), 1);
+      mbar_init(bar(B_QFREE0 + s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar(B_DO0 + s), 1);
+      mbar_init(bar(B_DOFREE0 + s), 1);
+    }
     mbar_init(bar(B_SFULL), 1);
     mbar_init(bar(B_DPFULL), 1);
     mbar_init(bar(B_PREADY), 8);
@@ -184,16 +195,17 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
       tma_load_2d(sV + SATOM, &tm_v, bar(B_KV), 2 * A + h * 128 + 64, row0 + kt * ST);
       const float2* stat_row = p.stats + ((long long)b * p.H + h) * p.T;
       for (int i = 0; i < n; ++i) {
-        const int s = i & 1;
-        if (i >= 2 && !mbar_wait(bar(B_FREE0 + s), ((i - 2) >> 1) & 1, abort_flag, p.err, ERR_WAIT_EMPTY)) break;
-        mbar_arrive_expect_tx(bar(B_QDO0 + s), 2 * STILE + 1024 + (p.doc_start ? 512u : 0u));
+        const int qs = i % 3, ds = i & 1;
         const int r = row0 + (kt + i) * ST;
-        tma_load_2d(sQ(s), &tm_qk, bar(B_QDO0 + s), h * 128, r);
-        tma_load_2d(sQ(s) + SATOM, &tm_qk, bar(B_QDO0 + s), h * 128 + 64, r);
-        tma_load_2d(sdO(s), &tm_dy, bar(B_QDO0 + s), h * 128, r);
-        tma_load_2d(sdO(s) + SATOM, &tm_dy, bar(B_QDO0 + s), h * 128 + 64, r);
-        bulk_load(base + DKV_STAT + s * 1024, stat_row + (kt + i) * ST, 1024, bar(B_QDO0 + s));
-        if (p.doc_start) bulk_load(base + DKV_LO + s * 512, p.doc_start + r, 512, bar(B_QDO0 + s));
+        if (i >= 3 && !mbar_wait(bar(B_QFREE0 + qs), (uint32_t)(((i - 3) / 3) & 1), abort_flag, p.err, ERR_WAIT_EMPTY)) break;
+        mbar_arrive_expect_tx(bar(B_Q0 + qs), STILE);
+        tma_load_2d(sQ(qs), &tm_qk, bar(B_Q0 + qs), h * 128, r);
+        tma_load_2d(sQ(qs) + SATOM, &tm_qk, bar(B_Q0 + qs), h * 128 + 64, r);
+        if (i >= 2 && !mbar_wait(bar(B_DOFREE0 + ds), (uint32_t)(((i - 2) >> 1) & 1), abort_flag, p.err, ERR_WAIT_EMPTY)) break;
+        mbar_arrive_expect_tx(bar(B_DO0 + ds), STILE + 1024);
+        tma_load_2d(sdO(ds), &tm_dy, bar(B_DO0 + ds), h * 128, r);
+        tma_load_2d(sdO(ds) + SATOM, &tm_dy, bar(B_DO0 + ds), h * 128 + 64, r);
+        bulk_load(base + DKV_STAT + ds * 1024, stat_row + (kt + i) * ST, 1024, bar(B_DO0 + ds));
       }
     }
   } else if (warp == 1) {
@@ -201,18 +213,22 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
       const uint32_t id_kk = umma_idesc_f16(128, 128, 1, 0, 0);
       const uint32_t id_km = umma_idesc_f16(128, 128, 1, 0, 1);
       bool ok = mbar_wait(bar(B_KV), 0, abort_flag, p.err, ERR_WAIT_FULL);
-      if (ok) ok = mbar_wait(bar(B_QDO0), 0, abort_flag, p.err, ERR_WAIT_FULL);
+      if (ok) ok = mbar_wait(bar(B_Q0), 0, abort_flag, p.err, ERR_WAIT_FULL);
       if (ok) {
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma_f16(tS, sdesc_k(sK, k), sdesc_k(sQ(0), k), id_kk, k ? 1u : 0u);
         tc_commit(bar(B_SFULL));
+        ok = mbar_wait(bar(B_DO0), 0, abort_flag, p.err, ERR_WAIT_FULL);
+      }
+      if (ok) {
+        tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma_f16(tdP, sdesc_k(sV, k), sdesc_k(sdO(0), k), id_kk, k ? 1u : 0u);
         tc_commit(bar(B_DPFULL));
       }
       for (int i = 0; i < n && ok; ++i) {
-        const int s = i & 1;
+        const int s = i & 1, qs = i % 3, qn = (i + 1) % 3;
         const uint32_t ph = (uint32_t)(i & 1);
         const bool more = i + 1 < n;
         // P^T(i) sits packed in the S^T columns: dV += P^T dO, then S^T(i+1) behind it (same pipe, in order)
@@ -221,19 +237,22 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma_f16_ts(tdV, tS + packed_col(k), sdesc_mn(sdO(s), k), id_km, (i | k) ? 1u : 0u);
         if (more) {
-          if (!mbar_wait(bar(B_QDO0 + (s ^ 1)), ((i + 1) >> 1) & 1, abort_flag, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+          if (!mbar_wait(bar(B_Q0 + qn), (uint32_t)(((i + 1) / 3) & 1), abort_flag, p.err, ERR_WAIT_FULL)) { ok = false; break; }
           tc_fence_after();
 #pragma unroll
-          for (int k = 0; k < 8; ++k) umma_f16(tS, sdesc_k(sK, k), sdesc_k(sQ(s ^ 1), k), id_kk, k ? 1u : 0u);
+          for (int k = 0; k < 8; ++k) umma_f16(tS, sdesc_k(sK, k), sdesc_k(sQ(qn), k), id_kk, k ? 1u : 0u);
           tc_commit(bar(B_SFULL));
         }
         // dS^T(i) sits packed in the dP^T columns: dK += dS^T Qh, then dP^T(i+1) behind it
         if (!mbar_wait(bar(B_DSREADY), ph, abort_flag, p.err, ERR_WAIT_AUX)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < 8; ++k) umma_f16_ts(tdK, tdP + packed_col(k), sdesc_mn(sQ(s), k), id_km, (i | k) ? 1u : 0u);
-        tc_commit(bar(B_FREE0 + s));
+        for (int k = 0; k < 8; ++k) umma_f16_ts(tdK, tdP + packed_col(k), sdesc_mn(sQ(qs), k), id_km, (i | k) ? 1u : 0u);
+        tc_commit(bar(B_QFREE0 + qs));
+        tc_commit(bar(B_DOFREE0 + s));       // dO(i) was read by dV(i); its statistics were in use until dS(i) was stored
         if (more) {
+          if (!mbar_wait(bar(B_DO0 + (s ^ 1)), (uint32_t)(((i + 1) >> 1) & 1), abort_flag, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+          tc_fence_after();
 #pragma unroll
           for (int k = 0; k < 8; ++k) umma_f16(tdP, sdesc_k(sV, k), sdesc_k(sdO(s ^ 1), k), id_kk, k ? 1u : 0u);
           tc_commit(bar(B_DPFULL));
@@ -249,14 +268,18 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
     const int c0 = half * 64;                          // first query column of this thread
     const int k0 = kt * ST, kpos = k0 + r;
     bool ok = true;
+    int nx_lo_last = (p.doc_start && n > 0) ? p.doc_start[(long long)b * p.T + kt * ST + ST - 1] : 0;
     for (int i = 0; i < n && ok; ++i) {
       const int s = i & 1;
       const uint32_t ph = (uint32_t)(i & 1);
-      bool got = mbar_wait(bar(B_QDO0 + s), (i >> 1) & 1, abort_flag, p.err, ERR_WAIT_FULL);   // this tile's statistics
+      bool got = mbar_wait(bar(B_DO0 + s), (i >> 1) & 1, abort_flag, p.err, ERR_WAIT_FULL);   // this tile's statistics
       if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
       const float4* st4 = reinterpret_cast<const float4*>(gen + DKV_STAT + s * 1024) + c0 / 2;   // two queries per float4
-      const int* slo = reinterpret_cast<const int*>(gen + DKV_LO + s * 512);
-      const bool need_doc = p.doc_start && slo[ST - 1] > k0;
+      // document starts of this tile's queries (global, cached): only the tile that straddles a document start past
+      // this key tile needs them element by element, and its last query decides that
+      const int* slo = p.doc_start ? p.doc_start + (long long)b * p.T + (kt + i) * ST : nullptr;
+      const bool need_doc = slo && nx_lo_last > k0;
+      if (slo && i + 1 < n) nx_lo_last = slo[2 * ST - 1];
       float pr[64];
       got = mbar_wait(bar(B_SFULL), ph, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
       if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
@@ -336,9 +359,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
 
 // ---------------------------------------------------------------------------------------------------------------
 // dQ  (TMEM lanes are queries, columns are keys; dP double-buffered so the MMAs of tile j+1 run under the
-//      exponentiation of tile j)
+//      exponentiation of tile j).  K tiles live from S(j) to dQ(j), V tiles only until dP(j): a K ring of three and a V
+//      ring of two keep every load a full tile ahead of its first use.
 // ---------------------------------------------------------------------------------------------------------------
-constexpr uint32_t DQ_BARS = STILE * 6;
+constexpr uint32_t DQ_BARS = STILE * 7;
 
 __global__ void __launch_bounds__(320, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant__ CUtensorMap tm_v,
@@ -348,10 +372,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_const
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - raw);
   const uint32_t sQ = base, sdO = base + STILE;
-  auto sK = [&](int s) { return base + STILE * (2 + 2 * s); };
-  auto sV = [&](int s) { return base + STILE * (3 + 2 * s); };
+  auto sK = [&](int s) { return base + STILE * (2 + s); };      // three stages
+  auto sV = [&](int s) { return base + STILE * (5 + s); };      // two stages
   const uint32_t bars = base + DQ_BARS;
-  enum { B_QDO = 0, B_KV0, B_KV1, B_FREE0, B_FREE1, B_SFULL, B_SFREE, B_DPFULL0, B_DPFULL1, B_DSREADY, B_DONE, B_COUNT };
+  enum { B_QDO = 0, B_K0, B_K1, B_K2, B_KFREE0, B_KFREE1, B_KFREE2, B_V0, B_V1, B_VFREE0, B_VFREE1, B_SFULL, B_SFREE, B_DPFULL0,
+         B_DPFULL1, B_DSREADY, B_DONE, B_COUNT };
   auto bar = [&](int i) { return bars + 8u * i; };
   const uint32_t tmem_slot = bars + 8u * B_COUNT;
   volatile uint32_t* tmem_slot_g = reinterpret_cast<volatile uint32_t*>(gen + DQ_BARS + 8 * B_COUNT);
@@ -363,9 +388,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_const
 
   if (threadIdx.x == 0) {
     mbar_init(bar(B_QDO), 1);
+    for (int s = 0; s < 3; ++s) {
+      mbar_init(bar(B_K0 + s), 1);
+      mbar_init(bar(B_KFREE0 + s), 1);
+    }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(bar(B_KV0 + s), 1);
-      mbar_init(bar(B_FREE0 + s), 1);
+      mbar_init(bar(B_V0 + s), 1);
+      mbar_init(bar(B_VFREE0 + s), 1);
       mbar_init(bar(B_DPFULL0 + s), 1);
     }
     mbar_init(bar(B_SFULL), 1);
@@ -403,14 +432,16 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_const
       tma_load_2d(sdO, &tm_dy, bar(B_QDO), h * 128, rq);
       tma_load_2d(sdO + SATOM, &tm_dy, bar(B_QDO), h * 128 + 64, rq);
       for (int j = 0; j < n; ++j) {
-        const int s = j & 1;
-        if (j >= 2 && !mbar_wait(bar(B_FREE0 + s), ((j - 2) >> 1) & 1, abort_flag, p.err, ERR_WAIT_EMPTY)) break;
-        mbar_arrive_expect_tx(bar(B_KV0 + s), 2 * STILE);
+        const int ks = j % 3, vs = j & 1;
         const int r = row0 + (kt0 + j) * ST;
-        tma_load_2d(sK(s), &tm_qk, bar(B_KV0 + s), A + h * 128, r);
-        tma_load_2d(sK(s) + SATOM, &tm_qk, bar(B_KV0 + s), A + h * 128 + 64, r);
-        tma_load_2d(sV(s), &tm_v, bar(B_KV0 + s), 2 * A + h * 128, r);
-        tma_load_2d(sV(s) + SATOM, &tm_v, bar(B_KV0 + s), 2 * A + h * 128 + 64, r);
+        if (j >= 3 && !mbar_wait(bar(B_KFREE0 + ks), (uint32_t)(((j - 3) / 3) & 1), abort_flag, p.err, ERR_WAIT_EMPTY)) break;
+        mbar_arrive_expect_tx(bar(B_K0 + ks), STILE);
+        tma_load_2d(sK(ks), &tm_qk, bar(B_K0 + ks), A + h * 128, r);
+        tma_load_2d(sK(ks) + SATOM, &tm_qk, bar(B_K0 + ks), A + h * 128 + 64, r);
+        if (j >= 2 && !mbar_wait(bar(B_VFREE0 + vs), (uint32_t)(((j - 2) >> 1) & 1), abort_flag, p.err, ERR_WAIT_EMPTY)) break;
+        mbar_arrive_expect_tx(bar(B_V0 + vs), STILE);
+        tma_load_2d(sV(vs), &tm_v, bar(B_V0 + vs), 2 * A + h * 128, r);
+        tma_load_2d(sV(vs) + SATOM, &tm_v, bar(B_V0 + vs), 2 * A + h * 128 + 64, r);
       }
     }
   } else if (warp == 1) {
@@ -418,37 +449,46 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_const
       const uint32_t id_kk = umma_idesc_f16(128, 128, 1, 0, 0);
       const uint32_t id_km = umma_idesc_f16(128, 128, 1, 0, 1);
       bool ok = mbar_wait(bar(B_QDO), 0, abort_flag, p.err, ERR_WAIT_FULL);
-      if (ok) ok = mbar_wait(bar(B_KV0), 0, abort_flag, p.err, ERR_WAIT_FULL);
+      if (ok) ok = mbar_wait(bar(B_K0), 0, abort_flag, p.err, ERR_WAIT_FULL);
       if (ok) {
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma_f16(tS, sdesc_k(sQ, k), sdesc_k(sK(0), k), id_kk, k ? 1u : 0u);
         tc_commit(bar(B_SFULL));
+        ok = mbar_wait(bar(B_V0), 0, abort_flag, p.err, ERR_WAIT_FULL);
+      }
+      if (ok) {
+        tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma_f16(tdP(0), sdesc_k(sdO, k), sdesc_k(sV(0), k), id_kk, k ? 1u : 0u);
         tc_commit(bar(B_DPFULL0));
+        tc_commit(bar(B_VFREE0));
       }
       for (int j = 0; j < n && ok; ++j) {
         const int s = j & 1;
         if (j + 1 < n) {
           // S(j+1) as soon as the compute warps hold S(j) in registers; dP(j+1) into the other dP buffer, whose packed
           // dS(j-1) the dQ MMAs of tile j-1 (issued earlier, same pipe) have read by then
-          if (!mbar_wait(bar(B_KV0 + (s ^ 1)), ((j + 1) >> 1) & 1, abort_flag, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+          const int kn = (j + 1) % 3;
+          if (!mbar_wait(bar(B_K0 + kn), (uint32_t)(((j + 1) / 3) & 1), abort_flag, p.err, ERR_WAIT_FULL)) { ok = false; break; }
           if (!mbar_wait(bar(B_SFREE), (uint32_t)(j & 1), abort_flag, p.err, ERR_WAIT_AUX)) { ok = false; break; }
           tc_fence_after();
 #pragma unroll
-          for (int k = 0; k < 8; ++k) umma_f16(tS, sdesc_k(sQ, k), sdesc_k(sK(s ^ 1), k), id_kk, k ? 1u : 0u);
+          for (int k = 0; k < 8; ++k) umma_f16(tS, sdesc_k(sQ, k), sdesc_k(sK(kn), k), id_kk, k ? 1u : 0u);
           tc_commit(bar(B_SFULL));
+          if (!mbar_wait(bar(B_V0 + (s ^ 1)), (uint32_t)(((j + 1) >> 1) & 1), abort_flag, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+          tc_fence_after();
 #pragma unroll
           for (int k = 0; k < 8; ++k) umma_f16(tdP(s ^ 1), sdesc_k(sdO, k), sdesc_k(sV(s ^ 1), k), id_kk, k ? 1u : 0u);
           tc_commit(bar(B_DPFULL0 + (s ^ 1)));
+          tc_commit(bar(B_VFREE0 + (s ^ 1)));
         }
         // dS(j) sits packed in the dP(j) columns: dQ += dS Kh(j), which also frees that K/V stage
         if (!mbar_wait(bar(B_DSREADY), (uint32_t)(j & 1), abort_flag, p.err, ERR_WAIT_AUX)) { ok = false; break; }
         tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < 8; ++k) umma_f16_ts(tdQ, tdP(s) + packed_col(k), sdesc_mn(sK(s), k), id_km, (j | k) ? 1u : 0u);
-        tc_commit(bar(B_FREE0 + s));
+        for (int k = 0; k < 8; ++k) umma_f16_ts(tdQ, tdP(s) + packed_col(k), sdesc_mn(sK(j % 3), k), id_km, (j | k) ? 1u : 0u);
+        tc_commit(bar(B_KFREE0 + j % 3));
         if (j + 1 == n) tc_commit(bar(B_DONE));
       }
     }
@@ -579,7 +619,7 @@ int bones_attn_bwd_split(const void* qk, const void* qkv, const void* dy, const 
   p.dv = (__nv_bfloat16*)dv;
   p.dv_ld = dv_ld;
   p.err = error_word();
-  constexpr size_t smem_dkv = (size_t)DKV_BARS + 160 + 1024;
+  constexpr size_t smem_dkv = (size_t)DKV_BARS + 160 + DKV_SLACK;
   constexpr size_t smem_dq = (size_t)DQ_BARS + 160 + 1024;
   static bool attr_done = false;
   if (!attr_done) {
