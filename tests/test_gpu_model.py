@@ -205,3 +205,9 @@ def test_native_decode_step_matches_cached_pytorch_route():
         torch.cuda.synchronize()
     assert torch.equal(full, out2)
     assert full.shape == (b, p + n_new) and torch.equal(full[:, :p], prompts)
+
+
+def test_first_call_selfcheck_passes_and_reports():
+    from them_bones_b200.ops.selfcheck import run
+    out = run("cuda")
+    assert len(out) >= 15 and max(out.values()) < 5e-2

@@ -221,6 +221,7 @@ def switches(refresh: bool = False) -> dict:
         TABLE_STALE=e("TABLE_STALE", False, bool), TABLE_HOST_STATE=e("TABLE_HOST_STATE", True, bool),
         DATA_RULE=e("DATA_RULE", "", str),           # e.g. "len:64-4096,band:0.05-0.95,dedup:32,from:0.1"
         # kernels / system
+        SELFCHECK=e("SELFCHECK", False, bool),       # compare every native op with the PyTorch path before training
         KERNELS=e("KERNELS", "auto", str),           # auto: CUDA kernels on a GPU, torch oracle on CPU | ref
         FUSED_COMM=e("FUSED_COMM", True, bool),      # in-kernel NVLink collectives (False: NCCL baseline path)
         LOSS_CHUNK=e("LOSS_CHUNK", 8192, int),

@@ -65,6 +65,10 @@ def main(argv=None):
     sw = C.switches(refresh=True)
     rt = init_runtime(args.device or None, seed=hyper.seed)
     print0(f"device {rt.device} world {rt.world} kernels {'ref' if ops.reference_path() else 'native'}")
+    if sw["SELFCHECK"] and rt.device_type == "cuda" and not ops.reference_path():
+        from them_bones_b200.ops.selfcheck import run as selfcheck
+        worst = max(selfcheck(rt.device).values())
+        print0(f"self-check: native kernels agree with the PyTorch path (worst relative error {worst:.2e})")
     cfg = C.build_config(args.depth, args.n_embd, args.n_head, args.seq_len, args.vocab, head_dim=args.head_dim,
                          hyper=hyper)
     print0("model_config " + json.dumps(C.model_config_dict(cfg)))
