@@ -28,19 +28,21 @@ PUBLISHED_TOK_S = 340000.0      # reference round-1 throughput on one Trainium2 
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs (read-only)."""
+    """Samples SM clocks and throttle reasons with nvidia-smi (read-only).  The process is started before the warm-up,
+    because nvidia-smi needs about a second before its first line; only lines read between ``mark_begin()`` and
+    ``stop()`` -- the timed region -- are used."""
 
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index: int):
-        self.gpu_index, self.proc, self.lines = gpu_index, None, []
+        self.gpu_index, self.proc, self.lines, self.t_begin = gpu_index, None, [], None
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.gpu_index)], stdout=subprocess.PIPE,
+                                          "-lms", "100", "-i", str(self.gpu_index)], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._pump, daemon=True).start()
         except OSError:
@@ -48,7 +50,10 @@ class ClockSampler:
 
     def _pump(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
+
+    def mark_begin(self):
+        self.t_begin = time.time()
 
     def stop(self) -> dict:
         if self.proc is None:
@@ -60,7 +65,10 @@ class ClockSampler:
             self.proc.kill()
         sm, smax, power, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        t_end = time.time()
+        for ts, ln in self.lines:
+            if self.t_begin is not None and not (self.t_begin <= ts <= t_end):
+                continue
             parts = [p.strip() for p in ln.split(",")]
             if len(parts) < 9:
                 continue
@@ -121,17 +129,18 @@ def run_ours(args, torch_path: bool = False):
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(rt.local_rank)
+    sampler.start()
     for i in range(args.warmup):
         tr.train_step(*dev[i % 2])
     barrier()
     _lib.check_error_word() if not torch_path else None
     # ---- device-timed region: inputs resident, CUDA events on the launching stream ----
-    sampler = ClockSampler(rt.local_rank)
     launches0 = _lib.LAUNCHES[0]
     counts0 = dict(ops.COUNTS)
-    sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    sampler.mark_begin()
     e0.record()
     for i in range(args.steps):
         loss = tr.train_step(*dev[i % 2])
