@@ -90,7 +90,7 @@ def parse():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torch"])
-    ap.add_argument("--device-batch", type=int, default=int(os.environ.get("BONES_DEVICE_BATCH", 16)))
+    ap.add_argument("--device-batch", type=int, default=int(os.environ.get("BONES_DEVICE_BATCH", 32)))
     ap.add_argument("--total-batch", type=int, default=524288)
     ap.add_argument("--depth", type=int, default=20)
     ap.add_argument("--mlp", default=os.environ.get("BONES_MLP", "bf16"))

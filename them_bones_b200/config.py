@@ -218,7 +218,7 @@ def switches(refresh: bool = False) -> dict:
         MOE_TOPK=e("MOE_TOPK", 2, int), MOE_HIDDEN=e("MOE_HIDDEN", 0, int), MOE_SHARED=e("MOE_SHARED", 0, int),
         MOE_AUX=e("MOE_AUX", 0.01, float), MOE_ZLOSS=e("MOE_ZLOSS", 0.0, float),
         TABLES=e("TABLES", "", str), TABLE_ROWS=e("TABLE_ROWS", 0, int), TABLE_SEED=e("TABLE_SEED", 0, int),
-        TABLE_STALE=e("TABLE_STALE", False, bool), TABLE_HOST_STATE=e("TABLE_HOST_STATE", True, bool),
+        TABLE_STALE=e("TABLE_STALE", False, bool), TABLE_HOST_STATE=e("TABLE_HOST_STATE", "auto", str),   # auto | 0 | 1: Adam moments of the tables in pinned host memory
         DATA_RULE=e("DATA_RULE", "", str),           # e.g. "len:64-4096,band:0.05-0.95,dedup:32,from:0.1"
         # kernels / system
         SELFCHECK=e("SELFCHECK", False, bool),       # compare every native op with the PyTorch path before training

@@ -57,7 +57,8 @@ class Trainer:
         if config.table_orders:
             self.tables = HashedTables(config.table_orders, config.table_rows, config.n_embd, seed=config.table_seed,
                                        device=rt.device, dtype=self.dtype, group=dist.group.WORLD if rt.ddp else None,
-                                       world=rt.world, rank=rt.rank, host_state=sw["TABLE_HOST_STATE"])
+                                       world=rt.world, rank=rt.rank, host_state=("auto" if sw["TABLE_HOST_STATE"] == "auto"
+                                                   else sw["TABLE_HOST_STATE"].lower() in ("1", "true")))
             if self.comm is not None and rt.world > 1:
                 self.tables.exchange = self.comm.table_exchange(self.tables)
             model.attach_tables(self.tables)
