@@ -224,6 +224,7 @@ def switches(refresh: bool = False) -> dict:
         SELFCHECK=e("SELFCHECK", False, bool),       # compare every native op with the PyTorch path before training
         KERNELS=e("KERNELS", "auto", str),           # auto: CUDA kernels on a GPU, torch oracle on CPU | ref
         FUSED_COMM=e("FUSED_COMM", True, bool),      # in-kernel NVLink collectives (False: NCCL baseline path)
+        WGRAD_PUSH=e("WGRAD_PUSH", False, bool),     # weight-gradient GEMMs reduce-scatter their tiles into the owner's slab
         LOSS_CHUNK=e("LOSS_CHUNK", 8192, int),
         OPT=e("OPT", "lean", str),                   # lean | dist | single
         OPT_OVERLAP_CHECK=e("OPT_OVERLAP_CHECK", False, bool),

@@ -44,6 +44,7 @@ struct GemmParams {
   int tiles_m, tiles_n;
   int wide;            // rows are 32-byte aligned: use 256-bit global accesses in the epilogue
   int splits;          // split-K factor (> 1 only with EPI_ACC_F32: partial tiles are added with vector atomics)
+  int atomic;          // EPI_ACC_F32: always add with atomics (other GPUs add into the same buffer at the same time)
 };
 
 constexpr int BM = 128;
@@ -203,7 +204,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
         if (row_ok && col0 < p.N) {
           const size_t esz = f32out ? 4 : 2;
           const uint4 none[4] = {};
-          gemm_store_chunk(r, p.epi, p.alpha, p.beta, p.wide != 0, p.splits > 1, reinterpret_cast<uint8_t*>(p.D) + (drow + col0) * esz,
+          gemm_store_chunk(r, p.epi, p.alpha, p.beta, p.wide != 0, p.splits > 1 || p.atomic, reinterpret_cast<uint8_t*>(p.D) + (drow + col0) * esz,
                            reinterpret_cast<const uint8_t*>(p.R) + (rrow + col0) * esz, false, none, min(32, p.N - col0));
         }
       }
@@ -289,7 +290,7 @@ extern "C" {
 // Returns 0 on success, a CUDA error code (> 0) or a negative descriptor-encoding error.
 int bones_gemm_bf16(const void* A, const void* B, void* D, const void* R, int M, int N, int K, int batch, long long lda,
                     long long ldb, long long ldd, long long ldr, long long strideA, long long strideB, long long strideD,
-                    long long strideR, int a_major, int b_major, int epi, float alpha, float beta, int force_bn, int splits, void* stream) {
+                    long long strideR, int a_major, int b_major, int epi, float alpha, float beta, int force_bn, int splits, int atomic, void* stream) {
   using namespace bones;
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 0;
   if ((lda % 8) || (ldb % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || ((uintptr_t)D & 15)) return -2;
@@ -307,6 +308,7 @@ int bones_gemm_bf16(const void* A, const void* B, void* D, const void* R, int M,
   p.wide = ((ldd % wal == 0) && (strideD % wal == 0) && (!R || (ldr % wal == 0 && strideR % wal == 0)) && (((uintptr_t)D & 31) == 0) &&
             (!R || ((uintptr_t)R & 31) == 0)) ? 1 : 0;
   p.splits = splits;
+  p.atomic = (atomic && epi == EPI_ACC_F32) ? 1 : 0;
   CUtensorMap ta, tb;
   int rc = operand_tmap(&ta, A, a_major, M, K, lda, strideA, batch, BM);
   if (rc) return rc;

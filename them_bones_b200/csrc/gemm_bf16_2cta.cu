@@ -37,6 +37,7 @@ struct Gemm2Params {
   int* err;
   int tiles_m, tiles_n;
   int splits;
+  int atomic;          // E2_ACC_F32: always add with atomics (other GPUs add into the same buffer at the same time)
   int wide;            // rows are 32-byte aligned: use 256-bit global accesses in the epilogue
 };
 
@@ -263,7 +264,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
         const int col0 = nb * PN + c * 32;
         if (row_ok && col0 < p.N) {
           const size_t esz = f32out ? 4 : 2;
-          gemm_store_chunk(r, p.epi, p.alpha, p.beta, p.wide != 0, p.splits > 1, reinterpret_cast<uint8_t*>(p.D) + (drow + col0) * esz,
+          gemm_store_chunk(r, p.epi, p.alpha, p.beta, p.wide != 0, p.splits > 1 || p.atomic, reinterpret_cast<uint8_t*>(p.D) + (drow + col0) * esz,
                            reinterpret_cast<const uint8_t*>(p.R) + (rrow + col0) * esz, pre && col0 + 32 <= p.N, rpre[cc],
                            min(32, p.N - col0));
         }
@@ -313,7 +314,7 @@ extern "C" {
 
 int bones_gemm_bf16_pair(const void* A, const void* B, void* D, const void* R, int M, int N, int K, int batch, long long lda,
                          long long ldb, long long ldd, long long ldr, long long strideA, long long strideB, long long strideD,
-                         long long strideR, int a_major, int b_major, int epi, float alpha, float beta, int splits, void* stream) {
+                         long long strideR, int a_major, int b_major, int epi, float alpha, float beta, int splits, int atomic, void* stream) {
   using namespace bones;
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 0;
   if ((lda % 8) || (ldb % 8) || ((uintptr_t)A & 15) || ((uintptr_t)B & 15) || ((uintptr_t)D & 15)) return -2;
@@ -348,6 +349,7 @@ int bones_gemm_bf16_pair(const void* A, const void* B, void* D, const void* R, i
   const int pairs = sms / 2;
   const int base_tiles = batch * p.tiles_m * p.tiles_n;
   const int KB = (K + PK - 1) / PK;
+  p.atomic = (atomic && epi == E2_ACC_F32) ? 1 : 0;
   p.splits = splits;
   if (p.splits <= 0) {
     p.splits = 1;

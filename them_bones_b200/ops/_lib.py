@@ -72,7 +72,7 @@ PAIR_MODE = os.environ.get("BONES_GEMM_PAIR", "auto")      # auto | 0 | 1
 
 
 def gemm(a, b, d, *, m, n, k, lda, ldb, ldd, a_major=0, b_major=0, epi=EPI_BF16, r=None, ldr=0, alpha=1.0, beta=1.0,
-         batch=1, stride_a=0, stride_b=0, stride_d=0, stride_r=0, force_bn=0, splits=0, pair=None):
+         batch=1, stride_a=0, stride_b=0, stride_d=0, stride_r=0, force_bn=0, splits=0, pair=None, d_ptr=None, atomic=False):
     """``d = epilogue(alpha * a @ b^T, r)``; see csrc/gemm_bf16.cu for operand layouts.  Large problems run on CTA
     pairs (csrc/gemm_bf16_2cta.cu: 256 x 256 tiles, one third less L2 traffic per flop); small ones on single CTAs."""
     if pair is None:
@@ -82,11 +82,14 @@ def gemm(a, b, d, *, m, n, k, lda, ldb, ldd, a_major=0, b_major=0, epi=EPI_BF16,
             pair = force_bn == 0 and m >= 256 and n >= 256 and (tiles >= 37 or (epi == EPI_ACC_F32 and k >= 8192 * 37 // tiles))
         else:
             pair = PAIR_MODE == "1" and force_bn == 0
+    # d_ptr: raw device address used instead of ``d`` (e.g. the same buffer in another GPU's memory); atomic: fp32
+    # accumulation by vector atomics even without split-K, for outputs several GPUs add into at once
+    dp = ptr(d) if d_ptr is None else ctypes.c_void_p(int(d_ptr))
     if pair:
-        call("bones_gemm_bf16_pair", ptr(a), ptr(b), ptr(d), ptr(r), _I(m), _I(n), _I(k), _I(batch), _L(lda), _L(ldb),
+        call("bones_gemm_bf16_pair", ptr(a), ptr(b), dp, ptr(r), _I(m), _I(n), _I(k), _I(batch), _L(lda), _L(ldb),
              _L(ldd), _L(ldr), _L(stride_a), _L(stride_b), _L(stride_d), _L(stride_r), _I(a_major), _I(b_major), _I(epi),
-             _F(alpha), _F(beta), _I(splits), stream())
+             _F(alpha), _F(beta), _I(splits), _I(int(atomic)), stream())
         return
-    call("bones_gemm_bf16", ptr(a), ptr(b), ptr(d), ptr(r), _I(m), _I(n), _I(k), _I(batch), _L(lda), _L(ldb), _L(ldd),
+    call("bones_gemm_bf16", ptr(a), ptr(b), dp, ptr(r), _I(m), _I(n), _I(k), _I(batch), _L(lda), _L(ldb), _L(ldd),
          _L(ldr), _L(stride_a), _L(stride_b), _L(stride_d), _L(stride_r), _I(a_major), _I(b_major), _I(epi), _F(alpha),
-         _F(beta), _I(force_bn), _I(splits), stream())
+         _F(beta), _I(force_bn), _I(splits), _I(int(atomic)), stream())

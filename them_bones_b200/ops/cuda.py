@@ -71,12 +71,15 @@ def mm_nn_acc(x, w, out32):
     return out32
 
 
-def mm_tn_acc(dy, x, grad, alpha=1.0):
-    """``grad [N,K] (fp32) += alpha * dy[M,N]^T @ x[M,K]`` (both operands MN-major: contraction over rows)"""
+def mm_tn_acc(dy, x, grad, alpha=1.0, push_ptr=None):
+    """``grad [N,K] (fp32) += alpha * dy[M,N]^T @ x[M,K]`` (both operands MN-major: contraction over rows).
+    ``push_ptr``: device address of the same gradient buffer on the GPU that owns this matrix; the GEMM epilogue then
+    adds its tiles there with vector atomics over NVLink, which is the reduce-scatter of the data-parallel gradient done
+    tile by tile inside the weight-gradient GEMM."""
     m, n = dy.shape
     k = x.shape[1]
     L.gemm(dy, x, grad, m=n, n=k, k=m, lda=dy.stride(0), ldb=x.stride(0), ldd=grad.stride(0), a_major=1, b_major=1,
-           epi=L.EPI_ACC_F32, alpha=alpha)
+           epi=L.EPI_ACC_F32, alpha=alpha, d_ptr=push_ptr, atomic=push_ptr is not None)
     COUNTS["gemm"] += 1
     return grad
 
@@ -85,8 +88,19 @@ def _wgrad(dy2, x2, ws):
     """Weight gradient for one or several row-adjacent weights.  Returns the tuple autograd expects."""
     grads = [getattr(w, "main_grad", None) for w in ws]
     if all(g is not None for g in grads):
+        push = [getattr(w, "main_grad_push", None) for w in ws]       # owner-side addresses (fused reduce-scatter)
         fused = _fused_rows(grads) if len(grads) > 1 else grads[0]
-        if fused is not None:
+        if all(p is not None for p in push):
+            # one GEMM when the weights are adjacent in the owner's buffer too (same owner), else one per weight
+            adjacent = all(push[j + 1] == push[j] + grads[j].numel() * 4 for j in range(len(ws) - 1))
+            if fused is not None and adjacent:
+                mm_tn_acc(dy2, x2, fused, push_ptr=push[0])
+            else:
+                o = 0
+                for w, g, pp in zip(ws, grads, push):
+                    mm_tn_acc(dy2[:, o:o + w.shape[0]], x2, g, push_ptr=pp)
+                    o += w.shape[0]
+        elif fused is not None:
             mm_tn_acc(dy2, x2, fused)
         else:
             o = 0

@@ -165,6 +165,25 @@ class LeanDistMuonAdamW(torch.optim.Optimizer):
             self.small.append((slice(o, o + k), g))
             o += k
         self._local = MuonLocal(self.local_groups, self.ns_dtype)
+        self._setup_push()
+
+    def _setup_push(self):
+        """Fused GEMM -> reduce-scatter for the Muon matrices: every rank's weight-gradient GEMM adds its tiles straight
+        into the gradient slab of the rank that owns the matrix (vector atomics over NVLink from the GEMM epilogue), so
+        when backward ends the owner already holds the sum over ranks and nothing is left to reduce at the step boundary.
+        Only with the peer-memory communicator on more than one GPU; ``BONES_WGRAD_PUSH=0`` keeps the reduction in the
+        optimizer prologue."""
+        from ..config import switches
+        comm = self.comm
+        self.push = bool(getattr(comm, "fused", False) and self.world > 1 and switches()["WGRAD_PUSH"]
+                         and hasattr(comm, "peer_addresses"))
+        if not self.push:
+            return
+        for u in self.muon_units:
+            addr = comm.peer_addresses(u.G)
+            mat = u.r * u.c * 4
+            for i, p in enumerate(u.params):
+                p.main_grad_push = addr[i // u.k] + i * mat
 
     def _ns(self, t):
         if self.ns_dtype is not None:
@@ -193,7 +212,8 @@ class LeanDistMuonAdamW(torch.optim.Optimizer):
 
     def zero_grad(self, set_to_none: bool = True):
         for u in self.muon_units:
-            u.G.zero_()
+            if not getattr(self, "push", False):          # pushed slabs are cleared by their owner inside step()
+                u.G.zero_()
         for u in self.row_units:
             u.G.zero_()
         self.SG.zero_()
@@ -270,7 +290,9 @@ class LeanDistMuonAdamW(torch.optim.Optimizer):
         for u in self.row_units:
             comm.fused_row_adamw(u, self.steps)
         for u in self.muon_units:
-            comm.fused_muon(u, self.steps, self._ns(u.W))
+            comm.fused_muon(u, self.steps, self._ns(u.W), own_only=getattr(self, "push", False))
+            if getattr(self, "push", False):
+                u.G.zero_()                               # consumed; peers add the next step's tiles after post_step()
         self._local.step(1.0 / self.world)
         comm.post_step()                                  # every peer's stores into my slabs have landed
         self._gsq_history = getattr(self, "_gsq_history", [])

@@ -64,6 +64,13 @@ class PeerComm:
         self._handles[t.data_ptr()] = (t, hdl, _ptr_array(hdl.buffer_ptrs))
         return t
 
+    def peer_addresses(self, t):
+        """The W device addresses of symmetric tensor ``t`` as Python ints (index = rank)."""
+        ent = self._handles.get(t.data_ptr())
+        if ent is None:
+            raise RuntimeError("tensor is not a symmetric allocation of this communicator")
+        return [int(p) for p in ent[1].buffer_ptrs]
+
     def peers(self, t):
         """ctypes array of the W peer pointers of symmetric tensor ``t`` (or of the allocation a view starts in)."""
         ent = self._handles.get(t.data_ptr())
@@ -116,7 +123,9 @@ class PeerComm:
                _F(g["eps"]), _F(g["weight_decay"]), _I(step), L.ptr(self.gsq), L.stream())
         self.launches += 1
 
-    def fused_muon(self, u, step, ns_dtype):
+    def fused_muon(self, u, step, ns_dtype, own_only=False):
+        # own_only: the owner's slab already holds the sum over ranks (pushed by the weight-gradient GEMMs), so only
+        # this rank's slab is read (still divided by the world size)
         from ..ops import muon_native as MN
         g = u.group
         n = u.momentum.numel()
@@ -126,7 +135,13 @@ class PeerComm:
             u.X = torch.empty(u.k, u.r, u.c, dtype=torch.bfloat16, device=u.W.device)
             u.sumsq = torch.zeros(u.k, dtype=torch.float32, device=u.W.device)
         u.sumsq.zero_()
-        L.call("bones_rs_muon_prep", self.peers(u.G), _L(off), _L(n), _I(self.world), _F(1.0 / self.world),
+        if own_only:
+            if not hasattr(u, "own_ptr"):
+                u.own_ptr = _ptr_array([self.peer_addresses(u.G)[self.rank]])
+            src, nsrc = u.own_ptr, 1
+        else:
+            src, nsrc = self.peers(u.G), self.world
+        L.call("bones_rs_muon_prep", src, _L(off), _L(n), _I(nsrc), _F(1.0 / self.world),
                _F(g["momentum"]), L.ptr(u.momentum), L.ptr(u.X), L.ptr(u.sumsq), _L(mat), L.ptr(self.gsq), L.stream())
         L.call("bones_muon_normalize", L.ptr(u.X), L.ptr(u.sumsq), _L(n), _L(mat), L.stream())
         x = MN.newton_schulz(u.X, g["ns_steps"])
