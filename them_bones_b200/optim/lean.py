@@ -359,5 +359,6 @@ class MuonLocal:
                 grad = p.main_grad * grad_scale
                 nd = self.ns_dtype or (torch.bfloat16 if p.is_cuda else torch.float32)
                 RF.muon_update(grad, st["master"], st["momentum"], st["second"], momentum=g["momentum"],
-                               beta2=g["beta2"], lr=g["lr"], wd=g["weight_decay"], ns_steps=g["ns_steps"], ns_dtype=nd)
+                               beta2=g["beta2"], lr=g["lr"], wd=g["weight_decay"], ns_steps=g["ns_steps"], ns_dtype=nd,
+                               ns_fn=LeanDistMuonAdamW._ns_fn(p))     # the experts' Newton-Schulz on the tcgen05 GEMMs too
                 p.copy_(st["master"])
