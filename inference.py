@@ -24,6 +24,10 @@ class ModelWrapper(torch.nn.Module):
         super().__init__()
         self.model, self.meta = model, meta
 
+    @property
+    def config(self):
+        return self.model.config
+
     @torch.no_grad()
     def forward(self, input_ids: torch.Tensor) -> torch.Tensor:
         return self.model(input_ids)
