@@ -332,6 +332,7 @@ struct AttnParams {
   __nv_bfloat16* y;  // [B*T, H*128]
   float* lse;        // [B, H, T]
   int* err;
+  int* items;        // device counter the persistent CTAs draw their work items from (zero at launch)
 };
 
 constexpr int AT = 128;                    // tile edge (queries and keys)
@@ -356,6 +357,8 @@ __device__ __forceinline__ int attn_first_tile(const AttnParams& p, int b, int q
 //   TMEM: S/P buffers at columns 0 and 128 (by running tile count), O buffers at 256 and 384 (by item parity).
 //   smem: Q x 2 (item parity), K x 2 and V x 3 stages (running tile count): a K stage is free again once its S tile is
 //   done, a V stage only after its O MMAs, so K and V rings of different depth keep the loads a full tile ahead.
+__device__ int g_fwd_items;      // item counter of the persistent forward (one launch at a time per device)
+
 struct FwdItem {
   int qt, h, b, kt0, n;
 };
@@ -395,6 +398,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
   volatile uint32_t* tmem_slot_g = reinterpret_cast<volatile uint32_t*>(gen + kBars + 176);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + kBars + 184);
   float* lsum = reinterpret_cast<float*>(gen + kBars + 256);           // [2 halves][128 rows]
+  const uint32_t ring_bars = bars + 192u;
+  volatile int* ring_slots = reinterpret_cast<volatile int*>(gen + kBars + 224);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int A = p.H * AD;
@@ -416,6 +421,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
       mbar_init(v_full(s), 1);
       mbar_init(v_free(s), 1);
     }
+    for (int s = 0; s < 4; ++s) mbar_init(ring_bars + 8u * s, 1);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tm_qk);
@@ -437,7 +443,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
     if (lane == 0) {
       int g = 0, it = 0;
       bool ok = true;
-      for (int w = blockIdx.x; w < total && ok; w += gridDim.x, ++it) {
+      for (;; ++it) {
+        const int w = ok ? item_publish(ring_bars, ring_slots, it, p.items, total) : -1;
+        if (w < 0) break;
         const FwdItem im = fwd_item(p, w, n_tiles);
         const int qb = it & 1, row0 = im.b * p.T;
         if (it >= 2 && !mbar_wait(q_free(qb), (uint32_t)(((it - 2) >> 1) & 1), abort_flag, p.err, ERR_WAIT_EMPTY)) break;
@@ -486,7 +494,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
       };
       int g = 0, it = 0;
       bool ok = true;
-      for (int w = blockIdx.x; w < total && ok; w += gridDim.x, ++it) {
+      for (;; ++it) {
+        const int w = ok ? item_take(ring_bars, ring_slots, it, abort_flag, p.err) : -1;
+        if (w < 0) break;
         const FwdItem im = fwd_item(p, w, n_tiles);
         const int qb = it & 1;
         if (!mbar_wait(q_full(qb), (uint32_t)((it >> 1) & 1), abort_flag, p.err, ERR_WAIT_FULL)) break;
@@ -550,7 +560,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
       return true;
     };
     int g = 0, it = 0;
-    for (int w = blockIdx.x; w < total && ok; w += gridDim.x, ++it) {
+    for (;; ++it) {
+      const int w = ok ? item_take(ring_bars, ring_slots, it, abort_flag, p.err) : -1;
+      if (w < 0) break;
       const FwdItem im = fwd_item(p, w, n_tiles);
       const int qpos = im.qt * AT + r, row0 = im.b * p.T;
       int lo = 0;
@@ -706,6 +718,11 @@ int bones_attn_fwd(const void* qk, const void* qkv, void* y, float* lse, const i
   BONES_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   const long long items = (long long)(T / AT) * H * B;
   const unsigned grid = (unsigned)(items < sms ? items : sms);       // persistent: one CTA per SM
+  static int* counter[64] = {};
+  if (dev < 0 || dev >= 64) return -2;
+  if (!counter[dev]) BONES_CHECK(cudaGetSymbolAddress(reinterpret_cast<void**>(&counter[dev]), g_fwd_items));
+  BONES_CHECK(cudaMemsetAsync(counter[dev], 0, sizeof(int), (cudaStream_t)stream));
+  p.items = counter[dev];
   attn_fwd_kernel<<<grid, 320, smem, (cudaStream_t)stream>>>(tq, tv, p);
   return (int)cudaGetLastError();
 }

@@ -32,6 +32,7 @@ struct SplitParams {
   __nv_bfloat16* dv;     // rows of dv_ld elements
   long long dv_ld;
   int* err;
+  int* items;            // device counter the persistent dQ CTAs draw their work items from (zero at launch)
 };
 
 __device__ __forceinline__ int split_first_tile(const SplitParams& p, int b, int qt) {
@@ -361,8 +362,28 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
 // dQ  (TMEM lanes are queries, columns are keys; dP double-buffered so the MMAs of tile j+1 run under the
 //      exponentiation of tile j).  K tiles live from S(j) to dQ(j), V tiles only until dP(j): a K ring of three and a V
 //      ring of two keep every load a full tile ahead of its first use.
+//      Persistent: one CTA per SM walks (query tile, head, batch) items in the forward kernel's order (the query tiles
+//      of one (head, batch) run at the same time and share K/V through L2).  Barrier phases, the K/V rings and the dP
+//      buffers run on across items; Q and dO are single-buffered and reloaded as soon as the item's last S and dP MMAs
+//      have been issued, so the next item's first tiles are computed while the compute warps drain dQ.
 // ---------------------------------------------------------------------------------------------------------------
 constexpr uint32_t DQ_BARS = STILE * 7;
+
+__device__ int g_dq_items;       // item counter of the persistent dQ kernel (one launch at a time per device)
+
+struct DqItem {
+  int qt, h, b, kt0, n;
+};
+__device__ __forceinline__ DqItem dq_item(const SplitParams& p, int w, int n_tiles) {
+  DqItem it;
+  const int grp = w / n_tiles;
+  it.qt = n_tiles - 1 - (w % n_tiles + grp) % n_tiles;
+  it.h = grp % p.H;
+  it.b = grp / p.H;
+  it.kt0 = split_first_tile(p, it.b, it.qt);
+  it.n = it.qt - it.kt0 + 1;
+  return it;
+}
 
 __global__ void __launch_bounds__(320, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant__ CUtensorMap tm_v,
@@ -375,19 +396,23 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_const
   auto sK = [&](int s) { return base + STILE * (2 + s); };      // three stages
   auto sV = [&](int s) { return base + STILE * (5 + s); };      // two stages
   const uint32_t bars = base + DQ_BARS;
-  enum { B_QDO = 0, B_K0, B_K1, B_K2, B_KFREE0, B_KFREE1, B_KFREE2, B_V0, B_V1, B_VFREE0, B_VFREE1, B_SFULL, B_SFREE, B_DPFULL0,
-         B_DPFULL1, B_DSREADY, B_DONE, B_COUNT };
+  enum { B_QDO = 0, B_QDOFREE, B_K0, B_K1, B_K2, B_KFREE0, B_KFREE1, B_KFREE2, B_V0, B_V1, B_VFREE0, B_VFREE1, B_SFULL, B_SFREE,
+         B_DPFULL0, B_DPFULL1, B_DSREADY, B_DONE, B_DQFREE, B_COUNT };
   auto bar = [&](int i) { return bars + 8u * i; };
   const uint32_t tmem_slot = bars + 8u * B_COUNT;
   volatile uint32_t* tmem_slot_g = reinterpret_cast<volatile uint32_t*>(gen + DQ_BARS + 8 * B_COUNT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + DQ_BARS + 8 * B_COUNT + 8);
+  const uint32_t ring_bars = bars + 176u;
+  volatile int* ring_slots = reinterpret_cast<volatile int*>(gen + DQ_BARS + 208);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = (int)gridDim.x - 1 - (int)blockIdx.x, h = blockIdx.y, b = blockIdx.z;   // longest rows first
   const int A = p.H * 128;
+  const int n_tiles = p.T / ST;
+  const int total = n_tiles * p.H * p.B;
 
   if (threadIdx.x == 0) {
     mbar_init(bar(B_QDO), 1);
+    mbar_init(bar(B_QDOFREE), 1);
     for (int s = 0; s < 3; ++s) {
       mbar_init(bar(B_K0 + s), 1);
       mbar_init(bar(B_KFREE0 + s), 1);
@@ -401,6 +426,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_const
     mbar_init(bar(B_SFREE), 8);
     mbar_init(bar(B_DSREADY), 8);
     mbar_init(bar(B_DONE), 1);
+    mbar_init(bar(B_DQFREE), 8);
+    for (int s = 0; s < 4; ++s) mbar_init(ring_bars + 8u * s, 1);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tm_qk);
@@ -419,77 +446,80 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_const
   const uint32_t tS = tmem, tdQ = tmem + 384;
   auto tdP = [&](int s) { return tmem + 128u + (uint32_t)s * 128u; };
 
-  const int kt0 = split_first_tile(p, b, qt);
-  const int n = qt - kt0 + 1;
-  const int row0 = b * p.T;
-
   if (warp == 0) {
     if (lane == 0) {
-      mbar_arrive_expect_tx(bar(B_QDO), 2 * STILE);
-      const int rq = row0 + qt * ST;
-      tma_load_2d(sQ, &tm_qk, bar(B_QDO), h * 128, rq);
-      tma_load_2d(sQ + SATOM, &tm_qk, bar(B_QDO), h * 128 + 64, rq);
-      tma_load_2d(sdO, &tm_dy, bar(B_QDO), h * 128, rq);
-      tma_load_2d(sdO + SATOM, &tm_dy, bar(B_QDO), h * 128 + 64, rq);
-      for (int j = 0; j < n; ++j) {
-        const int ks = j % 3, vs = j & 1;
-        const int r = row0 + (kt0 + j) * ST;
-        if (j >= 3 && !mbar_wait(bar(B_KFREE0 + ks), (uint32_t)(((j - 3) / 3) & 1), abort_flag, p.err, ERR_WAIT_EMPTY)) break;
-        mbar_arrive_expect_tx(bar(B_K0 + ks), STILE);
-        tma_load_2d(sK(ks), &tm_qk, bar(B_K0 + ks), A + h * 128, r);
-        tma_load_2d(sK(ks) + SATOM, &tm_qk, bar(B_K0 + ks), A + h * 128 + 64, r);
-        if (j >= 2 && !mbar_wait(bar(B_VFREE0 + vs), (uint32_t)(((j - 2) >> 1) & 1), abort_flag, p.err, ERR_WAIT_EMPTY)) break;
-        mbar_arrive_expect_tx(bar(B_V0 + vs), STILE);
-        tma_load_2d(sV(vs), &tm_v, bar(B_V0 + vs), 2 * A + h * 128, r);
-        tma_load_2d(sV(vs) + SATOM, &tm_v, bar(B_V0 + vs), 2 * A + h * 128 + 64, r);
+      int g = 0, it = 0;
+      bool ok = true;
+      for (;; ++it) {
+        const int w = ok ? item_publish(ring_bars, ring_slots, it, p.items, total) : -1;
+        if (w < 0) break;
+        const DqItem im = dq_item(p, w, n_tiles);
+        const int row0 = im.b * p.T, rq = row0 + im.qt * ST;
+        if (it >= 1 && !mbar_wait(bar(B_QDOFREE), (uint32_t)((it - 1) & 1), abort_flag, p.err, ERR_WAIT_EMPTY)) break;
+        mbar_arrive_expect_tx(bar(B_QDO), 2 * STILE);
+        tma_load_2d(sQ, &tm_qk, bar(B_QDO), im.h * 128, rq);
+        tma_load_2d(sQ + SATOM, &tm_qk, bar(B_QDO), im.h * 128 + 64, rq);
+        tma_load_2d(sdO, &tm_dy, bar(B_QDO), im.h * 128, rq);
+        tma_load_2d(sdO + SATOM, &tm_dy, bar(B_QDO), im.h * 128 + 64, rq);
+        for (int j = 0; j < im.n; ++j, ++g) {
+          const int ks = g % 3, vs = g & 1;
+          const int r = row0 + (im.kt0 + j) * ST;
+          if (g >= 3 && !mbar_wait(bar(B_KFREE0 + ks), (uint32_t)(((g - 3) / 3) & 1), abort_flag, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+          mbar_arrive_expect_tx(bar(B_K0 + ks), STILE);
+          tma_load_2d(sK(ks), &tm_qk, bar(B_K0 + ks), A + im.h * 128, r);
+          tma_load_2d(sK(ks) + SATOM, &tm_qk, bar(B_K0 + ks), A + im.h * 128 + 64, r);
+          if (g >= 2 && !mbar_wait(bar(B_VFREE0 + vs), (uint32_t)(((g - 2) >> 1) & 1), abort_flag, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+          mbar_arrive_expect_tx(bar(B_V0 + vs), STILE);
+          tma_load_2d(sV(vs), &tm_v, bar(B_V0 + vs), 2 * A + im.h * 128, r);
+          tma_load_2d(sV(vs) + SATOM, &tm_v, bar(B_V0 + vs), 2 * A + im.h * 128 + 64, r);
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t id_kk = umma_idesc_f16(128, 128, 1, 0, 0);
       const uint32_t id_km = umma_idesc_f16(128, 128, 1, 0, 1);
-      bool ok = mbar_wait(bar(B_QDO), 0, abort_flag, p.err, ERR_WAIT_FULL);
-      if (ok) ok = mbar_wait(bar(B_K0), 0, abort_flag, p.err, ERR_WAIT_FULL);
-      if (ok) {
+      // S(t) and dP(t) of running tile t; `last`: t is the last tile of its item, after which Q and dO may be reloaded
+      auto issue_sdp = [&](int t, bool last) -> bool {
+        if (!mbar_wait(bar(B_K0 + t % 3), (uint32_t)((t / 3) & 1), abort_flag, p.err, ERR_WAIT_FULL)) return false;
+        if (t >= 1 && !mbar_wait(bar(B_SFREE), (uint32_t)((t - 1) & 1), abort_flag, p.err, ERR_WAIT_AUX)) return false;
         tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < 8; ++k) umma_f16(tS, sdesc_k(sQ, k), sdesc_k(sK(0), k), id_kk, k ? 1u : 0u);
+        for (int k = 0; k < 8; ++k) umma_f16(tS, sdesc_k(sQ, k), sdesc_k(sK(t % 3), k), id_kk, k ? 1u : 0u);
         tc_commit(bar(B_SFULL));
-        ok = mbar_wait(bar(B_V0), 0, abort_flag, p.err, ERR_WAIT_FULL);
-      }
-      if (ok) {
+        if (!mbar_wait(bar(B_V0 + (t & 1)), (uint32_t)((t >> 1) & 1), abort_flag, p.err, ERR_WAIT_FULL)) return false;
         tc_fence_after();
+        // dP(t) goes into the buffer whose packed dS(t-2) the dQ MMAs of tile t-2 (issued earlier, same pipe) have read
 #pragma unroll
-        for (int k = 0; k < 8; ++k) umma_f16(tdP(0), sdesc_k(sdO, k), sdesc_k(sV(0), k), id_kk, k ? 1u : 0u);
-        tc_commit(bar(B_DPFULL0));
-        tc_commit(bar(B_VFREE0));
-      }
-      for (int j = 0; j < n && ok; ++j) {
-        const int s = j & 1;
-        if (j + 1 < n) {
-          // S(j+1) as soon as the compute warps hold S(j) in registers; dP(j+1) into the other dP buffer, whose packed
-          // dS(j-1) the dQ MMAs of tile j-1 (issued earlier, same pipe) have read by then
-          const int kn = (j + 1) % 3;
-          if (!mbar_wait(bar(B_K0 + kn), (uint32_t)(((j + 1) / 3) & 1), abort_flag, p.err, ERR_WAIT_FULL)) { ok = false; break; }
-          if (!mbar_wait(bar(B_SFREE), (uint32_t)(j & 1), abort_flag, p.err, ERR_WAIT_AUX)) { ok = false; break; }
+        for (int k = 0; k < 8; ++k) umma_f16(tdP(t & 1), sdesc_k(sdO, k), sdesc_k(sV(t & 1), k), id_kk, k ? 1u : 0u);
+        tc_commit(bar(B_DPFULL0 + (t & 1)));
+        tc_commit(bar(B_VFREE0 + (t & 1)));
+        if (last) tc_commit(bar(B_QDOFREE));
+        return true;
+      };
+      int g = 0, it = 0;
+      bool ok = true;
+      for (;; ++it) {
+        const int w = ok ? item_take(ring_bars, ring_slots, it, abort_flag, p.err) : -1;
+        if (w < 0) break;
+        const DqItem im = dq_item(p, w, n_tiles);
+        if (!mbar_wait(bar(B_QDO), (uint32_t)(it & 1), abort_flag, p.err, ERR_WAIT_FULL)) break;
+        for (int j = 0; j < im.n; ++j, ++g) {
+          if (j == 0 && !issue_sdp(g, im.n == 1)) { ok = false; break; }
+          if (j + 1 < im.n && !issue_sdp(g + 1, j + 2 == im.n)) { ok = false; break; }
+          // dS(g) sits packed in the dP(g) columns: dQ += dS Kh(g), which also frees that K stage
+          if (!mbar_wait(bar(B_DSREADY), (uint32_t)(g & 1), abort_flag, p.err, ERR_WAIT_AUX)) { ok = false; break; }
+          if (j == 0 && it >= 1 && !mbar_wait(bar(B_DQFREE), (uint32_t)((it - 1) & 1), abort_flag, p.err, ERR_WAIT_TMEM_EMPTY)) {
+            ok = false;
+            break;
+          }
           tc_fence_after();
 #pragma unroll
-          for (int k = 0; k < 8; ++k) umma_f16(tS, sdesc_k(sQ, k), sdesc_k(sK(kn), k), id_kk, k ? 1u : 0u);
-          tc_commit(bar(B_SFULL));
-          if (!mbar_wait(bar(B_V0 + (s ^ 1)), (uint32_t)(((j + 1) >> 1) & 1), abort_flag, p.err, ERR_WAIT_FULL)) { ok = false; break; }
-          tc_fence_after();
-#pragma unroll
-          for (int k = 0; k < 8; ++k) umma_f16(tdP(s ^ 1), sdesc_k(sdO, k), sdesc_k(sV(s ^ 1), k), id_kk, k ? 1u : 0u);
-          tc_commit(bar(B_DPFULL0 + (s ^ 1)));
-          tc_commit(bar(B_VFREE0 + (s ^ 1)));
+          for (int k = 0; k < 8; ++k)
+            umma_f16_ts(tdQ, tdP(g & 1) + packed_col(k), sdesc_mn(sK(g % 3), k), id_km, (j | k) ? 1u : 0u);
+          tc_commit(bar(B_KFREE0 + g % 3));
+          if (j + 1 == im.n) tc_commit(bar(B_DONE));
         }
-        // dS(j) sits packed in the dP(j) columns: dQ += dS Kh(j), which also frees that K/V stage
-        if (!mbar_wait(bar(B_DSREADY), (uint32_t)(j & 1), abort_flag, p.err, ERR_WAIT_AUX)) { ok = false; break; }
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < 8; ++k) umma_f16_ts(tdQ, tdP(s) + packed_col(k), sdesc_mn(sK(j % 3), k), id_km, (j | k) ? 1u : 0u);
-        tc_commit(bar(B_KFREE0 + j % 3));
-        if (j + 1 == n) tc_commit(bar(B_DONE));
       }
     }
   } else {
@@ -497,67 +527,74 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_const
     const int r = q * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
     const int c0 = half * 64;
-    const int qpos = qt * ST + r;
-    const float2 st = p.stats[((long long)b * p.H + h) * p.T + qpos];
-    int lo = 0;
-    if (p.doc_start) lo = p.doc_start[(long long)b * p.T + qpos];
     bool ok = true;
-    for (int j = 0; j < n && ok; ++j) {
-      const int s = j & 1;
-      bool got = mbar_wait(bar(B_SFULL), (uint32_t)(j & 1), abort_flag, p.err, ERR_WAIT_TMEM_FULL);
-      if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
-      tc_fence_after();
-      const int k0 = (kt0 + j) * ST + c0;
-      const bool need_mask = __any_sync(0xffffffffu, (k0 + 63 > qpos) || (k0 < lo));
-      float pr[64];
-      {
-        uint32_t v0[32], v1[32];
-        __syncwarp();
-        BONES_TMEM_LD32(tS + lane_addr + (uint32_t)c0, v0);
-        BONES_TMEM_LD32(tS + lane_addr + (uint32_t)(c0 + 32), v1);
-        tmem_ld_wait();
+    int g = 0, it = 0;
+    for (;; ++it) {
+      const int w = ok ? item_take(ring_bars, ring_slots, it, abort_flag, p.err) : -1;
+      if (w < 0) break;
+      const DqItem im = dq_item(p, w, n_tiles);
+      const int qpos = im.qt * ST + r, row0 = im.b * p.T;
+      const float2 st = p.stats[((long long)im.b * p.H + im.h) * p.T + qpos];
+      int lo = 0;
+      if (p.doc_start) lo = p.doc_start[(long long)im.b * p.T + qpos];
+      for (int j = 0; j < im.n; ++j, ++g) {
+        const int s = g & 1;
+        bool got = mbar_wait(bar(B_SFULL), (uint32_t)(g & 1), abort_flag, p.err, ERR_WAIT_TMEM_FULL);
+        if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+        tc_fence_after();
+        const int k0 = (im.kt0 + j) * ST + c0;
+        const bool need_mask = __any_sync(0xffffffffu, (k0 + 63 > qpos) || (k0 < lo));
+        float pr[64];
+        {
+          uint32_t v0[32], v1[32];
+          __syncwarp();
+          BONES_TMEM_LD32(tS + lane_addr + (uint32_t)c0, v0);
+          BONES_TMEM_LD32(tS + lane_addr + (uint32_t)(c0 + 32), v1);
+          tmem_ld_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(B_SFREE));
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            pr[i] = ex2_fast(fmaf(__uint_as_float(v0[i]), p.c1, st.x));
+            pr[32 + i] = ex2_fast(fmaf(__uint_as_float(v1[i]), p.c1, st.x));
+          }
+        }
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            const int kp = k0 + i;
+            if (kp > qpos || kp < lo) pr[i] = 0.f;
+          }
+        }
+        got = mbar_wait(bar(B_DPFULL0 + s), (uint32_t)((g >> 1) & 1), abort_flag, p.err, ERR_WAIT_TMEM_FULL);
+        if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+        tc_fence_after();
+        {
+          uint32_t v0[32], v1[32];
+          __syncwarp();
+          BONES_TMEM_LD32(tdP(s) + lane_addr + (uint32_t)c0, v0);
+          BONES_TMEM_LD32(tdP(s) + lane_addr + (uint32_t)(c0 + 32), v1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            pr[i] *= (__uint_as_float(v0[i]) - st.y) * p.scale;
+            pr[32 + i] *= (__uint_as_float(v1[i]) - st.y) * p.scale;
+          }
+        }
+        store_packed64(tdP(s) + lane_addr + (uint32_t)c0, pr);
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar(B_SFREE));
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          pr[i] = ex2_fast(fmaf(__uint_as_float(v0[i]), p.c1, st.x));
-          pr[32 + i] = ex2_fast(fmaf(__uint_as_float(v1[i]), p.c1, st.x));
-        }
+        if (lane == 0) mbar_arrive(bar(B_DSREADY));
       }
-      if (need_mask) {
-#pragma unroll
-        for (int i = 0; i < 64; ++i) {
-          const int kp = k0 + i;
-          if (kp > qpos || kp < lo) pr[i] = 0.f;
-        }
-      }
-      got = mbar_wait(bar(B_DPFULL0 + s), (uint32_t)((j >> 1) & 1), abort_flag, p.err, ERR_WAIT_TMEM_FULL);
+      if (!ok) break;
+      const bool got = mbar_wait(bar(B_DONE), (uint32_t)(it & 1), abort_flag, p.err, ERR_WAIT_TMEM_FULL);
       if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
       tc_fence_after();
-      {
-        uint32_t v0[32], v1[32];
-        __syncwarp();
-        BONES_TMEM_LD32(tdP(s) + lane_addr + (uint32_t)c0, v0);
-        BONES_TMEM_LD32(tdP(s) + lane_addr + (uint32_t)(c0 + 32), v1);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          pr[i] *= (__uint_as_float(v0[i]) - st.y) * p.scale;
-          pr[32 + i] *= (__uint_as_float(v1[i]) - st.y) * p.scale;
-        }
-      }
-      store_packed64(tdP(s) + lane_addr + (uint32_t)c0, pr);
+      drain_row64(tdQ + lane_addr + (uint32_t)c0, p.dqk + ((long long)(row0 + qpos)) * 2 * A + (long long)im.h * 128 + c0);
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_DSREADY));
-    }
-    if (ok && n > 0) {
-      const bool got = mbar_wait(bar(B_DONE), 0, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
-      if (__all_sync(0xffffffffu, got)) {
-        tc_fence_after();
-        drain_row64(tdQ + lane_addr + (uint32_t)c0, p.dqk + ((long long)(row0 + qpos)) * 2 * A + (long long)h * 128 + c0);
-      }
+      if (lane == 0) mbar_arrive(bar(B_DQFREE));
     }
   }
 
@@ -620,7 +657,7 @@ int bones_attn_bwd_split(const void* qk, const void* qkv, const void* dy, const 
   p.dv_ld = dv_ld;
   p.err = error_word();
   constexpr size_t smem_dkv = (size_t)DKV_BARS + 160 + DKV_SLACK;
-  constexpr size_t smem_dq = (size_t)DQ_BARS + 160 + 1024;
+  constexpr size_t smem_dq = (size_t)DQ_BARS + 256 + 1024;
   static bool attr_done = false;
   if (!attr_done) {
     BONES_CHECK(cudaFuncSetAttribute(attn_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dkv));
@@ -631,7 +668,17 @@ int bones_attn_bwd_split(const void* qk, const void* qkv, const void* dy, const 
   cudaStream_t s = (cudaStream_t)stream;
   attn_bwd_dkv_kernel<<<grid, 320, smem_dkv, s>>>(tq, tv, td, p);
   BONES_CHECK(cudaGetLastError());
-  attn_bwd_dq_kernel<<<grid, 320, smem_dq, s>>>(tq, tv, td, p);
+  int dev = 0, sms = 0;
+  BONES_CHECK(cudaGetDevice(&dev));
+  BONES_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const long long items = (long long)(T / ST) * H * B;
+  const unsigned grid_dq = (unsigned)(items < sms ? items : sms);       // persistent: one CTA per SM
+  static int* counter[64] = {};
+  if (dev < 0 || dev >= 64) return -2;
+  if (!counter[dev]) BONES_CHECK(cudaGetSymbolAddress(reinterpret_cast<void**>(&counter[dev]), g_dq_items));
+  BONES_CHECK(cudaMemsetAsync(counter[dev], 0, sizeof(int), s));
+  p.items = counter[dev];
+  attn_bwd_dq_kernel<<<grid_dq, 320, smem_dq, s>>>(tq, tv, td, p);
   return (int)cudaGetLastError();
 }
 }  // extern "C"

@@ -73,6 +73,22 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// Dynamic work distribution for persistent kernels: the CTA's producer thread draws item numbers from a global counter
+// (zeroed by the host before the launch) and hands them to the CTA's other roles through a four-slot ring in shared
+// memory (four mbarriers of count 1 at `bars`, four ints at `slots`).  A role may run at most three items behind the
+// producer.  -1 ends the walk.
+__device__ __forceinline__ int item_publish(uint32_t bars, volatile int* slots, int it, int* counter, int total) {
+  const int w = atomicAdd(counter, 1);
+  const int v = w < total ? w : -1;
+  slots[it & 3] = v;
+  mbar_arrive(bars + 8u * (uint32_t)(it & 3));
+  return v;
+}
+__device__ __forceinline__ int item_take(uint32_t bars, volatile int* slots, int it, volatile int* abort_flag, int* err) {
+  if (!mbar_wait(bars + 8u * (uint32_t)(it & 3), (uint32_t)((it >> 2) & 1), abort_flag, err, ERR_WAIT_AUX)) return -1;
+  return slots[it & 3];
+}
+
 // ---------------------------------------------------------------------------------------------------------------
 // TMA (bulk tensor copies; no cluster multicast anywhere)
 // ---------------------------------------------------------------------------------------------------------------
