@@ -32,7 +32,7 @@ struct SplitParams {
   __nv_bfloat16* dv;     // rows of dv_ld elements
   long long dv_ld;
   int* err;
-  int* items;            // device counter the persistent dQ CTAs draw their work items from (zero at launch)
+  int* items;            // device counter the persistent CTAs of a launch draw their work items from (zero at launch)
 };
 
 __device__ __forceinline__ int split_first_tile(const SplitParams& p, int b, int qt) {
@@ -116,10 +116,34 @@ __global__ void attn_bwd_stats_kernel(const __nv_bfloat16* __restrict__ dy, cons
 // dK / dV  (transposed: TMEM lanes are keys, columns are queries).  A Q tile lives from S^T(i) (issued during tile
 //          i-1) to dK(i), so Q has a ring of three; dO (with the tile's statistics) is first needed a tile later and
 //          has a ring of two.
+//          Persistent: one CTA per SM draws (key tile, head, batch) items from a device counter, the key tiles of one
+//          (head, batch) side by side.  Barrier phases and the Q / dO rings run on across items; K and V are
+//          single-buffered and reloaded as soon as the item's last S^T and dP^T MMAs have been issued, so the next
+//          item's first tiles are computed while the compute warps drain dK and dV.
 // ---------------------------------------------------------------------------------------------------------------
 constexpr uint32_t DKV_STAT = STILE * 7;            // two stages of 128 x (float2 stats), travelling with dO
 constexpr uint32_t DKV_BARS = DKV_STAT + 2 * 1024;
 constexpr uint32_t DKV_SLACK = 512;                 // room for aligning the tiles to 1024 bytes
+
+__device__ int g_dkv_items;      // item counter of the persistent dK/dV kernel (one launch at a time per device)
+
+struct DkvItem {
+  int kt, h, b, n;
+};
+__device__ __forceinline__ DkvItem dkv_item(const SplitParams& p, int w, int n_tiles) {
+  DkvItem it;
+  const int grp = w / n_tiles;
+  it.kt = w % n_tiles;                                // longest walks (small kt) of a (head, batch) first
+  it.h = grp % p.H;
+  it.b = grp / p.H;
+  int n = 0;
+  for (int qt = it.kt; qt < n_tiles; ++qt) {          // the query tiles that see this key tile
+    if (split_first_tile(p, it.b, qt) > it.kt) break;
+    ++n;
+  }
+  it.n = n;                                           // >= 1: a key tile is always seen by its own query tile
+  return it;
+}
 
 __global__ void __launch_bounds__(320, 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant__ CUtensorMap tm_v,
@@ -136,20 +160,23 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
   auto sQ = [&](int s) { return base + STILE * (2 + s); };       // three stages
   auto sdO = [&](int s) { return base + STILE * (5 + s); };      // two stages
   const uint32_t bars = base + DKV_BARS;
-  enum { B_KV = 0, B_Q0, B_Q1, B_Q2, B_QFREE0, B_QFREE1, B_QFREE2, B_DO0, B_DO1, B_DOFREE0, B_DOFREE1, B_SFULL, B_DPFULL, B_PREADY,
-         B_DSREADY, B_DONE, B_COUNT };
+  enum { B_KV = 0, B_KVFREE, B_Q0, B_Q1, B_Q2, B_QFREE0, B_QFREE1, B_QFREE2, B_DO0, B_DO1, B_DOFREE0, B_DOFREE1, B_SFULL, B_DPFULL,
+         B_PREADY, B_DSREADY, B_DONE, B_ACCFREE, B_COUNT };
   auto bar = [&](int i) { return bars + 8u * i; };
   const uint32_t tmem_slot = bars + 8u * B_COUNT;
   volatile uint32_t* tmem_slot_g = reinterpret_cast<volatile uint32_t*>(gen + DKV_BARS + 8 * B_COUNT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + DKV_BARS + 8 * B_COUNT + 8);
+  const uint32_t ring_bars = bars + 176u;
+  volatile int* ring_slots = reinterpret_cast<volatile int*>(gen + DKV_BARS + 208);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kt = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int A = p.H * 128;
   const int n_tiles = p.T / ST;
+  const int total = n_tiles * p.H * p.B;
 
   if (threadIdx.x == 0) {
     mbar_init(bar(B_KV), 1);
+    mbar_init(bar(B_KVFREE), 1);
     for (int s = 0; s < 3; ++s) {
       mbar_init(bar(B_Q0 + s), 1);
       mbar_init(bar(B_QFREE0 + s), 1);
@@ -163,6 +190,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
     mbar_init(bar(B_PREADY), 8);
     mbar_init(bar(B_DSREADY), 8);
     mbar_init(bar(B_DONE), 1);
+    mbar_init(bar(B_ACCFREE), 8);
+    for (int s = 0; s < 4; ++s) mbar_init(ring_bars + 8u * s, 1);
     *abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tm_qk);
@@ -180,85 +209,93 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
   const uint32_t tmem = *tmem_slot_g;
   const uint32_t tS = tmem, tdP = tmem + 128, tdV = tmem + 256, tdK = tmem + 384;
 
-  int n = 0;
-  for (int qt = kt; qt < n_tiles; ++qt) {
-    if (split_first_tile(p, b, qt) > kt) break;
-    ++n;
-  }
-  const int row0 = b * p.T;
-
   if (warp == 0) {
     if (lane == 0) {
-      mbar_arrive_expect_tx(bar(B_KV), 2 * STILE);
-      tma_load_2d(sK, &tm_qk, bar(B_KV), A + h * 128, row0 + kt * ST);
-      tma_load_2d(sK + SATOM, &tm_qk, bar(B_KV), A + h * 128 + 64, row0 + kt * ST);
-      tma_load_2d(sV, &tm_v, bar(B_KV), 2 * A + h * 128, row0 + kt * ST);
-      tma_load_2d(sV + SATOM, &tm_v, bar(B_KV), 2 * A + h * 128 + 64, row0 + kt * ST);
-      const float2* stat_row = p.stats + ((long long)b * p.H + h) * p.T;
-      for (int i = 0; i < n; ++i) {
-        const int qs = i % 3, ds = i & 1;
-        const int r = row0 + (kt + i) * ST;
-        if (i >= 3 && !mbar_wait(bar(B_QFREE0 + qs), (uint32_t)(((i - 3) / 3) & 1), abort_flag, p.err, ERR_WAIT_EMPTY)) break;
-        mbar_arrive_expect_tx(bar(B_Q0 + qs), STILE);
-        tma_load_2d(sQ(qs), &tm_qk, bar(B_Q0 + qs), h * 128, r);
-        tma_load_2d(sQ(qs) + SATOM, &tm_qk, bar(B_Q0 + qs), h * 128 + 64, r);
-        if (i >= 2 && !mbar_wait(bar(B_DOFREE0 + ds), (uint32_t)(((i - 2) >> 1) & 1), abort_flag, p.err, ERR_WAIT_EMPTY)) break;
-        mbar_arrive_expect_tx(bar(B_DO0 + ds), STILE + 1024);
-        tma_load_2d(sdO(ds), &tm_dy, bar(B_DO0 + ds), h * 128, r);
-        tma_load_2d(sdO(ds) + SATOM, &tm_dy, bar(B_DO0 + ds), h * 128 + 64, r);
-        bulk_load(base + DKV_STAT + ds * 1024, stat_row + (kt + i) * ST, 1024, bar(B_DO0 + ds));
+      int g = 0, it = 0;
+      bool ok = true;
+      for (;; ++it) {
+        const int w = ok ? item_publish(ring_bars, ring_slots, it, p.items, total) : -1;
+        if (w < 0) break;
+        const DkvItem im = dkv_item(p, w, n_tiles);
+        const int row0 = im.b * p.T;
+        if (it >= 1 && !mbar_wait(bar(B_KVFREE), (uint32_t)((it - 1) & 1), abort_flag, p.err, ERR_WAIT_EMPTY)) break;
+        mbar_arrive_expect_tx(bar(B_KV), 2 * STILE);
+        tma_load_2d(sK, &tm_qk, bar(B_KV), A + im.h * 128, row0 + im.kt * ST);
+        tma_load_2d(sK + SATOM, &tm_qk, bar(B_KV), A + im.h * 128 + 64, row0 + im.kt * ST);
+        tma_load_2d(sV, &tm_v, bar(B_KV), 2 * A + im.h * 128, row0 + im.kt * ST);
+        tma_load_2d(sV + SATOM, &tm_v, bar(B_KV), 2 * A + im.h * 128 + 64, row0 + im.kt * ST);
+        const float2* stat_row = p.stats + ((long long)im.b * p.H + im.h) * p.T;
+        for (int i = 0; i < im.n; ++i, ++g) {
+          const int qs = g % 3, ds = g & 1;
+          const int r = row0 + (im.kt + i) * ST;
+          if (g >= 3 && !mbar_wait(bar(B_QFREE0 + qs), (uint32_t)(((g - 3) / 3) & 1), abort_flag, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+          mbar_arrive_expect_tx(bar(B_Q0 + qs), STILE);
+          tma_load_2d(sQ(qs), &tm_qk, bar(B_Q0 + qs), im.h * 128, r);
+          tma_load_2d(sQ(qs) + SATOM, &tm_qk, bar(B_Q0 + qs), im.h * 128 + 64, r);
+          if (g >= 2 && !mbar_wait(bar(B_DOFREE0 + ds), (uint32_t)(((g - 2) >> 1) & 1), abort_flag, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+          mbar_arrive_expect_tx(bar(B_DO0 + ds), STILE + 1024);
+          tma_load_2d(sdO(ds), &tm_dy, bar(B_DO0 + ds), im.h * 128, r);
+          tma_load_2d(sdO(ds) + SATOM, &tm_dy, bar(B_DO0 + ds), im.h * 128 + 64, r);
+          bulk_load(base + DKV_STAT + ds * 1024, stat_row + (im.kt + i) * ST, 1024, bar(B_DO0 + ds));
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       const uint32_t id_kk = umma_idesc_f16(128, 128, 1, 0, 0);
       const uint32_t id_km = umma_idesc_f16(128, 128, 1, 0, 1);
-      bool ok = mbar_wait(bar(B_KV), 0, abort_flag, p.err, ERR_WAIT_FULL);
-      if (ok) ok = mbar_wait(bar(B_Q0), 0, abort_flag, p.err, ERR_WAIT_FULL);
-      if (ok) {
+      auto issue_s = [&](int t) -> bool {                 // S^T(t) = Kh Qh(t)^T
+        if (!mbar_wait(bar(B_Q0 + t % 3), (uint32_t)((t / 3) & 1), abort_flag, p.err, ERR_WAIT_FULL)) return false;
         tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < 8; ++k) umma_f16(tS, sdesc_k(sK, k), sdesc_k(sQ(0), k), id_kk, k ? 1u : 0u);
+        for (int k = 0; k < 8; ++k) umma_f16(tS, sdesc_k(sK, k), sdesc_k(sQ(t % 3), k), id_kk, k ? 1u : 0u);
         tc_commit(bar(B_SFULL));
-        ok = mbar_wait(bar(B_DO0), 0, abort_flag, p.err, ERR_WAIT_FULL);
-      }
-      if (ok) {
+        return true;
+      };
+      auto issue_dp = [&](int t, bool last) -> bool {     // dP^T(t) = V dO(t)^T; after the item's last one K and V are free
+        if (!mbar_wait(bar(B_DO0 + (t & 1)), (uint32_t)((t >> 1) & 1), abort_flag, p.err, ERR_WAIT_FULL)) return false;
         tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < 8; ++k) umma_f16(tdP, sdesc_k(sV, k), sdesc_k(sdO(0), k), id_kk, k ? 1u : 0u);
+        for (int k = 0; k < 8; ++k) umma_f16(tdP, sdesc_k(sV, k), sdesc_k(sdO(t & 1), k), id_kk, k ? 1u : 0u);
         tc_commit(bar(B_DPFULL));
-      }
-      for (int i = 0; i < n && ok; ++i) {
-        const int s = i & 1, qs = i % 3, qn = (i + 1) % 3;
-        const uint32_t ph = (uint32_t)(i & 1);
-        const bool more = i + 1 < n;
-        // P^T(i) sits packed in the S^T columns: dV += P^T dO, then S^T(i+1) behind it (same pipe, in order)
-        if (!mbar_wait(bar(B_PREADY), ph, abort_flag, p.err, ERR_WAIT_AUX)) { ok = false; break; }
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < 8; ++k) umma_f16_ts(tdV, tS + packed_col(k), sdesc_mn(sdO(s), k), id_km, (i | k) ? 1u : 0u);
-        if (more) {
-          if (!mbar_wait(bar(B_Q0 + qn), (uint32_t)(((i + 1) / 3) & 1), abort_flag, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+        if (last) tc_commit(bar(B_KVFREE));
+        return true;
+      };
+      int g = 0, it = 0;
+      bool ok = true;
+      for (;; ++it) {
+        const int w = ok ? item_take(ring_bars, ring_slots, it, abort_flag, p.err) : -1;
+        if (w < 0) break;
+        const DkvItem im = dkv_item(p, w, n_tiles);
+        if (!mbar_wait(bar(B_KV), (uint32_t)(it & 1), abort_flag, p.err, ERR_WAIT_FULL)) break;
+        // the first tile's S^T and dP^T go behind the previous item's last dV / dK MMAs on the same (in-order) pipe
+        if (!issue_s(g) || !issue_dp(g, im.n == 1)) break;
+        for (int i = 0; i < im.n; ++i, ++g) {
+          const int s = g & 1, qs = g % 3;
+          const uint32_t ph = (uint32_t)(g & 1);
+          const bool more = i + 1 < im.n;
+          // P^T(g) sits packed in the S^T columns: dV += P^T dO, then S^T(g+1) behind it
+          if (!mbar_wait(bar(B_PREADY), ph, abort_flag, p.err, ERR_WAIT_AUX)) { ok = false; break; }
+          if (i == 0 && it >= 1 && !mbar_wait(bar(B_ACCFREE), (uint32_t)((it - 1) & 1), abort_flag, p.err, ERR_WAIT_TMEM_EMPTY)) {
+            ok = false;                                   // the previous item's dK / dV have not been drained
+            break;
+          }
           tc_fence_after();
 #pragma unroll
-          for (int k = 0; k < 8; ++k) umma_f16(tS, sdesc_k(sK, k), sdesc_k(sQ(qn), k), id_kk, k ? 1u : 0u);
-          tc_commit(bar(B_SFULL));
-        }
-        // dS^T(i) sits packed in the dP^T columns: dK += dS^T Qh, then dP^T(i+1) behind it
-        if (!mbar_wait(bar(B_DSREADY), ph, abort_flag, p.err, ERR_WAIT_AUX)) { ok = false; break; }
-        tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < 8; ++k) umma_f16_ts(tdK, tdP + packed_col(k), sdesc_mn(sQ(qs), k), id_km, (i | k) ? 1u : 0u);
-        tc_commit(bar(B_QFREE0 + qs));
-        tc_commit(bar(B_DOFREE0 + s));       // dO(i) was read by dV(i); its statistics were in use until dS(i) was stored
-        if (more) {
-          if (!mbar_wait(bar(B_DO0 + (s ^ 1)), (uint32_t)(((i + 1) >> 1) & 1), abort_flag, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+          for (int k = 0; k < 8; ++k) umma_f16_ts(tdV, tS + packed_col(k), sdesc_mn(sdO(s), k), id_km, (i | k) ? 1u : 0u);
+          if (more && !issue_s(g + 1)) { ok = false; break; }
+          // dS^T(g) sits packed in the dP^T columns: dK += dS^T Qh, then dP^T(g+1) behind it
+          if (!mbar_wait(bar(B_DSREADY), ph, abort_flag, p.err, ERR_WAIT_AUX)) { ok = false; break; }
           tc_fence_after();
 #pragma unroll
-          for (int k = 0; k < 8; ++k) umma_f16(tdP, sdesc_k(sV, k), sdesc_k(sdO(s ^ 1), k), id_kk, k ? 1u : 0u);
-          tc_commit(bar(B_DPFULL));
-        } else {
-          tc_commit(bar(B_DONE));
+          for (int k = 0; k < 8; ++k) umma_f16_ts(tdK, tdP + packed_col(k), sdesc_mn(sQ(qs), k), id_km, (i | k) ? 1u : 0u);
+          tc_commit(bar(B_QFREE0 + qs));
+          tc_commit(bar(B_DOFREE0 + s));     // dO(g) was read by dV(g); its statistics were in use until dS(g) was stored
+          if (more) {
+            if (!issue_dp(g + 1, i + 2 == im.n)) { ok = false; break; }
+          } else {
+            tc_commit(bar(B_DONE));
+          }
         }
       }
     }
@@ -267,83 +304,90 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
     const int r = q * 32 + lane;                       // key row of this thread
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
     const int c0 = half * 64;                          // first query column of this thread
-    const int k0 = kt * ST, kpos = k0 + r;
     bool ok = true;
-    int nx_lo_last = (p.doc_start && n > 0) ? p.doc_start[(long long)b * p.T + kt * ST + ST - 1] : 0;
-    for (int i = 0; i < n && ok; ++i) {
-      const int s = i & 1;
-      const uint32_t ph = (uint32_t)(i & 1);
-      bool got = mbar_wait(bar(B_DO0 + s), (i >> 1) & 1, abort_flag, p.err, ERR_WAIT_FULL);   // this tile's statistics
-      if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
-      const float4* st4 = reinterpret_cast<const float4*>(gen + DKV_STAT + s * 1024) + c0 / 2;   // two queries per float4
-      // document starts of this tile's queries (global, cached): only the tile that straddles a document start past
-      // this key tile needs them element by element, and its last query decides that
-      const int* slo = p.doc_start ? p.doc_start + (long long)b * p.T + (kt + i) * ST : nullptr;
-      const bool need_doc = slo && nx_lo_last > k0;
-      if (slo && i + 1 < n) nx_lo_last = slo[2 * ST - 1];
-      float pr[64];
-      got = mbar_wait(bar(B_SFULL), ph, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
-      if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
-      tc_fence_after();
-      {
-        uint32_t v0[32], v1[32];
-        __syncwarp();
-        BONES_TMEM_LD32(tS + lane_addr + (uint32_t)c0, v0);
-        BONES_TMEM_LD32(tS + lane_addr + (uint32_t)(c0 + 32), v1);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const float4 a = st4[j], c = st4[16 + j];
-          pr[2 * j] = ex2_fast(fmaf(__uint_as_float(v0[2 * j]), p.c1, a.x));
-          pr[2 * j + 1] = ex2_fast(fmaf(__uint_as_float(v0[2 * j + 1]), p.c1, a.z));
-          pr[32 + 2 * j] = ex2_fast(fmaf(__uint_as_float(v1[2 * j]), p.c1, c.x));
-          pr[32 + 2 * j + 1] = ex2_fast(fmaf(__uint_as_float(v1[2 * j + 1]), p.c1, c.z));
-        }
-      }
-      if (i == 0) {                                    // diagonal tile: a key sees only queries at or after it
-#pragma unroll
-        for (int j = 0; j < 64; ++j)
-          if (r > c0 + j) pr[j] = 0.f;
-      }
-      if (need_doc) {                                  // a query sees only keys of its own document
-#pragma unroll
-        for (int j = 0; j < 64; ++j)
-          if (kpos < slo[c0 + j]) pr[j] = 0.f;
-      }
-      store_packed64(tS + lane_addr + (uint32_t)c0, pr);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_PREADY));
-      got = mbar_wait(bar(B_DPFULL), ph, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
-      if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
-      tc_fence_after();
-      {
-        uint32_t v0[32], v1[32];
-        __syncwarp();
-        BONES_TMEM_LD32(tdP + lane_addr + (uint32_t)c0, v0);
-        BONES_TMEM_LD32(tdP + lane_addr + (uint32_t)(c0 + 32), v1);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const float4 a = st4[j], c = st4[16 + j];
-          pr[2 * j] *= (__uint_as_float(v0[2 * j]) - a.y) * p.scale;
-          pr[2 * j + 1] *= (__uint_as_float(v0[2 * j + 1]) - a.w) * p.scale;
-          pr[32 + 2 * j] *= (__uint_as_float(v1[2 * j]) - c.y) * p.scale;
-          pr[32 + 2 * j + 1] *= (__uint_as_float(v1[2 * j + 1]) - c.w) * p.scale;
-        }
-      }
-      store_packed64(tdP + lane_addr + (uint32_t)c0, pr);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar(B_DSREADY));
-    }
-    if (ok && n > 0) {
-      const bool got = mbar_wait(bar(B_DONE), 0, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
-      if (__all_sync(0xffffffffu, got)) {
+    int g = 0, it = 0;
+    for (;; ++it) {
+      const int w = ok ? item_take(ring_bars, ring_slots, it, abort_flag, p.err) : -1;
+      if (w < 0) break;
+      const DkvItem im = dkv_item(p, w, n_tiles);
+      const int k0 = im.kt * ST, kpos = k0 + r, row0 = im.b * p.T;
+      int nx_lo_last = p.doc_start ? p.doc_start[(long long)im.b * p.T + im.kt * ST + ST - 1] : 0;
+      for (int i = 0; i < im.n; ++i, ++g) {
+        const int s = g & 1;
+        const uint32_t ph = (uint32_t)(g & 1);
+        bool got = mbar_wait(bar(B_DO0 + s), (uint32_t)((g >> 1) & 1), abort_flag, p.err, ERR_WAIT_FULL);   // this tile's statistics
+        if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+        const float4* st4 = reinterpret_cast<const float4*>(gen + DKV_STAT + s * 1024) + c0 / 2;   // two queries per float4
+        // document starts of this tile's queries (global, cached): only the tile that straddles a document start past
+        // this key tile needs them element by element, and its last query decides that
+        const int* slo = p.doc_start ? p.doc_start + (long long)im.b * p.T + (im.kt + i) * ST : nullptr;
+        const bool need_doc = slo && nx_lo_last > k0;
+        if (slo && i + 1 < im.n) nx_lo_last = slo[2 * ST - 1];
+        float pr[64];
+        got = mbar_wait(bar(B_SFULL), ph, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
+        if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
         tc_fence_after();
-        drain_row64(tdK + lane_addr + (uint32_t)c0, p.dqk + ((long long)(row0 + kpos)) * 2 * A + A + (long long)h * 128 + c0);
-        drain_row64(tdV + lane_addr + (uint32_t)c0, p.dv + ((long long)(row0 + kpos)) * p.dv_ld + (long long)h * 128 + c0);
+        {
+          uint32_t v0[32], v1[32];
+          __syncwarp();
+          BONES_TMEM_LD32(tS + lane_addr + (uint32_t)c0, v0);
+          BONES_TMEM_LD32(tS + lane_addr + (uint32_t)(c0 + 32), v1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float4 a = st4[j], c = st4[16 + j];
+            pr[2 * j] = ex2_fast(fmaf(__uint_as_float(v0[2 * j]), p.c1, a.x));
+            pr[2 * j + 1] = ex2_fast(fmaf(__uint_as_float(v0[2 * j + 1]), p.c1, a.z));
+            pr[32 + 2 * j] = ex2_fast(fmaf(__uint_as_float(v1[2 * j]), p.c1, c.x));
+            pr[32 + 2 * j + 1] = ex2_fast(fmaf(__uint_as_float(v1[2 * j + 1]), p.c1, c.z));
+          }
+        }
+        if (i == 0) {                                    // diagonal tile: a key sees only queries at or after it
+#pragma unroll
+          for (int j = 0; j < 64; ++j)
+            if (r > c0 + j) pr[j] = 0.f;
+        }
+        if (need_doc) {                                  // a query sees only keys of its own document
+#pragma unroll
+          for (int j = 0; j < 64; ++j)
+            if (kpos < slo[c0 + j]) pr[j] = 0.f;
+        }
+        store_packed64(tS + lane_addr + (uint32_t)c0, pr);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(B_PREADY));
+        got = mbar_wait(bar(B_DPFULL), ph, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
+        if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+        tc_fence_after();
+        {
+          uint32_t v0[32], v1[32];
+          __syncwarp();
+          BONES_TMEM_LD32(tdP + lane_addr + (uint32_t)c0, v0);
+          BONES_TMEM_LD32(tdP + lane_addr + (uint32_t)(c0 + 32), v1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float4 a = st4[j], c = st4[16 + j];
+            pr[2 * j] *= (__uint_as_float(v0[2 * j]) - a.y) * p.scale;
+            pr[2 * j + 1] *= (__uint_as_float(v0[2 * j + 1]) - a.w) * p.scale;
+            pr[32 + 2 * j] *= (__uint_as_float(v1[2 * j]) - c.y) * p.scale;
+            pr[32 + 2 * j + 1] *= (__uint_as_float(v1[2 * j + 1]) - c.w) * p.scale;
+          }
+        }
+        store_packed64(tdP + lane_addr + (uint32_t)c0, pr);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(B_DSREADY));
       }
+      if (!ok) break;
+      const bool got = mbar_wait(bar(B_DONE), (uint32_t)(it & 1), abort_flag, p.err, ERR_WAIT_TMEM_FULL);
+      if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+      tc_fence_after();
+      drain_row64(tdK + lane_addr + (uint32_t)c0, p.dqk + ((long long)(row0 + kpos)) * 2 * A + A + (long long)im.h * 128 + c0);
+      drain_row64(tdV + lane_addr + (uint32_t)c0, p.dv + ((long long)(row0 + kpos)) * p.dv_ld + (long long)im.h * 128 + c0);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B_ACCFREE));
     }
   }
 
@@ -656,7 +700,7 @@ int bones_attn_bwd_split(const void* qk, const void* qkv, const void* dy, const 
   p.dv = (__nv_bfloat16*)dv;
   p.dv_ld = dv_ld;
   p.err = error_word();
-  constexpr size_t smem_dkv = (size_t)DKV_BARS + 160 + DKV_SLACK;
+  constexpr size_t smem_dkv = (size_t)DKV_BARS + 256 + DKV_SLACK;
   constexpr size_t smem_dq = (size_t)DQ_BARS + 256 + 1024;
   static bool attr_done = false;
   if (!attr_done) {
@@ -664,21 +708,24 @@ int bones_attn_bwd_split(const void* qk, const void* qkv, const void* dy, const 
     BONES_CHECK(cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dq));
     attr_done = true;
   }
-  dim3 grid(T / ST, H, B);
   cudaStream_t s = (cudaStream_t)stream;
-  attn_bwd_dkv_kernel<<<grid, 320, smem_dkv, s>>>(tq, tv, td, p);
-  BONES_CHECK(cudaGetLastError());
   int dev = 0, sms = 0;
   BONES_CHECK(cudaGetDevice(&dev));
   BONES_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  const long long items = (long long)(T / ST) * H * B;
-  const unsigned grid_dq = (unsigned)(items < sms ? items : sms);       // persistent: one CTA per SM
-  static int* counter[64] = {};
   if (dev < 0 || dev >= 64) return -2;
-  if (!counter[dev]) BONES_CHECK(cudaGetSymbolAddress(reinterpret_cast<void**>(&counter[dev]), g_dq_items));
-  BONES_CHECK(cudaMemsetAsync(counter[dev], 0, sizeof(int), s));
-  p.items = counter[dev];
-  attn_bwd_dq_kernel<<<grid_dq, 320, smem_dq, s>>>(tq, tv, td, p);
+  const long long items = (long long)(T / ST) * H * B;
+  const unsigned grid = (unsigned)(items < sms ? items : sms);          // persistent: one CTA per SM in both kernels
+  static int* counter_dkv[64] = {};
+  static int* counter_dq[64] = {};
+  if (!counter_dkv[dev]) BONES_CHECK(cudaGetSymbolAddress(reinterpret_cast<void**>(&counter_dkv[dev]), g_dkv_items));
+  if (!counter_dq[dev]) BONES_CHECK(cudaGetSymbolAddress(reinterpret_cast<void**>(&counter_dq[dev]), g_dq_items));
+  BONES_CHECK(cudaMemsetAsync(counter_dkv[dev], 0, sizeof(int), s));
+  BONES_CHECK(cudaMemsetAsync(counter_dq[dev], 0, sizeof(int), s));
+  p.items = counter_dkv[dev];
+  attn_bwd_dkv_kernel<<<grid, 320, smem_dkv, s>>>(tq, tv, td, p);
+  BONES_CHECK(cudaGetLastError());
+  p.items = counter_dq[dev];
+  attn_bwd_dq_kernel<<<grid, 320, smem_dq, s>>>(tq, tv, td, p);
   return (int)cudaGetLastError();
 }
 }  // extern "C"
