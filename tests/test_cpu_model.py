@@ -277,3 +277,22 @@ def test_multi_token_prediction_targets_and_schedule():
     assert model.lm_head.weight.grad is not None
     model.eval()
     assert float(model(x, y)) == pytest.approx(base, rel=1e-6)   # evaluation is next-token only
+
+
+def test_label_smoothing_only_in_training():
+    torch.manual_seed(0)
+    cfg = tiny_cfg(n_layer=2, label_smoothing=0.1)
+    model = GPT(cfg)
+    model.init_weights()
+    with torch.no_grad():
+        model.lm_head.weight.normal_(0, 0.05)
+    x = torch.randint(1, 8192, (2, 64))
+    y = torch.roll(x, -1, 1)
+    model.train()
+    smooth = float(model(x, y))
+    model.eval()
+    plain = float(model(x, y))
+    with torch.no_grad():
+        h = model.trunk(x)
+        want = float(RF.softcap_cross_entropy(h, model.lm_head.weight, y, cfg.vocab_size, cfg.softcap, label_smoothing=0.1))
+    assert smooth == pytest.approx(want, rel=1e-6) and smooth != pytest.approx(plain, rel=1e-4)

@@ -129,9 +129,10 @@ def test_bounded_peer_wait_expires_with_an_error_code():
     assert float(x.sum()) == 8.0                           # the CUDA context is intact
 
 
+@pytest.mark.parametrize("smooth", [0.0, 0.1])
 @pytest.mark.parametrize("capped", [0, 1])
 @pytest.mark.parametrize("vocab,ld", [(65536, 65536), (50304, 50432), (8192, 8192), (2048, 2048)])
-def test_softcap_ce_row_kernel_matches_reference(vocab, ld, capped):
+def test_softcap_ce_row_kernel_matches_reference(vocab, ld, capped, smooth):
     """Loss-head kernel at full vocabulary width: per-row loss and the in-place logit gradient against fp32 PyTorch."""
     from them_bones_b200.ops import _lib as L
     from them_bones_b200.ops.cuda import _F, _I, _L
@@ -144,7 +145,7 @@ def test_softcap_ce_row_kernel_matches_reference(vocab, ld, capped):
     n_valid = torch.tensor([float((tg >= 0).sum())], device="cuda")
     lf = lg[:, :vocab].float().requires_grad_()
     z = cap * torch.tanh(lf / cap)
-    ref_rows = torch.nn.functional.cross_entropy(z, tg, ignore_index=-1, reduction="none")
+    ref_rows = torch.nn.functional.cross_entropy(z, tg, ignore_index=-1, reduction="none", label_smoothing=smooth)
     (ref_rows.sum() / n_valid[0]).backward()
     d = lg.clone()
     if capped:                                   # the kernel is handed logits that the GEMM epilogue already soft-capped
@@ -152,10 +153,10 @@ def test_softcap_ce_row_kernel_matches_reference(vocab, ld, capped):
         lf = lg[:, :vocab].float().requires_grad_()
         z = (cap * torch.tanh(lf / cap))
         z = z + (d[:, :vocab].float() - z).detach()          # forward value as stored (bf16), gradient through tanh
-        ref_rows = torch.nn.functional.cross_entropy(z, tg, ignore_index=-1, reduction="none")
+        ref_rows = torch.nn.functional.cross_entropy(z, tg, ignore_index=-1, reduction="none", label_smoothing=smooth)
         (ref_rows.sum() / n_valid[0]).backward()
     L.call("bones_softcap_ce", L.ptr(d), _L(ld), L.ptr(tg), _I(vocab), _F(cap), L.ptr(nll), L.ptr(d), L.ptr(None), L.ptr(n_valid),
-           _F(1.0), _I(m), _I(capped), L.ptr(None), L.ptr(None), L.ptr(None), L.ptr(None), L.ptr(None), L.stream())
+           _F(1.0), _I(m), _I(capped), L.ptr(None), L.ptr(None), L.ptr(None), L.ptr(None), L.ptr(None), _F(smooth), L.stream())
     torch.cuda.synchronize()
     L.check_error_word()
     assert float((nll - ref_rows).abs().max()) < 2e-2

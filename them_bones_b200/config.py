@@ -82,6 +82,7 @@ class GPTConfig:
     attn_layers: tuple = ()        # blocks that have attention (empty: all); the others are MLP-only
     mixer: str = "off"             # "shift1": attention-free blocks add mix_lambda * (x shifted by one token)
     mtp_offsets: tuple = ()        # extra next-token targets, e.g. (2, 3): predict t+2 and t+3 from position t
+    label_smoothing: float = 0.0   # training loss only; evaluation is the plain cross-entropy
     mlp_precision: str = "bf16"    # "bf16" | "mxfp8": block-scaled MLP / expert GEMMs
     moe_layers: tuple = ()
     moe_experts: int = 0
@@ -212,7 +213,7 @@ def switches(refresh: bool = False) -> dict:
         ROPE_BASE=e("ROPE_BASE", 100000.0, float), DOC_MASK=e("DOC_MASK", False, bool),
         ATTN_WINDOW=e("ATTN_WINDOW", 0, int), ATTN_LONG=e("ATTN_LONG", "", str),
         ATTN_LAYERS=e("ATTN_LAYERS", "", str), MIXER=e("MIXER", "off", str), MLP_RATIO=e("MLP_RATIO", 4, int),
-        MTP=e("MTP", "", str), MTP_WEIGHT=e("MTP_WEIGHT", 0.5, float), MTP_ANNEAL=e("MTP_ANNEAL", 0.5, float),
+        LABEL_SMOOTH=e("LABEL_SMOOTH", 0.0, float), MTP=e("MTP", "", str), MTP_WEIGHT=e("MTP_WEIGHT", 0.5, float), MTP_ANNEAL=e("MTP_ANNEAL", 0.5, float),
         MLP=e("MLP", "bf16", str),
         MOE=e("MOE", False, bool), MOE_LAYERS=e("MOE_LAYERS", "", str), MOE_EXPERTS=e("MOE_EXPERTS", 16, int),
         MOE_TOPK=e("MOE_TOPK", 2, int), MOE_HIDDEN=e("MOE_HIDDEN", 0, int), MOE_SHARED=e("MOE_SHARED", 0, int),
@@ -265,7 +266,7 @@ def build_config(depth: int, n_embd: int, n_head: int, seq_len: int, vocab: int,
     kw = dict(sequence_len=seq_len, vocab_size=vocab, n_layer=depth, n_head=n_head, n_embd=n_embd, head_dim=head_dim,
               rope_base=s["ROPE_BASE"], qk_scale=s["QK_SCALE"], bos_id=bos_id, doc_mask=s["DOC_MASK"], unet=s["UNET"],
               value_embeds=s["VE"], attn_window=s["ATTN_WINDOW"], mlp_precision=s["MLP"], mlp_ratio=s["MLP_RATIO"],
-              mixer=s["MIXER"])
+              mixer=s["MIXER"], label_smoothing=s["LABEL_SMOOTH"])
     if s["ATTN_LAYERS"]:
         kw["attn_layers"] = parse_layers(s["ATTN_LAYERS"], depth)
     if s["MTP"]:

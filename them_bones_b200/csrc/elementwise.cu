@@ -472,6 +472,7 @@ struct AuxTargets {
   const long long* tg[2];
   const float* w[2];        // absolute row weights (0 where the auxiliary target does not apply)
   float* nll_aux;           // [M], written when any auxiliary target is given
+  float smooth;             // label smoothing of the main target: loss = (1 - s) * nll + s * (lse - mean_v z_v)
 };
 
 // Softcap cross-entropy over full rows of bf16 logits [M, ldl] (first V columns valid), one CTA per row.
@@ -488,9 +489,9 @@ __global__ void softcap_ce_kernel(const __nv_bfloat16* logits, long long ldl, co
   const __nv_bfloat16* l = logits + (size_t)row * ldl;
   const long long tgt = targets[row];
   const float inv_cap = 1.0f / cap;
-  __shared__ float red[32];
-  __shared__ float s_total;
-  float s = 0.f;
+  __shared__ float red[32], red_t[32];
+  __shared__ float s_total, s_tsum;
+  float s = 0.f, st = 0.f;
   for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) {
     const uint4 u = *reinterpret_cast<const uint4*>(l + c);
     const uint32_t w[4] = {u.x, u.y, u.z, u.w};
@@ -499,22 +500,27 @@ __global__ void softcap_ce_kernel(const __nv_bfloat16* logits, long long ldl, co
       const float2 f = unpack_bf16(w[t]);
       const float t0 = capped ? f.x * inv_cap : tanhf(f.x * inv_cap), t1 = capped ? f.y * inv_cap : tanhf(f.y * inv_cap);
       s += __expf(cap * t0 - cap) + __expf(cap * t1 - cap);
+      st += t0 + t1;
     }
   }
   s = warp_sum(s);
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  st = warp_sum(st);
+  if ((threadIdx.x & 31) == 0) { red[threadIdx.x >> 5] = s; red_t[threadIdx.x >> 5] = st; }
   __syncthreads();
   if (threadIdx.x < 32) {
     float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    float vt = threadIdx.x < (blockDim.x >> 5) ? red_t[threadIdx.x] : 0.f;
     v = warp_sum(v);
-    if (threadIdx.x == 0) s_total = v;
+    vt = warp_sum(vt);
+    if (threadIdx.x == 0) { s_total = v; s_tsum = vt; }
   }
   __syncthreads();
   const float lse = logf(s_total) + cap;
+  const float sm = aux.smooth, mean_z = cap * s_tsum / (float)V;
   const bool valid = tgt >= 0 && tgt < V;
   if (threadIdx.x == 0) {
     float out = 0.f;
-    if (valid) out = lse - (capped ? __bfloat162float(l[tgt]) : cap * tanhf(__bfloat162float(l[tgt]) * inv_cap));
+    if (valid) out = lse - (1.0f - sm) * (capped ? __bfloat162float(l[tgt]) : cap * tanhf(__bfloat162float(l[tgt]) * inv_cap)) - sm * mean_z;
     nll[row] = out;
   }
   long long t2 = -1, t3 = -1;
@@ -531,6 +537,7 @@ __global__ void softcap_ce_kernel(const __nv_bfloat16* logits, long long ldl, co
   float w = 0.f;
   if (valid) w = row_w ? row_w[row] : inv_loss_div / fmaxf(1.0f, *n_valid);
   const float wsum = w + a2 + a3;
+  const float w_tgt = w * (1.0f - sm), w_uni = w * sm / (float)V;
   __nv_bfloat16* d = dlogits + (size_t)row * ldl;
   for (int c = threadIdx.x * 8; c < V; c += blockDim.x * 8) {
     const uint4 u = *reinterpret_cast<const uint4*>(l + c);
@@ -540,10 +547,10 @@ __global__ void softcap_ce_kernel(const __nv_bfloat16* logits, long long ldl, co
     for (int t = 0; t < 4; ++t) {
       const float2 f = unpack_bf16(wd[t]);
       const float t0 = capped ? f.x * inv_cap : tanhf(f.x * inv_cap), t1 = capped ? f.y * inv_cap : tanhf(f.y * inv_cap);
-      float p0 = wsum * __expf(cap * t0 - lse), p1 = wsum * __expf(cap * t1 - lse);
+      float p0 = wsum * __expf(cap * t0 - lse) - w_uni, p1 = wsum * __expf(cap * t1 - lse) - w_uni;
       const int c0i = c + 2 * t, c1i = c0i + 1;
-      if (c0i == tgt) p0 -= w;
-      if (c1i == tgt) p1 -= w;
+      if (c0i == tgt) p0 -= w_tgt;
+      if (c1i == tgt) p1 -= w_tgt;
       if (c0i == t2) p0 -= a2;
       if (c1i == t2) p1 -= a2;
       if (c0i == t3) p0 -= a3;
@@ -577,8 +584,8 @@ softcap_ce_row_kernel(const __nv_bfloat16* __restrict__ logits, long long ldl, c
   const __nv_bfloat16* l = logits + (size_t)row * ldl;
   const long long tgt = targets[row];
   const float inv_cap = 1.0f / cap, k2 = cap * 1.4426950408889634f;
-  __shared__ float red[32];
-  __shared__ float s_total;
+  __shared__ float red[32], red_t[32];
+  __shared__ float s_total, s_tsum;
   uint4 raw[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
@@ -587,7 +594,7 @@ softcap_ce_row_kernel(const __nv_bfloat16* __restrict__ logits, long long ldl, c
     if (c < V) raw[i] = *reinterpret_cast<const uint4*>(l + c);
   }
   __half2 th[8][4];
-  float s = 0.f;
+  float s = 0.f, st = 0.f;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int c = (i * 1024 + threadIdx.x) * 8;
@@ -598,23 +605,29 @@ softcap_ce_row_kernel(const __nv_bfloat16* __restrict__ logits, long long ldl, c
       // `capped`: the GEMM epilogue already applied cap * tanh(. / cap), only the scaling is left
       const float t0 = capped ? f.x * inv_cap : tanh_fast(f.x * inv_cap), t1 = capped ? f.y * inv_cap : tanh_fast(f.y * inv_cap);
       th[i][t] = __floats2half2_rn(t0, t1);
-      if (c < V) s += exp2f(k2 * t0 - k2) + exp2f(k2 * t1 - k2);
+      if (c < V) {
+        s += exp2f(k2 * t0 - k2) + exp2f(k2 * t1 - k2);
+        st += t0 + t1;
+      }
     }
   }
   s = warp_sum(s);
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  st = warp_sum(st);
+  if ((threadIdx.x & 31) == 0) { red[threadIdx.x >> 5] = s; red_t[threadIdx.x >> 5] = st; }
   __syncthreads();
   if (threadIdx.x < 32) {
-    float v = red[threadIdx.x];
+    float v = red[threadIdx.x], vt = red_t[threadIdx.x];
     v = warp_sum(v);
-    if (threadIdx.x == 0) s_total = v;
+    vt = warp_sum(vt);
+    if (threadIdx.x == 0) { s_total = v; s_tsum = vt; }
   }
   __syncthreads();
   const float lse2 = log2f(s_total) + k2;          // log-sum-exp in base-2 units
+  const float sm = aux.smooth, mean_z = cap * s_tsum / (float)V;
   const bool valid = tgt >= 0 && tgt < V;
   if (threadIdx.x == 0) {
     float out = 0.f;
-    if (valid) out = lse2 * 0.6931471805599453f - (capped ? __bfloat162float(l[tgt]) : cap * tanh_fast(__bfloat162float(l[tgt]) * inv_cap));
+    if (valid) out = lse2 * 0.6931471805599453f - (1.0f - sm) * (capped ? __bfloat162float(l[tgt]) : cap * tanh_fast(__bfloat162float(l[tgt]) * inv_cap)) - sm * mean_z;
     nll[row] = out;
   }
   long long t2 = -1, t3 = -1;
@@ -632,6 +645,7 @@ softcap_ce_row_kernel(const __nv_bfloat16* __restrict__ logits, long long ldl, c
   float w = 0.f;
   if (valid) w = row_w ? row_w[row] : inv_loss_div / fmaxf(1.0f, *n_valid);
   const float wsum = w + a2 + a3;
+  const float w_tgt = w * (1.0f - sm), w_uni = w * sm / (float)V;
   __nv_bfloat16* d = dlogits + (size_t)row * ldl;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
@@ -641,10 +655,10 @@ softcap_ce_row_kernel(const __nv_bfloat16* __restrict__ logits, long long ldl, c
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
       const float2 tt = __half22float2(th[i][t]);
-      float p0 = wsum * exp2f(k2 * tt.x - lse2), p1 = wsum * exp2f(k2 * tt.y - lse2);
+      float p0 = wsum * exp2f(k2 * tt.x - lse2) - w_uni, p1 = wsum * exp2f(k2 * tt.y - lse2) - w_uni;
       const int c0i = c + 2 * t, c1i = c0i + 1;
-      if (c0i == tgt) p0 -= w;
-      if (c1i == tgt) p1 -= w;
+      if (c0i == tgt) p0 -= w_tgt;
+      if (c1i == tgt) p1 -= w_tgt;
       if (c0i == t2) p0 -= a2;
       if (c1i == t2) p1 -= a2;
       if (c0i == t3) p0 -= a3;
@@ -793,10 +807,11 @@ int bones_moe_combine_bwd(const void* ys, const long long* slot, const float* ga
 }
 int bones_softcap_ce(const void* logits, long long ldl, const long long* targets, int V, float cap, float* nll, void* dlogits,
                      const float* row_w, const float* n_valid, float inv_loss_div, int M, int capped, const long long* tg2, const float* w2,
-                     const long long* tg3, const float* w3, float* nll_aux, void* stream) {
+                     const long long* tg3, const float* w3, float* nll_aux, float label_smoothing, void* stream) {
   if (V % 8 || ldl % 8) return -2;
   AuxTargets aux;
   aux.tg[0] = tg2; aux.w[0] = w2; aux.tg[1] = tg3; aux.w[1] = w3; aux.nll_aux = nll_aux;
+  aux.smooth = label_smoothing;
   if (V <= 65536 && V >= 8192) {
     softcap_ce_row_kernel<<<M, 1024, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, ldl, targets, V, cap, nll,
                                                                 (__nv_bfloat16*)dlogits, row_w, n_valid, inv_loss_div, M, capped, aux);

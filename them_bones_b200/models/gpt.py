@@ -284,8 +284,10 @@ class GPT(nn.Module):
         if targets is None:
             return ops.lmhead_logits(x, self.lm_head.weight, cfg.vocab_size, cfg.softcap)
         aux = self.mtp_terms(targets, loss_div) if (loss_reduction == "mean" and self.training) else None
+        smooth = cfg.label_smoothing if (self.training and loss_reduction == "mean") else 0.0
         loss = ops.lmhead_loss(x, self.lm_head.weight, targets, cfg.vocab_size, cfg.softcap,
-                               reduction=loss_reduction, row_weights=row_weights, loss_div=loss_div, aux=aux)
+                               reduction=loss_reduction, row_weights=row_weights, loss_div=loss_div, aux=aux,
+                               label_smoothing=smooth)
         if loss_reduction != "mean" or moe_aux is None:
             return loss
         aux = torch.stack([a[0] for a in moe_aux]).sum()

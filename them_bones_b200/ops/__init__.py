@@ -155,15 +155,16 @@ def lmhead_logits(x, w, vocab, cap):
     return RF.softcap_logits(F.linear(x, w.to(x.dtype))[..., :vocab], cap)
 
 
-def lmhead_loss(x, w, targets, vocab, cap, reduction="mean", row_weights=None, loss_div=1.0, aux=None):
+def lmhead_loss(x, w, targets, vocab, cap, reduction="mean", row_weights=None, loss_div=1.0, aux=None, label_smoothing=0.0):
     """Loss head: GEMM + softcap + log-sum-exp + target gather in row blocks; the full ``[M, V]`` logits never exist
     on the native path.  ``"mean"`` is divided by ``loss_div`` (gradient accumulation folded into the graph).
     ``aux``: up to two ``(targets, row_weights)`` pairs added as ``sum(row_weights * nll(targets))`` -- further targets
     that share each row's soft-max (multi-token prediction; reference: ``fused_loss_multi``,
-    round1/source/train.py:5070-5093)."""
+    round1/source/train.py:5070-5093).  ``label_smoothing``: the main target's loss becomes ``(1 - s) * nll + s * (lse -
+    mean_v z_v)`` (reference: the label-smoothing loss-head pair, round2/source/train.py:5697-5767)."""
     if native(x):
-        return _cuda().lmhead_loss(x, w, targets, vocab, cap, reduction, row_weights, loss_div, aux)
-    out = RF.softcap_cross_entropy(x, w.to(x.dtype), targets, vocab, cap, row_weights, reduction)
+        return _cuda().lmhead_loss(x, w, targets, vocab, cap, reduction, row_weights, loss_div, aux, label_smoothing)
+    out = RF.softcap_cross_entropy(x, w.to(x.dtype), targets, vocab, cap, row_weights, reduction, label_smoothing)
     out = out / loss_div if (reduction == "mean" and loss_div != 1.0) else out
     if aux and reduction == "mean":
         for tk, wk in aux:

@@ -350,7 +350,7 @@ class _LmHeadLossFn(torch.autograd.Function):
     ``loss_scaled`` :11712)."""
 
     @staticmethod
-    def forward(ctx, x, w, targets, vocab, cap, loss_div, row_weights, want_grad, aux=None):
+    def forward(ctx, x, w, targets, vocab, cap, loss_div, row_weights, want_grad, aux=None, label_smoothing=0.0):
         # aux: up to two (targets, absolute row weights) pairs that share the row's soft-max (multi-token prediction)
         shp = x.shape
         x2 = _c(x).view(-1, shp[-1])
@@ -383,7 +383,7 @@ class _LmHeadLossFn(torch.autograd.Function):
             mm_nt(x2[r0:r1], w, out=lg, epi=L.EPI_SOFTCAP, alpha=1.0 / cap, beta=cap)
             L.call("bones_softcap_ce", L.ptr(lg), _L(vp), L.ptr(tg[r0:r1]), _I(vocab), _F(cap), L.ptr(nll[r0:r1]),
                    L.ptr(lg if want_grad else None), L.ptr(rw[r0:r1] if rw is not None else None), L.ptr(n_valid),
-                   _F(1.0 / loss_div), _I(r1 - r0), _I(1), *aux_ptrs(r0, r1), L.stream())
+                   _F(1.0 / loss_div), _I(r1 - r0), _I(1), *aux_ptrs(r0, r1), _F(label_smoothing), L.stream())
             if want_grad:
                 mm_nn_acc(lg, w, dx32[r0:r1])
                 mm_tn_acc(lg, x2[r0:r1], grad_w)
@@ -403,12 +403,13 @@ class _LmHeadLossFn(torch.autograd.Function):
     def backward(ctx, dloss, _dnll):
         dx = ctx.dx.view(ctx.shp) * dloss.to(ctx.dx.dtype)
         gw = ctx.own_gw.to(ctx.wdtype) * dloss.to(ctx.wdtype) if ctx.own_gw is not None else None
-        return dx, gw, None, None, None, None, None, None, None
+        return dx, gw, None, None, None, None, None, None, None, None
 
 
-def lmhead_loss(x, w, targets, vocab, cap, reduction="mean", row_weights=None, loss_div=1.0, aux=None):
+def lmhead_loss(x, w, targets, vocab, cap, reduction="mean", row_weights=None, loss_div=1.0, aux=None, label_smoothing=0.0):
     want_grad = torch.is_grad_enabled() and (x.requires_grad or w.requires_grad) and reduction == "mean"
-    loss, nll = _LmHeadLossFn.apply(x, w, targets, vocab, cap, float(loss_div), row_weights, want_grad, aux)
+    loss, nll = _LmHeadLossFn.apply(x, w, targets, vocab, cap, float(loss_div), row_weights, want_grad, aux,
+                                    float(label_smoothing))
     if reduction == "mean":
         return loss
     if reduction == "sum":

@@ -119,15 +119,15 @@ def softcap_logits(logits: torch.Tensor, cap: float) -> torch.Tensor:
 
 
 def softcap_cross_entropy(x: torch.Tensor, w: torch.Tensor, targets: torch.Tensor, vocab: int, cap: float,
-                          weights: torch.Tensor | None = None, reduction: str = "mean"):
+                          weights: torch.Tensor | None = None, reduction: str = "mean", label_smoothing: float = 0.0):
     """lm_head GEMM + fp32 softcap + cross-entropy with ``ignore_index=-1``.  ``weights`` (per row) gives the
     row-weighted sum form of the chunked loss head (reference: ``chunked_loss_mean``, round2/source/train.py:6364)."""
     logits = softcap_logits(F.linear(x, w)[..., :vocab], cap)
     flat, tgt = logits.reshape(-1, vocab), targets.reshape(-1)
     if weights is not None:
-        nll = F.cross_entropy(flat, tgt, ignore_index=-1, reduction="none")
+        nll = F.cross_entropy(flat, tgt, ignore_index=-1, reduction="none", label_smoothing=label_smoothing)
         return (nll * weights.reshape(-1).float()).sum()
-    out = F.cross_entropy(flat, tgt, ignore_index=-1, reduction=reduction)
+    out = F.cross_entropy(flat, tgt, ignore_index=-1, reduction=reduction, label_smoothing=label_smoothing)
     return out.view_as(targets) if reduction == "none" else out
 
 
