@@ -296,3 +296,104 @@ def test_label_smoothing_only_in_training():
         h = model.trunk(x)
         want = float(RF.softcap_cross_entropy(h, model.lm_head.weight, y, cfg.vocab_size, cfg.softcap, label_smoothing=0.1))
     assert smooth == pytest.approx(want, rel=1e-6) and smooth != pytest.approx(plain, rel=1e-4)
+
+
+def test_output_table_keys_signs_and_row_step():
+    x = torch.randint(1, 512, (2, 40))
+    x[0, 20] = 0                                                              # a BOS inside the first window
+    row, hs = RF.os1_keys(x, 4, 1 << 10, bos_id=0, seed=3)
+    assert (row[:, :3] == -1).all() and (row[1, 3:] >= 0).all() and int(row.max()) < (1 << 10)
+    # a key spans a BOS only as its first id: the keys ending at 20..22 hold the BOS after their first id
+    assert (row[0, 20:23] == -1).all() and row[0, 19] >= 0 and row[0, 23] >= 0
+    # causal and deterministic: a key depends on its own `order` ids only
+    x2 = x.clone()
+    x2[1, 10] = (x2[1, 10] % 500) + 7
+    row2, hs2 = RF.os1_keys(x2, 4, 1 << 10, bos_id=0, seed=3)
+    same = torch.ones(40, dtype=torch.bool)
+    same[10:14] = False
+    assert (row2[1][same] == row[1][same]).all() and (hs2[1][same] == hs[1][same]).all()
+    assert (row2[1, 10:14] != row[1, 10:14]).any()
+    sg = RF.os1_signs(hs.reshape(-1), 128)
+    assert sg.shape == (80, 128) and set(sg.unique().tolist()) == {-1.0, 1.0}
+    assert abs(float(sg.mean())) < 0.05                                       # balanced
+    assert torch.equal(sg, RF.os1_signs(hs.reshape(-1), 128))
+    # the stateless row step: first step is full size whatever the gradient's scale, then the budget binds
+    g = torch.randn(5, 128) * 1e-4
+    x1 = RF.os1_row_step(torch.zeros(5, 128), g, lr=0.125, eps=1e-12, cap=4.0)
+    assert torch.allclose(x1.square().mean(1).sqrt(), torch.full((5,), 0.125), rtol=1e-3)
+    xs = x1
+    for _ in range(10):
+        xs = RF.os1_row_step(xs, g, lr=0.125, eps=1e-12, cap=4.0)
+    assert float(xs.square().mean(1).sqrt().max()) <= 0.5 + 1e-5
+    zero = RF.os1_row_step(x1, torch.zeros(5, 128), lr=0.125, eps=1e-12, cap=4.0)
+    assert torch.equal(zero, x1)                                              # a zero gradient takes no step
+
+
+def test_output_table_gate_is_causal_and_readout_gradient():
+    torch.manual_seed(0)
+    b, t, dim, v = 2, 24, 32, 64
+    code = RF.os1_codebook(v, dim, 7)
+    u = torch.randn(b * t, dim)
+    idx = torch.randint(0, v, (b, t))
+    g = RF.os1_gate(u, code, idx, a0=1.0, width=4, h0=0.3, slope=30.0)
+    assert g.shape == (b, t) and float(g[0, 0]) == pytest.approx(torch.sigmoid(torch.tensor(-9.0)).item(), rel=1e-5)
+    u2, idx2 = u.clone(), idx.clone()
+    u2.view(b, t, dim)[:, 12:] += 1.0                                          # later reads ...
+    idx2[:, 14:] = (idx2[:, 14:] + 1) % v                                      # ... and later tokens
+    g2 = RF.os1_gate(u2, code, idx2, a0=1.0, width=4, h0=0.3, slope=30.0)
+    assert torch.equal(g[:, :13], g2[:, :13])                                  # position t reads j <= t-1 and tokens <= t
+    # manual value at t = 5: mean over j = 1..4 of u_j . C[idx[j+1]]
+    want = torch.stack([(u.view(b, t, dim)[0, j] * code[idx[0, j + 1]]).sum() for j in range(1, 5)]).mean()
+    assert float(g[0, 5]) == pytest.approx(torch.sigmoid(30.0 * (want - 0.3)).item(), abs=1e-5)
+    # gradient reaches u through the linear term only: du = (glin / a0) * dpre @ C
+    x = torch.randn(b * t, 16)
+    w = torch.randn(v, 16) * 0.1
+    tg = torch.randint(0, v, (b * t,))
+    uu = (u * 0.5).requires_grad_(True)
+    loss = RF.softcap_cross_entropy_os1(x, w, tg, v, 15.0, uu, code, g.reshape(-1), a0=1.0, glin=0.01, beta=3.0, thr=0.7)
+    loss.backward()
+    pre = (x @ w.T + RF.os1_readout((uu.detach() @ code.T), g.reshape(-1), 0.01, 3.0, 0.7)).requires_grad_(True)
+    torch.nn.functional.cross_entropy(15.0 * torch.tanh(pre / 15.0), tg).backward()
+    assert torch.allclose(uu.grad, 0.01 * pre.grad @ code, atol=1e-7)
+
+
+def test_output_table_zero_init_is_identity_then_learns(tmp_path):
+    from them_bones_b200.utils import ckpt as CK
+    kw = dict(n_layer=1, n_embd=64, n_head=2, vocab_size=512, sequence_len=64)
+    cfg0 = tiny_cfg(**kw)
+    cfg1 = tiny_cfg(os1_rows=1 << 12, os1_order=3, os1_dim=32, **kw)
+    hy = Hyper()
+    hy.total_batch, hy.device_batch = 4 * 64, 2                               # two micro-steps per step
+    tr0 = Trainer(cfg0, hy, RT, optimizer_kind="lean", horizon_steps=10)
+    tr1 = Trainer(cfg1, hy, RT, optimizer_kind="lean", horizon_steps=10)
+    ld = SynthLoader(512, 64, 4, seed=0, doc_len=(16, 64))
+    x, y = ld.next_step()
+    l0, l1 = float(tr0.train_step(x.long(), y)), float(tr1.train_step(x.long(), y))
+    assert abs(l0 - l1) < 1e-5                                # zero rows: the first forward is the table-free model
+    st = tr1.os1.stats
+    assert st["updates"] == 1 and st["touched"] > 0
+    rms = tr1.os1.shard.float().square().mean(1).sqrt()
+    moved = rms > 0
+    assert st["touched"] - 8 <= int(moved.sum()) <= st["touched"]      # a row read only at masked targets has no gradient
+    assert torch.allclose(rms[moved], torch.full_like(rms[moved], cfg1.os1_lr), rtol=1e-3)   # full-size first step
+    # the same windows again: rows that were stepped now pull their contexts' next tokens up, beyond what the dense
+    # weights' own step gives
+    for _ in range(6):
+        l0, l1 = float(tr0.train_step(x.long(), y)), float(tr1.train_step(x.long(), y))
+    assert l1 < l0 - 0.02, (l0, l1)
+    assert float(tr1.os1.shard.float().square().mean(1).sqrt().max()) <= cfg1.os1_lr * hy.os1_cap * 1.001
+    # checkpoint: int8 rows + bf16 scales in model_state, the read-out's settings in model_config
+    path = str(tmp_path / "os1.pt")
+    CK.save_checkpoint(path, tr1.model, dict(steps=7))
+    raw = torch.load(path, weights_only=True)
+    assert raw["model_state"]["os1_table"].dtype == torch.int8 and raw["model_state"]["os1_scale"].dtype == torch.bfloat16
+    assert raw["model_config"]["os1_rows"] == 1 << 12 and raw["model_config"]["os1_order"] == 3
+    model, _ = CK.load_for_eval(path, "cpu")
+    xe = x[:2].long()
+    with torch.no_grad():
+        tr1.model.eval()
+        a, bb = model(xe), tr1.model(xe)
+        tr1.model.train()
+    # int8 rows: a score just above the threshold moves by the quantisation step times the thresholded term's gain
+    assert float((a - bb).abs().mean()) < 2e-3 and float((a - bb).abs().max()) < 0.5
+    assert model(xe, y[:2], loss_reduction="none").shape == (2, 64)

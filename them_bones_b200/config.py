@@ -95,6 +95,22 @@ class GPTConfig:
     table_orders: tuple = ()       # hashed n-gram input tables, e.g. (2, 3)
     table_rows: int = 0            # rows per table (power of two)
     table_seed: int = 0
+    # output-side hashed table (0 rows: off): keyed by the os1_order ids ending at a position; its sign-hashed row is read
+    # out through a fixed codebook and added to the logits before the soft-cap (reference: switch 59,
+    # round2/source/train.py:2310-2351; the defaults below are the reference's)
+    os1_rows: int = 0
+    os1_dim: int = 128
+    os1_order: int = 16
+    os1_lr: float = 0.125           # the read-out scale is os1_a0 * os1_lr, so the step size belongs to the model
+    os1_a0: float = 7.98
+    os1_thr: float = 0.7
+    os1_beta: float = 3.0
+    os1_glin: float = 0.01
+    os1_gate_w: int = 32
+    os1_gate_h0: float = 0.3
+    os1_gate_slope: float = 30.0
+    os1_seed: int = 0
+    os1_code_seed: int = 5901
 
     def __post_init__(self):
         for name in ("attn_long", "moe_layers", "table_orders", "attn_layers", "mtp_offsets"):
@@ -114,6 +130,8 @@ class GPTConfig:
                 raise ValueError("MoE layers need moe_experts, moe_topk in {1,2}, moe_capacity and moe_hidden")
         if self.table_orders and (self.table_rows & (self.table_rows - 1) or self.table_rows <= 0):
             raise ValueError("table_rows must be a positive power of two")
+        if self.os1_rows and (self.os1_rows & (self.os1_rows - 1) or self.os1_dim % 32 or self.os1_dim > 256):
+            raise ValueError("os1_rows must be a power of two and os1_dim a multiple of 32 up to 256")
 
     @property
     def padded_vocab(self) -> int:
@@ -170,6 +188,8 @@ class Hyper:
     scalar_lr: float = 0.20
     resid_lr_div: float = 28.0         # resid_lambda trains at scalar_lr / resid_lr_div
     table_lr: float = 0.02
+    os1_cap: float = 4.0               # output table: a row's RMS stays below os1_cap * os1_lr
+    os1_eps_rel: float = 1e-6          # ... and eps of its normalised step, relative to a typical one-position gradient
     weight_decay: float = 0.05
     warmup_steps: int = 40
     warmdown_frac: float = 0.85
@@ -220,6 +240,8 @@ def switches(refresh: bool = False) -> dict:
         MOE_AUX=e("MOE_AUX", 0.01, float), MOE_ZLOSS=e("MOE_ZLOSS", 0.0, float),
         TABLES=e("TABLES", "", str), TABLE_ROWS=e("TABLE_ROWS", 0, int), TABLE_SEED=e("TABLE_SEED", 0, int),
         TABLE_STALE=e("TABLE_STALE", False, bool), TABLE_HOST_STATE=e("TABLE_HOST_STATE", "auto", str),   # auto | 0 | 1: Adam moments of the tables in pinned host memory
+        OS1=e("OS1", False, bool), OS1_ROWS=e("OS1_ROWS", 1 << 24, int), OS1_ORDER=e("OS1_ORDER", 16, int),
+        OS1_LR=e("OS1_LR", 0.125, float), OS1_SEED=e("OS1_SEED", 0, int),
         DATA_RULE=e("DATA_RULE", "", str),           # e.g. "len:64-4096,band:0.05-0.95,dedup:32,from:0.1"
         # kernels / system
         SELFCHECK=e("SELFCHECK", False, bool),       # compare every native op with the PyTorch path before training
@@ -283,6 +305,8 @@ def build_config(depth: int, n_embd: int, n_head: int, seq_len: int, vocab: int,
     if s["TABLES"]:
         kw.update(table_orders=_env(PREFIX + "TABLES", (), tuple), table_rows=s["TABLE_ROWS"] or (1 << 20),
                   table_seed=s["TABLE_SEED"])
+    if s["OS1"]:
+        kw.update(os1_rows=s["OS1_ROWS"], os1_order=s["OS1_ORDER"], os1_lr=s["OS1_LR"], os1_seed=s["OS1_SEED"])
     return GPTConfig(**kw)
 
 

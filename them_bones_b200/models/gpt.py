@@ -123,6 +123,7 @@ class GPT(nn.Module):
                 blk.mlp.set_expert_parallel(ep_group, ep_world, ep_rank)
         self.tables: HashedTables | None = None           # attached by attach_tables(); not nn.Parameters
         self.table_lambda = nn.Parameter(torch.ones(len(config.table_orders))) if config.table_orders else None
+        self.os1 = None                                   # output-side table, attached by attach_os1()
         cos, sin = RF.rotary_tables(config.sequence_len, config.head_dim, config.rope_base)
         self.register_buffer("cos", cos, persistent=False)
         self.register_buffer("sin", sin, persistent=False)
@@ -175,6 +176,10 @@ class GPT(nn.Module):
 
     def attach_tables(self, tables: "HashedTables"):
         self.tables = tables
+
+    def attach_os1(self, table):
+        """``models.os1.OutputTable``: its read-out joins the logits before the soft-cap."""
+        self.os1 = table
 
     # ---------------------------------------------------------------------------------------------------------
     def estimate_flops(self) -> float:
@@ -281,15 +286,30 @@ class GPT(nn.Module):
         cfg = self.config
         moe_aux = [] if (self.has_moe and targets is not None and loss_reduction == "mean") else None
         x = self.trunk(idx, doc_start, moe_aux, table_rows)
-        if targets is None:
+        if self.os1 is not None:
+            u, gate = self.os1.read(idx)
+            kw = self.os1.readout_args()
+            if targets is None:
+                return ops.lmhead_logits_os1(x, self.lm_head.weight, cfg.vocab_size, cfg.softcap, u, self.os1.code, gate, **kw)
+            if self.training and (cfg.mtp_offsets or cfg.label_smoothing):
+                raise ValueError("the output table's loss head has no multi-token or label-smoothing form")
+            loss = ops.lmhead_loss_os1(x, self.lm_head.weight, targets, cfg.vocab_size, cfg.softcap, u.view(*idx.shape, -1),
+                                       self.os1.code, gate, reduction=loss_reduction, row_weights=row_weights,
+                                       loss_div=loss_div, **kw)
+        elif targets is None:
             return ops.lmhead_logits(x, self.lm_head.weight, cfg.vocab_size, cfg.softcap)
-        aux = self.mtp_terms(targets, loss_div) if (loss_reduction == "mean" and self.training) else None
-        smooth = cfg.label_smoothing if (self.training and loss_reduction == "mean") else 0.0
-        loss = ops.lmhead_loss(x, self.lm_head.weight, targets, cfg.vocab_size, cfg.softcap,
-                               reduction=loss_reduction, row_weights=row_weights, loss_div=loss_div, aux=aux,
-                               label_smoothing=smooth)
+        else:
+            loss = self._plain_loss(x, targets, loss_reduction, loss_div, row_weights)
         if loss_reduction != "mean" or moe_aux is None:
             return loss
         aux = torch.stack([a[0] for a in moe_aux]).sum()
         stats = torch.stack([a[1] for a in moe_aux])
         return loss + aux / loss_div, stats.detach()
+
+    def _plain_loss(self, x, targets, loss_reduction, loss_div, row_weights):
+        cfg = self.config
+        aux = self.mtp_terms(targets, loss_div) if (loss_reduction == "mean" and self.training) else None
+        smooth = cfg.label_smoothing if (self.training and loss_reduction == "mean") else 0.0
+        return ops.lmhead_loss(x, self.lm_head.weight, targets, cfg.vocab_size, cfg.softcap,
+                               reduction=loss_reduction, row_weights=row_weights, loss_div=loss_div, aux=aux,
+                               label_smoothing=smooth)

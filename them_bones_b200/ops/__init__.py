@@ -172,6 +172,64 @@ def lmhead_loss(x, w, targets, vocab, cap, reduction="mean", row_weights=None, l
     return out
 
 
+# -- output-side hashed table ------------------------------------------------------------------------------------
+def os1_apply_signs(x, hsign, out_dtype=None):
+    """Rows times their context's sign pattern: ``signs(hsign) * x`` (``x [n, dim]``, ``hsign [n]`` int64)."""
+    if native(x):
+        return _cuda().os1_apply_signs(x, hsign, out_dtype)
+    return (RF.os1_signs(hsign, x.shape[1]) * x.float()).to(out_dtype or x.dtype)
+
+
+def os1_gate(u, code, idx, a0, width, h0, slope):
+    """The read-out's gate ``[B, T]`` (no gradient): see ``ref.functional.os1_gate``.  Native: the per-position dot
+    product with the following token's code row is one kernel; the banded mean is a prefix sum."""
+    if not native(u):
+        return RF.os1_gate(u, code, idx, a0, width, h0, slope)
+    with torch.no_grad():
+        b, t = idx.shape
+        nxt = torch.full((b, t), -1, dtype=torch.int64, device=idx.device)
+        nxt[:, :-1] = idx[:, 1:]
+        sd = _cuda().os1_gate_dot(u.reshape(b * t, -1), code, nxt.view(-1), a0).view(b, t)
+        cs = F.pad(sd.cumsum(1), (1, 0))
+        pos = torch.arange(t, device=idx.device)
+        lo = (pos - width).clamp_min(0)
+        h = (cs[:, pos] - cs[:, lo]) / (pos - lo).clamp_min(1).float()
+        return torch.sigmoid(slope * (h - h0))
+
+
+def lmhead_loss_os1(x, w, targets, vocab, cap, u, code, gate, *, a0, glin, beta, thr, reduction="mean", row_weights=None,
+                    loss_div=1.0):
+    """Loss head with the output table's term ``glin s + G beta relu(sg(s) - thr) / (1 - thr)``, ``s = u C^T / a0``,
+    added to the logits before the soft-cap; the gradient reaches ``u`` through the linear term only."""
+    if native(x):
+        return _cuda().lmhead_loss_os1(x, w, targets, vocab, cap, u, code, gate, a0, glin, beta, thr, reduction,
+                                       row_weights, loss_div)
+    out = RF.softcap_cross_entropy_os1(x, w.to(x.dtype), targets, vocab, cap, u, code, gate, a0=a0, glin=glin, beta=beta,
+                                       thr=thr, weights=row_weights, reduction=reduction)
+    return out / loss_div if (reduction == "mean" and loss_div != 1.0) else out
+
+
+def lmhead_logits_os1(x, w, vocab, cap, u, code, gate, *, a0, glin, beta, thr):
+    if native(x):
+        return _cuda().lmhead_logits_os1(x, w, vocab, cap, u, code, gate, a0, glin, beta, thr)
+    s = F.linear(u.to(x.dtype), code.to(x.dtype)).float()[..., :vocab].reshape(-1, vocab) / a0
+    pre = F.linear(x, w.to(x.dtype)).float()[..., :vocab].reshape(-1, vocab) + RF.os1_readout(s, gate.reshape(-1), glin, beta, thr)
+    return RF.softcap_logits(pre, cap).view(*x.shape[:-1], vocab)
+
+
+@torch.no_grad()
+def os1_row_step(table, rows, g, *, lr, eps, cap):
+    """Stateless row update of the output table, in place on ``table[rows]``; returns how many rows the budget scaled."""
+    if native(table):
+        return _cuda().os1_row_step(table, rows, g, lr, eps, cap)
+    old = table.index_select(0, rows)
+    r = g.float().square().mean(1, keepdim=True).sqrt()
+    stepped = old.float() - g.float() * (lr / (r + eps))
+    new = RF.os1_row_step(old, g, lr, eps, cap)
+    table.index_copy_(0, rows, new.to(table.dtype))
+    return (stepped.square().mean(1).sqrt() > cap * lr).sum().to(torch.int32).reshape(1)
+
+
 # -- MoE ---------------------------------------------------------------------------------------------------------
 def moe_slots(idx, b, t, n_exp, cap):
     """Causal per-sequence capacity slotting: ``(slot [n, k], token_of_slot [E*b*cap])``."""

@@ -426,6 +426,121 @@ def lmhead_logits(x, w, vocab, cap):
     return out.view(*shp[:-1], vocab)
 
 
+# -- output-side hashed table ----------------------------------------------------------------------------------------
+def os1_apply_signs(x, hsign, out_dtype=None):
+    """``signs(hsign) * x`` for rows ``x [n, dim]`` (bf16 or fp32) and sign hashes ``hsign [n]`` int64."""
+    x = _c(x)
+    out_dtype = out_dtype or x.dtype
+    kind = {(BF16, BF16): 0, (torch.float32, torch.float32): 1, (torch.float32, BF16): 2}[(x.dtype, out_dtype)]
+    out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    L.call("bones_os1_signs", L.ptr(x), L.ptr(_c(hsign)), L.ptr(out), _L(x.shape[0]), _I(x.shape[1]), _I(kind), L.stream())
+    return out
+
+
+def os1_gate_dot(u, code, nxt, a0):
+    """``sd[i] = u[i] . code[nxt[i]] / a0`` (0 where ``nxt[i] < 0``), fp32."""
+    sd = torch.empty(u.shape[0], dtype=torch.float32, device=u.device)
+    L.call("bones_os1_gate_dot", L.ptr(_c(u)), L.ptr(code), L.ptr(_c(nxt)), L.ptr(sd), _L(u.shape[0]), _I(u.shape[1]),
+           _F(1.0 / a0), L.stream())
+    return sd
+
+
+def os1_row_step(table, rows, g, lr, eps, cap):
+    """In place on ``table[rows]``: the normalised step and the row budget.  Returns the count of rows the budget scaled
+    (a device int32 scalar)."""
+    capped = torch.zeros(1, dtype=torch.int32, device=table.device)
+    L.call("bones_os1_row_step", L.ptr(table), L.ptr(_c(rows)), L.ptr(_c(g)), _I(rows.numel()), _I(table.shape[1]), _F(lr),
+           _F(eps), _F(cap * lr), L.ptr(capped), _I(int(table.dtype == torch.float32)), L.stream())
+    return capped
+
+
+class _LmHeadLossOs1Fn(torch.autograd.Function):
+    """The chunked loss head with the output table's read-out: per block of rows the logits GEMM, the scores GEMM
+    ``S = U C^T / a0``, one element-wise kernel that adds ``glin S + G k relu(S - thr)`` and soft-caps, the
+    cross-entropy kernel (logits overwritten by their gradient), then dX, dW and ``dU = (glin / a0) dLogits C``
+    (reference: the OS1-fused loss-head pair, round2/source/train.py:5881-5957 and :6461-6501)."""
+
+    @staticmethod
+    def forward(ctx, x, w, u, code, gate, targets, vocab, cap, loss_div, row_weights, want_grad, a0, glin, kthr, thr):
+        shp = x.shape
+        x2 = _c(x).view(-1, shp[-1])
+        u2 = _c(u).view(-1, u.shape[-1])
+        m = x2.shape[0]
+        tg = _c(targets).view(-1).to(torch.int64)
+        gt = _c(gate).view(-1).float()
+        nll = torch.empty(m, dtype=torch.float32, device=x.device)
+        n_valid = (tg >= 0).sum().float().reshape(1)
+        dx32 = torch.zeros(x2.shape, dtype=torch.float32, device=x.device) if want_grad else None
+        du32 = torch.zeros(u2.shape, dtype=torch.float32, device=x.device) if want_grad else None
+        rw = _c(row_weights).view(-1).float() if row_weights is not None else None
+        vp = w.shape[0]
+        grad_w = getattr(w, "main_grad", None)
+        own_gw = None
+        if want_grad and grad_w is None:
+            own_gw = grad_w = torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+        rows = min(LOSS_ROWS, m)
+        buf = torch.empty(rows, vp, dtype=BF16, device=x.device)
+        sbuf = torch.empty(rows, vp, dtype=BF16, device=x.device)
+        null = L.ptr(None)
+        for r0 in range(0, m, LOSS_ROWS):
+            r1 = min(m, r0 + LOSS_ROWS)
+            lg, sc = buf[:r1 - r0], sbuf[:r1 - r0]
+            mm_nt(x2[r0:r1], w, out=lg)
+            mm_nt(u2[r0:r1], code, out=sc, alpha=1.0 / a0)
+            L.call("bones_os1_combine", L.ptr(lg), L.ptr(sc), L.ptr(gt[r0:r1]), _L(r1 - r0), _I(vp), _L(vp), _F(cap), _F(glin),
+                   _F(kthr), _F(thr), _I(1), L.stream())
+            L.call("bones_softcap_ce", L.ptr(lg), _L(vp), L.ptr(tg[r0:r1]), _I(vocab), _F(cap), L.ptr(nll[r0:r1]),
+                   L.ptr(lg if want_grad else None), L.ptr(rw[r0:r1] if rw is not None else None), L.ptr(n_valid),
+                   _F(1.0 / loss_div), _I(r1 - r0), _I(1), null, null, null, null, null, _F(0.0), L.stream())
+            if want_grad:
+                mm_nn_acc(lg, w, dx32[r0:r1])
+                mm_tn_acc(lg, x2[r0:r1], grad_w)
+                mm_nn_acc(lg, code, du32[r0:r1])
+        COUNTS["lmhead_loss_os1"] += 1
+        ctx.dx = dx32.to(x2.dtype) if want_grad else None
+        ctx.du = (du32 * (glin / a0)) if want_grad else None
+        ctx.shp, ctx.ushp, ctx.own_gw, ctx.wdtype, ctx.udtype = shp, u.shape, own_gw, w.dtype, u.dtype
+        if rw is not None:
+            loss = (nll * rw).sum()
+        else:
+            loss = nll.sum() / n_valid.clamp_min(1.0)[0] / loss_div
+        ctx.mark_non_differentiable(nll)
+        return loss, nll
+
+    @staticmethod
+    def backward(ctx, dloss, _dnll):
+        dx = ctx.dx.view(ctx.shp) * dloss.to(ctx.dx.dtype)
+        du = (ctx.du.view(ctx.ushp) * dloss.float()).to(ctx.udtype)
+        gw = ctx.own_gw.to(ctx.wdtype) * dloss.to(ctx.wdtype) if ctx.own_gw is not None else None
+        return (dx, gw, du) + (None,) * 12
+
+
+def lmhead_loss_os1(x, w, targets, vocab, cap, u, code, gate, a0, glin, beta, thr, reduction="mean", row_weights=None,
+                    loss_div=1.0):
+    want_grad = torch.is_grad_enabled() and (x.requires_grad or w.requires_grad or u.requires_grad) and reduction == "mean"
+    loss, nll = _LmHeadLossOs1Fn.apply(x, w, u, code, gate, targets, vocab, cap, float(loss_div), row_weights, want_grad,
+                                       float(a0), float(glin), float(beta / (1.0 - thr)), float(thr))
+    if reduction == "mean":
+        return loss
+    if reduction == "sum":
+        return nll.sum()
+    return nll.view(targets.shape)
+
+
+def lmhead_logits_os1(x, w, vocab, cap, u, code, gate, a0, glin, beta, thr):
+    shp = x.shape
+    x2 = _c(x).view(-1, shp[-1])
+    u2 = _c(u).view(-1, u.shape[-1])
+    vp = w.shape[0]
+    lg = mm_nt(x2, w)
+    sc = mm_nt(u2, code, alpha=1.0 / a0)
+    L.call("bones_os1_combine", L.ptr(lg), L.ptr(sc), L.ptr(_c(gate).view(-1).float()), _L(x2.shape[0]), _I(vp), _L(vp),
+           _F(cap), _F(glin), _F(beta / (1.0 - thr)), _F(thr), _I(0), L.stream())
+    out = torch.empty(x2.shape[0], vocab, dtype=torch.float32, device=x.device)
+    L.call("bones_softcap_logits", L.ptr(lg), _L(vp), L.ptr(out), _I(vocab), _F(cap), _L(x2.shape[0]), L.stream())
+    return out.view(*shp[:-1], vocab)
+
+
 # -- MoE -------------------------------------------------------------------------------------------------------------
 def moe_slots(idx, b, t, n_exp, cap):
     """Native capacity slotting: ``idx [b*t, k]`` int64 -> ``(slot [b*t, k], tok [E*b*cap])``."""

@@ -339,3 +339,116 @@ def ngram_rows(idx: torch.Tensor, order: int, rows: int, seed: int, doc_start: t
         h = h ^ ((h >> 29) & ((1 << 35) - 1))                 # logical shift of the wrapped value
     h = h * _as_i64(HASH_MULT[2])
     return ((h >> 32) & (rows - 1)).to(torch.int64) if rows <= (1 << 32) else (h & (rows - 1))
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# Output-side hashed table ("OS1"): keys, signs, codebook, gate, readout, row update
+# (reference: switch 59, round2/source/train.py:2310-2351 and the helpers at :2596-2680)
+# ----------------------------------------------------------------------------------------------------------------
+
+def _lsr(z: torch.Tensor, s: int) -> torch.Tensor:
+    """Logical right shift of int64 values holding wrapped 64-bit words."""
+    return (z >> s) & ((1 << (64 - s)) - 1)
+
+
+def _mix64(z: torch.Tensor) -> torch.Tensor:
+    """A splitmix64-style finaliser on wrapped int64 words."""
+    z = (z ^ _lsr(z, 30)) * _as_i64(0xBF58476D1CE4E5B9)
+    z = (z ^ _lsr(z, 27)) * _as_i64(0x94D049BB133111EB)
+    return z ^ _lsr(z, 31)
+
+
+def os1_keys(idx: torch.Tensor, order: int, rows: int, bos_id: int, seed: int = 0):
+    """For token ids ``[B, T]``: ``(row [B, T] int64, -1 where no key exists; sign_hash [B, T] int64)`` of the ``order``
+    ids ending at each position.  A key exists where all ``order`` ids lie in the window and none after the first is
+    BOS (reference: ``os1_keys``, round2/source/train.py:2596-2624, there with tabulation hashing on the host; here two
+    position-salted multiplicative hashes computed on the tokens' device)."""
+    b, t = idx.shape
+    x = idx.to(torch.int64)
+    h0 = torch.full((b, t), _as_i64(seed * HASH_MULT[0] + 0x51ED270B), dtype=torch.int64, device=idx.device)
+    h1 = torch.full((b, t), _as_i64(seed * HASH_MULT[1] + 0x2545F491), dtype=torch.int64, device=idx.device)
+    for j in range(min(order, t)):
+        tok = F.pad(x, (j, 0), value=0)[:, :t] + 1
+        h0 = _mix64(h0 + tok * _as_i64(HASH_MULT[j % 3]) + j)
+        h1 = _mix64(h1 ^ (tok * _as_i64(HASH_MULT[(j + 1) % 3]) + 7 * j))
+    c = (x == bos_id).to(torch.int64).cumsum(1)
+    prev = torch.zeros_like(c)
+    if order - 1 < t:
+        prev[:, order - 1:] = c[:, :t - order + 1]
+    pos = torch.arange(t, device=idx.device)[None, :]
+    valid = (pos >= order - 1) & (c - prev == 0)
+    row = torch.where(valid, _lsr(h0, 8) & (rows - 1), torch.full_like(h0, -1))
+    return row, h1
+
+
+def os1_signs(hsign: torch.Tensor, dim: int) -> torch.Tensor:
+    """``dim`` signs (+1 / -1, fp32 ``[n, dim]``) of each sign hash ``[n]``: the bits, low first, of mixed words
+    ``mix(hash + (k + 1) * golden)``, one word per 64 signs (reference: ``os1_signs``, round2/source/train.py:2627-2643)."""
+    h = hsign.reshape(-1, 1)
+    words = (dim + 63) // 64
+    gold = torch.tensor([_as_i64((k + 1) * 0x9E3779B97F4A7C15) for k in range(words)], dtype=torch.int64, device=h.device)
+    z = _mix64(h + gold[None, :])                                             # [n, words]
+    sh = torch.arange(64, dtype=torch.int64, device=h.device)
+    bits = (z[:, :, None] >> sh[None, None, :]) & 1                           # arithmetic shift, low bit kept
+    return (1 - 2 * bits).reshape(h.shape[0], words * 64)[:, :dim].to(torch.float32)
+
+
+def os1_codebook(vocab_pad: int, dim: int, seed: int) -> torch.Tensor:
+    """Fixed readout codebook, fp32 ``[vocab_pad, dim]`` unit rows from a generator of its own (reference:
+    ``os1_codebook``, round2/source/train.py:2646-2651)."""
+    g = torch.Generator().manual_seed(seed)
+    c = torch.randn(vocab_pad, dim, generator=g, dtype=torch.float32)
+    return c / c.norm(dim=1, keepdim=True)
+
+
+def os1_gate(u: torch.Tensor, code: torch.Tensor, idx: torch.Tensor, a0: float, width: int, h0: float, slope: float):
+    """Gate ``G [B, T]`` = sigmoid(slope * (h - h0)), ``h_t`` the mean over the previous ``width`` positions j of the
+    window of ``s_j`` read at the token that followed j (an input at t, so the gate is causal); ``h_0 = 0``.  No
+    gradient flows through it (reference: the banded mean ``os1_band``, round2/source/train.py:2654-2661)."""
+    with torch.no_grad():
+        b, t = idx.shape
+        nxt = idx[:, 1:].reshape(-1)
+        uu = u.view(b, t, -1)[:, :-1].reshape(-1, u.shape[-1]).float()
+        sd = (uu * code.index_select(0, nxt).float()).sum(-1).view(b, t - 1) / a0       # s_j at token j+1, j < T-1
+        cs = F.pad(sd.cumsum(1), (1, 0))                                               # cs[t] = sum_{j<t} sd[j]
+        pos = torch.arange(t, device=idx.device)
+        lo = (pos - width).clamp_min(0)
+        n = (pos - lo).clamp_min(1).float()
+        h = (cs[:, pos] - cs[:, lo]) / n
+        return torch.sigmoid(slope * (h - h0))
+
+
+def os1_readout(s: torch.Tensor, gate: torch.Tensor, glin: float, beta: float, thr: float) -> torch.Tensor:
+    """Additive pre-softcap logit term for scores ``s [M, V]`` and gate ``[M]``:
+    ``glin * s + G * beta * relu(sg(s) - thr) / (1 - thr)`` (reference: round2/source/train.py:2321-2323)."""
+    return glin * s + gate[:, None] * (beta / (1.0 - thr)) * torch.relu(s.detach() - thr)
+
+
+def os1_row_step(x: torch.Tensor, g: torch.Tensor, lr: float, eps: float, cap: float) -> torch.Tensor:
+    """The table's stateless update on rows ``x [n, dim]`` with summed gradients ``g``: ``x - lr g / (rms(g) + eps)``,
+    then scaled back onto ``rms(x) <= cap * lr`` (reference: ``os1_row_step``, round2/source/train.py:2671-2680).
+    Returns the new rows (fp32)."""
+    x, g = x.float(), g.float()
+    r = g.square().mean(1, keepdim=True).sqrt()
+    x = x - g * (lr / (r + eps))
+    q = x.square().mean(1, keepdim=True).sqrt()
+    return x * torch.clamp((cap * lr) / q.clamp_min(1e-30), max=1.0)
+
+
+def os1_typ_rms(glin: float, a0: float, dim: int, tokens: int, world: int) -> float:
+    """RMS of one position's row gradient when ``|C^T d(logits)| = 1`` under the mean loss over ``tokens`` and the
+    average over ``world`` ranks (reference: ``os1_typ_rms``, round2/source/train.py:2664-2668)."""
+    return glin / (a0 * math.sqrt(dim) * max(1, tokens) * max(1, world))
+
+
+def softcap_cross_entropy_os1(x, w, targets, vocab, cap, u, code, gate, *, a0, glin, beta, thr, weights=None,
+                              reduction="mean"):
+    """``softcap_cross_entropy`` with the output table's term added before the soft-cap."""
+    s = F.linear(u.to(x.dtype), code.to(x.dtype)).float()[..., :vocab] / a0
+    pre = F.linear(x, w).float()[..., :vocab].reshape(-1, vocab) + os1_readout(s.reshape(-1, vocab), gate.reshape(-1), glin, beta, thr)
+    flat, tgt = softcap_logits(pre, cap), targets.reshape(-1)
+    if weights is not None:
+        nll = F.cross_entropy(flat, tgt, ignore_index=-1, reduction="none")
+        return (nll * weights.reshape(-1).float()).sum()
+    out = F.cross_entropy(flat, tgt, ignore_index=-1, reduction=reduction)
+    return out.view_as(targets) if reduction == "none" else out

@@ -62,6 +62,12 @@ class Trainer:
             if self.comm is not None and rt.world > 1:
                 self.tables.exchange = self.comm.table_exchange(self.tables)
             model.attach_tables(self.tables)
+        self.os1 = None
+        if config.os1_rows:
+            from .models.os1 import OutputTable
+            self.os1 = OutputTable(config, device=rt.device, dtype=self.dtype, group=dist.group.WORLD if rt.ddp else None,
+                                   world=rt.world, rank=rt.rank, cap=hyper.os1_cap, eps_rel=hyper.os1_eps_rel)
+            model.attach_os1(self.os1)
         if self.comm is not None and config.moe_layers and rt.world > 1:
             self.comm.install_moe(model)
         self.step_index = 0
@@ -120,6 +126,8 @@ class Trainer:
             mxfp8.weights_updated()          # quantised weight copies are refreshed lazily on their next use
         if self.tables is not None:
             self.tables.step(self.sched["table_lr"])
+        if self.os1 is not None:
+            self.os1.step(x_all.shape[0] // self.grad_accum * accum * x_all.shape[1])
         self.step_index += 1
         return total
 

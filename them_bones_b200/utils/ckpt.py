@@ -55,22 +55,30 @@ def model_state(model, optimizer=None, group=None) -> dict:
     return state
 
 
+def _gather_rows(table) -> dict:
+    """A row-sharded table's checkpoint entries with every rank's share interleaved back (owner = row % world)."""
+    share = table.state_for_checkpoint()
+    if not _is_dist():
+        return share
+    parts = [None] * dist.get_world_size()
+    dist.all_gather_object(parts, share)
+    out = {}
+    for k in share:
+        full = torch.empty(table.rows, *share[k].shape[1:], dtype=share[k].dtype)
+        for r, part in enumerate(parts):
+            full[r::len(parts)] = part[k]
+        out[k] = full
+    return out
+
+
 def save_checkpoint(path: str, model, meta: dict, optimizer=None, tables=None, rank: int = 0, state: dict | None = None):
     """Collective when the model is sharded: every rank must call it; only rank 0 writes."""
     state = state if state is not None else model_state(model, optimizer)
     extra = {}
     if tables is not None:
-        share = tables.state_for_checkpoint()
-        if _is_dist():
-            parts = [None] * dist.get_world_size()
-            dist.all_gather_object(parts, share)
-            for k in share:
-                full = torch.empty(tables.rows, *share[k].shape[1:], dtype=share[k].dtype)
-                for r, part in enumerate(parts):
-                    full[r::len(parts)] = part[k]
-                extra[k] = full
-        else:
-            extra = share
+        extra.update(_gather_rows(tables))
+    if getattr(model, "os1", None) is not None:
+        extra.update(_gather_rows(model.os1))
     if rank != 0:
         return
     payload = {"model_state": {**state, **extra}, "model_config": model_config_dict(model.config), "meta": meta}
@@ -94,6 +102,7 @@ def load_for_eval(path: str, device="cpu", dtype=None):
     device = torch.device(device)
     model = GPT(config)
     table_state = {k: state.pop(k) for k in list(state) if k.startswith("table_") and not k.startswith("table_lambda")}
+    os1_state = {k: state.pop(k) for k in list(state) if k in ("os1_table", "os1_scale")}
     model.load_state_dict(state, strict=True)
     dtype = dtype or (torch.bfloat16 if device.type == "cuda" else torch.float32)
     model = model.to(device)
@@ -103,6 +112,11 @@ def load_for_eval(path: str, device="cpu", dtype=None):
                               device=device, dtype=dtype)
         tables.load_share(table_state)
         model.attach_tables(tables)
+    if config.os1_rows:
+        from ..models.os1 import OutputTable
+        os1 = OutputTable(config, device=device, dtype=dtype)
+        os1.load_share(os1_state)
+        model.attach_os1(os1)
     model.eval()
     return model, ckpt.get("meta", {})
 

@@ -208,7 +208,7 @@ def greedy_decode(model, prompts: torch.Tensor, n_new: int) -> torch.Tensor:
     b, p = prompts.shape
     if p + n_new > model.config.sequence_len:
         raise ValueError("prompt + new tokens exceed the model's sequence length")
-    if model.tables is not None or any(blk.attn is None for blk in model.transformer.h):
+    if model.tables is not None or getattr(model, "os1", None) is not None or any(blk.attn is None for blk in model.transformer.h):
         return greedy_decode_full(model, prompts, n_new)          # tables and attention-free blocks: cache-free route
     cache = KVCache(model, b, p + n_new)
     if NativeDecoder.eligible(model) and n_new >= 1:
