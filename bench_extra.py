@@ -2,6 +2,7 @@
 
     python bench_extra.py --what moe    [--gpus N under torch.distributed.run] --steps 2 --warmup 2
     python bench_extra.py --what full   --table-rows 4194304          (MoE + bigram/trigram tables)
+    python bench_extra.py --what os1    --os1-rows 16777216            (dense decoder + output-side table)
     python bench_extra.py --what infer  --requests 256 --decode-batch 64 --new-tokens 128
 
 Same timing rules as ``bench.py`` (CUDA events, max over ranks, warm-up first).  Prints one JSON line on rank 0.
@@ -18,7 +19,7 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--what", default="moe", choices=["moe", "full", "infer"])
+    ap.add_argument("--what", default="moe", choices=["moe", "full", "os1", "infer"])
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=2)
@@ -26,6 +27,7 @@ def main():
     ap.add_argument("--total-batch", type=int, default=524288)
     ap.add_argument("--device-batch", type=int, default=8)
     ap.add_argument("--table-rows", type=int, default=1 << 22)
+    ap.add_argument("--os1-rows", type=int, default=1 << 24)
     ap.add_argument("--requests", type=int, default=256)
     ap.add_argument("--decode-batch", type=int, default=64)
     ap.add_argument("--new-tokens", type=int, default=128)
@@ -47,6 +49,8 @@ def main():
                   moe_capacity=moe_capacity_for(1.25, 2048, 2, 16), moe_aux=0.01)
     if a.what == "full":
         kw.update(table_orders=(2, 3), table_rows=a.table_rows)
+    if a.what == "os1":
+        kw.update(os1_rows=a.os1_rows)
     cfg = GPTConfig(**kw)
 
     def barrier():
@@ -55,7 +59,7 @@ def main():
         torch.cuda.synchronize()
 
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    if a.what in ("moe", "full"):
+    if a.what in ("moe", "full", "os1"):
         from them_bones_b200.trainer import Trainer
         hy = Hyper()
         hy.total_batch, hy.device_batch = a.total_batch, a.device_batch
@@ -76,9 +80,11 @@ def main():
             print(json.dumps({"metric": "train tokens/sec (device-timed, max over ranks, host->device copies included)",
                               "what": a.what, "value": a.steps * tr.total_batch / (ms / 1e3), "unit": "tokens/s",
                               "n_gpus": rt.world, "ms_per_step": ms / a.steps, "loss": float(loss),
-                              "config": {"model": f"moe 16e top-2 {a.depth}Lx1280" + (f" + tables {a.table_rows} rows" if a.what == "full" else ""),
+                              "config": {"model": (f"dense {a.depth}Lx1280 + output table {a.os1_rows} rows x 128, order 16" if a.what == "os1" else
+                                                   f"moe 16e top-2 {a.depth}Lx1280" + (f" + tables {a.table_rows} rows" if a.what == "full" else "")),
                                          "global_batch": tr.total_batch, "experts_per_gpu": 16 // rt.world,
                                          "fused_comm": tr.comm is not None},
+                              "os1_stats": tr.os1.stats if tr.os1 is not None else None,
                               "native_ops": dict(ops.COUNTS), "moe_stats": (tr.last_moe_stats.float().mean(0)[:3].tolist()
                                                                             if tr.last_moe_stats is not None else None)}), flush=True)
     else:

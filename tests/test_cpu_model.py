@@ -397,3 +397,68 @@ def test_output_table_zero_init_is_identity_then_learns(tmp_path):
     # int8 rows: a score just above the threshold moves by the quantisation step times the thresholded term's gain
     assert float((a - bb).abs().mean()) < 2e-3 and float((a - bb).abs().max()) < 0.5
     assert model(xe, y[:2], loss_reduction="none").shape == (2, 64)
+
+
+def test_answer_span_marks_and_weighted_loss():
+    import numpy as np
+    from them_bones_b200.data.synth import slice_windows, tail_marks
+    row = np.array([0, 5, 6, 7, 8, 9, 10, 11, 0, 3, 4, 5, 0, 9, 9, 9, 9], dtype=np.int32)      # docs of 8, 4 and 5 tokens
+    m = tail_marks(row, 0, 0.25)
+    assert m.tolist() == [False] * 6 + [True] * 2 + [False] * 3 + [True] + [False] * 4 + [True]
+    x, y = slice_windows(row, 8, 0, mark_tail=0.25, vocab=100)
+    assert x.shape == (2, 8) and y.shape == (2, 8)
+    assert y[0].tolist() == [5, 6, 7, 8, 9, 110, 111, -1]               # marked targets carry +vocab; BOS stays masked
+    assert y[1].tolist() == [3, 4, 105, -1, 9, 9, 9, 109]
+    x0, y0 = slice_windows(row, 8, 0)
+    assert (np.where(y >= 100, y - 100, y) == y0).all()
+    # the model unmarks and weights: loss = sum(w * nll) / count(valid)
+    torch.manual_seed(0)
+    cfg = tiny_cfg(n_layer=1, n_embd=64, n_head=2, vocab_size=512, sequence_len=32)
+    model = GPT(cfg)
+    model.init_weights()
+    with torch.no_grad():
+        model.lm_head.weight.normal_(0, 0.05)
+    idx = torch.randint(1, 512, (2, 32))
+    tg = torch.randint(1, 512, (2, 32))
+    tg[0, 5] = -1
+    marked = torch.zeros(2, 32, dtype=torch.bool)
+    marked[:, 24:] = True
+    tgm = torch.where(marked & (tg >= 0), tg + 512, tg)
+    model.answer_weight = 3.0
+    model.train()
+    got = model(idx, tgm, loss_div=2.0)
+    nll = model(idx, tg, loss_reduction="none")
+    w = torch.where(marked, 3.0, 1.0) * (tg >= 0)
+    assert float(got) == pytest.approx(float((w * nll).sum() / (tg >= 0).sum() / 2.0), rel=1e-5)
+    model.eval()
+    assert torch.allclose(model(idx, tgm, loss_reduction="none"), nll)     # evaluation unmarks, no weights
+    model.answer_weight = None
+    model.train()
+    assert float(model(idx, tg, loss_div=2.0)) == pytest.approx(float(nll.sum() / (tg >= 0).sum() / 2.0), rel=1e-5)
+
+
+def test_split_evaluation_classes_and_totals():
+    import numpy as np
+    from them_bones_b200.utils.evalbpb import evaluate_bpb
+    from them_bones_b200.utils.evalsplit import ContextSet, SplitEval, bigram_repeats, evaluate_split
+    x = np.array([[0, 5, 6, 5, 6, 0, 5, 6]])
+    y = np.array([[5, 6, 5, 6, -1, 5, 6, 7]])
+    rep = bigram_repeats(x, y, 0)
+    assert rep.tolist() == [[False, False, False, True, False, False, False, False]]     # (5,6) again in document 1 only
+    cs = ContextSet(ctx=2)
+    cs.add(np.array([9, 5, 6, 9]))
+    seen = cs.seen(x)
+    assert seen.tolist() == [[False, False, True, False, True, False, False, True]]      # context (5,6) ends at 2, 4, 7
+    ev = SplitEval(16, 0, cs, token_bytes=torch.full((16,), 2))
+    ev.observe(torch.from_numpy(x), torch.from_numpy(y), torch.ones(1, 8))
+    m = ev.merged()
+    assert m["all"]["tokens"] == 7 and m["bi_rep"]["tokens"] == 1 and m["ctx_seen"]["tokens"] == 2
+    assert m["novel"]["tokens"] == 4 and m["all"]["bytes"] == 14 and m["all"]["nats"] == pytest.approx(7.0)
+    # on a model: the "all" class is evaluate_bpb's number
+    torch.manual_seed(0)
+    model = GPT(tiny_cfg(n_layer=1, n_embd=64, n_head=2, vocab_size=512, sequence_len=64))
+    model.init_weights()
+    a = evaluate_bpb(model, 512, 4, 64, torch.device("cpu"), max_tokens=1000)
+    b = evaluate_split(model, 512, 4, 64, torch.device("cpu"), max_tokens=1000)
+    assert b["all"]["bpb"] == pytest.approx(a["val_bpb"], rel=1e-6) and b["all"]["tokens"] == a["num_tokens"]
+    assert b["bi_rep"]["tokens"] + b["novel"]["tokens"] == b["all"]["tokens"]

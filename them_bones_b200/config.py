@@ -242,6 +242,11 @@ def switches(refresh: bool = False) -> dict:
         TABLE_STALE=e("TABLE_STALE", False, bool), TABLE_HOST_STATE=e("TABLE_HOST_STATE", "auto", str),   # auto | 0 | 1: Adam moments of the tables in pinned host memory
         OS1=e("OS1", False, bool), OS1_ROWS=e("OS1_ROWS", 1 << 24, int), OS1_ORDER=e("OS1_ORDER", 16, int),
         OS1_LR=e("OS1_LR", 0.125, float), OS1_SEED=e("OS1_SEED", 0, int),
+        # answer phase: from progress 1 - ANSWER_PHASE on, the loader marks the last ANSWER_TAIL of every document and the
+        # loss weights those targets by ANSWER_WEIGHT (reference: switch 29, QaPhase round2/source/train.py:19691)
+        ANSWER_PHASE=e("ANSWER_PHASE", 0.0, float), ANSWER_TAIL=e("ANSWER_TAIL", 0.25, float),
+        ANSWER_WEIGHT=e("ANSWER_WEIGHT", 2.0, float),
+        EVAL_SPLIT=e("EVAL_SPLIT", False, bool),     # after the final evaluation: held-out loss by position class
         DATA_RULE=e("DATA_RULE", "", str),           # e.g. "len:64-4096,band:0.05-0.95,dedup:32,from:0.1"
         # kernels / system
         SELFCHECK=e("SELFCHECK", False, bool),       # compare every native op with the PyTorch path before training

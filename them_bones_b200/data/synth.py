@@ -83,14 +83,32 @@ class PackedRows:
         return row
 
 
-def slice_windows(row: np.ndarray, seq_len: int, bos_id: int, mask_bos: bool = True):
-    """One packed row -> ``(inputs [n, T] int32, targets [n, T] int64)``."""
+def tail_marks(row: np.ndarray, bos_id: int, frac: float) -> np.ndarray:
+    """Boolean mask over a packed row: the last ``frac`` of every document (its "answer span"; the synthetic stand-in
+    for the reference's question-answer tails, ``QaPhase.spans`` round2/source/train.py:19717-19760)."""
+    n = len(row)
+    starts = np.flatnonzero(row == bos_id)
+    if len(starts) == 0 or starts[0] != 0:
+        starts = np.concatenate([[0], starts])
+    ends = np.concatenate([starts[1:], [n]])
+    doc = np.searchsorted(starts, np.arange(n), side="right") - 1
+    length = (ends - starts)[doc]
+    return (np.arange(n) - starts[doc]) >= np.ceil(length * (1.0 - frac))
+
+
+def slice_windows(row: np.ndarray, seq_len: int, bos_id: int, mask_bos: bool = True, mark_tail: float = 0.0, vocab: int = 0):
+    """One packed row -> ``(inputs [n, T] int32, targets [n, T] int64)``.  ``mark_tail > 0``: the targets inside the
+    last ``mark_tail`` of each document are marked by adding ``vocab`` (the model weights their loss; reference:
+    the loader's marks for ``qa_unmark``, round2/source/train.py:6504)."""
     n = (len(row) - 1) // seq_len
     x = row[:n * seq_len].reshape(n, seq_len)
-    y = row[1:n * seq_len + 1].reshape(n, seq_len).astype(np.int64)
+    y = row[1:n * seq_len + 1].astype(np.int64)
     if mask_bos:
         y = np.where(y == bos_id, -1, y)
-    return x, y
+    if mark_tail > 0.0:
+        marks = tail_marks(row, bos_id, mark_tail)[1:n * seq_len + 1]
+        y = np.where(marks & (y >= 0), y + vocab, y)
+    return x, y.reshape(n, seq_len)
 
 
 class SynthLoader:
@@ -99,7 +117,8 @@ class SynthLoader:
 
     def __init__(self, vocab: int, seq_len: int, local_windows: int, *, rank: int = 0, seed: int = 0,
                  doc_len=(128, 2048), zipf_s: float = 1.1, bos_id: int = 0, pin: bool = False, rule=None):
-        self.seq_len, self.local_windows, self.bos_id = seq_len, local_windows, bos_id
+        self.seq_len, self.local_windows, self.bos_id, self.vocab = seq_len, local_windows, bos_id, vocab
+        self.mark_tail = 0.0                 # > 0: answer-span marks on the targets (set when the answer phase starts)
         self.docs = ZipfDocs(vocab, zipf_s, doc_len, seed=seed * 1000003 + rank, bos_id=bos_id)
         self.rule = rule
         self.rows = PackedRows(self.docs, seq_len * local_windows, rule=rule)
@@ -108,7 +127,7 @@ class SynthLoader:
 
     def next_step(self):
         row = self.rows.next_row()
-        x, y = slice_windows(row, self.seq_len, self.bos_id)
+        x, y = slice_windows(row, self.seq_len, self.bos_id, mark_tail=self.mark_tail, vocab=self.vocab)
         xt, yt = torch.from_numpy(np.ascontiguousarray(x)), torch.from_numpy(np.ascontiguousarray(y))
         if self.pin:
             xt, yt = xt.pin_memory(), yt.pin_memory()

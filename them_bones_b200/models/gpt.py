@@ -124,6 +124,7 @@ class GPT(nn.Module):
         self.tables: HashedTables | None = None           # attached by attach_tables(); not nn.Parameters
         self.table_lambda = nn.Parameter(torch.ones(len(config.table_orders))) if config.table_orders else None
         self.os1 = None                                   # output-side table, attached by attach_os1()
+        self.answer_weight = None                         # float: the loader marks answer-span targets (target + vocab)
         cos, sin = RF.rotary_tables(config.sequence_len, config.head_dim, config.rope_base)
         self.register_buffer("cos", cos, persistent=False)
         self.register_buffer("sin", sin, persistent=False)
@@ -250,6 +251,18 @@ class GPT(nn.Module):
             out.append((tk, ok.float() * (w / loss_div) / n_valid))
         return out
 
+    def answer_terms(self, targets, loss_div: float = 1.0):
+        """Marked targets (``target + vocab_size``, set by the loader on answer spans) back to targets, and absolute
+        row weights ``w / n_valid / loss_div`` with ``w = answer_weight`` where marked and 1 elsewhere: the weighted
+        mean over the count of valid targets (reference: ``qa_unmark`` / ``qa_extra_loss``,
+        round2/source/train.py:6504-6521)."""
+        v = self.config.vocab_size
+        marked = targets >= v
+        tg = torch.where(marked, targets - v, targets)
+        valid = tg >= 0
+        w = torch.where(marked, float(self.answer_weight), 1.0) * valid
+        return tg, w / valid.sum().clamp_min(1).float() / loss_div
+
     def cos_dtype(self):
         return self.lm_head.weight.dtype
 
@@ -286,6 +299,10 @@ class GPT(nn.Module):
         cfg = self.config
         moe_aux = [] if (self.has_moe and targets is not None and loss_reduction == "mean") else None
         x = self.trunk(idx, doc_start, moe_aux, table_rows)
+        if targets is not None and self.answer_weight is not None:
+            targets, aw = self.answer_terms(targets, loss_div)
+            if self.training and loss_reduction == "mean" and row_weights is None:
+                row_weights = aw
         if self.os1 is not None:
             u, gate = self.os1.read(idx)
             kw = self.os1.readout_args()

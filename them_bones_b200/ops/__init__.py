@@ -158,6 +158,7 @@ def lmhead_logits(x, w, vocab, cap):
 def lmhead_loss(x, w, targets, vocab, cap, reduction="mean", row_weights=None, loss_div=1.0, aux=None, label_smoothing=0.0):
     """Loss head: GEMM + softcap + log-sum-exp + target gather in row blocks; the full ``[M, V]`` logits never exist
     on the native path.  ``"mean"`` is divided by ``loss_div`` (gradient accumulation folded into the graph).
+    ``row_weights`` (with ``"mean"``): the loss is ``sum(row_weights * nll)`` with absolute weights, nothing else applied.
     ``aux``: up to two ``(targets, row_weights)`` pairs added as ``sum(row_weights * nll(targets))`` -- further targets
     that share each row's soft-max (multi-token prediction; reference: ``fused_loss_multi``,
     round1/source/train.py:5070-5093).  ``label_smoothing``: the main target's loss becomes ``(1 - s) * nll + s * (lse -
@@ -165,7 +166,8 @@ def lmhead_loss(x, w, targets, vocab, cap, reduction="mean", row_weights=None, l
     if native(x):
         return _cuda().lmhead_loss(x, w, targets, vocab, cap, reduction, row_weights, loss_div, aux, label_smoothing)
     out = RF.softcap_cross_entropy(x, w.to(x.dtype), targets, vocab, cap, row_weights, reduction, label_smoothing)
-    out = out / loss_div if (reduction == "mean" and loss_div != 1.0) else out
+    # row weights are absolute (they carry the mean and loss_div themselves), as on the native path
+    out = out / loss_div if (reduction == "mean" and loss_div != 1.0 and row_weights is None) else out
     if aux and reduction == "mean":
         for tk, wk in aux:
             out = out + RF.softcap_cross_entropy(x, w.to(x.dtype), tk, vocab, cap, wk, "mean")
@@ -206,7 +208,7 @@ def lmhead_loss_os1(x, w, targets, vocab, cap, u, code, gate, *, a0, glin, beta,
                                        row_weights, loss_div)
     out = RF.softcap_cross_entropy_os1(x, w.to(x.dtype), targets, vocab, cap, u, code, gate, a0=a0, glin=glin, beta=beta,
                                        thr=thr, weights=row_weights, reduction=reduction)
-    return out / loss_div if (reduction == "mean" and loss_div != 1.0) else out
+    return out / loss_div if (reduction == "mean" and loss_div != 1.0 and row_weights is None) else out
 
 
 def lmhead_logits_os1(x, w, vocab, cap, u, code, gate, *, a0, glin, beta, thr):

@@ -90,6 +90,14 @@ def save_checkpoint(path: str, model, meta: dict, optimizer=None, tables=None, r
     os.replace(tmp, path)
 
 
+def check_declared_length(model, trained_seq_len: int) -> None:
+    """The scorer takes ``model_config.sequence_len`` as its maximum length, so a checkpoint must declare the window
+    length it was trained on (reference: ``check_declared_length``, round2/source/train.py:20767-20774)."""
+    declared = model.config.sequence_len
+    if declared != trained_seq_len:
+        raise RuntimeError(f"model_config.sequence_len={declared} differs from the trained window length {trained_seq_len}")
+
+
 def load_for_eval(path: str, device="cpu", dtype=None):
     """Rebuild the model from a checkpoint with no environment: ``GPTConfig(**model_config)``, strict load of the
     dense state, experts and tables attached separately, eval mode.  Every rank is an independent full replica (all

@@ -73,6 +73,8 @@ def main(argv=None):
                          hyper=hyper)
     print0("model_config " + json.dumps(C.model_config_dict(cfg)))
     tr = Trainer(cfg, hyper, rt, horizon_steps=args.steps, budget_seconds=args.budget_seconds)
+    if sw["ANSWER_PHASE"] > 0:
+        tr.model.answer_weight = sw["ANSWER_WEIGHT"]     # marked targets are unmarked and weighted inside the forward
     print0(tr.describe())
     n_params = tr.model.num_scaling_params()
     print0(f"parameters {n_params:,}; flops/token {tr.flops_per_token:.4e}")
@@ -118,6 +120,9 @@ def main(argv=None):
                 print0(f"step {step}: window length -> {want}")
         if rule is not None:
             rule.phase = tr.progress()
+        if sw["ANSWER_PHASE"] > 0 and loader.mark_tail == 0.0 and tr.progress() >= 1.0 - sw["ANSWER_PHASE"]:
+            loader.mark_tail = sw["ANSWER_TAIL"]         # rows fetched from here on carry answer-span marks
+            print0(f"step {step}: answer phase on (tail {sw['ANSWER_TAIL']}, weight {sw['ANSWER_WEIGHT']})")
         x, y = prefetch.finish() if prefetch else fetch()
         if prefetch:
             prefetch.start()
@@ -201,6 +206,7 @@ def main(argv=None):
                 median_dt=sorted(dts)[len(dts) // 2] if dts else None, bad=bad, native_ops=dict(ops.COUNTS),
                 save_opt_state=sw["SAVE_OPT_STATE"])
     if not args.no_save:
+        CK.check_declared_length(tr.model, loader.seq_len)
         CK.save_checkpoint(args.out, tr.model, meta, optimizer=tr.optimizer, tables=tr.tables, rank=rt.rank)
         print0(f"saved {args.out}")
     result = {}
@@ -210,6 +216,15 @@ def main(argv=None):
                           max_tokens=args.eval_tokens, bos_id=cfg.bos_id)
         result.update(causality=cc, **ev)
         print0(f"causality passed={cc['passed']} max_abs_diff={cc['max_abs_diff']:.3e}; val_bpb {ev['val_bpb']:.4f}")
+        if sw["EVAL_SPLIT"]:
+            # per-class held-out loss; the contexts of one training-stream row stand for "text the run has seen"
+            from them_bones_b200.utils.evalsplit import ContextSet, evaluate_split
+            seen = ContextSet(ctx=8)
+            seen.add(loader.rows.next_row())
+            split = evaluate_split(tr.model, cfg.vocab_size, tr.device_batch, cfg.sequence_len, rt.device,
+                                   max_tokens=args.eval_tokens, bos_id=cfg.bos_id, contexts=seen, rank=rt.rank)
+            result.update(eval_split=split)
+            print0("eval_split " + json.dumps({k: round(v["bpb"], 4) for k, v in split.items()}))
     med = meta["median_dt"]
     print0("---")
     print0(f"steps {step} tokens {meta['tokens']:,} seconds {total_s:.1f} median_dt "
