@@ -462,3 +462,22 @@ def test_split_evaluation_classes_and_totals():
     b = evaluate_split(model, 512, 4, 64, torch.device("cpu"), max_tokens=1000)
     assert b["all"]["bpb"] == pytest.approx(a["val_bpb"], rel=1e-6) and b["all"]["tokens"] == a["num_tokens"]
     assert b["bi_rep"]["tokens"] + b["novel"]["tokens"] == b["all"]["tokens"]
+
+
+def test_background_checkpoint_write(tmp_path):
+    from them_bones_b200.utils import ckpt as CK
+    model = GPT(tiny_cfg(n_layer=1, n_embd=64, n_head=2, vocab_size=512, sequence_len=64))
+    model.init_weights()
+    bg = CK.BackgroundSave()
+    for k in range(2):                                           # the second submit waits for the first
+        bg.submit(str(tmp_path / f"p{k}.pt"), CK.build_payload(model, dict(steps=k)))
+    bg.wait()
+    assert bg.done == 2
+    m, meta = CK.load_for_eval(str(tmp_path / "p1.pt"), "cpu")
+    assert meta["steps"] == 1 and torch.equal(m.lm_head.weight, model.lm_head.weight)
+    CK.check_declared_length(model, 64)
+    with pytest.raises(RuntimeError):
+        CK.check_declared_length(model, 32)
+    bg.submit(str(tmp_path / "no_such_dir" / "x" / ".." / ".." / "f\0.pt"), dict(a=1))
+    with pytest.raises(RuntimeError):
+        bg.wait()

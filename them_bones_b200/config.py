@@ -266,6 +266,7 @@ def switches(refresh: bool = False) -> dict:
         MICRO_BARRIER=e("MICRO_BARRIER", False, bool),
         CUDA_GRAPH=e("CUDA_GRAPH", False, bool),
         SAVE_OPT_STATE=e("SAVE_OPT_STATE", False, bool),
+        SAVE_EVERY=e("SAVE_EVERY", 0, int),          # > 0: a checkpoint every so many steps, written on a background thread
     )
     if s["MLP"] not in ("bf16", "mxfp8"):
         raise ValueError(f"{PREFIX}MLP={s['MLP']!r}: expected bf16 or mxfp8")

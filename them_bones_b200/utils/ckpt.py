@@ -71,23 +71,68 @@ def _gather_rows(table) -> dict:
     return out
 
 
-def save_checkpoint(path: str, model, meta: dict, optimizer=None, tables=None, rank: int = 0, state: dict | None = None):
-    """Collective when the model is sharded: every rank must call it; only rank 0 writes."""
+def build_payload(model, meta: dict, optimizer=None, tables=None, state: dict | None = None) -> dict:
+    """The checkpoint as host tensors.  Collective when the model is sharded: every rank must call it."""
     state = state if state is not None else model_state(model, optimizer)
     extra = {}
     if tables is not None:
         extra.update(_gather_rows(tables))
     if getattr(model, "os1", None) is not None:
         extra.update(_gather_rows(model.os1))
-    if rank != 0:
-        return
     payload = {"model_state": {**state, **extra}, "model_config": model_config_dict(model.config), "meta": meta}
     if optimizer is not None and meta.get("save_opt_state"):
         payload["optimizer_state"] = optimizer.state_dict()
+    return payload
+
+
+def write_payload(path: str, payload: dict) -> None:
+    """Atomic write: a temporary file beside ``path``, then a rename."""
     tmp = path + ".tmp"
     os.makedirs(os.path.dirname(os.path.abspath(path)), exist_ok=True)
     torch.save(payload, tmp)
     os.replace(tmp, path)
+
+
+def save_checkpoint(path: str, model, meta: dict, optimizer=None, tables=None, rank: int = 0, state: dict | None = None):
+    """Collective when the model is sharded: every rank must call it; only rank 0 writes."""
+    payload = build_payload(model, meta, optimizer, tables, state)
+    if rank == 0:
+        write_payload(path, payload)
+
+
+class BackgroundSave:
+    """Checkpoint writes off the training thread: the host copy of the state is taken by the caller (a collective on
+    sharded models), serialisation and the file write run on a worker thread while training goes on.  One write is in
+    flight at a time; a new one waits for the previous (reference: the overlapped background saves ``SaveovBg``,
+    round2/source/train.py:20203-20430)."""
+
+    def __init__(self):
+        self.thread, self.error, self.done, self.seconds = None, None, 0, 0.0
+
+    def submit(self, path: str, payload: dict) -> None:
+        import threading
+        import time
+        self.wait()
+
+        def work():
+            t0 = time.time()
+            try:
+                write_payload(path, payload)
+                self.done += 1
+            except Exception as exc:  # noqa: BLE001  (reported by wait(); training is not interrupted by a failed write)
+                self.error = exc
+            self.seconds += time.time() - t0
+
+        self.thread = threading.Thread(target=work, daemon=True)
+        self.thread.start()
+
+    def wait(self) -> None:
+        if self.thread is not None:
+            self.thread.join()
+            self.thread = None
+        if self.error is not None:
+            err, self.error = self.error, None
+            raise RuntimeError(f"background checkpoint write failed: {err}")
 
 
 def check_declared_length(model, trained_seq_len: int) -> None:

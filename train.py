@@ -97,6 +97,7 @@ def main(argv=None):
     stop_rule = StopRule(args.budget_seconds, reserve_s=0.02 * args.budget_seconds)
     boundary = AsyncBoundary(rt.device, hyper.sync_every) if sw["BOUNDARY_ASYNC"] else None
     rescue = CK.RescueCopy(hyper.rescue_from, hyper.rescue_every)
+    bg_save = CK.BackgroundSave()
     memphase = MemPhase(rt.device, sw["MEM_PHASE"])
     ema = EmaLawa(tr.model.parameters(), 1.0 - sw["EMA"], 10) if sw["EMA"] > 0 else None
     shed = ShedProbe(rt, tr.grad_accum) if sw["SHED"] else None
@@ -193,6 +194,10 @@ def main(argv=None):
         if ema is not None:
             ema.update(step, tr.progress())
         rescue.maybe_refresh(step, tr.progress(), tr.model, tr.optimizer)
+        if sw["SAVE_EVERY"] > 0 and step > 0 and step % sw["SAVE_EVERY"] == 0 and not args.no_save:
+            payload = CK.build_payload(tr.model, dict(steps=step, periodic=True), tr.optimizer, tr.tables)
+            if rt.is_master:
+                bg_save.submit(args.out + ".periodic", payload)
         step += 1
         if stop:
             print0(f"step {step}: stop rule fired at {elapsed:.1f}s")
@@ -205,6 +210,7 @@ def main(argv=None):
     meta = dict(steps=step, tokens=step * tokens_per_step, seconds=total_s, switches=sw, world=rt.world,
                 median_dt=sorted(dts)[len(dts) // 2] if dts else None, bad=bad, native_ops=dict(ops.COUNTS),
                 save_opt_state=sw["SAVE_OPT_STATE"])
+    bg_save.wait()
     if not args.no_save:
         CK.check_declared_length(tr.model, loader.seq_len)
         CK.save_checkpoint(args.out, tr.model, meta, optimizer=tr.optimizer, tables=tr.tables, rank=rt.rank)
