@@ -239,7 +239,7 @@ def switches(refresh: bool = False) -> dict:
         MOE_TOPK=e("MOE_TOPK", 2, int), MOE_HIDDEN=e("MOE_HIDDEN", 0, int), MOE_SHARED=e("MOE_SHARED", 0, int),
         MOE_AUX=e("MOE_AUX", 0.01, float), MOE_ZLOSS=e("MOE_ZLOSS", 0.0, float),
         TABLES=e("TABLES", "", str), TABLE_ROWS=e("TABLE_ROWS", 0, int), TABLE_SEED=e("TABLE_SEED", 0, int),
-        TABLE_STALE=e("TABLE_STALE", False, bool), TABLE_HOST_STATE=e("TABLE_HOST_STATE", "auto", str),   # auto | 0 | 1: Adam moments of the tables in pinned host memory
+        TABLE_HOST_STATE=e("TABLE_HOST_STATE", "auto", str),   # auto | 0 | 1: Adam moments of the tables in pinned host memory
         OS1=e("OS1", False, bool), OS1_ROWS=e("OS1_ROWS", 1 << 24, int), OS1_ORDER=e("OS1_ORDER", 16, int),
         OS1_LR=e("OS1_LR", 0.125, float), OS1_SEED=e("OS1_SEED", 0, int),
         # answer phase: from progress 1 - ANSWER_PHASE on, the loader marks the last ANSWER_TAIL of every document and the
@@ -253,7 +253,7 @@ def switches(refresh: bool = False) -> dict:
         KERNELS=e("KERNELS", "auto", str),           # auto: CUDA kernels on a GPU, torch oracle on CPU | ref
         FUSED_COMM=e("FUSED_COMM", True, bool),      # in-kernel NVLink collectives (False: NCCL baseline path)
         WGRAD_PUSH=e("WGRAD_PUSH", False, bool),     # weight-gradient GEMMs reduce-scatter their tiles into the owner's slab
-        LOSS_CHUNK=e("LOSS_CHUNK", 8192, int),
+        LOSS_ROWS=e("LOSS_ROWS", 4096, int),         # rows per block of the chunked loss head (one [rows, V] logits buffer)
         OPT=e("OPT", "lean", str),                   # lean | dist | single
         OPT_OVERLAP_CHECK=e("OPT_OVERLAP_CHECK", False, bool),
         FINITE_GATE=e("FINITE_GATE", True, bool),
@@ -264,7 +264,6 @@ def switches(refresh: bool = False) -> dict:
         EMA=e("EMA", 0.0, float),
         MEM_PRINT=e("MEM_PRINT", False, bool), MEM_PHASE=e("MEM_PHASE", -1, int),
         MICRO_BARRIER=e("MICRO_BARRIER", False, bool),
-        CUDA_GRAPH=e("CUDA_GRAPH", False, bool),
         SAVE_OPT_STATE=e("SAVE_OPT_STATE", False, bool),
         SAVE_EVERY=e("SAVE_EVERY", 0, int),          # > 0: a checkpoint every so many steps, written on a background thread
     )

@@ -6,8 +6,9 @@ reference keeps its n-gram table in host shared memory and exchanges sparse grad
 barriers (``NgramHostTable``, round2/source/train.py:3526-3862: ``ids`` 3621, ``gather`` 3627, ``_exchange`` 3653,
 ``step`` 3678); kept from it: zero initialisation (the first forward equals the table-free model), causal hashing with
 a pad id before the window start, owner-computes updates (owner = ``row % world``), gradients of duplicate rows summed
-then averaged over ranks, an update that is skipped when any owned gradient is non-finite, optional one-step-stale
-application, stochastic rounding of updated rows to bf16.
+then averaged over ranks, an update that is skipped when any owned gradient is non-finite, stochastic rounding of
+updated rows to bf16.  Not kept: the one-step-stale application (``NgramStaleT21``, :13934), which exists to hide the
+host table's update behind a worker thread; the device update here takes milliseconds and is applied in step.
 
 Here each rank owns ``rows / world`` rows in device memory; lookups and sparse gradients travel by all-to-all
 (``parallel.table_a2a``: fused peer-memory kernels on NVLink, or the NCCL/gloo baseline); the update is a sparse Adam

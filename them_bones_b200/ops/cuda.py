@@ -8,6 +8,7 @@ optimizer's buffer, ``GradFoldIn`` round2/source/train.py:4677-4723 and ``_Linea
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 import torch.nn.functional as F
@@ -339,7 +340,7 @@ def attention(qkv, cos, sin, n_head, head_dim, scale, doc_start, window):
 
 
 # -- loss head -------------------------------------------------------------------------------------------------------
-LOSS_ROWS = 4096
+LOSS_ROWS = max(128, int(os.environ.get("BONES_LOSS_ROWS", 4096)))       # rows per logits block
 
 
 class _LmHeadLossFn(torch.autograd.Function):
