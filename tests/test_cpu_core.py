@@ -241,3 +241,42 @@ def test_document_selection_rule():
     x, y = ld.next_step()
     assert x.shape == (4, 128) and ld.rule.count["drop_length"][1] > 0
     assert isinstance(ld.rows, PackedRows) and ld.rows.rule is ld.rule
+
+
+def test_native_call_sites_match_the_c_signatures():
+    """Every ``call("bones_...", ...)`` in the package and the tests passes as many arguments as the ``extern "C"``
+    entry point declares (ctypes does not check, and a short call reads garbage for the missing ones)."""
+    import ast
+    import glob
+    import re
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sigs = {}
+    for f in glob.glob(os.path.join(root, "them_bones_b200", "csrc", "*.cu")):
+        src = re.sub(r"//[^\n]*", "", open(f).read())
+        for m in re.finditer(r"\bint\s+(bones_\w+)\s*\(([^)]*)\)\s*\{", src):
+            args = m.group(2).strip()
+            sigs[m.group(1)] = 0 if args in ("", "void") else args.count(",") + 1
+    assert len(sigs) > 40
+    star = {"aux_ptrs": 5}                                     # helpers that expand to a fixed number of arguments
+    seen = 0
+    files = glob.glob(os.path.join(root, "them_bones_b200", "**", "*.py"), recursive=True) + \
+        glob.glob(os.path.join(root, "tests", "*.py")) + glob.glob(os.path.join(root, "*.py"))
+    for f in files:
+        for node in ast.walk(ast.parse(open(f).read())):
+            if not (isinstance(node, ast.Call) and node.args and isinstance(node.args[0], ast.Constant)
+                    and isinstance(node.args[0].value, str) and node.args[0].value.startswith("bones_")):
+                continue
+            fn = node.func
+            if (fn.attr if isinstance(fn, ast.Attribute) else getattr(fn, "id", "")) != "call":
+                continue
+            n = 0
+            for a in node.args[1:]:
+                if isinstance(a, ast.Starred):
+                    n += star[a.value.func.id]
+                else:
+                    n += 1
+            name = node.args[0].value
+            assert name in sigs, f"{f}: {name} is not an entry point of the library"
+            assert n == sigs[name], f"{f}:{node.lineno}: {name} takes {sigs[name]} arguments, the call passes {n}"
+            seen += 1
+    assert seen > 40
