@@ -575,10 +575,51 @@ __device__ __forceinline__ float tanh_fast(float x) {
   asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+__device__ __forceinline__ float ex2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Second pass of the row kernel for one thread: gradient of its 64 columns from the saved tanh values.
+// p = exp2(k2 * t - lw) already carries the row's weight (lw = lse2 - log2(weight sum)).  FIX: this thread owns the column
+// of a target (at most three threads of a row do) and subtracts the target weights; the others never compare.
+template <bool FIX>
+__device__ __forceinline__ void ce_row_grad(const __half2 (&th)[8][4], __nv_bfloat16* d, int V, float k2, float lw, float w_uni, int tg, float w_tgt,
+                                            int t2, float a2, int t3, float a3) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int c = (i * 1024 + threadIdx.x) * 8;
+    if (c >= V) continue;
+    float g[8];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const float2 tt = __half22float2(th[i][t]);
+      float p0 = ex2_fast(fmaf(k2, tt.x, -lw)) - w_uni, p1 = ex2_fast(fmaf(k2, tt.y, -lw)) - w_uni;
+      if (FIX) {
+        const int c0i = c + 2 * t, c1i = c0i + 1;
+        if (c0i == tg) p0 -= w_tgt;
+        if (c1i == tg) p1 -= w_tgt;
+        if (c0i == t2) p0 -= a2;
+        if (c1i == t2) p1 -= a2;
+        if (c0i == t3) p0 -= a3;
+        if (c1i == t3) p1 -= a3;
+      }
+      g[2 * t] = p0 * fmaf(-tt.x, tt.x, 1.0f);
+      g[2 * t + 1] = p1 * fmaf(-tt.y, tt.y, 1.0f);
+    }
+    uint4 o;
+    o.x = pack_bf16(g[0], g[1]); o.y = pack_bf16(g[2], g[3]); o.z = pack_bf16(g[4], g[5]); o.w = pack_bf16(g[6], g[7]);
+    *reinterpret_cast<uint4*>(d + c) = o;
+  }
+}
+
+template <bool CAPPED>
 __global__ void __launch_bounds__(1024, 1)
 softcap_ce_row_kernel(const __nv_bfloat16* __restrict__ logits, long long ldl, const long long* __restrict__ targets, int V, float cap,
                       float* __restrict__ nll, __nv_bfloat16* dlogits, const float* __restrict__ row_w, const float* __restrict__ n_valid,
-                      float inv_loss_div, int M, int capped, AuxTargets aux) {
+                      float inv_loss_div, int M, AuxTargets aux) {
+  constexpr bool capped = CAPPED;
   const int row = blockIdx.x;
   if (row >= M) return;
   const __nv_bfloat16* l = logits + (size_t)row * ldl;
@@ -606,7 +647,7 @@ softcap_ce_row_kernel(const __nv_bfloat16* __restrict__ logits, long long ldl, c
       const float t0 = capped ? f.x * inv_cap : tanh_fast(f.x * inv_cap), t1 = capped ? f.y * inv_cap : tanh_fast(f.y * inv_cap);
       th[i][t] = __floats2half2_rn(t0, t1);
       if (c < V) {
-        s += exp2f(k2 * t0 - k2) + exp2f(k2 * t1 - k2);
+        s += ex2_fast(fmaf(k2, t0, -k2)) + ex2_fast(fmaf(k2, t1, -k2));
         st += t0 + t1;
       }
     }
@@ -646,30 +687,16 @@ softcap_ce_row_kernel(const __nv_bfloat16* __restrict__ logits, long long ldl, c
   if (valid) w = row_w ? row_w[row] : inv_loss_div / fmaxf(1.0f, *n_valid);
   const float wsum = w + a2 + a3;
   const float w_tgt = w * (1.0f - sm), w_uni = w * sm / (float)V;
+  // a row without any live target has weight sum 0: lw = +inf makes every probability term exactly 0
+  const float lw = wsum > 0.f ? lse2 - log2f(wsum) : __int_as_float(0x7f800000);
+  const int tgi = (valid && w_tgt != 0.f) ? (int)tgt : -1, t2i = a2 != 0.f ? (int)t2 : -1, t3i = a3 != 0.f ? (int)t3 : -1;
+  // thread x holds columns (i * 1024 + x) * 8 .. + 7, so column c belongs to thread (c >> 3) & 1023
+  const int me = threadIdx.x;
+  const bool owner = (tgi >= 0 && ((tgi >> 3) & 1023) == me) || (t2i >= 0 && ((t2i >> 3) & 1023) == me) ||
+                     (t3i >= 0 && ((t3i >> 3) & 1023) == me);
   __nv_bfloat16* d = dlogits + (size_t)row * ldl;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int c = (i * 1024 + threadIdx.x) * 8;
-    if (c >= V) continue;
-    float g[8];
-#pragma unroll
-    for (int t = 0; t < 4; ++t) {
-      const float2 tt = __half22float2(th[i][t]);
-      float p0 = wsum * exp2f(k2 * tt.x - lse2) - w_uni, p1 = wsum * exp2f(k2 * tt.y - lse2) - w_uni;
-      const int c0i = c + 2 * t, c1i = c0i + 1;
-      if (c0i == tgt) p0 -= w_tgt;
-      if (c1i == tgt) p1 -= w_tgt;
-      if (c0i == t2) p0 -= a2;
-      if (c1i == t2) p1 -= a2;
-      if (c0i == t3) p0 -= a3;
-      if (c1i == t3) p1 -= a3;
-      g[2 * t] = p0 * (1.0f - tt.x * tt.x);
-      g[2 * t + 1] = p1 * (1.0f - tt.y * tt.y);
-    }
-    uint4 o;
-    o.x = pack_bf16(g[0], g[1]); o.y = pack_bf16(g[2], g[3]); o.z = pack_bf16(g[4], g[5]); o.w = pack_bf16(g[6], g[7]);
-    *reinterpret_cast<uint4*>(d + c) = o;
-  }
+  if (owner) ce_row_grad<true>(th, d, V, k2, lw, w_uni, tgi, w_tgt, t2i, a2, t3i, a3);
+  else ce_row_grad<false>(th, d, V, k2, lw, w_uni, tgi, w_tgt, t2i, a2, t3i, a3);
   for (int c = V + threadIdx.x; c < ldl; c += blockDim.x) d[c] = __float2bfloat16(0.f);
 }
 
@@ -813,8 +840,12 @@ int bones_softcap_ce(const void* logits, long long ldl, const long long* targets
   aux.tg[0] = tg2; aux.w[0] = w2; aux.tg[1] = tg3; aux.w[1] = w3; aux.nll_aux = nll_aux;
   aux.smooth = label_smoothing;
   if (V <= 65536 && V >= 8192) {
-    softcap_ce_row_kernel<<<M, 1024, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, ldl, targets, V, cap, nll,
-                                                                (__nv_bfloat16*)dlogits, row_w, n_valid, inv_loss_div, M, capped, aux);
+    if (capped)
+      softcap_ce_row_kernel<true><<<M, 1024, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, ldl, targets, V, cap, nll,
+                                                                        (__nv_bfloat16*)dlogits, row_w, n_valid, inv_loss_div, M, aux);
+    else
+      softcap_ce_row_kernel<false><<<M, 1024, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, ldl, targets, V, cap, nll,
+                                                                         (__nv_bfloat16*)dlogits, row_w, n_valid, inv_loss_div, M, aux);
     return (int)cudaGetLastError();
   }
   softcap_ce_kernel<<<M, 512, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, ldl, targets, V, cap, nll, (__nv_bfloat16*)dlogits,
