@@ -481,3 +481,41 @@ def test_background_checkpoint_write(tmp_path):
     bg.submit(str(tmp_path / "no_such_dir" / "x" / ".." / ".." / "f\0.pt"), dict(a=1))
     with pytest.raises(RuntimeError):
         bg.wait()
+
+
+@pytest.mark.parametrize("bits", [1, 4])
+def test_packed_table_views_train_straight_through_and_round_trip(tmp_path, bits):
+    from them_bones_b200.utils import ckpt as CK
+    m = torch.randn(5, 32) * 0.3
+    m[1] = 0
+    v = RF.table_view(m, bits)
+    assert float(v[1].abs().sum()) == 0 and torch.equal(RF.table_view(v, bits), v)          # zero stays zero; idempotent
+    if bits == 1:
+        assert torch.allclose(v.abs()[0], m[0].abs().mean().bfloat16().float().expand(32)) and torch.equal(v.sign()[0], torch.where(m[0] < 0, -1.0, 1.0))
+    else:
+        assert float((v - m).abs().max()) <= float(m.abs().amax()) / 7 * 0.51 + 1e-3 and len(torch.unique(v[0])) <= 15
+    pk, sc = RF.table_pack_view(m, bits)
+    assert pk.dtype == torch.uint8 and pk.shape == (5, 32 * bits // 8) and sc.dtype == torch.bfloat16
+    assert torch.allclose(RF.table_unpack_view(pk, sc, bits), v, atol=1e-6)
+    # both kinds of table read their views in training, learn through them, and save them packed
+    kw = dict(n_layer=1, n_embd=64, n_head=2, vocab_size=512, sequence_len=64)
+    cfg = tiny_cfg(table_orders=(2,), table_rows=1 << 10, table_bits=bits, os1_rows=1 << 10, os1_order=2, os1_dim=32,
+                   os1_bits=1, **kw)
+    hy = Hyper()
+    hy.total_batch, hy.device_batch = 4 * 64, 4
+    tr = Trainer(cfg, hy, RT, optimizer_kind="lean", horizon_steps=10)
+    x, y = SynthLoader(512, 64, 4, seed=0, doc_len=(16, 64)).next_step()
+    losses = [float(tr.train_step(x.long(), y)) for _ in range(6)]
+    assert losses[-1] < losses[0] - 0.5
+    assert float(tr.tables.shards[0].abs().sum()) > 0 and float(tr.os1.shard.abs().sum()) > 0
+    path = str(tmp_path / "views.pt")
+    CK.save_checkpoint(path, tr.model, dict(steps=6), tables=tr.tables)
+    raw = torch.load(path, weights_only=True)["model_state"]
+    assert raw["table_2"].dtype == torch.uint8 and raw["table_2"].shape == (1 << 10, 64 * bits // 8)
+    assert raw["os1_table"].dtype == torch.uint8 and raw["os1_table"].shape == (1 << 10, 4)
+    model, _ = CK.load_for_eval(path, "cpu")
+    assert model.tables.rows_are_views and model.os1.rows_are_views
+    tr.model.eval()
+    with torch.no_grad():
+        a, b = model(x[:2].long()), tr.model(x[:2].long())
+    assert torch.allclose(a, b, atol=2e-4)                        # the scored forward is the trained forward

@@ -95,6 +95,7 @@ class GPTConfig:
     table_orders: tuple = ()       # hashed n-gram input tables, e.g. (2, 3)
     table_rows: int = 0            # rows per table (power of two)
     table_seed: int = 0
+    table_bits: int = 0            # 1 or 4: every read takes a packed view of the row (0: the row itself)
     # output-side hashed table (0 rows: off): keyed by the os1_order ids ending at a position; its sign-hashed row is read
     # out through a fixed codebook and added to the logits before the soft-cap (reference: switch 59,
     # round2/source/train.py:2310-2351; the defaults below are the reference's)
@@ -111,6 +112,7 @@ class GPTConfig:
     os1_gate_slope: float = 30.0
     os1_seed: int = 0
     os1_code_seed: int = 5901
+    os1_bits: int = 0              # 1: every read takes the row's 1-bit view sign(m) * mean|m|
 
     def __post_init__(self):
         for name in ("attn_long", "moe_layers", "table_orders", "attn_layers", "mtp_offsets"):
@@ -130,6 +132,10 @@ class GPTConfig:
                 raise ValueError("MoE layers need moe_experts, moe_topk in {1,2}, moe_capacity and moe_hidden")
         if self.table_orders and (self.table_rows & (self.table_rows - 1) or self.table_rows <= 0):
             raise ValueError("table_rows must be a positive power of two")
+        if self.table_bits not in (0, 1, 4) or self.os1_bits not in (0, 1):
+            raise ValueError("table_bits is 0, 1 or 4 and os1_bits 0 or 1")
+        if (self.table_bits and self.n_embd % 8) or (self.os1_bits and self.os1_dim % 8):
+            raise ValueError("packed views need a row width that is a multiple of 8")
         if self.os1_rows and (self.os1_rows & (self.os1_rows - 1) or self.os1_dim % 32 or self.os1_dim > 256):
             raise ValueError("os1_rows must be a power of two and os1_dim a multiple of 32 up to 256")
 
@@ -238,7 +244,7 @@ def switches(refresh: bool = False) -> dict:
         MOE=e("MOE", False, bool), MOE_LAYERS=e("MOE_LAYERS", "", str), MOE_EXPERTS=e("MOE_EXPERTS", 16, int),
         MOE_TOPK=e("MOE_TOPK", 2, int), MOE_HIDDEN=e("MOE_HIDDEN", 0, int), MOE_SHARED=e("MOE_SHARED", 0, int),
         MOE_AUX=e("MOE_AUX", 0.01, float), MOE_ZLOSS=e("MOE_ZLOSS", 0.0, float),
-        TABLES=e("TABLES", "", str), TABLE_ROWS=e("TABLE_ROWS", 0, int), TABLE_SEED=e("TABLE_SEED", 0, int),
+        TABLES=e("TABLES", "", str), TABLE_ROWS=e("TABLE_ROWS", 0, int), TABLE_SEED=e("TABLE_SEED", 0, int), TABLE_BITS=e("TABLE_BITS", 0, int), OS1_BITS=e("OS1_BITS", 0, int),
         TABLE_HOST_STATE=e("TABLE_HOST_STATE", "auto", str),   # auto | 0 | 1: Adam moments of the tables in pinned host memory
         OS1=e("OS1", False, bool), OS1_ROWS=e("OS1_ROWS", 1 << 24, int), OS1_ORDER=e("OS1_ORDER", 16, int),
         OS1_LR=e("OS1_LR", 0.125, float), OS1_SEED=e("OS1_SEED", 0, int),
@@ -309,9 +315,9 @@ def build_config(depth: int, n_embd: int, n_head: int, seq_len: int, vocab: int,
                   moe_zloss=s["MOE_ZLOSS"])
     if s["TABLES"]:
         kw.update(table_orders=_env(PREFIX + "TABLES", (), tuple), table_rows=s["TABLE_ROWS"] or (1 << 20),
-                  table_seed=s["TABLE_SEED"])
+                  table_seed=s["TABLE_SEED"], table_bits=s["TABLE_BITS"])
     if s["OS1"]:
-        kw.update(os1_rows=s["OS1_ROWS"], os1_order=s["OS1_ORDER"], os1_lr=s["OS1_LR"], os1_seed=s["OS1_SEED"])
+        kw.update(os1_rows=s["OS1_ROWS"], os1_order=s["OS1_ORDER"], os1_lr=s["OS1_LR"], os1_seed=s["OS1_SEED"], os1_bits=s["OS1_BITS"])
     return GPTConfig(**kw)
 
 

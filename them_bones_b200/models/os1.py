@@ -35,6 +35,8 @@ class _ReadFn(torch.autograd.Function):
         u = torch.zeros(n_total, table.dim, dtype=dtype, device=ids.device)
         if ids.numel():
             rows = table.exchange.lookup(table.shard, ids, table.world)
+            if table.bits and not table.rows_are_views:
+                rows = RF.table_view(rows, table.bits)        # straight-through: backward hands d(u) to the master
             u[pos] = ops.os1_apply_signs(rows.to(dtype), hsign)
         return u
 
@@ -61,6 +63,7 @@ class OutputTable:
         self.code = RF.os1_codebook(config.padded_vocab, dim, config.os1_code_seed).to(self.device, dtype)
         self.a0 = config.os1_a0 * config.os1_lr
         self.lr, self.cap, self.eps_rel = config.os1_lr, cap, eps_rel
+        self.bits, self.rows_are_views = config.os1_bits, False   # 1-bit view (reference: R2_OS1_BITS, :2371-2390)
         self.pending = []
         self._anchor = torch.zeros((), requires_grad=True)
         from ..parallel import table_a2a
@@ -126,12 +129,19 @@ class OutputTable:
         """This rank's share as int8 rows with a bf16 row scale (reference: ``os1_table`` / ``os1_scale`` in
         ``model_state``, round2/source/train.py:2339-2341)."""
         t = self.shard.detach().float().cpu()
+        if self.bits:
+            packed, scale = RF.table_pack_view(t, self.bits)
+            return {"os1_table": packed, "os1_scale": scale}
         scale = (t.abs().amax(1, keepdim=True) / 127.0).clamp_min(1e-12).to(torch.bfloat16)
         q = torch.round(t / scale.float()).clamp(-127, 127).to(torch.int8)
         return {"os1_table": q, "os1_scale": scale}
 
     def load_share(self, state: dict):
-        t = state["os1_table"].float() * state["os1_scale"].float()
+        if state["os1_table"].dtype == torch.uint8:
+            t = RF.table_unpack_view(state["os1_table"], state["os1_scale"], self.bits)
+            self.rows_are_views = True
+        else:
+            t = state["os1_table"].float() * state["os1_scale"].float()
         if t.shape[0] == self.rows and self.world > 1:
             t = t[self.rank::self.world]
         self.shard.copy_(t.to(self.dtype))

@@ -41,12 +41,16 @@ class _LookupFn(torch.autograd.Function):
 class HashedTables:
     def __init__(self, orders, rows: int, dim: int, *, seed: int = 0, device="cpu", dtype=torch.float32,
                  group=None, world: int = 1, rank: int = 0, host_state: bool = False,
-                 betas=(0.9, 0.99), eps: float = 1e-8, decay: float = 0.0, exchange=None):
+                 betas=(0.9, 0.99), eps: float = 1e-8, decay: float = 0.0, exchange=None, bits: int = 0):
         if rows % world:
             raise ValueError("table rows must divide over the ranks")
         self.orders, self.rows, self.dim, self.seed = tuple(orders), rows, dim, seed
         self.group, self.world, self.rank = group, world, rank
         self.device, self.dtype = torch.device(device), dtype
+        # bits 1 / 4: every read (training and scoring alike) takes the row's packed view, the gradient goes straight
+        # through to the master row, and the checkpoint stores the view (reference: R2_NGRAM_BITS,
+        # round2/source/train.py:1016-1029).  rows_are_views: the shards were loaded from such a checkpoint.
+        self.bits, self.rows_are_views = bits, False
         self.local_rows = rows // world
         self.shards = [torch.zeros(self.local_rows, dim, dtype=dtype, device=self.device) for _ in self.orders]
         # Adam moments: on the device while they fit (two fp32 copies of the shard per table), else in pinned host memory
@@ -84,7 +88,8 @@ class HashedTables:
 
     def gather(self, order_slot: int, ids: torch.Tensor) -> torch.Tensor:
         """Rows for global ids ``[n]`` -> ``[n, dim]`` (all-to-all with the owners when sharded)."""
-        return self.exchange.lookup(self.shards[order_slot], ids, self.world)
+        rows = self.exchange.lookup(self.shards[order_slot], ids, self.world)
+        return RF.table_view(rows, self.bits) if (self.bits and not self.rows_are_views) else rows
 
     def add_lookup(self, x, idx, doc_start, gains, rows=None):
         ids = self.ids(idx, doc_start) if rows is None else rows
@@ -162,7 +167,9 @@ class HashedTables:
         out = {}
         for j, o in enumerate(self.orders):
             t = self.shards[j].detach().cpu()
-            if quantize:
+            if self.bits:
+                out[f"table_{o}"], out[f"table_{o}_scale"] = RF.table_pack_view(t, self.bits)
+            elif quantize:
                 scale = (t.float().abs().amax(1, keepdim=True) / 127.0).clamp_min(1e-12)
                 out[f"table_{o}"] = torch.round(t.float() / scale).clamp(-127, 127).to(torch.int8)
                 out[f"table_{o}_scale"] = scale.to(torch.bfloat16)
@@ -173,7 +180,10 @@ class HashedTables:
     def load_share(self, state: dict):
         for j, o in enumerate(self.orders):
             t = state[f"table_{o}"]
-            if t.dtype == torch.int8:
+            if t.dtype == torch.uint8:
+                t = RF.table_unpack_view(t, state[f"table_{o}_scale"], self.bits)
+                self.rows_are_views = True
+            elif t.dtype == torch.int8:
                 t = t.float() * state[f"table_{o}_scale"].float()
             if t.shape[0] == self.rows and self.world > 1:
                 t = t[self.rank::self.world]

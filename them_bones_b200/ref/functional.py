@@ -452,3 +452,73 @@ def softcap_cross_entropy_os1(x, w, targets, vocab, cap, u, code, gate, *, a0, g
         return (nll * weights.reshape(-1).float()).sum()
     out = F.cross_entropy(flat, tgt, ignore_index=-1, reduction=reduction)
     return out.view_as(targets) if reduction == "none" else out
+
+
+# ----------------------------------------------------------------------------------------------------------------
+# Packed views of table rows: the forward reads a 1-bit or 4-bit view of the master row, the gradient goes straight
+# through to the master, and the checkpoint stores the view itself
+# (reference: R2_NGRAM_BITS, round2/source/train.py:1016-1029; R2_OS1_BITS, :2371-2390 and helpers :2692-2732)
+# ----------------------------------------------------------------------------------------------------------------
+
+def _bf16_round_up(x: torch.Tensor) -> torch.Tensor:
+    """Positive fp32 values to the nearest bf16 value that is not below them."""
+    b = x.to(torch.bfloat16)
+    low = b.float() < x
+    bumped = (b.view(torch.int16) + 1).view(torch.bfloat16)
+    return torch.where(low, bumped, b)
+
+
+def table_view_scale(rows: torch.Tensor, bits: int) -> torch.Tensor:
+    """Per-row scale ``[n, 1]`` (bf16-representable fp32) of the ``bits``-bit view: the mean ``|value|`` (1 bit) or
+    ``max |value| / 7`` rounded up to bf16 (4 bits)."""
+    m = rows.float()
+    if bits == 1:
+        return m.abs().mean(1, keepdim=True).to(torch.bfloat16).float()
+    if bits == 4:
+        return _bf16_round_up(m.abs().amax(1, keepdim=True) / 7.0).float()
+    raise ValueError(f"view bits {bits}: 1 or 4")
+
+
+def table_view(rows: torch.Tensor, bits: int) -> torch.Tensor:
+    """The view the forward reads, in the rows' dtype: ``sign(m) * s`` with ``sign(0) = +1`` (1 bit) or
+    ``round(m / s) * s`` with levels -7..7 (4 bits); a zero row reads zero either way."""
+    if bits == 0:
+        return rows
+    m, s = rows.float(), table_view_scale(rows, bits)
+    if bits == 1:
+        v = torch.where(m < 0, -s, s)
+    else:
+        v = torch.round(m / s.clamp_min(1e-30)).clamp(-7, 7) * s
+    return v.to(rows.dtype)
+
+
+def table_pack_view(rows: torch.Tensor, bits: int):
+    """``(packed uint8 [n, dim * bits / 8], scale bf16 [n])`` of the view.  1 bit: sign bits eight to a byte along the
+    width, bit k of byte j = column 8 j + k, 1 = negative.  4 bits: two levels to a byte, column 2 j in the low nibble,
+    4-bit two's complement."""
+    m, s = rows.float(), table_view_scale(rows, bits)
+    n, dim = m.shape
+    if bits == 1:
+        neg = (m < 0).to(torch.uint8).view(n, dim // 8, 8)
+        w = (1 << torch.arange(8, device=m.device)).to(torch.uint8)
+        packed = (neg * w).sum(-1).to(torch.uint8)
+    else:
+        q = torch.round(m / s.clamp_min(1e-30)).clamp(-7, 7).to(torch.int16) & 0xF
+        q = q.view(n, dim // 2, 2)
+        packed = (q[..., 0] | (q[..., 1] << 4)).to(torch.uint8)
+    return packed, s.reshape(n).to(torch.bfloat16)
+
+
+def table_unpack_view(packed: torch.Tensor, scale: torch.Tensor, bits: int) -> torch.Tensor:
+    """Inverse of ``table_pack_view``: the view's rows, fp32 ``[n, dim]``."""
+    n = packed.shape[0]
+    s = scale.float().reshape(n, 1)
+    p = packed.to(torch.int16)
+    if bits == 1:
+        sh = torch.arange(8, device=packed.device)
+        neg = ((p[..., None] >> sh) & 1).reshape(n, -1).bool()
+        return torch.where(neg, -s, s)
+    lo, hi = p & 0xF, (p >> 4) & 0xF
+    q = torch.stack([lo, hi], -1).reshape(n, -1)
+    q = torch.where(q >= 8, q - 16, q).float()
+    return q * s

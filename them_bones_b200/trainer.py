@@ -55,7 +55,7 @@ class Trainer:
             setup_optimizer(model, hyper, kind=kind)
         self.tables = None
         if config.table_orders:
-            self.tables = HashedTables(config.table_orders, config.table_rows, config.n_embd, seed=config.table_seed,
+            self.tables = HashedTables(config.table_orders, config.table_rows, config.n_embd, seed=config.table_seed, bits=config.table_bits,
                                        device=rt.device, dtype=self.dtype, group=dist.group.WORLD if rt.ddp else None,
                                        world=rt.world, rank=rt.rank, host_state=("auto" if sw["TABLE_HOST_STATE"] == "auto"
                                                    else sw["TABLE_HOST_STATE"].lower() in ("1", "true")))

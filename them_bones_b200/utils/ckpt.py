@@ -161,7 +161,7 @@ def load_for_eval(path: str, device="cpu", dtype=None):
     model = model.to(device)
     model.cast_compute(dtype)
     if config.table_orders:
-        tables = HashedTables(config.table_orders, config.table_rows, config.n_embd, seed=config.table_seed,
+        tables = HashedTables(config.table_orders, config.table_rows, config.n_embd, seed=config.table_seed, bits=config.table_bits,
                               device=device, dtype=dtype)
         tables.load_share(table_state)
         model.attach_tables(tables)
