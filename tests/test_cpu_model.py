@@ -519,3 +519,28 @@ def test_packed_table_views_train_straight_through_and_round_trip(tmp_path, bits
     with torch.no_grad():
         a, b = model(x[:2].long()), tr.model(x[:2].long())
     assert torch.allclose(a, b, atol=2e-4)                        # the scored forward is the trained forward
+
+
+def test_grad_clip_and_bf16_stochastic_masters(monkeypatch):
+    from them_bones_b200 import config as C
+    # stochastic rounding is unbiased and lands on the two neighbouring bf16 values
+    x = torch.full((200000,), 1.0 + 2.0 ** -10)
+    y = RF.stochastic_round_bf16(x, torch.Generator().manual_seed(0)).float()
+    assert set(y.unique().tolist()) == {1.0, 1.0 + 2.0 ** -7} and abs(float(y.mean()) - float(x[0])) < 2e-5
+    assert torch.equal(RF.stochastic_round_bf16(torch.tensor([0.5, -2.0, float("inf")])).float(), torch.tensor([0.5, -2.0, float("inf")]))
+    cfg = tiny_cfg(n_layer=2, n_embd=64, n_head=2, vocab_size=512, sequence_len=64)
+    base = run_steps(cfg, "lean", steps=6, seq=64, batch=4)[1]
+    monkeypatch.setenv("BONES_GRAD_CLIP", "0.05")
+    C.switches(refresh=True)
+    tr, clipped = run_steps(cfg, "lean", steps=6, seq=64, batch=4)
+    assert float(tr.optimizer.last_grad_norm) > 0.05                      # the clip was active ...
+    assert clipped[0] == pytest.approx(base[0], abs=1e-5) and clipped[-1] < clipped[0]
+    assert any(abs(a - b) > 1e-4 for a, b in zip(base[1:], clipped[1:]))      # ... and changed the AdamW groups' steps
+    monkeypatch.delenv("BONES_GRAD_CLIP")
+    monkeypatch.setenv("BONES_MASTER", "bf16")
+    C.switches(refresh=True)
+    tr, lossy = run_steps(cfg, "lean", steps=6, seq=64, batch=4)
+    assert tr.optimizer.muon_units[0].master.dtype == torch.bfloat16
+    assert all(abs(a - b) < 0.05 for a, b in zip(base, lossy)) and lossy[-1] < lossy[0] - 0.1
+    monkeypatch.delenv("BONES_MASTER")
+    C.switches(refresh=True)

@@ -260,6 +260,8 @@ def switches(refresh: bool = False) -> dict:
         FUSED_COMM=e("FUSED_COMM", True, bool),      # in-kernel NVLink collectives (False: NCCL baseline path)
         WGRAD_PUSH=e("WGRAD_PUSH", False, bool),     # weight-gradient GEMMs reduce-scatter their tiles into the owner's slab
         LOSS_ROWS=e("LOSS_ROWS", 4096, int),         # rows per block of the chunked loss head (one [rows, V] logits buffer)
+        GRAD_CLIP=e("GRAD_CLIP", 0.0, float),        # > 0: global-norm clip of the reduced gradients (library-collective path)
+        MASTER=e("MASTER", "fp32", str),             # fp32 | bf16: Muon master copies (bf16 = stochastic rounding)
         OPT=e("OPT", "lean", str),                   # lean | dist | single
         OPT_OVERLAP_CHECK=e("OPT_OVERLAP_CHECK", False, bool),
         FINITE_GATE=e("FINITE_GATE", True, bool),

@@ -69,7 +69,7 @@ class _MuonUnit:
     """One shape group: weight slab ``W [n_pad, r, c]`` (replica dtype), gradient slab ``G`` (fp32), owner state for
     ``k = n_pad / world`` matrices."""
 
-    def __init__(self, group, params, comm, replica_dtype):
+    def __init__(self, group, params, comm, replica_dtype, master_dtype=torch.float32):
         p0 = params[0]
         self.group, self.params = group, params
         self.n, (self.r, self.c) = len(params), p0.shape
@@ -82,7 +82,7 @@ class _MuonUnit:
         full32 = torch.zeros(self.n_pad, self.r, self.c, dtype=torch.float32, device=dev)
         for i, p in enumerate(params):
             full32[i].copy_(p.detach())
-        self.master = full32[own].clone()
+        self.master = full32[own].clone().to(master_dtype)     # bf16: updated with stochastic rounding
         self.W.copy_(full32)
         del full32
         for i, p in enumerate(params):
@@ -114,8 +114,17 @@ class _RowUnit:
 
 class LeanDistMuonAdamW(torch.optim.Optimizer):
     def __init__(self, param_groups, group=None, comm=None, replica_dtype=None, ns_dtype=None, finite_gate=True,
-                 overlap_check=False):
+                 overlap_check=False, grad_clip: float = 0.0, bf16_master: bool = False):
         super().__init__(param_groups, defaults={})
+        # grad_clip > 0: the reduced gradients are scaled so their global norm does not exceed it (reference: the
+        # optional clip of ``GradReducer``, round1/source/train.py:9971-10080).  bf16_master: the Muon matrices' master
+        # copies are bf16, written back with stochastic rounding (reference: round1/source/train.py:10219-10226).
+        # Both are features of the library-collective path; the fused peer-memory path applies its update inside the
+        # reduction kernel and refuses them.
+        self.grad_clip, self.bf16_master = float(grad_clip), bool(bf16_master)
+        if (self.grad_clip > 0 or self.bf16_master) and getattr(comm, "fused", False):
+            raise ValueError("grad_clip / bf16_master need the library-collective optimizer path (BONES_FUSED_COMM=0)")
+        self.last_grad_norm = None
         self.comm = comm or TorchComm(group)
         self.world, self.rank = self.comm.world, self.comm.rank
         self.finite_gate = finite_gate
@@ -142,7 +151,7 @@ class LeanDistMuonAdamW(torch.optim.Optimizer):
                 for p in ps:
                     p.main_grad = torch.zeros_like(p, dtype=torch.float32)
             elif g["kind"] == "muon":
-                self.muon_units.append(_MuonUnit(g, ps, comm, rd))
+                self.muon_units.append(_MuonUnit(g, ps, comm, rd, torch.bfloat16 if self.bf16_master else torch.float32))
             else:
                 for p in ps:
                     if p.numel() >= 1024 and p.dim() >= 2 and p.shape[0] % comm.world == 0:
@@ -254,7 +263,22 @@ class LeanDistMuonAdamW(torch.optim.Optimizer):
             muon_g = [torch.where(okb, t, torch.zeros_like(t)) for t in muon_g]
             self.SG.copy_(torch.where(okb, self.SG, torch.zeros_like(self.SG)))
             self._last_ok = ok
-        # 5: updates on the owners' fp32 masters
+        # 4b: global-norm clip.  Every rank holds its own shards of the reduced gradients and all of the small ones.
+        if self.grad_clip > 0:
+            sq = torch.zeros((), dtype=torch.float32, device=self.SG.device)
+            for t in row_g + muon_g:
+                sq = sq + t.float().square().sum()
+            if self.world > 1:
+                sq = sq.reshape(1)
+                torch.distributed.all_reduce(sq, group=getattr(comm, "group", None))
+                sq = sq[0]
+            norm = (sq + self.SG.float().square().sum()).sqrt()
+            scale = torch.clamp(self.grad_clip / norm.clamp_min(1e-12), max=1.0)
+            row_g = [t * scale for t in row_g]
+            muon_g = [t * scale for t in muon_g]
+            self.SG.mul_(scale)
+            self.last_grad_norm = norm
+        # 5: updates on the owners' masters
         self._small_step()
         for u, g in zip(self.row_units, row_g):
             b1, b2 = u.group["betas"]
@@ -263,9 +287,12 @@ class LeanDistMuonAdamW(torch.optim.Optimizer):
             comm.all_gather(u.W, u.master.to(u.W.dtype))
         for u, g in zip(self.muon_units, muon_g):
             grp = u.group
-            RF.muon_update(g, u.master, u.momentum, u.second, momentum=grp["momentum"], beta2=grp["beta2"],
+            master = u.master.float() if self.bf16_master else u.master
+            RF.muon_update(g, master, u.momentum, u.second, momentum=grp["momentum"], beta2=grp["beta2"],
                            lr=grp["lr"], wd=grp["weight_decay"], ns_steps=grp["ns_steps"], ns_dtype=self._ns(u.W),
                            ns_fn=self._ns_fn(u.W))
+            if self.bf16_master:
+                u.master.copy_(RF.stochastic_round_bf16(master))
             comm.all_gather(u.W, u.master.to(u.W.dtype))
         # 5b: local experts
         self._local.step(1.0 / self.world)

@@ -522,3 +522,13 @@ def table_unpack_view(packed: torch.Tensor, scale: torch.Tensor, bits: int) -> t
     q = torch.stack([lo, hi], -1).reshape(n, -1)
     q = torch.where(q >= 8, q - 16, q).float()
     return q * s
+
+
+def stochastic_round_bf16(x: torch.Tensor, generator=None) -> torch.Tensor:
+    """fp32 -> bf16 with stochastic rounding: a uniform 16-bit integer is added to the low half of the fp32 pattern
+    before truncation, so the expected value of the result is ``x`` (the reference's bf16 master weights rely on the
+    accelerator runtime's stochastic rounding, round1/source/train.py:10219-10226)."""
+    bits = x.contiguous().view(torch.int32)
+    r = torch.randint(0, 1 << 16, bits.shape, dtype=torch.int32, device=x.device, generator=generator)
+    out = ((bits + r) & -65536).view(torch.float32)
+    return torch.where(torch.isfinite(x), out, x).to(torch.bfloat16)

@@ -46,12 +46,15 @@ class Trainer:
         self.model = model
         self.comm = None
         use_fused = sw["FUSED_COMM"] if fused_comm is None else fused_comm
+        extras = dict(grad_clip=sw["GRAD_CLIP"], bf16_master=sw["MASTER"] == "bf16")
+        if extras["grad_clip"] > 0 or extras["bf16_master"]:
+            use_fused = False                     # both live on the library-collective optimizer path
         if use_fused and rt.device_type == "cuda" and rt.world > 1 and not ops.reference_path():
             from .parallel import symm
             self.comm = symm.PeerComm.create(rt)
         kind = optimizer_kind or sw["OPT"]
         self.optimizer = setup_optimizer(model, hyper, kind=kind, comm=self.comm, finite_gate=sw["FINITE_GATE"],
-                                         overlap_check=sw["OPT_OVERLAP_CHECK"]) if kind == "lean" else \
+                                         overlap_check=sw["OPT_OVERLAP_CHECK"], **extras) if kind == "lean" else \
             setup_optimizer(model, hyper, kind=kind)
         self.tables = None
         if config.table_orders:
