@@ -121,3 +121,24 @@ def test_model_with_output_table_trains_like_the_reference_path():
     assert native[-1] < native[0] - 1.0
     for a, b in zip(native, refp):
         assert abs(a - b) < 0.03 * abs(b), (native, refp)
+
+
+def test_packed_views_and_stochastic_rounding_on_device():
+    from them_bones_b200.ref import functional as RF
+    torch.manual_seed(0)
+    m = (torch.randn(64, 128) * 0.3).bfloat16()
+    m[3] = 0
+    for bits in (1, 4):
+        md = m.cuda()
+        dev = RF.table_view(md, bits)
+        assert dev.dtype == torch.bfloat16 and float(dev[3].abs().sum()) == 0
+        # reductions run in another order on the device: the scale may differ from the CPU's by one bf16 step
+        assert torch.allclose(dev.cpu().float(), RF.table_view(m, bits).float(), rtol=1e-2, atol=1e-3)
+        pk, sc = RF.table_pack_view(md, bits)
+        assert pk.dtype == torch.uint8 and pk.shape == (64, 128 * bits // 8)
+        assert torch.allclose(RF.table_unpack_view(pk, sc, bits), dev.float(), rtol=4e-3, atol=1e-6)   # packed = the view
+        if bits == 1:
+            assert torch.equal(pk.cpu(), RF.table_pack_view(m, bits)[0])
+    x = torch.full((1 << 20,), 1.0 + 2.0 ** -10, device="cuda")
+    y = RF.stochastic_round_bf16(x).float()
+    assert set(y.unique().tolist()) == {1.0, 1.0 + 2.0 ** -7} and abs(float(y.mean()) - float(x[0])) < 5e-5

@@ -461,9 +461,10 @@ def softcap_cross_entropy_os1(x, w, targets, vocab, cap, u, code, gate, *, a0, g
 # ----------------------------------------------------------------------------------------------------------------
 
 def _bf16_round_up(x: torch.Tensor) -> torch.Tensor:
-    """Positive fp32 values to the nearest bf16 value that is not below them."""
+    """Positive fp64 values to the nearest bf16 value that is not below them (up to a 1e-12 relative slack, so that a
+    value that is a bf16 number up to the last bits of its fp64 computation maps to itself on every device)."""
     b = x.to(torch.bfloat16)
-    low = b.float() < x
+    low = b.double() < x * (1.0 - 1e-12)
     bumped = (b.view(torch.int16) + 1).view(torch.bfloat16)
     return torch.where(low, bumped, b)
 
@@ -475,7 +476,9 @@ def table_view_scale(rows: torch.Tensor, bits: int) -> torch.Tensor:
     if bits == 1:
         return m.abs().mean(1, keepdim=True).to(torch.bfloat16).float()
     if bits == 4:
-        return _bf16_round_up(m.abs().amax(1, keepdim=True) / 7.0).float()
+        # in fp64: a back end may turn the division by a constant into a multiplication, and the scale must come out
+        # the same on every device and map a view onto itself
+        return _bf16_round_up(m.abs().amax(1, keepdim=True).double() / 7.0).float()
     raise ValueError(f"view bits {bits}: 1 or 4")
 
 
