@@ -212,3 +212,51 @@ def test_first_call_selfcheck_passes_and_reports():
     from them_bones_b200.ops.selfcheck import run
     out = run("cuda")
     assert len(out) >= 15 and max(out.values()) < 5e-2
+
+
+def test_single_gpu_fused_optimizer_matches_library_path():
+    """World size 1: the fused reduce + update kernels (one 'peer') against the PyTorch statement of the same step."""
+    from them_bones_b200.config import GPTConfig, Hyper
+    from them_bones_b200.data.synth import SynthLoader
+    from them_bones_b200.ops import _lib as L
+    from them_bones_b200.runtime import Runtime
+    from them_bones_b200.trainer import Trainer
+    cfg = GPTConfig(sequence_len=256, vocab_size=8192, n_layer=2, n_head=2, n_embd=256, head_dim=128, doc_mask=True)
+    rt = Runtime(False, 0, 0, 1, torch.device("cuda", 0), "cuda")
+
+    def run(fused):
+        h = Hyper()
+        h.total_batch, h.device_batch = 8 * 256, 4
+        tr = Trainer(cfg, h, rt, optimizer_kind="lean", horizon_steps=10, fused_comm=fused)
+        assert (type(tr.comm).__name__ == "SoloComm") == fused
+        ld = SynthLoader(cfg.vocab_size, 256, tr.local_windows, seed=0, doc_len=(64, 256))
+        out = []
+        for _ in range(10):
+            x, y = ld.next_step()
+            out.append(float(tr.train_step(x.long(), y)))
+        return out, tr
+
+    a, tr = run(True)
+    L.check_error_word()
+    assert tr.optimizer.count_bad_steps() == 0
+    b, _ = run(False)
+    assert a[-1] < a[0] - 1.0
+    for x, y in zip(a, b):
+        assert abs(x - y) < 0.02 * abs(y), (a, b)
+
+
+@pytest.mark.parametrize("shape", [(3, 512, 128), (2, 128, 1280), (4, 256, 256)])
+def test_native_muon_finish_matches_pytorch(shape):
+    from them_bones_b200.ops import _lib as L
+    from them_bones_b200.ops import muon_native as MN
+    torch.manual_seed(0)
+    k, r, c = shape
+    g = (torch.randn(k, r, c, device="cuda") * 0.05).bfloat16()
+    w0 = torch.randn(k, r, c, device="cuda") * 0.1
+    s0 = torch.rand((k, r, 1) if r >= c else (k, 1, c), device="cuda") * 1e-3
+    w1, s1, w2, s2 = w0.clone(), s0.clone(), w0.clone(), s0.clone()
+    MN.muon_finish(g, w1, s1, beta2=0.9, lr=0.02, wd=0.05)
+    MN._muon_finish_torch(g, w2, s2, beta2=0.9, lr=0.02, wd=0.05)
+    L.check_error_word()
+    assert _rel(s1, s2) < 1e-5
+    assert _rel(w1 - w0, w2 - w0) < 1e-4

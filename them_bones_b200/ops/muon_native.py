@@ -50,7 +50,33 @@ def newton_schulz(x: torch.Tensor, steps: int = 5) -> torch.Tensor:
 @torch.no_grad()
 def muon_finish(g, w, second, *, beta2, lr, wd):
     """NorMuon second-moment rescale (keeps the Frobenius norm), cautious weight decay and the master update, on the
-    owner's fp32 master ``w [k, r, c]`` (reference: round2/source/train.py:11890-11905)."""
+    owner's fp32 master ``w [k, r, c]`` (reference: round2/source/train.py:11890-11905).  Two native passes over the
+    stack (``csrc/muon.cu``: line statistics, update); the arithmetic on the ``k * r`` or ``k * c`` line values between
+    them is PyTorch."""
+    import ctypes
+    k, r, c = g.shape
+    lr_eff = lr * max(1.0, r / c) ** 0.5
+    by_row = r >= c
+    if not (g.is_cuda and g.dtype == torch.bfloat16 and w.dtype == torch.float32 and c % 2 == 0 and g.is_contiguous()
+            and w.is_contiguous()):
+        return _muon_finish_torch(g, w, second, beta2=beta2, lr=lr, wd=wd)
+    _I, _F = ctypes.c_int, ctypes.c_float
+    v_mean = torch.empty(second.shape, dtype=torch.float32, device=g.device)
+    L.call("bones_muon_linesq", L.ptr(g), L.ptr(v_mean), _I(k), _I(r), _I(c), _I(int(by_row)), L.stream())
+    n_red = c if by_row else r
+    v_norm = (v_mean.sum(dim=(-2, -1), keepdim=True) * n_red).sqrt()
+    second.lerp_(v_mean, 1 - beta2)
+    step_size = second.clamp_min(1e-10).rsqrt()
+    v_norm_new = ((v_mean * n_red) * step_size.square()).sum(dim=(-2, -1), keepdim=True).sqrt()
+    line_scale = (step_size * (v_norm / v_norm_new.clamp_min(1e-10))).contiguous()
+    L.call("bones_muon_apply", L.ptr(g), L.ptr(w), L.ptr(line_scale), _I(k), _I(r), _I(c), _I(int(by_row)), _F(lr_eff),
+           _F(lr_eff * wd), L.stream())
+    COUNTS["muon_finish"] += 1
+    return w
+
+
+@torch.no_grad()
+def _muon_finish_torch(g, w, second, *, beta2, lr, wd):
     r, c = g.shape[-2:]
     lr_eff = lr * max(1.0, r / c) ** 0.5
     red_dim = -1 if r >= c else -2

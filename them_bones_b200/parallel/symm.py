@@ -171,6 +171,49 @@ class PeerComm:
         return PeerTableExchange(self, tables)
 
 
+class SoloComm(PeerComm):
+    """The same fused optimizer kernels on one GPU: the "peer" list is this GPU alone, slabs are ordinary device
+    tensors and the epoch barrier is a no-op.  The reduction kernels then read one gradient slab, apply the Muon
+    prologue / AdamW and write the bf16 replicas in a single pass each, instead of the dozen element-wise passes of the
+    PyTorch statement of the same update."""
+
+    def __init__(self, rt):
+        self.symm_mem, self.rt, self.group = None, rt, None
+        self.world, self.rank, self.device = 1, 0, rt.device
+        self._handles = {}
+        self.epoch = 0
+        self.gsq = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self.launches = 0
+
+    def alloc(self, shape, dtype, device):
+        t = torch.zeros(*shape, dtype=dtype, device=device)
+        self._handles[t.data_ptr()] = (t, None, _ptr_array([t.data_ptr()]))
+        return t
+
+    def peer_addresses(self, t):
+        if t.data_ptr() not in self._handles:
+            raise RuntimeError("tensor is not an allocation of this communicator")
+        return [t.data_ptr()]
+
+    def barrier(self):
+        pass
+
+    def all_reduce_mean(self, t):
+        return t
+
+    def all_reduce_min(self, t):
+        return t
+
+    def cross_check(self, opt) -> int:
+        return 0
+
+    def install_moe(self, model):
+        pass
+
+    def table_exchange(self, tables):
+        return tables.exchange
+
+
 class PeerMoeExchange:
     """Equal-split all-to-all of the slot buffer by peer stores into the destination's receive buffer."""
 
