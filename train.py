@@ -157,8 +157,8 @@ def main(argv=None):
             dt = time.perf_counter() - t_host0
         if shed is not None:
             shed.update(dt * 1e3)
-        if step >= hyper.startup_steps_excluded:
-            dts.append(dt)
+        if step >= hyper.startup_steps_excluded or (args.steps and args.steps <= hyper.startup_steps_excluded and step > 0):
+            dts.append(dt)              # runs shorter than the start-up exclusion report all but their first step
             stop_rule.observe(dt)
         if step == hyper.startup_steps_excluded:
             t_train0 = time.time()
