@@ -7,6 +7,8 @@ document and the layer's window.
 """
 from __future__ import annotations
 
+import ctypes
+
 import torch
 import torch.nn.functional as F
 
@@ -137,6 +139,28 @@ class NativeDecoder:
         b, a = self.tok.shape[0], cfg.n_head * cfg.head_dim
         self.qbuf = torch.empty(b, a, dtype=torch.bfloat16, device=dev)
         self.y = torch.empty(b, a, dtype=torch.bfloat16, device=dev)
+        # With few rows a projection has too few output tiles to pull its weights at memory speed, so its contraction
+        # is split over the SMs into an fp32 accumulator (kept zero between uses by the finishing kernel).
+        self.split = b <= 128 and cfg.mlp_precision == "bf16"
+        if self.split:
+            self.wqkv = [torch.cat([blk.attn.c_q.weight, blk.attn.c_k.weight, blk.attn.c_v.weight]).contiguous()
+                         for blk in model.transformer.h]
+            widest = max([w.shape[0] for w in self.wqkv] + [blk.mlp.c_fc.weight.shape[0] for blk in model.transformer.h]
+                         + [cfg.n_embd])
+            self.acc = torch.zeros(b * widest, dtype=torch.float32, device=dev)
+
+    def _lin(self, x, w, mode=0, residual=None):
+        """``x [b, k] @ w[n, k]^T`` as a split-K GEMM into the fp32 accumulator, then bf16 (mode 0), ReLU^2 (2) or
+        ``+ residual`` (1)."""
+        from ..ops import _lib as L
+        b, k = x.shape
+        n = w.shape[0]
+        acc = self.acc[:b * n].view(b, n)
+        L.gemm(x, w, acc, m=b, n=n, k=k, lda=x.stride(0), ldb=w.stride(0), ldd=n, epi=L.EPI_ACC_F32, force_bn=128,
+               splits=max(1, min(32, k // 256)), pair=False)
+        out = torch.empty(b, n, dtype=torch.bfloat16, device=x.device)
+        L.call("bones_acc_finish", L.ptr(acc), L.ptr(residual), L.ptr(out), ctypes.c_longlong(b * n), ctypes.c_int(mode), L.stream())
+        return out
 
     def _step(self):
         from ..ops import _lib as L
@@ -155,7 +179,7 @@ class NativeDecoder:
                 x = x + model.skip_lambda[i - (n_layer - n_skip)].to(x.dtype) * skips.pop()
             x, xn = ops.resid_mix_norm(x, x0, blk.resid_lambda, blk.x0_lambda)
             at = blk.attn
-            qkv = ops.linear_qkv(xn, at.c_q.weight, at.c_k.weight, at.c_v.weight)
+            qkv = self._lin(xn, self.wqkv[i]) if self.split else ops.linear_qkv(xn, at.c_q.weight, at.c_k.weight, at.c_v.weight)
             ve = lam = None
             if model.value_embeds is not None and str(i) in model.value_embeds:
                 ve = ops.embedding(tok, model.value_embeds[str(i)].weight, torch.bfloat16)
@@ -165,9 +189,14 @@ class NativeDecoder:
             L.call("bones_decode_attn", L.ptr(self.qbuf), L.ptr(cache.k[i]), L.ptr(cache.v[i]), L.ptr(pos),
                    L.ptr(cache.doc_start if cfg.doc_mask else None), L.ptr(self.y), C._I(b), C._I(at.n_head), C._I(tmax),
                    C._F(at.scale), C._I(at.window // 128), L.stream())
-            x = ops.linear(self.y, at.c_proj.weight, residual=x)
-            x, xn = ops.norm_split(x)
-            x = blk.mlp(xn, residual=x)
+            if self.split:
+                x = self._lin(self.y, at.c_proj.weight, 1, x)
+                x, xn = ops.norm_split(x)
+                x = self._lin(self._lin(xn, blk.mlp.c_fc.weight, 2), blk.mlp.c_proj.weight, 1, x)
+            else:
+                x = ops.linear(self.y, at.c_proj.weight, residual=x)
+                x, xn = ops.norm_split(x)
+                x = blk.mlp(xn, residual=x)
             if n_skip and i < n_skip:
                 skips.append(x)
         xn = ops.rms_norm(x)
