@@ -195,23 +195,18 @@ def test_native_decode_step_matches_cached_pytorch_route():
             tok = ref.argmax(-1)
         torch.cuda.synchronize()
         L.check_error_word()
-        # whole decode (stepwise prefill + decode as graph replays) against eager stepping of the same kernels that is
-        # teacher-forced on the decoded tokens: every decoded token is the eager arg-max up to the noise of the split-K
-        # accumulation order (fp32 atomics), which may swap two near-tied logits
+        # whole decode (stepwise prefill + decode as graph replays) reproduces eager stepping of the same kernels bit for
+        # bit: the split projections add their partial products in a fixed order
         full = D.greedy_decode(model, prompts, n_new)
         cc = D.KVCache(model, b, p + n_new)
-        out2 = full.clone()
-        dec2 = D.NativeDecoder(model, cc, prompts[:, 0], out2, prompt_len=p + n_new)
-        worst = 0.0
-        for s in range(p + n_new - 1):
+        out2 = torch.zeros_like(full)
+        out2[:, :p] = prompts
+        dec2 = D.NativeDecoder(model, cc, prompts[:, 0], out2, prompt_len=p)
+        assert dec2.split
+        for _ in range(p + n_new - 1):
             dec2._step()
-            if s + 1 >= p:
-                lg = dec2.last_logits[:, :cfg.vocab_size].float()
-                chosen = lg.gather(1, full[:, s + 1][:, None])[:, 0]
-                worst = max(worst, float((lg.max(-1).values - chosen).max()))
         torch.cuda.synchronize()
-    assert worst < 0.05, worst
-    assert torch.equal(out2, full)                        # forced positions are left as they were
+    assert torch.equal(full, out2)
     assert full.shape == (b, p + n_new) and torch.equal(full[:, :p], prompts)
 
 

@@ -5,7 +5,8 @@
 //   decode_qkv_kernel    RoPE + QK-norm of the new token's q and k, value-embedding add on v; q goes to a scratch
 //                        buffer, k and v are appended to the cache at the current position
 //   acc_finish_kernel    tail of the split-K projections of a decode step (few rows, so the contraction is split over
-//                        the SMs to stream the weights at memory speed): fp32 accumulator -> bf16, ReLU^2 or residual
+//                        the SMs to stream the weights at memory speed): ordered sum of the fp32 slices -> bf16,
+//                        ReLU^2 or residual
 //   decode_attn_kernel   one CTA per (head, sequence): soft-max of q . K over the cached keys of the current document
 //                        (and window), weighted sum of V.  The fixed soft-max shift of the forward kernel applies
 //                        (q and k are RMS-normalised), so no running maximum is kept.
@@ -142,14 +143,18 @@ __global__ void __launch_bounds__(256) decode_attn_kernel(const __nv_bfloat16* _
   }
 }
 
-// Tail of a split-K decode projection: the fp32 accumulator (filled by the GEMM's split-K atomics) becomes the bf16
-// output, optionally through ReLU^2 (mode 2) or plus a bf16 residual (mode 1), and is zeroed for its next use.
-__global__ void acc_finish_kernel(float* __restrict__ acc, const __nv_bfloat16* __restrict__ residual, __nv_bfloat16* __restrict__ out,
-                                  long long n, int mode) {
+// Tail of a split-K decode projection: the GEMM ran as `splits` batched products over K chunks, each writing its own fp32
+// slice; the slices are added in a fixed order (so a decode step is reproducible bit for bit) and become the bf16
+// output, optionally through ReLU^2 (mode 2) or plus a bf16 residual (mode 1).
+__global__ void acc_finish_kernel(const float* __restrict__ part, int splits, long long slice, const __nv_bfloat16* __restrict__ residual,
+                                  __nv_bfloat16* __restrict__ out, long long n, int mode) {
   const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
   if (i >= n) return;
-  float4 v = *reinterpret_cast<const float4*>(acc + i);
-  *reinterpret_cast<float4*>(acc + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 v = *reinterpret_cast<const float4*>(part + i);
+  for (int s = 1; s < splits; ++s) {
+    const float4 u = *reinterpret_cast<const float4*>(part + (long long)s * slice + i);
+    v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
+  }
   if (mode == 2) {
     v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f);
     v.x *= v.x; v.y *= v.y; v.z *= v.z; v.w *= v.w;
@@ -166,10 +171,11 @@ __global__ void acc_finish_kernel(float* __restrict__ acc, const __nv_bfloat16* 
 extern "C" {
 using namespace bones;
 
-int bones_acc_finish(float* acc, const void* residual, void* out, long long n, int mode, void* stream) {
-  if (n % 4 || (mode == 1 && !residual)) return -2;
+int bones_acc_finish(const float* part, int splits, long long slice, const void* residual, void* out, long long n, int mode, void* stream) {
+  if (n % 4 || slice % 4 || splits < 1 || (mode == 1 && !residual)) return -2;
   if (n == 0) return 0;
-  acc_finish_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(acc, (const __nv_bfloat16*)residual, (__nv_bfloat16*)out, n, mode);
+  acc_finish_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(part, splits, slice, (const __nv_bfloat16*)residual,
+                                                                                      (__nv_bfloat16*)out, n, mode);
   return (int)cudaGetLastError();
 }
 

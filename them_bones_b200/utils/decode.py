@@ -140,26 +140,30 @@ class NativeDecoder:
         self.qbuf = torch.empty(b, a, dtype=torch.bfloat16, device=dev)
         self.y = torch.empty(b, a, dtype=torch.bfloat16, device=dev)
         # With few rows a projection has too few output tiles to pull its weights at memory speed, so its contraction
-        # is split over the SMs into an fp32 accumulator (kept zero between uses by the finishing kernel).
-        self.split = b <= 128 and cfg.mlp_precision == "bf16"
+        # runs as a batch of products over K chunks of 256, each into its own fp32 slice, which the finishing kernel
+        # adds in a fixed order (no atomics: a step is reproducible bit for bit).
+        self.split = b <= 128 and cfg.mlp_precision == "bf16" and cfg.n_embd % 256 == 0 and a % 256 == 0
         if self.split:
             self.wqkv = [torch.cat([blk.attn.c_q.weight, blk.attn.c_k.weight, blk.attn.c_v.weight]).contiguous()
                          for blk in model.transformer.h]
-            widest = max([w.shape[0] for w in self.wqkv] + [blk.mlp.c_fc.weight.shape[0] for blk in model.transformer.h]
-                         + [cfg.n_embd])
-            self.acc = torch.zeros(b * widest, dtype=torch.float32, device=dev)
+            ws = self.wqkv + [w for blk in model.transformer.h for w in (blk.attn.c_proj.weight, blk.mlp.c_fc.weight,
+                                                                         blk.mlp.c_proj.weight)]
+            self.split = all(w.shape[1] % 256 == 0 for w in ws)
+            self.part = torch.empty(max(b * w.shape[0] * (w.shape[1] // 256) for w in ws), dtype=torch.float32, device=dev)
 
     def _lin(self, x, w, mode=0, residual=None):
-        """``x [b, k] @ w[n, k]^T`` as a split-K GEMM into the fp32 accumulator, then bf16 (mode 0), ReLU^2 (2) or
-        ``+ residual`` (1)."""
+        """``x [b, k] @ w[n, k]^T`` as ``k / 256`` batched partial products into fp32 slices, then their ordered sum as
+        bf16 (mode 0), through ReLU^2 (2) or ``+ residual`` (1)."""
         from ..ops import _lib as L
         b, k = x.shape
         n = w.shape[0]
-        acc = self.acc[:b * n].view(b, n)
-        L.gemm(x, w, acc, m=b, n=n, k=k, lda=x.stride(0), ldb=w.stride(0), ldd=n, epi=L.EPI_ACC_F32, force_bn=128,
-               splits=max(1, min(32, k // 256)), pair=False)
+        splits = k // 256
+        part = self.part[:splits * b * n]
+        L.gemm(x, w, part, m=b, n=n, k=256, lda=x.stride(0), ldb=w.stride(0), ldd=n, epi=L.EPI_F32, force_bn=128, pair=False,
+               batch=splits, stride_a=256, stride_b=256, stride_d=b * n)
         out = torch.empty(b, n, dtype=torch.bfloat16, device=x.device)
-        L.call("bones_acc_finish", L.ptr(acc), L.ptr(residual), L.ptr(out), ctypes.c_longlong(b * n), ctypes.c_int(mode), L.stream())
+        L.call("bones_acc_finish", L.ptr(part), ctypes.c_int(splits), ctypes.c_longlong(b * n), L.ptr(residual), L.ptr(out),
+               ctypes.c_longlong(b * n), ctypes.c_int(mode), L.stream())
         return out
 
     def _step(self):
