@@ -90,7 +90,8 @@ def parse():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torch"])
-    ap.add_argument("--device-batch", type=int, default=int(os.environ.get("BONES_DEVICE_BATCH", 32)))
+    ap.add_argument("--device-batch", type=int, default=int(os.environ.get("BONES_DEVICE_BATCH", 64)),
+                    help="sequences per micro-step per GPU (clamped to the rank's share of the global batch)")
     ap.add_argument("--total-batch", type=int, default=524288)
     ap.add_argument("--depth", type=int, default=20)
     ap.add_argument("--mlp", default=os.environ.get("BONES_MLP", "bf16"))
@@ -115,7 +116,12 @@ def run_ours(args, torch_path: bool = False):
     cfg = GPTConfig(sequence_len=2048, vocab_size=65536, n_layer=args.depth, n_head=10, n_embd=1280, head_dim=128,
                     doc_mask=True, mlp_precision=args.mlp)
     hyper = Hyper()
-    hyper.total_batch, hyper.device_batch = args.total_batch, args.device_batch
+    # the global batch is fixed, so with more GPUs a rank's share shrinks below the preferred micro-batch
+    share = max(1, args.total_batch // (2048 * rt.world))
+    db = min(args.device_batch if not torch_path else min(args.device_batch, 32), share)     # the PyTorch bodies hold whole logits
+    while share % db:
+        db -= 1
+    hyper.total_batch, hyper.device_batch = args.total_batch, db
     from them_bones_b200.trainer import Trainer
     tr = Trainer(cfg, hyper, rt, horizon_steps=10000)
     loader = SynthLoader(cfg.vocab_size, cfg.sequence_len, tr.local_windows, rank=rt.rank, seed=hyper.seed,
@@ -188,6 +194,7 @@ def run_ours(args, torch_path: bool = False):
             "gpu_launches": int(launches),
             "native_ops": {k: v - counts0.get(k, 0) for k, v in ops.COUNTS.items()},
             "tflops_per_gpu": value * tr.flops_per_token / rt.world / 1e12,
+            "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30,
         }
         print(json.dumps(out), flush=True)
     if rt.ddp:
