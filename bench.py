@@ -117,11 +117,9 @@ def run_ours(args, torch_path: bool = False):
                     doc_mask=True, mlp_precision=args.mlp)
     hyper = Hyper()
     # the global batch is fixed, so with more GPUs a rank's share shrinks below the preferred micro-batch
-    share = max(1, args.total_batch // (2048 * rt.world))
-    db = min(args.device_batch if not torch_path else min(args.device_batch, 32), share)     # the PyTorch bodies hold whole logits
-    while share % db:
-        db -= 1
-    hyper.total_batch, hyper.device_batch = args.total_batch, db
+    from them_bones_b200.config import micro_batch_for
+    pref = args.device_batch if not torch_path else min(args.device_batch, 32)       # the PyTorch bodies hold whole logits
+    hyper.total_batch, hyper.device_batch = args.total_batch, micro_batch_for(args.total_batch, rt.world, pref, 2048)
     from them_bones_b200.trainer import Trainer
     tr = Trainer(cfg, hyper, rt, horizon_steps=10000)
     loader = SynthLoader(cfg.vocab_size, cfg.sequence_len, tr.local_windows, rank=rt.rank, seed=hyper.seed,

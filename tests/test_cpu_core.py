@@ -280,3 +280,11 @@ def test_native_call_sites_match_the_c_signatures():
             assert n == sigs[name], f"{f}:{node.lineno}: {name} takes {sigs[name]} arguments, the call passes {n}"
             seen += 1
     assert seen > 40
+
+
+def test_micro_batch_follows_the_ranks_share_of_a_fixed_global_batch():
+    from them_bones_b200.config import micro_batch_for
+    got = [micro_batch_for(524288, w, 64, 2048) for w in (1, 2, 4, 8, 16)]
+    assert got == [64, 64, 64, 32, 16]
+    assert micro_batch_for(524288, 1, 48, 2048) == 32          # must divide the 256 windows of the step
+    assert micro_batch_for(2048, 8, 64, 2048) == 1

@@ -323,6 +323,16 @@ def build_config(depth: int, n_embd: int, n_head: int, seq_len: int, vocab: int,
     return GPTConfig(**kw)
 
 
+def micro_batch_for(total_batch: int, world: int, preferred: int, seq_len: int) -> int:
+    """Sequences per micro-step per rank: the largest value not above ``preferred`` that divides the rank's share of the
+    global batch (with a fixed global batch the share shrinks as ranks are added)."""
+    share = max(1, total_batch // (seq_len * world))
+    db = max(1, min(preferred, share))
+    while share % db:
+        db -= 1
+    return db
+
+
 # Named model geometries of the five benchmark configurations.
 GEOMETRY = {
     "tiny": dict(depth=4, n_embd=256, n_head=4, seq_len=256, vocab=8192),
