@@ -139,6 +139,21 @@ def test_sharded_output_table_matches_single_rank():
     assert float(close.float().mean()) > 0.95, float(close.float().mean())
 
 
+def test_grad_clip_on_two_ranks(monkeypatch):
+    """The global norm of the clip spans the ranks' shards: two ranks reproduce the single-process curve."""
+    from them_bones_b200 import config as C
+    monkeypatch.setenv("BONES_GRAD_CLIP", "0.05")
+    C.switches(refresh=True)
+    try:
+        single = _single(DENSE)
+        multi = _spawn(_worker_train, DENSE, "lean")
+    finally:
+        monkeypatch.delenv("BONES_GRAD_CLIP")
+        C.switches(refresh=True)
+    for a, b in zip(single, multi):
+        assert abs(a - b) < 2e-3 * abs(a), (single, multi)
+
+
 def _worker_control(rank, world, path, out):
     from them_bones_b200.utils.control import StepControl
     rt = _init(rank, world, path)
