@@ -46,21 +46,40 @@ def test_attention_forward(b, t, h, window, docs):
     assert _rel(y, ref) < 2e-2, _rel(y, ref)
 
 
-def test_attention_backward():
+@pytest.mark.parametrize("b,t,h,window,docs", [(2, 512, 2, 256, True), (1, 2048, 2, 0, True), (1, 2048, 1, 512, True),
+                                               (2, 1024, 1, 0, False)])
+def test_attention_backward(b, t, h, window, docs):
+    """Full-causal and banded, at the training length, with a document start inside the last 128-token tile
+    (``_inputs`` puts one at ``t - 5``) and without documents."""
     from them_bones_b200.ops import _lib as L
     from them_bones_b200.ops import attention_native as AN
     from them_bones_b200.ref import functional as RF
-    b, t, h, d = 2, 512, 2, 128
-    qkv, cos, sin, ds = _inputs(b, t, h, d, seed=3)
+    d = 128
+    qkv, cos, sin, ds = _inputs(b, t, h, d, seed=3, docs=docs)
     scale = 0.11
     g = torch.randn(b, t, h * d, device="cuda", dtype=torch.bfloat16)
     x = qkv.clone().requires_grad_(True)
-    y = AN.attention(x, cos, sin, h, d, scale, ds, 256)
+    y = AN.attention(x, cos, sin, h, d, scale, ds, window)
     y.backward(g)
     xr = qkv.float().requires_grad_(True)
-    yr = RF.attention(xr, cos, sin, h, d, scale, ds, 256)
+    yr = RF.attention(xr, cos, sin, h, d, scale, ds, window)
     yr.backward(g.float())
     torch.cuda.synchronize()
     L.check_error_word()
     assert _rel(y, yr) < 2e-2
     assert _rel(x.grad, xr.grad) < 4e-2, _rel(x.grad, xr.grad)
+
+
+def test_attention_ragged_length_is_padded_and_unsupported_shapes_raise():
+    """The operator layer pads a length that is not a multiple of 128 (scoring, cache-free decoding) and raises --
+    rather than taking a library path -- for what the kernels do not cover."""
+    from them_bones_b200 import ops
+    from them_bones_b200.ref import functional as RF
+    b, t, h, d = 2, 200, 2, 128
+    qkv, cos, sin, ds = _inputs(b, t, h, d, seed=5)
+    with torch.no_grad():
+        y = ops.attention(qkv, cos, sin, h, d, 0.11, ds, 0)
+        ref = RF.attention(qkv.float(), cos, sin, h, d, 0.11, ds, 0)
+    assert y.shape == (b, t, h * d) and _rel(y, ref) < 2e-2
+    with pytest.raises(ValueError):
+        ops.attention(qkv.float(), cos, sin, h, d, 0.11, ds, 0)

@@ -147,18 +147,3 @@ def test_gemm_softcap_epilogue(pair):
     ref = cap * torch.tanh(x.float() @ w.float().T / cap)
     assert float((out[:, :n].float() - ref).abs().max()) < 0.08
     assert float(out[:, n:].float().abs().sum()) == 0.0
-
-
-def test_mma_issue_probe_reports_plausible_cycles():
-    """The tcgen05.mma issue-rate probe: a 128 x 128 x 16 instruction cannot beat its 64 tensor-pipe cycles."""
-    import ctypes
-
-    from them_bones_b200.ops import _lib as L
-    res = torch.zeros(2, dtype=torch.int64, device="cuda")
-    for nsize, a_tmem in ((128, 0), (128, 1), (256, 1)):
-        for _ in range(2):
-            L.call("bones_mma_probe", L.ptr(res), ctypes.c_int(256), ctypes.c_int(a_tmem), ctypes.c_int(nsize), L.stream())
-        torch.cuda.synchronize()
-        L.check_error_word()
-        per = res[1].item() / 256
-        assert nsize / 2 * 0.95 <= per < 600, (nsize, a_tmem, per)

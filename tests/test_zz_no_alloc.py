@@ -4,7 +4,9 @@ Some users of the native library cannot allocate device memory at the point wher
 (no PyTorch allocator in the process, or a phase in which cudaMalloc is forbidden), so ``bones_attn_bwd_noalloc`` keeps
 its scratch inside the library.  This test drives that symbol with ctypes, twice in a row on different data (the second
 call meets the scratch left by the first), and checks both results against the regular entry points
-``bones_attn_delta`` + ``bones_attn_bwd`` on the same inputs.  It also checks that an oversized problem is refused.
+``bones_attn_delta`` + ``bones_attn_bwd`` on the same inputs and, after the RoPE / QK-norm backward pass, against the
+gradient of the plain fp32 PyTorch statement of the same attention.  It also reads the entry point's own status word
+(an expired bounded wait would show there and nowhere else) and checks that an oversized problem is refused.
 The file name sorts last so a run that stops at the first failure has already run every other test.
 """
 import ctypes
@@ -30,6 +32,7 @@ def _case(lib, seed, b, t, h, window):
     qkv = torch.randn(b * t, 3 * h * d, device="cuda", dtype=torch.bfloat16)
     dy = torch.randn(b * t, h * d, device="cuda", dtype=torch.bfloat16)
     cos, sin = RF.rotary_tables(t, d, 10000.0, device="cuda")
+    cos, sin = cos.bfloat16().float().contiguous(), sin.bfloat16().float().contiguous()
     idx = torch.randint(1, 50, (b, t), device="cuda")
     idx[:, 0] = 0
     idx[0, t // 2 + 3] = 0
@@ -55,6 +58,15 @@ def _case(lib, seed, b, t, h, window):
     rel = lambda a, r: float((a.float() - r.float()).norm() / r.float().norm().clamp_min(1e-12))  # noqa: E731
     assert torch.isfinite(dqk).all()
     assert rel(dqk, dqk_ref) < 1e-3 and rel(dv, dv_ref) < 1e-3, (rel(dqk, dqk_ref), rel(dv, dv_ref))
+    assert lib.bones_attn_bwd_noalloc_error_read_clear(stream) == 0
+    # oracle: the fp32 PyTorch statement of the whole op, differentiated by autograd
+    dqkv = torch.empty(b * t, 3 * h * d, device="cuda", dtype=torch.bfloat16)
+    assert lib.bones_rope_qknorm_bwd(_p(qkv), _p(cos), _p(sin), _p(dqk), _p(dv), _p(dqkv), _L(b * t), _I(t), _I(h), _I(d),
+                                     stream) == 0
+    x = qkv.float().view(b, t, -1).requires_grad_(True)
+    RF.attention(x, cos, sin, h, d, scale, ds, window).backward(dy.float().view(b, t, -1))
+    torch.cuda.synchronize()
+    assert rel(dqkv.view(b, t, -1), x.grad) < 4e-2, rel(dqkv.view(b, t, -1), x.grad)
 
 
 def test_noalloc_attention_backward_twice_and_limit():

@@ -13,6 +13,9 @@
 //
 // Warp roles: warp 0 TMA producer (Kh, V once; Qh, dO double-buffered), warp 1 MMA issuer + TMEM owner, warps 2-9
 // compute (two warps per 32-lane TMEM quadrant, 64 columns each).  TMEM: S/dQ | dP | dV | dK = 4 x 128 columns.
+#include <mutex>
+
+#include "bones_noalloc.h"
 #include "common.cuh"
 
 namespace bones {
@@ -404,9 +407,34 @@ static __device__ __align__(256) int g_noalloc_err[64];
 struct NoAllocDevice {
   float* delta = nullptr;   // device addresses resolved from the symbols above (the symbol names are host stand-ins)
   int* err = nullptr;
-  bool ready = false;
+  bool ready = false;       // symbol addresses resolved
+  bool attr = false;        // the kernel's shared-memory limit has been raised
 };
 static NoAllocDevice g_noalloc_dev[64];
+static std::mutex g_noalloc_mu;      // guards the per-device set-up: two host threads may make the first call at once
+
+// Resolves the scratch and error-word addresses of the current device once.  0 or a negative set-up code.
+static int noalloc_setup(int dev, size_t smem, NoAllocDevice** out) {
+  if (dev < 0 || dev >= 64) return -12;
+  std::lock_guard<std::mutex> lk(g_noalloc_mu);
+  NoAllocDevice& nd = g_noalloc_dev[dev];
+  if (!nd.ready) {
+    // once per device, with that device current: turn the symbols into device addresses
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_delta) != cudaSuccess || !p) return -11;
+    nd.delta = static_cast<float*>(p);
+    if (cudaGetSymbolAddress(&p, g_noalloc_err) != cudaSuccess || !p) return -11;
+    nd.err = static_cast<int*>(p);
+    nd.ready = true;
+  }
+  if (smem && !nd.attr) {
+    cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    nd.attr = true;
+  }
+  *out = &nd;
+  return 0;
+}
 }  // namespace bones
 
 extern "C" {
@@ -430,19 +458,11 @@ int bones_attn_bwd_noalloc(const void* qk, const void* qkv, const void* dy, cons
   if (M * H > kNoAllocMaxRows) return -10;
   int dev = 0;
   BONES_CHECK(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64) return -12;
   constexpr size_t smem = (size_t)BTILE * 7 + 160 + 1024;
-  NoAllocDevice& nd = g_noalloc_dev[dev];
-  if (!nd.ready) {
-    // once per device, with that device current: turn the symbols into device addresses
-    void* p = nullptr;
-    if (cudaGetSymbolAddress(&p, g_noalloc_delta) != cudaSuccess || !p) return -11;
-    nd.delta = static_cast<float*>(p);
-    if (cudaGetSymbolAddress(&p, g_noalloc_err) != cudaSuccess || !p) return -11;
-    nd.err = static_cast<int*>(p);
-    BONES_CHECK(cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    nd.ready = true;
-  }
+  NoAllocDevice* ndp = nullptr;
+  const int src = noalloc_setup(dev, smem, &ndp);
+  if (src) return src;
+  NoAllocDevice& nd = *ndp;
   CUtensorMap tq, tv, td;
   int rc = tmap_rows_2d_b(&tq, qk, M, 2 * A);
   if (rc) return rc;
@@ -466,5 +486,25 @@ int bones_attn_bwd_noalloc(const void* qk, const void* qkv, const void* dy, cons
   dim3 grid(T / BT, H, B);
   attn_bwd_kernel<<<grid, 320, smem, s>>>(tq, tv, td, p);
   return (int)cudaGetLastError();
+}
+
+// Status of the calls made so far on the current device: 0, or the code of the first bounded wait that ran out inside
+// the kernel since the last read (the call itself had returned 0: launches are asynchronous).  Waits for `stream`, copies
+// one word out of the library's own error word and clears it; allocates nothing.
+int bones_attn_bwd_noalloc_error_read_clear(void* stream) {
+  int dev = 0;
+  BONES_CHECK(cudaGetDevice(&dev));
+  NoAllocDevice* ndp = nullptr;
+  const int src = noalloc_setup(dev, 0, &ndp);
+  if (src) return src;
+  cudaStream_t s = (cudaStream_t)stream;
+  int v = 0;
+  BONES_CHECK(cudaMemcpyAsync(&v, ndp->err, sizeof(int), cudaMemcpyDeviceToHost, s));
+  BONES_CHECK(cudaStreamSynchronize(s));
+  if (v != 0) {
+    BONES_CHECK(cudaMemsetAsync(ndp->err, 0, sizeof(int), s));
+    BONES_CHECK(cudaStreamSynchronize(s));
+  }
+  return v;
 }
 }  // extern "C"

@@ -15,6 +15,14 @@
  *   limit      B * H * T <= 1,048,576.  Larger problems are refused with -10 (see bones_attn_bwd_noalloc_strerror).
  *   first call the first call on each device resolves the scratch symbol's device address (cudaGetSymbolAddress) and
  *              raises the kernel's shared-memory limit; make that first call before any stream capture on the device.
+ *              The set-up is guarded by a mutex, so two host threads may race to make it; only the set-up is guarded,
+ *              the scratch itself is not (see "sharing").
+ *   errors     every wait inside the kernel is bounded.  If one runs out (it should not: it would mean a lost TMA or MMA
+ *              completion) the kernel stops early, leaves `dqk` / `dv` incomplete and records a code in an error word
+ *              that belongs to this entry point alone; the call has returned 0 long before, because launches are
+ *              asynchronous.  Read it with bones_attn_bwd_noalloc_error_read_clear(stream) after the calls whose
+ *              results you are about to use: it waits for the stream, returns 0 or the first recorded code (1..7: which
+ *              wait gave up) and clears the word.  It allocates nothing either.
  *   sharing    all calls on a device share the one scratch array, and it keeps the previous call's contents.  The
  *              range a call uses is fully rewritten before it is read, and the dq-hat half of `dqk` is zeroed by the
  *              call itself, so back-to-back calls on one stream are safe.  Two calls that can overlap on the GPU
@@ -31,6 +39,7 @@ extern "C" {
 int bones_attn_bwd_noalloc(const void* qk, const void* qkv, const void* dy, const void* y, const float* lse, float* dqk,
                            void* dv, const int* doc_start, int B, int T, int H, float scale, int window_tiles,
                            void* stream);
+int bones_attn_bwd_noalloc_error_read_clear(void* stream);
 const char* bones_attn_bwd_noalloc_strerror(int code);
 #ifdef __cplusplus
 }

@@ -135,6 +135,9 @@ class HashedTables:
             self._sparse_adam(j, uniq, acc, lr)
             self.stats["updates"] += 1
             self.stats["touched"] += int(len(uniq))
+        done = getattr(self.exchange, "after_update", None)
+        if done is not None:
+            done()          # peers read these shards directly: no rank starts its next lookup before every owner is done
 
     def _sparse_adam(self, j, rows, g, lr):
         from .. import ops

@@ -1,11 +1,11 @@
-"""Autograd wrapper of the sm_100a attention kernels (``csrc/attention.cu``, ``csrc/attention_bwd.cu``).
+"""Autograd wrapper of the sm_100a attention kernels (``csrc/attention.cu``, ``csrc/attention_bwd_split.cu``).
 
-Forward: RoPE + QK-norm pre-pass into a ``[B*T, 2*H*D]`` buffer, then the tcgen05 flash-attention kernel reading the
-values in place from the packed ``qkv``.  Saved for backward: ``qkv``, the rotated/normalised ``qk``, the output and
-``lse``.  Backward: ``delta = rowsum(dO * O)``, the tcgen05 backward kernel (dQ-hat accumulated in fp32 by vector
-atomics, dK-hat / dV per key tile), then the pre-pass backward that applies the norm Jacobian and the inverse rotation
-and writes one packed ``[B, T, 3*H*D]`` gradient (reference: the fused backward emits one packed gradient,
-round2/source/kernels/nki_attn_bandpro.py:1-134).
+Forward: RoPE + QK-norm pre-pass into a ``[B*T, 2*H*D]`` buffer, then the persistent tcgen05 flash-attention kernel
+reading the values in place from the packed ``qkv``.  Saved for backward: ``qkv``, the rotated/normalised ``qk``, the
+output and ``lse``.  Backward (``ops/attention_bwd.py``): a statistics pre-pass, the dK/dV kernel and the dQ kernel
+(every accumulator in TMEM, bf16 outputs, no atomics), then the pre-pass backward that applies the norm Jacobian and
+the inverse rotation and writes one packed ``[B, T, 3*H*D]`` gradient (reference: the fused backward emits one packed
+gradient, round2/source/kernels/nki_attn_bandpro.py:1-134).
 """
 from __future__ import annotations
 
@@ -16,11 +16,24 @@ import torch
 from . import _lib as L
 
 _I, _L, _F = ctypes.c_int, ctypes.c_longlong, ctypes.c_float
-HAVE_BWD = True
+SUPPORTED_HEAD_DIMS = (128,)
+
+
+def why_not(qkv, n_head, head_dim, window=0) -> str:
+    """Empty when the kernels cover the call, else the reason."""
+    if qkv.dtype != torch.bfloat16:
+        return f"dtype {qkv.dtype} (bf16 only)"
+    if head_dim not in SUPPORTED_HEAD_DIMS:
+        return f"head_dim {head_dim} (supported: {SUPPORTED_HEAD_DIMS})"
+    if qkv.shape[1] % 128:
+        return f"sequence length {qkv.shape[1]} is not a multiple of 128"
+    if window % 128:
+        return f"window {window} is not a multiple of 128"
+    return ""
 
 
 def applies(qkv, n_head, head_dim) -> bool:
-    return qkv.dtype == torch.bfloat16 and head_dim == 128 and qkv.shape[1] % 128 == 0
+    return not why_not(qkv, n_head, head_dim)
 
 
 def rope_qknorm(qkv2, cos, sin, t, n_head, head_dim):
@@ -56,17 +69,9 @@ class _AttnFn(torch.autograd.Function):
     def backward(ctx, dy):
         qkv2, qk, y, lse, cos, sin, ds = ctx.saved_tensors
         b, t, n_head, head_dim, scale, window = ctx.meta
-        if HAVE_BWD:
-            from . import attention_bwd as AB
-            dqkv = AB.backward(dy, qkv2, qk, y, lse, cos, sin, ds, b, t, n_head, head_dim, scale, window)
-            return dqkv.view(b, t, -1), None, None, None, None, None, None, None
-        # interim route: differentiate the library path on the saved inputs
-        from . import _sdpa_attention
-        with torch.enable_grad():
-            x = qkv2.view(b, t, -1).detach().requires_grad_(True)
-            out = _sdpa_attention(x, cos, sin, n_head, head_dim, scale, ds, window)
-            (dqkv,) = torch.autograd.grad(out, x, dy)
-        return dqkv, None, None, None, None, None, None, None
+        from . import attention_bwd as AB
+        dqkv = AB.backward(dy, qkv2, qk, y, lse, cos, sin, ds, b, t, n_head, head_dim, scale, window)
+        return dqkv.view(b, t, -1), None, None, None, None, None, None, None
 
 
 def attention(qkv, cos, sin, n_head, head_dim, scale, doc_start, window):

@@ -335,8 +335,26 @@ def embedding(idx, weight, dtype):
 
 # -- attention -------------------------------------------------------------------------------------------------------
 def attention(qkv, cos, sin, n_head, head_dim, scale, doc_start, window):
-    from . import attn_dispatch as A
-    return A.attention(qkv, cos, sin, n_head, head_dim, scale, doc_start, window)
+    """RoPE + QK-norm + causal (document-reset, optionally banded) attention on the tcgen05 flash-attention kernels
+    (``csrc/attention.cu``, ``csrc/attention_bwd_split.cu``).  A shape the kernels do not cover raises: the SDPA route
+    exists only as the explicit baseline (``BONES_KERNELS=ref``), never as a silent fallback (reference: a kernel
+    route that does not apply on the device raises, round2/source/train.py:4882-4887)."""
+    from . import attention_native as AN
+    t = qkv.shape[1]
+    pad = -t % 128
+    if pad:
+        # the kernels work on 128-token tiles: a ragged length (scoring, cache-free decoding) is zero-padded at the end,
+        # which causal masking keeps away from the real positions, and the padding rows are dropped again
+        qkv = F.pad(qkv, (0, 0, 0, pad))
+        cos, sin = F.pad(cos, (0, 0, 0, pad)), F.pad(sin, (0, 0, 0, pad))
+        if doc_start is not None:
+            doc_start = F.pad(doc_start, (0, pad), value=t)
+    why = AN.why_not(qkv, n_head, head_dim, window)
+    if why:
+        raise ValueError(f"native attention does not cover this call: {why}")
+    COUNTS["attention"] += 1
+    y = AN.attention(qkv, cos, sin, n_head, head_dim, scale, doc_start, window)
+    return y[:, :t] if pad else y
 
 
 # -- loss head -------------------------------------------------------------------------------------------------------

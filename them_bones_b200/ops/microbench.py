@@ -5,7 +5,6 @@
     python -m them_bones_b200.ops.microbench attn_bwd --b 4 --t 2048 --h 10
     python -m them_bones_b200.ops.microbench norm --rows 65536 --cols 1280
     python -m them_bones_b200.ops.microbench ce --rows 4096 --vocab 65536
-    python -m them_bones_b200.ops.microbench mma                       (cycles per 128 x N x 16 tcgen05.mma, one CTA)
 
 Timing: CUDA events on the launching stream, ``--warmup`` untimed iterations, an L2 flush (a 256 MiB write) between
 timed iterations, mean over ``--iters``.  Fractions are against the measured peaks in ``MEASURED_PEAKS.json`` at the
@@ -54,7 +53,7 @@ def timeit(fn, iters, warmup, flush):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn_fwd", "attn_bwd", "norm", "ce", "mma"])
+    ap.add_argument("what", choices=["gemm", "attn_fwd", "attn_bwd", "norm", "ce"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -75,21 +74,6 @@ def main():
     bf = torch.bfloat16
     out = {"what": a.what, "peaks": src}
     torch.manual_seed(0)
-    if a.what == "mma":
-        import ctypes
-        res = torch.zeros(2, dtype=torch.int64, device="cuda")
-        rows = []
-        for nsize in (128, 256):
-            for a_tmem in (0, 1):
-                for _ in range(2):
-                    L.call("bones_mma_probe", L.ptr(res), ctypes.c_int(256), ctypes.c_int(a_tmem), ctypes.c_int(nsize), L.stream())
-                torch.cuda.synchronize()
-                L.check_error_word()
-                rows.append({"n": nsize, "a_operand": "tmem" if a_tmem else "smem", "cycles_per_mma_issue": res[0].item() / 256,
-                             "cycles_per_mma_complete": res[1].item() / 256, "tensor_pipe_cycles": nsize // 2})
-        out.update(shape="128 x N x 16 bf16, 256 instructions into one accumulator", results=rows)
-        print(json.dumps(out))
-        return
     if a.what == "gemm":
         m, n, k = a.m, a.n, a.k
         if a.layout == "nt":

@@ -263,6 +263,9 @@ class LeanDistMuonAdamW(torch.optim.Optimizer):
             muon_g = [torch.where(okb, t, torch.zeros_like(t)) for t in muon_g]
             self.SG.copy_(torch.where(okb, self.SG, torch.zeros_like(self.SG)))
             self._last_ok = ok
+            if not hasattr(self, "_bad_dev"):
+                self._bad_dev = torch.zeros(1, dtype=torch.int64, device=ok.device)
+            self._bad_dev += (ok <= 0).to(torch.int64)
         # 4b: global-norm clip.  Every rank holds its own shards of the reduced gradients and all of the small ones.
         if self.grad_clip > 0:
             sq = torch.zeros((), dtype=torch.float32, device=self.SG.device)
@@ -313,7 +316,10 @@ class LeanDistMuonAdamW(torch.optim.Optimizer):
         over NVLink and applies the owner update; one launch publishes the updated shard into every peer's slab."""
         comm = self.comm
         comm.pre_step()                                   # all ranks' gradients are complete and visible
-        self._small_step(comm.all_reduce_mean(self.SG))
+        sg = comm.all_reduce_mean(self.SG)
+        # the matrices and tables are gated element-wise inside their kernels; the scalar stack gets the same gate here,
+        # so one non-finite step cannot poison S / S_m / S_v for good
+        self._small_step(torch.where(torch.isfinite(sg), sg, torch.zeros_like(sg)))
         for u in self.row_units:
             comm.fused_row_adamw(u, self.steps)
         for u in self.muon_units:
@@ -322,8 +328,12 @@ class LeanDistMuonAdamW(torch.optim.Optimizer):
                 u.G.zero_()                               # consumed; peers add the next step's tiles after post_step()
         self._local.step(1.0 / self.world)
         comm.post_step()                                  # every peer's stores into my slabs have landed
-        self._gsq_history = getattr(self, "_gsq_history", [])
-        self._gsq_history.append(comm.gsq.clone())        # read lazily: no host synchronisation in the step
+        # sum(g^2) of the step, folded into a device-side count of non-finite steps: no host synchronisation in the step
+        # and nothing that grows with the number of steps
+        if not hasattr(self, "_bad_dev"):
+            self._bad_dev = torch.zeros(1, dtype=torch.int64, device=comm.gsq.device)
+        bad = ~torch.isfinite(comm.gsq + sg.square().sum())
+        self._bad_dev += bad.to(torch.int64)
         if self.overlap_check and self.steps == 2:
             self.check_mismatches += comm.cross_check(self)
 
@@ -350,13 +360,43 @@ class LeanDistMuonAdamW(torch.optim.Optimizer):
             out[u.p] = full
         return out
 
+    def unit_state_dict(self) -> dict:
+        """This rank's optimizer state (the state lives in the units, not in ``Optimizer.state``): the owner's masters,
+        Muon momentum / second moments, AdamW moments, the scalar stack and the local expert state, as host tensors.
+        One file per rank restores a run at the same world size; the replicas are rebuilt from the checkpoint's
+        ``model_state`` (the consolidated masters) before the optimizer is constructed, so only owner state is kept here
+        (the reference never saves optimizer state)."""
+        cpu = lambda t: t.detach().cpu().clone()  # noqa: E731
+        return {
+            "world": self.world, "rank": self.rank, "steps": self.steps,
+            "muon": [dict(master=cpu(u.master), momentum=cpu(u.momentum), second=cpu(u.second)) for u in self.muon_units],
+            "rows": [dict(master=cpu(u.master), exp_avg=cpu(u.exp_avg), exp_avg_sq=cpu(u.exp_avg_sq)) for u in self.row_units],
+            "small": dict(S=cpu(self.S), S_m=cpu(self.S_m), S_v=cpu(self.S_v)),
+            "local": [{k: cpu(v) for k, v in self._local.state.get(p, {}).items()}
+                      for g in self.local_groups for p in g["params"]],
+        }
+
+    @torch.no_grad()
+    def load_unit_state_dict(self, sd: dict) -> None:
+        if sd["world"] != self.world or sd["rank"] != self.rank:
+            raise ValueError(f"optimizer state of rank {sd['rank']}/{sd['world']} loaded on rank {self.rank}/{self.world}")
+        self.steps = int(sd["steps"])
+        for u, st in zip(self.muon_units, sd["muon"]):
+            u.master.copy_(st["master"]); u.momentum.copy_(st["momentum"]); u.second.copy_(st["second"])
+        for u, st in zip(self.row_units, sd["rows"]):
+            u.master.copy_(st["master"]); u.exp_avg.copy_(st["exp_avg"]); u.exp_avg_sq.copy_(st["exp_avg_sq"])
+        self.S.copy_(sd["small"]["S"]); self.S_m.copy_(sd["small"]["S_m"]); self.S_v.copy_(sd["small"]["S_v"])
+        ps = [p for g in self.local_groups for p in g["params"]]
+        for p, st in zip(ps, sd["local"]):
+            if st:
+                self._local.state[p] = {k: v.to(p.device) for k, v in st.items()}
+                p.copy_(self._local.state[p]["master"])
+
     def count_bad_steps(self) -> int:
         """Steps whose reduced gradient held a non-finite value (the fused kernels zeroed those entries).  Synchronises;
         call at a step boundary that synchronises anyway."""
-        hist = getattr(self, "_gsq_history", [])
-        if hist:
-            self.bad_steps += int((~torch.isfinite(torch.stack(hist))).sum())
-            self._gsq_history = []
+        if hasattr(self, "_bad_dev"):
+            self.bad_steps = int(self._bad_dev.item())
         return self.bad_steps
 
     def describe(self) -> str:

@@ -319,3 +319,9 @@ class PeerTableExchange:
 
     def all_ok(self, ok):
         return self.fallback.all_ok(ok)
+
+    def after_update(self):
+        """Called by every rank at the end of the tables' update.  Lookups are peer loads with no collective of their
+        own, so without this a fast rank could gather rows from a shard its owner is still updating (stale or torn
+        rows); the epoch barrier (bounded wait) orders every owner's update before any rank's next gather."""
+        self.comm.barrier()

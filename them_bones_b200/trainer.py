@@ -24,7 +24,7 @@ from .runtime import Runtime, compute_dtype_for, print0
 class Trainer:
     def __init__(self, config: GPTConfig, hyper: Hyper, rt: Runtime, *, device_batch: int | None = None,
                  total_batch: int | None = None, optimizer_kind: str | None = None, fused_comm: bool | None = None,
-                 horizon_steps: int = 0, budget_seconds: float = 0.0):
+                 horizon_steps: int = 0, budget_seconds: float = 0.0, init_state: dict | None = None):
         sw = switches()
         self.config, self.hyper, self.rt = config, hyper, rt
         self.dtype = compute_dtype_for(rt.device_type)
@@ -41,6 +41,10 @@ class Trainer:
         model = GPT(config, ep_group=ep_group, ep_world=rt.world if config.moe_layers else 1,
                     ep_rank=rt.rank if config.moe_layers else 0)
         model.init_weights(hyper.seed)
+        if init_state is not None:                 # resume: a checkpoint's ``model_state`` replaces the fresh weights
+            from .utils.ckpt import load_model_state
+            load_model_state(model, init_state, ep_world=rt.world if config.moe_layers else 1,
+                             ep_rank=rt.rank if config.moe_layers else 0)
         model = model.to(rt.device)
         model.cast_compute(self.dtype)
         self.model = model
@@ -64,6 +68,8 @@ class Trainer:
                                                    else sw["TABLE_HOST_STATE"].lower() in ("1", "true")))
             if self.comm is not None and rt.world > 1:
                 self.tables.exchange = self.comm.table_exchange(self.tables)
+            if init_state is not None:
+                self.tables.load_share({k: v for k, v in init_state.items() if k.startswith("table_")})
             model.attach_tables(self.tables)
         self.os1 = None
         if config.os1_rows:
@@ -74,19 +80,41 @@ class Trainer:
         if self.comm is not None and config.moe_layers and rt.world > 1:
             self.comm.install_moe(model)
         self.step_index = 0
+        self.bad_steps = 0
         self.t_start = time.time()
+        self._agreed_clock = None                 # set by the step loop once the ranks have exchanged rank 0's clock
         self.sched = dict(lrm=1.0, momentum=hyper.muon_momentum, table_lr=hyper.table_lr)
         self.last_moe_stats = None
         self._dev_x = self._dev_y = None
         self.flops_per_token = model.estimate_flops()
 
     # ------------------------------------------------------------------------------------------------------
+    def set_agreed_clock(self, elapsed_seconds: float) -> None:
+        """The training clock every rank agreed on (rank 0's, from the step-control all-reduce).  Everything that is
+        decided on the clock -- schedules, the rescue copy, the tail average, the sequence ramp -- reads it through
+        ``progress()``, so all ranks cross a threshold on the same step (reference: the MAX-all-reduced
+        ``rank0_clock_ms``, round2/source/train.py:22959-22975)."""
+        self._agreed_clock = float(elapsed_seconds)
+
     def progress(self) -> float:
         if self.budget_seconds > 0:
-            return min(1.0, (time.time() - self.t_start) / self.budget_seconds)
+            clock = self._agreed_clock if self._agreed_clock is not None else time.time() - self.t_start
+            return min(1.0, clock / self.budget_seconds)
         if self.horizon_steps > 0:
             return min(1.0, self.step_index / self.horizon_steps)
         return 0.0
+
+    def check_device_health(self) -> int:
+        """Call where the host synchronises anyway (a forced synchronous step boundary, before a save).  Raises if a
+        native kernel gave up on a bounded wait since the last call (training must not go on with data a peer never
+        delivered); returns the running count of optimizer steps whose reduced gradient was non-finite (reference:
+        ``bad_steps``, round1/source/train.py:10356-10363)."""
+        if self.rt.device_type == "cuda" and not ops.reference_path():
+            from .ops import _lib
+            _lib.check_error_word()
+        if hasattr(self.optimizer, "count_bad_steps"):
+            self.bad_steps = self.optimizer.count_bad_steps()
+        return self.bad_steps
 
     def h2d(self, inputs: torch.Tensor, targets: torch.Tensor):
         """Host windows -> persistent device tensors (non-blocking from pinned memory)."""

@@ -5,7 +5,8 @@
 :21031-21126).  Experts are gathered to rank 0 one tensor at a time (``moe_gather_experts`` :20027-20046) and stored as
 ``transformer.h.{i}.mlp.w_fc [E,H,d]`` / ``w_proj [E,d,H]``; table shares are stored as extra state keys.  Files are
 written to ``<path>.tmp`` and renamed so a reader never sees a partial file.  Optimizer state is saved only on request
-(``BONES_SAVE_OPT_STATE=1``; the reference never saves it).
+(``BONES_SAVE_OPT_STATE=1``: one ``<path>.opt.rank<r>`` file per rank with the owner state of that rank, read back by
+``train.py --resume``; the reference never saves it).
 """
 from __future__ import annotations
 
@@ -71,6 +72,32 @@ def _gather_rows(table) -> dict:
     return out
 
 
+def load_model_state(model, state: dict, ep_world: int = 1, ep_rank: int = 0) -> None:
+    """Checkpoint ``model_state`` -> a freshly built model (resume).  Expert tensors are stored gathered ``[E, ...]``;
+    an expert-parallel rank keeps its own ``E / ep_world`` of them.  Table and output-table shares are not parameters
+    and are loaded by their owners."""
+    own = dict(model.named_parameters())
+    with torch.no_grad():
+        for name, p in own.items():
+            t = state[name]
+            if t.shape != p.shape and t.dim() == p.dim() and t.shape[1:] == p.shape[1:] and t.shape[0] == p.shape[0] * ep_world:
+                t = t[ep_rank * p.shape[0]:(ep_rank + 1) * p.shape[0]]
+            p.copy_(t.to(p.dtype))
+
+
+def opt_state_path(path: str, rank: int) -> str:
+    return f"{path}.opt.rank{rank}"
+
+
+def save_optimizer_state(path: str, optimizer, rank: int) -> str | None:
+    """Every rank writes its own owner state beside the checkpoint (``BONES_SAVE_OPT_STATE=1``)."""
+    if not hasattr(optimizer, "unit_state_dict"):
+        return None
+    out = opt_state_path(path, rank)
+    write_payload(out, optimizer.unit_state_dict())
+    return out
+
+
 def build_payload(model, meta: dict, optimizer=None, tables=None, state: dict | None = None) -> dict:
     """The checkpoint as host tensors.  Collective when the model is sharded: every rank must call it."""
     state = state if state is not None else model_state(model, optimizer)
@@ -79,10 +106,7 @@ def build_payload(model, meta: dict, optimizer=None, tables=None, state: dict | 
         extra.update(_gather_rows(tables))
     if getattr(model, "os1", None) is not None:
         extra.update(_gather_rows(model.os1))
-    payload = {"model_state": {**state, **extra}, "model_config": model_config_dict(model.config), "meta": meta}
-    if optimizer is not None and meta.get("save_opt_state"):
-        payload["optimizer_state"] = optimizer.state_dict()
-    return payload
+    return {"model_state": {**state, **extra}, "model_config": model_config_dict(model.config), "meta": meta}
 
 
 def write_payload(path: str, payload: dict) -> None:

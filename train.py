@@ -49,6 +49,8 @@ def parse_args(argv=None):
     ap.add_argument("--doc-len", default=e("BONES_DOC_LEN", "128,2048"))
     ap.add_argument("--out", default=e("BONES_OUT", "final.pt"))
     ap.add_argument("--no-save", action="store_true")
+    ap.add_argument("--resume", default=e("BONES_RESUME", ""), help="checkpoint to continue from (weights, tables and, "
+                    "when <path>.opt.rank<r> files exist, the optimizer state; same world size)")
     ap.add_argument("--eval-tokens", type=int, default=int(e("BONES_EVAL_TOKENS", 0)))
     ap.add_argument("--compile-only", action="store_true")
     ap.add_argument("--device", default=e("BONES_DEVICE", ""))
@@ -72,7 +74,20 @@ def main(argv=None):
     cfg = C.build_config(args.depth, args.n_embd, args.n_head, args.seq_len, args.vocab, head_dim=args.head_dim,
                          hyper=hyper)
     print0("model_config " + json.dumps(C.model_config_dict(cfg)))
-    tr = Trainer(cfg, hyper, rt, horizon_steps=args.steps, budget_seconds=args.budget_seconds)
+    init_state, resumed_steps = None, 0
+    if args.resume:
+        ck = torch.load(args.resume, map_location="cpu", weights_only=True, mmap=True)
+        if ck["model_config"] != C.model_config_dict(cfg):
+            raise ValueError("--resume: the checkpoint's model_config differs from this run's")
+        init_state, resumed_steps = ck["model_state"], int(ck.get("meta", {}).get("steps", 0))
+    tr = Trainer(cfg, hyper, rt, horizon_steps=args.steps, budget_seconds=args.budget_seconds, init_state=init_state)
+    if args.resume:
+        opt_file = CK.opt_state_path(args.resume, rt.rank)
+        if os.path.exists(opt_file) and hasattr(tr.optimizer, "load_unit_state_dict"):
+            tr.optimizer.load_unit_state_dict(torch.load(opt_file, map_location="cpu", weights_only=True))
+        tr.step_index = resumed_steps               # step-driven schedules continue where the checkpoint stopped
+        print0(f"resumed from {args.resume} (checkpoint step {resumed_steps}, optimizer state "
+               f"{'loaded' if os.path.exists(opt_file) else 'fresh'})")
     if sw["ANSWER_PHASE"] > 0:
         tr.model.answer_weight = sw["ANSWER_WEIGHT"]     # marked targets are unmarked and weighted inside the forward
     print0(tr.describe())
@@ -151,6 +166,10 @@ def main(argv=None):
             dt = timer.stop() / 1e3
             if boundary is None:
                 loss_value = float(loss)
+            # a forced synchronous boundary is where latent device errors surface: a bounded wait that ran out inside a
+            # kernel (peer barrier, mbarrier) left its code in the error word, and the fused optimizer kernels counted
+            # the steps whose reduced gradient held a non-finite value
+            tr.check_device_health()
         else:
             # asynchronous boundary: the host runs at most a queue's depth ahead, so in steady state the host time per
             # loop iteration equals the device time per step
@@ -165,7 +184,9 @@ def main(argv=None):
             tr.t_start = t_train0
         elapsed = time.time() - t_train0
         want_stop = stop_rule.should_stop(elapsed)
-        bad, stop, _ = control.decide(loss_value, want_stop, elapsed * 1e3)
+        bad, stop, clock_ms = control.decide(loss_value, want_stop, elapsed * 1e3)
+        if step >= hyper.startup_steps_excluded:
+            tr.set_agreed_clock(clock_ms / 1e3)      # every clock-driven decision below and in the next step uses it
         if loss_value is not None:
             ema_loss = 0.9 * ema_loss + 0.1 * loss_value
         if step % hyper.log_every == 0 and loss_value is not None:
@@ -204,16 +225,24 @@ def main(argv=None):
             break
     if memphase.rows:
         print0("mem-phase: " + memphase.report())
-    if ema is not None:
+    averaged = ema is not None and ema.avg is not None
+    if averaged:
         ema.swap_in()
     total_s = time.time() - t_train0
     meta = dict(steps=step, tokens=step * tokens_per_step, seconds=total_s, switches=sw, world=rt.world,
                 median_dt=sorted(dts)[len(dts) // 2] if dts else None, bad=bad, native_ops=dict(ops.COUNTS),
                 save_opt_state=sw["SAVE_OPT_STATE"])
     bg_save.wait()
+    tr.check_device_health()
+    meta["bad_steps"] = tr.bad_steps
     if not args.no_save:
         CK.check_declared_length(tr.model, loader.seq_len)
-        CK.save_checkpoint(args.out, tr.model, meta, optimizer=tr.optimizer, tables=tr.tables, rank=rt.rank)
+        # after the tail average was swapped in, the in-memory replicas are the model (the owners' fp32 masters still
+        # hold the un-averaged weights), so the file is written from the replicas and equals what is evaluated below
+        CK.save_checkpoint(args.out, tr.model, meta, optimizer=None if averaged else tr.optimizer, tables=tr.tables,
+                           rank=rt.rank)
+        if sw["SAVE_OPT_STATE"]:
+            CK.save_optimizer_state(args.out, tr.optimizer, rt.rank)
         print0(f"saved {args.out}")
     result = {}
     if args.eval_tokens:
