@@ -122,8 +122,10 @@ def run_ours(args, torch_path: bool = False):
     hyper.total_batch, hyper.device_batch = args.total_batch, micro_batch_for(args.total_batch, rt.world, pref, 2048)
     from them_bones_b200.trainer import Trainer
     tr = Trainer(cfg, hyper, rt, horizon_steps=10000)
+    # one stream for the whole job, rank r keeping windows r, r + W, ...: every rank count sees the same global batches,
+    # so `final_loss` is comparable across N
     loader = SynthLoader(cfg.vocab_size, cfg.sequence_len, tr.local_windows, rank=rt.rank, seed=hyper.seed,
-                         doc_len=(128, 2048), bos_id=cfg.bos_id, pin=True)
+                         doc_len=(128, 2048), bos_id=cfg.bos_id, pin=True, shard_of=rt.world)
     n_batches = max(2, min(4, args.steps))
     host = [loader.next_step() for _ in range(n_batches)]         # pinned host windows, larger than L2 per step
     dev = [(x.to(rt.device), y.to(rt.device)) for x, y in host[:2]]
@@ -170,6 +172,10 @@ def run_ours(args, torch_path: bool = False):
     e1.record()
     barrier()
     wall_ms = (time.perf_counter() - t0) * 1e3
+    if rt.ddp:        # outside the timed region: the last step's loss as the mean over all ranks' windows
+        t = torch.tensor([last], device=rt.device)
+        dist.all_reduce(t)
+        last = float(t[0]) / rt.world
     ms_e2e = max_over_ranks(max(e0.elapsed_time(e1), wall_ms), rt)
     e2e_value = tokens / (ms_e2e / 1e3)
     if not torch_path:

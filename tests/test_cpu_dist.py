@@ -199,3 +199,33 @@ def test_lost_rank_is_detected_by_timeout():
             p.join(90)
         assert os.path.exists(out)
         assert torch.load(out) is not None                      # the surviving rank saw an exception, not a hang
+
+
+def _worker_probe(rank, world, path, out):
+    """Rank 1's peer-memory substrate fails at start-up; both ranks must fall back together."""
+    from them_bones_b200.parallel import symm
+    rt = _init(rank, world, path)
+
+    class Fake:
+        launches = 0
+
+    def factory(rt_):
+        if rt_.rank == 1:
+            raise RuntimeError("symmetric memory rendezvous failed")
+        return Fake()
+
+    def stage2_only(rt_):
+        # on the healthy rank the probe's alloc / barrier calls would need a GPU: fail it on purpose as well, later
+        raise RuntimeError("probe kernel unavailable on CPU")
+
+    got = symm.create_or_fallback(rt, factory=factory if rank == 1 else stage2_only)
+    torch.save(got is None, f"{out}.{rank}")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_comm_probe_falls_back_on_every_rank_together():
+    with tempfile.TemporaryDirectory() as d:
+        out = os.path.join(d, "probe")
+        mp.spawn(_worker_probe, args=(WORLD, os.path.join(d, "rdv"), out), nprocs=WORLD, join=True)
+        assert torch.load(f"{out}.0") is True and torch.load(f"{out}.1") is True

@@ -47,28 +47,84 @@ def test_mx_gemm_matches_emulation(m, n, k):
     assert _rel(y, x.float() @ w.float().T) < 6e-2             # and close to the unquantised product
 
 
-def test_mx_mlp_forward_backward():
-    from them_bones_b200 import ops
+def _unpack_sf2(sf, rows, k, group):
+    """Scale chunks of an operand with ``group`` rows per tile -> [rows, ceil(k/32)] biased exponents."""
+    kb = -(-k // 128)
+    groups = -(-rows // group)
+    chunks = -(-group // 128)
+    t = sf.view(groups, kb, chunks, 32, 4, 4)          # [g, kb, chunk, r%32, (r%128)/32, ksub]
+    t = t.permute(0, 2, 4, 3, 1, 5).reshape(groups, chunks * 128, kb * 4)[:, :group]
+    return t.reshape(groups * group, kb * 4)[:rows, :-(-k // 32)]
+
+
+def _deq(q, e, axis):
+    from them_bones_b200.ref import functional as RF
+    return RF.mx_dequantize(q.view(torch.float8_e4m3fn), e, axis)
+
+
+@pytest.mark.parametrize("group_r,group_c", [(128, 128), (224, 256)])
+def test_dual_quantiser_matches_emulation(group_r, group_c):
+    from them_bones_b200.ops import mxfp8 as MX
+    from them_bones_b200.ref import functional as RF
+    torch.manual_seed(0)
+    r, c = 320, 512
+    x = (torch.randn(r, c, device="cuda") * torch.logspace(-4, 2, r, device="cuda")[:, None]).bfloat16()
+    x[5, 64:96] = 0
+    x[32:64, 7] = 0
+    qr, sfr, qc, sfc = MX.quant2(x, col=True, group_r=group_r, group_c=group_c)
+    rr, er = RF.mx_quantize(x.float(), -1)
+    rc, ec = RF.mx_quantize(x.float(), 0)                       # scales [c, r/32]
+    torch.cuda.synchronize()
+    assert torch.equal(_unpack_sf2(sfr, r, c, group_r), er)
+    assert torch.equal(qr.view(torch.float8_e4m3fn).float(), rr.float())
+    assert torch.equal(_unpack_sf2(sfc, c, r, group_c), ec)
+    assert torch.equal(qc.view(torch.float8_e4m3fn).float(), rc.float())
+
+
+@pytest.mark.parametrize("bn", [160, 224, 256])
+@pytest.mark.parametrize("m,n,k", [(256, 320, 512), (384, 1280, 1280), (1000, 5120, 1280), (8192, 1280, 5120)])
+def test_pair_gemm_matches_emulation(m, n, k, bn):
     from them_bones_b200.ops import _lib as L
     from them_bones_b200.ops import mxfp8 as MX
-    torch.manual_seed(2)
-    m, c, f = 512, 256, 1024
-    x = torch.randn(m, c, device="cuda").bfloat16().requires_grad_(True)
-    w_fc = (torch.randn(f, c, device="cuda") * 0.06).bfloat16().requires_grad_(True)
-    w_proj = (torch.randn(c, f, device="cuda") * 0.03).bfloat16().requires_grad_(True)
-    res = torch.randn(m, c, device="cuda").bfloat16()
-    g = torch.randn(m, c, device="cuda").bfloat16()
-    y = MX.mlp(x, w_fc, w_proj, res)
-    y.backward(g)
-    got = (y.detach(), x.grad.clone(), w_fc.grad.clone(), w_proj.grad.clone())
-    for t in (x, w_fc, w_proj):
-        t.grad = None
-    yr = ops._MxMlpRef.apply(x, w_fc, w_proj) + res
-    yr.backward(g)
+    from them_bones_b200.ref import functional as RF
+    torch.manual_seed(1)
+    x = torch.randn(m, k, device="cuda").bfloat16()
+    w = (torch.randn(n, k, device="cuda") * 0.05).bfloat16()
+    xq, xsf, _, _ = MX.quant2(x)
+    wq, wsf, _, _ = MX.quant2(w, group_r=bn)
+    y = MX.gemm2(xq, xsf, wq, wsf, m, n, k, bn=bn)[0]
     torch.cuda.synchronize()
     L.check_error_word()
-    assert _rel(got[0], yr) < 2e-2
-    assert _rel(got[1], x.grad) < 6e-2 and _rel(got[2], w_fc.grad) < 6e-2 and _rel(got[3], w_proj.grad) < 6e-2
-    # and the whole thing approximates the bf16 MLP
-    yb = torch.relu(x.float() @ w_fc.float().T).square() @ w_proj.float().T + res.float()
-    assert _rel(got[0], yb) < 6e-2
+    ref = RF.mx_qdq(x.float(), -1) @ RF.mx_qdq(w.float(), -1).T
+    assert _rel(y, ref) < 5e-3, _rel(y, ref)                    # bf16 output rounding only
+
+
+@pytest.mark.parametrize("epi", ["relu2", "res", "mul2sqrt"])
+def test_pair_gemm_quantising_epilogues(epi):
+    """The epilogue's bf16 result and its two MXFP8 copies (along N and along M) against the emulation applied to the
+    stored bf16 tensor."""
+    from them_bones_b200.ops import _lib as L
+    from them_bones_b200.ops import mxfp8 as MX
+    from them_bones_b200.ref import functional as RF
+    torch.manual_seed(2)
+    m, n, k = 640, 1280, 256
+    x = torch.randn(m, k, device="cuda").bfloat16()
+    w = (torch.randn(n, k, device="cuda") * 0.1).bfloat16()
+    r = torch.rand(m, n, device="cuda").bfloat16()
+    xq, xsf, _, _ = MX.quant2(x)
+    wq, wsf, _, _ = MX.quant2(w, group_r=MX.BN_FWD)
+    code = {"relu2": MX.GE_RELU2, "res": MX.GE_BF16_RES, "mul2sqrt": MX.GE_MUL_2SQRT}[epi]
+    d, dq, dsf, dt, dtsf = MX.gemm2(xq, xsf, wq, wsf, m, n, k, epi=code, r=None if epi == "relu2" else r, beta=0.5,
+                                    want_q=True, want_t=True, dq_group=128, dt_group=256)
+    torch.cuda.synchronize()
+    L.check_error_word()
+    acc = RF.mx_qdq(x.float(), -1) @ RF.mx_qdq(w.float(), -1).T
+    ref = {"relu2": torch.relu(acc).square(), "res": acc + 0.5 * r.float(), "mul2sqrt": acc * 2 * r.float().sqrt()}[epi]
+    assert _rel(d, ref) < 6e-3, _rel(d, ref)
+    # the quantised copies describe the stored tensor exactly
+    qr, er = RF.mx_quantize(d.float(), -1)
+    assert torch.equal(_unpack_sf2(dsf, m, n, 128), er)
+    assert torch.equal(dq.view(torch.float8_e4m3fn).float(), qr.float())
+    qc, ec = RF.mx_quantize(d.float(), 0)
+    assert torch.equal(_unpack_sf2(dtsf, n, m, 256), ec)
+    assert torch.equal(dt.view(torch.float8_e4m3fn).float(), qc.float())

@@ -1,0 +1,627 @@
+// MXFP8 block-scaled GEMM on CTA pairs: `tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale`, 256 x BN output tiles.
+//
+//   D[b] = epilogue( alpha * (A_q 2^sfa)[b] * (B_q 2^sfb)[b]^T , R[b] )        A: logical [M, K]   B: logical [N, K]
+//
+// Elements are E4M3, one UE8M0 scale per 32 elements of K (OCP microscaling).  Either operand may be K-major (K
+// contiguous: forward and input-gradient GEMMs) or MN-major (the M / N index contiguous: the weight-gradient GEMM
+// `dW = dY^T X` contracts over tokens and reads both activations as stored, quantised along the token axis).
+//
+// Why pairs: an fp8 MMA retires twice the flops of a bf16 one per operand byte the SM has to pull out of L2.  A single
+// CTA with a 128 x 160 tile needs about 115 bytes per clock from L2 at full tensor rate and is bound by that path at
+// half of it.  In a pair each CTA loads its own 128 rows of A and only half of the B tile; both tensor cores read both
+// halves through the cluster's shared-memory window, which cuts the demand to 64-83 bytes per clock.
+//
+// Tile N (`bn`, a run-time argument): 160 or 224 with two accumulators in TMEM (the epilogue of a tile overlaps the MMAs
+// of the next), or 256 with one (weight gradients: the contraction is tens of thousands long, the epilogue a few per
+// cent).  TMEM columns: accumulators from 0, A scales at 496, B scales at 500.
+//
+// Scales in global memory are 512-byte chunks, one per (128 rows, 128 of K), in the image `tcgen05.cp.32x128b.warpx4`
+// spreads over four TMEM columns: byte (r % 32) * 16 + ((r % 128) / 32) * 4 + (k % 128) / 32.  Chunks of an operand
+// with `group` rows per tile (128 for A, `bn` for B) are ordered [row group][K block][chunk in group], so the scales of
+// one tile and K block are one contiguous run (512 bytes for A, 1024 for B) fetched by one TMA copy into each CTA's own
+// shared memory; the leader's `tcgen05.cp.cta_group::2` then moves them into both CTAs' TMEM.
+//
+// Epilogues: bf16 / residual / ReLU^2 / ReLU^2-backward (acc * 2 sqrt(h)) / fp32 accumulate (split-K, vector atomics).
+// The first four can also emit the result re-quantised to MXFP8 -- along N (each thread owns 32 consecutive columns of
+// its row: one block of the next GEMM's K axis) and along M (32 consecutive rows are the 32 lanes of a warp: one
+// `redux.sync.max` per column gives every lane the block maximum) -- so a chain c_fc -> ReLU^2 -> c_proj and its
+// backward never re-read bf16 activations to quantise them, and the weight-gradient GEMMs find their token-axis
+// operands ready.
+//
+// Protocol (every wait bounded, see common.cuh) as in gemm_bf16_2cta.cu: each CTA's producer thread issues its TMA loads
+// in the `.cta_group::2` form that credits the leader's `full[s]`; the leader's MMA thread copies the scales, issues the
+// pair MMAs and commits with `.multicast::cluster` to `empty[s]` / `tmem_full[a]` of both CTAs; sixteen epilogue warps
+// per CTA (the quantising epilogues are instruction-bound: eight warps took 2.4 times the MMA time of a K = 1280 tile)
+// drain their 128 rows and arrive on the leader's `tmem_empty[a]`.  No TMA load uses cluster multicast.
+//
+// Reference counterparts: fp8 fused MLP forward / backward (round2/source/kernels/nki_mlp_fused8.py:508-570), fp8
+// projections (nki_attn_tt8g.py:616-623) and the fp8 weight-gradient GEMM (nki_dw8.py:239); per-block scales replace
+// their per-tensor power-of-two scales.
+#include "common.cuh"
+#include "gemm_epilogue.cuh"
+
+namespace bones {
+
+struct Mx2Params {
+  int M, N, K, batch;
+  int a_major, b_major;
+  int bn;                       // pair tile N
+  int acc_stages;               // 2 (bn <= 224) or 1
+  int epi;                      // GemmEpi numbering: 0 bf16, 1 + beta*R, 2 ReLU^2, 3 fp32 +=, 4 * 2 sqrt(R)
+  float alpha, beta;
+  void* D;                      // bf16 (fp32 with epi 3); may be null when only quantised outputs are wanted
+  long long ldd, strideD;
+  const void* R;
+  long long ldr, strideR;
+  uint8_t* Dq;                  // optional [batch, M, N] E4M3, quantised along N ...
+  uint8_t* Dsf;                 // ... with scale chunks of an operand with `dq_group` rows per tile and K = N
+  int dq_group;
+  long long dsf_batch;          // bytes between batches of Dsf
+  uint8_t* Dt;                  // optional [batch, M, N] E4M3, quantised along M ...
+  uint8_t* Dtsf;                // ... with scale chunks of an operand with rows = N, `dt_group` rows per tile, K = M
+  int dt_group;
+  long long dtsf_batch;
+  int sfa_rows_per_batch;       // rows of the [*, 256] scale maps per batch
+  int sfb_rows_per_batch;
+  int* err;
+  int tiles_m, tiles_n;
+  int splits, atomic, wide;
+};
+
+constexpr int QM = 256, QK = 128, QSTAGES = 6;
+constexpr uint32_t QA_BYTES = 128 * QK;            // 16384
+constexpr uint32_t QB_BYTES = 128 * QK;            // up to 128 rows (K-major: bn / 2 rows; MN-major: 128 K rows)
+constexpr uint32_t QSFA_BYTES = 512, QSFB_BYTES = 1024;
+constexpr uint32_t QSTAGE_STRIDE = 34816;          // 34 KB >= 16384 + 16384 + 512 + 1024, tiles stay 1024-aligned
+constexpr uint32_t QTMEM_SFA = 496, QTMEM_SFB = 500;
+constexpr int kGroupMq = 8;
+
+__device__ __forceinline__ void decode_tile_q(int tile, int tiles_m, int tiles_n, int& b, int& mb, int& nb) {
+  const int per_batch = tiles_m * tiles_n;
+  b = tile / per_batch;
+  const int rem = tile - b * per_batch;
+  const int group_size = kGroupMq * tiles_n;
+  const int gid = rem / group_size;
+  const int first_m = gid * kGroupMq;
+  const int gsz = min(tiles_m - first_m, kGroupMq);
+  const int in_group = rem - gid * group_size;
+  mb = first_m + in_group % gsz;
+  nb = in_group / gsz;
+}
+
+__device__ __forceinline__ uint32_t q_cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void q_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void q_mbar_arrive_cluster(uint32_t local_bar, uint32_t cta) {
+  asm volatile(
+      "{\n"
+      ".reg .b32 rem;\n"
+      "mapa.shared::cluster.u32 rem, %0, %1;\n"
+      "mbarrier.arrive.shared::cluster.b64 _, [rem];\n"
+      "}\n" ::"r"(local_bar),
+      "r"(cta)
+      : "memory");
+}
+// Pair-mode TMA loads: the destination is this CTA's shared memory, the transaction bytes go to the leader's barrier.
+__device__ __forceinline__ void q_tma_3d(uint32_t dst, const CUtensorMap* m, uint32_t bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(m)), "r"(bar & 0xFEFFFFFFu), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void q_tma_2d(uint32_t dst, const CUtensorMap* m, uint32_t bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(m)), "r"(bar & 0xFEFFFFFFu), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void q_umma_mxf8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate,
+                                                 uint32_t sfa_tmem, uint32_t sfb_tmem) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+// shared -> TMEM copy of 32 lanes x 128 bits, replicated to the four sub-partitions, in both CTAs of the pair (each from
+// its own shared memory at the descriptor's offset)
+__device__ __forceinline__ void q_cp_sf_pair(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void q_commit_pair(uint32_t bar) {
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"(mask)
+               : "memory");
+}
+
+// smallest power of two 2^e with amax / 2^e <= 448 = 1.75 * 2^8; returns 2^-e and the biased exponent
+__device__ __forceinline__ float q_scale_pow2(float amax, int& biased) {
+  if (!(amax > 0.f)) { biased = 0; return 0.f; }
+  const uint32_t bits = __float_as_uint(amax);
+  int e = (int)((bits >> 23) & 0xff) - 127 - 8;
+  if ((bits & 0x7fffffu) > 0x600000u) e += 1;
+  e = max(-127, min(127, e));
+  biased = e + 127;
+  return __uint_as_float((uint32_t)(127 - e) << 23);
+}
+__device__ __forceinline__ uint32_t q_pack_e4m3x4(float a, float b, float c, float d) {
+  const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return (uint32_t)lo | ((uint32_t)hi << 16);
+}
+// byte offset of the scale of (row r, contraction index k) in an operand with `kblocks` K blocks of 128 and `group` rows
+// per tile
+__device__ __host__ __forceinline__ size_t q_sf_offset(long long r, long long k, long long kblocks, int group) {
+  const long long g = r / group, t = r - g * group;
+  const int chunks = (group + 127) >> 7;
+  return (size_t)(((g * kblocks + (k >> 7)) * chunks + (t >> 7)) * 512 + (t & 31) * 16 + ((t & 127) >> 5) * 4 + ((k & 127) >> 5));
+}
+
+// One warp, lane = row, v = the 32 values of columns [col0, col0 + 32) of that row.
+// Row copy: the thread's 32 values are one block; 32 bytes and one scale byte per thread.
+__device__ __forceinline__ void q_emit_row(const float (&v)[32], uint8_t* q_dst, uint8_t* sf_dst, bool ok) {
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(v[j]));
+  int biased;
+  const float inv = q_scale_pow2(amax, biased);
+  if (ok) {
+    uint32_t o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = q_pack_e4m3x4(v[4 * j] * inv, v[4 * j + 1] * inv, v[4 * j + 2] * inv, v[4 * j + 3] * inv);
+    *reinterpret_cast<uint4*>(q_dst) = make_uint4(o[0], o[1], o[2], o[3]);
+    *reinterpret_cast<uint4*>(q_dst + 16) = make_uint4(o[4], o[5], o[6], o[7]);
+    *sf_dst = (uint8_t)biased;
+  }
+}
+// Column copy: a block is one column over the warp's 32 rows.  `redux.sync.max` on the magnitudes' bit patterns hands every
+// lane the block maximum of column j; lane j keeps it, derives that column's scale once, and the 32 inverse scales are
+// passed round with one shuffle each.  Lane j also stores the scale byte of column j (`sf_dst` is its address).
+__device__ __forceinline__ void q_emit_col(const float (&v)[32], int lane, uint8_t* q_dst, uint8_t* sf_dst, bool ok, bool sf_ok) {
+  uint32_t mine = 0u;
+#pragma unroll
+  for (int j = 0; j < 32; ++j) {
+    const uint32_t mx = __reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(v[j])));
+    if (lane == j) mine = mx;
+  }
+  int biased;
+  const float my_inv = q_scale_pow2(__uint_as_float(mine), biased);
+  uint32_t o[8];
+#pragma unroll
+  for (int j4 = 0; j4 < 8; ++j4) {
+    float s[4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) s[t] = v[j4 * 4 + t] * __shfl_sync(0xffffffffu, my_inv, j4 * 4 + t);
+    o[j4] = q_pack_e4m3x4(s[0], s[1], s[2], s[3]);
+  }
+  if (ok) {
+    *reinterpret_cast<uint4*>(q_dst) = make_uint4(o[0], o[1], o[2], o[3]);
+    *reinterpret_cast<uint4*>(q_dst + 16) = make_uint4(o[4], o[5], o[6], o[7]);
+  }
+  if (sf_ok) *sf_dst = (uint8_t)biased;
+}
+
+constexpr int kEpiWarps = 16;                      // four per 32-lane TMEM quadrant
+constexpr int kPairThreads = 64 + 32 * kEpiWarps;
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
+gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
+                       const __grid_constant__ CUtensorMap tma_sfa, const __grid_constant__ CUtensorMap tma_sfb, const Mx2Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* gen = smem_raw + (base - raw);
+  const uint32_t bars = base + QSTAGES * QSTAGE_STRIDE;
+  auto full = [&](int s) { return bars + 8u * s; };
+  auto empty = [&](int s) { return bars + 8u * (QSTAGES + s); };
+  auto tfull = [&](int a) { return bars + 8u * (2 * QSTAGES + a); };
+  auto tempty = [&](int a) { return bars + 8u * (2 * QSTAGES + 2 + a); };
+  const uint32_t tmem_slot = bars + 8u * (2 * QSTAGES + 4);
+  volatile uint32_t* tmem_slot_g = reinterpret_cast<volatile uint32_t*>(gen + QSTAGES * QSTAGE_STRIDE + 8 * (2 * QSTAGES + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + QSTAGES * QSTAGE_STRIDE + 8 * (2 * QSTAGES + 4) + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = q_cluster_ctarank();
+  const bool leader = rank == 0;
+  const int bn = p.bn, half_n = p.bn >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < QSTAGES; ++s) {
+      mbar_init(full(s), 2);        // leader: its own arrive.expect_tx + the peer's remote arrive
+      mbar_init(empty(s), 1);       // one multicast commit
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(tfull(a), 1);       // one multicast commit
+      mbar_init(tempty(a), 2 * kEpiWarps);     // leader: the epilogue warps of both CTAs
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tma_a);
+    tma_prefetch_desc(&tma_b);
+    tma_prefetch_desc(&tma_sfa);
+    tma_prefetch_desc(&tma_sfb);
+  }
+  q_cluster_sync();
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  q_cluster_sync();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot_g;
+
+  const int base_tiles = p.batch * p.tiles_m * p.tiles_n;
+  const int total = base_tiles * p.splits;
+  const int KB = p.K / QK;
+  const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+  // bytes each CTA brings per stage (the leader's barrier expects both CTAs' bytes)
+  const uint32_t b_bytes = p.b_major ? QB_BYTES : (uint32_t)half_n * QK;
+  const uint32_t cta_bytes = QA_BYTES + b_bytes + QSFA_BYTES + QSFB_BYTES;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < total && ok; tile += n_clusters) {
+        int b, mb, nb;
+        const int sp = tile / base_tiles;
+        decode_tile_q(tile - sp * base_tiles, p.tiles_m, p.tiles_n, b, mb, nb);
+        const int kb0 = (int)((long long)KB * sp / p.splits), kb1 = (int)((long long)KB * (sp + 1) / p.splits);
+        const int m0 = mb * QM + (int)rank * 128, n0 = nb * bn + (int)rank * half_n;
+        const int sfa_row = b * p.sfa_rows_per_batch + (2 * mb + (int)rank) * KB * 2;      // 256-byte rows, 2 per chunk
+        const int sfb_row = b * p.sfb_rows_per_batch + nb * KB * 4;                         // 4 per (tile, K block)
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(empty(stage), phase ^ 1u, abort_flag, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+          const uint32_t sa = base + stage * QSTAGE_STRIDE, sb = sa + QA_BYTES, ssfa = sb + QB_BYTES, ssfb = ssfa + QSFA_BYTES;
+          if (leader) mbar_arrive_expect_tx(full(stage), 2 * cta_bytes);
+          if (p.a_major == 0) q_tma_3d(sa, &tma_a, full(stage), kb * QK, m0, b);
+          else                q_tma_3d(sa, &tma_a, full(stage), m0, kb * QK, b);
+          if (p.b_major == 0) q_tma_3d(sb, &tma_b, full(stage), kb * QK, n0, b);
+          else                q_tma_3d(sb, &tma_b, full(stage), n0, kb * QK, b);
+          q_tma_2d(ssfa, &tma_sfa, full(stage), 0, sfa_row + kb * 2);
+          q_tma_2d(ssfb, &tma_sfb, full(stage), 0, sfb_row + kb * 4);
+          if (!leader) q_mbar_arrive_cluster(full(stage), 0);
+          if (++stage == QSTAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      // K-major: 32 bytes of K per MMA step (descriptor unit 16 bytes); MN-major: 32 K rows of 128 bytes
+      const uint32_t a_step = p.a_major ? (32 * 128) >> 4 : 32 >> 4;
+      const uint32_t b_step = p.b_major ? (32 * 128) >> 4 : 32 >> 4;
+      const uint32_t a_lbo = p.a_major ? 128 * 128 : 0, b_lbo = p.b_major ? 128 * 128 : 0;
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < total && ok; tile += n_clusters) {
+        if (!mbar_wait(tempty(acc), acc_phase ^ 1u, abort_flag, p.err, ERR_WAIT_TMEM_EMPTY)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem + (uint32_t)(acc * bn);
+        const int sp = tile / base_tiles;
+        const int kb0 = (int)((long long)KB * sp / p.splits), kb1 = (int)((long long)KB * (sp + 1) / p.splits);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(full(stage), phase, abort_flag, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = base + stage * QSTAGE_STRIDE, sb = sa + QA_BYTES, ssfa = sb + QB_BYTES, ssfb = ssfa + QSFA_BYTES;
+          q_cp_sf_pair(tmem + QTMEM_SFA, umma_smem_desc(ssfa, 0, 128, kLayoutNone));
+          q_cp_sf_pair(tmem + QTMEM_SFB, umma_smem_desc(ssfb, 0, 128, kLayoutNone));
+          q_cp_sf_pair(tmem + QTMEM_SFB + 4, umma_smem_desc(ssfb + 512, 0, 128, kLayoutNone));
+          const uint64_t adesc = umma_smem_desc(sa, a_lbo, 1024, kLayoutSw128);
+          const uint64_t bdesc = umma_smem_desc(sb, b_lbo, 1024, kLayoutSw128);
+#pragma unroll
+          for (int k = 0; k < QK / 32; ++k) {
+            const uint32_t idesc = umma_idesc_mxf8(QM, (uint32_t)bn, 0, 0, (uint32_t)p.a_major, (uint32_t)p.b_major, (uint32_t)k, (uint32_t)k);
+            q_umma_mxf8_pair(d_tmem, adesc + (uint64_t)(k * a_step), bdesc + (uint64_t)(k * b_step), idesc, ((kb - kb0) | k) ? 1u : 0u,
+                             tmem + QTMEM_SFA, tmem + QTMEM_SFB);
+          }
+          q_commit_pair(empty(stage));
+          if (++stage == QSTAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        q_commit_pair(tfull(acc));
+        if (++acc == p.acc_stages) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else {
+    // epilogue warps: four per 32-lane TMEM quadrant; the four of a quadrant take every fourth 32-column chunk
+    const int q = warp & 3, sub = (warp - 2) >> 2;
+    const int nchunks = bn >> 5;
+    const bool f32out = p.epi == GE_ACC_F32;
+    const bool need_r = p.epi == GE_BF16_RES || p.epi == GE_MUL_2SQRT;
+    const bool quant = p.Dq != nullptr || p.Dt != nullptr;
+    const long long kblocks_n = (p.N + 127) >> 7, kblocks_m = (p.M + 127) >> 7;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = cluster_id; tile < total; tile += n_clusters) {
+      int b, mb, nb;
+      decode_tile_q(tile % base_tiles, p.tiles_m, p.tiles_n, b, mb, nb);
+      const int row0 = mb * QM + (int)rank * 128 + q * 32;
+      const int row = row0 + lane;
+      const bool row_ok = row < p.M;
+      const long long drow = (long long)b * p.strideD + (long long)row * p.ldd;
+      const long long rrow = (long long)b * p.strideR + (long long)row * p.ldr;
+      const bool got = mbar_wait(tfull(acc), acc_phase, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
+      if (!__all_sync(0xffffffffu, got)) break;
+      tc_fence_after();
+#pragma unroll 1
+      for (int c = sub; c < nchunks; c += kEpiWarps / 4) {
+        uint32_t r[32];
+        const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * bn + c * 32);
+        __syncwarp();
+        BONES_TMEM_LD32(taddr, r);
+        tmem_ld_wait();
+        const int col0 = nb * bn + c * 32;
+        if (col0 >= p.N) continue;                 // warp-uniform: the ragged last tile's columns beyond N
+        if (!quant) {
+          if (row_ok) {
+            const size_t esz = f32out ? 4 : 2;
+            uint4 nopre[4];
+            gemm_store_chunk(r, p.epi, p.alpha, p.beta, p.wide != 0, p.splits > 1 || p.atomic, reinterpret_cast<uint8_t*>(p.D) + (drow + col0) * esz,
+                             reinterpret_cast<const uint8_t*>(p.R) + (rrow + col0) * esz, false, nopre, min(32, p.N - col0));
+          }
+          continue;
+        }
+        // quantising epilogues: N is a multiple of 32, so the chunk is whole
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = row_ok ? __uint_as_float(r[j]) : 0.f;
+        if (p.alpha != 1.0f) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
+        }
+        if (need_r && row_ok) {
+          const __nv_bfloat16* R = reinterpret_cast<const __nv_bfloat16*>(p.R) + rrow + col0;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint4 u = *reinterpret_cast<const uint4*>(R + j * 8);
+            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              const float2 f = unpack_bf16(w[t]);
+              if (p.epi == GE_BF16_RES) {
+                v[j * 8 + 2 * t] = fmaf(p.beta, f.x, v[j * 8 + 2 * t]);
+                v[j * 8 + 2 * t + 1] = fmaf(p.beta, f.y, v[j * 8 + 2 * t + 1]);
+              } else {
+                v[j * 8 + 2 * t] *= 2.0f * sqrt_fast(f.x);
+                v[j * 8 + 2 * t + 1] *= 2.0f * sqrt_fast(f.y);
+              }
+            }
+          }
+        } else if (p.epi == GE_RELU2) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float t = fmaxf(v[j], 0.0f);
+            v[j] = t * t;
+          }
+        }
+        // the bf16 rounding comes first: the quantised copies describe the tensor that is stored
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 u;
+          u.x = pack_bf16(v[j * 8 + 0], v[j * 8 + 1]);
+          u.y = pack_bf16(v[j * 8 + 2], v[j * 8 + 3]);
+          u.z = pack_bf16(v[j * 8 + 4], v[j * 8 + 5]);
+          u.w = pack_bf16(v[j * 8 + 6], v[j * 8 + 7]);
+          if (p.D != nullptr && row_ok) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D) + drow + col0 + j * 8) = u;
+          const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const float2 f = unpack_bf16(w[t]);
+            v[j * 8 + 2 * t] = f.x;
+            v[j * 8 + 2 * t + 1] = f.y;
+          }
+        }
+        const long long qoff = ((long long)b * p.M + row) * p.N + col0;
+        if (p.Dq != nullptr)
+          q_emit_row(v, p.Dq + qoff, p.Dsf + (size_t)b * p.dsf_batch + q_sf_offset(row, col0, kblocks_n, p.dq_group), row_ok);
+        if (p.Dt != nullptr)     // rows beyond M contribute zeros to their column blocks
+          q_emit_col(v, lane, p.Dt + qoff, p.Dtsf + (size_t)b * p.dtsf_batch + q_sf_offset(col0 + lane, row0, kblocks_m, p.dt_group),
+                     row_ok, row0 < p.M);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) q_mbar_arrive_cluster(tempty(acc), 0);
+      if (++acc == p.acc_stages) { acc = 0; acc_phase ^= 1u; }
+    }
+  }
+
+  // tear-down: both CTAs of the pair always arrive here (every wait above is bounded)
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  q_cluster_sync();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Quantiser for both axes in one pass: x bf16 [R, C] -> q_row (blocks of 32 along C) and q_col (blocks of 32 along R),
+// each with its scale chunks.  Same thread mapping as the GEMM epilogue: a warp takes 32 rows, a lane one row and 32
+// consecutive columns at a time (64 contiguous bytes: two full sectors), two such chunks per warp.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kQuantChunks = 2;                    // 32-column chunks per warp (64 columns)
+__global__ void __launch_bounds__(256, 2)
+mx_quant_dual_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t* __restrict__ qr, uint8_t* __restrict__ sfr, int group_r,
+                     uint8_t* __restrict__ qc, uint8_t* __restrict__ sfc, int group_c, long long R, long long C) {
+  const int lane = threadIdx.x & 31;
+  const long long tiles_c = C / (32 * kQuantChunks);
+  const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long tr = wid / tiles_c, tc = wid - tr * tiles_c;
+  const long long row0 = tr * 32, row = row0 + lane;
+  if (row0 >= R) return;                                        // warp-uniform
+  const bool row_ok = row < R;
+  const long long kb_c = (C + 127) >> 7, kb_r = (R + 127) >> 7;
+  uint4 raw[kQuantChunks][4];
+#pragma unroll
+  for (int c = 0; c < kQuantChunks; ++c) {
+    const __nv_bfloat16* src = x + row * ldx + (tc * kQuantChunks + c) * 32;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) raw[c][j] = row_ok ? *reinterpret_cast<const uint4*>(src + j * 8) : make_uint4(0u, 0u, 0u, 0u);
+  }
+#pragma unroll
+  for (int c = 0; c < kQuantChunks; ++c) {
+    const long long col0 = (tc * kQuantChunks + c) * 32;
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t w[4] = {raw[c][j].x, raw[c][j].y, raw[c][j].z, raw[c][j].w};
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float2 f = unpack_bf16(w[t]);
+        v[j * 8 + 2 * t] = f.x;
+        v[j * 8 + 2 * t + 1] = f.y;
+      }
+    }
+    if (qr != nullptr) q_emit_row(v, qr + row * C + col0, sfr + q_sf_offset(row, col0, kb_c, group_r), row_ok);
+    if (qc != nullptr) q_emit_col(v, lane, qc + row * C + col0, sfc + q_sf_offset(col0 + lane, row0, kb_r, group_c), row_ok, true);
+  }
+}
+
+static int tmap_operand_q(CUtensorMap* out, const void* ptr, int major, long long rows, long long K, long long ld, long long stride, int batch,
+                          int box_rows) {
+  uint64_t dims[3], strides[2];
+  uint32_t box[3];
+  if (major == 0) {
+    dims[0] = (uint64_t)K; dims[1] = (uint64_t)rows;
+    box[0] = QK; box[1] = (uint32_t)box_rows;
+  } else {
+    dims[0] = (uint64_t)rows; dims[1] = (uint64_t)K;
+    box[0] = 128; box[1] = QK;
+  }
+  dims[2] = (uint64_t)batch;
+  box[2] = 1;
+  strides[0] = (uint64_t)ld;
+  strides[1] = batch > 1 ? (uint64_t)stride : strides[0] * dims[1];
+  return make_tmap(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, ptr, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+// scale chunks seen as rows of 256 bytes; a box of `box_rows` rows is one K block's scales of one tile
+static int tmap_scales_q(CUtensorMap* out, const void* ptr, long long bytes, int box_rows) {
+  uint64_t dims[2] = {256, (uint64_t)(bytes / 256)};
+  uint64_t strides[1] = {256};
+  uint32_t box[2] = {256, (uint32_t)box_rows};
+  return make_tmap(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, ptr, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
+}  // namespace bones
+
+extern "C" {
+using namespace bones;
+
+// Bytes of the scale chunks of one operand: `rows` rows in tiles of `group` rows, contraction length K.
+long long bones_mx2_sf_bytes(long long rows, long long K, int group) {
+  return ((rows + group - 1) / group) * ((K + 127) >> 7) * ((group + 127) >> 7) * 512;
+}
+
+// x bf16 [R, C] -> optional row-quantised copy (qr, sfr: blocks along C, scale tiles of `group_r` rows) and optional
+// column-quantised copy (qc, sfc: blocks along R; its scale chunks describe an operand with rows = C, K = R, tiles of
+// `group_c` rows).  C a multiple of 128; a last, partial block of rows is quantised as a block of its own.
+int bones_mx2_quant(const void* x, long long ldx, void* qr, void* sfr, int group_r, void* qc, void* sfc, int group_c, long long R, long long C,
+                    void* stream) {
+  if ((C % 128) || (ldx % 8) || ((uintptr_t)x & 15)) return -2;
+  if (R == 0) return 0;
+  const long long warps = ((R + 31) / 32) * (C / (32 * kQuantChunks));
+  mx_quant_dual_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ldx, (uint8_t*)qr, (uint8_t*)sfr, group_r,
+                                                                                      (uint8_t*)qc, (uint8_t*)sfc, group_c, R, C);
+  return (int)cudaGetLastError();
+}
+
+// A_q: [batch, M, K] (a_major 0, lda = row pitch in bytes) or [batch, K, M] (a_major 1); likewise B_q with N.  sfa: scale
+// chunks with tiles of 128 rows; sfb: with tiles of `bn` rows.  D: bf16 [batch, M, N] (fp32 with epi 3; null when only
+// quantised outputs are wanted).  Dq / Dsf: the result quantised along N (scale tiles of `dq_group` rows, K = N);
+// Dt / Dtsf: quantised along M (scale chunks of an operand with rows = N in tiles of `dt_group`, K = M).
+int bones_gemm_mxfp8_pair(const void* Aq, const void* sfa, const void* Bq, const void* sfb, void* D, const void* R, void* Dq, void* Dsf,
+                          int dq_group, void* Dt, void* Dtsf, int dt_group, int M, int N, int K, int batch, long long lda, long long ldb,
+                          long long ldd, long long ldr, long long strideA, long long strideB, long long strideD, long long strideR, int a_major,
+                          int b_major, int epi, float alpha, float beta, int bn, int splits, int atomic, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 0;
+  if ((K % 128) || (lda % 16) || (ldb % 16) || ((uintptr_t)Aq & 15) || ((uintptr_t)Bq & 15) || ((uintptr_t)sfa & 15) || ((uintptr_t)sfb & 15))
+    return -2;
+  if (bn != 160 && bn != 224 && bn != 256) return -3;
+  if (b_major && bn != 256) return -4;          // an MN-major B tile is one 128-byte swizzle atom per CTA
+  const bool f32out = epi == GE_ACC_F32;
+  if (!(epi == GE_BF16 || epi == GE_BF16_RES || epi == GE_RELU2 || epi == GE_ACC_F32 || epi == GE_MUL_2SQRT)) return -5;
+  if ((Dq || Dt) && (f32out || (N % 32) || ((Dq != nullptr) && (N % 128)) || ((Dt != nullptr) && (M % 32)))) return -6;
+  if (D && (ldd % (f32out ? 4 : 8))) return -7;
+  if (!D && !Dq && !Dt) return -8;
+  Mx2Params p;
+  p.M = M; p.N = N; p.K = K; p.batch = batch;
+  p.a_major = a_major; p.b_major = b_major;
+  p.bn = bn;
+  p.acc_stages = (2 * bn <= (int)QTMEM_SFA) ? 2 : 1;
+  p.epi = epi; p.alpha = alpha; p.beta = beta;
+  p.D = D; p.ldd = ldd; p.strideD = strideD;
+  p.R = R ? R : D; p.ldr = R ? ldr : ldd; p.strideR = R ? strideR : strideD;
+  p.Dq = (uint8_t*)Dq; p.Dsf = (uint8_t*)Dsf; p.dq_group = dq_group > 0 ? dq_group : 128;
+  p.Dt = (uint8_t*)Dt; p.Dtsf = (uint8_t*)Dtsf; p.dt_group = dt_group > 0 ? dt_group : 128;
+  p.dsf_batch = bones_mx2_sf_bytes(M, N, p.dq_group);
+  p.dtsf_batch = bones_mx2_sf_bytes(N, M, p.dt_group);
+  p.err = error_word();
+  const long long wal = f32out ? 8 : 16;
+  p.wide = (D && (ldd % wal == 0) && (strideD % wal == 0) && (!R || (ldr % wal == 0 && strideR % wal == 0)) && (((uintptr_t)D & 31) == 0) &&
+            (!R || ((uintptr_t)R & 31) == 0)) ? 1 : 0;
+  p.tiles_m = (M + QM - 1) / QM;
+  p.tiles_n = (N + bn - 1) / bn;
+  const int KB = K / QK;
+  const long long sfa_bytes = bones_mx2_sf_bytes(M, K, 128), sfb_bytes = bones_mx2_sf_bytes(N, K, bn);
+  p.sfa_rows_per_batch = (int)(sfa_bytes / 256);
+  p.sfb_rows_per_batch = (int)(sfb_bytes / 256);
+  CUtensorMap ta, tb, tsa, tsb;
+  int rc = tmap_operand_q(&ta, Aq, a_major, M, K, lda, strideA, batch, 128);
+  if (rc) return rc;
+  rc = tmap_operand_q(&tb, Bq, b_major, N, K, ldb, strideB, batch, bn / 2);
+  if (rc) return rc;
+  rc = tmap_scales_q(&tsa, sfa, sfa_bytes * batch, 2);
+  if (rc) return rc;
+  rc = tmap_scales_q(&tsb, sfb, sfb_bytes * batch, 4);
+  if (rc) return rc;
+  constexpr size_t smem = (size_t)QSTAGES * QSTAGE_STRIDE + 8 * (2 * QSTAGES + 4) + 16 + 1024;
+  static bool attr_done = false;
+  if (!attr_done) {
+    BONES_CHECK(cudaFuncSetAttribute(gemm_mxfp8_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr_done = true;
+  }
+  int dev = 0, sms = 0;
+  BONES_CHECK(cudaGetDevice(&dev));
+  BONES_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const int pairs = sms / 2;
+  const int base_tiles = batch * p.tiles_m * p.tiles_n;
+  p.atomic = (atomic && f32out) ? 1 : 0;
+  p.splits = splits;
+  if (p.splits <= 0) {
+    p.splits = 1;
+    if (f32out && base_tiles < 4 * pairs && KB >= 16) {
+      long long best = -1;
+      for (int c = 1; c <= 32; ++c) {
+        if (c > KB / 4) break;
+        const long long waves = ((long long)base_tiles * c + pairs - 1) / pairs;
+        const long long cost = waves * (((long long)KB + c - 1) / c + 8) + (c > 1 ? 2 * c : 0);
+        if (best < 0 || cost < best) { best = cost; p.splits = c; }
+      }
+    }
+  }
+  if (p.splits > 1 && !f32out) p.splits = 1;
+  if (p.splits > KB) p.splits = KB;
+  const int total = base_tiles * p.splits;
+  const int clusters = total < pairs ? total : pairs;
+  gemm_mxfp8_pair_kernel<<<2 * clusters, kPairThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(ta, tb, tsa, tsb, p);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

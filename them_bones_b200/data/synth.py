@@ -116,18 +116,25 @@ class SynthLoader:
     ``inputs [local_windows, T] int32`` and ``targets [local_windows, T] int64``."""
 
     def __init__(self, vocab: int, seq_len: int, local_windows: int, *, rank: int = 0, seed: int = 0,
-                 doc_len=(128, 2048), zipf_s: float = 1.1, bos_id: int = 0, pin: bool = False, rule=None):
+                 doc_len=(128, 2048), zipf_s: float = 1.1, bos_id: int = 0, pin: bool = False, rule=None,
+                 shard_of: int = 0):
+        # shard_of = W > 0: every rank draws the same stream (the seed alone decides it), packs the whole job's step and
+        # keeps windows rank, rank + W, ...: the global batch of a step is then the same set of windows at any rank
+        # count, which makes losses comparable across 1, 2, 4 and 8 ranks.  0: one independent stream per rank.
         self.seq_len, self.local_windows, self.bos_id, self.vocab = seq_len, local_windows, bos_id, vocab
         self.mark_tail = 0.0                 # > 0: answer-span marks on the targets (set when the answer phase starts)
-        self.docs = ZipfDocs(vocab, zipf_s, doc_len, seed=seed * 1000003 + rank, bos_id=bos_id)
+        self.shard_of, self.rank = int(shard_of), rank
+        self.docs = ZipfDocs(vocab, zipf_s, doc_len, seed=seed * 1000003 + (0 if shard_of else rank), bos_id=bos_id)
         self.rule = rule
-        self.rows = PackedRows(self.docs, seq_len * local_windows, rule=rule)
+        self.rows = PackedRows(self.docs, seq_len * local_windows * max(1, self.shard_of), rule=rule)
         self.pin = pin and torch.cuda.is_available()
         self.epoch = 0
 
     def next_step(self):
         row = self.rows.next_row()
         x, y = slice_windows(row, self.seq_len, self.bos_id, mark_tail=self.mark_tail, vocab=self.vocab)
+        if self.shard_of:
+            x, y = x[self.rank::self.shard_of], y[self.rank::self.shard_of]
         xt, yt = torch.from_numpy(np.ascontiguousarray(x)), torch.from_numpy(np.ascontiguousarray(y))
         if self.pin:
             xt, yt = xt.pin_memory(), yt.pin_memory()

@@ -1,6 +1,8 @@
 """Kernel micro-benchmarks with roofline fractions.
 
     python -m them_bones_b200.ops.microbench gemm --m 8192 --n 8192 --k 8192 [--pair 1] [--layout nt|nn|tn]
+    python -m them_bones_b200.ops.microbench mxgemm --m 65536 --n 5120 --k 1280 [--bn 160|224|256] [--layout nt|tn] [--epi plain|relu2q|relu2qt]
+    python -m them_bones_b200.ops.microbench mxquant --rows 65536 --cols 1280
     python -m them_bones_b200.ops.microbench attn_fwd --b 4 --t 2048 --h 10
     python -m them_bones_b200.ops.microbench attn_bwd --b 4 --t 2048 --h 10
     python -m them_bones_b200.ops.microbench norm --rows 65536 --cols 1280
@@ -53,12 +55,14 @@ def timeit(fn, iters, warmup, flush):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "attn_fwd", "attn_bwd", "norm", "ce"])
+    ap.add_argument("what", choices=["gemm", "mxgemm", "mxquant", "attn_fwd", "attn_bwd", "norm", "ce"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
     ap.add_argument("--pair", type=int, default=1)
     ap.add_argument("--layout", default="nt")
+    ap.add_argument("--bn", type=int, default=0, help="mxgemm: pair tile N (0: the operator default)")
+    ap.add_argument("--epi", default="plain", help="mxgemm: plain | relu2q (+ copy quantised along N) | relu2qt (+ along M too)")
     ap.add_argument("--b", type=int, default=4)
     ap.add_argument("--t", type=int, default=2048)
     ap.add_argument("--h", type=int, default=10)
@@ -88,6 +92,40 @@ def main():
         ms = timeit(fn, a.iters, a.warmup, not a.no_flush)
         fl = 2.0 * m * n * k
         out.update(shape=[m, n, k], layout=a.layout, pair=a.pair, ms=ms, tflops=fl / ms / 1e9, frac_of_bf16_peak=fl / ms / 1e9 / tf)
+    elif a.what == "mxgemm":
+        from . import mxfp8 as MX
+        m, n, k = a.m, a.n, a.k
+        if a.layout == "tn":          # weight gradient: contraction over the token axis, both operands MN-major
+            _, _, aq, asf = MX.quant2(torch.randn(k, m, device="cuda", dtype=bf), row=False, col=True, group_c=128)
+            _, _, bq, bsf = MX.quant2(torch.randn(k, n, device="cuda", dtype=bf), row=False, col=True, group_c=MX.BN_WGRAD)
+            d = torch.zeros(m, n, device="cuda")
+            fn = lambda: MX.gemm2(aq, asf, bq, bsf, m, n, k, a_major=1, b_major=1, epi=MX.GE_ACC_F32, out=d, bn=MX.BN_WGRAD)  # noqa: E731
+        else:
+            bn = a.bn or MX.BN_FWD
+            aq, asf, _, _ = MX.quant2(torch.randn(m, k, device="cuda", dtype=bf))
+            bq, bsf, _, _ = MX.quant2(torch.randn(n, k, device="cuda", dtype=bf), group_r=bn)
+            d = torch.empty(m, n, device="cuda", dtype=bf)
+            dq = torch.empty(m, n, device="cuda", dtype=torch.uint8)
+            dsf = torch.zeros(MX.sf2_bytes(m, n, 128), device="cuda", dtype=torch.uint8)
+            dt = torch.empty(m, n, device="cuda", dtype=torch.uint8)
+            dtsf = torch.zeros(MX.sf2_bytes(n, m, 256), device="cuda", dtype=torch.uint8)
+            import ctypes
+            I, LL, F = ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+            epi = MX.GE_BF16 if a.epi == "plain" else MX.GE_RELU2
+            wq, wt = a.epi in ("relu2q", "relu2qt"), a.epi == "relu2qt"
+            fn = lambda: L.call("bones_gemm_mxfp8_pair", L.ptr(aq), L.ptr(asf), L.ptr(bq), L.ptr(bsf), L.ptr(d), L.ptr(None),  # noqa: E731
+                                L.ptr(dq if wq else None), L.ptr(dsf if wq else None), I(128), L.ptr(dt if wt else None),
+                                L.ptr(dtsf if wt else None), I(256), I(m), I(n), I(k), I(1), LL(k), LL(k), LL(n), LL(0), LL(0), LL(0),
+                                LL(0), LL(0), I(0), I(0), I(epi), F(1.0), F(1.0), I(bn), I(0), I(0), L.stream())
+        ms = timeit(fn, a.iters, a.warmup, not a.no_flush)
+        fl = 2.0 * m * n * k
+        out.update(shape=[m, n, k], layout=a.layout, bn=a.bn, epi=a.epi, ms=ms, tflops=fl / ms / 1e9, frac_of_bf16_peak=fl / ms / 1e9 / tf)
+    elif a.what == "mxquant":
+        from . import mxfp8 as MX
+        x = torch.randn(a.rows, a.cols, device="cuda", dtype=bf)
+        ms = timeit(lambda: MX.quant2(x, col=True), a.iters, a.warmup, not a.no_flush)
+        by = 4.0 * x.numel()                                    # one bf16 read, two fp8 writes
+        out.update(shape=[a.rows, a.cols], ms=ms, gbs=by / ms / 1e6, frac_of_hbm_peak=by / ms / 1e6 / hbm)
     elif a.what in ("attn_fwd", "attn_bwd"):
         from . import attention_bwd as AB
         from . import attention_native as AN

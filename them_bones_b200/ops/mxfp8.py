@@ -13,6 +13,7 @@ round1/source/train.py:2059-2076).
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -80,42 +81,164 @@ def linear(x2: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return gemm(xq, xsf, wq, wsf, x2.shape[0], w.shape[0], x2.shape[1])
 
 
+# ----------------------------------------------------------------------------------------------------------------
+# CTA-pair kernel (csrc/gemm_mxfp8_2cta.cu): both operand layouts, quantising epilogues for both axes, weight gradients
+# ----------------------------------------------------------------------------------------------------------------
+GE_BF16, GE_BF16_RES, GE_RELU2, GE_ACC_F32, GE_MUL_2SQRT = 0, 1, 2, 3, 4
+# Tile N of forward / input-gradient GEMMs.  224 keeps two accumulators in TMEM, so a tile's epilogue hides behind the
+# next tile's MMAs: the choice for a short contraction or a quantising epilogue.  256 (one accumulator) moves fewer
+# operand bytes per flop and wins once the contraction is long enough to dwarf the exposed epilogue (measured on
+# 65536 x 1280 x 5120: 2316 against 2212 TFLOP/s).  BONES_MX_BN=160|224|256 forces one value.
+_BN_FORCED = int(os.environ.get("BONES_MX_BN", 0))
+BN_FWD = _BN_FORCED or 224
+BN_WGRAD = 256                                             # weight gradients: MN-major operands, one accumulator
+
+
+def bn_for(k: int, heavy_epilogue: bool = False) -> int:
+    if _BN_FORCED:
+        return _BN_FORCED
+    return 256 if (k >= 2560 and not heavy_epilogue) else 224
+
+
+def sf2_bytes(rows: int, k: int, group: int = 128) -> int:
+    return -(-rows // group) * -(-k // 128) * -(-group // 128) * 512
+
+
+def quant2(x2: torch.Tensor, *, row: bool = True, col: bool = False, group_r: int = 128, group_c: int = 128):
+    """bf16 ``[R, C]`` -> ``(q_row, sf_row, q_col, sf_col)``: E4M3 copies quantised in 1 x 32 blocks along C (``row``) and
+    along R (``col``), each with UE8M0 scale chunks laid out for an operand whose tiles are ``group`` rows.  The column
+    copy's chunks describe the transposed operand (rows = C, contraction = R) that a weight-gradient GEMM reads."""
+    r, c = x2.shape
+    dev = x2.device
+    qr = sfr = qc = sfc = None
+    if row:
+        qr = torch.empty(r, c, dtype=torch.uint8, device=dev)
+        sfr = torch.zeros(sf2_bytes(r, c, group_r), dtype=torch.uint8, device=dev)
+    if col:
+        qc = torch.empty(r, c, dtype=torch.uint8, device=dev)
+        sfc = torch.zeros(sf2_bytes(c, r, group_c), dtype=torch.uint8, device=dev)
+    L.call("bones_mx2_quant", L.ptr(x2), _L(x2.stride(0)), L.ptr(qr), L.ptr(sfr), _I(group_r), L.ptr(qc), L.ptr(sfc), _I(group_c),
+           _L(r), _L(c), L.stream())
+    COUNTS["mx_quant"] += 1
+    return qr, sfr, qc, sfc
+
+
+def weight_q2(w: torch.Tensor, transposed: bool, bn: int):
+    """Quantised weight as the B operand of a GEMM with tile N ``bn``: ``x @ w.T`` (``transposed=False``: blocks along
+    ``in``) or ``dy @ w`` (``True``: ``w.T``, blocks along ``out``).  Cached until ``weights_updated()``."""
+    key = (w.data_ptr(), tuple(w.shape), transposed, bn)
+    ent = _CACHE.get(key)
+    if ent is None or ent[0] != _EPOCH[0] or ent[1] != w._version:
+        src = w.detach().t().contiguous() if transposed else w.detach()
+        q, sf, _, _ = quant2(src, group_r=bn)
+        ent = (_EPOCH[0], w._version, q, sf)
+        _CACHE[key] = ent
+    return ent[2], ent[3]
+
+
+def gemm2(aq, sfa, bq, sfb, m, n, k, *, a_major=0, b_major=0, epi=GE_BF16, r=None, alpha=1.0, beta=1.0, bn=None, out=None,
+          want_d=True, want_q=False, want_t=False, dq_group=128, dt_group=128, splits=0):
+    """``epilogue(alpha * A B^T)`` on the CTA-pair block-scaled kernel.  ``aq``: ``[m, k]`` (``a_major=0``) or ``[k, m]``
+    (``a_major=1``) E4M3; ``bq`` likewise with ``n``.  Returns ``(d, dq, dsf, dt, dtsf)``: the bf16 result (``out`` for the
+    fp32 accumulate form), its copy quantised along ``n`` and its copy quantised along ``m`` (None where not asked)."""
+    bn = bn or (BN_WGRAD if b_major else BN_FWD)
+    dev = aq.device
+    d = out
+    if d is None and want_d:
+        d = torch.empty(m, n, dtype=torch.float32 if epi == GE_ACC_F32 else torch.bfloat16, device=dev)
+    dq = dsf = dt = dtsf = None
+    if want_q:
+        dq = torch.empty(m, n, dtype=torch.uint8, device=dev)
+        dsf = torch.zeros(sf2_bytes(m, n, dq_group), dtype=torch.uint8, device=dev)
+    if want_t:
+        dt = torch.empty(m, n, dtype=torch.uint8, device=dev)
+        dtsf = torch.zeros(sf2_bytes(n, m, dt_group), dtype=torch.uint8, device=dev)
+    L.call("bones_gemm_mxfp8_pair", L.ptr(aq), L.ptr(sfa), L.ptr(bq), L.ptr(sfb), L.ptr(d), L.ptr(r), L.ptr(dq), L.ptr(dsf),
+           _I(dq_group), L.ptr(dt), L.ptr(dtsf), _I(dt_group), _I(m), _I(n), _I(k), _I(1), _L(aq.stride(0)), _L(bq.stride(0)),
+           _L(d.stride(0) if d is not None else 0), _L(r.stride(0) if r is not None else 0), _L(0), _L(0), _L(0), _L(0),
+           _I(a_major), _I(b_major), _I(epi), _F(alpha), _F(beta), _I(bn), _I(splits), _I(0), L.stream())
+    COUNTS["mx_gemm"] += 1
+    return d, dq, dsf, dt, dtsf
+
+
+def wgrad2(dyq_c, dysf_c, xq_c, xsf_c, w):
+    """``dW[out, in] += dY^T X`` with both activations quantised along the token axis (MN-major operands), accumulated in
+    fp32 straight into the weight's gradient slab (reference: the fp8 weight-gradient GEMM,
+    round2/source/kernels/nki_dw8.py:239, routed by ``dw8_grad`` round2/source/train.py:8185)."""
+    tokens, n_out = dyq_c.shape
+    n_in = xq_c.shape[1]
+    g = getattr(w, "main_grad", None)
+    ret = None
+    if g is None:
+        g = ret = torch.zeros(n_out, n_in, dtype=torch.float32, device=dyq_c.device)
+    gemm2(dyq_c, dysf_c, xq_c, xsf_c, n_out, n_in, tokens, a_major=1, b_major=1, epi=GE_ACC_F32, out=g, bn=BN_WGRAD)
+    return ret.to(w.dtype) if ret is not None else None
+
+
+def linear2(x2: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    xq, xsf, _, _ = quant2(x2)
+    bn = bn_for(x2.shape[1])
+    wq, wsf = weight_q2(w, False, bn)
+    return gemm2(xq, xsf, wq, wsf, x2.shape[0], w.shape[0], x2.shape[1], bn=bn)[0]
+
+
 def applies(x, w_fc, w_proj) -> bool:
     c, f = w_fc.shape[1], w_fc.shape[0]
     return x.dtype == torch.bfloat16 and c % 128 == 0 and f % 128 == 0
 
 
 class _MxMlpFn(torch.autograd.Function):
+    """Six block-scaled GEMMs and two quantiser passes per layer.  Forward: ``x`` is quantised once along both axes; the
+    c_fc epilogue applies ReLU^2 and emits ``h`` in bf16 (kept for the ReLU^2 backward) and in MXFP8 along the hidden axis
+    (c_proj's operand) and along the token axis (kept for ``dW_proj``).  Backward: ``dy`` is quantised along both axes;
+    ``dpre = (dy W_proj) * 2 sqrt(h)`` leaves its GEMM only in MXFP8, along the hidden axis for ``dx = dpre W_fc`` and along
+    the token axis for ``dW_fc``; both weight gradients are block-scaled GEMMs over the token axis."""
+
     @staticmethod
     def forward(ctx, x, w_fc, w_proj, residual):
         shp = x.shape
         x2 = C._c(x).view(-1, shp[-1])
         m, c = x2.shape
         f = w_fc.shape[0]
-        xq, xsf = quantize(x2)
-        wq, wsf = weight_q(w_fc, False)
-        h, hq, hsf = gemm(xq, xsf, wq, wsf, m, f, c, epi=MX_RELU2, want_q=True)
-        pq, psf = weight_q(w_proj, False)
-        r2 = C._c(residual).view(-1, w_proj.shape[0]) if residual is not None else None
-        y = gemm(hq, hsf, pq, psf, m, w_proj.shape[0], f, epi=MX_BF16_RES if r2 is not None else MX_BF16, r=r2)
-        ctx.save_for_backward(x2, h, w_fc, w_proj)
-        ctx.has_res, ctx.shp, ctx.ws = residual is not None, shp, (w_fc, w_proj)
+        pad = -m % 128
+        if pad:                                    # the token axis is a contraction axis in backward: whole K blocks
+            x2 = torch.nn.functional.pad(x2, (0, 0, 0, pad))
+        mp = m + pad
+        xq, xsf, xq_c, xsf_c = quant2(x2, col=True, group_c=BN_WGRAD)
+        bn1, bn2 = bn_for(c, True), bn_for(f)
+        wq, wsf = weight_q2(w_fc, False, bn1)
+        h, hq, hsf, hq_c, hsf_c = gemm2(xq, xsf, wq, wsf, mp, f, c, epi=GE_RELU2, want_q=True, want_t=True, dt_group=BN_WGRAD,
+                                        bn=bn1)
+        pq, psf = weight_q2(w_proj, False, bn2)
+        r2 = None
+        if residual is not None:
+            r2 = C._c(residual).view(-1, w_proj.shape[0])
+            if pad:
+                r2 = torch.nn.functional.pad(r2, (0, 0, 0, pad))
+        y = gemm2(hq, hsf, pq, psf, mp, w_proj.shape[0], f, epi=GE_BF16_RES if r2 is not None else GE_BF16, r=r2, bn=bn2)[0]
+        ctx.save_for_backward(xq_c, xsf_c, h, hq_c, hsf_c, w_fc, w_proj)
+        ctx.has_res, ctx.shp, ctx.ws, ctx.m = residual is not None, shp, (w_fc, w_proj), m
         COUNTS["mlp_mxfp8"] += 1
-        return y.view(shp[:-1] + (w_proj.shape[0],))
+        return y[:m].view(shp[:-1] + (w_proj.shape[0],))
 
     @staticmethod
     def backward(ctx, dy):
-        x2, h, w_fc, w_proj = ctx.saved_tensors
-        m, c = x2.shape
-        f = w_fc.shape[0]
+        xq_c, xsf_c, h, hq_c, hsf_c, w_fc, w_proj = ctx.saved_tensors
+        mp, f = h.shape
+        c = w_fc.shape[1]
+        m = ctx.m
         dy2 = C._c(dy).view(m, -1)
-        dyq, dysf = quantize(dy2)
-        ptq, ptsf = weight_q(w_proj, True)                   # [f, c]: dh = dy @ w_proj
-        dpre, dpq, dpsf = gemm(dyq, dysf, ptq, ptsf, m, f, c, epi=MX_MUL_2SQRT, r=h, want_q=True)
-        (g_proj,) = C._wgrad(dy2, h, (ctx.ws[1],))
-        ftq, ftsf = weight_q(w_fc, True)                     # [c, f]: dx = dpre @ w_fc
-        dx = gemm(dpq, dpsf, ftq, ftsf, m, c, f).view(ctx.shp)
-        (g_fc,) = C._wgrad(dpre, x2, (ctx.ws[0],))
+        if mp != m:
+            dy2 = torch.nn.functional.pad(dy2, (0, 0, 0, mp - m))
+        dyq, dysf, dyq_c, dysf_c = quant2(dy2, col=True, group_c=128)
+        bn1, bn2 = bn_for(c, True), bn_for(f)
+        ptq, ptsf = weight_q2(w_proj, True, bn1)                    # [f, c]: dh = dy @ w_proj
+        _, dpq, dpsf, dpq_c, dpsf_c = gemm2(dyq, dysf, ptq, ptsf, mp, f, c, epi=GE_MUL_2SQRT, r=h, want_d=False, want_q=True,
+                                             want_t=True, dt_group=128, bn=bn1)
+        g_proj = wgrad2(dyq_c, dysf_c, hq_c, hsf_c, ctx.ws[1])
+        ftq, ftsf = weight_q2(w_fc, True, bn2)                      # [c, f]: dx = dpre @ w_fc
+        dx = gemm2(dpq, dpsf, ftq, ftsf, mp, c, f, bn=bn2)[0][:m].view(ctx.shp)
+        g_fc = wgrad2(dpq_c, dpsf_c, xq_c, xsf_c, ctx.ws[0])
         return dx, g_fc, g_proj, (dy if ctx.has_res else None)
 
 

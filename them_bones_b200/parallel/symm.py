@@ -171,6 +171,61 @@ class PeerComm:
         return PeerTableExchange(self, tables)
 
 
+def create_or_fallback(rt, factory=None):
+    """Start-up probe of the peer-memory substrate: build the communicator, run one fused all-reduce and one epoch
+    barrier on known values, and let the ranks agree on the outcome.  Any rank's failure (no symmetric-memory support,
+    no peer access, a wrong sum, an expired wait) sends *every* rank to the library-collective path: returns ``None`` and
+    rank 0 prints one line (reference: ``configure_sharding`` probes its collectives on tiny tensors at start-up and
+    falls back, round1/source/train.py:9742-9774).  ``factory`` builds the communicator (tests inject a failing one)."""
+    def agree(flag: bool) -> bool:
+        ok = torch.tensor([1 if flag else 0], dtype=torch.int32)
+        if rt.ddp and rt.world > 1:
+            group = getattr(rt, "control_group", None)
+            if group is None:
+                ok = ok.to(rt.device)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        return int(ok[0]) == 1
+
+    def give_up(why: str):
+        if rt.rank == 0:
+            print(f"peer-memory communicator unavailable ({why or 'another rank failed its probe'}); "
+                  "using the library collectives", flush=True)
+        return None
+
+    # stage 1, local and cheap: what a rank can tell without talking to the others (a rank that failed alone in stage 2
+    # would leave the others waiting in the rendezvous, so obvious causes are caught here, where all ranks still agree)
+    why = ""
+    try:
+        import torch.distributed._symmetric_memory  # noqa: F401
+        if factory is None and rt.device_type == "cuda":
+            me = torch.cuda.current_device()
+            n_dev = torch.cuda.device_count()
+            if rt.world > n_dev:
+                why = f"{rt.world} ranks on {n_dev} visible GPUs"
+            elif not all(torch.cuda.can_device_access_peer(me, d) for d in range(n_dev) if d != me and d < rt.world):
+                why = "no peer access between the GPUs"
+    except Exception as exc:  # noqa: BLE001
+        why = f"{type(exc).__name__}: {exc}"
+    if not agree(not why):
+        return give_up(why)
+    comm = None
+    try:
+        comm = (factory or PeerComm.create)(rt)
+        probe = comm.alloc((256,), torch.float32, rt.device)
+        probe.fill_(float(rt.rank + 1))
+        comm.barrier()
+        got = comm.all_reduce_mean(probe)
+        comm.barrier()
+        torch.cuda.synchronize(rt.device)
+        L.check_error_word()
+        want = (rt.world + 1) / 2.0
+        if not bool(((got - want).abs() < 1e-5).all()):
+            why = f"fused all-reduce returned {float(got[0])}, expected {want}"
+    except Exception as exc:  # noqa: BLE001 - any failure of the substrate means: use the library collectives
+        why = f"{type(exc).__name__}: {exc}"
+    return comm if agree(not why) else give_up(why)
+
+
 class SoloComm(PeerComm):
     """The same fused optimizer kernels on one GPU: the "peer" list is this GPU alone, slabs are ordinary device
     tensors and the epoch barrier is a no-op.  The reduction kernels then read one gradient slab, apply the Muon

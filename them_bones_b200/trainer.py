@@ -55,7 +55,7 @@ class Trainer:
             use_fused = False                     # both live on the library-collective optimizer path
         if use_fused and rt.device_type == "cuda" and not ops.reference_path():
             from .parallel import symm
-            self.comm = symm.PeerComm.create(rt) if rt.world > 1 else symm.SoloComm(rt)
+            self.comm = symm.create_or_fallback(rt) if rt.world > 1 else symm.SoloComm(rt)
         kind = optimizer_kind or sw["OPT"]
         self.optimizer = setup_optimizer(model, hyper, kind=kind, comm=self.comm, finite_gate=sw["FINITE_GATE"],
                                          overlap_check=sw["OPT_OVERLAP_CHECK"], **extras) if kind == "lean" else \
