@@ -95,6 +95,7 @@ def parse():
     ap.add_argument("--total-batch", type=int, default=524288)
     ap.add_argument("--depth", type=int, default=20)
     ap.add_argument("--mlp", default=os.environ.get("BONES_MLP", "bf16"))
+    ap.add_argument("--attn-proj", default=os.environ.get("BONES_ATTN_PROJ", "bf16"))
     return ap.parse_args()
 
 
@@ -114,7 +115,7 @@ def run_ours(args, torch_path: bool = False):
     if rt.world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE is {rt.world}: launch with torch.distributed.run")
     cfg = GPTConfig(sequence_len=2048, vocab_size=65536, n_layer=args.depth, n_head=10, n_embd=1280, head_dim=128,
-                    doc_mask=True, mlp_precision=args.mlp)
+                    doc_mask=True, mlp_precision=args.mlp, attn_proj_precision=args.attn_proj)
     hyper = Hyper()
     # the global batch is fixed, so with more GPUs a rank's share shrinks below the preferred micro-batch
     from them_bones_b200.config import micro_batch_for
@@ -190,7 +191,7 @@ def run_ours(args, torch_path: bool = False):
             "config": {"model": "round1-dense 20Lx1280 10hx128 relu2-mlp x4 vocab65536" if args.depth == 20 else
                        f"dense {args.depth}Lx1280", "global_batch": tr.total_batch, "seq_len": 2048,
                        "parallelism": f"dp{rt.world}", "device_batch": tr.device_batch, "grad_accum": tr.grad_accum,
-                       "mlp_precision": args.mlp, "optimizer": "Muon+AdamW (sharded)",
+                       "mlp_precision": args.mlp, "attn_proj_precision": args.attn_proj, "optimizer": "Muon+AdamW (sharded)",
                        "l2": "inputs and activations per step exceed L2 (126 MB); two alternating batches"},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,

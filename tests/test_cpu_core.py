@@ -288,3 +288,44 @@ def test_micro_batch_follows_the_ranks_share_of_a_fixed_global_batch():
     assert got == [64, 64, 64, 32, 16]
     assert micro_batch_for(524288, 1, 48, 2048) == 32          # must divide the 256 windows of the step
     assert micro_batch_for(2048, 8, 64, 2048) == 1
+
+
+def test_mxfp8_linear_statement_trains_like_the_plain_one():
+    """The block-scaled projections' PyTorch statement (the CPU path and the GPU kernels' oracle): forward and all three
+    gradients stay within quantisation noise of the plain linear."""
+    import torch
+    from them_bones_b200 import ops
+    torch.manual_seed(0)
+    x = torch.randn(256, 128, requires_grad=True)
+    w = (torch.randn(384, 128) * 0.1).requires_grad_(True)
+    g = torch.randn(256, 384)
+    ops.linear(x, w, precision="mxfp8").backward(g)
+    got = (x.grad.clone(), w.grad.clone())
+    x.grad = w.grad = None
+    ops.linear(x, w).backward(g)
+    rel = lambda a, b: float((a - b).norm() / b.norm())  # noqa: E731
+    assert rel(got[0], x.grad) < 0.06 and rel(got[1], w.grad) < 0.06
+    q = ops.linear_qkv(x, w[:128], w[128:256], w[256:], precision="mxfp8")
+    assert q.shape == (256, 384) and rel(q, x @ w.T) < 0.06
+
+
+def test_library_ops_have_fake_and_autograd_registrations():
+    """The kernels registered with torch.library trace on fake tensors (shapes, dtypes and the autograd graph) without
+    running anything: what torch.compile / export need from an op."""
+    import torch
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    from them_bones_b200.ops import registry as R
+    assert all(hasattr(torch.ops.bones, n) for n in R.OPS)
+    with FakeTensorMode():
+        qkv = torch.empty(2, 256, 3 * 2 * 128, dtype=torch.bfloat16, requires_grad=True)
+        cos, sin = torch.empty(256, 64), torch.empty(256, 64)
+        ds = torch.zeros(2, 256, dtype=torch.int32)
+        y = R.attention(qkv, cos, sin, 2, 128, 0.1, ds, 128)
+        assert y.shape == (2, 256, 256) and y.dtype == torch.bfloat16 and y.requires_grad
+        (g,) = torch.autograd.grad(y.sum(), qkv)
+        assert g.shape == qkv.shape
+        y2, lse, qk = torch.ops.bones.attention_fwd(qkv, cos, sin, None, 2, 128, 0.1, 0)
+        assert lse.shape == (2, 2, 256) and lse.dtype == torch.float32 and not lse.requires_grad and qk.shape == (512, 512)
+        x = torch.empty(8, 1280, dtype=torch.bfloat16, requires_grad=True)
+        z = R.rms_norm(x)
+        assert z.shape == x.shape and torch.autograd.grad(z.sum(), x)[0].shape == x.shape

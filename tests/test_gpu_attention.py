@@ -83,3 +83,26 @@ def test_attention_ragged_length_is_padded_and_unsupported_shapes_raise():
     assert y.shape == (b, t, h * d) and _rel(y, ref) < 2e-2
     with pytest.raises(ValueError):
         ops.attention(qkv.float(), cos, sin, h, d, 0.11, ds, 0)
+
+
+def test_library_ops_match_the_eager_wrappers():
+    """The torch.library custom ops run the same kernels: identical outputs and gradients, and they pass opcheck's
+    schema / fake-tensor / autograd-registration checks."""
+    from them_bones_b200.ops import attention_native as AN
+    from them_bones_b200.ops import registry as R
+    b, t, h, d = 2, 512, 2, 128
+    qkv, cos, sin, ds = _inputs(b, t, h, d, seed=7)
+    g = torch.randn(b, t, h * d, device="cuda", dtype=torch.bfloat16)
+    x1 = qkv.clone().requires_grad_(True)
+    AN.attention(x1, cos, sin, h, d, 0.11, ds, 256).backward(g)
+    x2 = qkv.clone().requires_grad_(True)
+    y2 = R.attention(x2, cos, sin, h, d, 0.11, ds, 256)
+    y2.backward(g)
+    torch.cuda.synchronize()
+    assert torch.equal(x1.grad, x2.grad)
+    z = torch.randn(64, 1280, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    from them_bones_b200.ref import functional as RF
+    assert _rel(R.rms_norm(z), RF.rms_norm(z.float())) < 1e-2
+    torch.library.opcheck(torch.ops.bones.rmsnorm_fwd.default, (z.detach(),), test_utils=("test_schema", "test_faketensor"))
+    torch.library.opcheck(torch.ops.bones.attention_fwd.default, (qkv, cos, sin, ds.to(torch.int32), h, d, 0.11, 256),
+                          test_utils=("test_schema", "test_faketensor"))

@@ -71,8 +71,62 @@ def test_trainer_with_moe_and_tables_steps_on_gpu():
     torch.cuda.synchronize()
     L.check_error_word()
     assert all(l == l for l in losses) and losses[-1] < losses[0]
-    assert tr.tables.stats["updates"] == 12 and ops.COUNTS["sparse_adam"] > 0
+    st = tr.tables.exchange.read_stats()                     # the peer-memory table path, here on a one-entry peer list
+    assert st["touched"] > 0 and st["skipped"] == 0 and st["overflow"] == 0
     assert float(tr.tables.shards[0].float().abs().sum()) > 0
+
+
+@pytest.mark.parametrize("opt", ["rowrms", "adam"])
+def test_native_table_push_and_update_match_the_statement(opt):
+    """Gradient rows pushed into the owner's staging buffer, duplicates summed in sorted order, the table updated in
+    place: against the PyTorch statement of the same step (bf16 rows are rounded stochastically, so one bf16 step of
+    slack per element)."""
+    from them_bones_b200.models.tables import HashedTables
+    from them_bones_b200.ops import _lib as L
+    from them_bones_b200.parallel.symm import SoloComm
+    from them_bones_b200.ref import functional as RF
+    from them_bones_b200.runtime import Runtime
+    rt = Runtime(False, 0, 0, 1, torch.device("cuda", 0), "cuda")
+    torch.manual_seed(0)
+    rows, dim, n = 4096, 256, 3000
+    tab = HashedTables((2,), rows, dim, device="cuda", dtype=torch.bfloat16, opt=opt, decay=1e-3)
+    tab.exchange = SoloComm(rt).table_exchange(tab, entries_per_step=n)
+    assert tab.exchange.native
+    tab.shards[0].copy_(torch.randn(rows, dim, device="cuda") * 0.1)
+    before = tab.shards[0].float().clone()
+    ids = torch.randint(0, 200, (n,), device="cuda")          # many duplicates per row
+    ids[:50] = torch.arange(3000, 3050, device="cuda")        # and some rows touched once
+    g = (torch.randn(n, dim, device="cuda") * 0.01).bfloat16()
+    tab.record_grad(0, ids[:1000], g[:1000])                  # pushed in several pieces, as the micro-steps do
+    tab.record_grad(0, ids[1000:], g[1000:])
+    tab.step(0.02)
+    torch.cuda.synchronize()
+    L.check_error_word()
+    st = tab.exchange.read_stats()
+    uniq, inv = torch.unique(ids, return_inverse=True)
+    assert st["touched"] == len(uniq) and st["skipped"] == 0 and st["overflow"] == 0
+    acc = torch.zeros(len(uniq), dim, device="cuda").index_add_(0, inv, g.float())
+    want = before.clone()
+    if opt == "rowrms":
+        sq = torch.zeros(rows, device="cuda")
+        RF.table_rowrms_update(want, uniq, acc, sq, lr=0.02, beta=0.99, eps=1e-8, decay=1e-3)
+        assert torch.allclose(tab.row_sq[0], sq, rtol=1e-4, atol=1e-12)
+    else:
+        m, v = torch.zeros(len(uniq), dim, device="cuda"), torch.zeros(len(uniq), dim, device="cuda")
+        w = want.index_select(0, uniq)
+        m.lerp_(acc, 0.1); v.lerp_(acc.square(), 0.01)
+        w = w * (1 - 0.02 * 1e-3) - 0.02 * (m / 0.1) / ((v / 0.01).sqrt() + 1e-8)
+        want.index_copy_(0, uniq, w)
+    got = tab.shards[0].float()
+    untouched = torch.ones(rows, dtype=torch.bool, device="cuda")
+    untouched[uniq] = False
+    assert torch.equal(got[untouched], before[untouched])
+    ulp = want.abs().clamp_min(1e-6) * 2.0 ** -7
+    assert bool(((got - want).abs() <= ulp).all()), float(((got - want).abs() / ulp).max())
+    # a second step meets a clean staging buffer
+    tab.record_grad(0, ids[:10], g[:10])
+    tab.step(0.02)
+    assert tab.exchange.read_stats()["touched"] == len(uniq) + len(torch.unique(ids[:10]))
 
 
 def test_native_newton_schulz_matches_reference():

@@ -54,3 +54,68 @@ def test_mx_mlp_forward_backward():
     # and the whole thing approximates the bf16 MLP
     yb = torch.relu(x.float() @ w_fc.float().T).square() @ w_proj.float().T + res.float()
     assert _rel(got[0], yb) < 6e-2
+
+
+def test_mx_linear_qkv_forward_backward_into_slab():
+    """The block-scaled projection for three row-adjacent weights with gradient slabs (the optimizer's layout): output,
+    input gradient and the fp32 slab against the rounding-exact statement."""
+    from them_bones_b200 import ops
+    from them_bones_b200.ops import _lib as L
+    torch.manual_seed(4)
+    m, c, a = 640, 256, 256
+    x = torch.randn(m, c, device="cuda").bfloat16().requires_grad_(True)
+    slab = (torch.randn(3 * a, c, device="cuda") * 0.08).bfloat16()
+    gslab = torch.zeros(3 * a, c, device="cuda")
+    ws = []
+    for j in range(3):
+        w = slab[j * a:(j + 1) * a].requires_grad_(True)
+        w.main_grad = gslab[j * a:(j + 1) * a]
+        ws.append(w)
+    g = torch.randn(m, 3 * a, device="cuda").bfloat16()
+    y = ops.linear_qkv(x, *ws, precision="mxfp8")
+    y.backward(g)
+    torch.cuda.synchronize()
+    L.check_error_word()
+    assert all(w.grad is None for w in ws)                      # the gradient went into the slab
+    xr = x.detach().clone().requires_grad_(True)
+    wr = slab.detach().clone().requires_grad_(True)
+    yr = ops._MxLinearRef.apply(xr, wr)
+    yr.backward(g)
+    assert _rel(y, yr) < 1e-2
+    assert _rel(x.grad, xr.grad) < 1e-2
+    assert _rel(gslab, wr.grad) < 1e-2, _rel(gslab, wr.grad)
+    # with a fused residual, and weights that are not adjacent (the gradient comes back through autograd)
+    w1 = (torch.randn(c, c, device="cuda") * 0.08).bfloat16().requires_grad_(True)
+    res = torch.randn(m, c, device="cuda").bfloat16()
+    y1 = ops.linear(x.detach(), w1, residual=res, precision="mxfp8")
+    y1.backward(torch.ones_like(y1))
+    ref = ops._MxLinearRef.apply(x.detach(), w1.detach()) + res
+    assert _rel(y1, ref) < 1e-2 and w1.grad is not None
+
+
+def test_mx_experts_batched_forward_backward():
+    """Grouped experts on the batched block-scaled GEMMs against the per-expert rounding-exact statement."""
+    from them_bones_b200 import ops
+    from them_bones_b200.ops import _lib as L
+    torch.manual_seed(5)
+    e, rows, d, f = 2, 384, 256, 512
+    xs = torch.randn(e * rows, d, device="cuda").bfloat16().requires_grad_(True)
+    w_fc = (torch.randn(e, f, d, device="cuda") * 0.06).bfloat16().requires_grad_(True)
+    w_proj = (torch.randn(e, d, f, device="cuda") * 0.04).bfloat16().requires_grad_(True)
+    g = torch.randn(e * rows, d, device="cuda").bfloat16()
+    y = ops.moe_experts(xs, w_fc, w_proj, "mxfp8")
+    y.backward(g)
+    torch.cuda.synchronize()
+    L.check_error_word()
+    assert ops.COUNTS["moe_experts_mxfp8"] > 0
+    got = (y.detach(), xs.grad.clone(), w_fc.grad.clone(), w_proj.grad.clone())
+    for t in (xs, w_fc, w_proj):
+        t.grad = None
+    ops.set_reference_path(True)
+    try:
+        yr = ops.moe_experts(xs, w_fc, w_proj, "mxfp8")
+        yr.backward(g)
+    finally:
+        ops.set_reference_path(False)
+    assert _rel(got[0], yr) < 2e-2
+    assert _rel(got[1], xs.grad) < 6e-2 and _rel(got[2], w_fc.grad) < 6e-2 and _rel(got[3], w_proj.grad) < 6e-2

@@ -84,6 +84,7 @@ class GPTConfig:
     mtp_offsets: tuple = ()        # extra next-token targets, e.g. (2, 3): predict t+2 and t+3 from position t
     label_smoothing: float = 0.0   # training loss only; evaluation is the plain cross-entropy
     mlp_precision: str = "bf16"    # "bf16" | "mxfp8": block-scaled MLP / expert GEMMs
+    attn_proj_precision: str = "bf16"   # "bf16" | "mxfp8": block-scaled qkv / out projections (attention core stays bf16)
     moe_layers: tuple = ()
     moe_experts: int = 0
     moe_topk: int = 0
@@ -127,6 +128,8 @@ class GPTConfig:
             raise ValueError("mtp_offsets are distances beyond the next token: each must be >= 2")
         if self.mlp_precision not in ("bf16", "mxfp8"):
             raise ValueError(f"mlp_precision={self.mlp_precision!r}")
+        if self.attn_proj_precision not in ("bf16", "mxfp8"):
+            raise ValueError(f"attn_proj_precision={self.attn_proj_precision!r}")
         if self.moe_layers:
             if not (self.moe_experts and self.moe_topk in (1, 2) and self.moe_capacity and self.moe_hidden):
                 raise ValueError("MoE layers need moe_experts, moe_topk in {1,2}, moe_capacity and moe_hidden")
@@ -241,11 +244,13 @@ def switches(refresh: bool = False) -> dict:
         ATTN_LAYERS=e("ATTN_LAYERS", "", str), MIXER=e("MIXER", "off", str), MLP_RATIO=e("MLP_RATIO", 4, int),
         LABEL_SMOOTH=e("LABEL_SMOOTH", 0.0, float), MTP=e("MTP", "", str), MTP_WEIGHT=e("MTP_WEIGHT", 0.5, float), MTP_ANNEAL=e("MTP_ANNEAL", 0.5, float),
         MLP=e("MLP", "bf16", str),
+        ATTN_PROJ=e("ATTN_PROJ", "bf16", str),       # bf16 | mxfp8: the attention projections' GEMMs and weight gradients
         MOE=e("MOE", False, bool), MOE_LAYERS=e("MOE_LAYERS", "", str), MOE_EXPERTS=e("MOE_EXPERTS", 16, int),
         MOE_TOPK=e("MOE_TOPK", 2, int), MOE_HIDDEN=e("MOE_HIDDEN", 0, int), MOE_SHARED=e("MOE_SHARED", 0, int),
         MOE_AUX=e("MOE_AUX", 0.01, float), MOE_ZLOSS=e("MOE_ZLOSS", 0.0, float),
         TABLES=e("TABLES", "", str), TABLE_ROWS=e("TABLE_ROWS", 0, int), TABLE_SEED=e("TABLE_SEED", 0, int), TABLE_BITS=e("TABLE_BITS", 0, int), OS1_BITS=e("OS1_BITS", 0, int),
         TABLE_HOST_STATE=e("TABLE_HOST_STATE", "auto", str),   # auto | 0 | 1: Adam moments of the tables in pinned host memory
+        TABLE_OPT=e("TABLE_OPT", "auto", str),       # auto | adam | rowrms (one fp32 second moment per row)
         OS1=e("OS1", False, bool), OS1_ROWS=e("OS1_ROWS", 1 << 24, int), OS1_ORDER=e("OS1_ORDER", 16, int),
         OS1_LR=e("OS1_LR", 0.125, float), OS1_SEED=e("OS1_SEED", 0, int),
         # answer phase: from progress 1 - ANSWER_PHASE on, the loader marks the last ANSWER_TAIL of every document and the
@@ -300,7 +305,8 @@ def build_config(depth: int, n_embd: int, n_head: int, seq_len: int, vocab: int,
     h = hyper or Hyper.from_env()
     kw = dict(sequence_len=seq_len, vocab_size=vocab, n_layer=depth, n_head=n_head, n_embd=n_embd, head_dim=head_dim,
               rope_base=s["ROPE_BASE"], qk_scale=s["QK_SCALE"], bos_id=bos_id, doc_mask=s["DOC_MASK"], unet=s["UNET"],
-              value_embeds=s["VE"], attn_window=s["ATTN_WINDOW"], mlp_precision=s["MLP"], mlp_ratio=s["MLP_RATIO"],
+              value_embeds=s["VE"], attn_window=s["ATTN_WINDOW"], mlp_precision=s["MLP"], attn_proj_precision=s["ATTN_PROJ"],
+              mlp_ratio=s["MLP_RATIO"],
               mixer=s["MIXER"], label_smoothing=s["LABEL_SMOOTH"])
     if s["ATTN_LAYERS"]:
         kw["attn_layers"] = parse_layers(s["ATTN_LAYERS"], depth)

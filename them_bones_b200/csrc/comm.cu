@@ -229,6 +229,51 @@ __global__ void peer_dispatch_rows_kernel(const __nv_bfloat16* __restrict__ h, c
   }
 }
 
+// MoE dispatch written in the consumer's layout: slot s = (expert e, j) of the [E, rows] slot buffer (rows = b * C)
+// belongs to rank d = e / m and lands there at [(e % m), source rank, j] of a [m, W, rows] buffer, which is exactly the
+// [local expert][all ranks' rows] grouping the expert GEMMs read: no transposing copy after the exchange.
+__global__ void peer_dispatch_grouped_kernel(const __nv_bfloat16* __restrict__ h, const long long* __restrict__ tok, PeerPtrs dst, long long rows,
+                                             int m, long long n_slots, long long n_tokens, int C, int rank, int world) {
+  const long long s = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (s >= n_slots) return;
+  const long long e = s / rows, j = s - e * rows;
+  const int d = (int)(e / m), el = (int)(e - (long long)d * m);
+  const long long t = tok[s];
+  const bool valid = t >= 0 && t < n_tokens;
+  __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(dst.p[d]) + (((long long)el * world + rank) * rows + j) * C;
+  for (int c = lane * 8; c < C; c += 256) {
+    uint4 u = make_uint4(0, 0, 0, 0);
+    if (valid) u = *reinterpret_cast<const uint4*>(h + t * C + c);
+    *reinterpret_cast<uint4*>(out + c) = u;
+  }
+}
+
+// Block-permuting all-to-all between the two MoE layouts (blocks of `rows` rows of C bf16), by peer stores:
+//   mode 0, to the experts:  source [W(dst), m, rows]  ->  on rank w: [m, W(src), rows]   block (w, e) -> (e, rank)
+//   mode 1, to the sources:  source [m, W(dst), rows]  ->  on rank w: [W * m, rows]        block (e, w) -> (rank * m + e)
+// One warp per row.
+__global__ void peer_blocks_kernel(const __nv_bfloat16* __restrict__ src, PeerPtrs dst, long long rows, int m, int C, int rank, int world,
+                                   int mode) {
+  const long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const long long total = rows * m * world;
+  if (r >= total) return;
+  const long long blk = r / rows, j = r - blk * rows;
+  int w, e;
+  long long dblk;
+  if (mode == 0) {
+    w = (int)(blk / m); e = (int)(blk - (long long)w * m);
+    dblk = (long long)e * world + rank;
+  } else {
+    e = (int)(blk / world); w = (int)(blk - (long long)e * world);
+    dblk = (long long)rank * m + e;
+  }
+  const __nv_bfloat16* in = src + r * C;
+  __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(dst.p[w]) + (dblk * rows + j) * C;
+  for (int c = lane * 8; c < C; c += 256) *reinterpret_cast<uint4*>(out + c) = *reinterpret_cast<const uint4*>(in + c);
+}
+
 static PeerPtrs make_ptrs(void* const* ptrs, int world) {
   PeerPtrs p;
   for (int i = 0; i < kMaxPeers; ++i) p.p[i] = i < world ? ptrs[i] : nullptr;
@@ -294,6 +339,22 @@ int bones_peer_dispatch_rows(const void* h, const long long* tok, void* const* d
   if (world > kMaxPeers || (C % 8)) return -2;
   peer_dispatch_rows_kernel<<<(unsigned)((n_slots + 7) / 8), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)h, tok, make_ptrs(dst_ptrs, world),
                                                                                            rows_per_dest, n_slots, n_tokens, C, rank);
+  return (int)cudaGetLastError();
+}
+
+int bones_peer_dispatch_grouped(const void* h, const long long* tok, void* const* dst_ptrs, long long rows, int m, long long n_slots,
+                                long long n_tokens, int C, int rank, int world, void* stream) {
+  if (world > kMaxPeers || (C % 8)) return -2;
+  peer_dispatch_grouped_kernel<<<(unsigned)((n_slots + 7) / 8), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)h, tok, make_ptrs(dst_ptrs, world),
+                                                                                              rows, m, n_slots, n_tokens, C, rank, world);
+  return (int)cudaGetLastError();
+}
+
+int bones_peer_blocks(const void* src, void* const* dst_ptrs, long long rows, int m, int C, int rank, int world, int mode, void* stream) {
+  if (world > kMaxPeers || (C % 8)) return -2;
+  const long long total = rows * m * world;
+  peer_blocks_kernel<<<(unsigned)((total + 7) / 8), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)src, make_ptrs(dst_ptrs, world), rows, m, C,
+                                                                                    rank, world, mode);
   return (int)cudaGetLastError();
 }
 

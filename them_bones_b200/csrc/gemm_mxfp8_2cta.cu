@@ -13,7 +13,7 @@
 //
 // Tile N (`bn`, a run-time argument): 160 or 224 with two accumulators in TMEM (the epilogue of a tile overlaps the MMAs
 // of the next), or 256 with one (weight gradients: the contraction is tens of thousands long, the epilogue a few per
-// cent).  TMEM columns: accumulators from 0, A scales at 496, B scales at 500.
+// cent).  TMEM columns: accumulators from 0, four rotating sets of scale columns from 464.
 //
 // Scales in global memory are 512-byte chunks, one per (128 rows, 128 of K), in the image `tcgen05.cp.32x128b.warpx4`
 // spreads over four TMEM columns: byte (r % 32) * 16 + ((r % 128) / 32) * 4 + (k % 128) / 32.  Chunks of an operand
@@ -37,6 +37,8 @@
 // Reference counterparts: fp8 fused MLP forward / backward (round2/source/kernels/nki_mlp_fused8.py:508-570), fp8
 // projections (nki_attn_tt8g.py:616-623) and the fp8 weight-gradient GEMM (nki_dw8.py:239); per-block scales replace
 // their per-tensor power-of-two scales.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "gemm_epilogue.cuh"
 
@@ -66,6 +68,7 @@ struct Mx2Params {
   int* err;
   int tiles_m, tiles_n;
   int splits, atomic, wide;
+  int sf_sets;                  // copies of the scale columns in TMEM that the K blocks rotate through (1, 2 or 4)
 };
 
 constexpr int QM = 256, QK = 128, QSTAGES = 6;
@@ -73,7 +76,10 @@ constexpr uint32_t QA_BYTES = 128 * QK;            // 16384
 constexpr uint32_t QB_BYTES = 128 * QK;            // up to 128 rows (K-major: bn / 2 rows; MN-major: 128 K rows)
 constexpr uint32_t QSFA_BYTES = 512, QSFB_BYTES = 1024;
 constexpr uint32_t QSTAGE_STRIDE = 34816;          // 34 KB >= 16384 + 16384 + 512 + 1024, tiles stay 1024-aligned
-constexpr uint32_t QTMEM_SFA = 496, QTMEM_SFB = 500;
+// scale columns: up to four sets of (A: 4 columns, B: 8 columns) from column 464.  With one set the `tcgen05.cp` of a K
+// block has to wait for the MMAs of the block before (they read the columns it overwrites) and the MMAs for the copy:
+// the tensor pipe idles for the copies' latency every 128 of K.  Rotating sets removes the first wait.
+constexpr uint32_t QTMEM_SF0 = 464, QTMEM_SF_STRIDE = 12;
 constexpr int kGroupMq = 8;
 
 __device__ __forceinline__ void decode_tile_q(int tile, int tiles_m, int tiles_n, int& b, int& mb, int& nb) {
@@ -210,10 +216,104 @@ __device__ __forceinline__ void q_emit_col(const float (&v)[32], int lane, uint8
   if (sf_ok) *sf_dst = (uint8_t)biased;
 }
 
-constexpr int kEpiWarps = 16;                      // four per 32-lane TMEM quadrant
-constexpr int kPairThreads = 64 + 32 * kEpiWarps;
+// Epilogue warps per CTA: a multiple of four (one set per 32-lane TMEM quadrant).  16 warps leave 96 registers per
+// thread, 12 leave 128.
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
+// scale-chunk offset with 32-bit arithmetic; `shift` >= 0 when the tile height is a power of two
+__device__ __forceinline__ uint32_t q_sf_offset32(uint32_t r, uint32_t k, uint32_t kblocks, int group, int shift) {
+  const uint32_t g = shift >= 0 ? (r >> shift) : r / (uint32_t)group;
+  const uint32_t t = r - g * (uint32_t)group;
+  const uint32_t chunks = ((uint32_t)group + 127u) >> 7;
+  return ((g * kblocks + (k >> 7)) * chunks + (t >> 7)) * 512u + (t & 31u) * 16u + ((t & 127u) >> 5) * 4u + ((k & 127u) >> 5);
+}
+__device__ __forceinline__ int q_log2_or_neg(int v) { return (v & (v - 1)) == 0 ? 31 - __clz(v) : -1; }
+
+// One epilogue warp's share of a tile with quantised outputs, specialised at compile time on the epilogue and on which
+// copies are written (every branch on them would otherwise sit inside the fully unrolled 32-value loops).
+template <int EPI, bool WQ, bool WT, int kEpiWarps>
+__device__ __forceinline__ void q_quant_tile(const Mx2Params& p, uint32_t taddr0, int b, int row0, int ncol0, int lane, int sub, int nchunks) {
+  const int row = row0 + lane;
+  const bool row_ok = row < p.M;
+  const bool ragged = row0 + 32 > p.M;                      // warp-uniform: some of the warp's rows lie beyond M
+  __nv_bfloat16* Drow = p.D ? reinterpret_cast<__nv_bfloat16*>(p.D) + (long long)b * p.strideD + (long long)row * p.ldd : nullptr;
+  const __nv_bfloat16* Rrow = reinterpret_cast<const __nv_bfloat16*>(p.R) + (long long)b * p.strideR + (long long)row * p.ldr;
+  const long long qrow = ((long long)b * p.M + row) * p.N;
+  const uint32_t kblocks_n = (uint32_t)((p.N + 127) >> 7), kblocks_m = (uint32_t)((p.M + 127) >> 7);
+  const int qshift = q_log2_or_neg(p.dq_group), tshift = q_log2_or_neg(p.dt_group);
+  uint8_t* sfq = WQ ? p.Dsf + (size_t)b * p.dsf_batch + q_sf_offset32((uint32_t)row, 0u, kblocks_n, p.dq_group, qshift) : nullptr;
+  const uint32_t sfq_step = (((uint32_t)p.dq_group + 127u) >> 7) * 512u;          // per 128 columns
+  uint8_t* sft = WT ? p.Dtsf + (size_t)b * p.dtsf_batch : nullptr;
+#pragma unroll 1
+  for (int c = sub; c < nchunks; c += kEpiWarps / 4) {
+    uint32_t r[32];
+    __syncwarp();
+    BONES_TMEM_LD32(taddr0 + (uint32_t)(c * 32), r);
+    tmem_ld_wait();
+    const int col0 = ncol0 + c * 32;
+    if (col0 >= p.N) continue;                     // warp-uniform: the ragged last tile's columns beyond N
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+    if (ragged) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = row_ok ? v[j] : 0.f;
+    }
+    if (p.alpha != 1.0f) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
+    }
+    if (EPI == GE_BF16_RES || EPI == GE_MUL_2SQRT) {
+      if (row_ok) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint4 u = *reinterpret_cast<const uint4*>(Rrow + col0 + j * 8);
+          const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const float2 f = unpack_bf16(w[t]);
+            if (EPI == GE_BF16_RES) {
+              v[j * 8 + 2 * t] = fmaf(p.beta, f.x, v[j * 8 + 2 * t]);
+              v[j * 8 + 2 * t + 1] = fmaf(p.beta, f.y, v[j * 8 + 2 * t + 1]);
+            } else {
+              v[j * 8 + 2 * t] *= 2.0f * sqrt_fast(f.x);
+              v[j * 8 + 2 * t + 1] *= 2.0f * sqrt_fast(f.y);
+            }
+          }
+        }
+      }
+    } else if (EPI == GE_RELU2) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float t = fmaxf(v[j], 0.0f);
+        v[j] = t * t;
+      }
+    }
+    // the bf16 rounding comes first: the quantised copies describe the tensor that is stored
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint4 u;
+      u.x = pack_bf16(v[j * 8 + 0], v[j * 8 + 1]);
+      u.y = pack_bf16(v[j * 8 + 2], v[j * 8 + 3]);
+      u.z = pack_bf16(v[j * 8 + 4], v[j * 8 + 5]);
+      u.w = pack_bf16(v[j * 8 + 6], v[j * 8 + 7]);
+      if (Drow != nullptr && row_ok) *reinterpret_cast<uint4*>(Drow + col0 + j * 8) = u;
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const float2 f = unpack_bf16(w[t]);
+        v[j * 8 + 2 * t] = f.x;
+        v[j * 8 + 2 * t + 1] = f.y;
+      }
+    }
+    if (WQ) q_emit_row(v, p.Dq + qrow + col0, sfq + (uint32_t)(col0 >> 7) * sfq_step + (uint32_t)((col0 & 127) >> 5), row_ok);
+    if (WT)      // rows beyond M contribute zeros to their column blocks
+      q_emit_col(v, lane, p.Dt + qrow + col0, sft + q_sf_offset32((uint32_t)(col0 + lane), (uint32_t)row0, kblocks_m, p.dt_group, tshift), row_ok,
+                 row0 < p.M);
+  }
+}
+
+template <int kEpiWarps>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64 + 32 * kEpiWarps, 1)
 gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                        const __grid_constant__ CUtensorMap tma_sfa, const __grid_constant__ CUtensorMap tma_sfb, const Mx2Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -302,9 +402,17 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
       const uint32_t a_step = p.a_major ? (32 * 128) >> 4 : 32 >> 4;
       const uint32_t b_step = p.b_major ? (32 * 128) >> 4 : 32 >> 4;
       const uint32_t a_lbo = p.a_major ? 128 * 128 : 0, b_lbo = p.b_major ? 128 * 128 : 0;
-      int stage = 0, acc = 0;
+      int stage = 0, acc = 0, sfset = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
+      uint32_t idesc[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        idesc[k] = umma_idesc_mxf8(QM, (uint32_t)bn, 0, 0, (uint32_t)p.a_major, (uint32_t)p.b_major, (uint32_t)k, (uint32_t)k);
+      // descriptors of stage 0; a stage adds QSTAGE_STRIDE >> 4 to the address field
+      const uint64_t adesc0 = umma_smem_desc(base, a_lbo, 1024, kLayoutSw128);
+      const uint64_t bdesc0 = umma_smem_desc(base + QA_BYTES, b_lbo, 1024, kLayoutSw128);
+      const uint64_t sdesc0 = umma_smem_desc(base + QA_BYTES + QB_BYTES, 0, 128, kLayoutNone);
       for (int tile = cluster_id; tile < total && ok; tile += n_clusters) {
         if (!mbar_wait(tempty(acc), acc_phase ^ 1u, abort_flag, p.err, ERR_WAIT_TMEM_EMPTY)) break;
         tc_fence_after();
@@ -314,20 +422,19 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(full(stage), phase, abort_flag, p.err, ERR_WAIT_FULL)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sa = base + stage * QSTAGE_STRIDE, sb = sa + QA_BYTES, ssfa = sb + QB_BYTES, ssfb = ssfa + QSFA_BYTES;
-          q_cp_sf_pair(tmem + QTMEM_SFA, umma_smem_desc(ssfa, 0, 128, kLayoutNone));
-          q_cp_sf_pair(tmem + QTMEM_SFB, umma_smem_desc(ssfb, 0, 128, kLayoutNone));
-          q_cp_sf_pair(tmem + QTMEM_SFB + 4, umma_smem_desc(ssfb + 512, 0, 128, kLayoutNone));
-          const uint64_t adesc = umma_smem_desc(sa, a_lbo, 1024, kLayoutSw128);
-          const uint64_t bdesc = umma_smem_desc(sb, b_lbo, 1024, kLayoutSw128);
+          const uint64_t soff = (uint64_t)(stage * (QSTAGE_STRIDE >> 4));
+          const uint32_t sfa_t = tmem + QTMEM_SF0 + (uint32_t)sfset * QTMEM_SF_STRIDE, sfb_t = sfa_t + 4;
+          q_cp_sf_pair(sfa_t, sdesc0 + soff);
+          q_cp_sf_pair(sfb_t, sdesc0 + soff + (QSFA_BYTES >> 4));
+          q_cp_sf_pair(sfb_t + 4, sdesc0 + soff + ((QSFA_BYTES + 512) >> 4));
+          const uint64_t adesc = adesc0 + soff, bdesc = bdesc0 + soff;
 #pragma unroll
-          for (int k = 0; k < QK / 32; ++k) {
-            const uint32_t idesc = umma_idesc_mxf8(QM, (uint32_t)bn, 0, 0, (uint32_t)p.a_major, (uint32_t)p.b_major, (uint32_t)k, (uint32_t)k);
-            q_umma_mxf8_pair(d_tmem, adesc + (uint64_t)(k * a_step), bdesc + (uint64_t)(k * b_step), idesc, ((kb - kb0) | k) ? 1u : 0u,
-                             tmem + QTMEM_SFA, tmem + QTMEM_SFB);
-          }
+          for (int k = 0; k < QK / 32; ++k)
+            q_umma_mxf8_pair(d_tmem, adesc + (uint64_t)(k * a_step), bdesc + (uint64_t)(k * b_step), idesc[k], ((kb - kb0) | k) ? 1u : 0u,
+                             sfa_t, sfb_t);
           q_commit_pair(empty(stage));
           if (++stage == QSTAGES) { stage = 0; phase ^= 1u; }
+          if (++sfset == p.sf_sets) sfset = 0;
         }
         if (!ok) break;
         q_commit_pair(tfull(acc));
@@ -339,96 +446,49 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
     const int q = warp & 3, sub = (warp - 2) >> 2;
     const int nchunks = bn >> 5;
     const bool f32out = p.epi == GE_ACC_F32;
-    const bool need_r = p.epi == GE_BF16_RES || p.epi == GE_MUL_2SQRT;
-    const bool quant = p.Dq != nullptr || p.Dt != nullptr;
-    const long long kblocks_n = (p.N + 127) >> 7, kblocks_m = (p.M + 127) >> 7;
+    const int variant = (p.Dq != nullptr ? 1 : 0) | (p.Dt != nullptr ? 2 : 0);
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int tile = cluster_id; tile < total; tile += n_clusters) {
       int b, mb, nb;
       decode_tile_q(tile % base_tiles, p.tiles_m, p.tiles_n, b, mb, nb);
       const int row0 = mb * QM + (int)rank * 128 + q * 32;
-      const int row = row0 + lane;
-      const bool row_ok = row < p.M;
-      const long long drow = (long long)b * p.strideD + (long long)row * p.ldd;
-      const long long rrow = (long long)b * p.strideR + (long long)row * p.ldr;
       const bool got = mbar_wait(tfull(acc), acc_phase, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
       if (!__all_sync(0xffffffffu, got)) break;
       tc_fence_after();
+      const uint32_t taddr0 = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * bn);
+      if (variant == 0) {
+        const int row = row0 + lane;
+        const bool row_ok = row < p.M;
+        const long long drow = (long long)b * p.strideD + (long long)row * p.ldd;
+        const long long rrow = (long long)b * p.strideR + (long long)row * p.ldr;
 #pragma unroll 1
-      for (int c = sub; c < nchunks; c += kEpiWarps / 4) {
-        uint32_t r[32];
-        const uint32_t taddr = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * bn + c * 32);
-        __syncwarp();
-        BONES_TMEM_LD32(taddr, r);
-        tmem_ld_wait();
-        const int col0 = nb * bn + c * 32;
-        if (col0 >= p.N) continue;                 // warp-uniform: the ragged last tile's columns beyond N
-        if (!quant) {
-          if (row_ok) {
-            const size_t esz = f32out ? 4 : 2;
-            uint4 nopre[4];
-            gemm_store_chunk(r, p.epi, p.alpha, p.beta, p.wide != 0, p.splits > 1 || p.atomic, reinterpret_cast<uint8_t*>(p.D) + (drow + col0) * esz,
-                             reinterpret_cast<const uint8_t*>(p.R) + (rrow + col0) * esz, false, nopre, min(32, p.N - col0));
-          }
-          continue;
+        for (int c = sub; c < nchunks; c += kEpiWarps / 4) {
+          uint32_t r[32];
+          __syncwarp();
+          BONES_TMEM_LD32(taddr0 + (uint32_t)(c * 32), r);
+          tmem_ld_wait();
+          const int col0 = nb * bn + c * 32;
+          if (col0 >= p.N || !row_ok) continue;
+          const size_t esz = f32out ? 4 : 2;
+          uint4 nopre[4];
+          gemm_store_chunk(r, p.epi, p.alpha, p.beta, p.wide != 0, p.splits > 1 || p.atomic, reinterpret_cast<uint8_t*>(p.D) + (drow + col0) * esz,
+                           reinterpret_cast<const uint8_t*>(p.R) + (rrow + col0) * esz, false, nopre, min(32, p.N - col0));
         }
-        // quantising epilogues: N is a multiple of 32, so the chunk is whole
-        float v[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = row_ok ? __uint_as_float(r[j]) : 0.f;
-        if (p.alpha != 1.0f) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
-        }
-        if (need_r && row_ok) {
-          const __nv_bfloat16* R = reinterpret_cast<const __nv_bfloat16*>(p.R) + rrow + col0;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const uint4 u = *reinterpret_cast<const uint4*>(R + j * 8);
-            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-            for (int t = 0; t < 4; ++t) {
-              const float2 f = unpack_bf16(w[t]);
-              if (p.epi == GE_BF16_RES) {
-                v[j * 8 + 2 * t] = fmaf(p.beta, f.x, v[j * 8 + 2 * t]);
-                v[j * 8 + 2 * t + 1] = fmaf(p.beta, f.y, v[j * 8 + 2 * t + 1]);
-              } else {
-                v[j * 8 + 2 * t] *= 2.0f * sqrt_fast(f.x);
-                v[j * 8 + 2 * t + 1] *= 2.0f * sqrt_fast(f.y);
-              }
-            }
-          }
-        } else if (p.epi == GE_RELU2) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float t = fmaxf(v[j], 0.0f);
-            v[j] = t * t;
-          }
-        }
-        // the bf16 rounding comes first: the quantised copies describe the tensor that is stored
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint4 u;
-          u.x = pack_bf16(v[j * 8 + 0], v[j * 8 + 1]);
-          u.y = pack_bf16(v[j * 8 + 2], v[j * 8 + 3]);
-          u.z = pack_bf16(v[j * 8 + 4], v[j * 8 + 5]);
-          u.w = pack_bf16(v[j * 8 + 6], v[j * 8 + 7]);
-          if (p.D != nullptr && row_ok) *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.D) + drow + col0 + j * 8) = u;
-          const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-          for (int t = 0; t < 4; ++t) {
-            const float2 f = unpack_bf16(w[t]);
-            v[j * 8 + 2 * t] = f.x;
-            v[j * 8 + 2 * t + 1] = f.y;
-          }
-        }
-        const long long qoff = ((long long)b * p.M + row) * p.N + col0;
-        if (p.Dq != nullptr)
-          q_emit_row(v, p.Dq + qoff, p.Dsf + (size_t)b * p.dsf_batch + q_sf_offset(row, col0, kblocks_n, p.dq_group), row_ok);
-        if (p.Dt != nullptr)     // rows beyond M contribute zeros to their column blocks
-          q_emit_col(v, lane, p.Dt + qoff, p.Dtsf + (size_t)b * p.dtsf_batch + q_sf_offset(col0 + lane, row0, kblocks_m, p.dt_group),
-                     row_ok, row0 < p.M);
+      } else {
+#define BONES_Q_TILE(E, WQ, WT) q_quant_tile<E, WQ, WT, kEpiWarps>(p, taddr0, b, row0, nb * bn, lane, sub, nchunks)
+#define BONES_Q_EPI(WQ, WT)                                         \
+  switch (p.epi) {                                                  \
+    case GE_BF16_RES: BONES_Q_TILE(GE_BF16_RES, WQ, WT); break;     \
+    case GE_RELU2: BONES_Q_TILE(GE_RELU2, WQ, WT); break;           \
+    case GE_MUL_2SQRT: BONES_Q_TILE(GE_MUL_2SQRT, WQ, WT); break;   \
+    default: BONES_Q_TILE(GE_BF16, WQ, WT); break;                  \
+  }
+        if (variant == 1) { BONES_Q_EPI(true, false) }
+        else if (variant == 2) { BONES_Q_EPI(false, true) }
+        else { BONES_Q_EPI(true, true) }
+#undef BONES_Q_EPI
+#undef BONES_Q_TILE
       }
       tc_fence_before();
       __syncwarp();
@@ -564,7 +624,16 @@ int bones_gemm_mxfp8_pair(const void* Aq, const void* sfa, const void* Bq, const
   p.M = M; p.N = N; p.K = K; p.batch = batch;
   p.a_major = a_major; p.b_major = b_major;
   p.bn = bn;
-  p.acc_stages = (2 * bn <= (int)QTMEM_SFA) ? 2 : 1;
+  p.acc_stages = (2 * bn <= (int)QTMEM_SF0) ? 2 : 1;
+  {
+    static int sets = -1;
+    if (sets < 0) {
+      const char* e = getenv("BONES_MX_SF_SETS");
+      sets = e ? atoi(e) : 4;
+      if (sets != 1 && sets != 2 && sets != 4) sets = 4;
+    }
+    p.sf_sets = sets;
+  }
   p.epi = epi; p.alpha = alpha; p.beta = beta;
   p.D = D; p.ldd = ldd; p.strideD = strideD;
   p.R = R ? R : D; p.ldr = R ? ldr : ldd; p.strideR = R ? strideR : strideD;
@@ -592,10 +661,12 @@ int bones_gemm_mxfp8_pair(const void* Aq, const void* sfa, const void* Bq, const
   rc = tmap_scales_q(&tsb, sfb, sfb_bytes * batch, 4);
   if (rc) return rc;
   constexpr size_t smem = (size_t)QSTAGES * QSTAGE_STRIDE + 8 * (2 * QSTAGES + 4) + 16 + 1024;
-  static bool attr_done = false;
-  if (!attr_done) {
-    BONES_CHECK(cudaFuncSetAttribute(gemm_mxfp8_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    attr_done = true;
+  static int epi_warps = 0;
+  if (epi_warps == 0) {
+    const char* e = getenv("BONES_MX_EPI_WARPS");
+    epi_warps = (e && atoi(e) == 12) ? 12 : 16;
+    BONES_CHECK(cudaFuncSetAttribute(gemm_mxfp8_pair_kernel<12>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    BONES_CHECK(cudaFuncSetAttribute(gemm_mxfp8_pair_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   }
   int dev = 0, sms = 0;
   BONES_CHECK(cudaGetDevice(&dev));
@@ -620,7 +691,10 @@ int bones_gemm_mxfp8_pair(const void* Aq, const void* sfa, const void* Bq, const
   if (p.splits > KB) p.splits = KB;
   const int total = base_tiles * p.splits;
   const int clusters = total < pairs ? total : pairs;
-  gemm_mxfp8_pair_kernel<<<2 * clusters, kPairThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(ta, tb, tsa, tsb, p);
+  if (epi_warps == 12)
+    gemm_mxfp8_pair_kernel<12><<<2 * clusters, 64 + 32 * 12, smem, reinterpret_cast<cudaStream_t>(stream)>>>(ta, tb, tsa, tsb, p);
+  else
+    gemm_mxfp8_pair_kernel<16><<<2 * clusters, 64 + 32 * 16, smem, reinterpret_cast<cudaStream_t>(stream)>>>(ta, tb, tsa, tsb, p);
   return (int)cudaGetLastError();
 }
 

@@ -53,17 +53,18 @@ class CausalSelfAttention(nn.Module):
         self.n_head, self.head_dim = config.n_head, config.head_dim
         self.scale = config.qk_scale if config.qk_scale > 0 else 1.0 / math.sqrt(config.head_dim)
         self.window = config.attn_window if (config.attn_window and layer not in config.attn_long) else 0
+        self.precision = config.attn_proj_precision
         self.c_q, self.c_k, self.c_v = Linear(c, a), Linear(c, a), Linear(c, a)
         self.c_proj = Linear(a, c)
 
     def forward(self, xn, cos, sin, doc_start, ve=None, ve_lambda=None, residual=None):
         b, t, _ = xn.shape
-        qkv = ops.linear_qkv(xn, self.c_q.weight, self.c_k.weight, self.c_v.weight)
+        qkv = ops.linear_qkv(xn, self.c_q.weight, self.c_k.weight, self.c_v.weight, precision=self.precision)
         if ve is not None:
             a = self.n_head * self.head_dim
             qkv = torch.cat([qkv[..., :2 * a], qkv[..., 2 * a:] + ve_lambda.to(qkv.dtype) * ve], dim=-1)
         y = ops.attention(qkv, cos, sin, self.n_head, self.head_dim, self.scale, doc_start, self.window)
-        return ops.linear(y, self.c_proj.weight, residual=residual)
+        return ops.linear(y, self.c_proj.weight, residual=residual, precision=self.precision)
 
 
 class MLP(nn.Module):

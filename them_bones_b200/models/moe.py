@@ -113,9 +113,9 @@ class MoeMLP(nn.Module):
         p, idx, gates = RF.moe_route(logits, self.topk)
         slot, tok = ops.moe_slots(idx, b, t, self.n_exp, self.cap)
         # slot gather ([E*b*C, d], empty slots are zero rows) + exchange to the expert owners
-        xs = ops.moe_dispatch_exchange(h, tok, self.ep_group, self.ep_world, self.n_exp, slot)
+        xs = ops.moe_dispatch_exchange(h, tok, self.ep_group, self.ep_world, self.n_exp, slot, key=self.layer)
         ys = ops.moe_experts(xs, self.w_fc, self.w_proj, self.precision)   # rows grouped by local expert
-        ys = ops.moe_exchange(ys, self.ep_group, self.ep_world, self.n_exp, forward=False)
+        ys = ops.moe_exchange(ys, self.ep_group, self.ep_world, self.n_exp, forward=False, key=self.layer)
         out = ops.moe_combine(ys, slot, gates)                            # [n, d]
         if self.shared is not None:
             out = out + ops.mlp(h, self.shared.c_fc.weight, self.shared.c_proj.weight, precision=self.precision)

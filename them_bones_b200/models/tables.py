@@ -6,13 +6,24 @@ reference keeps its n-gram table in host shared memory and exchanges sparse grad
 barriers (``NgramHostTable``, round2/source/train.py:3526-3862: ``ids`` 3621, ``gather`` 3627, ``_exchange`` 3653,
 ``step`` 3678); kept from it: zero initialisation (the first forward equals the table-free model), causal hashing with
 a pad id before the window start, owner-computes updates (owner = ``row % world``), gradients of duplicate rows summed
-then averaged over ranks, an update that is skipped when any owned gradient is non-finite, stochastic rounding of
-updated rows to bf16.  Not kept: the one-step-stale application (``NgramStaleT21``, :13934), which exists to hide the
-host table's update behind a worker thread; the device update here takes milliseconds and is applied in step.
+then averaged over ranks, its row-wise RMS update with one fp32 second moment per row, stochastic rounding of updated
+rows to bf16, and no update from a non-finite gradient.  Not kept: the one-step-stale application (``NgramStaleT21``,
+:13934), which exists to hide the host table's update behind a worker thread; the device update here takes
+milliseconds and is applied in step.
 
-Here each rank owns ``rows / world`` rows in device memory; lookups and sparse gradients travel by all-to-all
-(``parallel.table_a2a``: fused peer-memory kernels on NVLink, or the NCCL/gloo baseline); the update is a sparse Adam
-on the touched rows whose fp32 moments live in pinned host memory and are streamed on a side stream.
+Here each rank owns ``rows / world`` rows in device memory.  Two transports (``exchange``):
+
+* the peer-memory one (``parallel.symm.PeerTableExchange``, GPUs): lookups read the owners' shards through NVLink peer
+  pointers; gradient rows are pushed into the owner's staging buffer from inside backward, and the owner's update
+  (``csrc/tables.cu``) sums duplicates in sorted order and writes the table in place -- no library collective, no host
+  synchronisation anywhere in a step;
+* ``parallel.table_a2a.CollectiveExchange`` (NCCL / gloo all-to-all; CPU path, baseline and oracle), whose update is
+  the PyTorch statement of the same arithmetic.
+
+Optimizer state (``opt``): ``"rowrms"`` keeps one fp32 second moment per row (4 bytes per row: 2^26 rows x 2 tables over
+8 ranks is 67 MB per rank); ``"adam"`` keeps dense fp32 first and second moments (8 bytes per element: the same tables
+would need 1.4 TB), on the device or, with ``host_state``, in pinned host memory streamed on a side stream.  ``"auto"``
+takes Adam while its moments fit in a quarter of the device and the row-wise form beyond that.
 """
 from __future__ import annotations
 
@@ -41,9 +52,11 @@ class _LookupFn(torch.autograd.Function):
 class HashedTables:
     def __init__(self, orders, rows: int, dim: int, *, seed: int = 0, device="cpu", dtype=torch.float32,
                  group=None, world: int = 1, rank: int = 0, host_state: bool = False,
-                 betas=(0.9, 0.99), eps: float = 1e-8, decay: float = 0.0, exchange=None, bits: int = 0):
+                 betas=(0.9, 0.99), eps: float = 1e-8, decay: float = 0.0, exchange=None, bits: int = 0, opt: str = "auto"):
         if rows % world:
             raise ValueError("table rows must divide over the ranks")
+        if opt not in ("auto", "adam", "rowrms"):
+            raise ValueError(f"table optimizer {opt!r}: expected auto, adam or rowrms")
         self.orders, self.rows, self.dim, self.seed = tuple(orders), rows, dim, seed
         self.group, self.world, self.rank = group, world, rank
         self.device, self.dtype = torch.device(device), dtype
@@ -53,22 +66,29 @@ class HashedTables:
         self.bits, self.rows_are_views = bits, False
         self.local_rows = rows // world
         self.shards = [torch.zeros(self.local_rows, dim, dtype=dtype, device=self.device) for _ in self.orders]
-        # Adam moments: on the device while they fit (two fp32 copies of the shard per table), else in pinned host memory
-        # and streamed per step.  The host route costs a CPU gather/scatter of every touched row (measured: 826 ms per
-        # 131 072-token step on 2 GPUs against 8 ms on the device), so it is for tables the GPU cannot hold.
-        if host_state == "auto":
-            need = 2 * 4 * self.local_rows * dim * len(self.orders)
-            have = torch.cuda.get_device_properties(self.device).total_memory if self.device.type == "cuda" else 0
-            host_state = self.device.type == "cuda" and need > 0.35 * have
-        self.host_state = bool(host_state) and self.device.type == "cuda"
-        sdev = "cpu" if self.host_state else self.device
-        mk = lambda: torch.zeros(self.local_rows, dim, dtype=torch.float32, device=sdev)  # noqa: E731
-        self.exp_avg = [mk() for _ in self.orders]
-        self.exp_avg_sq = [mk() for _ in self.orders]
-        if self.host_state:
-            self.exp_avg = [t.pin_memory() for t in self.exp_avg]
-            self.exp_avg_sq = [t.pin_memory() for t in self.exp_avg_sq]
-            self.side_stream = torch.cuda.Stream(device=self.device)
+        dense_state = 2 * 4 * self.local_rows * dim * len(self.orders)
+        have = torch.cuda.get_device_properties(self.device).total_memory if self.device.type == "cuda" else 0
+        if opt == "auto":
+            opt = "adam" if (self.device.type != "cuda" or dense_state <= 0.25 * have or host_state is True) else "rowrms"
+        self.opt = opt
+        self.host_state = False
+        self.exp_avg, self.exp_avg_sq, self.row_sq = [], [], []
+        if opt == "adam":
+            # dense moments: on the device while they fit, else (or on request) in pinned host memory, streamed per step;
+            # the host route pays a CPU gather / scatter of every touched row and is for tables the GPU cannot hold
+            if host_state == "auto":
+                host_state = self.device.type == "cuda" and dense_state > 0.35 * have
+            self.host_state = bool(host_state) and self.device.type == "cuda"
+            sdev = "cpu" if self.host_state else self.device
+            mk = lambda: torch.zeros(self.local_rows, dim, dtype=torch.float32, device=sdev)  # noqa: E731
+            self.exp_avg = [mk() for _ in self.orders]
+            self.exp_avg_sq = [mk() for _ in self.orders]
+            if self.host_state:
+                self.exp_avg = [t.pin_memory() for t in self.exp_avg]
+                self.exp_avg_sq = [t.pin_memory() for t in self.exp_avg_sq]
+                self.side_stream = torch.cuda.Stream(device=self.device)
+        else:
+            self.row_sq = [torch.zeros(self.local_rows, dtype=torch.float32, device=self.device) for _ in self.orders]
         self.betas, self.eps, self.decay = betas, eps, decay
         self.steps = 0
         self.pending = []           # [(order_slot, ids [n], grads [n, dim])] recorded by backward
@@ -76,6 +96,12 @@ class HashedTables:
         from ..parallel import table_a2a
         self.exchange = exchange or table_a2a.make_exchange(group, world, rank, self.device)
         self.stats = dict(updates=0, skipped=0, touched=0)
+
+    def state_bytes(self) -> dict:
+        """Bytes this rank holds: table shards and optimizer state (device or pinned host)."""
+        shards = sum(t.numel() * t.element_size() for t in self.shards)
+        state = sum(t.numel() * t.element_size() for t in self.exp_avg + self.exp_avg_sq + self.row_sq)
+        return dict(shards=shards, state=state, state_on_host=self.host_state, opt=self.opt)
 
     # -- hashing / lookup -----------------------------------------------------------------------------------
     def ids(self, idx: torch.Tensor, doc_start=None):
@@ -104,15 +130,23 @@ class HashedTables:
         return x
 
     def record_grad(self, order_slot, ids, g):
-        self.pending.append((order_slot, ids.detach(), g.detach()))
+        push = getattr(self.exchange, "push_grads", None)
+        if push is not None:         # peer-memory transport: the rows leave for their owners now, inside backward
+            push(order_slot, ids.detach(), g.detach())
+        else:
+            self.pending.append((order_slot, ids.detach(), g.detach()))
 
     # -- update ---------------------------------------------------------------------------------------------
     @torch.no_grad()
     def step(self, lr: float):
         """Apply every recorded gradient: route ``(id, grad)`` pairs to the owners, sum duplicates, average over ranks,
-        sparse Adam on the touched rows."""
-        pend, self.pending = self.pending, []
+        update the touched rows."""
         self.steps += 1
+        apply_fused = getattr(self.exchange, "apply_updates", None)
+        if apply_fused is not None:
+            apply_fused(self, lr)
+            return
+        pend, self.pending = self.pending, []
         for j in range(len(self.orders)):
             parts = [(i, g) for (o, i, g) in pend if o == j]
             if parts:
@@ -132,7 +166,11 @@ class HashedTables:
             acc = torch.zeros(len(uniq), self.dim, dtype=torch.float32, device=lgrads.device)
             acc.index_add_(0, inv, lgrads)
             acc /= self.world
-            self._sparse_adam(j, uniq, acc, lr)
+            if self.opt == "rowrms":
+                RF.table_rowrms_update(self.shards[j], uniq, acc, self.row_sq[j], lr=lr, beta=self.betas[1], eps=self.eps,
+                                       decay=self.decay)
+            else:
+                self._sparse_adam(j, uniq, acc, lr)
             self.stats["updates"] += 1
             self.stats["touched"] += int(len(uniq))
         done = getattr(self.exchange, "after_update", None)

@@ -75,20 +75,42 @@ def resid_mix_norm(x, x0, a, b, acc=None):
     return xm, RF.rms_norm(xm)
 
 
-def linear(x, w, residual=None):
-    """``x @ w.T (+ residual)``; the residual add is fused into the GEMM epilogue on the native path."""
+def linear(x, w, residual=None, precision="bf16"):
+    """``x @ w.T (+ residual)``; the residual add is fused into the GEMM epilogue on the native path.  ``"mxfp8"``: both
+    operands block-quantised along the contraction, in the forward, the input gradient and the weight gradient."""
     if native(x):
-        return _cuda().linear(x, w, residual)
-    y = F.linear(x, w.to(x.dtype))
+        return _cuda().linear(x, w, residual, precision)
+    y = _MxLinearRef.apply(x, w.to(x.dtype)) if precision == "mxfp8" else F.linear(x, w.to(x.dtype))
     return y if residual is None else y + residual
 
 
-def linear_qkv(x, wq, wk, wv):
+def linear_qkv(x, wq, wk, wv, precision="bf16"):
     """Packed ``[.., 3*A]`` projection from three weights.  When the three weights are adjacent rows of one optimizer
     stack the native path reads them as a single ``[3A, C]`` operand with no concatenation."""
     if native(x):
-        return _cuda().linear_qkv(x, wq, wk, wv)
+        return _cuda().linear_qkv(x, wq, wk, wv, precision)
+    if precision == "mxfp8":
+        return torch.cat([_MxLinearRef.apply(x, w.to(x.dtype)) for w in (wq, wk, wv)], dim=-1)
     return torch.cat([F.linear(x, wq.to(x.dtype)), F.linear(x, wk.to(x.dtype)), F.linear(x, wv.to(x.dtype))], dim=-1)
+
+
+class _MxLinearRef(torch.autograd.Function):
+    """Rounding-exact statement of the block-scaled linear: every GEMM sees both operands quantised in 1 x 32 blocks along
+    its own contraction axis (reference: the fp8 projections and their fp8 weight gradient,
+    round2/source/kernels/nki_attn_tt8g.py:745-757, nki_dw8.py:313-335, there with per-tensor scales)."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        ctx.save_for_backward(x, w)
+        return (RF.mx_qdq(x.float(), -1) @ RF.mx_qdq(w.float(), -1).T).to(x.dtype)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        x2, dy2 = x.reshape(-1, x.shape[-1]).float(), dy.reshape(-1, dy.shape[-1]).float()
+        dx = RF.mx_qdq(dy2, -1) @ RF.mx_qdq(w.float(), 0)
+        dw = RF.mx_qdq(dy2, 0).T @ RF.mx_qdq(x2, 0)
+        return dx.view(x.shape).to(x.dtype), dw.to(w.dtype)
 
 
 def attention(qkv, cos, sin, n_head, head_dim, scale, doc_start=None, window=0):
@@ -259,14 +281,14 @@ def moe_combine(ys, slot, gates):
     return out
 
 
-def moe_dispatch_exchange(h, tok, group, world, n_exp, slot=None):
+def moe_dispatch_exchange(h, tok, group, world, n_exp, slot=None, key=None):
     from ..parallel import moe_a2a
-    return moe_a2a.dispatch_exchange(h, tok, group, world, n_exp, slot)
+    return moe_a2a.dispatch_exchange(h, tok, group, world, n_exp, slot, key)
 
 
-def moe_exchange(xs, group, world, n_exp, forward=True):
+def moe_exchange(xs, group, world, n_exp, forward=True, key=None):
     from ..parallel import moe_a2a
-    return moe_a2a.exchange(xs, group, world, n_exp, forward)
+    return moe_a2a.exchange(xs, group, world, n_exp, forward, key)
 
 
 def moe_experts(xs, w_fc, w_proj, precision="bf16"):

@@ -18,6 +18,7 @@ from . import COUNTS
 
 _I, _L, _F = ctypes.c_int, ctypes.c_longlong, ctypes.c_float
 BF16 = torch.bfloat16
+_LIBRARY_OPS = os.environ.get("BONES_LIBRARY_OPS", "0") not in ("0", "", "false")
 
 
 def _c(t):
@@ -141,11 +142,22 @@ class _LinearFn(torch.autograd.Function):
         return (dx, dy if ctx.has_res else None) + gws
 
 
-def linear(x, w, residual=None):
+def _mx_linear_ok(x, ws):
+    return (x.dtype == BF16 and x.shape[-1] % 128 == 0 and all(w.shape[0] % 128 == 0 for w in ws)
+            and not any(getattr(w, "main_grad_push", None) is not None for w in ws))
+
+
+def linear(x, w, residual=None, precision="bf16"):
+    if precision == "mxfp8" and _mx_linear_ok(x, (w,)):
+        from . import mxfp8
+        return mxfp8._MxLinearFn.apply(x, residual, w)
     return _LinearFn.apply(x, residual, w)
 
 
-def linear_qkv(x, wq, wk, wv):
+def linear_qkv(x, wq, wk, wv, precision="bf16"):
+    if precision == "mxfp8" and _mx_linear_ok(x, (wq, wk, wv)):
+        from . import mxfp8
+        return mxfp8._MxLinearFn.apply(x, None, wq, wk, wv)
     return _LinearFn.apply(x, None, wq, wk, wv)
 
 
@@ -210,6 +222,10 @@ def rms_norm(x):
     if x.dtype != BF16:
         from ..ref import functional as RF
         return RF.rms_norm(x)
+    if _LIBRARY_OPS:
+        from . import registry
+        COUNTS["rmsnorm"] += 1
+        return registry.rms_norm(x)
     return _RmsNormFn.apply(x)
 
 
@@ -353,7 +369,11 @@ def attention(qkv, cos, sin, n_head, head_dim, scale, doc_start, window):
     if why:
         raise ValueError(f"native attention does not cover this call: {why}")
     COUNTS["attention"] += 1
-    y = AN.attention(qkv, cos, sin, n_head, head_dim, scale, doc_start, window)
+    if _LIBRARY_OPS:             # the same kernels behind torch.library custom ops (ops/registry.py)
+        from . import registry
+        y = registry.attention(qkv, cos, sin, n_head, head_dim, scale, doc_start, window)
+    else:
+        y = AN.attention(qkv, cos, sin, n_head, head_dim, scale, doc_start, window)
     return y[:, :t] if pad else y
 
 
@@ -679,6 +699,10 @@ class _ExpertsFn(torch.autograd.Function):
 
 
 def moe_experts(xs, w_fc, w_proj, precision="bf16"):
+    if precision == "mxfp8":
+        from . import mxfp8
+        if mxfp8.experts_apply(xs, w_fc, w_proj):
+            return mxfp8._MxExpertsFn.apply(xs, w_fc, w_proj)
     return _ExpertsFn.apply(xs, w_fc, w_proj)
 
 

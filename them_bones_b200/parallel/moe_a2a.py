@@ -39,13 +39,14 @@ class _AllToAll(torch.autograd.Function):
         return out, None
 
 
-def exchange(xs: torch.Tensor, group, world: int, n_exp: int, forward: bool) -> torch.Tensor:
+def exchange(xs: torch.Tensor, group, world: int, n_exp: int, forward: bool, key=None) -> torch.Tensor:
+    """``key`` names the calling layer: the peer-memory transport keeps one receive buffer per layer and direction."""
     if world == 1:
         return xs
     d = xs.shape[-1]
     m = n_exp // world
     if _FUSED is not None and xs.is_cuda:
-        return _FUSED.exchange(xs, world, m, forward)
+        return _FUSED.exchange(xs, world, m, forward, key)
     if forward:
         ys = _AllToAll.apply(xs, group)                                   # [W(src), m, bC, d]
         return ys.view(world, m, -1, d).transpose(0, 1).reshape(-1, d)    # [m, W*bC, d]
@@ -53,10 +54,10 @@ def exchange(xs: torch.Tensor, group, world: int, n_exp: int, forward: bool) -> 
     return _AllToAll.apply(back, group)
 
 
-def dispatch_exchange(h: torch.Tensor, tok: torch.Tensor, group, world: int, n_exp: int, slot=None) -> torch.Tensor:
+def dispatch_exchange(h: torch.Tensor, tok: torch.Tensor, group, world: int, n_exp: int, slot=None, key=None) -> torch.Tensor:
     """Slot gather + forward exchange.  With the fused transport installed this is one kernel (rows are stored straight
-    into the destination rank's expert buffer); otherwise gather then all-to-all."""
+    into the destination rank's expert buffer, already grouped by local expert); otherwise gather then all-to-all."""
     from .. import ops
     if world > 1 and _FUSED is not None and h.is_cuda and hasattr(_FUSED, "dispatch"):
-        return _FUSED.dispatch(h, tok, world, n_exp // world)
-    return exchange(ops.moe_dispatch(h, tok, slot), group, world, n_exp, True)
+        return _FUSED.dispatch(h, tok, world, n_exp // world, slot, key)
+    return exchange(ops.moe_dispatch(h, tok, slot), group, world, n_exp, True, key)

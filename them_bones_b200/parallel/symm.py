@@ -167,8 +167,8 @@ class PeerComm:
         from . import moe_a2a
         moe_a2a.install_fused(PeerMoeExchange(self))
 
-    def table_exchange(self, tables):
-        return PeerTableExchange(self, tables)
+    def table_exchange(self, tables, entries_per_step: int = 0):
+        return PeerTableExchange(self, tables, entries_per_step)
 
 
 def create_or_fallback(rt, factory=None):
@@ -265,12 +265,23 @@ class SoloComm(PeerComm):
     def install_moe(self, model):
         pass
 
-    def table_exchange(self, tables):
-        return tables.exchange
+    def peers(self, t):
+        ent = self._handles.get(t.data_ptr())
+        if ent is None:
+            raise RuntimeError("tensor is not an allocation of this communicator")
+        return ent[2]
 
 
 class PeerMoeExchange:
-    """Equal-split all-to-all of the slot buffer by peer stores into the destination's receive buffer."""
+    """Expert-parallel exchange by peer stores, written straight in the layout the consumer reads.
+
+    Buffers are symmetric allocations that persist: the dispatch buffer and the return buffer of a layer are per layer
+    (``key``), because the expert GEMMs and the combine keep them for their backward passes and nothing is copied out;
+    the two gradient exchanges share one buffer each across layers.  One epoch barrier per exchange, after the stores
+    ("every peer's rows have landed"); none is needed before them: a peer can only reach the next writer of a buffer after
+    a barrier that this rank arrives at later in its stream than the last reader of that buffer (the next writer of a
+    per-layer buffer is the same layer one micro-step on, behind that layer's backward exchanges; the next writer of a
+    shared gradient buffer is the layer below, behind the other gradient exchange of this layer)."""
 
     def __init__(self, comm: PeerComm):
         self.comm = comm
@@ -283,6 +294,7 @@ class PeerMoeExchange:
         return self.bufs[k]
 
     def _a2a(self, x, key):
+        """Plain equal-split all-to-all (chunk d of ``x`` to slot ``rank`` of peer d); used by the self-test."""
         comm = self.comm
         x = x.contiguous()
         recv = self._recv(x.numel(), x.dtype, key)
@@ -292,76 +304,116 @@ class PeerMoeExchange:
         comm.barrier()                                   # every peer's rows have landed
         return recv.view(x.shape).clone()
 
-    def exchange(self, xs, world, m, forward):
-        return _PeerA2A.apply(xs, self, world, m, forward)
+    def _blocks(self, x, world, m, mode, key):
+        """``x [m * W * rows, d]`` bf16 -> the other layout on the peers (see ``peer_blocks_kernel``); returns this rank's
+        receive buffer as a ``[m * W * rows, d]`` view."""
+        comm = self.comm
+        x = x.contiguous()
+        d = x.shape[-1]
+        rows = x.shape[0] // (m * world)
+        recv = self._recv(x.numel(), x.dtype, key)
+        L.call("bones_peer_blocks", L.ptr(x), comm.peers(recv), _L(rows), _I(m), _I(d), _I(comm.rank), _I(world), _I(mode), L.stream())
+        comm.barrier()
+        comm.launches += 1
+        return recv.view(x.shape)
 
-    def dispatch(self, h, tok, world, m):
+    def exchange(self, xs, world, m, forward, key=None):
+        return _PeerBlocksFn.apply(xs, self, world, m, forward, key)
+
+    def dispatch(self, h, tok, world, m, slot=None, key=None):
         """Permute + exchange in one kernel: token rows go straight into the owning rank's expert buffer."""
-        return _PeerDispatch.apply(h, tok, self, world, m)
+        return _PeerDispatch.apply(h, tok, slot, self, world, m, key)
 
 
 class _PeerDispatch(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, h, tok, ex, world, m):
+    def forward(ctx, h, tok, slot, ex, world, m, key):
         comm = ex.comm
         h = h.contiguous()
         n_slots, d = tok.numel(), h.shape[1]
-        recv = ex._recv(n_slots * d, h.dtype, "disp")
-        comm.barrier()
-        L.call("bones_peer_dispatch_rows", L.ptr(h), L.ptr(tok), comm.peers(recv), _L(n_slots // world), _L(n_slots),
-               _L(h.shape[0]), _I(d), _I(comm.rank), _I(world), L.stream())
+        rows = n_slots // (world * m)                                      # rows per (expert, source rank) block
+        recv = ex._recv(n_slots * d, h.dtype, ("disp", key))
+        L.call("bones_peer_dispatch_grouped", L.ptr(h), L.ptr(tok), comm.peers(recv), _L(rows), _I(m), _L(n_slots), _L(h.shape[0]),
+               _I(d), _I(comm.rank), _I(world), L.stream())
         comm.barrier()
         comm.launches += 1
-        ctx.save_for_backward(tok)
-        ctx.ex, ctx.world, ctx.m, ctx.n = ex, world, m, h.shape[0]
-        ys = recv.view(n_slots, d).clone()                                  # [W(src), m, bC, d]
-        return ys.view(world, m, -1, d).transpose(0, 1).reshape(-1, d)      # [m, W*bC, d]
+        ctx.save_for_backward(tok, slot if slot is not None else tok)
+        ctx.ex, ctx.world, ctx.m, ctx.n, ctx.has_slot = ex, world, m, h.shape[0], slot is not None
+        return recv.view(n_slots, d)                                        # [m, W(src), rows, d]: grouped by local expert
 
     @staticmethod
     def backward(ctx, g):
-        (tok,) = ctx.saved_tensors
+        tok, slot = ctx.saved_tensors
         ex, world, m, d = ctx.ex, ctx.world, ctx.m, g.shape[-1]
-        back = g.reshape(m, world, -1, d).transpose(0, 1).reshape(-1, d)
-        dxs = ex._a2a(back, "gdisp")                                        # gradients of my slots
+        dxs = ex._blocks(g.reshape(-1, d), world, m, 1, "gdisp")            # gradients of my slots, [E * rows, d]
+        if ctx.has_slot:            # every token sums its (at most k) slots: the combine kernel with unit gates
+            from ..ops import cuda as C
+            ones = torch.ones(slot.shape, dtype=torch.float32, device=g.device)
+            dh = torch.empty(ctx.n, d, dtype=g.dtype, device=g.device)
+            L.call("bones_moe_combine", L.ptr(dxs), L.ptr(slot), L.ptr(ones), L.ptr(dh), _I(ctx.n), _I(d), _I(slot.shape[1]),
+                   _L(dxs.shape[0]), L.stream())
+            return dh, None, None, None, None, None, None
         dh = torch.zeros(ctx.n + 1, d, dtype=torch.float32, device=g.device)
         dh.index_add_(0, tok, dxs.float())
-        return dh[:ctx.n].to(g.dtype), None, None, None, None
+        return dh[:ctx.n].to(g.dtype), None, None, None, None, None, None
 
 
-class _PeerA2A(torch.autograd.Function):
+class _PeerBlocksFn(torch.autograd.Function):
+    """forward=True: slot layout ``[W(dst), m, rows]`` to the experts' ``[m, W(src), rows]``; forward=False: the experts'
+    layout back to the sources' slot layout.  The backward of each is the other, through a buffer shared by all layers."""
+
     @staticmethod
-    def forward(ctx, xs, ex, world, m, forward):
+    def forward(ctx, xs, ex, world, m, forward, key):
         ctx.ex, ctx.world, ctx.m, ctx.fwd = ex, world, m, forward
-        d = xs.shape[-1]
-        if forward:
-            ys = ex._a2a(xs, "f")
-            return ys.view(world, m, -1, d).transpose(0, 1).reshape(-1, d)
-        back = xs.view(m, world, -1, d).transpose(0, 1).reshape(-1, d)
-        return ex._a2a(back, "b")
+        return ex._blocks(xs, world, m, 0 if forward else 1, ("f" if forward else "r", key))
 
     @staticmethod
     def backward(ctx, g):
-        ex, world, m, d = ctx.ex, ctx.world, ctx.m, g.shape[-1]
-        if ctx.fwd:      # reverse of (a2a, permute): permute back, a2a
-            back = g.reshape(m, world, -1, d).transpose(0, 1).reshape(-1, d)
-            return ex._a2a(back, "gf"), None, None, None, None
-        ys = ex._a2a(g.contiguous(), "gb")
-        return ys.view(world, m, -1, d).transpose(0, 1).reshape(-1, d), None, None, None, None
+        ex, world, m = ctx.ex, ctx.world, ctx.m
+        out = ex._blocks(g.reshape(-1, g.shape[-1]), world, m, 1 if ctx.fwd else 0, "gf" if ctx.fwd else "gr")
+        return out, None, None, None, None, None
 
 
 class PeerTableExchange:
-    """Lookups read the owners' shards directly through peer pointers (one gather kernel, no id exchange, no NCCL);
-    sparse gradients travel with the library all-to-all of the baseline exchange."""
+    """Tables over peer memory, both directions.  Lookups read the owners' shards directly through peer pointers (one
+    gather kernel, no id exchange).  Gradients: every ``(row id, gradient row)`` recorded by backward is pushed straight
+    into the owning rank's staging buffer (a system-scope atomic reserves the slot, peer stores fill it); at the step
+    boundary the owner sorts the staged ids on the device and one kernel sums each row's duplicates and updates the table
+    in place (``csrc/tables.cu``).  No library collective and no host synchronisation in a step.  With one rank the
+    same kernels run on a one-entry peer list."""
 
-    def __init__(self, comm: PeerComm, tables):
+    fused_grads = True
+
+    def __init__(self, comm: PeerComm, tables, entries_per_step: int = 0, headroom: float = 1.5):
         from .table_a2a import CollectiveExchange
         self.comm = comm
-        self.fallback = CollectiveExchange(comm.group, comm.world, comm.rank, comm.device)
+        self.world = comm.world
+        self.fallback = (CollectiveExchange(comm.group, comm.world, comm.rank, comm.device) if comm.world > 1 else None)
         # re-home the shards in symmetric memory so peers can read them
         for j, sh in enumerate(tables.shards):
             sym = comm.alloc(tuple(sh.shape), sh.dtype, sh.device)
             sym.copy_(sh)
             tables.shards[j] = sym
+        dim = tables.dim
+        self.native = (tables.dtype == torch.bfloat16 and dim % 256 == 0 and dim <= 2048 and entries_per_step > 0
+                       and not tables.host_state)
+        if not self.native:
+            self.push_grads = None          # gradients travel by the library all-to-all; the update is the PyTorch one
+            self.apply_updates = None
+            return
+        # staging per table: an owner receives about its share of all ranks' entries, i.e. one rank's worth; hashing
+        # spreads the rows evenly, the headroom covers the heavy hitters that all land on one owner
+        self.cap = int(entries_per_step * headroom) + 4096
+        self.stage_ids, self.stage_g, self.stage_cnt, self.stats = [], [], [], []
+        for _ in tables.orders:
+            ids = comm.alloc((self.cap,), torch.int64, comm.device)
+            ids.fill_(0x7FFFFFFFFFFFFFFF)
+            self.stage_ids.append(ids)
+            self.stage_g.append(comm.alloc((self.cap, dim), torch.bfloat16, comm.device))
+            self.stage_cnt.append(comm.alloc((4,), torch.int32, comm.device))
+            self.stats.append(torch.zeros(2, dtype=torch.int32, device=comm.device))
+        self.overflow = torch.zeros(1, dtype=torch.int32, device=comm.device)
+        comm.barrier()
 
     def lookup(self, shard, ids, world):
         out = torch.empty(ids.numel(), shard.shape[1], dtype=shard.dtype, device=shard.device)
@@ -369,14 +421,47 @@ class PeerTableExchange:
                _I(shard.shape[1]), _I(world), L.stream())
         return out
 
+    # -- gradients: native route -------------------------------------------------------------------------------
+    def push_grads(self, j, ids, g):
+        g = g.contiguous()
+        if g.dtype != torch.bfloat16:
+            g = g.to(torch.bfloat16)
+        comm = self.comm
+        L.call("bones_table_push", L.ptr(ids.contiguous()), L.ptr(g), _L(ids.numel()), _I(g.shape[1]), comm.peers(self.stage_ids[j]),
+               comm.peers(self.stage_g[j]), comm.peers(self.stage_cnt[j]), _I(self.cap), _I(self.world), L.ptr(self.overflow), L.stream())
+
+    def apply_updates(self, tables, lr):
+        comm = self.comm
+        comm.barrier()                       # every rank's pushes of this step have landed in my staging buffers
+        mode = 0 if tables.opt == "rowrms" else 1
+        b1, b2 = tables.betas
+        for j in range(len(tables.orders)):
+            sorted_ids, order = torch.sort(self.stage_ids[j])          # device-side; empty slots hold the largest key
+            s0 = tables.row_sq[j] if mode == 0 else tables.exp_avg[j]
+            s1 = None if mode == 0 else tables.exp_avg_sq[j]
+            L.call("bones_table_update", L.ptr(sorted_ids), L.ptr(order), L.ptr(self.stage_g[j]), L.ptr(self.stage_cnt[j]), _I(self.cap),
+                   L.ptr(tables.shards[j]), L.ptr(s0), L.ptr(s1), _I(mode), _I(tables.dim), _F(lr), _F(b1), _F(b2), _F(tables.eps),
+                   _F(tables.decay), _I(tables.steps), _F(1.0 / self.world), ctypes.c_uint((tables.steps * 2654435761 + j) & 0xFFFFFFFF),
+                   L.ptr(self.stats[j]), L.stream())
+            L.call("bones_table_reset", L.ptr(self.stage_ids[j]), L.ptr(self.stage_cnt[j]), _I(self.cap), L.stream())
+        comm.barrier()                       # updates and resets are done before any rank looks up or pushes again
+
+    def read_stats(self) -> dict:
+        """Rows updated / skipped so far and entries dropped for a full staging buffer (synchronises)."""
+        st = torch.stack(self.stats).sum(0).tolist() if self.native else [0, 0]
+        return dict(touched=int(st[0]), skipped=int(st[1]), overflow=int(self.overflow.item()) if self.native else 0)
+
+    # -- gradients: library route (tables the native kernels do not cover) -------------------------------------
     def send_grads(self, ids, grads, world):
+        if self.fallback is None:
+            return ids, grads
         return self.fallback.send_grads(ids, grads, world)
 
     def all_ok(self, ok):
-        return self.fallback.all_ok(ok)
+        return ok if self.fallback is None else self.fallback.all_ok(ok)
 
     def after_update(self):
-        """Called by every rank at the end of the tables' update.  Lookups are peer loads with no collective of their
-        own, so without this a fast rank could gather rows from a shard its owner is still updating (stale or torn
-        rows); the epoch barrier (bounded wait) orders every owner's update before any rank's next gather."""
+        """Library route only.  Lookups are peer loads with no collective of their own, so without this a fast rank
+        could gather rows from a shard its owner is still updating (stale or torn rows); the epoch barrier (bounded
+        wait) orders every owner's update before any rank's next gather."""
         self.comm.barrier()

@@ -527,6 +527,17 @@ def table_unpack_view(packed: torch.Tensor, scale: torch.Tensor, bits: int) -> t
     return q * s
 
 
+@torch.no_grad()
+def table_rowrms_update(table, rows, g, row_sq, *, lr, beta, eps, decay, generator=None):
+    """Row-wise RMS update of the touched rows (in place on ``table[rows]`` and ``row_sq[rows]``): one fp32 second moment
+    per row, ``acc = beta acc + (1 - beta) mean(g^2)``, ``row = row (1 - decay) - lr g / (sqrt(acc) + eps)``; a bf16 table
+    is written back with stochastic rounding (reference: ``NgramHostTable.step``, round2/source/train.py:3686-3701)."""
+    a = row_sq.index_select(0, rows) * beta + (1.0 - beta) * g.float().square().mean(dim=1)
+    row_sq.index_copy_(0, rows, a)
+    w = table.index_select(0, rows).float() * (1.0 - lr * decay) - (lr / (a.sqrt() + eps)).unsqueeze(1) * g.float()
+    table.index_copy_(0, rows, stochastic_round_bf16(w, generator) if table.dtype == torch.bfloat16 else w.to(table.dtype))
+
+
 def stochastic_round_bf16(x: torch.Tensor, generator=None) -> torch.Tensor:
     """fp32 -> bf16 with stochastic rounding: a uniform 16-bit integer is added to the low half of the fp32 pattern
     before truncation, so the expected value of the result is ``x`` (the reference's bf16 master weights rely on the

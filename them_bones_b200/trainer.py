@@ -65,9 +65,11 @@ class Trainer:
             self.tables = HashedTables(config.table_orders, config.table_rows, config.n_embd, seed=config.table_seed, bits=config.table_bits,
                                        device=rt.device, dtype=self.dtype, group=dist.group.WORLD if rt.ddp else None,
                                        world=rt.world, rank=rt.rank, host_state=("auto" if sw["TABLE_HOST_STATE"] == "auto"
-                                                   else sw["TABLE_HOST_STATE"].lower() in ("1", "true")))
-            if self.comm is not None and rt.world > 1:
-                self.tables.exchange = self.comm.table_exchange(self.tables)
+                                                   else sw["TABLE_HOST_STATE"].lower() in ("1", "true")),
+                                       opt=sw["TABLE_OPT"])
+            if self.comm is not None:
+                # (row id, gradient) entries this rank records per step and table: one per token
+                self.tables.exchange = self.comm.table_exchange(self.tables, self.total_batch // rt.world)
             if init_state is not None:
                 self.tables.load_share({k: v for k, v in init_state.items() if k.startswith("table_")})
             model.attach_tables(self.tables)
@@ -152,7 +154,7 @@ class Trainer:
             total = loss.detach() if total is None else total + loss.detach()
         self.sched = schedules.apply_schedules(opt, self.hyper, self.step_index, self.progress())
         opt.step()
-        if self.config.mlp_precision == "mxfp8" and self.rt.device_type == "cuda":
+        if "mxfp8" in (self.config.mlp_precision, self.config.attn_proj_precision) and self.rt.device_type == "cuda":
             from .ops import mxfp8
             mxfp8.weights_updated()          # quantised weight copies are refreshed lazily on their next use
         if self.tables is not None:
