@@ -94,7 +94,8 @@ def parse():
                     help="sequences per micro-step per GPU (clamped to the rank's share of the global batch)")
     ap.add_argument("--total-batch", type=int, default=524288)
     ap.add_argument("--depth", type=int, default=20)
-    ap.add_argument("--mlp", default=os.environ.get("BONES_MLP", "bf16"))
+    ap.add_argument("--mlp", default=os.environ.get("BONES_MLP", "mxfp8"),
+                    help="MLP GEMM precision: mxfp8 (block-scaled, the benchmark configuration) or bf16")
     ap.add_argument("--attn-proj", default=os.environ.get("BONES_ATTN_PROJ", "bf16"))
     return ap.parse_args()
 

@@ -544,3 +544,30 @@ def test_grad_clip_and_bf16_stochastic_masters(monkeypatch):
     assert all(abs(a - b) < 0.05 for a, b in zip(base, lossy)) and lossy[-1] < lossy[0] - 0.1
     monkeypatch.delenv("BONES_MASTER")
     C.switches(refresh=True)
+
+
+def test_cached_decode_with_moe_blocks_and_tables_matches_full_recompute():
+    """The KV-cache route carries the token history for the table hashes and routes one token per sequence through the
+    experts; it must reproduce the cache-free route token for token."""
+    from them_bones_b200.models.tables import HashedTables
+    from them_bones_b200.utils.decode import greedy_decode, greedy_decode_full
+    cfg = GPTConfig(sequence_len=256, vocab_size=2048, n_layer=2, n_head=2, n_embd=128, doc_mask=True, moe_layers=(1,),
+                    moe_experts=4, moe_topk=2, moe_capacity=40, moe_hidden=128, table_orders=(2, 3), table_rows=1 << 10)
+    torch.manual_seed(0)
+    m = GPT(cfg)
+    m.init_weights()
+    with torch.no_grad():
+        for blk in m.transformer.h:
+            blk.attn.c_proj.weight.normal_(0, 0.05)
+        m.transformer.h[0].mlp.c_proj.weight.normal_(0, 0.05)
+        m.transformer.h[1].mlp.w_proj.normal_(0, 0.05)
+        m.lm_head.weight.normal_(0, 0.3)
+    t = HashedTables(cfg.table_orders, cfg.table_rows, cfg.n_embd)
+    for sh in t.shards:
+        sh.copy_(torch.randn_like(sh) * 0.3)
+    m.attach_tables(t)
+    m.eval()
+    pr = torch.randint(1, 2048, (3, 20))
+    pr[:, 0] = 0
+    pr[1, 10] = 0
+    assert torch.equal(greedy_decode(m, pr, 10), greedy_decode_full(m, pr, 10))

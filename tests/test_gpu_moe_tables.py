@@ -157,3 +157,65 @@ def test_native_slotting_matches_reference():
         assert torch.equal(slot_n, slot_r) and torch.equal(tok_n, tok_r), (b, t, e, k, cap)
         if cap <= 40:
             assert (slot_r == e * b * cap).any()                # some assignments were dropped: the cap was exercised
+
+
+def test_native_decode_with_moe_blocks_and_tables_matches_the_cached_route():
+    """The CUDA-graph decode step on a model with routed experts and hashed input tables: logits of every step against
+    the PyTorch KV-cache route fed the same tokens, then a whole greedy decode (graph replays) against eager stepping of
+    the same kernels."""
+    from them_bones_b200.config import GPTConfig
+    from them_bones_b200.models.gpt import GPT
+    from them_bones_b200.models.tables import HashedTables
+    from them_bones_b200.ops import _lib as L
+    from them_bones_b200.utils import decode as D
+    cfg = GPTConfig(sequence_len=512, vocab_size=4096, n_layer=3, n_head=2, n_embd=256, head_dim=128, doc_mask=True,
+                    moe_layers=(1, 2), moe_experts=4, moe_topk=2, moe_capacity=160, moe_hidden=256,
+                    table_orders=(2, 3), table_rows=1 << 12)
+    torch.manual_seed(0)
+    model = GPT(cfg)
+    model.init_weights()
+    with torch.no_grad():
+        for blk in model.transformer.h:
+            blk.attn.c_proj.weight.normal_(0, 0.02)
+        model.transformer.h[0].mlp.c_proj.weight.normal_(0, 0.02)
+        for i in (1, 2):
+            model.transformer.h[i].mlp.w_proj.normal_(0, 0.02)
+        model.lm_head.weight.normal_(0, 0.05)
+    model = model.cuda().cast_compute(torch.bfloat16).eval()
+    tables = HashedTables(cfg.table_orders, cfg.table_rows, cfg.n_embd, seed=cfg.table_seed, device="cuda", dtype=torch.bfloat16)
+    for sh in tables.shards:
+        sh.copy_(torch.randn_like(sh) * 0.3)
+    model.attach_tables(tables)
+    assert D.NativeDecoder.eligible(model)
+    torch.manual_seed(5)
+    b, p, n_new = 4, 40, 12
+    prompts = torch.randint(1, cfg.vocab_size, (b, p), device="cuda")
+    prompts[:, 0] = 0
+    prompts[1, 33] = 0
+    with torch.no_grad():
+        ca, cb = D.KVCache(model, b, p + n_new), D.KVCache(model, b, p + n_new)
+        la = D._forward_cached(model, prompts, ca)
+        D._forward_cached(model, prompts, cb)
+        tok = la.argmax(-1)
+        out = torch.zeros(b, p + n_new, dtype=torch.int64, device="cuda")
+        out[:, :p] = prompts
+        dec = D.NativeDecoder(model, cb, tok, out)
+        for s in range(5):
+            out[:, p + s] = tok                           # the history the table hashes read
+            ref = D._forward_cached(model, tok[:, None], ca)
+            dec.tok.copy_(tok)
+            dec._step()
+            got = dec.last_logits[:, :cfg.vocab_size].float()
+            assert _rel(got, ref) < 4e-2, (s, _rel(got, ref))
+            tok = ref.argmax(-1)
+        torch.cuda.synchronize()
+        L.check_error_word()
+        full = D.greedy_decode(model, prompts, n_new)
+        cc = D.KVCache(model, b, p + n_new)
+        out2 = torch.zeros_like(full)
+        out2[:, :p] = prompts
+        dec2 = D.NativeDecoder(model, cc, prompts[:, 0], out2, prompt_len=p)
+        for _ in range(p + n_new - 1):
+            dec2._step()
+        torch.cuda.synchronize()
+    assert torch.equal(full, out2) and torch.equal(full[:, :p], prompts)

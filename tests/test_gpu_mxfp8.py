@@ -121,10 +121,15 @@ def test_pair_gemm_quantising_epilogues(epi):
     acc = RF.mx_qdq(x.float(), -1) @ RF.mx_qdq(w.float(), -1).T
     ref = {"relu2": torch.relu(acc).square(), "res": acc + 0.5 * r.float(), "mul2sqrt": acc * 2 * r.float().sqrt()}[epi]
     assert _rel(d, ref) < 6e-3, _rel(d, ref)
-    # the quantised copies describe the stored tensor exactly
+    # the quantised copies are rounded from the same fp32 values as the bf16 copy: against the emulation applied to the
+    # stored bf16 tensor nearly every scale agrees (a block maximum that sits on a power-of-two boundary may differ by
+    # the bf16 rounding) and the dequantised values carry only E4M3 rounding noise
     qr, er = RF.mx_quantize(d.float(), -1)
-    assert torch.equal(_unpack_sf2(dsf, m, n, 128), er)
-    assert torch.equal(dq.view(torch.float8_e4m3fn).float(), qr.float())
+    got_e = _unpack_sf2(dsf, m, n, 128)
+    assert float((got_e.int() - er.int()).abs().max()) <= 1 and float((got_e != er).float().mean()) < 0.01
+    assert _rel(_deq(dq, got_e, -1), d) < 0.04
+    assert _rel(_deq(dq, got_e, -1), RF.mx_dequantize(qr, er, -1)) < 0.02
     qc, ec = RF.mx_quantize(d.float(), 0)
-    assert torch.equal(_unpack_sf2(dtsf, n, m, 256), ec)
-    assert torch.equal(dt.view(torch.float8_e4m3fn).float(), qc.float())
+    got_t = _unpack_sf2(dtsf, n, m, 256)
+    assert float((got_t.int() - ec.int()).abs().max()) <= 1 and float((got_t != ec).float().mean()) < 0.01
+    assert _rel(_deq(dt, got_t, 0), d) < 0.04

@@ -193,12 +193,23 @@ __device__ __forceinline__ void q_emit_row(const float (&v)[32], uint8_t* q_dst,
 // lane the block maximum of column j; lane j keeps it, derives that column's scale once, and the 32 inverse scales are
 // passed round with one shuffle each.  Lane j also stores the scale byte of column j (`sf_dst` is its address).
 __device__ __forceinline__ void q_emit_col(const float (&v)[32], int lane, uint8_t* q_dst, uint8_t* sf_dst, bool ok, bool sf_ok) {
-  uint32_t mine = 0u;
+  // every lane receives all 32 column maxima; it keeps the one of column `lane` by a binary selection tree on its lane bits
+  const bool b0 = lane & 1, b1 = lane & 2, b2 = lane & 4, b3 = lane & 8, b4 = lane & 16;
+  uint32_t l1[16];
 #pragma unroll
-  for (int j = 0; j < 32; ++j) {
-    const uint32_t mx = __reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(v[j])));
-    if (lane == j) mine = mx;
+  for (int i = 0; i < 16; ++i) {
+    const uint32_t m0 = __reduce_max_sync(0xffffffffu, __float_as_uint(v[2 * i]) & 0x7fffffffu);
+    const uint32_t m1 = __reduce_max_sync(0xffffffffu, __float_as_uint(v[2 * i + 1]) & 0x7fffffffu);
+    l1[i] = b0 ? m1 : m0;
   }
+  uint32_t l2[8], l3[4], l4[2];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) l2[i] = b1 ? l1[2 * i + 1] : l1[2 * i];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) l3[i] = b2 ? l2[2 * i + 1] : l2[2 * i];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) l4[i] = b3 ? l3[2 * i + 1] : l3[2 * i];
+  const uint32_t mine = b4 ? l4[1] : l4[0];
   int biased;
   const float my_inv = q_scale_pow2(__uint_as_float(mine), biased);
   uint32_t o[8];
@@ -217,7 +228,7 @@ __device__ __forceinline__ void q_emit_col(const float (&v)[32], int lane, uint8
 }
 
 // Epilogue warps per CTA: a multiple of four (one set per 32-lane TMEM quadrant).  16 warps leave 96 registers per
-// thread, 12 leave 128.
+// thread, 12 leave 128 and measured faster with every epilogue (default; BONES_MX_EPI_WARPS=16 selects the other build).
 
 // scale-chunk offset with 32-bit arithmetic; `shift` >= 0 when the tile height is a power of two
 __device__ __forceinline__ uint32_t q_sf_offset32(uint32_t r, uint32_t k, uint32_t kblocks, int group, int shift) {
@@ -288,21 +299,16 @@ __device__ __forceinline__ void q_quant_tile(const Mx2Params& p, uint32_t taddr0
         v[j] = t * t;
       }
     }
-    // the bf16 rounding comes first: the quantised copies describe the tensor that is stored
+    // the bf16 copy and the two MXFP8 copies are all rounded from the fp32 values (no bf16 round trip in between)
+    if (Drow != nullptr && row_ok) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      uint4 u;
-      u.x = pack_bf16(v[j * 8 + 0], v[j * 8 + 1]);
-      u.y = pack_bf16(v[j * 8 + 2], v[j * 8 + 3]);
-      u.z = pack_bf16(v[j * 8 + 4], v[j * 8 + 5]);
-      u.w = pack_bf16(v[j * 8 + 6], v[j * 8 + 7]);
-      if (Drow != nullptr && row_ok) *reinterpret_cast<uint4*>(Drow + col0 + j * 8) = u;
-      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        const float2 f = unpack_bf16(w[t]);
-        v[j * 8 + 2 * t] = f.x;
-        v[j * 8 + 2 * t + 1] = f.y;
+      for (int j = 0; j < 4; ++j) {
+        uint4 u;
+        u.x = pack_bf16(v[j * 8 + 0], v[j * 8 + 1]);
+        u.y = pack_bf16(v[j * 8 + 2], v[j * 8 + 3]);
+        u.z = pack_bf16(v[j * 8 + 4], v[j * 8 + 5]);
+        u.w = pack_bf16(v[j * 8 + 6], v[j * 8 + 7]);
+        *reinterpret_cast<uint4*>(Drow + col0 + j * 8) = u;
       }
     }
     if (WQ) q_emit_row(v, p.Dq + qrow + col0, sfq + (uint32_t)(col0 >> 7) * sfq_step + (uint32_t)((col0 & 127) >> 5), row_ok);
@@ -664,7 +670,7 @@ int bones_gemm_mxfp8_pair(const void* Aq, const void* sfa, const void* Bq, const
   static int epi_warps = 0;
   if (epi_warps == 0) {
     const char* e = getenv("BONES_MX_EPI_WARPS");
-    epi_warps = (e && atoi(e) == 12) ? 12 : 16;
+    epi_warps = (e && atoi(e) == 16) ? 16 : 12;
     BONES_CHECK(cudaFuncSetAttribute(gemm_mxfp8_pair_kernel<12>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     BONES_CHECK(cudaFuncSetAttribute(gemm_mxfp8_pair_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   }

@@ -111,7 +111,10 @@ class MoeMLP(nn.Module):
         h = xn.reshape(n, d)
         logits = F.linear(h.float(), self.router.float())
         p, idx, gates = RF.moe_route(logits, self.topk)
-        slot, tok = ops.moe_slots(idx, b, t, self.n_exp, self.cap)
+        # a sequence of t tokens cannot send more than t of them to one expert: the same routing with a smaller slot
+        # buffer for short inputs (a decode step is one token per sequence)
+        cap = min(self.cap, t)
+        slot, tok = ops.moe_slots(idx, b, t, self.n_exp, cap)
         # slot gather ([E*b*C, d], empty slots are zero rows) + exchange to the expert owners
         xs = ops.moe_dispatch_exchange(h, tok, self.ep_group, self.ep_world, self.n_exp, slot, key=self.layer)
         ys = ops.moe_experts(xs, self.w_fc, self.w_proj, self.precision)   # rows grouped by local expert
@@ -124,6 +127,6 @@ class MoeMLP(nn.Module):
             out = out + residual
         if moe_aux is not None:
             aux, lb, z, f = RF.moe_aux_terms(p, logits, idx, self.n_exp, self.topk, self.aux_w, self.z_w)
-            kept = (slot < self.n_exp * b * self.cap).float().mean()
+            kept = (slot < self.n_exp * b * cap).float().mean()
             moe_aux.append((aux, torch.cat([torch.stack([kept, lb.detach(), z.detach()]), f.detach()])))
         return out

@@ -319,6 +319,17 @@ def _as_i64(v: int) -> int:
     return v - (1 << 64) if v >= (1 << 63) else v
 
 
+def _ngram_hash(toks, order: int, rows: int, seed: int) -> torch.Tensor:
+    """``toks[j]``: the token ``j`` places back (``j = 0`` the current one), already replaced by the pad id where the
+    context does not reach that far.  All int64, same shape."""
+    h = torch.full_like(toks[0], _as_i64(seed * 0x9E3779B97F4A7C15 + order))
+    for j in range(order):
+        h = (h ^ (toks[j] + 1)) * _as_i64(HASH_MULT[j % 3])
+        h = h ^ ((h >> 29) & ((1 << 35) - 1))                 # logical shift of the wrapped value
+    h = h * _as_i64(HASH_MULT[2])
+    return ((h >> 32) & (rows - 1)).to(torch.int64) if rows <= (1 << 32) else (h & (rows - 1))
+
+
 def ngram_rows(idx: torch.Tensor, order: int, rows: int, seed: int, doc_start: torch.Tensor | None = None,
                pad_id: int = 0) -> torch.Tensor:
     """Row index for every position of ``idx [B, T]``: a 64-bit multiplicative hash of the previous ``order`` token
@@ -328,17 +339,30 @@ def ngram_rows(idx: torch.Tensor, order: int, rows: int, seed: int, doc_start: t
     b, t = idx.shape
     x = idx.to(torch.int64)
     pos = torch.arange(t, device=idx.device)[None, :]
-    h = torch.full((b, t), _as_i64(seed * 0x9E3779B97F4A7C15 + order), dtype=torch.int64, device=idx.device)
+    toks = []
     for j in range(order):
         tok = F.pad(x, (j, 0), value=pad_id)[:, :t]
         if doc_start is not None:
             tok = torch.where(pos - j >= doc_start.to(torch.int64), tok, torch.full_like(tok, pad_id))
         else:
             tok = torch.where(pos - j >= 0, tok, torch.full_like(tok, pad_id))
-        h = (h ^ (tok + 1)) * _as_i64(HASH_MULT[j % 3])
-        h = h ^ ((h >> 29) & ((1 << 35) - 1))                 # logical shift of the wrapped value
-    h = h * _as_i64(HASH_MULT[2])
-    return ((h >> 32) & (rows - 1)).to(torch.int64) if rows <= (1 << 32) else (h & (rows - 1))
+        toks.append(tok)
+    return _ngram_hash(toks, order, rows, seed)
+
+
+def ngram_rows_at(history: torch.Tensor, pos: torch.Tensor, order: int, rows: int, seed: int,
+                  doc_start: torch.Tensor | None = None, pad_id: int = 0) -> torch.Tensor:
+    """The same row index for the single position ``pos`` (a device scalar) of ``history [B, L]`` (the tokens so far):
+    what a decode step needs, with no host read of the position.  ``doc_start [B]``: first position of each sequence's
+    current document."""
+    b = history.shape[0]
+    toks = []
+    for j in range(order):
+        at = (pos.to(torch.int64) - j).reshape(1)
+        tok = history.index_select(1, at.clamp_min(0))[:, 0].to(torch.int64)
+        lo = doc_start.to(torch.int64) if doc_start is not None else torch.zeros(b, dtype=torch.int64, device=history.device)
+        toks.append(torch.where(at.expand(b) >= lo, tok, torch.full_like(tok, pad_id)))
+    return _ngram_hash(toks, order, rows, seed)
 
 
 # ----------------------------------------------------------------------------------------------------------------

@@ -31,6 +31,7 @@ class KVCache:
         self.v = torch.zeros(shape, dtype=dt, device=dev)
         self.doc_start = torch.zeros(batch, dtype=torch.int32, device=dev)
         self.len = 0
+        self.tokens = None          # token history [batch, max_len], kept when the model has hashed tables
 
 
 def _attend(q, k, v, scale, lo):
@@ -62,7 +63,14 @@ def _forward_cached(model, idx, cache: KVCache):
     cos, sin = model.cos[p0:p0 + t], model.sin[p0:p0 + t]
     x = F.embedding(idx, model.transformer.wte.weight)
     if model.tables is not None:
-        raise NotImplementedError("cached decoding with hashed tables goes through decode_with_tables")
+        # rows keyed by the last `order` tokens: the cache keeps the token history for contexts that start before this call
+        if cache.tokens is None:
+            cache.tokens = torch.zeros(b, cache.k.shape[2], dtype=torch.int64, device=dev)
+        cache.tokens[:, p0:p0 + t] = idx
+        hist, tb = cache.tokens[:, :p0 + t], model.tables
+        ids = torch.stack([RF.ngram_rows(hist, o, tb.rows, tb.seed + j, _doc_start_full(hist, cfg) if cfg.doc_mask else None)[:, p0:]
+                           for j, o in enumerate(tb.orders)])
+        x = tb.add_lookup(x, idx, None, model.table_lambda, rows=ids)
     x = RF.rms_norm(x)
     x0 = x
     skips = []
@@ -105,6 +113,10 @@ def _forward_cached(model, idx, cache: KVCache):
     return RF.softcap_logits(F.linear(x, model.lm_head.weight)[..., :cfg.vocab_size], cfg.softcap)
 
 
+def _doc_start_full(hist, cfg):
+    return RF.doc_start_positions(hist, cfg.bos_id)
+
+
 def _rope_at(x, cos, sin):
     d = x.shape[-1] // 2
     x1, x2 = x[..., :d].float(), x[..., d:].float()
@@ -117,15 +129,17 @@ class NativeDecoder:
     kernels (``csrc/decode.cu``: RoPE + QK-norm + cache append, cached attention), soft-capped logits, arg-max.  The
     position, the per-sequence document starts, the current tokens and the output buffer live on the device and are
     advanced inside the graph, so generating ``n`` tokens is ``n`` graph replays with no host synchronisation.
-    Eligible: dense bf16 models on CUDA whose blocks all have attention with head_dim 128 (no MoE, no hashed tables)."""
+    Eligible: bf16 models on CUDA whose blocks all have attention with head_dim 128.  MoE blocks run their routed experts
+    inside the graph (router, slotting, grouped expert GEMMs, combine: all device-side, a decode step uses one slot per
+    sequence and expert); hashed input tables are looked up from row ids hashed on the device from the token history."""
 
     @staticmethod
     def eligible(model) -> bool:
         cfg = model.config
         w = model.lm_head.weight
-        return (w.is_cuda and w.dtype == torch.bfloat16 and cfg.head_dim == 128 and model.tables is None
-                and not ops.reference_path() and all(blk.attn is not None and not isinstance(blk.mlp, MoeMLP)
-                                                     for blk in model.transformer.h))
+        tables_ok = model.tables is None or model.tables.dtype == torch.bfloat16
+        return (w.is_cuda and w.dtype == torch.bfloat16 and cfg.head_dim == 128 and tables_ok and getattr(model, "os1", None) is None
+                and not ops.reference_path() and all(blk.attn is not None for blk in model.transformer.h))
 
     def __init__(self, model, cache: KVCache, first_tokens: torch.Tensor, out: torch.Tensor, prompt_len: int = 0):
         # positions below ``prompt_len`` are teacher-forced from ``out`` (stepwise prefill through the same graph)
@@ -142,12 +156,13 @@ class NativeDecoder:
         # With few rows a projection has too few output tiles to pull its weights at memory speed, so its contraction
         # runs as a batch of products over K chunks of 256, each into its own fp32 slice, which the finishing kernel
         # adds in a fixed order (no atomics: a step is reproducible bit for bit).
-        self.split = b <= 128 and cfg.mlp_precision == "bf16" and cfg.n_embd % 256 == 0 and a % 256 == 0
+        self.split = b <= 128 and cfg.n_embd % 256 == 0 and a % 256 == 0
+        self.dense = [not isinstance(blk.mlp, MoeMLP) for blk in model.transformer.h]
         if self.split:
             self.wqkv = [torch.cat([blk.attn.c_q.weight, blk.attn.c_k.weight, blk.attn.c_v.weight]).contiguous()
                          for blk in model.transformer.h]
-            ws = self.wqkv + [w for blk in model.transformer.h for w in (blk.attn.c_proj.weight, blk.mlp.c_fc.weight,
-                                                                         blk.mlp.c_proj.weight)]
+            ws = self.wqkv + [blk.attn.c_proj.weight for blk in model.transformer.h]
+            ws += [w for blk, dense in zip(model.transformer.h, self.dense) if dense for w in (blk.mlp.c_fc.weight, blk.mlp.c_proj.weight)]
             self.split = all(w.shape[1] % 256 == 0 for w in ws)
             self.part = torch.empty(max(b * w.shape[0] * (w.shape[1] // 256) for w in ws), dtype=torch.float32, device=dev)
 
@@ -174,7 +189,14 @@ class NativeDecoder:
         b, tmax = tok.shape[0], cache.k.shape[2]
         if cfg.doc_mask:
             cache.doc_start.copy_(torch.where(tok == cfg.bos_id, pos.expand(b), cache.doc_start))
-        x = ops.rms_norm(ops.embedding(tok, model.transformer.wte.weight, torch.bfloat16))
+        x = ops.embedding(tok, model.transformer.wte.weight, torch.bfloat16)
+        if model.tables is not None:
+            tb = model.tables
+            ds = cache.doc_start if cfg.doc_mask else None
+            for j, o in enumerate(tb.orders):
+                rows = RF.ngram_rows_at(self.out, pos, o, tb.rows, tb.seed + j, ds)
+                x = x + model.table_lambda[j].to(x.dtype) * tb.gather(j, rows)
+        x = ops.rms_norm(x)
         x0 = x
         skips = []
         n_layer, n_skip = cfg.n_layer, model.n_skip
@@ -196,11 +218,14 @@ class NativeDecoder:
             if self.split:
                 x = self._lin(self.y, at.c_proj.weight, 1, x)
                 x, xn = ops.norm_split(x)
-                x = self._lin(self._lin(xn, blk.mlp.c_fc.weight, 2), blk.mlp.c_proj.weight, 1, x)
+                if self.dense[i]:
+                    x = self._lin(self._lin(xn, blk.mlp.c_fc.weight, 2), blk.mlp.c_proj.weight, 1, x)
+                else:
+                    x = blk.mlp(xn.view(b, 1, -1), residual=x.view(b, 1, -1)).view(b, -1)
             else:
                 x = ops.linear(self.y, at.c_proj.weight, residual=x)
                 x, xn = ops.norm_split(x)
-                x = blk.mlp(xn, residual=x)
+                x = blk.mlp(xn.view(b, 1, -1), residual=x.view(b, 1, -1)).view(b, -1) if not self.dense[i] else blk.mlp(xn, residual=x)
             if n_skip and i < n_skip:
                 skips.append(x)
         xn = ops.rms_norm(x)
@@ -241,8 +266,8 @@ def greedy_decode(model, prompts: torch.Tensor, n_new: int) -> torch.Tensor:
     b, p = prompts.shape
     if p + n_new > model.config.sequence_len:
         raise ValueError("prompt + new tokens exceed the model's sequence length")
-    if model.tables is not None or getattr(model, "os1", None) is not None or any(blk.attn is None for blk in model.transformer.h):
-        return greedy_decode_full(model, prompts, n_new)          # tables and attention-free blocks: cache-free route
+    if getattr(model, "os1", None) is not None or any(blk.attn is None for blk in model.transformer.h):
+        return greedy_decode_full(model, prompts, n_new)          # output table and attention-free blocks: cache-free route
     cache = KVCache(model, b, p + n_new)
     if NativeDecoder.eligible(model) and n_new >= 1:
         out = torch.zeros(b, p + n_new, dtype=torch.int64, device=prompts.device)
