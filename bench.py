@@ -149,11 +149,14 @@ def run_ours(args, torch_path: bool = False):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     sampler.mark_begin()
+    tr.time_optimizer = True
     e0.record()
     for i in range(args.steps):
         loss = tr.train_step(*dev[i % 2])
     e1.record()
     barrier()
+    tr.time_optimizer = False
+    opt_ms = max_over_ranks(sum(a.elapsed_time(b) for a, b in tr.optimizer_events) / max(1, len(tr.optimizer_events)), rt)
     clocks = sampler.stop()
     ms = max_over_ranks(e0.elapsed_time(e1), rt)
     launches = _lib.LAUNCHES[0] - launches0
@@ -198,6 +201,7 @@ def run_ours(args, torch_path: bool = False):
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4,
                     "ms_per_step": ms_e2e / args.steps, "final_loss": last},
             "gpu_launches": int(launches),
+            "optimizer_ms_per_step": opt_ms,      # device time of the step-boundary optimizer chain, max over ranks
             "native_ops": {k: v - counts0.get(k, 0) for k, v in ops.COUNTS.items()},
             "tflops_per_gpu": value * tr.flops_per_token / rt.world / 1e12,
             "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30,

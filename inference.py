@@ -46,8 +46,10 @@ class ModelWrapper(torch.nn.Module):
         return rank, world
 
 
-def load_for_eval(checkpoint_path: str, device="cuda"):
-    model, meta = CK.load_for_eval(checkpoint_path, device)
+def load_for_eval(checkpoint_path: str, device="cuda", rt=None):
+    """``rt``: a multi-rank runtime serves the model sharded (experts and table rows split over the ranks, which then
+    score and decode in lockstep); without it every rank is an independent replica, as in the reference."""
+    model, meta = CK.load_for_eval(checkpoint_path, device, rt=rt)
     return ModelWrapper(model, meta)
 
 

@@ -120,11 +120,13 @@ def test_bounded_peer_wait_expires_with_an_error_code():
     flags = torch.zeros(64, dtype=torch.int32, device="cuda")
     ptrs = (ctypes.c_void_p * 2)(ctypes.c_void_p(flags.data_ptr()), ctypes.c_void_p(flags.data_ptr()))
     # "rank 0 of 2": it publishes slot 0 itself, but slot 1 would have to come from the absent peer
-    L.call("bones_peer_barrier", ptrs, ctypes.c_int(0), ctypes.c_int(2), ctypes.c_int(1), ctypes.c_double(0.2), L.stream())
+    epoch = torch.zeros(1, dtype=torch.int32, device="cuda")       # the rank's barrier counter, advanced by the kernel
+    L.call("bones_peer_barrier", ptrs, ctypes.c_int(0), ctypes.c_int(2), L.ptr(epoch), ctypes.c_double(0.2), L.stream())
     torch.cuda.synchronize()
     with pytest.raises(RuntimeError, match="error code 5"):
         L.check_error_word()
     L.check_error_word()                                   # cleared: the next check passes
+    assert int(epoch) == 1
     x = torch.ones(8, device="cuda")
     assert float(x.sum()) == 8.0                           # the CUDA context is intact
 
@@ -262,3 +264,21 @@ def test_native_muon_finish_matches_pytorch(shape):
     L.check_error_word()
     assert _rel(s1, s2) < 1e-5
     assert _rel(w1 - w0, w2 - w0) < 1e-4
+
+
+def test_canary_words_after_peer_buffers_catch_an_overrun():
+    """Every peer-mapped buffer is followed by canary bytes inside its own allocation; a kernel that runs past the end of
+    the buffer changes them and the health check reports which buffer it was."""
+    from them_bones_b200.parallel.symm import SoloComm
+    from them_bones_b200.runtime import Runtime
+    comm = SoloComm(Runtime(False, 0, 0, 1, torch.device("cuda", 0), "cuda"))
+    a = comm.alloc((100, 8), torch.bfloat16, "cuda")
+    b = comm.alloc((7,), torch.float32, "cuda")
+    a.fill_(1.0)
+    b.fill_(2.0)
+    comm.check_canaries()                                         # full writes of the buffers leave the canaries alone
+    flat = a.view(-1)
+    overrun = torch.as_strided(flat, (flat.numel() + 4,), (1,))   # a view four elements past the end, still inside the allocation
+    overrun[-1] = 3.0
+    with pytest.raises(RuntimeError, match=r"\(100, 8\)"):
+        comm.check_canaries()

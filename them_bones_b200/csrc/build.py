@@ -22,9 +22,17 @@ def _newer(a, b):
     return not os.path.exists(b) or os.path.getmtime(a) > os.path.getmtime(b)
 
 
-def build(verbose: bool = False, force: bool = False) -> str:
+LIB_DEBUG = os.path.join(LIB_DIR, "libbones_b200_dbg.so")
+
+
+def build(verbose: bool = False, force: bool = False, debug_bounds: bool = False) -> str:
+    """``debug_bounds``: the second library, compiled with ``-DBONES_DEBUG_BOUNDS`` (every data-dependent index is checked,
+    a miss is counted and skipped; see ``csrc/common.cuh``), loaded instead of the release one when
+    ``BONES_DEBUG_BOUNDS=1``."""
     os.makedirs(LIB_DIR, exist_ok=True)
-    objdir = os.path.join(LIB_DIR, "obj")
+    objdir = os.path.join(LIB_DIR, "obj_dbg" if debug_bounds else "obj")
+    lib = LIB_DEBUG if debug_bounds else LIB
+    flags = FLAGS + (["-DBONES_DEBUG_BOUNDS"] if debug_bounds else [])
     os.makedirs(objdir, exist_ok=True)
     srcs = sorted(f for f in os.listdir(HERE) if f.endswith(".cu"))
     hdrs = [os.path.join(HERE, f) for f in os.listdir(HERE) if f.endswith((".cuh", ".h"))]
@@ -36,7 +44,7 @@ def build(verbose: bool = False, force: bool = False) -> str:
 
     def compile_one(job):
         src, obj = job
-        r = subprocess.run([NVCC, *FLAGS, "-c", src, "-o", obj], capture_output=True, text=True)
+        r = subprocess.run([NVCC, *flags, "-c", src, "-o", obj], capture_output=True, text=True)
         return src, r
 
     failed = False
@@ -53,13 +61,14 @@ def build(verbose: bool = False, force: bool = False) -> str:
     if failed:
         raise RuntimeError("nvcc failed")
     objs = [os.path.join(objdir, s[:-3] + ".o") for s in srcs]
-    if jobs or not os.path.exists(LIB):
-        r = subprocess.run([NVCC, "-shared", "-o", LIB, *objs, "-lcudart"], capture_output=True, text=True)
+    if jobs or not os.path.exists(lib):
+        r = subprocess.run([NVCC, "-shared", "-o", lib, *objs, "-lcudart"], capture_output=True, text=True)
         if r.returncode != 0:
             sys.stderr.write(r.stdout + r.stderr)
             raise RuntimeError("link failed")
-    return LIB
+    return lib
 
 
 if __name__ == "__main__":
     print(build(verbose="-v" in sys.argv, force="-f" in sys.argv))
+    print(build(verbose="-v" in sys.argv, force="-f" in sys.argv, debug_bounds=True))

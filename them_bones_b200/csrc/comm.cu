@@ -36,10 +36,16 @@ __device__ __forceinline__ float4 ld_peer_f4(const float* addr) {
   return v;
 }
 
-// All-rank barrier: flags[rank][slot j] lives on `rank`; rank r writes `epoch` into slot r of every peer, then waits for
-// all slots of its own array.  One block; thread j handles peer j.
-__global__ void peer_barrier_kernel(PeerPtrs flags, int rank, int world, int epoch, long long limit_cycles, int* err) {
+// All-rank barrier: flags[rank][slot j] lives on `rank`; rank r writes its epoch into slot r of every peer, then waits for
+// all slots of its own array.  The epoch is a device-side counter of this rank that the kernel itself advances (every
+// rank runs the same sequence of barriers, so the counters agree): nothing about a barrier is baked into its launch
+// arguments, and a CUDA graph that contains barriers can be replayed.  One block; thread j handles peer j.
+__global__ void peer_barrier_kernel(PeerPtrs flags, int rank, int world, int* epoch_dev, long long limit_cycles, int* err) {
+  __shared__ int epoch_s;
   const int j = threadIdx.x;
+  if (j == 0) epoch_s = *epoch_dev + 1;
+  __syncthreads();
+  const int epoch = epoch_s;
   __threadfence_system();
   if (j < world) st_release_sys(reinterpret_cast<int*>(flags.p[j]) + rank, epoch);
   if (j < world) {
@@ -53,6 +59,8 @@ __global__ void peer_barrier_kernel(PeerPtrs flags, int rank, int world, int epo
       __nanosleep(64);
     }
   }
+  __syncthreads();
+  if (j == 0) *epoch_dev = epoch;
 }
 
 // Sum of W fp32 vectors, identical on every rank (small scalar stacks): out[i] = scale * sum_r in_r[i].
@@ -183,12 +191,13 @@ __global__ void peer_publish_kernel(const float* __restrict__ src, PeerPtrs Wt, 
 
 // MoE / table exchange helper: rows gathered from peers.  out[i] = table_{owner[i]}[local[i]] (bf16 rows of C columns).
 __global__ void peer_gather_rows_kernel(PeerPtrs tables, const long long* __restrict__ ids, __nv_bfloat16* __restrict__ out, int n, int C,
-                                        int world) {
+                                        int world, long long rows_per_shard) {
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (row >= n) return;
   const long long id = ids[row];
   const int owner = (int)(id % world);
   const long long local = id / world;
+  if (!BONES_INDEX_OK(local, 0, rows_per_shard)) return;
   const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(tables.p[owner]) + local * C;
   for (int c = lane * 8; c < C; c += 256) {
     uint4 u;
@@ -240,7 +249,9 @@ __global__ void peer_dispatch_grouped_kernel(const __nv_bfloat16* __restrict__ h
   const long long e = s / rows, j = s - e * rows;
   const int d = (int)(e / m), el = (int)(e - (long long)d * m);
   const long long t = tok[s];
+  (void)BONES_INDEX_OK(t, 0, n_tokens + 1);               // n_tokens itself marks an empty slot
   const bool valid = t >= 0 && t < n_tokens;
+  if (!BONES_INDEX_OK(d, 0, world)) return;
   __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(dst.p[d]) + (((long long)el * world + rank) * rows + j) * C;
   for (int c = lane * 8; c < C; c += 256) {
     uint4 u = make_uint4(0, 0, 0, 0);
@@ -285,10 +296,10 @@ static PeerPtrs make_ptrs(void* const* ptrs, int world) {
 extern "C" {
 using namespace bones;
 
-int bones_peer_barrier(void* const* flag_ptrs, int rank, int world, int epoch, double limit_seconds, void* stream) {
+int bones_peer_barrier(void* const* flag_ptrs, int rank, int world, int* epoch_dev, double limit_seconds, void* stream) {
   if (world > kMaxPeers) return -2;
   const long long limit = (long long)(limit_seconds * 1.9e9);
-  peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(make_ptrs(flag_ptrs, world), rank, world, epoch, limit, error_word());
+  peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(make_ptrs(flag_ptrs, world), rank, world, epoch_dev, limit, error_word());
   return (int)cudaGetLastError();
 }
 
@@ -328,9 +339,11 @@ int bones_peer_publish(const float* src, void* const* w_ptrs, long long off, lon
   return (int)cudaGetLastError();
 }
 
-int bones_peer_gather_rows(void* const* table_ptrs, const long long* ids, void* out, int n, int C, int world, void* stream) {
+int bones_peer_gather_rows(void* const* table_ptrs, const long long* ids, void* out, int n, int C, int world, long long rows_per_shard,
+                           void* stream) {
   if (world > kMaxPeers || (C % 8)) return -2;
-  peer_gather_rows_kernel<<<(n + 7) / 8, 256, 0, (cudaStream_t)stream>>>(make_ptrs(table_ptrs, world), ids, (__nv_bfloat16*)out, n, C, world);
+  peer_gather_rows_kernel<<<(n + 7) / 8, 256, 0, (cudaStream_t)stream>>>(make_ptrs(table_ptrs, world), ids, (__nv_bfloat16*)out, n, C, world,
+                                                                         rows_per_shard);
   return (int)cudaGetLastError();
 }
 
@@ -366,3 +379,4 @@ int bones_peer_all_to_all(const void* src, void* const* dst_ptrs, long long chun
   return (int)cudaGetLastError();
 }
 }  // extern "C"
+BONES_BOUNDS_EXPORT(comm)

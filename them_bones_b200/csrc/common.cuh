@@ -323,6 +323,37 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Debug-bounds build (-DBONES_DEBUG_BOUNDS, library libbones_b200_dbg.so): every data-dependent index (token ids, slot
+// tables, hashed row ids, staging positions) is checked against the extent it addresses; a miss is counted, its value
+// and source line are kept, and the access is skipped.  No memory checker runs on the machines this library is
+// developed on; this build is its stand-in for the index-driven kernels.  The release build compiles the checks away.
+// ---------------------------------------------------------------------------------------------------------------
+#ifdef BONES_DEBUG_BOUNDS
+static __device__ int g_bounds_hits = 0;
+static __device__ long long g_bounds_last[2] = {0, 0};
+__device__ __forceinline__ bool bones_index_ok(long long i, long long lo, long long hi, int line) {
+  if (i >= lo && i < hi) return true;
+  atomicAdd(&g_bounds_hits, 1);
+  g_bounds_last[0] = i;
+  g_bounds_last[1] = line;
+  return false;
+}
+#define BONES_INDEX_OK(idx, lo, hi) bones::bones_index_ok((long long)(idx), (long long)(lo), (long long)(hi), __LINE__)
+// one per source file: reads and clears that file's counter; last[0] = the offending index, last[1] = the source line
+#define BONES_BOUNDS_EXPORT(tu)                                                    \
+  extern "C" int bones_bounds_hits_##tu(long long* last) {                          \
+    int h = 0, z = 0;                                                               \
+    if (cudaMemcpyFromSymbol(&h, bones::g_bounds_hits, sizeof(int)) != cudaSuccess) return -1;   \
+    if (last) cudaMemcpyFromSymbol(last, bones::g_bounds_last, 2 * sizeof(long long));           \
+    cudaMemcpyToSymbol(bones::g_bounds_hits, &z, sizeof(int));                      \
+    return h;                                                                       \
+  }
+#else
+#define BONES_INDEX_OK(idx, lo, hi) true
+#define BONES_BOUNDS_EXPORT(tu)
+#endif
+
 }  // namespace bones
 
 // ---------------------------------------------------------------------------------------------------------------

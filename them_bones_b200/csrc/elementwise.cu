@@ -327,6 +327,7 @@ __global__ void gather_rows_kernel(const __nv_bfloat16* table, const IdxT* idx, 
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (row >= n) return;
   const long long src = (long long)idx[row];
+  (void)BONES_INDEX_OK(src, 0, n_rows + 1);            // n_rows itself is the "empty slot" marker
   const bool valid = src >= 0 && src < n_rows;
   for (int c = lane * 8; c < C; c += 256) {
     uint4 u = make_uint4(0, 0, 0, 0);
@@ -341,6 +342,7 @@ __global__ void scatter_add_rows_kernel(const __nv_bfloat16* dy, const IdxT* idx
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (row >= n) return;
   const long long dst = (long long)idx[row];
+  (void)BONES_INDEX_OK(dst, 0, n_rows + 1);
   if (dst < 0 || dst >= n_rows) return;
   for (int c = lane * 8; c < C; c += 256) {
     const uint4 u = *reinterpret_cast<const uint4*>(dy + (size_t)row * C + c);
@@ -871,3 +873,4 @@ int bones_sparse_adam(void* table, const long long* rows, const float* g, float*
   return (int)cudaGetLastError();
 }
 }  // extern "C"
+BONES_BOUNDS_EXPORT(elementwise)

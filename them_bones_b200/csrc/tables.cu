@@ -37,13 +37,14 @@ __device__ __forceinline__ uint32_t tab_hash(uint32_t a, uint32_t b, uint32_t c)
 }
 
 __global__ void table_push_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ g, long long n, int C, TabPeers stage_ids,
-                                  TabPeers stage_g, TabPeers stage_cnt, int cap, int world, int* __restrict__ overflow) {
+                                  TabPeers stage_g, TabPeers stage_cnt, int cap, int world, int* __restrict__ overflow, long long rows_per_shard) {
   const long long e = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (e >= n) return;
   const long long id = ids[e];
   const int owner = (int)(id % world);
   const long long local = id / world;
+  if (!BONES_INDEX_OK(local, 0, rows_per_shard)) return;
   int pos = 0;
   if (lane == 0) pos = atomicAdd_system(reinterpret_cast<int*>(stage_cnt.p[owner]), 1);
   pos = __shfl_sync(0xffffffffu, pos, 0);
@@ -63,19 +64,21 @@ __global__ void table_update_kernel(const long long* __restrict__ sorted_ids, co
                                     const __nv_bfloat16* __restrict__ stage_g, const int* __restrict__ cnt_ptr, int cap,
                                     __nv_bfloat16* __restrict__ table, float* __restrict__ state0, float* __restrict__ state1, int mode, float lr,
                                     float beta1, float beta2, float eps, float decay, float c1, float c2, float inv_world, uint32_t seed,
-                                    int* __restrict__ stats) {
+                                    int* __restrict__ stats, long long rows_per_shard) {
   constexpr int C = NV * 256;
   const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   const int n = min(*cnt_ptr, cap);
   if (i >= n) return;
   const long long id = sorted_ids[i];
   if (i > 0 && sorted_ids[i - 1] == id) return;           // not the head of its run
+  if (!BONES_INDEX_OK(id, 0, rows_per_shard)) return;
   float acc[NV][8];
 #pragma unroll
   for (int v = 0; v < NV; ++v)
 #pragma unroll
     for (int t = 0; t < 8; ++t) acc[v][t] = 0.f;
   for (int j = i; j < n && sorted_ids[j] == id; ++j) {
+    if (!BONES_INDEX_OK(order[j], 0, cap)) break;
     const __nv_bfloat16* src = stage_g + order[j] * (long long)C + lane * 8;
 #pragma unroll
     for (int v = 0; v < NV; ++v) {
@@ -171,12 +174,12 @@ using namespace bones;
 // ids [n] global row ids, g [n, C] bf16 gradient rows.  stage_*_ptrs: the W ranks' staging buffers (ids int64 [cap],
 // rows bf16 [cap, C], counter int32 [1]).  overflow: local int32 counter of entries that found the owner's buffer full.
 int bones_table_push(const long long* ids, const void* g, long long n, int C, void* const* stage_ids_ptrs, void* const* stage_g_ptrs,
-                     void* const* stage_cnt_ptrs, int cap, int world, int* overflow, void* stream) {
+                     void* const* stage_cnt_ptrs, int cap, int world, int* overflow, long long rows_per_shard, void* stream) {
   if (world > kTabMaxPeers || (C % 8)) return -2;
   if (n == 0) return 0;
   table_push_kernel<<<(unsigned)((n + 7) / 8), 256, 0, (cudaStream_t)stream>>>(ids, (const __nv_bfloat16*)g, n, C, tab_ptrs(stage_ids_ptrs, world),
                                                                               tab_ptrs(stage_g_ptrs, world), tab_ptrs(stage_cnt_ptrs, world), cap,
-                                                                              world, overflow);
+                                                                              world, overflow, rows_per_shard);
   return (int)cudaGetLastError();
 }
 
@@ -184,7 +187,7 @@ int bones_table_push(const long long* ids, const void* g, long long n, int C, vo
 // permutation that sorted them.  stats[0] += rows updated, stats[1] += rows skipped for a non-finite gradient.
 int bones_table_update(const long long* sorted_ids, const long long* order, const void* stage_g, const int* cnt, int cap, void* table, float* state0,
                        float* state1, int mode, int C, float lr, float beta1, float beta2, float eps, float decay, int step, float inv_world,
-                       unsigned seed, int* stats, void* stream) {
+                       unsigned seed, int* stats, long long rows_per_shard, void* stream) {
   if ((C % 256) || C > 2048 || cap <= 0) return -2;
   const float c1 = 1.0f - powf(beta1, (float)step), c2 = 1.0f - powf(beta2, (float)step);
   const dim3 grid((unsigned)((cap + 7) / 8)), block(256);
@@ -192,7 +195,8 @@ int bones_table_update(const long long* sorted_ids, const long long* order, cons
 #define BONES_TAB_CASE(NV)                                                                                                                 \
   case NV:                                                                                                                                 \
     table_update_kernel<NV><<<grid, block, 0, st>>>(sorted_ids, order, (const __nv_bfloat16*)stage_g, cnt, cap, (__nv_bfloat16*)table, state0, \
-                                                    state1, mode, lr, beta1, beta2, eps, decay, c1, c2, inv_world, seed, stats);          \
+                                                    state1, mode, lr, beta1, beta2, eps, decay, c1, c2, inv_world, seed, stats,           \
+                                                    rows_per_shard);                                                                       \
     break;
   switch (C / 256) {
     BONES_TAB_CASE(1) BONES_TAB_CASE(2) BONES_TAB_CASE(3) BONES_TAB_CASE(4) BONES_TAB_CASE(5) BONES_TAB_CASE(6) BONES_TAB_CASE(7) BONES_TAB_CASE(8)
@@ -209,3 +213,4 @@ int bones_table_reset(long long* stage_ids, int* cnt, int cap, void* stream) {
   return (int)cudaGetLastError();
 }
 }  // extern "C"
+BONES_BOUNDS_EXPORT(tables)

@@ -12,7 +12,9 @@ import os
 import torch
 
 _LIB = None
-_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib", "libbones_b200.so")
+DEBUG_BOUNDS = os.environ.get("BONES_DEBUG_BOUNDS", "0") not in ("0", "", "false")
+_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib",
+                     "libbones_b200_dbg.so" if DEBUG_BOUNDS else "libbones_b200.so")
 
 
 def lib_path() -> str:
@@ -63,6 +65,26 @@ def check_error_word():
     rc = load().bones_error_read_clear()
     if rc != 0:
         raise RuntimeError(f"a native kernel reported error code {rc} (bounded wait expired or bad argument)")
+    if DEBUG_BOUNDS:
+        hits = bounds_hits()
+        if hits:
+            raise RuntimeError(f"debug-bounds build: out-of-range indices were caught and skipped: {hits}")
+
+
+def bounds_hits() -> dict:
+    """Debug-bounds library only: ``{source file: (count, offending index, source line)}`` of the index checks that
+    failed since the last call (read and cleared; synchronises)."""
+    out = {}
+    lib = load()
+    for tu in ("elementwise", "comm", "tables"):
+        fn = getattr(lib, f"bones_bounds_hits_{tu}", None)
+        if fn is None:
+            continue
+        last = (ctypes.c_longlong * 2)()
+        n = fn(last)
+        if n:
+            out[tu] = (int(n), int(last[0]), int(last[1]))
+    return out
 
 
 EPI_BF16, EPI_BF16_RES, EPI_RELU2, EPI_ACC_F32, EPI_MUL_2SQRT, EPI_F32, EPI_F32_RES, EPI_SOFTCAP = range(8)

@@ -108,6 +108,12 @@ def main():
         print(f"moe+tables losses nccl {mres['nccl']} fused {mres['fused']} ok {moe_ok}")
     if not moe_ok:
         ok = False
+    try:                                   # nothing wrote past the end of a symmetric buffer in any of the runs above
+        tr.comm.check_canaries()
+        tr2.comm.check_canaries()
+    except RuntimeError as exc:
+        print(f"rank {rt.rank}: {exc}")
+        ok = False
     flag = torch.tensor([int(ok)], device=rt.device)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     L.check_error_word()

@@ -47,7 +47,8 @@ class PeerComm:
         self.device = rt.device
         self.wait_seconds = wait_seconds
         self._handles = {}                    # data_ptr -> (tensor, handle, ptr array)
-        self.epoch = 0
+        self._canaries = []
+        self.epoch_dev = torch.zeros(1, dtype=torch.int32, device=self.device)    # advanced by the barrier kernel itself
         self.flags = self.alloc((64,), torch.int32, self.device)
         self.gsq = torch.zeros(1, dtype=torch.float32, device=self.device)
         self.launches = 0
@@ -57,12 +58,34 @@ class PeerComm:
         return cls(rt)
 
     # -- symmetric allocation ---------------------------------------------------------------------------------
+    CANARY = 0xA5
+
     def alloc(self, shape, dtype, device):
-        t = self.symm_mem.empty(*shape, dtype=dtype, device=device)
-        t.zero_()
-        hdl = self.symm_mem.rendezvous(t, self.group)
+        """Symmetric allocation of ``shape``, zeroed, followed by 256 bytes of canary that no kernel should ever touch:
+        peers write into these buffers with offsets computed on other GPUs, and ``check_canaries()`` is how an overrun
+        shows up (no memory checker runs on these machines)."""
+        n = 1
+        for d in shape:
+            n *= int(d)
+        item = torch.empty((), dtype=dtype).element_size()
+        pad = 256 // item
+        base = self.symm_mem.empty(n + pad, dtype=dtype, device=device)
+        base.zero_()
+        base[n:].view(torch.uint8).fill_(self.CANARY)
+        hdl = self.symm_mem.rendezvous(base, self.group)
+        t = base[:n].view(*shape)
         self._handles[t.data_ptr()] = (t, hdl, _ptr_array(hdl.buffer_ptrs))
+        self._canaries.append((tuple(shape), dtype, base[n:].view(torch.uint8)))
         return t
+
+    def check_canaries(self) -> None:
+        """Raises if any byte after a symmetric buffer changed (synchronises)."""
+        if not self._canaries:
+            return
+        bad = torch.stack([(c != self.CANARY).any() for _, _, c in self._canaries])
+        if bool(bad.any()):
+            which = [f"{shape} {dtype}" for (shape, dtype, _), b in zip(self._canaries, bad.tolist()) if b]
+            raise RuntimeError(f"a kernel wrote past the end of a symmetric buffer: {which}")
 
     def peer_addresses(self, t):
         """The W device addresses of symmetric tensor ``t`` as Python ints (index = rank)."""
@@ -80,8 +103,7 @@ class PeerComm:
 
     # -- ordering -----------------------------------------------------------------------------------------------
     def barrier(self):
-        self.epoch += 1
-        L.call("bones_peer_barrier", self.peers(self.flags), _I(self.rank), _I(self.world), _I(self.epoch),
+        L.call("bones_peer_barrier", self.peers(self.flags), _I(self.rank), _I(self.world), L.ptr(self.epoch_dev),
                _D(self.wait_seconds), L.stream())
         self.launches += 1
 
@@ -236,13 +258,20 @@ class SoloComm(PeerComm):
         self.symm_mem, self.rt, self.group = None, rt, None
         self.world, self.rank, self.device = 1, 0, rt.device
         self._handles = {}
-        self.epoch = 0
+        self._canaries = []
         self.gsq = torch.zeros(1, dtype=torch.float32, device=self.device)
         self.launches = 0
 
     def alloc(self, shape, dtype, device):
-        t = torch.zeros(*shape, dtype=dtype, device=device)
+        n = 1
+        for d in shape:
+            n *= int(d)
+        pad = 256 // torch.empty((), dtype=dtype).element_size()
+        base = torch.zeros(n + pad, dtype=dtype, device=device)
+        base[n:].view(torch.uint8).fill_(self.CANARY)
+        t = base[:n].view(*shape)
         self._handles[t.data_ptr()] = (t, None, _ptr_array([t.data_ptr()]))
+        self._canaries.append((tuple(shape), dtype, base[n:].view(torch.uint8)))
         return t
 
     def peer_addresses(self, t):
@@ -395,6 +424,7 @@ class PeerTableExchange:
             sym.copy_(sh)
             tables.shards[j] = sym
         dim = tables.dim
+        self.rows_per_shard = tables.local_rows
         self.native = (tables.dtype == torch.bfloat16 and dim % 256 == 0 and dim <= 2048 and entries_per_step > 0
                        and not tables.host_state)
         if not self.native:
@@ -418,7 +448,7 @@ class PeerTableExchange:
     def lookup(self, shard, ids, world):
         out = torch.empty(ids.numel(), shard.shape[1], dtype=shard.dtype, device=shard.device)
         L.call("bones_peer_gather_rows", self.comm.peers(shard), L.ptr(ids.contiguous()), L.ptr(out), _I(ids.numel()),
-               _I(shard.shape[1]), _I(world), L.stream())
+               _I(shard.shape[1]), _I(world), _L(shard.shape[0]), L.stream())
         return out
 
     # -- gradients: native route -------------------------------------------------------------------------------
@@ -428,7 +458,8 @@ class PeerTableExchange:
             g = g.to(torch.bfloat16)
         comm = self.comm
         L.call("bones_table_push", L.ptr(ids.contiguous()), L.ptr(g), _L(ids.numel()), _I(g.shape[1]), comm.peers(self.stage_ids[j]),
-               comm.peers(self.stage_g[j]), comm.peers(self.stage_cnt[j]), _I(self.cap), _I(self.world), L.ptr(self.overflow), L.stream())
+               comm.peers(self.stage_g[j]), comm.peers(self.stage_cnt[j]), _I(self.cap), _I(self.world), L.ptr(self.overflow),
+               _L(self.rows_per_shard), L.stream())
 
     def apply_updates(self, tables, lr):
         comm = self.comm
@@ -442,7 +473,7 @@ class PeerTableExchange:
             L.call("bones_table_update", L.ptr(sorted_ids), L.ptr(order), L.ptr(self.stage_g[j]), L.ptr(self.stage_cnt[j]), _I(self.cap),
                    L.ptr(tables.shards[j]), L.ptr(s0), L.ptr(s1), _I(mode), _I(tables.dim), _F(lr), _F(b1), _F(b2), _F(tables.eps),
                    _F(tables.decay), _I(tables.steps), _F(1.0 / self.world), ctypes.c_uint((tables.steps * 2654435761 + j) & 0xFFFFFFFF),
-                   L.ptr(self.stats[j]), L.stream())
+                   L.ptr(self.stats[j]), _L(self.rows_per_shard), L.stream())
             L.call("bones_table_reset", L.ptr(self.stage_ids[j]), L.ptr(self.stage_cnt[j]), _I(self.cap), L.stream())
         comm.barrier()                       # updates and resets are done before any rank looks up or pushes again
 

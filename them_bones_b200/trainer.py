@@ -82,6 +82,7 @@ class Trainer:
         if self.comm is not None and config.moe_layers and rt.world > 1:
             self.comm.install_moe(model)
         self.step_index = 0
+        self.time_optimizer, self.optimizer_events = False, []
         self.bad_steps = 0
         self.t_start = time.time()
         self._agreed_clock = None                 # set by the step loop once the ranks have exchanged rank 0's clock
@@ -114,6 +115,8 @@ class Trainer:
         if self.rt.device_type == "cuda" and not ops.reference_path():
             from .ops import _lib
             _lib.check_error_word()
+        if self.comm is not None:
+            self.comm.check_canaries()           # a write past the end of a peer-mapped buffer
         if hasattr(self.optimizer, "count_bad_steps"):
             self.bad_steps = self.optimizer.count_bad_steps()
         return self.bad_steps
@@ -153,7 +156,14 @@ class Trainer:
             opt.accumulate()
             total = loss.detach() if total is None else total + loss.detach()
         self.sched = schedules.apply_schedules(opt, self.hyper, self.step_index, self.progress())
-        opt.step()
+        if self.time_optimizer:          # device time of the step-boundary optimizer chain (events only, read by the caller)
+            ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            ev[0].record()
+            opt.step()
+            ev[1].record()
+            self.optimizer_events.append(ev)
+        else:
+            opt.step()
         if "mxfp8" in (self.config.mlp_precision, self.config.attn_proj_precision) and self.rt.device_type == "cuda":
             from .ops import mxfp8
             mxfp8.weights_updated()          # quantised weight copies are refreshed lazily on their next use

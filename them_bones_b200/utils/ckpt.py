@@ -59,7 +59,7 @@ def model_state(model, optimizer=None, group=None) -> dict:
 def _gather_rows(table) -> dict:
     """A row-sharded table's checkpoint entries with every rank's share interleaved back (owner = row % world)."""
     share = table.state_for_checkpoint()
-    if not _is_dist():
+    if not _is_dist() or getattr(table, "world", 1) == 1:       # an unsharded table already holds every row
         return share
     parts = [None] * dist.get_world_size()
     dist.all_gather_object(parts, share)
@@ -167,28 +167,49 @@ def check_declared_length(model, trained_seq_len: int) -> None:
         raise RuntimeError(f"model_config.sequence_len={declared} differs from the trained window length {trained_seq_len}")
 
 
-def load_for_eval(path: str, device="cpu", dtype=None):
+def load_for_eval(path: str, device="cpu", dtype=None, rt=None):
     """Rebuild the model from a checkpoint with no environment: ``GPTConfig(**model_config)``, strict load of the
-    dense state, experts and tables attached separately, eval mode.  Every rank is an independent full replica (all
-    experts local)."""
+    dense state, experts and tables attached separately, eval mode.
+
+    Without ``rt`` every rank is an independent full replica (all experts local, whole tables), as in the reference
+    (round2/source/train.py:21031-21126).  With a multi-rank ``rt`` (``runtime.init_runtime``) the model is served
+    sharded: each rank keeps ``E / world`` experts and ``rows / world`` rows of every table, the ranks score / decode in
+    lockstep, experts are reached by the fused peer-memory dispatch and table rows by peer gathers -- the layout a model
+    whose tables do not fit one GPU needs."""
     from ..models.gpt import GPT
     from ..models.tables import HashedTables
     ckpt = torch.load(path, map_location="cpu", weights_only=True, mmap=True)
     config = GPTConfig(**ckpt["model_config"])
     state = dict(ckpt["model_state"])
     device = torch.device(device)
-    model = GPT(config)
+    sharded = rt is not None and rt.world > 1 and (bool(config.moe_layers) or bool(config.table_orders))
+    world, rank = (rt.world, rt.rank) if sharded else (1, 0)
+    model = GPT(config, ep_group=dist.group.WORLD if (sharded and config.moe_layers) else None,
+                ep_world=world if config.moe_layers else 1, ep_rank=rank if config.moe_layers else 0)
     table_state = {k: state.pop(k) for k in list(state) if k.startswith("table_") and not k.startswith("table_lambda")}
     os1_state = {k: state.pop(k) for k in list(state) if k in ("os1_table", "os1_scale")}
-    model.load_state_dict(state, strict=True)
+    if sharded:
+        load_model_state(model, state, ep_world=world if config.moe_layers else 1, ep_rank=rank)
+    else:
+        model.load_state_dict(state, strict=True)
     dtype = dtype or (torch.bfloat16 if device.type == "cuda" else torch.float32)
     model = model.to(device)
     model.cast_compute(dtype)
+    comm = None
+    if sharded and device.type == "cuda":
+        from ..parallel import symm
+        comm = symm.create_or_fallback(rt)
     if config.table_orders:
         tables = HashedTables(config.table_orders, config.table_rows, config.n_embd, seed=config.table_seed, bits=config.table_bits,
-                              device=device, dtype=dtype)
+                              device=device, dtype=dtype, group=dist.group.WORLD if sharded else None, world=world, rank=rank,
+                              opt="rowrms")
         tables.load_share(table_state)
+        if comm is not None:
+            tables.exchange = comm.table_exchange(tables)
         model.attach_tables(tables)
+    if comm is not None and config.moe_layers:
+        comm.install_moe(model)
+    model.comm = comm
     if config.os1_rows:
         from ..models.os1 import OutputTable
         os1 = OutputTable(config, device=device, dtype=dtype)
