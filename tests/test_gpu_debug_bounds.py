@@ -37,7 +37,7 @@ L.call("bones_gather_rows", L.ptr(table), L.ptr(idx), ctypes.c_int(1), L.ptr(out
        ctypes.c_longlong(100), L.stream())
 torch.cuda.synchronize()
 hits = L.bounds_hits()
-assert hits["elementwise"][0] == 1 and hits["elementwise"][1] == 250, hits
+assert hits["elementwise"][0] >= 1 and hits["elementwise"][1] == 250, hits      # every lane of the row's warp reports it
 assert torch.equal(out[0], table[3]) and float(out[1].float().abs().sum()) == 0.0
 assert L.bounds_hits() == {}                   # read and cleared
 print("DEBUG_BOUNDS_OK")

@@ -69,6 +69,7 @@ struct Mx2Params {
   int tiles_m, tiles_n;
   int splits, atomic, wide;
   int sf_sets;                  // copies of the scale columns in TMEM that the K blocks rotate through (1, 2 or 4)
+  int sf_warp;                  // 1: a warp of its own issues the scale copies, ahead of the MMA thread
 };
 
 constexpr int QM = 256, QK = 128, QSTAGES = 6;
@@ -142,6 +143,10 @@ __device__ __forceinline__ void q_umma_mxf8_pair(uint32_t d_tmem, uint64_t a_des
 // its own shared memory at the descriptor's offset)
 __device__ __forceinline__ void q_cp_sf_pair(uint32_t taddr, uint64_t sdesc) {
   asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+// commit that arrives on a barrier of the issuing (leader) CTA only
+__device__ __forceinline__ void q_commit_local(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void q_commit_pair(uint32_t bar) {
   const uint16_t mask = 3;
@@ -318,8 +323,11 @@ __device__ __forceinline__ void q_quant_tile(const Mx2Params& p, uint32_t taddr0
   }
 }
 
+constexpr int kSfSetsMax = 4;
+constexpr int kNumBars = 2 * QSTAGES + 4 + 2 * kSfSetsMax;
+
 template <int kEpiWarps>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(64 + 32 * kEpiWarps, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(96 + 32 * kEpiWarps, 1)
 gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                        const __grid_constant__ CUtensorMap tma_sfa, const __grid_constant__ CUtensorMap tma_sfb, const Mx2Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -331,9 +339,11 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
   auto empty = [&](int s) { return bars + 8u * (QSTAGES + s); };
   auto tfull = [&](int a) { return bars + 8u * (2 * QSTAGES + a); };
   auto tempty = [&](int a) { return bars + 8u * (2 * QSTAGES + 2 + a); };
-  const uint32_t tmem_slot = bars + 8u * (2 * QSTAGES + 4);
-  volatile uint32_t* tmem_slot_g = reinterpret_cast<volatile uint32_t*>(gen + QSTAGES * QSTAGE_STRIDE + 8 * (2 * QSTAGES + 4));
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + QSTAGES * QSTAGE_STRIDE + 8 * (2 * QSTAGES + 4) + 8);
+  auto sffull = [&](int i) { return bars + 8u * (2 * QSTAGES + 4 + i); };
+  auto sfempty = [&](int i) { return bars + 8u * (2 * QSTAGES + 4 + kSfSetsMax + i); };
+  const uint32_t tmem_slot = bars + 8u * kNumBars;
+  volatile uint32_t* tmem_slot_g = reinterpret_cast<volatile uint32_t*>(gen + QSTAGES * QSTAGE_STRIDE + 8 * kNumBars);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + QSTAGES * QSTAGE_STRIDE + 8 * kNumBars + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = q_cluster_ctarank();
@@ -348,6 +358,10 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull(a), 1);       // one multicast commit
       mbar_init(tempty(a), 2 * kEpiWarps);     // leader: the epilogue warps of both CTAs
+    }
+    for (int i = 0; i < kSfSetsMax; ++i) {
+      mbar_init(sffull(i), 1);      // the scale-copy thread's commit
+      mbar_init(sfempty(i), 1);     // the MMA thread's commit
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -381,9 +395,9 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
       bool ok = true;
       for (int tile = cluster_id; tile < total && ok; tile += n_clusters) {
         int b, mb, nb;
-        const int sp = tile / base_tiles;
+        const int sp = p.splits == 1 ? 0 : tile / base_tiles;
         decode_tile_q(tile - sp * base_tiles, p.tiles_m, p.tiles_n, b, mb, nb);
-        const int kb0 = (int)((long long)KB * sp / p.splits), kb1 = (int)((long long)KB * (sp + 1) / p.splits);
+        const int kb0 = p.splits == 1 ? 0 : (int)((long long)KB * sp / p.splits), kb1 = p.splits == 1 ? KB : (int)((long long)KB * (sp + 1) / p.splits);
         const int m0 = mb * QM + (int)rank * 128, n0 = nb * bn + (int)rank * half_n;
         const int sfa_row = b * p.sfa_rows_per_batch + (2 * mb + (int)rank) * KB * 2;      // 256-byte rows, 2 per chunk
         const int sfb_row = b * p.sfb_rows_per_batch + nb * KB * 4;                         // 4 per (tile, K block)
@@ -409,7 +423,7 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
       const uint32_t b_step = p.b_major ? (32 * 128) >> 4 : 32 >> 4;
       const uint32_t a_lbo = p.a_major ? 128 * 128 : 0, b_lbo = p.b_major ? 128 * 128 : 0;
       int stage = 0, acc = 0, sfset = 0;
-      uint32_t phase = 0, acc_phase = 0;
+      uint32_t phase = 0, acc_phase = 0, sf_phase = 0;
       bool ok = true;
       uint32_t idesc[4];
 #pragma unroll
@@ -423,33 +437,68 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
         if (!mbar_wait(tempty(acc), acc_phase ^ 1u, abort_flag, p.err, ERR_WAIT_TMEM_EMPTY)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem + (uint32_t)(acc * bn);
-        const int sp = tile / base_tiles;
-        const int kb0 = (int)((long long)KB * sp / p.splits), kb1 = (int)((long long)KB * (sp + 1) / p.splits);
+        const int sp = p.splits == 1 ? 0 : tile / base_tiles;
+        const int kb0 = p.splits == 1 ? 0 : (int)((long long)KB * sp / p.splits), kb1 = p.splits == 1 ? KB : (int)((long long)KB * (sp + 1) / p.splits);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(full(stage), phase, abort_flag, p.err, ERR_WAIT_FULL)) { ok = false; break; }
           tc_fence_after();
           const uint64_t soff = (uint64_t)(stage * (QSTAGE_STRIDE >> 4));
           const uint32_t sfa_t = tmem + QTMEM_SF0 + (uint32_t)sfset * QTMEM_SF_STRIDE, sfb_t = sfa_t + 4;
-          q_cp_sf_pair(sfa_t, sdesc0 + soff);
-          q_cp_sf_pair(sfb_t, sdesc0 + soff + (QSFA_BYTES >> 4));
-          q_cp_sf_pair(sfb_t + 4, sdesc0 + soff + ((QSFA_BYTES + 512) >> 4));
+          if (p.sf_warp) {
+            if (!mbar_wait(sffull(sfset), sf_phase, abort_flag, p.err, ERR_WAIT_AUX)) { ok = false; break; }
+            tc_fence_after();
+          } else {
+            q_cp_sf_pair(sfa_t, sdesc0 + soff);
+            q_cp_sf_pair(sfb_t, sdesc0 + soff + (QSFA_BYTES >> 4));
+            q_cp_sf_pair(sfb_t + 4, sdesc0 + soff + ((QSFA_BYTES + 512) >> 4));
+          }
           const uint64_t adesc = adesc0 + soff, bdesc = bdesc0 + soff;
 #pragma unroll
           for (int k = 0; k < QK / 32; ++k)
             q_umma_mxf8_pair(d_tmem, adesc + (uint64_t)(k * a_step), bdesc + (uint64_t)(k * b_step), idesc[k], ((kb - kb0) | k) ? 1u : 0u,
                              sfa_t, sfb_t);
           q_commit_pair(empty(stage));
+          if (p.sf_warp) q_commit_local(sfempty(sfset));        // this set of scale columns is free once these MMAs are done
           if (++stage == QSTAGES) { stage = 0; phase ^= 1u; }
-          if (++sfset == p.sf_sets) sfset = 0;
+          if (++sfset == p.sf_sets) { sfset = 0; sf_phase ^= 1u; }
         }
         if (!ok) break;
         q_commit_pair(tfull(acc));
         if (++acc == p.acc_stages) { acc = 0; acc_phase ^= 1u; }
       }
     }
+  } else if (warp == 2) {
+    // Scale-copy thread (leader only): `tcgen05.cp` of a K block's scales into the next free set of scale columns, as
+    // soon as the block's data has landed, running up to `sf_sets` blocks ahead of the MMA thread.  Issued from the MMA
+    // thread itself the copies sit in its in-order stream between two blocks' MMAs, and the tensor pipe was measured at
+    // 42-55 % active; from a thread of their own they can complete while the previous block's MMAs execute.
+    if (lane == 0 && leader && p.sf_warp) {
+      int stage = 0, sfset = 0;
+      uint32_t phase = 0, sf_phase = 0;
+      bool ok = true;
+      const uint64_t sdesc0 = umma_smem_desc(base + QA_BYTES + QB_BYTES, 0, 128, kLayoutNone);
+      for (int tile = cluster_id; tile < total && ok; tile += n_clusters) {
+        const int sp = p.splits == 1 ? 0 : tile / base_tiles;
+        const int kb0 = p.splits == 1 ? 0 : (int)((long long)KB * sp / p.splits), kb1 = p.splits == 1 ? KB : (int)((long long)KB * (sp + 1) / p.splits);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(full(stage), phase, abort_flag, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+          if (!mbar_wait(sfempty(sfset), sf_phase ^ 1u, abort_flag, p.err, ERR_WAIT_AUX)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t soff = (uint64_t)(stage * (QSTAGE_STRIDE >> 4));
+          const uint32_t sfa_t = tmem + QTMEM_SF0 + (uint32_t)sfset * QTMEM_SF_STRIDE, sfb_t = sfa_t + 4;
+          q_cp_sf_pair(sfa_t, sdesc0 + soff);
+          q_cp_sf_pair(sfb_t, sdesc0 + soff + (QSFA_BYTES >> 4));
+          q_cp_sf_pair(sfb_t + 4, sdesc0 + soff + ((QSFA_BYTES + 512) >> 4));
+          q_commit_local(sffull(sfset));
+          if (++stage == QSTAGES) { stage = 0; phase ^= 1u; }
+          if (++sfset == p.sf_sets) { sfset = 0; sf_phase ^= 1u; }
+        }
+      }
+    }
   } else {
-    // epilogue warps: four per 32-lane TMEM quadrant; the four of a quadrant take every fourth 32-column chunk
-    const int q = warp & 3, sub = (warp - 2) >> 2;
+    // epilogue warps: kEpiWarps / 4 per 32-lane TMEM quadrant (a warp reaches the quadrant warp % 4); the warps of a
+    // quadrant take every (kEpiWarps / 4)-th 32-column chunk
+    const int q = warp & 3, sub = (warp - 3) >> 2;
     const int nchunks = bn >> 5;
     const bool f32out = p.epi == GE_ACC_F32;
     const int variant = (p.Dq != nullptr ? 1 : 0) | (p.Dt != nullptr ? 2 : 0);
@@ -639,6 +688,12 @@ int bones_gemm_mxfp8_pair(const void* Aq, const void* sfa, const void* Bq, const
       if (sets != 1 && sets != 2 && sets != 4) sets = 4;
     }
     p.sf_sets = sets;
+    static int sfw = -1;
+    if (sfw < 0) {
+      const char* e = getenv("BONES_MX_SF_WARP");
+      sfw = e ? (atoi(e) != 0) : 1;
+    }
+    p.sf_warp = sfw;
   }
   p.epi = epi; p.alpha = alpha; p.beta = beta;
   p.D = D; p.ldd = ldd; p.strideD = strideD;
@@ -666,7 +721,7 @@ int bones_gemm_mxfp8_pair(const void* Aq, const void* sfa, const void* Bq, const
   if (rc) return rc;
   rc = tmap_scales_q(&tsb, sfb, sfb_bytes * batch, 4);
   if (rc) return rc;
-  constexpr size_t smem = (size_t)QSTAGES * QSTAGE_STRIDE + 8 * (2 * QSTAGES + 4) + 16 + 1024;
+  constexpr size_t smem = (size_t)QSTAGES * QSTAGE_STRIDE + 8 * kNumBars + 16 + 1024;
   static int epi_warps = 0;
   if (epi_warps == 0) {
     const char* e = getenv("BONES_MX_EPI_WARPS");
@@ -698,9 +753,9 @@ int bones_gemm_mxfp8_pair(const void* Aq, const void* sfa, const void* Bq, const
   const int total = base_tiles * p.splits;
   const int clusters = total < pairs ? total : pairs;
   if (epi_warps == 12)
-    gemm_mxfp8_pair_kernel<12><<<2 * clusters, 64 + 32 * 12, smem, reinterpret_cast<cudaStream_t>(stream)>>>(ta, tb, tsa, tsb, p);
+    gemm_mxfp8_pair_kernel<12><<<2 * clusters, 96 + 32 * 12, smem, reinterpret_cast<cudaStream_t>(stream)>>>(ta, tb, tsa, tsb, p);
   else
-    gemm_mxfp8_pair_kernel<16><<<2 * clusters, 64 + 32 * 16, smem, reinterpret_cast<cudaStream_t>(stream)>>>(ta, tb, tsa, tsb, p);
+    gemm_mxfp8_pair_kernel<16><<<2 * clusters, 96 + 32 * 16, smem, reinterpret_cast<cudaStream_t>(stream)>>>(ta, tb, tsa, tsb, p);
   return (int)cudaGetLastError();
 }
 
