@@ -109,7 +109,7 @@ class MoeMLP(nn.Module):
         b, t, d = xn.shape
         n = b * t
         h = xn.reshape(n, d)
-        logits = F.linear(h.float(), self.router.float())
+        logits = ops.router_logits(h, self.router)
         p, idx, gates = RF.moe_route(logits, self.topk)
         # a sequence of t tokens cannot send more than t of them to one expert: the same routing with a smaller slot
         # buffer for short inputs (a decode step is one token per sequence)

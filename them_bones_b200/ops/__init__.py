@@ -255,6 +255,13 @@ def os1_row_step(table, rows, g, *, lr, eps, cap):
 
 
 # -- MoE ---------------------------------------------------------------------------------------------------------
+def router_logits(h, router):
+    """fp32 router logits ``h @ router^T`` (bf16 inputs, fp32 accumulation)."""
+    if native(h):
+        return _cuda().router_logits(h, router)
+    return F.linear(h.float(), router.float())
+
+
 def moe_slots(idx, b, t, n_exp, cap):
     """Causal per-sequence capacity slotting: ``(slot [n, k], token_of_slot [E*b*cap])``."""
     if native(idx):

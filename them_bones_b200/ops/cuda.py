@@ -581,6 +581,42 @@ def lmhead_logits_os1(x, w, vocab, cap, u, code, gate, a0, glin, beta, thr):
 
 
 # -- MoE -------------------------------------------------------------------------------------------------------------
+class _RouterFn(torch.autograd.Function):
+    """Router logits ``h [T, C] @ R[E, C]^T`` in fp32 on the tcgen05 GEMM.  ``E`` (16) is far below a tensor-core tile, so
+    the router is padded to 128 rows: the padding costs a few GFLOP, while the library route this replaces converted the
+    whole activation to fp32 and ran SIMT fp32 GEMMs (a fifth of an MoE layer's non-GEMM time).  Inputs are the exact
+    bf16 values and the accumulation is fp32, which is what ``F.linear(h.float(), R.float())`` computes (reference: the
+    fp32 router, round2/source/train.py:11023)."""
+
+    @staticmethod
+    def forward(ctx, h, router):
+        e, c = router.shape
+        rp = torch.zeros(128, c, dtype=BF16, device=h.device)
+        rp[:e].copy_(router.detach())
+        out = mm_nt(h, rp, epi=L.EPI_F32, out_dtype=torch.float32)
+        ctx.save_for_backward(h, rp)
+        ctx.e, ctx.rdtype = e, router.dtype
+        COUNTS["moe_router"] += 1
+        return out[:, :e].contiguous()
+
+    @staticmethod
+    def backward(ctx, dl):
+        h, rp = ctx.saved_tensors
+        t, c = h.shape
+        dlp = torch.zeros(t, 128, dtype=BF16, device=h.device)
+        dlp[:, :ctx.e].copy_(dl)
+        dh = mm_nn(dlp, rp)
+        dr32 = torch.zeros(128, c, dtype=torch.float32, device=h.device)
+        mm_tn_acc(dlp, h, dr32)
+        return dh, dr32[:ctx.e].to(ctx.rdtype)
+
+
+def router_logits(h, router):
+    if h.dtype != BF16 or router.shape[0] > 128 or h.shape[1] % 8:
+        return F.linear(h.float(), router.float())
+    return _RouterFn.apply(_c(h), router)
+
+
 def moe_slots(idx, b, t, n_exp, cap):
     """Native capacity slotting: ``idx [b*t, k]`` int64 -> ``(slot [b*t, k], tok [E*b*cap])``."""
     n, k = idx.shape
