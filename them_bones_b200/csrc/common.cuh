@@ -60,6 +60,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// One lane of a fully active warp (`elect.sync`).  The role loops of the tensor-core kernels run on all 32 lanes with
+// warp-uniform operands and issue their `tcgen05` / TMA instructions from the elected lane: those instructions take
+// their operands from uniform registers, and operands computed under a `lane == 0` branch live in per-thread
+// registers and are moved over one by one (measured: about 80 clocks per `tcgen05.mma` issued that way).
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "elect.sync _|p, 0xffffffff;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(pred));
+  return pred != 0;
+}
 // Bounded wait.  `abort_flag` lives in shared memory and is raised by whichever role gives up first.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code) {
   if (mbar_try_wait(bar, parity)) return true;

@@ -70,7 +70,30 @@ struct Mx2Params {
   int splits, atomic, wide;
   int sf_sets;                  // copies of the scale columns in TMEM that the K blocks rotate through (1, 2 or 4)
   int sf_warp;                  // 1: a warp of its own issues the scale copies, ahead of the MMA thread
+  long long* prof;              // BONES_MX_PROF builds only: 32 cycle counters per CTA (null otherwise)
 };
+
+// Cycle accounting of the roles, compiled in only with -DBONES_MX_PROF (a measuring build; the regular library carries
+// none of it).  Each role thread sums the clocks it spends in each of its waits and in issuing, and stores the sums in
+// its CTA's 32 slots of `prof` on the way out:
+//   0 MMA: wait accumulator free   1 MMA: wait stage full   2 MMA: wait scales copied   3 MMA: issue   4 MMA: total
+//   5 producer: wait stage empty   6 producer: issue        7 producer: total
+//   8 scale copy: wait stage full  9 scale copy: wait columns free   10 scale copy: issue
+//   11 epilogue warp 3: wait accumulator full   12 epilogue warp 3: drain   13 epilogue warp 3: total   14 K blocks   15 tiles
+//   16 MMA: the MMA instructions and commits of a block
+#ifdef BONES_MX_PROF
+#define QPROF_DECL(n) long long qp_[n] = {}; long long qp_t_ = clock64(); const long long qp_t0_ = qp_t_
+#define QPROF_ADD(i) do { const long long n_ = clock64(); qp_[i] += n_ - qp_t_; qp_t_ = n_; } while (0)
+#define QPROF_COUNT(i) (++qp_[i])
+#define QPROF_STORE(slot, i) do { if (p.prof) p.prof[(long long)blockIdx.x * 32 + (slot)] = qp_[i]; } while (0)
+#define QPROF_TOTAL(slot) do { if (p.prof) p.prof[(long long)blockIdx.x * 32 + (slot)] = clock64() - qp_t0_; } while (0)
+#else
+#define QPROF_DECL(n)
+#define QPROF_ADD(i)
+#define QPROF_COUNT(i)
+#define QPROF_STORE(slot, i)
+#define QPROF_TOTAL(slot)
+#endif
 
 constexpr int QM = 256, QK = 128, QSTAGES = 6;
 constexpr uint32_t QA_BYTES = 128 * QK;            // 16384
@@ -388,22 +411,28 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
   const uint32_t b_bytes = p.b_major ? QB_BYTES : (uint32_t)half_n * QK;
   const uint32_t cta_bytes = QA_BYTES + b_bytes + QSFA_BYTES + QSFB_BYTES;
 
+  // The three issuing roles run on all 32 lanes of their warp with warp-uniform state and issue from the elected lane
+  // (see `elect_one`).  A lane whose bounded wait ran out turns `dead`: it keeps walking the loops without waiting or
+  // issuing, so the warp stays together for the `elect.sync` of every iteration and reaches the tear-down as one.
   if (warp == 0) {
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int tile = cluster_id; tile < total && ok; tile += n_clusters) {
-        int b, mb, nb;
-        const int sp = p.splits == 1 ? 0 : tile / base_tiles;
-        decode_tile_q(tile - sp * base_tiles, p.tiles_m, p.tiles_n, b, mb, nb);
-        const int kb0 = p.splits == 1 ? 0 : (int)((long long)KB * sp / p.splits), kb1 = p.splits == 1 ? KB : (int)((long long)KB * (sp + 1) / p.splits);
-        const int m0 = mb * QM + (int)rank * 128, n0 = nb * bn + (int)rank * half_n;
-        const int sfa_row = b * p.sfa_rows_per_batch + (2 * mb + (int)rank) * KB * 2;      // 256-byte rows, 2 per chunk
-        const int sfb_row = b * p.sfb_rows_per_batch + nb * KB * 4;                         // 4 per (tile, K block)
-        for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(empty(stage), phase ^ 1u, abort_flag, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
-          const uint32_t sa = base + stage * QSTAGE_STRIDE, sb = sa + QA_BYTES, ssfa = sb + QB_BYTES, ssfb = ssfa + QSFA_BYTES;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool dead = false;
+    QPROF_DECL(2);
+    for (int tile = cluster_id; tile < total; tile += n_clusters) {
+      int b, mb, nb;
+      const int sp = p.splits == 1 ? 0 : tile / base_tiles;
+      decode_tile_q(tile - sp * base_tiles, p.tiles_m, p.tiles_n, b, mb, nb);
+      const int kb0 = p.splits == 1 ? 0 : (int)((long long)KB * sp / p.splits), kb1 = p.splits == 1 ? KB : (int)((long long)KB * (sp + 1) / p.splits);
+      const int m0 = mb * QM + (int)rank * 128, n0 = nb * bn + (int)rank * half_n;
+      const int sfa_row = b * p.sfa_rows_per_batch + (2 * mb + (int)rank) * KB * 2;      // 256-byte rows, 2 per chunk
+      const int sfb_row = b * p.sfb_rows_per_batch + nb * KB * 4;                         // 4 per (tile, K block)
+      for (int kb = kb0; kb < kb1; ++kb) {
+        QPROF_ADD(1);
+        if (!dead) dead = !mbar_wait(empty(stage), phase ^ 1u, abort_flag, p.err, ERR_WAIT_EMPTY);
+        QPROF_ADD(0);
+        const uint32_t sa = base + stage * QSTAGE_STRIDE, sb = sa + QA_BYTES, ssfa = sb + QB_BYTES, ssfb = ssfa + QSFA_BYTES;
+        if (elect_one() && !dead) {
           if (leader) mbar_arrive_expect_tx(full(stage), 2 * cta_bytes);
           if (p.a_major == 0) q_tma_3d(sa, &tma_a, full(stage), kb * QK, m0, b);
           else                q_tma_3d(sa, &tma_a, full(stage), m0, kb * QK, b);
@@ -412,19 +441,21 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
           q_tma_2d(ssfa, &tma_sfa, full(stage), 0, sfa_row + kb * 2);
           q_tma_2d(ssfb, &tma_sfb, full(stage), 0, sfb_row + kb * 4);
           if (!leader) q_mbar_arrive_cluster(full(stage), 0);
-          if (++stage == QSTAGES) { stage = 0; phase ^= 1u; }
         }
+        if (++stage == QSTAGES) { stage = 0; phase ^= 1u; }
       }
     }
+    QPROF_ADD(1);
+    if (lane == 0) { QPROF_STORE(5, 0); QPROF_STORE(6, 1); QPROF_TOTAL(7); }
   } else if (warp == 1) {
-    if (lane == 0 && leader) {
+    if (leader) {
       // K-major: 32 bytes of K per MMA step (descriptor unit 16 bytes); MN-major: 32 K rows of 128 bytes
       const uint32_t a_step = p.a_major ? (32 * 128) >> 4 : 32 >> 4;
       const uint32_t b_step = p.b_major ? (32 * 128) >> 4 : 32 >> 4;
       const uint32_t a_lbo = p.a_major ? 128 * 128 : 0, b_lbo = p.b_major ? 128 * 128 : 0;
       int stage = 0, acc = 0, sfset = 0;
       uint32_t phase = 0, acc_phase = 0, sf_phase = 0;
-      bool ok = true;
+      bool dead = false;
       uint32_t idesc[4];
 #pragma unroll
       for (int k = 0; k < 4; ++k)
@@ -433,67 +464,95 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
       const uint64_t adesc0 = umma_smem_desc(base, a_lbo, 1024, kLayoutSw128);
       const uint64_t bdesc0 = umma_smem_desc(base + QA_BYTES, b_lbo, 1024, kLayoutSw128);
       const uint64_t sdesc0 = umma_smem_desc(base + QA_BYTES + QB_BYTES, 0, 128, kLayoutNone);
-      for (int tile = cluster_id; tile < total && ok; tile += n_clusters) {
-        if (!mbar_wait(tempty(acc), acc_phase ^ 1u, abort_flag, p.err, ERR_WAIT_TMEM_EMPTY)) break;
+      QPROF_DECL(9);
+      for (int tile = cluster_id; tile < total; tile += n_clusters) {
+        QPROF_ADD(3);
+        if (!dead) dead = !mbar_wait(tempty(acc), acc_phase ^ 1u, abort_flag, p.err, ERR_WAIT_TMEM_EMPTY);
+        QPROF_ADD(0);
+        QPROF_COUNT(5);
         tc_fence_after();
         const uint32_t d_tmem = tmem + (uint32_t)(acc * bn);
         const int sp = p.splits == 1 ? 0 : tile / base_tiles;
         const int kb0 = p.splits == 1 ? 0 : (int)((long long)KB * sp / p.splits), kb1 = p.splits == 1 ? KB : (int)((long long)KB * (sp + 1) / p.splits);
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(full(stage), phase, abort_flag, p.err, ERR_WAIT_FULL)) { ok = false; break; }
-          tc_fence_after();
+          QPROF_ADD(3);
+          // With the scale-copy warp, its commit on `sffull` implies the stage's data: that warp waited for `full[s]`
+          // before it copied.  Waiting for `full[s]` here as well cost about 100 clocks per K block.
+          if (!p.sf_warp) {
+            if (!dead) dead = !mbar_wait(full(stage), phase, abort_flag, p.err, ERR_WAIT_FULL);
+          }
+          QPROF_ADD(1);
+          QPROF_COUNT(4);
           const uint64_t soff = (uint64_t)(stage * (QSTAGE_STRIDE >> 4));
           const uint32_t sfa_t = tmem + QTMEM_SF0 + (uint32_t)sfset * QTMEM_SF_STRIDE, sfb_t = sfa_t + 4;
           if (p.sf_warp) {
-            if (!mbar_wait(sffull(sfset), sf_phase, abort_flag, p.err, ERR_WAIT_AUX)) { ok = false; break; }
-            tc_fence_after();
-          } else {
-            q_cp_sf_pair(sfa_t, sdesc0 + soff);
-            q_cp_sf_pair(sfb_t, sdesc0 + soff + (QSFA_BYTES >> 4));
-            q_cp_sf_pair(sfb_t + 4, sdesc0 + soff + ((QSFA_BYTES + 512) >> 4));
+            if (!dead) dead = !mbar_wait(sffull(sfset), sf_phase, abort_flag, p.err, ERR_WAIT_AUX);
           }
+          QPROF_ADD(2);
+          tc_fence_after();
           const uint64_t adesc = adesc0 + soff, bdesc = bdesc0 + soff;
+          QPROF_ADD(3);
+          if (elect_one() && !dead) {
+            if (!p.sf_warp) {
+              q_cp_sf_pair(sfa_t, sdesc0 + soff);
+              q_cp_sf_pair(sfb_t, sdesc0 + soff + (QSFA_BYTES >> 4));
+              q_cp_sf_pair(sfb_t + 4, sdesc0 + soff + ((QSFA_BYTES + 512) >> 4));
+            }
 #pragma unroll
-          for (int k = 0; k < QK / 32; ++k)
-            q_umma_mxf8_pair(d_tmem, adesc + (uint64_t)(k * a_step), bdesc + (uint64_t)(k * b_step), idesc[k], ((kb - kb0) | k) ? 1u : 0u,
-                             sfa_t, sfb_t);
-          q_commit_pair(empty(stage));
-          if (p.sf_warp) q_commit_local(sfempty(sfset));        // this set of scale columns is free once these MMAs are done
+            for (int k = 0; k < QK / 32; ++k)
+              q_umma_mxf8_pair(d_tmem, adesc + (uint64_t)(k * a_step), bdesc + (uint64_t)(k * b_step), idesc[k], ((kb - kb0) | k) ? 1u : 0u,
+                               sfa_t, sfb_t);
+            q_commit_pair(empty(stage));
+            if (p.sf_warp) q_commit_local(sfempty(sfset));        // this set of scale columns is free once these MMAs are done
+            if (kb == kb1 - 1) q_commit_pair(tfull(acc));
+          }
+          QPROF_ADD(6);
           if (++stage == QSTAGES) { stage = 0; phase ^= 1u; }
           if (++sfset == p.sf_sets) { sfset = 0; sf_phase ^= 1u; }
         }
-        if (!ok) break;
-        q_commit_pair(tfull(acc));
         if (++acc == p.acc_stages) { acc = 0; acc_phase ^= 1u; }
+      }
+      QPROF_ADD(3);
+      if (lane == 0) {
+        QPROF_STORE(0, 0); QPROF_STORE(1, 1); QPROF_STORE(2, 2); QPROF_STORE(3, 3); QPROF_TOTAL(4); QPROF_STORE(14, 4); QPROF_STORE(15, 5);
+        QPROF_STORE(16, 6);
       }
     }
   } else if (warp == 2) {
-    // Scale-copy thread (leader only): `tcgen05.cp` of a K block's scales into the next free set of scale columns, as
-    // soon as the block's data has landed, running up to `sf_sets` blocks ahead of the MMA thread.  Issued from the MMA
-    // thread itself the copies sit in its in-order stream between two blocks' MMAs, and the tensor pipe was measured at
-    // 42-55 % active; from a thread of their own they can complete while the previous block's MMAs execute.
-    if (lane == 0 && leader && p.sf_warp) {
+    // Scale-copy warp (leader only): `tcgen05.cp` of a K block's scales into the next free set of scale columns, as
+    // soon as the block's data has landed, running up to `sf_sets` blocks ahead of the MMA warp.  Issued from the MMA
+    // warp itself the copies sit in its in-order stream between two blocks' MMAs, and the tensor pipe was measured at
+    // 42-55 % active; from a warp of their own they can complete while the previous block's MMAs execute.
+    if (leader && p.sf_warp) {
       int stage = 0, sfset = 0;
       uint32_t phase = 0, sf_phase = 0;
-      bool ok = true;
+      bool dead = false;
       const uint64_t sdesc0 = umma_smem_desc(base + QA_BYTES + QB_BYTES, 0, 128, kLayoutNone);
-      for (int tile = cluster_id; tile < total && ok; tile += n_clusters) {
+      QPROF_DECL(3);
+      for (int tile = cluster_id; tile < total; tile += n_clusters) {
         const int sp = p.splits == 1 ? 0 : tile / base_tiles;
         const int kb0 = p.splits == 1 ? 0 : (int)((long long)KB * sp / p.splits), kb1 = p.splits == 1 ? KB : (int)((long long)KB * (sp + 1) / p.splits);
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(full(stage), phase, abort_flag, p.err, ERR_WAIT_FULL)) { ok = false; break; }
-          if (!mbar_wait(sfempty(sfset), sf_phase ^ 1u, abort_flag, p.err, ERR_WAIT_AUX)) { ok = false; break; }
+          QPROF_ADD(2);
+          if (!dead) dead = !mbar_wait(full(stage), phase, abort_flag, p.err, ERR_WAIT_FULL);
+          QPROF_ADD(0);
+          if (!dead) dead = !mbar_wait(sfempty(sfset), sf_phase ^ 1u, abort_flag, p.err, ERR_WAIT_AUX);
+          QPROF_ADD(1);
           tc_fence_after();
           const uint64_t soff = (uint64_t)(stage * (QSTAGE_STRIDE >> 4));
           const uint32_t sfa_t = tmem + QTMEM_SF0 + (uint32_t)sfset * QTMEM_SF_STRIDE, sfb_t = sfa_t + 4;
-          q_cp_sf_pair(sfa_t, sdesc0 + soff);
-          q_cp_sf_pair(sfb_t, sdesc0 + soff + (QSFA_BYTES >> 4));
-          q_cp_sf_pair(sfb_t + 4, sdesc0 + soff + ((QSFA_BYTES + 512) >> 4));
-          q_commit_local(sffull(sfset));
+          if (elect_one() && !dead) {
+            q_cp_sf_pair(sfa_t, sdesc0 + soff);
+            q_cp_sf_pair(sfb_t, sdesc0 + soff + (QSFA_BYTES >> 4));
+            q_cp_sf_pair(sfb_t + 4, sdesc0 + soff + ((QSFA_BYTES + 512) >> 4));
+            q_commit_local(sffull(sfset));
+          }
           if (++stage == QSTAGES) { stage = 0; phase ^= 1u; }
           if (++sfset == p.sf_sets) { sfset = 0; sf_phase ^= 1u; }
         }
       }
+      QPROF_ADD(2);
+      if (lane == 0) { QPROF_STORE(8, 0); QPROF_STORE(9, 1); QPROF_STORE(10, 2); }
     }
   } else {
     // epilogue warps: kEpiWarps / 4 per 32-lane TMEM quadrant (a warp reaches the quadrant warp % 4); the warps of a
@@ -504,11 +563,14 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
     const int variant = (p.Dq != nullptr ? 1 : 0) | (p.Dt != nullptr ? 2 : 0);
     int acc = 0;
     uint32_t acc_phase = 0;
+    QPROF_DECL(2);
     for (int tile = cluster_id; tile < total; tile += n_clusters) {
       int b, mb, nb;
       decode_tile_q(tile % base_tiles, p.tiles_m, p.tiles_n, b, mb, nb);
       const int row0 = mb * QM + (int)rank * 128 + q * 32;
+      QPROF_ADD(1);
       const bool got = mbar_wait(tfull(acc), acc_phase, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
+      QPROF_ADD(0);
       if (!__all_sync(0xffffffffu, got)) break;
       tc_fence_after();
       const uint32_t taddr0 = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * bn);
@@ -550,6 +612,8 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
       if (lane == 0) q_mbar_arrive_cluster(tempty(acc), 0);
       if (++acc == p.acc_stages) { acc = 0; acc_phase ^= 1u; }
     }
+    QPROF_ADD(1);
+    if (warp == 3 && lane == 0) { QPROF_STORE(11, 0); QPROF_STORE(12, 1); QPROF_TOTAL(13); }
   }
 
   // tear-down: both CTAs of the pair always arrive here (every wait above is bounded)
@@ -636,6 +700,12 @@ static int tmap_scales_q(CUtensorMap* out, const void* ptr, long long bytes, int
 
 }  // namespace bones
 
+#ifdef BONES_MX_PROF
+static long long* g_mx_prof = nullptr;
+// measuring build: device buffer of 32 counters per CTA that the next launches fill (null switches it off)
+extern "C" void bones_mx2_set_prof(void* buf) { g_mx_prof = (long long*)buf; }
+#endif
+
 extern "C" {
 using namespace bones;
 
@@ -703,6 +773,11 @@ int bones_gemm_mxfp8_pair(const void* Aq, const void* sfa, const void* Bq, const
   p.dsf_batch = bones_mx2_sf_bytes(M, N, p.dq_group);
   p.dtsf_batch = bones_mx2_sf_bytes(N, M, p.dt_group);
   p.err = error_word();
+#ifdef BONES_MX_PROF
+  p.prof = g_mx_prof;
+#else
+  p.prof = nullptr;
+#endif
   const long long wal = f32out ? 8 : 16;
   p.wide = (D && (ldd % wal == 0) && (strideD % wal == 0) && (!R || (ldr % wal == 0 && strideR % wal == 0)) && (((uintptr_t)D & 31) == 0) &&
             (!R || ((uintptr_t)R & 31) == 0)) ? 1 : 0;

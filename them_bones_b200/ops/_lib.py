@@ -13,8 +13,9 @@ import torch
 
 _LIB = None
 DEBUG_BOUNDS = os.environ.get("BONES_DEBUG_BOUNDS", "0") not in ("0", "", "false")
-_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib",
-                     "libbones_b200_dbg.so" if DEBUG_BOUNDS else "libbones_b200.so")
+# BONES_LIB: path of another build of the library (for instance one compiled with a measuring define)
+_PATH = os.environ.get("BONES_LIB") or os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib",
+                                                    "libbones_b200_dbg.so" if DEBUG_BOUNDS else "libbones_b200.so")
 
 
 def lib_path() -> str:
