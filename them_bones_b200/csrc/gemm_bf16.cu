@@ -115,20 +115,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
   const int total = base_tiles * p.splits;
   const int KB = (p.K + BK - 1) / BK;
 
+  // The producer and MMA roles run on all 32 lanes of their warp with warp-uniform state and issue from the elected lane
+  // (see `elect_one` in common.cuh).  A lane whose bounded wait ran out turns `dead`: it walks the rest of the loops
+  // without waiting or issuing, so the warp stays together for every `elect.sync`.
   if (warp == 0) {
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
-        int b, mb, nb;
-        const int sp = tile / base_tiles;
-        decode_tile(tile - sp * base_tiles, p.tiles_m, p.tiles_n, b, mb, nb);
-        const int kb0 = (int)((long long)KB * sp / p.splits), kb1 = (int)((long long)KB * (sp + 1) / p.splits);
-        for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(empty(stage), phase ^ 1u, abort_flag, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+    int stage = 0;
+    uint32_t phase = 0;
+    bool dead = false;
+    for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
+      int b, mb, nb;
+      const int sp = p.splits == 1 ? 0 : tile / base_tiles;
+      decode_tile(tile - sp * base_tiles, p.tiles_m, p.tiles_n, b, mb, nb);
+      const int kb0 = p.splits == 1 ? 0 : (int)((long long)KB * sp / p.splits), kb1 = p.splits == 1 ? KB : (int)((long long)KB * (sp + 1) / p.splits);
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!dead) dead = !mbar_wait(empty(stage), phase ^ 1u, abort_flag, p.err, ERR_WAIT_EMPTY);
+        const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_BYTES;
+        if (elect_one() && !dead) {
           mbar_arrive_expect_tx(full(stage), STAGE_BYTES);
-          const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_BYTES;
           if (p.a_major == 0) {
             tma_load_3d(sa, &tma_a, full(stage), kb * BK, mb * BM, b);
           } else {
@@ -141,42 +144,43 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constan
 #pragma unroll
             for (int i = 0; i < BN / 64; ++i) tma_load_3d(sb + i * (BK * 128), &tma_b, full(stage), nb * BN + i * 64, kb * BK, b);
           }
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc = umma_idesc_f16(BM, BN, 1, (uint32_t)p.a_major, (uint32_t)p.b_major);
-      const uint32_t a_lbo = p.a_major ? BK * 128 : 0, b_lbo = p.b_major ? BK * 128 : 0;
-      const uint32_t a_step = p.a_major ? (16 * 128) >> 4 : 32 >> 4;   // descriptor address units of 16 bytes per UMMA_K
-      const uint32_t b_step = p.b_major ? (16 * 128) >> 4 : 32 >> 4;
-      int stage = 0, acc = 0;
-      uint32_t phase = 0, acc_phase = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
-        if (!mbar_wait(tempty(acc), acc_phase ^ 1u, abort_flag, p.err, ERR_WAIT_TMEM_EMPTY)) break;
+    const uint32_t idesc = umma_idesc_f16(BM, BN, 1, (uint32_t)p.a_major, (uint32_t)p.b_major);
+    const uint32_t a_lbo = p.a_major ? BK * 128 : 0, b_lbo = p.b_major ? BK * 128 : 0;
+    const uint32_t a_step = p.a_major ? (16 * 128) >> 4 : 32 >> 4;   // descriptor address units of 16 bytes per UMMA_K
+    const uint32_t b_step = p.b_major ? (16 * 128) >> 4 : 32 >> 4;
+    // descriptors of stage 0; a stage adds STAGE_BYTES >> 4 to the address field
+    const uint64_t adesc0 = umma_smem_desc(base, a_lbo, 1024, kLayoutSw128);
+    const uint64_t bdesc0 = umma_smem_desc(base + A_BYTES, b_lbo, 1024, kLayoutSw128);
+    int stage = 0, acc = 0;
+    uint32_t phase = 0, acc_phase = 0;
+    bool dead = false;
+    for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
+      if (!dead) dead = !mbar_wait(tempty(acc), acc_phase ^ 1u, abort_flag, p.err, ERR_WAIT_TMEM_EMPTY);
+      tc_fence_after();
+      const uint32_t d_tmem = tmem + acc * BN;
+      const int sp = p.splits == 1 ? 0 : tile / base_tiles;
+      const int kb0 = p.splits == 1 ? 0 : (int)((long long)KB * sp / p.splits), kb1 = p.splits == 1 ? KB : (int)((long long)KB * (sp + 1) / p.splits);
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!dead) dead = !mbar_wait(full(stage), phase, abort_flag, p.err, ERR_WAIT_FULL);
         tc_fence_after();
-        const uint32_t d_tmem = tmem + acc * BN;
-        const int sp = tile / base_tiles;
-        const int kb0 = (int)((long long)KB * sp / p.splits), kb1 = (int)((long long)KB * (sp + 1) / p.splits);
-        for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(full(stage), phase, abort_flag, p.err, ERR_WAIT_FULL)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_BYTES;
-          const uint64_t adesc = umma_smem_desc(sa, a_lbo, 1024, kLayoutSw128);
-          const uint64_t bdesc = umma_smem_desc(sb, b_lbo, 1024, kLayoutSw128);
+        const uint64_t soff = (uint64_t)(stage * (STAGE_BYTES >> 4));
+        const uint64_t adesc = adesc0 + soff, bdesc = bdesc0 + soff;
+        if (elect_one() && !dead) {
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k)
             umma_f16(d_tmem, adesc + (uint64_t)(k * a_step), bdesc + (uint64_t)(k * b_step), idesc, ((kb - kb0) | k) ? 1u : 0u);
           tc_commit(empty(stage));
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          if (kb == kb1 - 1) tc_commit(tfull(acc));
         }
-        if (!ok) break;
-        tc_commit(tfull(acc));
-        acc ^= 1;
-        if (acc == 0) acc_phase ^= 1u;
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
       }
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
     }
   } else {
     const int q = warp & 3;
@@ -258,6 +262,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams 
     }
   }
   if (p.splits > 1 && p.epi != EPI_ACC_F32) p.splits = 1;
+  if (p.splits > KB) p.splits = KB;          // every split owns at least one K block (its last block signals the epilogue)
   const int total = base_tiles * p.splits;
   const int grid = total < sms ? total : sms;
   gemm_bf16_kernel<BN, STAGES><<<grid, 192, smem, stream>>>(ta, tb, p);

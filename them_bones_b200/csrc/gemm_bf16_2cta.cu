@@ -156,20 +156,23 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
   const int KB = (p.K + PK - 1) / PK;
   const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
 
+  // The producer and MMA roles run on all 32 lanes of their warp with warp-uniform state and issue from the elected lane
+  // (see `elect_one` in common.cuh).  A lane whose bounded wait ran out turns `dead`: it walks the rest of the loops
+  // without waiting or issuing, so the warp stays together for every `elect.sync` and reaches the tear-down as one.
   if (warp == 0) {
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int tile = cluster_id; tile < total && ok; tile += n_clusters) {
-        int b, mb, nb;
-        const int sp = tile / base_tiles;
-        decode_tile2(tile - sp * base_tiles, p.tiles_m, p.tiles_n, b, mb, nb);
-        const int kb0 = (int)((long long)KB * sp / p.splits), kb1 = (int)((long long)KB * (sp + 1) / p.splits);
-        const int m0 = mb * PM + (int)rank * 128, n0 = nb * PN + (int)rank * 128;
-        for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(empty(stage), phase ^ 1u, abort_flag, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
-          const uint32_t sa = base + stage * PSTAGE_BYTES, sb = sa + PA_BYTES;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool dead = false;
+    for (int tile = cluster_id; tile < total; tile += n_clusters) {
+      int b, mb, nb;
+      const int sp = p.splits == 1 ? 0 : tile / base_tiles;
+      decode_tile2(tile - sp * base_tiles, p.tiles_m, p.tiles_n, b, mb, nb);
+      const int kb0 = p.splits == 1 ? 0 : (int)((long long)KB * sp / p.splits), kb1 = p.splits == 1 ? KB : (int)((long long)KB * (sp + 1) / p.splits);
+      const int m0 = mb * PM + (int)rank * 128, n0 = nb * PN + (int)rank * 128;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!dead) dead = !mbar_wait(empty(stage), phase ^ 1u, abort_flag, p.err, ERR_WAIT_EMPTY);
+        const uint32_t sa = base + stage * PSTAGE_BYTES, sb = sa + PA_BYTES;
+        if (elect_one() && !dead) {
           if (leader) mbar_arrive_expect_tx(full(stage), 2 * PSTAGE_BYTES);
           if (p.a_major == 0) {
             tma_load_3d_pair(sa, &tma_a, full(stage), kb * PK, m0, b);
@@ -184,39 +187,42 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_co
             tma_load_3d_pair(sb + PK * 128, &tma_b, full(stage), n0 + 64, kb * PK, b);
           }
           if (!leader) mbar_arrive_cluster(full(stage), 0);
-          if (++stage == PSTAGES) { stage = 0; phase ^= 1u; }
         }
+        if (++stage == PSTAGES) { stage = 0; phase ^= 1u; }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && leader) {
+    if (leader) {
       const uint32_t idesc = umma_idesc_f16(PM, PN, 1, (uint32_t)p.a_major, (uint32_t)p.b_major);
       const uint32_t a_lbo = p.a_major ? PK * 128 : 0, b_lbo = p.b_major ? PK * 128 : 0;
       const uint32_t a_step = p.a_major ? (16 * 128) >> 4 : 32 >> 4;
       const uint32_t b_step = p.b_major ? (16 * 128) >> 4 : 32 >> 4;
+      // descriptors of stage 0; a stage adds PSTAGE_BYTES >> 4 to the address field
+      const uint64_t adesc0 = umma_smem_desc(base, a_lbo, 1024, kLayoutSw128);
+      const uint64_t bdesc0 = umma_smem_desc(base + PA_BYTES, b_lbo, 1024, kLayoutSw128);
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
-      bool ok = true;
-      for (int tile = cluster_id; tile < total && ok; tile += n_clusters) {
-        if (!mbar_wait(tempty(acc), acc_phase ^ 1u, abort_flag, p.err, ERR_WAIT_TMEM_EMPTY)) break;
+      bool dead = false;
+      for (int tile = cluster_id; tile < total; tile += n_clusters) {
+        if (!dead) dead = !mbar_wait(tempty(acc), acc_phase ^ 1u, abort_flag, p.err, ERR_WAIT_TMEM_EMPTY);
         tc_fence_after();
         const uint32_t d_tmem = tmem + acc * PN;
-        const int sp = tile / base_tiles;
-        const int kb0 = (int)((long long)KB * sp / p.splits), kb1 = (int)((long long)KB * (sp + 1) / p.splits);
+        const int sp = p.splits == 1 ? 0 : tile / base_tiles;
+        const int kb0 = p.splits == 1 ? 0 : (int)((long long)KB * sp / p.splits), kb1 = p.splits == 1 ? KB : (int)((long long)KB * (sp + 1) / p.splits);
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(full(stage), phase, abort_flag, p.err, ERR_WAIT_FULL)) { ok = false; break; }
+          if (!dead) dead = !mbar_wait(full(stage), phase, abort_flag, p.err, ERR_WAIT_FULL);
           tc_fence_after();
-          const uint32_t sa = base + stage * PSTAGE_BYTES, sb = sa + PA_BYTES;
-          const uint64_t adesc = umma_smem_desc(sa, a_lbo, 1024, kLayoutSw128);
-          const uint64_t bdesc = umma_smem_desc(sb, b_lbo, 1024, kLayoutSw128);
+          const uint64_t soff = (uint64_t)(stage * (PSTAGE_BYTES >> 4));
+          const uint64_t adesc = adesc0 + soff, bdesc = bdesc0 + soff;
+          if (elect_one() && !dead) {
 #pragma unroll
-          for (int k = 0; k < PK / 16; ++k)
-            umma_f16_pair(d_tmem, adesc + (uint64_t)(k * a_step), bdesc + (uint64_t)(k * b_step), idesc, ((kb - kb0) | k) ? 1u : 0u);
-          tc_commit_pair(empty(stage));
+            for (int k = 0; k < PK / 16; ++k)
+              umma_f16_pair(d_tmem, adesc + (uint64_t)(k * a_step), bdesc + (uint64_t)(k * b_step), idesc, ((kb - kb0) | k) ? 1u : 0u);
+            tc_commit_pair(empty(stage));
+            if (kb == kb1 - 1) tc_commit_pair(tfull(acc));
+          }
           if (++stage == PSTAGES) { stage = 0; phase ^= 1u; }
         }
-        if (!ok) break;
-        tc_commit_pair(tfull(acc));
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
@@ -364,6 +370,7 @@ int bones_gemm_bf16_pair(const void* A, const void* B, void* D, const void* R, i
     }
   }
   if (p.splits > 1 && epi != E2_ACC_F32) p.splits = 1;
+  if (p.splits > KB) p.splits = KB;          // every split owns at least one K block (its last block signals the epilogue)
   const int total = base_tiles * p.splits;
   const int clusters = total < pairs ? total : pairs;
   gemm_bf16_pair_kernel<<<2 * clusters, 320, smem, reinterpret_cast<cudaStream_t>(stream)>>>(ta, tb, p);

@@ -38,6 +38,7 @@
 // projections (nki_attn_tt8g.py:616-623) and the fp8 weight-gradient GEMM (nki_dw8.py:239); per-block scales replace
 // their per-tensor power-of-two scales.
 #include <cstdlib>
+#include <cstring>
 
 #include "common.cuh"
 #include "gemm_epilogue.cuh"
@@ -70,6 +71,7 @@ struct Mx2Params {
   int splits, atomic, wide;
   int sf_sets;                  // copies of the scale columns in TMEM that the K blocks rotate through (1, 2 or 4)
   int sf_warp;                  // 1: a warp of its own issues the scale copies, ahead of the MMA thread
+  int staged;                   // 1: bf16 / E4M3 outputs leave through shared memory and TMA stores
   long long* prof;              // BONES_MX_PROF builds only: 32 cycle counters per CTA (null otherwise)
 };
 
@@ -95,7 +97,8 @@ struct Mx2Params {
 #define QPROF_TOTAL(slot)
 #endif
 
-constexpr int QM = 256, QK = 128, QSTAGES = 6;
+constexpr int QM = 256, QK = 128, QSTAGES = 6;          // stages: 6, or 5 with the epilogue's staging tiles behind them
+constexpr int QSTAGES_STAGED = 5;
 constexpr uint32_t QA_BYTES = 128 * QK;            // 16384
 constexpr uint32_t QB_BYTES = 128 * QK;            // up to 128 rows (K-major: bn / 2 rows; MN-major: 128 K rows)
 constexpr uint32_t QSFA_BYTES = 512, QSFB_BYTES = 1024;
@@ -105,6 +108,17 @@ constexpr uint32_t QSTAGE_STRIDE = 34816;          // 34 KB >= 16384 + 16384 + 5
 // the tensor pipe idles for the copies' latency every 128 of K.  Rotating sets removes the first wait.
 constexpr uint32_t QTMEM_SF0 = 464, QTMEM_SF_STRIDE = 12;
 constexpr int kGroupMq = 8;
+constexpr int kSfSetsMax = 4;
+constexpr int kNumBars = 2 * QSTAGES + 4 + 2 * kSfSetsMax;
+// Epilogue staging behind the stages: per epilogue warp one 32 x 32 bf16 tile (64-byte swizzle), two 32 x 32 E4M3 tiles
+// (32-byte swizzle) and, behind all of them, 32 floats of scratch per warp.
+constexpr int kEpiWarpsQ = 12;
+constexpr uint32_t QSTG_D = 0, QSTG_Q = 2048, QSTG_T = 3072, QSTG_BYTES = 4096, QSTG_SCRATCH = 128;
+constexpr uint32_t QSTG_BASE = QSTAGES_STAGED * QSTAGE_STRIDE;
+constexpr uint32_t QSCRATCH_BASE = QSTG_BASE + kEpiWarpsQ * QSTG_BYTES;
+constexpr uint32_t QBARS_BASE = QSCRATCH_BASE + kEpiWarpsQ * QSTG_SCRATCH;
+static_assert(QBARS_BASE >= QSTAGES * QSTAGE_STRIDE, "the barriers sit behind both layouts");
+constexpr size_t QSMEM_BYTES = (size_t)QBARS_BASE + 8 * kNumBars + 16 + 1024;
 
 __device__ __forceinline__ void decode_tile_q(int tile, int tiles_m, int tiles_n, int& b, int& mb, int& nb) {
   const int per_batch = tiles_m * tiles_n;
@@ -255,9 +269,6 @@ __device__ __forceinline__ void q_emit_col(const float (&v)[32], int lane, uint8
   if (sf_ok) *sf_dst = (uint8_t)biased;
 }
 
-// Epilogue warps per CTA: a multiple of four (one set per 32-lane TMEM quadrant).  16 warps leave 96 registers per
-// thread, 12 leave 128 and measured faster with every epilogue (default; BONES_MX_EPI_WARPS=16 selects the other build).
-
 // scale-chunk offset with 32-bit arithmetic; `shift` >= 0 when the tile height is a power of two
 __device__ __forceinline__ uint32_t q_sf_offset32(uint32_t r, uint32_t k, uint32_t kblocks, int group, int shift) {
   const uint32_t g = shift >= 0 ? (r >> shift) : r / (uint32_t)group;
@@ -267,29 +278,83 @@ __device__ __forceinline__ uint32_t q_sf_offset32(uint32_t r, uint32_t k, uint32
 }
 __device__ __forceinline__ int q_log2_or_neg(int v) { return (v & (v - 1)) == 0 ? 31 - __clz(v) : -1; }
 
-// One epilogue warp's share of a tile with quantised outputs, specialised at compile time on the epilogue and on which
-// copies are written (every branch on them would otherwise sit inside the fully unrolled 32-value loops).
-template <int EPI, bool WQ, bool WT, int kEpiWarps>
-__device__ __forceinline__ void q_quant_tile(const Mx2Params& p, uint32_t taddr0, int b, int row0, int ncol0, int lane, int sub, int nchunks) {
+// ---------------------------------------------------------------------------------------------------------------
+// Staged epilogue.  A thread of an epilogue warp holds one row of the accumulator (TMEM lane = row), so a 16-byte store
+// per thread touches 32 different rows: 32 cache lines per instruction, and with the bf16 copy, the two quantised copies
+// and an auxiliary operand per 32 x 32 chunk the load/store path, not the arithmetic, took 17 000 clocks per 128 x 224
+// tile against 4 480 clocks of MMAs.  Here every chunk goes through the warp's own staging tiles in shared memory
+// (swizzled so that the row-per-thread accesses are conflict free) and leaves with one TMA store per copy; the auxiliary
+// operand comes in with coalesced loads (four threads per row) and is turned round through the same tile.  The block
+// maxima along M come from the staged bf16 tile read column-wise (16 conflict-free loads per thread and packed bf16 max)
+// instead of 32 `redux.sync` and a selection tree.
+// ---------------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void q_tma_store_3d(const CUtensorMap* m, uint32_t src, int c0, int c1, int c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src),
+               "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void q_bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void q_bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void q_sts128(uint32_t a, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+__device__ __forceinline__ uint4 q_lds128(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t q_lds32(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(a) : "memory");
+  return v;
+}
+__device__ __forceinline__ void q_sts32(uint32_t a, uint32_t v) { asm volatile("st.shared.b32 [%0], %1;" ::"r"(a), "r"(v) : "memory"); }
+__device__ __forceinline__ uint32_t q_max_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("max.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+// One epilogue warp's chunks of a tile: `stg` / `scratch` are the warp's staging tiles and scratch floats.
+template <int EPI, bool WQ, bool WT>
+__device__ __forceinline__ void q_staged_tile(const Mx2Params& p, const CUtensorMap* tm_d, const CUtensorMap* tm_q, const CUtensorMap* tm_t,
+                                              uint32_t taddr0, uint32_t stg, uint32_t scratch, int b, int row0, int ncol0, int lane, int sub,
+                                              int nchunks) {       // `sub`: the warp's first chunk of this tile (rotates from tile to tile)
+  constexpr bool kNeedR = EPI == GE_BF16_RES || EPI == GE_MUL_2SQRT;
+  if (row0 >= p.M) return;                                  // warp-uniform: the whole warp lies beyond M
   const int row = row0 + lane;
   const bool row_ok = row < p.M;
   const bool ragged = row0 + 32 > p.M;                      // warp-uniform: some of the warp's rows lie beyond M
-  __nv_bfloat16* Drow = p.D ? reinterpret_cast<__nv_bfloat16*>(p.D) + (long long)b * p.strideD + (long long)row * p.ldd : nullptr;
-  const __nv_bfloat16* Rrow = reinterpret_cast<const __nv_bfloat16*>(p.R) + (long long)b * p.strideR + (long long)row * p.ldr;
-  const long long qrow = ((long long)b * p.M + row) * p.N;
+  const uint32_t sw64 = (uint32_t)((lane >> 1) & 3), sw32 = (uint32_t)((lane >> 2) & 1);
+  const uint32_t d_row = stg + QSTG_D + (uint32_t)lane * 64u;
+  const uint32_t q_row = stg + QSTG_Q + (uint32_t)lane * 32u;
+  const uint32_t t_row = stg + QSTG_T + (uint32_t)lane * 32u;
+  const int r_sub = lane >> 2, r_piece = lane & 3;          // coalesced loads of the auxiliary operand: four threads per row
+  const __nv_bfloat16* Rb = reinterpret_cast<const __nv_bfloat16*>(p.R) + (long long)b * p.strideR;
   const uint32_t kblocks_n = (uint32_t)((p.N + 127) >> 7), kblocks_m = (uint32_t)((p.M + 127) >> 7);
   const int qshift = q_log2_or_neg(p.dq_group), tshift = q_log2_or_neg(p.dt_group);
   uint8_t* sfq = WQ ? p.Dsf + (size_t)b * p.dsf_batch + q_sf_offset32((uint32_t)row, 0u, kblocks_n, p.dq_group, qshift) : nullptr;
   const uint32_t sfq_step = (((uint32_t)p.dq_group + 127u) >> 7) * 512u;          // per 128 columns
   uint8_t* sft = WT ? p.Dtsf + (size_t)b * p.dtsf_batch : nullptr;
 #pragma unroll 1
-  for (int c = sub; c < nchunks; c += kEpiWarps / 4) {
+  for (int c = sub; c < nchunks; c += kEpiWarpsQ / 4) {
+    const int col0 = ncol0 + c * 32;
+    if (col0 >= p.N) break;                        // warp-uniform: the ragged last tile's columns beyond N
+    uint4 rin[4];
+    if (kNeedR) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int rr = row0 + i * 8 + r_sub, cc = col0 + r_piece * 8;
+        rin[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (rr < p.M && cc < p.N) rin[i] = *reinterpret_cast<const uint4*>(Rb + (long long)rr * p.ldr + cc);
+      }
+    }
     uint32_t r[32];
     __syncwarp();
     BONES_TMEM_LD32(taddr0 + (uint32_t)(c * 32), r);
     tmem_ld_wait();
-    const int col0 = ncol0 + c * 32;
-    if (col0 >= p.N) continue;                     // warp-uniform: the ragged last tile's columns beyond N
+    if (elect_one()) q_bulk_wait_read();           // the stores of the warp's previous chunk have read the staging tiles
+    __syncwarp();
     float v[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
@@ -301,25 +366,30 @@ __device__ __forceinline__ void q_quant_tile(const Mx2Params& p, uint32_t taddr0
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
     }
-    if (EPI == GE_BF16_RES || EPI == GE_MUL_2SQRT) {
-      if (row_ok) {
+    if (kNeedR) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint4 u = *reinterpret_cast<const uint4*>(Rrow + col0 + j * 8);
-          const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t rr = (uint32_t)(i * 8 + r_sub);
+        q_sts128(stg + QSTG_D + rr * 64u + ((((uint32_t)r_piece) ^ ((rr >> 1) & 3u)) << 4), rin[i].x, rin[i].y, rin[i].z, rin[i].w);
+      }
+      __syncwarp();
 #pragma unroll
-          for (int t = 0; t < 4; ++t) {
-            const float2 f = unpack_bf16(w[t]);
-            if (EPI == GE_BF16_RES) {
-              v[j * 8 + 2 * t] = fmaf(p.beta, f.x, v[j * 8 + 2 * t]);
-              v[j * 8 + 2 * t + 1] = fmaf(p.beta, f.y, v[j * 8 + 2 * t + 1]);
-            } else {
-              v[j * 8 + 2 * t] *= 2.0f * sqrt_fast(f.x);
-              v[j * 8 + 2 * t + 1] *= 2.0f * sqrt_fast(f.y);
-            }
+      for (int j = 0; j < 4; ++j) {
+        const uint4 u = q_lds128(d_row + ((((uint32_t)j) ^ sw64) << 4));
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float2 f = unpack_bf16(w[t]);
+          if (EPI == GE_BF16_RES) {
+            v[j * 8 + 2 * t] = fmaf(p.beta, f.x, v[j * 8 + 2 * t]);
+            v[j * 8 + 2 * t + 1] = fmaf(p.beta, f.y, v[j * 8 + 2 * t + 1]);
+          } else {
+            v[j * 8 + 2 * t] *= 2.0f * sqrt_fast(f.x);
+            v[j * 8 + 2 * t + 1] *= 2.0f * sqrt_fast(f.y);
           }
         }
       }
+      __syncwarp();
     } else if (EPI == GE_RELU2) {
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
@@ -327,37 +397,78 @@ __device__ __forceinline__ void q_quant_tile(const Mx2Params& p, uint32_t taddr0
         v[j] = t * t;
       }
     }
-    // the bf16 copy and the two MXFP8 copies are all rounded from the fp32 values (no bf16 round trip in between)
-    if (Drow != nullptr && row_ok) {
+    // bf16 tile: the copy that leaves as D and the source of the column maxima
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        uint4 u;
-        u.x = pack_bf16(v[j * 8 + 0], v[j * 8 + 1]);
-        u.y = pack_bf16(v[j * 8 + 2], v[j * 8 + 3]);
-        u.z = pack_bf16(v[j * 8 + 4], v[j * 8 + 5]);
-        u.w = pack_bf16(v[j * 8 + 6], v[j * 8 + 7]);
-        *reinterpret_cast<uint4*>(Drow + col0 + j * 8) = u;
-      }
+    for (int j = 0; j < 4; ++j)
+      q_sts128(d_row + ((((uint32_t)j) ^ sw64) << 4), pack_bf16(v[j * 8 + 0], v[j * 8 + 1]), pack_bf16(v[j * 8 + 2], v[j * 8 + 3]),
+               pack_bf16(v[j * 8 + 4], v[j * 8 + 5]), pack_bf16(v[j * 8 + 6], v[j * 8 + 7]));
+    if (WQ) {                                      // along N: the thread's 32 values are one block
+      float amax = 0.f;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(v[j]));
+      int biased;
+      const float inv = q_scale_pow2(amax, biased);
+      uint32_t o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = q_pack_e4m3x4(v[4 * j] * inv, v[4 * j + 1] * inv, v[4 * j + 2] * inv, v[4 * j + 3] * inv);
+      q_sts128(q_row + ((0u ^ sw32) << 4), o[0], o[1], o[2], o[3]);
+      q_sts128(q_row + ((1u ^ sw32) << 4), o[4], o[5], o[6], o[7]);
+      if (row_ok) sfq[(uint32_t)(col0 >> 7) * sfq_step + (uint32_t)((col0 & 127) >> 5)] = (uint8_t)biased;
     }
-    if (WQ) q_emit_row(v, p.Dq + qrow + col0, sfq + (uint32_t)(col0 >> 7) * sfq_step + (uint32_t)((col0 & 127) >> 5), row_ok);
-    if (WT)      // rows beyond M contribute zeros to their column blocks
-      q_emit_col(v, lane, p.Dt + qrow + col0, sft + q_sf_offset32((uint32_t)(col0 + lane), (uint32_t)row0, kblocks_m, p.dt_group, tshift), row_ok,
-                 row0 < p.M);
+    if (WT) {
+      __syncwarp();                                // the bf16 tile is complete
+      // along M: a block is one column over the warp's 32 rows (rows beyond M were zeroed).  Thread j reads the word of
+      // columns 2w, 2w + 1 (w = j % 16) in the 16 rows of parity j / 16.
+      const uint32_t w = (uint32_t)(lane & 15), par = (uint32_t)(lane >> 4);
+      uint32_t m2 = 0u;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const uint32_t rr = 2u * (uint32_t)i + par;
+        const uint32_t x = q_lds32(stg + QSTG_D + rr * 64u + (((w >> 2) ^ ((uint32_t)i & 3u)) << 4) + (w & 3u) * 4u);
+        m2 = q_max_bf16x2(m2, x & 0x7fff7fffu);
+      }
+      m2 = q_max_bf16x2(m2, __shfl_xor_sync(0xffffffffu, m2, 16));
+      const uint32_t mine2 = __shfl_sync(0xffffffffu, m2, lane >> 1);
+      const uint32_t mine = (lane & 1) ? (mine2 & 0xffff0000u) : (mine2 << 16);
+      int biased;
+      const float my_inv = q_scale_pow2(__uint_as_float(mine), biased);
+      sft[q_sf_offset32((uint32_t)(col0 + lane), (uint32_t)row0, kblocks_m, p.dt_group, tshift)] = (uint8_t)biased;
+      q_sts32(scratch + (uint32_t)lane * 4u, __float_as_uint(my_inv));
+      __syncwarp();
+      uint32_t o[8];
+#pragma unroll
+      for (int j4 = 0; j4 < 8; ++j4) {
+        const uint4 sc = q_lds128(scratch + (uint32_t)j4 * 16u);
+        o[j4] = q_pack_e4m3x4(v[j4 * 4] * __uint_as_float(sc.x), v[j4 * 4 + 1] * __uint_as_float(sc.y), v[j4 * 4 + 2] * __uint_as_float(sc.z),
+                              v[j4 * 4 + 3] * __uint_as_float(sc.w));
+      }
+      q_sts128(t_row + ((0u ^ sw32) << 4), o[0], o[1], o[2], o[3]);
+      q_sts128(t_row + ((1u ^ sw32) << 4), o[4], o[5], o[6], o[7]);
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (elect_one()) {
+      if (p.D != nullptr) q_tma_store_3d(tm_d, stg + QSTG_D, col0, row0, b);
+      if (WQ) q_tma_store_3d(tm_q, stg + QSTG_Q, col0, row0, b);
+      if (WT) q_tma_store_3d(tm_t, stg + QSTG_T, col0, row0, b);
+      q_bulk_commit();
+    }
   }
 }
 
-constexpr int kSfSetsMax = 4;
-constexpr int kNumBars = 2 * QSTAGES + 4 + 2 * kSfSetsMax;
 
 template <int kEpiWarps>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(96 + 32 * kEpiWarps, 1)
 gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
-                       const __grid_constant__ CUtensorMap tma_sfa, const __grid_constant__ CUtensorMap tma_sfb, const Mx2Params p) {
+                       const __grid_constant__ CUtensorMap tma_sfa, const __grid_constant__ CUtensorMap tma_sfb,
+                       const __grid_constant__ CUtensorMap tma_d, const __grid_constant__ CUtensorMap tma_dq,
+                       const __grid_constant__ CUtensorMap tma_dt, const Mx2Params p) {
+  static_assert(kEpiWarps == kEpiWarpsQ, "the staging tiles are laid out for twelve epilogue warps");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - raw);
-  const uint32_t bars = base + QSTAGES * QSTAGE_STRIDE;
+  const uint32_t bars = base + QBARS_BASE;
   auto full = [&](int s) { return bars + 8u * s; };
   auto empty = [&](int s) { return bars + 8u * (QSTAGES + s); };
   auto tfull = [&](int a) { return bars + 8u * (2 * QSTAGES + a); };
@@ -365,13 +476,14 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
   auto sffull = [&](int i) { return bars + 8u * (2 * QSTAGES + 4 + i); };
   auto sfempty = [&](int i) { return bars + 8u * (2 * QSTAGES + 4 + kSfSetsMax + i); };
   const uint32_t tmem_slot = bars + 8u * kNumBars;
-  volatile uint32_t* tmem_slot_g = reinterpret_cast<volatile uint32_t*>(gen + QSTAGES * QSTAGE_STRIDE + 8 * kNumBars);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + QSTAGES * QSTAGE_STRIDE + 8 * kNumBars + 8);
+  volatile uint32_t* tmem_slot_g = reinterpret_cast<volatile uint32_t*>(gen + QBARS_BASE + 8 * kNumBars);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + QBARS_BASE + 8 * kNumBars + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = q_cluster_ctarank();
   const bool leader = rank == 0;
   const int bn = p.bn, half_n = p.bn >> 1;
+  const int nstages = p.staged ? QSTAGES_STAGED : QSTAGES;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < QSTAGES; ++s) {
@@ -392,6 +504,11 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
     tma_prefetch_desc(&tma_b);
     tma_prefetch_desc(&tma_sfa);
     tma_prefetch_desc(&tma_sfb);
+    if (p.staged) {
+      tma_prefetch_desc(&tma_d);
+      tma_prefetch_desc(&tma_dq);
+      tma_prefetch_desc(&tma_dt);
+    }
   }
   q_cluster_sync();
   if (warp == 1) {
@@ -442,7 +559,7 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
           q_tma_2d(ssfb, &tma_sfb, full(stage), 0, sfb_row + kb * 4);
           if (!leader) q_mbar_arrive_cluster(full(stage), 0);
         }
-        if (++stage == QSTAGES) { stage = 0; phase ^= 1u; }
+        if (++stage == nstages) { stage = 0; phase ^= 1u; }
       }
     }
     QPROF_ADD(1);
@@ -507,7 +624,7 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
             if (kb == kb1 - 1) q_commit_pair(tfull(acc));
           }
           QPROF_ADD(6);
-          if (++stage == QSTAGES) { stage = 0; phase ^= 1u; }
+          if (++stage == nstages) { stage = 0; phase ^= 1u; }
           if (++sfset == p.sf_sets) { sfset = 0; sf_phase ^= 1u; }
         }
         if (++acc == p.acc_stages) { acc = 0; acc_phase ^= 1u; }
@@ -547,7 +664,7 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
             q_cp_sf_pair(sfb_t + 4, sdesc0 + soff + ((QSFA_BYTES + 512) >> 4));
             q_commit_local(sffull(sfset));
           }
-          if (++stage == QSTAGES) { stage = 0; phase ^= 1u; }
+          if (++stage == nstages) { stage = 0; phase ^= 1u; }
           if (++sfset == p.sf_sets) { sfset = 0; sf_phase ^= 1u; }
         }
       }
@@ -561,7 +678,9 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
     const int nchunks = bn >> 5;
     const bool f32out = p.epi == GE_ACC_F32;
     const int variant = (p.Dq != nullptr ? 1 : 0) | (p.Dt != nullptr ? 2 : 0);
-    int acc = 0;
+    const uint32_t stg = base + QSTG_BASE + (uint32_t)(warp - 3) * QSTG_BYTES;
+    const uint32_t scratch = base + QSCRATCH_BASE + (uint32_t)(warp - 3) * QSTG_SCRATCH;
+    int acc = 0, tile_iter = 0;
     uint32_t acc_phase = 0;
     QPROF_DECL(2);
     for (int tile = cluster_id; tile < total; tile += n_clusters) {
@@ -574,13 +693,18 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
       if (!__all_sync(0xffffffffu, got)) break;
       tc_fence_after();
       const uint32_t taddr0 = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * bn);
-      if (variant == 0) {
+      // the three warps of a quadrant take every third chunk; which of them starts at chunk 0 rotates from tile to tile,
+      // so with seven or eight chunks a tile the odd one falls on each warp in turn
+      const int first = (sub + tile_iter) % (kEpiWarps / 4);
+      ++tile_iter;
+      if (!p.staged) {
+        // fp32 accumulate (split-K weight gradients) or a bf16 result whose pitch does not allow a TMA store
         const int row = row0 + lane;
         const bool row_ok = row < p.M;
         const long long drow = (long long)b * p.strideD + (long long)row * p.ldd;
         const long long rrow = (long long)b * p.strideR + (long long)row * p.ldr;
 #pragma unroll 1
-        for (int c = sub; c < nchunks; c += kEpiWarps / 4) {
+        for (int c = first; c < nchunks; c += kEpiWarps / 4) {
           uint32_t r[32];
           __syncwarp();
           BONES_TMEM_LD32(taddr0 + (uint32_t)(c * 32), r);
@@ -593,7 +717,7 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
                            reinterpret_cast<const uint8_t*>(p.R) + (rrow + col0) * esz, false, nopre, min(32, p.N - col0));
         }
       } else {
-#define BONES_Q_TILE(E, WQ, WT) q_quant_tile<E, WQ, WT, kEpiWarps>(p, taddr0, b, row0, nb * bn, lane, sub, nchunks)
+#define BONES_Q_TILE(E, WQ, WT) q_staged_tile<E, WQ, WT>(p, &tma_d, &tma_dq, &tma_dt, taddr0, stg, scratch, b, row0, nb * bn, lane, first, nchunks)
 #define BONES_Q_EPI(WQ, WT)                                         \
   switch (p.epi) {                                                  \
     case GE_BF16_RES: BONES_Q_TILE(GE_BF16_RES, WQ, WT); break;     \
@@ -601,7 +725,8 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
     case GE_MUL_2SQRT: BONES_Q_TILE(GE_MUL_2SQRT, WQ, WT); break;   \
     default: BONES_Q_TILE(GE_BF16, WQ, WT); break;                  \
   }
-        if (variant == 1) { BONES_Q_EPI(true, false) }
+        if (variant == 0) { BONES_Q_EPI(false, false) }
+        else if (variant == 1) { BONES_Q_EPI(true, false) }
         else if (variant == 2) { BONES_Q_EPI(false, true) }
         else { BONES_Q_EPI(true, true) }
 #undef BONES_Q_EPI
@@ -612,6 +737,8 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
       if (lane == 0) q_mbar_arrive_cluster(tempty(acc), 0);
       if (++acc == p.acc_stages) { acc = 0; acc_phase ^= 1u; }
     }
+    __syncwarp();
+    if (p.staged && elect_one()) q_bulk_wait_read();          // the last stores have read the staging tiles
     QPROF_ADD(1);
     if (warp == 3 && lane == 0) { QPROF_STORE(11, 0); QPROF_STORE(12, 1); QPROF_TOTAL(13); }
   }
@@ -688,6 +815,16 @@ static int tmap_operand_q(CUtensorMap* out, const void* ptr, int major, long lon
   strides[0] = (uint64_t)ld;
   strides[1] = batch > 1 ? (uint64_t)stride : strides[0] * dims[1];
   return make_tmap(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, ptr, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+// output [batch, M, N] with `esz`-byte elements, row pitch `ld` and batch pitch `stride` (in elements), stored in boxes
+// of 32 x 32 from the epilogue's staging tiles (64-byte swizzle for bf16 rows of 64 bytes, 32-byte for E4M3)
+static int tmap_out_q(CUtensorMap* out, const void* ptr, int esz, long long M, long long N, long long ld, long long stride, int batch) {
+  uint64_t dims[3] = {(uint64_t)N, (uint64_t)M, (uint64_t)batch};
+  uint64_t strides[2] = {(uint64_t)(ld * esz), (uint64_t)((batch > 1 ? stride : ld * M) * esz)};
+  uint32_t box[3] = {32, 32, 1};
+  return make_tmap(out, esz == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, ptr, dims, strides, box,
+                   esz == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
 }
 
 // scale chunks seen as rows of 256 bytes; a box of `box_rows` rows is one K block's scales of one tile
@@ -796,13 +933,25 @@ int bones_gemm_mxfp8_pair(const void* Aq, const void* sfa, const void* Bq, const
   if (rc) return rc;
   rc = tmap_scales_q(&tsb, sfb, sfb_bytes * batch, 4);
   if (rc) return rc;
-  constexpr size_t smem = (size_t)QSTAGES * QSTAGE_STRIDE + 8 * kNumBars + 16 + 1024;
-  static int epi_warps = 0;
-  if (epi_warps == 0) {
-    const char* e = getenv("BONES_MX_EPI_WARPS");
-    epi_warps = (e && atoi(e) == 16) ? 16 : 12;
-    BONES_CHECK(cudaFuncSetAttribute(gemm_mxfp8_pair_kernel<12>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    BONES_CHECK(cudaFuncSetAttribute(gemm_mxfp8_pair_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  // bf16 / E4M3 results leave through shared memory and TMA stores when their pitches allow it (16-byte multiples)
+  const bool d_tma = !D || ((ldd % 8 == 0) && (strideD % 8 == 0) && (((uintptr_t)D & 15) == 0));
+  const bool r_vec = !R || ((ldr % 8 == 0) && (strideR % 8 == 0) && (((uintptr_t)R & 15) == 0));
+  // short contractions and quantised copies: the epilogue is the larger part of a tile and gets the staging tiles (at
+  // the price of the sixth stage); long contractions keep six stages and store from registers
+  p.staged = (!f32out && d_tma && r_vec && (Dq || Dt || K <= 2560)) ? 1 : 0;
+  if (!p.staged && (Dq || Dt)) return -7;
+  CUtensorMap td, tdq, tdt;
+  memset(&td, 0, sizeof(td)); memset(&tdq, 0, sizeof(tdq)); memset(&tdt, 0, sizeof(tdt));
+  if (p.staged) {
+    if (D) { rc = tmap_out_q(&td, D, 2, M, N, ldd, strideD, batch); if (rc) return rc; }
+    if (Dq) { rc = tmap_out_q(&tdq, Dq, 1, M, N, N, (long long)M * N, batch); if (rc) return rc; }
+    if (Dt) { rc = tmap_out_q(&tdt, Dt, 1, M, N, N, (long long)M * N, batch); if (rc) return rc; }
+  }
+  constexpr size_t smem = QSMEM_BYTES;
+  static bool attr_set = false;
+  if (!attr_set) {
+    BONES_CHECK(cudaFuncSetAttribute(gemm_mxfp8_pair_kernel<kEpiWarpsQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    attr_set = true;
   }
   int dev = 0, sms = 0;
   BONES_CHECK(cudaGetDevice(&dev));
@@ -827,10 +976,7 @@ int bones_gemm_mxfp8_pair(const void* Aq, const void* sfa, const void* Bq, const
   if (p.splits > KB) p.splits = KB;
   const int total = base_tiles * p.splits;
   const int clusters = total < pairs ? total : pairs;
-  if (epi_warps == 12)
-    gemm_mxfp8_pair_kernel<12><<<2 * clusters, 96 + 32 * 12, smem, reinterpret_cast<cudaStream_t>(stream)>>>(ta, tb, tsa, tsb, p);
-  else
-    gemm_mxfp8_pair_kernel<16><<<2 * clusters, 96 + 32 * 16, smem, reinterpret_cast<cudaStream_t>(stream)>>>(ta, tb, tsa, tsb, p);
+  gemm_mxfp8_pair_kernel<kEpiWarpsQ><<<2 * clusters, 96 + 32 * kEpiWarpsQ, smem, reinterpret_cast<cudaStream_t>(stream)>>>(ta, tb, tsa, tsb, td, tdq, tdt, p);
   return (int)cudaGetLastError();
 }
 
