@@ -439,27 +439,40 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
   auto tS = [&](int s) { return tmem + (uint32_t)s * 128u; };
   auto tO = [&](int s) { return tmem + 256u + (uint32_t)s * 128u; };
 
+  // The producer and MMA roles run on all 32 lanes of their warp with warp-uniform state and issue from the elected lane
+  // (`elect_one` in common.cuh: operands computed under a `lane == 0` branch cost about 80 clocks per `tcgen05.mma`, more
+  // than the 64 clocks a 128 x 128 x 16 MMA executes).  Work items are drawn by lane 0 and handed round with a shuffle.
+  // A lane whose bounded wait ran out turns `dead`: it walks on without waiting or issuing; when lane 0 is dead no
+  // further item is drawn and the warp leaves together.
   if (warp == 0) {
-    if (lane == 0) {
-      int g = 0, it = 0;
-      bool ok = true;
-      for (;; ++it) {
-        const int w = ok ? item_publish(ring_bars, ring_slots, it, p.items, total) : -1;
-        if (w < 0) break;
-        const FwdItem im = fwd_item(p, w, n_tiles);
-        const int qb = it & 1, row0 = im.b * p.T;
-        if (it >= 2 && !mbar_wait(q_free(qb), (uint32_t)(((it - 2) >> 1) & 1), abort_flag, p.err, ERR_WAIT_EMPTY)) break;
+    int g = 0, it = 0;
+    bool dead = false;
+    for (;; ++it) {
+      int w = -1;
+      if (lane == 0 && !dead) w = item_publish(ring_bars, ring_slots, it, p.items, total);
+      w = warp_uniform(w);
+      if (w < 0) break;
+      FwdItem im = fwd_item(p, w, n_tiles);
+      im.kt0 = warp_uniform(im.kt0);
+      im.n = im.qt - im.kt0 + 1;
+      const int qb = it & 1, row0 = im.b * p.T;
+      if (it >= 2 && !dead) dead = !mbar_wait(q_free(qb), (uint32_t)(((it - 2) >> 1) & 1), abort_flag, p.err, ERR_WAIT_EMPTY);
+      if (elect_one() && !dead) {
         mbar_arrive_expect_tx(q_full(qb), TILE_BYTES);
         tma_load_2d(sQ(qb), &tm_qk, q_full(qb), im.h * AD, row0 + im.qt * AT);
         tma_load_2d(sQ(qb) + ATOM_BYTES, &tm_qk, q_full(qb), im.h * AD + 64, row0 + im.qt * AT);
-        for (int j = 0; j < im.n; ++j, ++g) {
-          const int ks = g & 1, vs = g % 3;
-          const int r = row0 + (im.kt0 + j) * AT;
-          if (g >= 2 && !mbar_wait(k_free(ks), (uint32_t)(((g - 2) >> 1) & 1), abort_flag, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+      }
+      for (int j = 0; j < im.n; ++j, ++g) {
+        const int ks = g & 1, vs = g % 3;
+        const int r = row0 + (im.kt0 + j) * AT;
+        if (g >= 2 && !dead) dead = !mbar_wait(k_free(ks), (uint32_t)(((g - 2) >> 1) & 1), abort_flag, p.err, ERR_WAIT_EMPTY);
+        if (elect_one() && !dead) {
           mbar_arrive_expect_tx(k_full(ks), TILE_BYTES);
           tma_load_2d(sK(ks), &tm_qk, k_full(ks), A + im.h * AD, r);
           tma_load_2d(sK(ks) + ATOM_BYTES, &tm_qk, k_full(ks), A + im.h * AD + 64, r);
-          if (g >= 3 && !mbar_wait(v_free(vs), (uint32_t)(((g - 3) / 3) & 1), abort_flag, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+        }
+        if (g >= 3 && !dead) dead = !mbar_wait(v_free(vs), (uint32_t)(((g - 3) / 3) & 1), abort_flag, p.err, ERR_WAIT_EMPTY);
+        if (elect_one() && !dead) {
           mbar_arrive_expect_tx(v_full(vs), TILE_BYTES);
           tma_load_2d(sV(vs), &tm_v, v_full(vs), 2 * A + im.h * AD, r);
           tma_load_2d(sV(vs) + ATOM_BYTES, &tm_v, v_full(vs), 2 * A + im.h * AD + 64, r);
@@ -467,22 +480,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc_s = umma_idesc_f16(128, 128, 1, 0, 0);   // Q (K-major) x K (K-major)
-      const uint32_t idesc_o = umma_idesc_f16(128, 128, 1, 0, 1);   // P (TMEM) x V (MN-major)
-      // the O += P V step of a tile is issued one tile late, behind the next tile's S, so the softmax of tile g runs
-      // under the S MMAs of tile g+1.  P(g) sits in TMEM as packed bf16 pairs over the S(g) columns it was computed
-      // from (each softmax warp packs its 64 columns into the first 32 of its own range).
-      int pg = -1, p_item = 0;
-      bool p_first = false, p_last = false;
-      auto issue_pv = [&]() -> bool {
-        const int sb = pg & 1, ob = p_item & 1, vs = pg % 3;
-        if (!mbar_wait(v_full(vs), (uint32_t)((pg / 3) & 1), abort_flag, p.err, ERR_WAIT_FULL)) return false;
-        if (!mbar_wait(p_full(sb), (uint32_t)((pg >> 1) & 1), abort_flag, p.err, ERR_WAIT_AUX)) return false;
-        if (p_first && p_item >= 2 &&
-            !mbar_wait(o_free(ob), (uint32_t)(((p_item - 2) >> 1) & 1), abort_flag, p.err, ERR_WAIT_TMEM_EMPTY))
-          return false;
-        tc_fence_after();
+    const uint32_t idesc_s = umma_idesc_f16(128, 128, 1, 0, 0);   // Q (K-major) x K (K-major)
+    const uint32_t idesc_o = umma_idesc_f16(128, 128, 1, 0, 1);   // P (TMEM) x V (MN-major)
+    // the O += P V step of a tile is issued one tile late, behind the next tile's S, so the softmax of tile g runs
+    // under the S MMAs of tile g+1.  P(g) sits in TMEM as packed bf16 pairs over the S(g) columns it was computed
+    // from (each softmax warp packs its 64 columns into the first 32 of its own range).
+    int pg = -1, p_item = 0;
+    bool p_first = false, p_last = false, dead = false;
+    auto issue_pv = [&]() {
+      const int sb = pg & 1, ob = p_item & 1, vs = pg % 3;
+      if (!dead) dead = !mbar_wait(v_full(vs), (uint32_t)((pg / 3) & 1), abort_flag, p.err, ERR_WAIT_FULL);
+      if (!dead) dead = !mbar_wait(p_full(sb), (uint32_t)((pg >> 1) & 1), abort_flag, p.err, ERR_WAIT_AUX);
+      if (p_first && p_item >= 2 && !dead)
+        dead = !mbar_wait(o_free(ob), (uint32_t)(((p_item - 2) >> 1) & 1), abort_flag, p.err, ERR_WAIT_TMEM_EMPTY);
+      tc_fence_after();
+      if (elect_one() && !dead) {
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint64_t bd = umma_smem_desc(sV(vs) + k * 2048, ATOM_BYTES, 1024, kLayoutSw128);
@@ -490,21 +502,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
         }
         tc_commit(v_free(vs));
         if (p_last) tc_commit(o_full(ob));
-        return true;
-      };
-      int g = 0, it = 0;
-      bool ok = true;
-      for (;; ++it) {
-        const int w = ok ? item_take(ring_bars, ring_slots, it, abort_flag, p.err) : -1;
-        if (w < 0) break;
-        const FwdItem im = fwd_item(p, w, n_tiles);
-        const int qb = it & 1;
-        if (!mbar_wait(q_full(qb), (uint32_t)((it >> 1) & 1), abort_flag, p.err, ERR_WAIT_FULL)) break;
-        for (int j = 0; j < im.n; ++j, ++g) {
-          const int sb = g & 1;
-          if (!mbar_wait(k_full(sb), (uint32_t)((g >> 1) & 1), abort_flag, p.err, ERR_WAIT_FULL)) { ok = false; break; }
-          tc_fence_after();
-          // S(g) overwrites the buffer that held P(g-2): its O MMAs were issued earlier on the same (in-order) pipe
+      }
+    };
+    int g = 0, it = 0;
+    for (;; ++it) {
+      int w = -1;
+      if (!dead) w = item_take(ring_bars, ring_slots, it, abort_flag, p.err);
+      w = warp_uniform(w);
+      if (w < 0) break;
+      FwdItem im = fwd_item(p, w, n_tiles);
+      im.kt0 = warp_uniform(im.kt0);
+      im.n = im.qt - im.kt0 + 1;
+      const int qb = it & 1;
+      if (!dead) dead = !mbar_wait(q_full(qb), (uint32_t)((it >> 1) & 1), abort_flag, p.err, ERR_WAIT_FULL);
+      for (int j = 0; j < im.n; ++j, ++g) {
+        const int sb = g & 1;
+        if (!dead) dead = !mbar_wait(k_full(sb), (uint32_t)((g >> 1) & 1), abort_flag, p.err, ERR_WAIT_FULL);
+        tc_fence_after();
+        // S(g) overwrites the buffer that held P(g-2): its O MMAs were issued earlier on the same (in-order) pipe
+        if (elect_one() && !dead) {
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             const uint32_t off = (k >> 2) * ATOM_BYTES + (k & 3) * 32;
@@ -514,12 +530,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
           tc_commit(s_full(sb));
           tc_commit(k_free(sb));
           if (j == im.n - 1) tc_commit(q_free(qb));
-          if (pg >= 0 && !issue_pv()) { ok = false; break; }
-          pg = g; p_item = it; p_first = j == 0; p_last = j == im.n - 1;
         }
+        if (pg >= 0) issue_pv();
+        pg = g; p_item = it; p_first = j == 0; p_last = j == im.n - 1;
       }
-      if (ok && pg >= 0) issue_pv();
     }
+    if (pg >= 0) issue_pv();
   } else {
     // Softmax: eight warps, two per 32-lane TMEM quadrant; each thread owns one query row and 64 of the tile's 128 keys.
     const int q = warp & 3, half = (warp - 2) >> 2;

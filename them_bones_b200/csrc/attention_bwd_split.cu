@@ -209,30 +209,40 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
   const uint32_t tmem = *tmem_slot_g;
   const uint32_t tS = tmem, tdP = tmem + 128, tdV = tmem + 256, tdK = tmem + 384;
 
+  // The producer and MMA roles run on all 32 lanes of their warp with warp-uniform state and issue from the elected lane
+  // (`elect_one` in common.cuh).  Work items are drawn by lane 0 and handed round with a shuffle.  A lane whose bounded
+  // wait ran out turns `dead`: it walks on without waiting or issuing; when lane 0 is dead no further item is drawn.
   if (warp == 0) {
-    if (lane == 0) {
-      int g = 0, it = 0;
-      bool ok = true;
-      for (;; ++it) {
-        const int w = ok ? item_publish(ring_bars, ring_slots, it, p.items, total) : -1;
-        if (w < 0) break;
-        const DkvItem im = dkv_item(p, w, n_tiles);
-        const int row0 = im.b * p.T;
-        if (it >= 1 && !mbar_wait(bar(B_KVFREE), (uint32_t)((it - 1) & 1), abort_flag, p.err, ERR_WAIT_EMPTY)) break;
+    int g = 0, it = 0;
+    bool dead = false;
+    for (;; ++it) {
+      int w = -1;
+      if (lane == 0 && !dead) w = item_publish(ring_bars, ring_slots, it, p.items, total);
+      w = warp_uniform(w);
+      if (w < 0) break;
+      DkvItem im = dkv_item(p, w, n_tiles);
+      im.n = warp_uniform(im.n);
+      const int row0 = im.b * p.T;
+      if (it >= 1 && !dead) dead = !mbar_wait(bar(B_KVFREE), (uint32_t)((it - 1) & 1), abort_flag, p.err, ERR_WAIT_EMPTY);
+      if (elect_one() && !dead) {
         mbar_arrive_expect_tx(bar(B_KV), 2 * STILE);
         tma_load_2d(sK, &tm_qk, bar(B_KV), A + im.h * 128, row0 + im.kt * ST);
         tma_load_2d(sK + SATOM, &tm_qk, bar(B_KV), A + im.h * 128 + 64, row0 + im.kt * ST);
         tma_load_2d(sV, &tm_v, bar(B_KV), 2 * A + im.h * 128, row0 + im.kt * ST);
         tma_load_2d(sV + SATOM, &tm_v, bar(B_KV), 2 * A + im.h * 128 + 64, row0 + im.kt * ST);
-        const float2* stat_row = p.stats + ((long long)im.b * p.H + im.h) * p.T;
-        for (int i = 0; i < im.n; ++i, ++g) {
-          const int qs = g % 3, ds = g & 1;
-          const int r = row0 + (im.kt + i) * ST;
-          if (g >= 3 && !mbar_wait(bar(B_QFREE0 + qs), (uint32_t)(((g - 3) / 3) & 1), abort_flag, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+      }
+      const float2* stat_row = p.stats + ((long long)im.b * p.H + im.h) * p.T;
+      for (int i = 0; i < im.n; ++i, ++g) {
+        const int qs = g % 3, ds = g & 1;
+        const int r = row0 + (im.kt + i) * ST;
+        if (g >= 3 && !dead) dead = !mbar_wait(bar(B_QFREE0 + qs), (uint32_t)(((g - 3) / 3) & 1), abort_flag, p.err, ERR_WAIT_EMPTY);
+        if (elect_one() && !dead) {
           mbar_arrive_expect_tx(bar(B_Q0 + qs), STILE);
           tma_load_2d(sQ(qs), &tm_qk, bar(B_Q0 + qs), im.h * 128, r);
           tma_load_2d(sQ(qs) + SATOM, &tm_qk, bar(B_Q0 + qs), im.h * 128 + 64, r);
-          if (g >= 2 && !mbar_wait(bar(B_DOFREE0 + ds), (uint32_t)(((g - 2) >> 1) & 1), abort_flag, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+        }
+        if (g >= 2 && !dead) dead = !mbar_wait(bar(B_DOFREE0 + ds), (uint32_t)(((g - 2) >> 1) & 1), abort_flag, p.err, ERR_WAIT_EMPTY);
+        if (elect_one() && !dead) {
           mbar_arrive_expect_tx(bar(B_DO0 + ds), STILE + 1024);
           tma_load_2d(sdO(ds), &tm_dy, bar(B_DO0 + ds), im.h * 128, r);
           tma_load_2d(sdO(ds) + SATOM, &tm_dy, bar(B_DO0 + ds), im.h * 128 + 64, r);
@@ -241,62 +251,65 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t id_kk = umma_idesc_f16(128, 128, 1, 0, 0);
-      const uint32_t id_km = umma_idesc_f16(128, 128, 1, 0, 1);
-      auto issue_s = [&](int t) -> bool {                 // S^T(t) = Kh Qh(t)^T
-        if (!mbar_wait(bar(B_Q0 + t % 3), (uint32_t)((t / 3) & 1), abort_flag, p.err, ERR_WAIT_FULL)) return false;
-        tc_fence_after();
+    const uint32_t id_kk = umma_idesc_f16(128, 128, 1, 0, 0);
+    const uint32_t id_km = umma_idesc_f16(128, 128, 1, 0, 1);
+    bool dead = false;
+    auto issue_s = [&](int t) {                           // S^T(t) = Kh Qh(t)^T
+      if (!dead) dead = !mbar_wait(bar(B_Q0 + t % 3), (uint32_t)((t / 3) & 1), abort_flag, p.err, ERR_WAIT_FULL);
+      tc_fence_after();
+      if (elect_one() && !dead) {
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma_f16(tS, sdesc_k(sK, k), sdesc_k(sQ(t % 3), k), id_kk, k ? 1u : 0u);
         tc_commit(bar(B_SFULL));
-        return true;
-      };
-      auto issue_dp = [&](int t, bool last) -> bool {     // dP^T(t) = V dO(t)^T; after the item's last one K and V are free
-        if (!mbar_wait(bar(B_DO0 + (t & 1)), (uint32_t)((t >> 1) & 1), abort_flag, p.err, ERR_WAIT_FULL)) return false;
-        tc_fence_after();
+      }
+    };
+    auto issue_dp = [&](int t, bool last) {               // dP^T(t) = V dO(t)^T; after the item's last one K and V are free
+      if (!dead) dead = !mbar_wait(bar(B_DO0 + (t & 1)), (uint32_t)((t >> 1) & 1), abort_flag, p.err, ERR_WAIT_FULL);
+      tc_fence_after();
+      if (elect_one() && !dead) {
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma_f16(tdP, sdesc_k(sV, k), sdesc_k(sdO(t & 1), k), id_kk, k ? 1u : 0u);
         tc_commit(bar(B_DPFULL));
         if (last) tc_commit(bar(B_KVFREE));
-        return true;
-      };
-      int g = 0, it = 0;
-      bool ok = true;
-      for (;; ++it) {
-        const int w = ok ? item_take(ring_bars, ring_slots, it, abort_flag, p.err) : -1;
-        if (w < 0) break;
-        const DkvItem im = dkv_item(p, w, n_tiles);
-        if (!mbar_wait(bar(B_KV), (uint32_t)(it & 1), abort_flag, p.err, ERR_WAIT_FULL)) break;
-        // the first tile's S^T and dP^T go behind the previous item's last dV / dK MMAs on the same (in-order) pipe
-        if (!issue_s(g) || !issue_dp(g, im.n == 1)) break;
-        for (int i = 0; i < im.n; ++i, ++g) {
-          const int s = g & 1, qs = g % 3;
-          const uint32_t ph = (uint32_t)(g & 1);
-          const bool more = i + 1 < im.n;
-          // P^T(g) sits packed in the S^T columns: dV += P^T dO, then S^T(g+1) behind it
-          if (!mbar_wait(bar(B_PREADY), ph, abort_flag, p.err, ERR_WAIT_AUX)) { ok = false; break; }
-          if (i == 0 && it >= 1 && !mbar_wait(bar(B_ACCFREE), (uint32_t)((it - 1) & 1), abort_flag, p.err, ERR_WAIT_TMEM_EMPTY)) {
-            ok = false;                                   // the previous item's dK / dV have not been drained
-            break;
-          }
-          tc_fence_after();
+      }
+    };
+    int g = 0, it = 0;
+    for (;; ++it) {
+      int w = -1;
+      if (!dead) w = item_take(ring_bars, ring_slots, it, abort_flag, p.err);
+      w = warp_uniform(w);
+      if (w < 0) break;
+      DkvItem im = dkv_item(p, w, n_tiles);
+      im.n = warp_uniform(im.n);
+      if (!dead) dead = !mbar_wait(bar(B_KV), (uint32_t)(it & 1), abort_flag, p.err, ERR_WAIT_FULL);
+      // the first tile's S^T and dP^T go behind the previous item's last dV / dK MMAs on the same (in-order) pipe
+      issue_s(g);
+      issue_dp(g, im.n == 1);
+      for (int i = 0; i < im.n; ++i, ++g) {
+        const int s = g & 1, qs = g % 3;
+        const uint32_t ph = (uint32_t)(g & 1);
+        const bool more = i + 1 < im.n;
+        // P^T(g) sits packed in the S^T columns: dV += P^T dO, then S^T(g+1) behind it
+        if (!dead) dead = !mbar_wait(bar(B_PREADY), ph, abort_flag, p.err, ERR_WAIT_AUX);
+        // the previous item's dK / dV must have been drained
+        if (i == 0 && it >= 1 && !dead) dead = !mbar_wait(bar(B_ACCFREE), (uint32_t)((it - 1) & 1), abort_flag, p.err, ERR_WAIT_TMEM_EMPTY);
+        tc_fence_after();
+        if (elect_one() && !dead) {
 #pragma unroll
           for (int k = 0; k < 8; ++k) umma_f16_ts(tdV, tS + packed_col(k), sdesc_mn(sdO(s), k), id_km, (i | k) ? 1u : 0u);
-          if (more && !issue_s(g + 1)) { ok = false; break; }
-          // dS^T(g) sits packed in the dP^T columns: dK += dS^T Qh, then dP^T(g+1) behind it
-          if (!mbar_wait(bar(B_DSREADY), ph, abort_flag, p.err, ERR_WAIT_AUX)) { ok = false; break; }
-          tc_fence_after();
+        }
+        if (more) issue_s(g + 1);
+        // dS^T(g) sits packed in the dP^T columns: dK += dS^T Qh, then dP^T(g+1) behind it
+        if (!dead) dead = !mbar_wait(bar(B_DSREADY), ph, abort_flag, p.err, ERR_WAIT_AUX);
+        tc_fence_after();
+        if (elect_one() && !dead) {
 #pragma unroll
           for (int k = 0; k < 8; ++k) umma_f16_ts(tdK, tdP + packed_col(k), sdesc_mn(sQ(qs), k), id_km, (i | k) ? 1u : 0u);
           tc_commit(bar(B_QFREE0 + qs));
           tc_commit(bar(B_DOFREE0 + s));     // dO(g) was read by dV(g); its statistics were in use until dS(g) was stored
-          if (more) {
-            if (!issue_dp(g + 1, i + 2 == im.n)) { ok = false; break; }
-          } else {
-            tc_commit(bar(B_DONE));
-          }
+          if (!more) tc_commit(bar(B_DONE));
         }
+        if (more) issue_dp(g + 1, i + 2 == im.n);
       }
     }
   } else {
@@ -490,29 +503,38 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_const
   const uint32_t tS = tmem, tdQ = tmem + 384;
   auto tdP = [&](int s) { return tmem + 128u + (uint32_t)s * 128u; };
 
+  // producer and MMA roles: warp-uniform loops issuing from the elected lane, as in the dK / dV kernel above
   if (warp == 0) {
-    if (lane == 0) {
-      int g = 0, it = 0;
-      bool ok = true;
-      for (;; ++it) {
-        const int w = ok ? item_publish(ring_bars, ring_slots, it, p.items, total) : -1;
-        if (w < 0) break;
-        const DqItem im = dq_item(p, w, n_tiles);
-        const int row0 = im.b * p.T, rq = row0 + im.qt * ST;
-        if (it >= 1 && !mbar_wait(bar(B_QDOFREE), (uint32_t)((it - 1) & 1), abort_flag, p.err, ERR_WAIT_EMPTY)) break;
+    int g = 0, it = 0;
+    bool dead = false;
+    for (;; ++it) {
+      int w = -1;
+      if (lane == 0 && !dead) w = item_publish(ring_bars, ring_slots, it, p.items, total);
+      w = warp_uniform(w);
+      if (w < 0) break;
+      DqItem im = dq_item(p, w, n_tiles);
+      im.kt0 = warp_uniform(im.kt0);
+      im.n = im.qt - im.kt0 + 1;
+      const int row0 = im.b * p.T, rq = row0 + im.qt * ST;
+      if (it >= 1 && !dead) dead = !mbar_wait(bar(B_QDOFREE), (uint32_t)((it - 1) & 1), abort_flag, p.err, ERR_WAIT_EMPTY);
+      if (elect_one() && !dead) {
         mbar_arrive_expect_tx(bar(B_QDO), 2 * STILE);
         tma_load_2d(sQ, &tm_qk, bar(B_QDO), im.h * 128, rq);
         tma_load_2d(sQ + SATOM, &tm_qk, bar(B_QDO), im.h * 128 + 64, rq);
         tma_load_2d(sdO, &tm_dy, bar(B_QDO), im.h * 128, rq);
         tma_load_2d(sdO + SATOM, &tm_dy, bar(B_QDO), im.h * 128 + 64, rq);
-        for (int j = 0; j < im.n; ++j, ++g) {
-          const int ks = g % 3, vs = g & 1;
-          const int r = row0 + (im.kt0 + j) * ST;
-          if (g >= 3 && !mbar_wait(bar(B_KFREE0 + ks), (uint32_t)(((g - 3) / 3) & 1), abort_flag, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+      }
+      for (int j = 0; j < im.n; ++j, ++g) {
+        const int ks = g % 3, vs = g & 1;
+        const int r = row0 + (im.kt0 + j) * ST;
+        if (g >= 3 && !dead) dead = !mbar_wait(bar(B_KFREE0 + ks), (uint32_t)(((g - 3) / 3) & 1), abort_flag, p.err, ERR_WAIT_EMPTY);
+        if (elect_one() && !dead) {
           mbar_arrive_expect_tx(bar(B_K0 + ks), STILE);
           tma_load_2d(sK(ks), &tm_qk, bar(B_K0 + ks), A + im.h * 128, r);
           tma_load_2d(sK(ks) + SATOM, &tm_qk, bar(B_K0 + ks), A + im.h * 128 + 64, r);
-          if (g >= 2 && !mbar_wait(bar(B_VFREE0 + vs), (uint32_t)(((g - 2) >> 1) & 1), abort_flag, p.err, ERR_WAIT_EMPTY)) { ok = false; break; }
+        }
+        if (g >= 2 && !dead) dead = !mbar_wait(bar(B_VFREE0 + vs), (uint32_t)(((g - 2) >> 1) & 1), abort_flag, p.err, ERR_WAIT_EMPTY);
+        if (elect_one() && !dead) {
           mbar_arrive_expect_tx(bar(B_V0 + vs), STILE);
           tma_load_2d(sV(vs), &tm_v, bar(B_V0 + vs), 2 * A + im.h * 128, r);
           tma_load_2d(sV(vs) + SATOM, &tm_v, bar(B_V0 + vs), 2 * A + im.h * 128 + 64, r);
@@ -520,44 +542,48 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_const
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t id_kk = umma_idesc_f16(128, 128, 1, 0, 0);
-      const uint32_t id_km = umma_idesc_f16(128, 128, 1, 0, 1);
-      // S(t) and dP(t) of running tile t; `last`: t is the last tile of its item, after which Q and dO may be reloaded
-      auto issue_sdp = [&](int t, bool last) -> bool {
-        if (!mbar_wait(bar(B_K0 + t % 3), (uint32_t)((t / 3) & 1), abort_flag, p.err, ERR_WAIT_FULL)) return false;
-        if (t >= 1 && !mbar_wait(bar(B_SFREE), (uint32_t)((t - 1) & 1), abort_flag, p.err, ERR_WAIT_AUX)) return false;
-        tc_fence_after();
+    const uint32_t id_kk = umma_idesc_f16(128, 128, 1, 0, 0);
+    const uint32_t id_km = umma_idesc_f16(128, 128, 1, 0, 1);
+    bool dead = false;
+    // S(t) and dP(t) of running tile t; `last`: t is the last tile of its item, after which Q and dO may be reloaded
+    auto issue_sdp = [&](int t, bool last) {
+      if (!dead) dead = !mbar_wait(bar(B_K0 + t % 3), (uint32_t)((t / 3) & 1), abort_flag, p.err, ERR_WAIT_FULL);
+      if (t >= 1 && !dead) dead = !mbar_wait(bar(B_SFREE), (uint32_t)((t - 1) & 1), abort_flag, p.err, ERR_WAIT_AUX);
+      tc_fence_after();
+      if (elect_one() && !dead) {
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma_f16(tS, sdesc_k(sQ, k), sdesc_k(sK(t % 3), k), id_kk, k ? 1u : 0u);
         tc_commit(bar(B_SFULL));
-        if (!mbar_wait(bar(B_V0 + (t & 1)), (uint32_t)((t >> 1) & 1), abort_flag, p.err, ERR_WAIT_FULL)) return false;
-        tc_fence_after();
-        // dP(t) goes into the buffer whose packed dS(t-2) the dQ MMAs of tile t-2 (issued earlier, same pipe) have read
+      }
+      if (!dead) dead = !mbar_wait(bar(B_V0 + (t & 1)), (uint32_t)((t >> 1) & 1), abort_flag, p.err, ERR_WAIT_FULL);
+      tc_fence_after();
+      // dP(t) goes into the buffer whose packed dS(t-2) the dQ MMAs of tile t-2 (issued earlier, same pipe) have read
+      if (elect_one() && !dead) {
 #pragma unroll
         for (int k = 0; k < 8; ++k) umma_f16(tdP(t & 1), sdesc_k(sdO, k), sdesc_k(sV(t & 1), k), id_kk, k ? 1u : 0u);
         tc_commit(bar(B_DPFULL0 + (t & 1)));
         tc_commit(bar(B_VFREE0 + (t & 1)));
         if (last) tc_commit(bar(B_QDOFREE));
-        return true;
-      };
-      int g = 0, it = 0;
-      bool ok = true;
-      for (;; ++it) {
-        const int w = ok ? item_take(ring_bars, ring_slots, it, abort_flag, p.err) : -1;
-        if (w < 0) break;
-        const DqItem im = dq_item(p, w, n_tiles);
-        if (!mbar_wait(bar(B_QDO), (uint32_t)(it & 1), abort_flag, p.err, ERR_WAIT_FULL)) break;
-        for (int j = 0; j < im.n; ++j, ++g) {
-          if (j == 0 && !issue_sdp(g, im.n == 1)) { ok = false; break; }
-          if (j + 1 < im.n && !issue_sdp(g + 1, j + 2 == im.n)) { ok = false; break; }
-          // dS(g) sits packed in the dP(g) columns: dQ += dS Kh(g), which also frees that K stage
-          if (!mbar_wait(bar(B_DSREADY), (uint32_t)(g & 1), abort_flag, p.err, ERR_WAIT_AUX)) { ok = false; break; }
-          if (j == 0 && it >= 1 && !mbar_wait(bar(B_DQFREE), (uint32_t)((it - 1) & 1), abort_flag, p.err, ERR_WAIT_TMEM_EMPTY)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
+      }
+    };
+    int g = 0, it = 0;
+    for (;; ++it) {
+      int w = -1;
+      if (!dead) w = item_take(ring_bars, ring_slots, it, abort_flag, p.err);
+      w = warp_uniform(w);
+      if (w < 0) break;
+      DqItem im = dq_item(p, w, n_tiles);
+      im.kt0 = warp_uniform(im.kt0);
+      im.n = im.qt - im.kt0 + 1;
+      if (!dead) dead = !mbar_wait(bar(B_QDO), (uint32_t)(it & 1), abort_flag, p.err, ERR_WAIT_FULL);
+      for (int j = 0; j < im.n; ++j, ++g) {
+        if (j == 0) issue_sdp(g, im.n == 1);
+        if (j + 1 < im.n) issue_sdp(g + 1, j + 2 == im.n);
+        // dS(g) sits packed in the dP(g) columns: dQ += dS Kh(g), which also frees that K stage
+        if (!dead) dead = !mbar_wait(bar(B_DSREADY), (uint32_t)(g & 1), abort_flag, p.err, ERR_WAIT_AUX);
+        if (j == 0 && it >= 1 && !dead) dead = !mbar_wait(bar(B_DQFREE), (uint32_t)((it - 1) & 1), abort_flag, p.err, ERR_WAIT_TMEM_EMPTY);
+        tc_fence_after();
+        if (elect_one() && !dead) {
 #pragma unroll
           for (int k = 0; k < 8; ++k)
             umma_f16_ts(tdQ, tdP(g & 1) + packed_col(k), sdesc_mn(sK(g % 3), k), id_km, (j | k) ? 1u : 0u);

@@ -75,6 +75,9 @@ __device__ __forceinline__ bool elect_one() {
       : "=r"(pred));
   return pred != 0;
 }
+// Lane 0's value on every lane.  Besides handing a value round, the shuffle tells the compiler that what follows from it
+// (loop bounds, stage indices, descriptors) is warp-uniform.
+__device__ __forceinline__ int warp_uniform(int v) { return __shfl_sync(0xffffffffu, v, 0); }
 // Bounded wait.  `abort_flag` lives in shared memory and is raised by whichever role gives up first.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code) {
   if (mbar_try_wait(bar, parity)) return true;
