@@ -22,6 +22,27 @@ constexpr uint32_t STILE = ST * 128 * 2;   // 32 KB: two 128-byte-swizzled atoms
 constexpr uint32_t SATOM = STILE / 2;
 constexpr float kLog2e = 1.4426950408889634f;
 
+// Cycle accounting of the dK / dV kernel's roles, compiled in only with -DBONES_ATTN_PROF (a measuring build; the regular
+// library carries none of it).  Each role sums the clocks it spends in each of its waits and in its work and stores the
+// sums in its CTA's 32 slots of the buffer given to `bones_attn_set_prof`:
+//   MMA warp: 0 wait item + K/V  1 wait Q  2 wait dO  3 wait P ready  4 wait accumulators free  5 wait dS ready  6 issue  7 total
+//             8 tiles;  compute warp 2: 10 wait statistics  11 wait S  12 P  13 wait dP  14 dS  15 wait done  16 drain  17 total;
+//   producer: 20 waits  21 issue.
+#ifdef BONES_ATTN_PROF
+__device__ long long* g_attn_prof = nullptr;
+#define APROF_DECL(n) long long ap_[n] = {}; long long ap_t_ = clock64(); const long long ap_t0_ = ap_t_
+#define APROF_ADD(i) do { const long long n_ = clock64(); ap_[i] += n_ - ap_t_; ap_t_ = n_; } while (0)
+#define APROF_COUNT(i) (++ap_[i])
+#define APROF_STORE(slot, i) do { if (g_attn_prof) g_attn_prof[(long long)blockIdx.x * 32 + (slot)] = ap_[i]; } while (0)
+#define APROF_TOTAL(slot) do { if (g_attn_prof) g_attn_prof[(long long)blockIdx.x * 32 + (slot)] = clock64() - ap_t0_; } while (0)
+#else
+#define APROF_DECL(n)
+#define APROF_ADD(i)
+#define APROF_COUNT(i)
+#define APROF_STORE(slot, i)
+#define APROF_TOTAL(slot)
+#endif
+
 struct SplitParams {
   int B, T, H;
   float c1, scale;
@@ -215,6 +236,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
   if (warp == 0) {
     int g = 0, it = 0;
     bool dead = false;
+    APROF_DECL(2);
     for (;; ++it) {
       int w = -1;
       if (lane == 0 && !dead) w = item_publish(ring_bars, ring_slots, it, p.items, total);
@@ -223,7 +245,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
       DkvItem im = dkv_item(p, w, n_tiles);
       im.n = warp_uniform(im.n);
       const int row0 = im.b * p.T;
+      APROF_ADD(1);
       if (it >= 1 && !dead) dead = !mbar_wait(bar(B_KVFREE), (uint32_t)((it - 1) & 1), abort_flag, p.err, ERR_WAIT_EMPTY);
+      APROF_ADD(0);
       if (elect_one() && !dead) {
         mbar_arrive_expect_tx(bar(B_KV), 2 * STILE);
         tma_load_2d(sK, &tm_qk, bar(B_KV), A + im.h * 128, row0 + im.kt * ST);
@@ -235,13 +259,17 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
       for (int i = 0; i < im.n; ++i, ++g) {
         const int qs = g % 3, ds = g & 1;
         const int r = row0 + (im.kt + i) * ST;
+        APROF_ADD(1);
         if (g >= 3 && !dead) dead = !mbar_wait(bar(B_QFREE0 + qs), (uint32_t)(((g - 3) / 3) & 1), abort_flag, p.err, ERR_WAIT_EMPTY);
+        APROF_ADD(0);
         if (elect_one() && !dead) {
           mbar_arrive_expect_tx(bar(B_Q0 + qs), STILE);
           tma_load_2d(sQ(qs), &tm_qk, bar(B_Q0 + qs), im.h * 128, r);
           tma_load_2d(sQ(qs) + SATOM, &tm_qk, bar(B_Q0 + qs), im.h * 128 + 64, r);
         }
+        APROF_ADD(1);
         if (g >= 2 && !dead) dead = !mbar_wait(bar(B_DOFREE0 + ds), (uint32_t)(((g - 2) >> 1) & 1), abort_flag, p.err, ERR_WAIT_EMPTY);
+        APROF_ADD(0);
         if (elect_one() && !dead) {
           mbar_arrive_expect_tx(bar(B_DO0 + ds), STILE + 1024);
           tma_load_2d(sdO(ds), &tm_dy, bar(B_DO0 + ds), im.h * 128, r);
@@ -250,12 +278,17 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
         }
       }
     }
+    APROF_ADD(1);
+    if (lane == 0) { APROF_STORE(20, 0); APROF_STORE(21, 1); }
   } else if (warp == 1) {
     const uint32_t id_kk = umma_idesc_f16(128, 128, 1, 0, 0);
     const uint32_t id_km = umma_idesc_f16(128, 128, 1, 0, 1);
     bool dead = false;
+    APROF_DECL(8);
     auto issue_s = [&](int t) {                           // S^T(t) = Kh Qh(t)^T
+      APROF_ADD(6);
       if (!dead) dead = !mbar_wait(bar(B_Q0 + t % 3), (uint32_t)((t / 3) & 1), abort_flag, p.err, ERR_WAIT_FULL);
+      APROF_ADD(1);
       tc_fence_after();
       if (elect_one() && !dead) {
 #pragma unroll
@@ -264,7 +297,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
       }
     };
     auto issue_dp = [&](int t, bool last) {               // dP^T(t) = V dO(t)^T; after the item's last one K and V are free
+      APROF_ADD(6);
       if (!dead) dead = !mbar_wait(bar(B_DO0 + (t & 1)), (uint32_t)((t >> 1) & 1), abort_flag, p.err, ERR_WAIT_FULL);
+      APROF_ADD(2);
       tc_fence_after();
       if (elect_one() && !dead) {
 #pragma unroll
@@ -276,12 +311,14 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
     int g = 0, it = 0;
     for (;; ++it) {
       int w = -1;
+      APROF_ADD(6);
       if (!dead) w = item_take(ring_bars, ring_slots, it, abort_flag, p.err);
       w = warp_uniform(w);
       if (w < 0) break;
       DkvItem im = dkv_item(p, w, n_tiles);
       im.n = warp_uniform(im.n);
       if (!dead) dead = !mbar_wait(bar(B_KV), (uint32_t)(it & 1), abort_flag, p.err, ERR_WAIT_FULL);
+      APROF_ADD(0);
       // the first tile's S^T and dP^T go behind the previous item's last dV / dK MMAs on the same (in-order) pipe
       issue_s(g);
       issue_dp(g, im.n == 1);
@@ -290,9 +327,13 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
         const uint32_t ph = (uint32_t)(g & 1);
         const bool more = i + 1 < im.n;
         // P^T(g) sits packed in the S^T columns: dV += P^T dO, then S^T(g+1) behind it
+        APROF_ADD(6);
+        APROF_COUNT(7);
         if (!dead) dead = !mbar_wait(bar(B_PREADY), ph, abort_flag, p.err, ERR_WAIT_AUX);
+        APROF_ADD(3);
         // the previous item's dK / dV must have been drained
         if (i == 0 && it >= 1 && !dead) dead = !mbar_wait(bar(B_ACCFREE), (uint32_t)((it - 1) & 1), abort_flag, p.err, ERR_WAIT_TMEM_EMPTY);
+        APROF_ADD(4);
         tc_fence_after();
         if (elect_one() && !dead) {
 #pragma unroll
@@ -300,7 +341,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
         }
         if (more) issue_s(g + 1);
         // dS^T(g) sits packed in the dP^T columns: dK += dS^T Qh, then dP^T(g+1) behind it
+        APROF_ADD(6);
         if (!dead) dead = !mbar_wait(bar(B_DSREADY), ph, abort_flag, p.err, ERR_WAIT_AUX);
+        APROF_ADD(5);
         tc_fence_after();
         if (elect_one() && !dead) {
 #pragma unroll
@@ -312,6 +355,12 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
         if (more) issue_dp(g + 1, i + 2 == im.n);
       }
     }
+    APROF_ADD(6);
+    if (lane == 0) {
+      for (int i = 0; i < 7; ++i) APROF_STORE(i, i);
+      APROF_TOTAL(7);
+      APROF_STORE(8, 7);
+    }
   } else {
     const int q = warp & 3, half = (warp - 2) >> 2;
     const int r = q * 32 + lane;                       // key row of this thread
@@ -319,6 +368,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
     const int c0 = half * 64;                          // first query column of this thread
     bool ok = true;
     int g = 0, it = 0;
+    APROF_DECL(8);
     for (;; ++it) {
       const int w = ok ? item_take(ring_bars, ring_slots, it, abort_flag, p.err) : -1;
       if (w < 0) break;
@@ -328,7 +378,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
       for (int i = 0; i < im.n; ++i, ++g) {
         const int s = g & 1;
         const uint32_t ph = (uint32_t)(g & 1);
+        APROF_ADD(2);
         bool got = mbar_wait(bar(B_DO0 + s), (uint32_t)((g >> 1) & 1), abort_flag, p.err, ERR_WAIT_FULL);   // this tile's statistics
+        APROF_ADD(0);
         if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
         const float4* st4 = reinterpret_cast<const float4*>(gen + DKV_STAT + s * 1024) + c0 / 2;   // two queries per float4
         // document starts of this tile's queries (global, cached): only the tile that straddles a document start past
@@ -337,7 +389,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
         const bool need_doc = slo && nx_lo_last > k0;
         if (slo && i + 1 < im.n) nx_lo_last = slo[2 * ST - 1];
         float pr[64];
+        APROF_ADD(2);
         got = mbar_wait(bar(B_SFULL), ph, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
+        APROF_ADD(1);
         if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
         tc_fence_after();
         {
@@ -369,7 +423,9 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(B_PREADY));
+        APROF_ADD(2);
         got = mbar_wait(bar(B_DPFULL), ph, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
+        APROF_ADD(3);
         if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
         tc_fence_after();
         {
@@ -391,9 +447,11 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(B_DSREADY));
+        APROF_ADD(4);
       }
       if (!ok) break;
       const bool got = mbar_wait(bar(B_DONE), (uint32_t)(it & 1), abort_flag, p.err, ERR_WAIT_TMEM_FULL);
+      APROF_ADD(5);
       if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
       tc_fence_after();
       drain_row64(tdK + lane_addr + (uint32_t)c0, p.dqk + ((long long)(row0 + kpos)) * 2 * A + A + (long long)im.h * 128 + c0);
@@ -401,6 +459,11 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_ACCFREE));
+      APROF_ADD(6);
+    }
+    if (warp == 2 && lane == 0) {
+      APROF_STORE(10, 0); APROF_STORE(11, 1); APROF_STORE(12, 2); APROF_STORE(13, 3); APROF_STORE(14, 4); APROF_STORE(15, 5); APROF_STORE(16, 6);
+      APROF_TOTAL(17);
     }
   }
 
@@ -754,4 +817,12 @@ int bones_attn_bwd_split(const void* qk, const void* qkv, const void* dy, const 
   attn_bwd_dq_kernel<<<grid, 320, smem_dq, s>>>(tq, tv, td, p);
   return (int)cudaGetLastError();
 }
+
+#ifdef BONES_ATTN_PROF
+// measuring build: device buffer of 32 counters per CTA that the next dK / dV launches fill (null switches it off)
+void bones_attn_set_prof(void* buf) {
+  long long* b = (long long*)buf;
+  cudaMemcpyToSymbol(bones::g_attn_prof, &b, sizeof(b));
+}
+#endif
 }  // extern "C"

@@ -23,16 +23,20 @@ def _newer(a, b):
 
 
 LIB_DEBUG = os.path.join(LIB_DIR, "libbones_b200_dbg.so")
+LIB_MEASURE = os.path.join(LIB_DIR, "libbones_b200_prof.so")
+MEASURE_DEFINES = ("BONES_MX_PROF", "BONES_ATTN_PROF")
 
 
-def build(verbose: bool = False, force: bool = False, debug_bounds: bool = False) -> str:
+def build(verbose: bool = False, force: bool = False, debug_bounds: bool = False, measure: bool = False) -> str:
     """``debug_bounds``: the second library, compiled with ``-DBONES_DEBUG_BOUNDS`` (every data-dependent index is checked,
     a miss is counted and skipped; see ``csrc/common.cuh``), loaded instead of the release one when
-    ``BONES_DEBUG_BOUNDS=1``."""
+    ``BONES_DEBUG_BOUNDS=1``.  ``measure``: a third library whose tensor-core kernels account the clocks each of their
+    roles spends waiting and issuing (``-DBONES_MX_PROF -DBONES_ATTN_PROF``); ``ops.microbench mxroles / attnroles``
+    read it when ``BONES_LIB`` points at it.  Neither is needed to train."""
     os.makedirs(LIB_DIR, exist_ok=True)
-    objdir = os.path.join(LIB_DIR, "obj_dbg" if debug_bounds else "obj")
-    lib = LIB_DEBUG if debug_bounds else LIB
-    flags = FLAGS + (["-DBONES_DEBUG_BOUNDS"] if debug_bounds else [])
+    objdir = os.path.join(LIB_DIR, "obj_prof" if measure else "obj_dbg" if debug_bounds else "obj")
+    lib = LIB_MEASURE if measure else LIB_DEBUG if debug_bounds else LIB
+    flags = FLAGS + (["-DBONES_DEBUG_BOUNDS"] if debug_bounds else []) + ([f"-D{d}" for d in MEASURE_DEFINES] if measure else [])
     os.makedirs(objdir, exist_ok=True)
     srcs = sorted(f for f in os.listdir(HERE) if f.endswith(".cu"))
     hdrs = [os.path.join(HERE, f) for f in os.listdir(HERE) if f.endswith((".cuh", ".h"))]
@@ -72,3 +76,5 @@ def build(verbose: bool = False, force: bool = False, debug_bounds: bool = False
 if __name__ == "__main__":
     print(build(verbose="-v" in sys.argv, force="-f" in sys.argv))
     print(build(verbose="-v" in sys.argv, force="-f" in sys.argv, debug_bounds=True))
+    if "--measure" in sys.argv:
+        print(build(verbose="-v" in sys.argv, force="-f" in sys.argv, measure=True))

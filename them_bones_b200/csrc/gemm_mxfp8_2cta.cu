@@ -71,7 +71,7 @@ struct Mx2Params {
   int splits, atomic, wide;
   int sf_sets;                  // copies of the scale columns in TMEM that the K blocks rotate through (1, 2 or 4)
   int sf_warp;                  // 1: a warp of its own issues the scale copies, ahead of the MMA thread
-  int staged;                   // 1: bf16 / E4M3 outputs leave through shared memory and TMA stores
+  int staged;                   // 1: bf16 / E4M3 outputs are turned round through the staging tiles (five stages)
   long long* prof;              // BONES_MX_PROF builds only: 32 cycle counters per CTA (null otherwise)
 };
 
@@ -83,13 +83,21 @@ struct Mx2Params {
 //   8 scale copy: wait stage full  9 scale copy: wait columns free   10 scale copy: issue
 //   11 epilogue warp 3: wait accumulator full   12 epilogue warp 3: drain   13 epilogue warp 3: total   14 K blocks   15 tiles
 //   16 MMA: the MMA instructions and commits of a block
+//   epilogue warp 3, staged epilogue, per phase: 19 TMEM load  20 wait for the previous TMA store  21 auxiliary operand + maths + bf16 tile
+//   + copy along N  22 copy along M  23 fence + read-back + stores  24 chunks
 #ifdef BONES_MX_PROF
 #define QPROF_DECL(n) long long qp_[n] = {}; long long qp_t_ = clock64(); const long long qp_t0_ = qp_t_
 #define QPROF_ADD(i) do { const long long n_ = clock64(); qp_[i] += n_ - qp_t_; qp_t_ = n_; } while (0)
 #define QPROF_COUNT(i) (++qp_[i])
 #define QPROF_STORE(slot, i) do { if (p.prof) p.prof[(long long)blockIdx.x * 32 + (slot)] = qp_[i]; } while (0)
 #define QPROF_TOTAL(slot) do { if (p.prof) p.prof[(long long)blockIdx.x * 32 + (slot)] = clock64() - qp_t0_; } while (0)
+#define QEPI_ARG , long long* qe_, long long& qe_t_
+#define QEPI_PASS , qe_, qe_t_
+#define QEPI_ADD(i) do { const long long n_ = clock64(); qe_[i] += n_ - qe_t_; qe_t_ = n_; } while (0)
 #else
+#define QEPI_ARG
+#define QEPI_PASS
+#define QEPI_ADD(i)
 #define QPROF_DECL(n)
 #define QPROF_ADD(i)
 #define QPROF_COUNT(i)
@@ -214,61 +222,6 @@ __device__ __host__ __forceinline__ size_t q_sf_offset(long long r, long long k,
   return (size_t)(((g * kblocks + (k >> 7)) * chunks + (t >> 7)) * 512 + (t & 31) * 16 + ((t & 127) >> 5) * 4 + ((k & 127) >> 5));
 }
 
-// One warp, lane = row, v = the 32 values of columns [col0, col0 + 32) of that row.
-// Row copy: the thread's 32 values are one block; 32 bytes and one scale byte per thread.
-__device__ __forceinline__ void q_emit_row(const float (&v)[32], uint8_t* q_dst, uint8_t* sf_dst, bool ok) {
-  float amax = 0.f;
-#pragma unroll
-  for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(v[j]));
-  int biased;
-  const float inv = q_scale_pow2(amax, biased);
-  if (ok) {
-    uint32_t o[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) o[j] = q_pack_e4m3x4(v[4 * j] * inv, v[4 * j + 1] * inv, v[4 * j + 2] * inv, v[4 * j + 3] * inv);
-    *reinterpret_cast<uint4*>(q_dst) = make_uint4(o[0], o[1], o[2], o[3]);
-    *reinterpret_cast<uint4*>(q_dst + 16) = make_uint4(o[4], o[5], o[6], o[7]);
-    *sf_dst = (uint8_t)biased;
-  }
-}
-// Column copy: a block is one column over the warp's 32 rows.  `redux.sync.max` on the magnitudes' bit patterns hands every
-// lane the block maximum of column j; lane j keeps it, derives that column's scale once, and the 32 inverse scales are
-// passed round with one shuffle each.  Lane j also stores the scale byte of column j (`sf_dst` is its address).
-__device__ __forceinline__ void q_emit_col(const float (&v)[32], int lane, uint8_t* q_dst, uint8_t* sf_dst, bool ok, bool sf_ok) {
-  // every lane receives all 32 column maxima; it keeps the one of column `lane` by a binary selection tree on its lane bits
-  const bool b0 = lane & 1, b1 = lane & 2, b2 = lane & 4, b3 = lane & 8, b4 = lane & 16;
-  uint32_t l1[16];
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const uint32_t m0 = __reduce_max_sync(0xffffffffu, __float_as_uint(v[2 * i]) & 0x7fffffffu);
-    const uint32_t m1 = __reduce_max_sync(0xffffffffu, __float_as_uint(v[2 * i + 1]) & 0x7fffffffu);
-    l1[i] = b0 ? m1 : m0;
-  }
-  uint32_t l2[8], l3[4], l4[2];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) l2[i] = b1 ? l1[2 * i + 1] : l1[2 * i];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) l3[i] = b2 ? l2[2 * i + 1] : l2[2 * i];
-#pragma unroll
-  for (int i = 0; i < 2; ++i) l4[i] = b3 ? l3[2 * i + 1] : l3[2 * i];
-  const uint32_t mine = b4 ? l4[1] : l4[0];
-  int biased;
-  const float my_inv = q_scale_pow2(__uint_as_float(mine), biased);
-  uint32_t o[8];
-#pragma unroll
-  for (int j4 = 0; j4 < 8; ++j4) {
-    float s[4];
-#pragma unroll
-    for (int t = 0; t < 4; ++t) s[t] = v[j4 * 4 + t] * __shfl_sync(0xffffffffu, my_inv, j4 * 4 + t);
-    o[j4] = q_pack_e4m3x4(s[0], s[1], s[2], s[3]);
-  }
-  if (ok) {
-    *reinterpret_cast<uint4*>(q_dst) = make_uint4(o[0], o[1], o[2], o[3]);
-    *reinterpret_cast<uint4*>(q_dst + 16) = make_uint4(o[4], o[5], o[6], o[7]);
-  }
-  if (sf_ok) *sf_dst = (uint8_t)biased;
-}
-
 // scale-chunk offset with 32-bit arithmetic; `shift` >= 0 when the tile height is a power of two
 __device__ __forceinline__ uint32_t q_sf_offset32(uint32_t r, uint32_t k, uint32_t kblocks, int group, int shift) {
   const uint32_t g = shift >= 0 ? (r >> shift) : r / (uint32_t)group;
@@ -282,12 +235,20 @@ __device__ __forceinline__ int q_log2_or_neg(int v) { return (v & (v - 1)) == 0 
 // Staged epilogue.  A thread of an epilogue warp holds one row of the accumulator (TMEM lane = row), so a 16-byte store
 // per thread touches 32 different rows: 32 cache lines per instruction, and with the bf16 copy, the two quantised copies
 // and an auxiliary operand per 32 x 32 chunk the load/store path, not the arithmetic, took 17 000 clocks per 128 x 224
-// tile against 4 480 clocks of MMAs.  Here every chunk goes through the warp's own staging tiles in shared memory
-// (swizzled so that the row-per-thread accesses are conflict free) and leaves with one TMA store per copy; the auxiliary
-// operand comes in with coalesced loads (four threads per row) and is turned round through the same tile.  The block
-// maxima along M come from the staged bf16 tile read column-wise (16 conflict-free loads per thread and packed bf16 max)
-// instead of 32 `redux.sync` and a selection tree.
+// tile against 4 480 clocks of MMAs.  Here every chunk is turned round through the warp's own staging tiles in shared
+// memory (swizzled so that both the row-per-thread and the several-threads-per-row accesses are conflict free): it is
+// written row-per-thread, read back with four (bf16) or two (E4M3) threads per row and stored with whole row segments
+// per group of threads -- 8 or 16 rows per instruction instead of 32 rows of 16 bytes.  The auxiliary operand comes in
+// the same way round.  The block maxima along M come from the staged bf16 tile read column-wise (16 conflict-free loads
+// per thread and packed bf16 max) instead of 32 `redux.sync` and a selection tree.
+// Who stores what was settled by measurement.  With all three copies leaving as TMA stores, their 96 row requests per
+// chunk on top of the 240 per K block of the operand loads overran the TMA unit (producer issue time per K block
+// 600 -> 790 clocks, 153 us for the c_fc shape); with all three leaving through the load/store unit that pipe was 63 %
+// busy over the whole kernel and the epilogue took 10 000 clocks a tile (170 us).  So: a bf16 copy on its own leaves
+// through the load/store unit (102 us against 108); when quantised copies are written as well, the bf16 tile leaves as
+// one TMA store and the E4M3 tiles through the load/store unit.
 // ---------------------------------------------------------------------------------------------------------------
+// TMA store of a staged 32 x 32 bf16 tile (the bf16 copy when quantised copies are written too: see below)
 __device__ __forceinline__ void q_tma_store_3d(const CUtensorMap* m, uint32_t src, int c0, int c1, int c2) {
   asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];" ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src),
                "r"(c0), "r"(c1), "r"(c2)
@@ -295,6 +256,7 @@ __device__ __forceinline__ void q_tma_store_3d(const CUtensorMap* m, uint32_t sr
 }
 __device__ __forceinline__ void q_bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void q_bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void q_sts8(uint32_t a, uint32_t v) { asm volatile("st.shared.u8 [%0], %1;" ::"r"(a), "r"(v) : "memory"); }
 __device__ __forceinline__ void q_sts128(uint32_t a, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(a), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
 }
@@ -317,10 +279,10 @@ __device__ __forceinline__ uint32_t q_max_bf16x2(uint32_t a, uint32_t b) {
 
 // One epilogue warp's chunks of a tile: `stg` / `scratch` are the warp's staging tiles and scratch floats.
 template <int EPI, bool WQ, bool WT>
-__device__ __forceinline__ void q_staged_tile(const Mx2Params& p, const CUtensorMap* tm_d, const CUtensorMap* tm_q, const CUtensorMap* tm_t,
-                                              uint32_t taddr0, uint32_t stg, uint32_t scratch, int b, int row0, int ncol0, int lane, int sub,
-                                              int nchunks) {       // `sub`: the warp's first chunk of this tile (rotates from tile to tile)
+__device__ __forceinline__ void q_staged_tile(const Mx2Params& p, const CUtensorMap* tm_d, uint32_t taddr0, uint32_t stg, uint32_t scratch, int b, int row0, int ncol0, int lane, int sub,
+                                              int nchunks QEPI_ARG) {       // `sub`: the warp's first chunk of this tile (rotates from tile to tile)
   constexpr bool kNeedR = EPI == GE_BF16_RES || EPI == GE_MUL_2SQRT;
+  constexpr bool kDTma = WQ || WT;                          // the bf16 copy leaves as a TMA store
   if (row0 >= p.M) return;                                  // warp-uniform: the whole warp lies beyond M
   const int row = row0 + lane;
   const bool row_ok = row < p.M;
@@ -331,15 +293,28 @@ __device__ __forceinline__ void q_staged_tile(const Mx2Params& p, const CUtensor
   const uint32_t t_row = stg + QSTG_T + (uint32_t)lane * 32u;
   const int r_sub = lane >> 2, r_piece = lane & 3;          // coalesced loads of the auxiliary operand: four threads per row
   const __nv_bfloat16* Rb = reinterpret_cast<const __nv_bfloat16*>(p.R) + (long long)b * p.strideR;
+  __nv_bfloat16* Dbase = p.D ? reinterpret_cast<__nv_bfloat16*>(p.D) + (long long)b * p.strideD : nullptr;
   const uint32_t kblocks_n = (uint32_t)((p.N + 127) >> 7), kblocks_m = (uint32_t)((p.M + 127) >> 7);
   const int qshift = q_log2_or_neg(p.dq_group), tshift = q_log2_or_neg(p.dt_group);
   uint8_t* sfq = WQ ? p.Dsf + (size_t)b * p.dsf_batch + q_sf_offset32((uint32_t)row, 0u, kblocks_n, p.dq_group, qshift) : nullptr;
   const uint32_t sfq_step = (((uint32_t)p.dq_group + 127u) >> 7) * 512u;          // per 128 columns
   uint8_t* sft = WT ? p.Dtsf + (size_t)b * p.dtsf_batch : nullptr;
+  // staged bf16 tile, four threads per row: the address of this thread's piece in rows r_sub + 8 i
+  uint32_t t_in[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t rr = (uint32_t)(i * 8 + r_sub);
+    t_in[i] = stg + QSTG_D + rr * 64u + ((((uint32_t)r_piece) ^ ((rr >> 1) & 3u)) << 4);
+  }
 #pragma unroll 1
   for (int c = sub; c < nchunks; c += kEpiWarpsQ / 4) {
     const int col0 = ncol0 + c * 32;
     if (col0 >= p.N) break;                        // warp-uniform: the ragged last tile's columns beyond N
+    QEPI_ADD(4);
+    if (kDTma) {
+      if (elect_one()) q_bulk_wait_read();         // the store of the warp's previous bf16 tile has read the staging tile
+    }
+    QEPI_ADD(1);
     uint4 rin[4];
     if (kNeedR) {
 #pragma unroll
@@ -351,10 +326,10 @@ __device__ __forceinline__ void q_staged_tile(const Mx2Params& p, const CUtensor
     }
     uint32_t r[32];
     __syncwarp();
+    QEPI_ADD(2);
     BONES_TMEM_LD32(taddr0 + (uint32_t)(c * 32), r);
     tmem_ld_wait();
-    if (elect_one()) q_bulk_wait_read();           // the stores of the warp's previous chunk have read the staging tiles
-    __syncwarp();
+    QEPI_ADD(0);
     float v[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
@@ -408,50 +383,97 @@ __device__ __forceinline__ void q_staged_tile(const Mx2Params& p, const CUtensor
       for (int j = 0; j < 32; ++j) amax = fmaxf(amax, fabsf(v[j]));
       int biased;
       const float inv = q_scale_pow2(amax, biased);
-      uint32_t o[8];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] = q_pack_e4m3x4(v[4 * j] * inv, v[4 * j + 1] * inv, v[4 * j + 2] * inv, v[4 * j + 3] * inv);
-      q_sts128(q_row + ((0u ^ sw32) << 4), o[0], o[1], o[2], o[3]);
-      q_sts128(q_row + ((1u ^ sw32) << 4), o[4], o[5], o[6], o[7]);
+      for (int hh = 0; hh < 2; ++hh) {
+        uint32_t o[4];
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          const int j = hh * 4 + jj;
+          o[jj] = q_pack_e4m3x4(v[4 * j] * inv, v[4 * j + 1] * inv, v[4 * j + 2] * inv, v[4 * j + 3] * inv);
+        }
+        q_sts128(q_row + ((((uint32_t)hh) ^ sw32) << 4), o[0], o[1], o[2], o[3]);
+      }
       if (row_ok) sfq[(uint32_t)(col0 >> 7) * sfq_step + (uint32_t)((col0 & 127) >> 5)] = (uint8_t)biased;
     }
+    QEPI_ADD(2);
     if (WT) {
       __syncwarp();                                // the bf16 tile is complete
-      // along M: a block is one column over the warp's 32 rows (rows beyond M were zeroed).  Thread j reads the word of
-      // columns 2w, 2w + 1 (w = j % 16) in the 16 rows of parity j / 16.
-      const uint32_t w = (uint32_t)(lane & 15), par = (uint32_t)(lane >> 4);
-      uint32_t m2 = 0u;
+      // along M: a block is one column over the warp's 32 rows (rows beyond M were zeroed).  Four threads per row as in
+      // the read-back below: thread (r_sub, r_piece) reads the 8 columns of its piece in rows r_sub + 8 i, folds the four
+      // rows, and three shuffles fold the eight threads of the piece.
+      uint32_t cm[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        const uint32_t rr = 2u * (uint32_t)i + par;
-        const uint32_t x = q_lds32(stg + QSTG_D + rr * 64u + (((w >> 2) ^ ((uint32_t)i & 3u)) << 4) + (w & 3u) * 4u);
-        m2 = q_max_bf16x2(m2, x & 0x7fff7fffu);
+      for (int i = 0; i < 4; ++i) {
+        const uint4 u = q_lds128(t_in[i]);
+        cm[0] = q_max_bf16x2(cm[0], u.x & 0x7fff7fffu);
+        cm[1] = q_max_bf16x2(cm[1], u.y & 0x7fff7fffu);
+        cm[2] = q_max_bf16x2(cm[2], u.z & 0x7fff7fffu);
+        cm[3] = q_max_bf16x2(cm[3], u.w & 0x7fff7fffu);
       }
-      m2 = q_max_bf16x2(m2, __shfl_xor_sync(0xffffffffu, m2, 16));
-      const uint32_t mine2 = __shfl_sync(0xffffffffu, m2, lane >> 1);
-      const uint32_t mine = (lane & 1) ? (mine2 & 0xffff0000u) : (mine2 << 16);
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        cm[t] = q_max_bf16x2(cm[t], __shfl_xor_sync(0xffffffffu, cm[t], 4));
+        cm[t] = q_max_bf16x2(cm[t], __shfl_xor_sync(0xffffffffu, cm[t], 8));
+        cm[t] = q_max_bf16x2(cm[t], __shfl_xor_sync(0xffffffffu, cm[t], 16));
+      }
+      // thread (r_sub, r_piece) derives the scale of column r_piece * 8 + r_sub
+      const uint32_t pair = (r_sub & 4) ? ((r_sub & 2) ? cm[3] : cm[2]) : ((r_sub & 2) ? cm[1] : cm[0]);
       int biased;
-      const float my_inv = q_scale_pow2(__uint_as_float(mine), biased);
-      sft[q_sf_offset32((uint32_t)(col0 + lane), (uint32_t)row0, kblocks_m, p.dt_group, tshift)] = (uint8_t)biased;
-      q_sts32(scratch + (uint32_t)lane * 4u, __float_as_uint(my_inv));
+      const float my_inv = q_scale_pow2(__uint_as_float((r_sub & 1) ? (pair & 0xffff0000u) : (pair << 16)), biased);
+      sft[q_sf_offset32((uint32_t)(col0 + r_piece * 8 + r_sub), (uint32_t)row0, kblocks_m, p.dt_group, tshift)] = (uint8_t)biased;
+      q_sts32(scratch + (uint32_t)(r_piece * 8 + r_sub) * 4u, __float_as_uint(my_inv));
       __syncwarp();
-      uint32_t o[8];
 #pragma unroll
-      for (int j4 = 0; j4 < 8; ++j4) {
-        const uint4 sc = q_lds128(scratch + (uint32_t)j4 * 16u);
-        o[j4] = q_pack_e4m3x4(v[j4 * 4] * __uint_as_float(sc.x), v[j4 * 4 + 1] * __uint_as_float(sc.y), v[j4 * 4 + 2] * __uint_as_float(sc.z),
-                              v[j4 * 4 + 3] * __uint_as_float(sc.w));
+      for (int hh = 0; hh < 2; ++hh) {             // 16 columns = one 16-byte piece of the staged row at a time
+        uint32_t o[4];
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          const int j4 = hh * 4 + jj;
+          const uint4 sc = q_lds128(scratch + (uint32_t)j4 * 16u);      // four columns' inverse scales, the same on every lane
+          o[jj] = q_pack_e4m3x4(v[j4 * 4] * __uint_as_float(sc.x), v[j4 * 4 + 1] * __uint_as_float(sc.y), v[j4 * 4 + 2] * __uint_as_float(sc.z),
+                                v[j4 * 4 + 3] * __uint_as_float(sc.w));
+        }
+        q_sts128(t_row + ((((uint32_t)hh) ^ sw32) << 4), o[0], o[1], o[2], o[3]);
       }
-      q_sts128(t_row + ((0u ^ sw32) << 4), o[0], o[1], o[2], o[3]);
-      q_sts128(t_row + ((1u ^ sw32) << 4), o[4], o[5], o[6], o[7]);
     }
-    fence_proxy_async_smem();
+    QEPI_ADD(3);
+    if (kDTma && Dbase != nullptr) fence_proxy_async_smem();
     __syncwarp();
-    if (elect_one()) {
-      if (p.D != nullptr) q_tma_store_3d(tm_d, stg + QSTG_D, col0, row0, b);
-      if (WQ) q_tma_store_3d(tm_q, stg + QSTG_Q, col0, row0, b);
-      if (WT) q_tma_store_3d(tm_t, stg + QSTG_T, col0, row0, b);
-      q_bulk_commit();
+    // out: whole row segments per group of threads
+    if (kDTma) {
+      if (Dbase != nullptr && elect_one()) {
+        q_tma_store_3d(tm_d, stg + QSTG_D, col0, row0, b);
+        q_bulk_commit();
+      }
+    } else if (Dbase != nullptr) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t rr = (uint32_t)(i * 8 + r_sub);
+        const uint4 u = q_lds128(stg + QSTG_D + rr * 64u + ((((uint32_t)r_piece) ^ ((rr >> 1) & 3u)) << 4));
+        const int grow = row0 + (int)rr, cc = col0 + r_piece * 8;
+        if (grow < p.M) {
+          __nv_bfloat16* dst = Dbase + (long long)grow * p.ldd + cc;
+          if (cc + 8 <= p.N) {
+            *reinterpret_cast<uint4*>(dst) = u;
+          } else if (cc < p.N) {                     // ragged N: the last piece element by element
+            const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+            for (int e = 0; e < p.N - cc; ++e) reinterpret_cast<uint16_t*>(dst)[e] = (uint16_t)(w4[e >> 1] >> ((e & 1) * 16));
+          }
+        }
+      }
+    }
+    if (WQ || WT) {
+      const int h_sub = lane >> 1, h_piece = lane & 1;       // two threads per 32-byte row
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const uint32_t rr = (uint32_t)(i * 16 + h_sub);
+        const uint32_t off = rr * 32u + ((((uint32_t)h_piece) ^ ((rr >> 2) & 1u)) << 4);
+        const long long g = ((long long)b * p.M + row0 + (int)rr) * p.N + col0 + h_piece * 16;
+        if (row0 + (int)rr < p.M) {
+          if (WQ) *reinterpret_cast<uint4*>(p.Dq + g) = q_lds128(stg + QSTG_Q + off);
+          if (WT) *reinterpret_cast<uint4*>(p.Dt + g) = q_lds128(stg + QSTG_T + off);
+        }
+      }
     }
   }
 }
@@ -461,8 +483,7 @@ template <int kEpiWarps>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(96 + 32 * kEpiWarps, 1)
 gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                        const __grid_constant__ CUtensorMap tma_sfa, const __grid_constant__ CUtensorMap tma_sfb,
-                       const __grid_constant__ CUtensorMap tma_d, const __grid_constant__ CUtensorMap tma_dq,
-                       const __grid_constant__ CUtensorMap tma_dt, const Mx2Params p) {
+                       const __grid_constant__ CUtensorMap tma_d, const Mx2Params p) {
   static_assert(kEpiWarps == kEpiWarpsQ, "the staging tiles are laid out for twelve epilogue warps");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
@@ -504,11 +525,6 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
     tma_prefetch_desc(&tma_b);
     tma_prefetch_desc(&tma_sfa);
     tma_prefetch_desc(&tma_sfb);
-    if (p.staged) {
-      tma_prefetch_desc(&tma_d);
-      tma_prefetch_desc(&tma_dq);
-      tma_prefetch_desc(&tma_dt);
-    }
   }
   q_cluster_sync();
   if (warp == 1) {
@@ -683,6 +699,10 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
     int acc = 0, tile_iter = 0;
     uint32_t acc_phase = 0;
     QPROF_DECL(2);
+#ifdef BONES_MX_PROF
+    long long qe_[5] = {};
+    long long qe_t_ = clock64();
+#endif
     for (int tile = cluster_id; tile < total; tile += n_clusters) {
       int b, mb, nb;
       decode_tile_q(tile % base_tiles, p.tiles_m, p.tiles_n, b, mb, nb);
@@ -717,7 +737,10 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
                            reinterpret_cast<const uint8_t*>(p.R) + (rrow + col0) * esz, false, nopre, min(32, p.N - col0));
         }
       } else {
-#define BONES_Q_TILE(E, WQ, WT) q_staged_tile<E, WQ, WT>(p, &tma_d, &tma_dq, &tma_dt, taddr0, stg, scratch, b, row0, nb * bn, lane, first, nchunks)
+#ifdef BONES_MX_PROF
+        qe_t_ = clock64();
+#endif
+#define BONES_Q_TILE(E, WQ, WT) q_staged_tile<E, WQ, WT>(p, &tma_d, taddr0, stg, scratch, b, row0, nb * bn, lane, first, nchunks QEPI_PASS)
 #define BONES_Q_EPI(WQ, WT)                                         \
   switch (p.epi) {                                                  \
     case GE_BF16_RES: BONES_Q_TILE(GE_BF16_RES, WQ, WT); break;     \
@@ -738,9 +761,14 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
       if (++acc == p.acc_stages) { acc = 0; acc_phase ^= 1u; }
     }
     __syncwarp();
-    if (p.staged && elect_one()) q_bulk_wait_read();          // the last stores have read the staging tiles
+    if (p.staged && elect_one()) q_bulk_wait_read();          // the last TMA store has read its staging tile
     QPROF_ADD(1);
-    if (warp == 3 && lane == 0) { QPROF_STORE(11, 0); QPROF_STORE(12, 1); QPROF_TOTAL(13); }
+    if (warp == 3 && lane == 0) {
+      QPROF_STORE(11, 0); QPROF_STORE(12, 1); QPROF_TOTAL(13);
+#ifdef BONES_MX_PROF
+      if (p.prof) for (int i = 0; i < 5; ++i) p.prof[(long long)blockIdx.x * 32 + 19 + i] = qe_[i];
+#endif
+    }
   }
 
   // tear-down: both CTAs of the pair always arrive here (every wait above is bounded)
@@ -762,40 +790,97 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
 // consecutive columns at a time (64 contiguous bytes: two full sectors), two such chunks per warp.
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int kQuantChunks = 2;                    // 32-column chunks per warp (64 columns)
+__device__ __forceinline__ uint2 q_pack_e4m3x8(const float (&f)[8], float inv) {
+  return make_uint2(q_pack_e4m3x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv), q_pack_e4m3x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv));
+}
 __global__ void __launch_bounds__(256, 2)
 mx_quant_dual_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t* __restrict__ qr, uint8_t* __restrict__ sfr, int group_r,
                      uint8_t* __restrict__ qc, uint8_t* __restrict__ sfc, int group_c, long long R, long long C) {
-  const int lane = threadIdx.x & 31;
+  // A warp takes 32 rows x 64 columns, 32 x 32 at a time, four threads per row: thread (sub = lane / 4, piece = lane % 4)
+  // holds the 8 values of columns piece * 8 .. + 7 in rows sub, sub + 8, sub + 16, sub + 24.  Every load and store
+  // instruction then covers 8 whole row segments (with a thread per row it touches 32 cache lines and the kernel was
+  // bound by the load/store unit at 40 % of the copy bandwidth), a row block's maximum needs two shuffles among the four
+  // threads of the row and a column block's maximum three among the eight threads of the column group.
+  const int lane = threadIdx.x & 31, sub = lane >> 2, piece = lane & 3;
   const long long tiles_c = C / (32 * kQuantChunks);
   const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const long long tr = wid / tiles_c, tc = wid - tr * tiles_c;
-  const long long row0 = tr * 32, row = row0 + lane;
+  const long long row0 = tr * 32;
   if (row0 >= R) return;                                        // warp-uniform
-  const bool row_ok = row < R;
   const long long kb_c = (C + 127) >> 7, kb_r = (R + 127) >> 7;
   uint4 raw[kQuantChunks][4];
 #pragma unroll
   for (int c = 0; c < kQuantChunks; ++c) {
-    const __nv_bfloat16* src = x + row * ldx + (tc * kQuantChunks + c) * 32;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) raw[c][j] = row_ok ? *reinterpret_cast<const uint4*>(src + j * 8) : make_uint4(0u, 0u, 0u, 0u);
+    for (int i = 0; i < 4; ++i) {
+      const long long row = row0 + i * 8 + sub;
+      raw[c][i] = row < R ? *reinterpret_cast<const uint4*>(x + row * ldx + (tc * kQuantChunks + c) * 32 + piece * 8) : make_uint4(0u, 0u, 0u, 0u);
+    }
   }
 #pragma unroll
   for (int c = 0; c < kQuantChunks; ++c) {
     const long long col0 = (tc * kQuantChunks + c) * 32;
-    float v[32];
+    uint32_t cm[4] = {0u, 0u, 0u, 0u};                           // packed bf16 maxima of this thread's 8 columns over its 4 rows
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const uint32_t w[4] = {raw[c][j].x, raw[c][j].y, raw[c][j].z, raw[c][j].w};
+    for (int i = 0; i < 4; ++i) {
+      const long long row = row0 + i * 8 + sub;
+      const uint32_t w[4] = {raw[c][i].x, raw[c][i].y, raw[c][i].z, raw[c][i].w};
+      uint32_t a[4];
 #pragma unroll
       for (int t = 0; t < 4; ++t) {
-        const float2 f = unpack_bf16(w[t]);
-        v[j * 8 + 2 * t] = f.x;
-        v[j * 8 + 2 * t + 1] = f.y;
+        a[t] = w[t] & 0x7fff7fffu;
+        cm[t] = q_max_bf16x2(cm[t], a[t]);
+      }
+      if (qr != nullptr) {
+        const uint32_t m2 = q_max_bf16x2(q_max_bf16x2(a[0], a[1]), q_max_bf16x2(a[2], a[3]));
+        float amax = fmaxf(__uint_as_float(m2 << 16), __uint_as_float(m2 & 0xffff0000u));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        int biased;
+        const float inv = q_scale_pow2(amax, biased);
+        float f[8];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float2 u = unpack_bf16(w[t]);
+          f[2 * t] = u.x;
+          f[2 * t + 1] = u.y;
+        }
+        if (row < R) {
+          *reinterpret_cast<uint2*>(qr + row * C + col0 + piece * 8) = q_pack_e4m3x8(f, inv);
+          if (piece == 0) sfr[q_sf_offset(row, col0, kb_c, group_r)] = (uint8_t)biased;
+        }
       }
     }
-    if (qr != nullptr) q_emit_row(v, qr + row * C + col0, sfr + q_sf_offset(row, col0, kb_c, group_r), row_ok);
-    if (qc != nullptr) q_emit_col(v, lane, qc + row * C + col0, sfc + q_sf_offset(col0 + lane, row0, kb_r, group_c), row_ok, true);
+    if (qc != nullptr) {
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        cm[t] = q_max_bf16x2(cm[t], __shfl_xor_sync(0xffffffffu, cm[t], 4));
+        cm[t] = q_max_bf16x2(cm[t], __shfl_xor_sync(0xffffffffu, cm[t], 8));
+        cm[t] = q_max_bf16x2(cm[t], __shfl_xor_sync(0xffffffffu, cm[t], 16));
+      }
+      // thread (sub, piece) derives the scale of column piece * 8 + sub and hands it to the eight threads of its group
+      const uint32_t pair = (sub & 4) ? ((sub & 2) ? cm[3] : cm[2]) : ((sub & 2) ? cm[1] : cm[0]);
+      const float my_amax = __uint_as_float((sub & 1) ? (pair & 0xffff0000u) : (pair << 16));
+      int biased;
+      const float my_inv = q_scale_pow2(my_amax, biased);
+      sfc[q_sf_offset(col0 + piece * 8 + sub, row0, kb_r, group_c)] = (uint8_t)biased;
+      float inv[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) inv[e] = __shfl_sync(0xffffffffu, my_inv, (e << 2) | piece);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const long long row = row0 + i * 8 + sub;
+        const uint32_t w[4] = {raw[c][i].x, raw[c][i].y, raw[c][i].z, raw[c][i].w};
+        float f[8];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          const float2 u = unpack_bf16(w[t]);
+          f[2 * t] = u.x * inv[2 * t];
+          f[2 * t + 1] = u.y * inv[2 * t + 1];
+        }
+        if (row < R) *reinterpret_cast<uint2*>(qc + row * C + col0 + piece * 8) = q_pack_e4m3x8(f, 1.0f);
+      }
+    }
   }
 }
 
@@ -817,14 +902,13 @@ static int tmap_operand_q(CUtensorMap* out, const void* ptr, int major, long lon
   return make_tmap(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, ptr, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
-// output [batch, M, N] with `esz`-byte elements, row pitch `ld` and batch pitch `stride` (in elements), stored in boxes
-// of 32 x 32 from the epilogue's staging tiles (64-byte swizzle for bf16 rows of 64 bytes, 32-byte for E4M3)
-static int tmap_out_q(CUtensorMap* out, const void* ptr, int esz, long long M, long long N, long long ld, long long stride, int batch) {
+// bf16 result [batch, M, N], row pitch `ld` and batch pitch `stride` in elements, stored in boxes of 32 x 32 from the
+// epilogue's staging tiles (rows of 64 bytes, 64-byte swizzle)
+static int tmap_out_q(CUtensorMap* out, const void* ptr, long long M, long long N, long long ld, long long stride, int batch) {
   uint64_t dims[3] = {(uint64_t)N, (uint64_t)M, (uint64_t)batch};
-  uint64_t strides[2] = {(uint64_t)(ld * esz), (uint64_t)((batch > 1 ? stride : ld * M) * esz)};
+  uint64_t strides[2] = {(uint64_t)(ld * 2), (uint64_t)((batch > 1 ? stride : ld * M) * 2)};
   uint32_t box[3] = {32, 32, 1};
-  return make_tmap(out, esz == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, ptr, dims, strides, box,
-                   esz == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+  return make_tmap(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, ptr, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B);
 }
 
 // scale chunks seen as rows of 256 bytes; a box of `box_rows` rows is one K block's scales of one tile
@@ -933,19 +1017,18 @@ int bones_gemm_mxfp8_pair(const void* Aq, const void* sfa, const void* Bq, const
   if (rc) return rc;
   rc = tmap_scales_q(&tsb, sfb, sfb_bytes * batch, 4);
   if (rc) return rc;
-  // bf16 / E4M3 results leave through shared memory and TMA stores when their pitches allow it (16-byte multiples)
+  // bf16 / E4M3 results are turned round through shared memory when their pitches allow 16-byte accesses
   const bool d_tma = !D || ((ldd % 8 == 0) && (strideD % 8 == 0) && (((uintptr_t)D & 15) == 0));
   const bool r_vec = !R || ((ldr % 8 == 0) && (strideR % 8 == 0) && (((uintptr_t)R & 15) == 0));
   // short contractions and quantised copies: the epilogue is the larger part of a tile and gets the staging tiles (at
   // the price of the sixth stage); long contractions keep six stages and store from registers
   p.staged = (!f32out && d_tma && r_vec && (Dq || Dt || K <= 2560)) ? 1 : 0;
   if (!p.staged && (Dq || Dt)) return -7;
-  CUtensorMap td, tdq, tdt;
-  memset(&td, 0, sizeof(td)); memset(&tdq, 0, sizeof(tdq)); memset(&tdt, 0, sizeof(tdt));
-  if (p.staged) {
-    if (D) { rc = tmap_out_q(&td, D, 2, M, N, ldd, strideD, batch); if (rc) return rc; }
-    if (Dq) { rc = tmap_out_q(&tdq, Dq, 1, M, N, N, (long long)M * N, batch); if (rc) return rc; }
-    if (Dt) { rc = tmap_out_q(&tdt, Dt, 1, M, N, N, (long long)M * N, batch); if (rc) return rc; }
+  CUtensorMap td;
+  memset(&td, 0, sizeof(td));
+  if (p.staged && D && (Dq || Dt)) {
+    rc = tmap_out_q(&td, D, M, N, ldd, strideD, batch);
+    if (rc) return rc;
   }
   constexpr size_t smem = QSMEM_BYTES;
   static bool attr_set = false;
@@ -976,7 +1059,7 @@ int bones_gemm_mxfp8_pair(const void* Aq, const void* sfa, const void* Bq, const
   if (p.splits > KB) p.splits = KB;
   const int total = base_tiles * p.splits;
   const int clusters = total < pairs ? total : pairs;
-  gemm_mxfp8_pair_kernel<kEpiWarpsQ><<<2 * clusters, 96 + 32 * kEpiWarpsQ, smem, reinterpret_cast<cudaStream_t>(stream)>>>(ta, tb, tsa, tsb, td, tdq, tdt, p);
+  gemm_mxfp8_pair_kernel<kEpiWarpsQ><<<2 * clusters, 96 + 32 * kEpiWarpsQ, smem, reinterpret_cast<cudaStream_t>(stream)>>>(ta, tb, tsa, tsb, td, p);
   return (int)cudaGetLastError();
 }
 

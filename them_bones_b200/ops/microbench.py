@@ -7,6 +7,12 @@
     python -m them_bones_b200.ops.microbench attn_bwd --b 4 --t 2048 --h 10
     python -m them_bones_b200.ops.microbench norm --rows 65536 --cols 1280
     python -m them_bones_b200.ops.microbench ce --rows 4096 --vocab 65536
+    BONES_LIB=them_bones_b200/lib/libbones_b200_prof.so python -m them_bones_b200.ops.microbench mxroles --m 16384 --n 5120 --k 1280 [--epi ...]
+    BONES_LIB=them_bones_b200/lib/libbones_b200_prof.so python -m them_bones_b200.ops.microbench attnroles --b 16 --t 2048 --h 10
+
+``mxroles`` / ``attnroles`` need the measuring build of the library (``python -m them_bones_b200.csrc.build --measure``):
+they print, per K block or per tile, the clocks each role of the kernel (TMA producer, MMA warp, scale-copy warp,
+epilogue / compute warps) spent in each of its waits and in issuing, averaged over the CTAs.
 
 Timing: CUDA events on the launching stream, ``--warmup`` untimed iterations, an L2 flush (a 256 MiB write) between
 timed iterations, mean over ``--iters``.  Fractions are against the measured peaks in ``MEASURED_PEAKS.json`` at the
@@ -53,9 +59,92 @@ def timeit(fn, iters, warmup, flush):
     return total / iters
 
 
+def roles(a):
+    """Role cycle accounting from the measuring build (see the module docstring)."""
+    import ctypes
+    lib = L.load()
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    prof = torch.zeros(sms * 32, dtype=torch.int64, device="cuda")
+    bf = torch.bfloat16
+    if a.what == "mxroles":
+        from . import mxfp8 as MX
+        if not hasattr(lib, "bones_mx2_set_prof"):
+            raise SystemExit("mxroles needs the measuring build: python -m them_bones_b200.csrc.build --measure, then BONES_LIB=...")
+        m, n, k = a.m, a.n, a.k
+        if a.layout == "tn":
+            _, _, aq, asf = MX.quant2(torch.randn(k, m, device="cuda", dtype=bf), row=False, col=True, group_c=128)
+            _, _, bq, bsf = MX.quant2(torch.randn(k, n, device="cuda", dtype=bf), row=False, col=True, group_c=MX.BN_WGRAD)
+            d = torch.zeros(m, n, device="cuda")
+            fn = lambda: MX.gemm2(aq, asf, bq, bsf, m, n, k, a_major=1, b_major=1, epi=MX.GE_ACC_F32, out=d, bn=MX.BN_WGRAD)  # noqa: E731
+        else:
+            bn = a.bn or MX.BN_FWD
+            aq, asf, _, _ = MX.quant2(torch.randn(m, k, device="cuda", dtype=bf))
+            bq, bsf, _, _ = MX.quant2(torch.randn(n, k, device="cuda", dtype=bf), group_r=bn)
+            epi = MX.GE_BF16 if a.epi == "plain" else MX.GE_RELU2
+            wq, wt = a.epi in ("relu2q", "relu2qt"), a.epi == "relu2qt"
+            fn = lambda: MX.gemm2(aq, asf, bq, bsf, m, n, k, bn=bn, epi=epi, want_q=wq, want_t=wt, dt_group=256)  # noqa: E731
+        ms = timeit(fn, a.iters, a.warmup, not a.no_flush)
+        lib.bones_mx2_set_prof(ctypes.c_void_p(prof.data_ptr()))
+        fn()
+        torch.cuda.synchronize()
+        lib.bones_mx2_set_prof(ctypes.c_void_p(0))
+        pr = prof.view(sms, 32).double()
+        lead, peer = pr[0::2].mean(0), pr[1::2].mean(0)
+        kb, tiles = float(lead[14]), float(lead[15])
+        per = lambda v, d: round(float(v) / max(d, 1.0))  # noqa: E731
+        out = {"what": a.what, "shape": [m, n, k], "layout": a.layout, "epi": a.epi, "ms": ms, "tflops": 2.0 * m * n * k / ms / 1e9,
+               "k_blocks_per_cta": kb, "tiles_per_cta": tiles,
+               "mma_warp_clocks_per_k_block": {"total": per(lead[4], kb), "wait_stage": per(lead[1], kb), "wait_scales": per(lead[2], kb),
+                                               "issue": per(lead[16], kb), "loop": per(lead[3], kb), "wait_accumulator": per(lead[0], kb)},
+               "producer_clocks_per_k_block": {"wait_empty": per(lead[5], kb), "issue": per(lead[6], kb), "peer_wait_empty": per(peer[5], kb),
+                                               "peer_issue": per(peer[6], kb)},
+               "scale_copy_clocks_per_k_block": {"wait_stage": per(lead[8], kb), "wait_columns": per(lead[9], kb), "issue": per(lead[10], kb)},
+               "epilogue_warp_clocks_per_tile": {"wait_accumulator": per(lead[11], tiles), "drain": per(lead[12], tiles),
+                                                 "tmem_load": per(lead[19], tiles), "wait_tma_store": per(lead[20], tiles),
+                                                 "maths_and_copy_along_n": per(lead[21], tiles), "copy_along_m": per(lead[22], tiles),
+                                                 "read_back_and_stores": per(lead[23], tiles)}}
+    else:
+        from . import attention_native as AN
+        from ..ref import functional as RF
+        if not hasattr(lib, "bones_attn_set_prof"):
+            raise SystemExit("attnroles needs the measuring build: python -m them_bones_b200.csrc.build --measure, then BONES_LIB=...")
+        I, LL, F = ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+        b, t, h, d = a.b, a.t, a.h, 128
+        ad, m = h * d, b * t
+        qkv = torch.randn(m, 3 * ad, device="cuda", dtype=bf)
+        cos, sin = RF.rotary_tables(t, d, 10000.0, device="cuda")
+        scale = 1.0 / math.sqrt(d)
+        qk = AN.rope_qknorm(qkv, cos, sin, t, h, d)
+        y, lse = AN.attn_forward(qk, qkv, None, b, t, h, scale, 0)
+        dy = torch.randn(m, ad, device="cuda", dtype=bf)
+        stats = torch.empty(b, h, t, 2, dtype=torch.float32, device="cuda")
+        dqk = torch.empty(m, 2 * ad, dtype=bf, device="cuda")
+        dqkv = torch.empty(m, 3 * ad, dtype=bf, device="cuda")
+        dv = dqkv[:, 2 * ad:]
+        L.call("bones_attn_bwd_stats", L.ptr(dy), L.ptr(y), L.ptr(lse), L.ptr(stats), LL(m), I(t), I(h), L.stream())
+        fn = lambda: L.call("bones_attn_bwd_split", L.ptr(qk), L.ptr(qkv), L.ptr(dy), L.ptr(stats), L.ptr(dqk), L.ptr(dv), LL(3 * ad),  # noqa: E731
+                            L.ptr(None), I(b), I(t), I(h), F(scale), I(0), L.stream())
+        ms = timeit(fn, a.iters, a.warmup, not a.no_flush)
+        lib.bones_attn_set_prof(ctypes.c_void_p(prof.data_ptr()))
+        fn()
+        torch.cuda.synchronize()
+        lib.bones_attn_set_prof(ctypes.c_void_p(0))
+        pr = prof.view(sms, 32).double().mean(0)
+        tiles = float(pr[8])
+        per = lambda v: round(float(v) / max(tiles, 1.0))  # noqa: E731
+        out = {"what": a.what, "shape": [b, t, h, d], "ms_both_kernels": ms, "dkv_tiles_per_cta": tiles,
+               "dkv_mma_warp_clocks_per_tile": {"total": per(pr[7]), "wait_item_kv": per(pr[0]), "wait_q": per(pr[1]), "wait_do": per(pr[2]),
+                                                "wait_p_ready": per(pr[3]), "wait_acc_free": per(pr[4]), "wait_ds_ready": per(pr[5]),
+                                                "issue": per(pr[6])},
+               "dkv_compute_warp_clocks_per_tile": {"total": per(pr[17]), "wait_stats": per(pr[10]), "wait_s": per(pr[11]), "p": per(pr[12]),
+                                                    "wait_dp": per(pr[13]), "ds": per(pr[14]), "wait_done": per(pr[15]), "drain": per(pr[16])},
+               "dkv_producer_clocks_per_tile": {"waits": per(pr[20]), "issue": per(pr[21])}}
+    print(json.dumps(out))
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "mxgemm", "mxquant", "attn_fwd", "attn_bwd", "norm", "ce"])
+    ap.add_argument("what", choices=["gemm", "mxgemm", "mxquant", "attn_fwd", "attn_bwd", "norm", "ce", "mxroles", "attnroles"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -78,6 +167,8 @@ def main():
     bf = torch.bfloat16
     out = {"what": a.what, "peaks": src}
     torch.manual_seed(0)
+    if a.what in ("mxroles", "attnroles"):
+        return roles(a)
     if a.what == "gemm":
         m, n, k = a.m, a.n, a.k
         if a.layout == "nt":
