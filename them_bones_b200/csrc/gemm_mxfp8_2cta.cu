@@ -479,7 +479,9 @@ __device__ __forceinline__ void q_staged_tile(const Mx2Params& p, const CUtensor
 }
 
 
-template <int kEpiWarps>
+// kVariant: which quantised copies the epilogue writes (bit 0 along N, bit 1 along M).  One kernel per variant: with all
+// sixteen (epilogue, variant) bodies inlined behind one switch the register allocator spilled inside the chunk loop.
+template <int kEpiWarps, int kVariant>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(96 + 32 * kEpiWarps, 1)
 gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b,
                        const __grid_constant__ CUtensorMap tma_sfa, const __grid_constant__ CUtensorMap tma_sfb,
@@ -693,7 +695,6 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
     const int q = warp & 3, sub = (warp - 3) >> 2;
     const int nchunks = bn >> 5;
     const bool f32out = p.epi == GE_ACC_F32;
-    const int variant = (p.Dq != nullptr ? 1 : 0) | (p.Dt != nullptr ? 2 : 0);
     const uint32_t stg = base + QSTG_BASE + (uint32_t)(warp - 3) * QSTG_BYTES;
     const uint32_t scratch = base + QSCRATCH_BASE + (uint32_t)(warp - 3) * QSTG_SCRATCH;
     int acc = 0, tile_iter = 0;
@@ -748,10 +749,7 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
     case GE_MUL_2SQRT: BONES_Q_TILE(GE_MUL_2SQRT, WQ, WT); break;   \
     default: BONES_Q_TILE(GE_BF16, WQ, WT); break;                  \
   }
-        if (variant == 0) { BONES_Q_EPI(false, false) }
-        else if (variant == 1) { BONES_Q_EPI(true, false) }
-        else if (variant == 2) { BONES_Q_EPI(false, true) }
-        else { BONES_Q_EPI(true, true) }
+        BONES_Q_EPI((kVariant & 1) != 0, (kVariant & 2) != 0)
 #undef BONES_Q_EPI
 #undef BONES_Q_TILE
       }
@@ -1033,7 +1031,10 @@ int bones_gemm_mxfp8_pair(const void* Aq, const void* sfa, const void* Bq, const
   constexpr size_t smem = QSMEM_BYTES;
   static bool attr_set = false;
   if (!attr_set) {
-    BONES_CHECK(cudaFuncSetAttribute(gemm_mxfp8_pair_kernel<kEpiWarpsQ>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    BONES_CHECK(cudaFuncSetAttribute(gemm_mxfp8_pair_kernel<kEpiWarpsQ, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    BONES_CHECK(cudaFuncSetAttribute(gemm_mxfp8_pair_kernel<kEpiWarpsQ, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    BONES_CHECK(cudaFuncSetAttribute(gemm_mxfp8_pair_kernel<kEpiWarpsQ, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    BONES_CHECK(cudaFuncSetAttribute(gemm_mxfp8_pair_kernel<kEpiWarpsQ, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     attr_set = true;
   }
   int dev = 0, sms = 0;
@@ -1059,7 +1060,15 @@ int bones_gemm_mxfp8_pair(const void* Aq, const void* sfa, const void* Bq, const
   if (p.splits > KB) p.splits = KB;
   const int total = base_tiles * p.splits;
   const int clusters = total < pairs ? total : pairs;
-  gemm_mxfp8_pair_kernel<kEpiWarpsQ><<<2 * clusters, 96 + 32 * kEpiWarpsQ, smem, reinterpret_cast<cudaStream_t>(stream)>>>(ta, tb, tsa, tsb, td, p);
+  const int variant = (Dq != nullptr ? 1 : 0) | (Dt != nullptr ? 2 : 0);
+  const dim3 grid(2 * clusters), block(96 + 32 * kEpiWarpsQ);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  switch (variant) {
+    case 0: gemm_mxfp8_pair_kernel<kEpiWarpsQ, 0><<<grid, block, smem, st>>>(ta, tb, tsa, tsb, td, p); break;
+    case 1: gemm_mxfp8_pair_kernel<kEpiWarpsQ, 1><<<grid, block, smem, st>>>(ta, tb, tsa, tsb, td, p); break;
+    case 2: gemm_mxfp8_pair_kernel<kEpiWarpsQ, 2><<<grid, block, smem, st>>>(ta, tb, tsa, tsb, td, p); break;
+    default: gemm_mxfp8_pair_kernel<kEpiWarpsQ, 3><<<grid, block, smem, st>>>(ta, tb, tsa, tsb, td, p); break;
+  }
   return (int)cudaGetLastError();
 }
 
