@@ -329,3 +329,19 @@ def test_library_ops_have_fake_and_autograd_registrations():
         x = torch.empty(8, 1280, dtype=torch.bfloat16, requires_grad=True)
         z = R.rms_norm(x)
         assert z.shape == x.shape and torch.autograd.grad(z.sum(), x)[0].shape == x.shape
+
+
+def test_muon_placement_balances_newton_schulz_work():
+    """Every rank's share of the orthogonalisation work with the planned placement against the plain ceil split."""
+    from them_bones_b200.optim.lean import plan_muon_counts
+    shapes = [(20, 3840, 1280), (20, 1280, 1280), (20, 5120, 1280), (20, 1280, 5120)]
+    cost = [max(r, c) * min(r, c) ** 2 for _, r, c in shapes]
+    counts = plan_muon_counts(shapes, 8)
+    for (n, _, _), c in zip(shapes, counts):
+        assert sum(c) == n and max(c) - min(c) <= 1
+    load = [sum(counts[g][r] * cost[g] for g in range(4)) for r in range(8)]
+    naive = [sum(min(3, max(0, 20 - r * 3)) * cost[g] for g in range(4)) for r in range(8)]
+    assert max(load) < 0.87 * max(naive)                 # 10 matrices on the busiest rank instead of 12
+    assert max(load) - min(load) <= max(cost)
+    assert plan_muon_counts([(4, 64, 64)], 1) == [[4]]
+    assert plan_muon_counts([(3, 64, 32)], 4) == [[1, 1, 1, 0]]

@@ -494,10 +494,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
       if (p_first && p_item >= 2 && !dead)
         dead = !mbar_wait(o_free(ob), (uint32_t)(((p_item - 2) >> 1) & 1), abort_flag, p.err, ERR_WAIT_TMEM_EMPTY);
       tc_fence_after();
+      const uint64_t vdesc0 = umma_smem_desc(sV(vs), ATOM_BYTES, 1024, kLayoutSw128);     // + a compile-time step per UMMA_K
       if (elect_one() && !dead) {
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          const uint64_t bd = umma_smem_desc(sV(vs) + k * 2048, ATOM_BYTES, 1024, kLayoutSw128);
+          const uint64_t bd = vdesc0 + (uint64_t)((k * 2048) >> 4);
           umma_f16_ts(tO(ob), tS(sb) + (uint32_t)((k & 3) * 8 + (k >> 2) * 64), bd, idesc_o, (p_first && k == 0) ? 0u : 1u);
         }
         tc_commit(v_free(vs));
@@ -520,12 +521,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
         if (!dead) dead = !mbar_wait(k_full(sb), (uint32_t)((g >> 1) & 1), abort_flag, p.err, ERR_WAIT_FULL);
         tc_fence_after();
         // S(g) overwrites the buffer that held P(g-2): its O MMAs were issued earlier on the same (in-order) pipe
+        const uint64_t qdesc0 = umma_smem_desc(sQ(qb), 0, 1024, kLayoutSw128), kdesc0 = umma_smem_desc(sK(sb), 0, 1024, kLayoutSw128);
         if (elect_one() && !dead) {
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
-            const uint32_t off = (k >> 2) * ATOM_BYTES + (k & 3) * 32;
-            umma_f16(tS(sb), umma_smem_desc(sQ(qb) + off, 0, 1024, kLayoutSw128), umma_smem_desc(sK(sb) + off, 0, 1024, kLayoutSw128),
-                     idesc_s, k ? 1u : 0u);
+            const uint64_t off = (uint64_t)(((k >> 2) * ATOM_BYTES + (k & 3) * 32) >> 4);
+            umma_f16(tS(sb), qdesc0 + off, kdesc0 + off, idesc_s, k ? 1u : 0u);
           }
           tc_commit(s_full(sb));
           tc_commit(k_free(sb));

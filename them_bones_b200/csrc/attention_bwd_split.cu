@@ -62,11 +62,14 @@ __device__ __forceinline__ int split_first_tile(const SplitParams& p, int b, int
   if (p.window_tiles > 0) lo = max(lo, qt - p.window_tiles + 1);
   return lo;
 }
+// Descriptors are the tile's base descriptor plus a compile-time step in the address field (16-byte units; shared-memory
+// addresses stay below 2^18, so the field never carries): one 64-bit add per operand and MMA in the issuing loop instead
+// of the mask-shift-or chain of a fresh descriptor.
 __device__ __forceinline__ uint64_t sdesc_k(uint32_t tile, int k) {   // K-major view, UMMA_K step k
-  return umma_smem_desc(tile + (k >> 2) * SATOM + (k & 3) * 32, 0, 1024, kLayoutSw128);
+  return umma_smem_desc(tile, 0, 1024, kLayoutSw128) + (uint64_t)(((k >> 2) * SATOM + (k & 3) * 32) >> 4);
 }
 __device__ __forceinline__ uint64_t sdesc_mn(uint32_t tile, int k) {  // MN-major view of the same bytes
-  return umma_smem_desc(tile + k * 2048, SATOM, 1024, kLayoutSw128);
+  return umma_smem_desc(tile, SATOM, 1024, kLayoutSw128) + (uint64_t)((k * 2048) >> 4);
 }
 // TMEM column of UMMA_K step k of a packed bf16 A operand: each of the two compute warps of a lane quadrant packs its
 // 64 fp32 columns (c0 = 0 or 64) into the first 32 columns of its own range

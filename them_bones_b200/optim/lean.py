@@ -65,29 +65,57 @@ class TorchComm:
         return t
 
 
+def plan_muon_counts(shapes, world):
+    """How many matrices of each shape group every rank owns.  ``shapes``: ``[(n, rows, cols), ...]`` in group order.
+    A group of ``n`` matrices gives every rank ``n // world`` and one more to ``n % world`` ranks; which ranks get the
+    extra one is chosen group by group, heaviest groups first, for the ranks with the least Newton-Schulz work so far
+    (``max(r, c) * min(r, c)^2`` per matrix), so the step-boundary chain of the busiest rank is as short as the shapes
+    allow (reference: ``plan_layout`` / ``ns_flops``, round2/source/train.py:12171-12250).  With a plain
+    ``ceil(n / world)`` split of 4 x 20 matrices over 8 ranks, six ranks run 12 orthogonalisations and one runs none;
+    here every rank runs 10."""
+    cost = [max(r, c) * min(r, c) ** 2 for _, r, c in shapes]
+    load = [0.0] * world
+    counts = [None] * len(shapes)
+    for gi in sorted(range(len(shapes)), key=lambda i: -cost[i]):
+        n = shapes[gi][0]
+        base, extra = divmod(n, world)
+        order = sorted(range(world), key=lambda r: (load[r], r))
+        lucky = set(order[:extra])
+        counts[gi] = [base + (1 if r in lucky else 0) for r in range(world)]
+        for r in range(world):
+            load[r] += counts[gi][r] * cost[gi]
+    return counts
+
+
 class _MuonUnit:
     """One shape group: weight slab ``W [n_pad, r, c]`` (replica dtype), gradient slab ``G`` (fp32), owner state for
-    ``k = n_pad / world`` matrices."""
+    ``k = n_pad / world`` slots per rank, of which the first ``counts[rank]`` hold matrices (the rest is padding that the
+    fused path skips).  ``slots[i]`` is the slab row of parameter ``i``."""
 
-    def __init__(self, group, params, comm, replica_dtype, master_dtype=torch.float32):
+    def __init__(self, group, params, comm, replica_dtype, master_dtype=torch.float32, counts=None):
         p0 = params[0]
         self.group, self.params = group, params
         self.n, (self.r, self.c) = len(params), p0.shape
         self.k = -(-self.n // comm.world)
         self.n_pad = self.k * comm.world
+        if counts is None:
+            counts = [min(self.k, max(0, self.n - r * self.k)) for r in range(comm.world)]
+        assert sum(counts) == self.n and max(counts) <= self.k
+        self.counts, self.kr = list(counts), counts[comm.rank]
+        self.slots = [r * self.k + j for r in range(comm.world) for j in range(counts[r])]
         dev = p0.device
         self.W = comm.alloc((self.n_pad, self.r, self.c), replica_dtype, dev)
         self.G = comm.alloc((self.n_pad, self.r, self.c), torch.float32, dev)
         own = slice(comm.rank * self.k, (comm.rank + 1) * self.k)
         full32 = torch.zeros(self.n_pad, self.r, self.c, dtype=torch.float32, device=dev)
         for i, p in enumerate(params):
-            full32[i].copy_(p.detach())
+            full32[self.slots[i]].copy_(p.detach())
         self.master = full32[own].clone().to(master_dtype)     # bf16: updated with stochastic rounding
         self.W.copy_(full32)
         del full32
         for i, p in enumerate(params):
-            p.data = self.W[i]
-            p.main_grad = self.G[i]
+            p.data = self.W[self.slots[i]]
+            p.main_grad = self.G[self.slots[i]]
         self.momentum = torch.zeros(self.k, self.r, self.c, dtype=torch.float32, device=dev)
         self.second = torch.zeros((self.k, self.r, 1) if self.r >= self.c else (self.k, 1, self.c),
                                   dtype=torch.float32, device=dev)
@@ -141,6 +169,9 @@ class LeanDistMuonAdamW(torch.optim.Optimizer):
         comm = self.comm
         self.muon_units, self.row_units, self.local_groups = [], [], []
         small = []                                        # (param, group)
+        muon_groups = [g for g in self.param_groups if g["params"] and not g.get("moe_local") and g["kind"] == "muon"]
+        plan = plan_muon_counts([(len(g["params"]),) + tuple(g["params"][0].shape) for g in muon_groups], comm.world)
+        plan = {id(g): c for g, c in zip(muon_groups, plan)}
         for g in self.param_groups:
             ps = [p for p in g["params"]]
             if not ps:
@@ -151,7 +182,8 @@ class LeanDistMuonAdamW(torch.optim.Optimizer):
                 for p in ps:
                     p.main_grad = torch.zeros_like(p, dtype=torch.float32)
             elif g["kind"] == "muon":
-                self.muon_units.append(_MuonUnit(g, ps, comm, rd, torch.bfloat16 if self.bf16_master else torch.float32))
+                self.muon_units.append(_MuonUnit(g, ps, comm, rd, torch.bfloat16 if self.bf16_master else torch.float32,
+                                                 counts=plan[id(g)]))
             else:
                 for p in ps:
                     if p.numel() >= 1024 and p.dim() >= 2 and p.shape[0] % comm.world == 0:
@@ -192,7 +224,7 @@ class LeanDistMuonAdamW(torch.optim.Optimizer):
             addr = comm.peer_addresses(u.G)
             mat = u.r * u.c * 4
             for i, p in enumerate(u.params):
-                p.main_grad_push = addr[i // u.k] + i * mat
+                p.main_grad_push = addr[u.slots[i] // u.k] + u.slots[i] * mat
 
     def _ns(self, t):
         if self.ns_dtype is not None:
@@ -353,7 +385,7 @@ class LeanDistMuonAdamW(torch.optim.Optimizer):
             full = torch.empty(u.n_pad, u.r, u.c, dtype=torch.float32, device=u.master.device)
             self._gather_full(full, u.master)
             for i, p in enumerate(u.params):
-                out[p] = full[i]
+                out[p] = full[u.slots[i]]
         for u in self.row_units:
             full = torch.empty(u.p.shape, dtype=torch.float32, device=u.master.device)
             self._gather_full(full, u.master)
@@ -400,7 +432,7 @@ class LeanDistMuonAdamW(torch.optim.Optimizer):
         return self.bad_steps
 
     def describe(self) -> str:
-        mu = ", ".join(f"{u.n}x[{u.r},{u.c}] (k={u.k})" for u in self.muon_units)
+        mu = ", ".join(f"{u.n}x[{u.r},{u.c}] (own {u.kr} of {u.k} slots)" for u in self.muon_units)
         rows = ", ".join(f"[{u.p.shape[0]},{u.p.shape[1]}]/{self.world}" for u in self.row_units)
         return (f"lean optimizer: world {self.world}; muon slabs: {mu}; row tables: {rows}; scalars: {self.S.numel()}; "
                 f"local expert groups: {len(self.local_groups)}; comm: {type(self.comm).__name__}")

@@ -150,9 +150,12 @@ class PeerComm:
         # this rank's slab is read (still divided by the world size)
         from ..ops import muon_native as MN
         g = u.group
-        n = u.momentum.numel()
-        off = self.rank * n
         mat = u.r * u.c
+        kr = getattr(u, "kr", u.k)                         # matrices this rank owns; the rest of its slots is padding
+        if kr == 0:
+            return
+        n = kr * mat
+        off = self.rank * u.k * mat
         if not hasattr(u, "X"):
             u.X = torch.empty(u.k, u.r, u.c, dtype=torch.bfloat16, device=u.W.device)
             u.sumsq = torch.zeros(u.k, dtype=torch.float32, device=u.W.device)
@@ -166,8 +169,8 @@ class PeerComm:
         L.call("bones_rs_muon_prep", src, _L(off), _L(n), _I(nsrc), _F(1.0 / self.world),
                _F(g["momentum"]), L.ptr(u.momentum), L.ptr(u.X), L.ptr(u.sumsq), _L(mat), L.ptr(self.gsq), L.stream())
         L.call("bones_muon_normalize", L.ptr(u.X), L.ptr(u.sumsq), _L(n), _L(mat), L.stream())
-        x = MN.newton_schulz(u.X, g["ns_steps"])
-        MN.muon_finish(x, u.master, u.second, beta2=g["beta2"], lr=g["lr"], wd=g["weight_decay"])
+        x = MN.newton_schulz(u.X[:kr], g["ns_steps"])
+        MN.muon_finish(x, u.master[:kr], u.second[:kr], beta2=g["beta2"], lr=g["lr"], wd=g["weight_decay"])
         L.call("bones_peer_publish", L.ptr(u.master), self.peers(u.W), _L(off), _L(n), _I(self.world), L.stream())
         self.launches += 3
 
