@@ -373,11 +373,21 @@ __device__ __forceinline__ FwdItem fwd_item(const AttnParams& p, int w, int n_ti
   return it;
 }
 
-__global__ void __launch_bounds__(320, 1)
+// Threads: producer warp, MMA warp and sixteen softmax warps (four per 32-lane TMEM quadrant, 32 keys a thread).
+constexpr int FWD_SW = 16;
+constexpr uint32_t FWD_SLACK = 768;           // room for aligning the tiles to 1024 bytes (the seven tiles, the barriers and
+                                             // the scratch fill the rest of the 227 KB)
+constexpr int FWD_THREADS = 64 + 32 * FWD_SW;
+
+__global__ void __launch_bounds__(FWD_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
+  if (base - raw > FWD_SLACK) {                       // the tiles would not fit behind the alignment gap
+    if (threadIdx.x == 0) atomicCAS(p.err, 0, ERR_WAIT_AUX);
+    return;
+  }
   uint8_t* gen = smem_raw + (base - raw);
   auto sQ = [&](int s) { return base + TILE_BYTES * s; };
   auto sK = [&](int s) { return base + TILE_BYTES * (2 + s); };
@@ -397,7 +407,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
   const uint32_t tmem_slot = bars + 8u * 22;
   volatile uint32_t* tmem_slot_g = reinterpret_cast<volatile uint32_t*>(gen + kBars + 176);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + kBars + 184);
-  float* lsum = reinterpret_cast<float*>(gen + kBars + 256);           // [2 halves][128 rows]
+  float* lsum = reinterpret_cast<float*>(gen + kBars + 256);           // [4 column parts][128 rows]
   const uint32_t ring_bars = bars + 192u;
   volatile int* ring_slots = reinterpret_cast<volatile int*>(gen + kBars + 224);
 
@@ -413,9 +423,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
       mbar_init(k_full(s), 1);
       mbar_init(k_free(s), 1);
       mbar_init(s_full(s), 1);
-      mbar_init(p_full(s), 8);
+      mbar_init(p_full(s), FWD_SW);
       mbar_init(o_full(s), 1);
-      mbar_init(o_free(s), 8);
+      mbar_init(o_free(s), FWD_SW);
     }
     for (int s = 0; s < 3; ++s) {
       mbar_init(v_full(s), 1);
@@ -484,7 +494,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
     const uint32_t idesc_o = umma_idesc_f16(128, 128, 1, 0, 1);   // P (TMEM) x V (MN-major)
     // the O += P V step of a tile is issued one tile late, behind the next tile's S, so the softmax of tile g runs
     // under the S MMAs of tile g+1.  P(g) sits in TMEM as packed bf16 pairs over the S(g) columns it was computed
-    // from (each softmax warp packs its 64 columns into the first 32 of its own range).
+    // from (each softmax warp packs its 32 columns into the first 16 of its own range).
     int pg = -1, p_item = 0;
     bool p_first = false, p_last = false, dead = false;
     auto issue_pv = [&]() {
@@ -499,7 +509,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint64_t bd = vdesc0 + (uint64_t)((k * 2048) >> 4);
-          umma_f16_ts(tO(ob), tS(sb) + (uint32_t)((k & 3) * 8 + (k >> 2) * 64), bd, idesc_o, (p_first && k == 0) ? 0u : 1u);
+          umma_f16_ts(tO(ob), tS(sb) + (uint32_t)((k >> 1) * 32 + (k & 1) * 8), bd, idesc_o, (p_first && k == 0) ? 0u : 1u);
         }
         tc_commit(v_free(vs));
         if (p_last) tc_commit(o_full(ob));
@@ -538,10 +548,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
     }
     if (pg >= 0) issue_pv();
   } else {
-    // Softmax: eight warps, two per 32-lane TMEM quadrant; each thread owns one query row and 64 of the tile's 128 keys.
-    const int q = warp & 3, half = (warp - 2) >> 2;
+    // Softmax: sixteen warps, four per 32-lane TMEM quadrant; each thread owns one query row and 32 of the tile's 128
+    // keys.  A tile's softmax is a chain -- TMEM load, exponentials, TMEM store -- that every warp runs at the same
+    // time; with eight warps and 64 keys a thread a tile took 2 400 clocks against 1 024 of MMAs, sixteen warps take a
+    // little less (0.207 -> 0.196 ms at B = 16, T = 2048, H = 10).  Two groups of eight warps that take alternate key
+    // tiles (each chain then has two tile periods) were measured as well and were no faster (0.204 ms): with 64 keys a
+    // thread the chain itself is twice as long.
+    const int q = warp & 3, part = (warp - 2) >> 2;
     const int r = q * 32 + lane;            // row within the tile == TMEM lane
-    const int c0 = half * 64;
+    const int c0 = part * 32;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
     // the drain of an item's output is deferred until the first tile of the next item has been exponentiated
     bool pend = false, ok = true;
@@ -553,11 +568,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
       const bool got = mbar_wait(o_full(ob), (uint32_t)((pend_it >> 1) & 1), abort_flag, p.err, ERR_WAIT_TMEM_FULL);
       if (!__all_sync(0xffffffffu, got)) return false;
       tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      {
         uint32_t v[32];
         __syncwarp();
-        BONES_TMEM_LD32(tO(ob) + lane_addr + (uint32_t)(c0 + c * 32), v);
+        BONES_TMEM_LD32(tO(ob) + lane_addr + (uint32_t)c0, v);
         tmem_ld_wait();
         uint4 u[4];
 #pragma unroll
@@ -567,8 +581,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
           u[gq].z = pack_bf16(__uint_as_float(v[gq * 8 + 4]) * pend_inv, __uint_as_float(v[gq * 8 + 5]) * pend_inv);
           u[gq].w = pack_bf16(__uint_as_float(v[gq * 8 + 6]) * pend_inv, __uint_as_float(v[gq * 8 + 7]) * pend_inv);
         }
-        st_global_v8(pend_y + c * 32, u[0], u[1]);       // one full 32-byte sector per store
-        st_global_v8(pend_y + c * 32 + 16, u[2], u[3]);
+        st_global_v8(pend_y, u[0], u[1]);                // one full 32-byte sector per store
+        st_global_v8(pend_y + 16, u[2], u[3]);
       }
       tc_fence_before();
       __syncwarp();
@@ -591,34 +605,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
         if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
         tc_fence_after();
         const int k0 = (im.kt0 + j) * AT + c0;
-        // warp-uniform: does any row of this warp need the element mask for these 64 keys (diagonal or document start)?
-        const bool need_mask = __any_sync(0xffffffffu, (k0 + 63 > qpos) || (k0 < lo));
-        uint32_t v0[32], v1[32], pk[32];
+        // warp-uniform: does any row of this warp need the element mask for these 32 keys (diagonal or document start)?
+        const bool need_mask = __any_sync(0xffffffffu, (k0 + 31 > qpos) || (k0 < lo));
+        uint32_t v0[32], pk[16];
         __syncwarp();
         BONES_TMEM_LD32(tS(sb) + lane_addr + (uint32_t)c0, v0);
-        BONES_TMEM_LD32(tS(sb) + lane_addr + (uint32_t)(c0 + 32), v1);
         tmem_ld_wait();
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
+        {
           float e[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            const float x = fmaf(__uint_as_float(c ? v1[i] : v0[i]), p.c1, -p.c2);
+            const float x = fmaf(__uint_as_float(v0[i]), p.c1, -p.c2);
             asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e[i]) : "f"(x));
           }
           if (need_mask) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-              const int kpos = k0 + c * 32 + i;
+              const int kpos = k0 + i;
               if (kpos > qpos || kpos < lo) e[i] = 0.f;
             }
           }
 #pragma unroll
           for (int i = 0; i < 32; ++i) l += e[i];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) pk[c * 16 + i] = pack_bf16(e[2 * i], e[2 * i + 1]);
+          for (int i = 0; i < 16; ++i) pk[i] = pack_bf16(e[2 * i], e[2 * i + 1]);
         }
-        BONES_TMEM_ST32(tS(sb) + lane_addr + (uint32_t)c0, pk);
+        BONES_TMEM_ST16(tS(sb) + lane_addr + (uint32_t)c0, pk);
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
@@ -626,12 +638,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant
         if (pend && !drain()) { ok = false; break; }
       }
       if (!ok) break;
-      // the two threads of a row exchange their partial row sums through shared memory
-      lsum[half * AT + r] = l;
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      l += lsum[(half ^ 1) * AT + r];
-      asm volatile("bar.sync 1, 256;" ::: "memory");      // nobody rewrites the scratch before everybody has read it
-      if (half == 0) p.lse[((long long)im.b * p.H + im.h) * p.T + qpos] = logf(l) + p.shift_ln;
+      // the four threads of a row exchange their partial row sums through shared memory
+      lsum[part * AT + r] = l;
+      asm volatile("bar.sync 1, 512;" ::: "memory");
+      l = (lsum[r] + lsum[AT + r]) + (lsum[2 * AT + r] + lsum[3 * AT + r]);      // the same order in all four threads
+      asm volatile("bar.sync 1, 512;" ::: "memory");      // nobody rewrites the scratch before everybody has read it
+      if (part == 0) p.lse[((long long)im.b * p.H + im.h) * p.T + qpos] = logf(l) + p.shift_ln;
       pend = true;
       pend_it = it;
       pend_inv = 1.0f / l;
@@ -724,7 +736,7 @@ int bones_attn_fwd(const void* qk, const void* qkv, void* y, float* lse, const i
   p.y = (__nv_bfloat16*)y;
   p.lse = lse;
   p.err = error_word();
-  constexpr size_t smem = (size_t)TILE_BYTES * 7 + 256 + 1024 + 1024;   // tiles, barriers, row-sum scratch, alignment slack
+  constexpr size_t smem = (size_t)TILE_BYTES * 7 + 256 + 2048 + FWD_SLACK;   // tiles, barriers, row-sum scratch, alignment slack
   static bool attr_done = false;
   if (!attr_done) {
     BONES_CHECK(cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -740,7 +752,7 @@ int bones_attn_fwd(const void* qk, const void* qkv, void* y, float* lse, const i
   if (!counter[dev]) BONES_CHECK(cudaGetSymbolAddress(reinterpret_cast<void**>(&counter[dev]), g_fwd_items));
   BONES_CHECK(cudaMemsetAsync(counter[dev], 0, sizeof(int), (cudaStream_t)stream));
   p.items = counter[dev];
-  attn_fwd_kernel<<<grid, 320, smem, (cudaStream_t)stream>>>(tq, tv, p);
+  attn_fwd_kernel<<<grid, FWD_THREADS, smem, (cudaStream_t)stream>>>(tq, tv, p);
   return (int)cudaGetLastError();
 }
 }  // extern "C"

@@ -71,42 +71,48 @@ __device__ __forceinline__ uint64_t sdesc_k(uint32_t tile, int k) {   // K-major
 __device__ __forceinline__ uint64_t sdesc_mn(uint32_t tile, int k) {  // MN-major view of the same bytes
   return umma_smem_desc(tile, SATOM, 1024, kLayoutSw128) + (uint64_t)((k * 2048) >> 4);
 }
-// TMEM column of UMMA_K step k of a packed bf16 A operand: each of the two compute warps of a lane quadrant packs its
-// 64 fp32 columns (c0 = 0 or 64) into the first 32 columns of its own range
-__device__ __forceinline__ uint32_t packed_col(int k) { return (uint32_t)((k & 3) * 8 + (k >> 2) * 64); }
+// Compute warps: four per 32-lane TMEM quadrant, each thread one row and 32 of the tile's 128 columns.  With two per
+// quadrant (64 columns a thread) the exponentials and the dS arithmetic of a tile took 3 300 clocks one after the other
+// against 2 048 clocks of MMAs; the same work over twice the warps hides a little more of its latency (0.836 -> 0.812 ms
+// for the whole backward at B = 16, T = 2048, H = 10).  A P phase still takes about 2 000 clocks: TMEM load, 1 024
+// clocks of exponentials on the special-function units, TMEM store, one after the other in every warp at once.
+// Computing every other exponential with a cubic on the FMA pipe was measured and made both kernels slower (the
+// arithmetic of the dS phase competes for the same issue slots), so all exponentials stay on `ex2.approx`.
+constexpr int SCW = 16;                      // compute warps per CTA
+constexpr int STHREADS = 64 + 32 * SCW;      // producer warp + MMA warp + compute warps
+// TMEM column of UMMA_K step k of a packed bf16 A operand: each compute warp packs its 32 fp32 columns (c0 = 0, 32,
+// 64, 96) into the first 16 columns of its own range, two K steps of 8 packed columns each
+__device__ __forceinline__ uint32_t packed_col(int k) { return (uint32_t)((k >> 1) * 32 + (k & 1) * 8); }
 
 __device__ __forceinline__ float ex2_fast(float x) {
   float e;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x));
   return e;
 }
-// 64 fp32 values -> 32 packed bf16 pairs -> 32 TMEM columns starting at taddr
-__device__ __forceinline__ void store_packed64(uint32_t taddr, const float* v) {
-  uint32_t pk[32];
+// 32 fp32 values -> 16 packed bf16 pairs -> 16 TMEM columns starting at taddr
+__device__ __forceinline__ void store_packed32(uint32_t taddr, const float* v) {
+  uint32_t pk[16];
 #pragma unroll
-  for (int j = 0; j < 32; ++j) pk[j] = pack_bf16(v[2 * j], v[2 * j + 1]);
-  BONES_TMEM_ST32(taddr, pk);
+  for (int j = 0; j < 16; ++j) pk[j] = pack_bf16(v[2 * j], v[2 * j + 1]);
+  BONES_TMEM_ST16(taddr, pk);
   tmem_st_wait();
 }
-// 64 accumulator columns of this thread's row -> 64 bf16 in global memory (four 32-byte sectors)
-__device__ __forceinline__ void drain_row64(uint32_t taddr, __nv_bfloat16* dst) {
+// 32 accumulator columns of this thread's row -> 32 bf16 in global memory (two 32-byte sectors)
+__device__ __forceinline__ void drain_row32(uint32_t taddr, __nv_bfloat16* dst) {
+  uint32_t v[32];
+  __syncwarp();
+  BONES_TMEM_LD32(taddr, v);
+  tmem_ld_wait();
+  uint4 u[4];
 #pragma unroll
-  for (int c = 0; c < 2; ++c) {
-    uint32_t v[32];
-    __syncwarp();
-    BONES_TMEM_LD32(taddr + (uint32_t)(c * 32), v);
-    tmem_ld_wait();
-    uint4 u[4];
-#pragma unroll
-    for (int g = 0; g < 4; ++g) {
-      u[g].x = pack_bf16(__uint_as_float(v[g * 8 + 0]), __uint_as_float(v[g * 8 + 1]));
-      u[g].y = pack_bf16(__uint_as_float(v[g * 8 + 2]), __uint_as_float(v[g * 8 + 3]));
-      u[g].z = pack_bf16(__uint_as_float(v[g * 8 + 4]), __uint_as_float(v[g * 8 + 5]));
-      u[g].w = pack_bf16(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7]));
-    }
-    st_global_v8(dst + c * 32, u[0], u[1]);
-    st_global_v8(dst + c * 32 + 16, u[2], u[3]);
+  for (int g = 0; g < 4; ++g) {
+    u[g].x = pack_bf16(__uint_as_float(v[g * 8 + 0]), __uint_as_float(v[g * 8 + 1]));
+    u[g].y = pack_bf16(__uint_as_float(v[g * 8 + 2]), __uint_as_float(v[g * 8 + 3]));
+    u[g].z = pack_bf16(__uint_as_float(v[g * 8 + 4]), __uint_as_float(v[g * 8 + 5]));
+    u[g].w = pack_bf16(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7]));
   }
+  st_global_v8(dst, u[0], u[1]);
+  st_global_v8(dst + 16, u[2], u[3]);
 }
 
 // stats[b,h,t] = (-lse * log2(e), sum_d dO * O); sixteen lanes per (row, head), 16 bytes of each operand per lane
@@ -169,7 +175,7 @@ __device__ __forceinline__ DkvItem dkv_item(const SplitParams& p, int w, int n_t
   return it;
 }
 
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(STHREADS, 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant__ CUtensorMap tm_v,
                     const __grid_constant__ CUtensorMap tm_dy, const SplitParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -211,10 +217,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
     }
     mbar_init(bar(B_SFULL), 1);
     mbar_init(bar(B_DPFULL), 1);
-    mbar_init(bar(B_PREADY), 8);
-    mbar_init(bar(B_DSREADY), 8);
+    mbar_init(bar(B_PREADY), SCW);
+    mbar_init(bar(B_DSREADY), SCW);
     mbar_init(bar(B_DONE), 1);
-    mbar_init(bar(B_ACCFREE), 8);
+    mbar_init(bar(B_ACCFREE), SCW);
     for (int s = 0; s < 4; ++s) mbar_init(ring_bars + 8u * s, 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -365,10 +371,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
       APROF_STORE(8, 7);
     }
   } else {
-    const int q = warp & 3, half = (warp - 2) >> 2;
+    const int q = warp & 3, part = (warp - 2) >> 2;
     const int r = q * 32 + lane;                       // key row of this thread
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-    const int c0 = half * 64;                          // first query column of this thread
+    const int c0 = part * 32;                          // first query column of this thread
     bool ok = true;
     int g = 0, it = 0;
     APROF_DECL(8);
@@ -391,38 +397,34 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
         const int* slo = p.doc_start ? p.doc_start + (long long)im.b * p.T + (im.kt + i) * ST : nullptr;
         const bool need_doc = slo && nx_lo_last > k0;
         if (slo && i + 1 < im.n) nx_lo_last = slo[2 * ST - 1];
-        float pr[64];
-        APROF_ADD(2);
+        float pr[32];
         got = mbar_wait(bar(B_SFULL), ph, abort_flag, p.err, ERR_WAIT_TMEM_FULL);
         APROF_ADD(1);
         if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
         tc_fence_after();
         {
-          uint32_t v0[32], v1[32];
+          uint32_t v0[32];
           __syncwarp();
           BONES_TMEM_LD32(tS + lane_addr + (uint32_t)c0, v0);
-          BONES_TMEM_LD32(tS + lane_addr + (uint32_t)(c0 + 32), v1);
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const float4 a = st4[j], c = st4[16 + j];
+            const float4 a = st4[j];
             pr[2 * j] = ex2_fast(fmaf(__uint_as_float(v0[2 * j]), p.c1, a.x));
             pr[2 * j + 1] = ex2_fast(fmaf(__uint_as_float(v0[2 * j + 1]), p.c1, a.z));
-            pr[32 + 2 * j] = ex2_fast(fmaf(__uint_as_float(v1[2 * j]), p.c1, c.x));
-            pr[32 + 2 * j + 1] = ex2_fast(fmaf(__uint_as_float(v1[2 * j + 1]), p.c1, c.z));
           }
         }
         if (i == 0) {                                    // diagonal tile: a key sees only queries at or after it
 #pragma unroll
-          for (int j = 0; j < 64; ++j)
+          for (int j = 0; j < 32; ++j)
             if (r > c0 + j) pr[j] = 0.f;
         }
         if (need_doc) {                                  // a query sees only keys of its own document
 #pragma unroll
-          for (int j = 0; j < 64; ++j)
+          for (int j = 0; j < 32; ++j)
             if (kpos < slo[c0 + j]) pr[j] = 0.f;
         }
-        store_packed64(tS + lane_addr + (uint32_t)c0, pr);
+        store_packed32(tS + lane_addr + (uint32_t)c0, pr);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(B_PREADY));
@@ -432,21 +434,18 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
         if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
         tc_fence_after();
         {
-          uint32_t v0[32], v1[32];
+          uint32_t v0[32];
           __syncwarp();
           BONES_TMEM_LD32(tdP + lane_addr + (uint32_t)c0, v0);
-          BONES_TMEM_LD32(tdP + lane_addr + (uint32_t)(c0 + 32), v1);
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const float4 a = st4[j], c = st4[16 + j];
+            const float4 a = st4[j];
             pr[2 * j] *= (__uint_as_float(v0[2 * j]) - a.y) * p.scale;
             pr[2 * j + 1] *= (__uint_as_float(v0[2 * j + 1]) - a.w) * p.scale;
-            pr[32 + 2 * j] *= (__uint_as_float(v1[2 * j]) - c.y) * p.scale;
-            pr[32 + 2 * j + 1] *= (__uint_as_float(v1[2 * j + 1]) - c.w) * p.scale;
           }
         }
-        store_packed64(tdP + lane_addr + (uint32_t)c0, pr);
+        store_packed32(tdP + lane_addr + (uint32_t)c0, pr);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(B_DSREADY));
@@ -457,8 +456,8 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
       APROF_ADD(5);
       if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
       tc_fence_after();
-      drain_row64(tdK + lane_addr + (uint32_t)c0, p.dqk + ((long long)(row0 + kpos)) * 2 * A + A + (long long)im.h * 128 + c0);
-      drain_row64(tdV + lane_addr + (uint32_t)c0, p.dv + ((long long)(row0 + kpos)) * p.dv_ld + (long long)im.h * 128 + c0);
+      drain_row32(tdK + lane_addr + (uint32_t)c0, p.dqk + ((long long)(row0 + kpos)) * 2 * A + A + (long long)im.h * 128 + c0);
+      drain_row32(tdV + lane_addr + (uint32_t)c0, p.dv + ((long long)(row0 + kpos)) * p.dv_ld + (long long)im.h * 128 + c0);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_ACCFREE));
@@ -508,7 +507,7 @@ __device__ __forceinline__ DqItem dq_item(const SplitParams& p, int w, int n_til
   return it;
 }
 
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(STHREADS, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_constant__ CUtensorMap tm_v,
                    const __grid_constant__ CUtensorMap tm_dy, const SplitParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -546,10 +545,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_const
       mbar_init(bar(B_DPFULL0 + s), 1);
     }
     mbar_init(bar(B_SFULL), 1);
-    mbar_init(bar(B_SFREE), 8);
-    mbar_init(bar(B_DSREADY), 8);
+    mbar_init(bar(B_SFREE), SCW);
+    mbar_init(bar(B_DSREADY), SCW);
     mbar_init(bar(B_DONE), 1);
-    mbar_init(bar(B_DQFREE), 8);
+    mbar_init(bar(B_DQFREE), SCW);
     for (int s = 0; s < 4; ++s) mbar_init(ring_bars + 8u * s, 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -659,10 +658,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_const
       }
     }
   } else {
-    const int q = warp & 3, half = (warp - 2) >> 2;
+    const int q = warp & 3, part = (warp - 2) >> 2;
     const int r = q * 32 + lane;
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-    const int c0 = half * 64;
+    const int c0 = part * 32;
     bool ok = true;
     int g = 0, it = 0;
     for (;; ++it) {
@@ -679,26 +678,22 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_const
         if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
         tc_fence_after();
         const int k0 = (im.kt0 + j) * ST + c0;
-        const bool need_mask = __any_sync(0xffffffffu, (k0 + 63 > qpos) || (k0 < lo));
-        float pr[64];
+        const bool need_mask = __any_sync(0xffffffffu, (k0 + 31 > qpos) || (k0 < lo));
+        float pr[32];
         {
-          uint32_t v0[32], v1[32];
+          uint32_t v0[32];
           __syncwarp();
           BONES_TMEM_LD32(tS + lane_addr + (uint32_t)c0, v0);
-          BONES_TMEM_LD32(tS + lane_addr + (uint32_t)(c0 + 32), v1);
           tmem_ld_wait();
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar(B_SFREE));
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            pr[i] = ex2_fast(fmaf(__uint_as_float(v0[i]), p.c1, st.x));
-            pr[32 + i] = ex2_fast(fmaf(__uint_as_float(v1[i]), p.c1, st.x));
-          }
+          for (int i = 0; i < 32; ++i) pr[i] = ex2_fast(fmaf(__uint_as_float(v0[i]), p.c1, st.x));
         }
         if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < 64; ++i) {
+          for (int i = 0; i < 32; ++i) {
             const int kp = k0 + i;
             if (kp > qpos || kp < lo) pr[i] = 0.f;
           }
@@ -707,18 +702,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_const
         if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
         tc_fence_after();
         {
-          uint32_t v0[32], v1[32];
+          uint32_t v0[32];
           __syncwarp();
           BONES_TMEM_LD32(tdP(s) + lane_addr + (uint32_t)c0, v0);
-          BONES_TMEM_LD32(tdP(s) + lane_addr + (uint32_t)(c0 + 32), v1);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            pr[i] *= (__uint_as_float(v0[i]) - st.y) * p.scale;
-            pr[32 + i] *= (__uint_as_float(v1[i]) - st.y) * p.scale;
-          }
+          for (int i = 0; i < 32; ++i) pr[i] *= (__uint_as_float(v0[i]) - st.y) * p.scale;
         }
-        store_packed64(tdP(s) + lane_addr + (uint32_t)c0, pr);
+        store_packed32(tdP(s) + lane_addr + (uint32_t)c0, pr);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(B_DSREADY));
@@ -727,7 +718,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_const
       const bool got = mbar_wait(bar(B_DONE), (uint32_t)(it & 1), abort_flag, p.err, ERR_WAIT_TMEM_FULL);
       if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
       tc_fence_after();
-      drain_row64(tdQ + lane_addr + (uint32_t)c0, p.dqk + ((long long)(row0 + qpos)) * 2 * A + (long long)im.h * 128 + c0);
+      drain_row32(tdQ + lane_addr + (uint32_t)c0, p.dqk + ((long long)(row0 + qpos)) * 2 * A + (long long)im.h * 128 + c0);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(B_DQFREE));
@@ -814,10 +805,10 @@ int bones_attn_bwd_split(const void* qk, const void* qkv, const void* dy, const 
   BONES_CHECK(cudaMemsetAsync(counter_dkv[dev], 0, sizeof(int), s));
   BONES_CHECK(cudaMemsetAsync(counter_dq[dev], 0, sizeof(int), s));
   p.items = counter_dkv[dev];
-  attn_bwd_dkv_kernel<<<grid, 320, smem_dkv, s>>>(tq, tv, td, p);
+  attn_bwd_dkv_kernel<<<grid, STHREADS, smem_dkv, s>>>(tq, tv, td, p);
   BONES_CHECK(cudaGetLastError());
   p.items = counter_dq[dev];
-  attn_bwd_dq_kernel<<<grid, 320, smem_dq, s>>>(tq, tv, td, p);
+  attn_bwd_dq_kernel<<<grid, STHREADS, smem_dq, s>>>(tq, tv, td, p);
   return (int)cudaGetLastError();
 }
 
