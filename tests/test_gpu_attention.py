@@ -70,6 +70,30 @@ def test_attention_backward(b, t, h, window, docs):
     assert _rel(x.grad, xr.grad) < 4e-2, _rel(x.grad, xr.grad)
 
 
+@pytest.mark.parametrize("b,t,h,window,docs", [(2, 512, 3, 0, True), (1, 1024, 2, 256, True)])
+def test_attention_head_dim_64(b, t, h, window, docs):
+    """head_dim 64 runs on the 128-wide kernels with zero-padded heads: forward and gradients against the fp32
+    statement, through the operator layer."""
+    from them_bones_b200 import ops
+    from them_bones_b200.ops import _lib as L
+    from them_bones_b200.ref import functional as RF
+    d = 64
+    qkv, cos, sin, ds = _inputs(b, t, h, d, seed=11, docs=docs)
+    scale = 1.0 / math.sqrt(d)
+    g = torch.randn(b, t, h * d, device="cuda", dtype=torch.bfloat16)
+    x = qkv.clone().requires_grad_(True)
+    y = ops.attention(x, cos, sin, h, d, scale, ds, window)
+    y.backward(g)
+    xr = qkv.float().requires_grad_(True)
+    yr = RF.attention(xr, cos, sin, h, d, scale, ds, window)
+    yr.backward(g.float())
+    torch.cuda.synchronize()
+    L.check_error_word()
+    assert y.shape == (b, t, h * d)
+    assert _rel(y, yr) < 2e-2, _rel(y, yr)
+    assert _rel(x.grad, xr.grad) < 4e-2, _rel(x.grad, xr.grad)
+
+
 def test_attention_ragged_length_is_padded_and_unsupported_shapes_raise():
     """The operator layer pads a length that is not a multiple of 128 (scoring, cache-free decoding) and raises --
     rather than taking a library path -- for what the kernels do not cover."""

@@ -369,7 +369,7 @@ def attention(qkv, cos, sin, n_head, head_dim, scale, doc_start, window):
     if why:
         raise ValueError(f"native attention does not cover this call: {why}")
     COUNTS["attention"] += 1
-    if _LIBRARY_OPS:             # the same kernels behind torch.library custom ops (ops/registry.py)
+    if _LIBRARY_OPS and head_dim == 128:             # the same kernels behind torch.library custom ops (ops/registry.py)
         from . import registry
         y = registry.attention(qkv, cos, sin, n_head, head_dim, scale, doc_start, window)
     else:
