@@ -185,6 +185,8 @@ def run_ours(args, torch_path: bool = False):
     e2e_value = tokens / (ms_e2e / 1e3)
     if not torch_path:
         _lib.check_error_word()
+    # steps whose reduced gradient held a non-finite value (the fused optimizer zeroes those entries and counts the step)
+    bad_steps = tr.optimizer.count_bad_steps() if hasattr(tr.optimizer, "count_bad_steps") else 0
     if rt.rank == 0:
         out = {
             "metric": "train tokens/sec (device-timed, max over ranks)", "value": value, "unit": "tokens/s",
@@ -202,6 +204,7 @@ def run_ours(args, torch_path: bool = False):
                     "ms_per_step": ms_e2e / args.steps, "final_loss": last},
             "gpu_launches": int(launches),
             "optimizer_ms_per_step": opt_ms,      # device time of the step-boundary optimizer chain, max over ranks
+            "non_finite_steps": int(bad_steps),
             "native_ops": {k: v - counts0.get(k, 0) for k, v in ops.COUNTS.items()},
             "tflops_per_gpu": value * tr.flops_per_token / rt.world / 1e12,
             "peak_mem_gb": torch.cuda.max_memory_allocated() / 2 ** 30,

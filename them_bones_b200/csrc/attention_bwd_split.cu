@@ -484,6 +484,11 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_cons
 // dQ  (TMEM lanes are queries, columns are keys; dP double-buffered so the MMAs of tile j+1 run under the
 //      exponentiation of tile j).  K tiles live from S(j) to dQ(j), V tiles only until dP(j): a K ring of three and a V
 //      ring of two keep every load a full tile ahead of its first use.
+//      One "dS ready" barrier per dP buffer: S(j+1) and dP(j+1) are issued before dS(j) is awaited, so a compute warp
+//      can finish tile j+1 while a slower one is still on tile j; with one barrier for both buffers its second
+//      arrival completed the slower warp's phase and the dQ MMAs read that warp's columns before it had stored them
+//      (a few non-finite rows of dq once in a few hundred calls, more often with sixteen compute warps whose masking
+//      work differs).  dP(j+2) is only issued after dQ(j), so nobody can be two tiles ahead.
 //      Persistent: one CTA per SM walks (query tile, head, batch) items in the forward kernel's order (the query tiles
 //      of one (head, batch) run at the same time and share K/V through L2).  Barrier phases, the K/V rings and the dP
 //      buffers run on across items; Q and dO are single-buffered and reloaded as soon as the item's last S and dP MMAs
@@ -519,7 +524,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_const
   auto sV = [&](int s) { return base + STILE * (5 + s); };      // two stages
   const uint32_t bars = base + DQ_BARS;
   enum { B_QDO = 0, B_QDOFREE, B_K0, B_K1, B_K2, B_KFREE0, B_KFREE1, B_KFREE2, B_V0, B_V1, B_VFREE0, B_VFREE1, B_SFULL, B_SFREE,
-         B_DPFULL0, B_DPFULL1, B_DSREADY, B_DONE, B_DQFREE, B_COUNT };
+         B_DPFULL0, B_DPFULL1, B_DSREADY0, B_DSREADY1, B_DONE, B_DQFREE, B_COUNT };
   auto bar = [&](int i) { return bars + 8u * i; };
   const uint32_t tmem_slot = bars + 8u * B_COUNT;
   volatile uint32_t* tmem_slot_g = reinterpret_cast<volatile uint32_t*>(gen + DQ_BARS + 8 * B_COUNT);
@@ -546,7 +551,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_const
     }
     mbar_init(bar(B_SFULL), 1);
     mbar_init(bar(B_SFREE), SCW);
-    mbar_init(bar(B_DSREADY), SCW);
+    mbar_init(bar(B_DSREADY0), SCW);
+    mbar_init(bar(B_DSREADY1), SCW);
     mbar_init(bar(B_DONE), 1);
     mbar_init(bar(B_DQFREE), SCW);
     for (int s = 0; s < 4; ++s) mbar_init(ring_bars + 8u * s, 1);
@@ -645,7 +651,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_const
         if (j == 0) issue_sdp(g, im.n == 1);
         if (j + 1 < im.n) issue_sdp(g + 1, j + 2 == im.n);
         // dS(g) sits packed in the dP(g) columns: dQ += dS Kh(g), which also frees that K stage
-        if (!dead) dead = !mbar_wait(bar(B_DSREADY), (uint32_t)(g & 1), abort_flag, p.err, ERR_WAIT_AUX);
+        if (!dead) dead = !mbar_wait(bar(B_DSREADY0 + (g & 1)), (uint32_t)((g >> 1) & 1), abort_flag, p.err, ERR_WAIT_AUX);
         if (j == 0 && it >= 1 && !dead) dead = !mbar_wait(bar(B_DQFREE), (uint32_t)((it - 1) & 1), abort_flag, p.err, ERR_WAIT_TMEM_EMPTY);
         tc_fence_after();
         if (elect_one() && !dead) {
@@ -712,7 +718,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_qk, const __grid_const
         store_packed32(tdP(s) + lane_addr + (uint32_t)c0, pr);
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar(B_DSREADY));
+        if (lane == 0) mbar_arrive(bar(B_DSREADY0 + s));
       }
       if (!ok) break;
       const bool got = mbar_wait(bar(B_DONE), (uint32_t)(it & 1), abort_flag, p.err, ERR_WAIT_TMEM_FULL);

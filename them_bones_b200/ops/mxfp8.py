@@ -53,6 +53,14 @@ def sf2_bytes(rows: int, k: int, group: int = 128) -> int:
     return -(-rows // group) * -(-k // 128) * -(-group // 128) * 512
 
 
+def _sf_buf(rows: int, k: int, group: int, dev, lead=()):
+    """Scale-chunk buffer of an operand.  When the rows fill whole tiles of whole 128-row chunks and K whole 128-blocks
+    every byte is written by the producing kernel; otherwise the slots of rows that do not exist must read as zero."""
+    full = group % 128 == 0 and rows % group == 0 and k % 128 == 0
+    mk = torch.empty if full else torch.zeros
+    return mk(*lead, sf2_bytes(rows, k, group), dtype=torch.uint8, device=dev)
+
+
 def quant2(x2: torch.Tensor, *, row: bool = True, col: bool = False, group_r: int = 128, group_c: int = 128, out=None):
     """bf16 ``[R, C]`` -> ``(q_row, sf_row, q_col, sf_col)``: E4M3 copies quantised in 1 x 32 blocks along C (``row``) and
     along R (``col``), each with UE8M0 scale chunks laid out for an operand whose tiles are ``group`` rows.  The column
@@ -66,10 +74,10 @@ def quant2(x2: torch.Tensor, *, row: bool = True, col: bool = False, group_r: in
     else:
         if row:
             qr = torch.empty(r, c, dtype=torch.uint8, device=dev)
-            sfr = torch.zeros(sf2_bytes(r, c, group_r), dtype=torch.uint8, device=dev)
+            sfr = _sf_buf(r, c, group_r, dev)
         if col:
             qc = torch.empty(r, c, dtype=torch.uint8, device=dev)
-            sfc = torch.zeros(sf2_bytes(c, r, group_c), dtype=torch.uint8, device=dev)
+            sfc = _sf_buf(c, r, group_c, dev)
     L.call("bones_mx2_quant", L.ptr(x2), _L(x2.stride(0)), L.ptr(qr), L.ptr(sfr), _I(group_r), L.ptr(qc), L.ptr(sfc), _I(group_c),
            _L(r), _L(c), L.stream())
     COUNTS["mx_quant"] += 1
@@ -120,10 +128,10 @@ def gemm2(aq, sfa, bq, sfb, m, n, k, *, a_major=0, b_major=0, epi=GE_BF16, r=Non
     dq = dsf = dt = dtsf = None
     if want_q:
         dq = torch.empty(*lead, m, n, dtype=torch.uint8, device=dev)
-        dsf = torch.zeros(*lead, sf2_bytes(m, n, dq_group), dtype=torch.uint8, device=dev)
+        dsf = _sf_buf(m, n, dq_group, dev, lead)
     if want_t:
         dt = torch.empty(*lead, m, n, dtype=torch.uint8, device=dev)
-        dtsf = torch.zeros(*lead, sf2_bytes(n, m, dt_group), dtype=torch.uint8, device=dev)
+        dtsf = _sf_buf(n, m, dt_group, dev, lead)
     sa, sb = (aq.stride(0), bq.stride(0)) if batch > 1 else (0, 0)
     lda, ldb = aq.stride(-2), bq.stride(-2)
     sd = d.stride(0) if (d is not None and batch > 1) else 0
