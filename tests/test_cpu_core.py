@@ -345,3 +345,28 @@ def test_muon_placement_balances_newton_schulz_work():
     assert max(load) - min(load) <= max(cost)
     assert plan_muon_counts([(4, 64, 64)], 1) == [[4]]
     assert plan_muon_counts([(3, 64, 32)], 4) == [[1, 1, 1, 0]]
+
+
+def test_local_expert_step_gates_a_non_finite_gradient_per_expert():
+    """An expert whose gradient holds a NaN sits the step out (its weights stay finite); the other experts of the same
+    stacked parameter step exactly as they would without it; the step is reported as bad without a host read."""
+    from them_bones_b200.optim.lean import MuonLocal
+    torch.manual_seed(0)
+    group = dict(momentum=0.95, beta2=0.95, lr=0.02, weight_decay=0.0, ns_steps=5)
+    grads = torch.randn(4, 32, 16)
+
+    def run(poison):
+        p = torch.nn.Parameter(torch.randn(4, 32, 16, generator=torch.Generator().manual_seed(1)))
+        p.main_grad = grads.clone()
+        if poison:
+            p.main_grad[2, 3, 5] = float("nan")
+        opt = MuonLocal([dict(group, params=[p])], ns_dtype=torch.float32)
+        return p, opt.step(1.0)
+
+    clean, bad0 = run(False)
+    gated, bad1 = run(True)
+    assert not bool(bad0) and bool(bad1)
+    assert torch.isfinite(gated).all()
+    keep = [0, 1, 3]
+    assert torch.allclose(gated[keep], clean[keep], atol=1e-6)
+    assert not torch.allclose(gated[2], clean[2], atol=1e-4)      # the poisoned expert did not take the clean step

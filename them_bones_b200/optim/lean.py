@@ -330,7 +330,9 @@ class LeanDistMuonAdamW(torch.optim.Optimizer):
                 u.master.copy_(RF.stochastic_round_bf16(master))
             comm.all_gather(u.W, u.master.to(u.W.dtype))
         # 5b: local experts
-        self._local.step(1.0 / self.world)
+        local_bad = self._local.step(1.0 / self.world)
+        if local_bad is not None and self.finite_gate:
+            self._bad_dev += local_bad.to(torch.int64) * (self._last_ok > 0).to(torch.int64)   # a step counts once
 
     def _small_step(self, g=None):
         if not self.small:
@@ -358,13 +360,15 @@ class LeanDistMuonAdamW(torch.optim.Optimizer):
             comm.fused_muon(u, self.steps, self._ns(u.W), own_only=getattr(self, "push", False))
             if getattr(self, "push", False):
                 u.G.zero_()                               # consumed; peers add the next step's tiles after post_step()
-        self._local.step(1.0 / self.world)
+        local_bad = self._local.step(1.0 / self.world)
         comm.post_step()                                  # every peer's stores into my slabs have landed
         # sum(g^2) of the step, folded into a device-side count of non-finite steps: no host synchronisation in the step
         # and nothing that grows with the number of steps
         if not hasattr(self, "_bad_dev"):
             self._bad_dev = torch.zeros(1, dtype=torch.int64, device=comm.gsq.device)
         bad = ~torch.isfinite(comm.gsq + sg.square().sum())
+        if local_bad is not None:
+            bad = bad | local_bad
         self._bad_dev += bad.to(torch.int64)
         if self.overlap_check and self.steps == 2:
             self.check_mismatches += comm.cross_check(self)
@@ -446,6 +450,9 @@ class MuonLocal:
 
     @torch.no_grad()
     def step(self, grad_scale: float):
+        """Returns a one-element bool tensor, true when any expert gradient of this step was non-finite (None without
+        expert groups); no host synchronisation."""
+        bad = None
         for g in self.groups:
             for p in g["params"]:
                 st = self.state.setdefault(p, {})
@@ -456,8 +463,15 @@ class MuonLocal:
                     st["second"] = torch.zeros((*p.shape[:-2], r, 1) if r >= c else (*p.shape[:-2], 1, c),
                                                dtype=torch.float32, device=p.device)
                 grad = p.main_grad * grad_scale
+                # per-matrix finiteness gate: an expert whose gradient holds a non-finite value sits the step out
+                # (momentum decays, weight decay applies), as the fused kernels do element-wise for the shared matrices
+                fin = torch.isfinite(grad).all(dim=-1, keepdim=True).all(dim=-2, keepdim=True)
+                grad = torch.where(fin, grad, torch.zeros_like(grad))
+                nb = (~fin).any().reshape(1)
+                bad = nb if bad is None else bad | nb
                 nd = self.ns_dtype or (torch.bfloat16 if p.is_cuda else torch.float32)
                 RF.muon_update(grad, st["master"], st["momentum"], st["second"], momentum=g["momentum"],
                                beta2=g["beta2"], lr=g["lr"], wd=g["weight_decay"], ns_steps=g["ns_steps"], ns_dtype=nd,
                                ns_fn=LeanDistMuonAdamW._ns_fn(p))     # the experts' Newton-Schulz on the tcgen05 GEMMs too
                 p.copy_(st["master"])
+        return bad
