@@ -24,18 +24,21 @@ def _deq(q, e, axis):
     return RF.mx_dequantize(q.view(torch.float8_e4m3fn), e, axis)
 
 
+@pytest.mark.parametrize("r,c", [(320, 512), (1000, 1280), (4096 + 17, 384)])
 @pytest.mark.parametrize("group_r,group_c", [(128, 128), (224, 256)])
-def test_dual_quantiser_matches_emulation(group_r, group_c):
+def test_dual_quantiser_matches_emulation(group_r, group_c, r, c):
+    """Whole and ragged row counts (a last block of fewer than 32 rows is quantised as a block of its own)."""
     from them_bones_b200.ops import mxfp8 as MX
     from them_bones_b200.ref import functional as RF
     torch.manual_seed(0)
-    r, c = 320, 512
     x = (torch.randn(r, c, device="cuda") * torch.logspace(-4, 2, r, device="cuda")[:, None]).bfloat16()
     x[5, 64:96] = 0
     x[32:64, 7] = 0
     qr, sfr, qc, sfc = MX.quant2(x, col=True, group_r=group_r, group_c=group_c)
     rr, er = RF.mx_quantize(x.float(), -1)
-    rc, ec = RF.mx_quantize(x.float(), 0)                       # scales [c, r/32]
+    xp = torch.nn.functional.pad(x.float(), (0, 0, 0, -r % 32))
+    rc, ec = RF.mx_quantize(xp, 0)                              # scales [c, ceil(r/32)]
+    rc = rc[:r]
     torch.cuda.synchronize()
     assert torch.equal(_unpack_sf2(sfr, r, c, group_r), er)
     assert torch.equal(qr.view(torch.float8_e4m3fn).float(), rr.float())

@@ -784,101 +784,178 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
 
 // ---------------------------------------------------------------------------------------------------------------
 // Quantiser for both axes in one pass: x bf16 [R, C] -> q_row (blocks of 32 along C) and q_col (blocks of 32 along R),
-// each with its scale chunks.  Same thread mapping as the GEMM epilogue: a warp takes 32 rows, a lane one row and 32
-// consecutive columns at a time (64 contiguous bytes: two full sectors), two such chunks per warp.
+// each with its scale chunks.  Persistent: one CTA per SM, twelve warps, each warp a pipeline of its own.  A warp tile is
+// 32 rows x 128 columns (one K block of the row copy, so a row's four scale bytes leave as one 32-bit store); its 32
+// rows of 256 bytes arrive as bulk asynchronous copies (one per lane) in one of the warp's two 8 KB stages, signalled
+// by an mbarrier.  The warp copies a landed tile into registers, hands the stage straight back to the copy engine for
+// the tile after next, and then does the arithmetic, so that about two tiles per warp (190 KB per SM) are in flight
+// whatever the arithmetic is doing.  (With plain loads the kernel waited on them: 13 instructions per value, 35 % of
+// the issue slots, 47 % of the DRAM bandwidth, nearly all stalls on the loads' scoreboard.)
+// Eight threads per row: thread (rsub = lane / 8, piece = lane % 8) holds the 8 values of columns piece * 8 .. + 7 of
+// each 64-column half in rows rsub, rsub + 4, ..., rsub + 28.  A quarter warp reads 128 contiguous bytes of shared
+// memory (conflict free) and stores 64 contiguous bytes per row; a row block's maximum needs two shuffles among the
+// four threads of the block and a column block's maximum two among the four threads of the column group.
+// All 32 rows (and the 32 columns of a chunk) fall into one scale tile because the tile heights are multiples of 32,
+// so the scale offsets are a base plus a lane term: no per-row division and no 64-bit index arithmetic.  Values are
+// scaled as packed bf16 pairs (a power of two: exact) before the conversion.
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int kQuantChunks = 2;                    // 32-column chunks per warp (64 columns)
-__device__ __forceinline__ uint2 q_pack_e4m3x8(const float (&f)[8], float inv) {
-  return make_uint2(q_pack_e4m3x4(f[0] * inv, f[1] * inv, f[2] * inv, f[3] * inv), q_pack_e4m3x4(f[4] * inv, f[5] * inv, f[6] * inv, f[7] * inv));
+constexpr int QD_WARPS = 12, QD_STAGES = 2;
+constexpr int QD_TILE_BYTES = 32 * 256;
+constexpr int QD_BARS_BASE = QD_WARPS * QD_STAGES * QD_TILE_BYTES;
+constexpr int QD_SMEM_BYTES = QD_BARS_BASE + QD_WARPS * QD_STAGES * 8 + 16;
+__device__ __forceinline__ uint32_t q_mul_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
 }
-__global__ void __launch_bounds__(256, 2)
+// From the bf16 bit pattern of a block's largest magnitude: the biased UE8M0 exponent of the smallest power of two 2^e with
+// amax / 2^e <= 448, and 2^-e as a bf16 pair (the same rule as q_scale_pow2; an all-zero block gets exponent 0).
+__device__ __forceinline__ uint32_t q_scale_bf16(uint32_t amax16, uint32_t& biased) {
+  const int b = max((int)(amax16 >> 7) - 8 + ((amax16 & 0x7fu) > 0x60u ? 1 : 0), 0);
+  biased = (uint32_t)b;
+  return ((uint32_t)(254 - b) << 7) * 0x10001u;
+}
+// 8 bf16 values (4 packed words) times their packed power-of-two factors -> 8 E4M3 bytes
+__device__ __forceinline__ uint2 q_cvt_e4m3x8(const uint32_t (&w)[4], const uint32_t (&inv2)[4]) {
+  uint32_t s[4];
+#pragma unroll
+  for (int t = 0; t < 4; ++t) s[t] = q_mul_bf16x2(w[t], inv2[t]);
+  return make_uint2(q_pack_e4m3x4(__uint_as_float(s[0] << 16), __uint_as_float(s[0] & 0xffff0000u), __uint_as_float(s[1] << 16),
+                                  __uint_as_float(s[1] & 0xffff0000u)),
+                    q_pack_e4m3x4(__uint_as_float(s[2] << 16), __uint_as_float(s[2] & 0xffff0000u), __uint_as_float(s[3] << 16),
+                                  __uint_as_float(s[3] & 0xffff0000u)));
+}
+// part of a scale offset shared by rows r0 .. r0 + 31 of one scale tile (r0 and the tile height multiples of 32) at
+// K block `kb`; a row r0 + j adds j * 16 and the 32-wide block `ks` of the K block adds ks
+__device__ __forceinline__ size_t q_sf_base32(uint32_t r0, uint32_t kb, uint32_t kblocks, int group) {
+  const uint32_t g = r0 / (uint32_t)group;
+  const uint32_t t0 = r0 - g * (uint32_t)group;
+  const uint32_t chunks = ((uint32_t)group + 127u) >> 7;
+  return ((size_t)g * kblocks + kb) * (size_t)(chunks * 512u) + (size_t)((t0 >> 7) * 512u + ((t0 & 127u) >> 5) * 4u);
+}
+template <bool kRow, bool kCol>
+__global__ void __launch_bounds__(QD_WARPS * 32, 1)
 mx_quant_dual_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t* __restrict__ qr, uint8_t* __restrict__ sfr, int group_r,
-                     uint8_t* __restrict__ qc, uint8_t* __restrict__ sfc, int group_c, long long R, long long C) {
-  // A warp takes 32 rows x 64 columns, 32 x 32 at a time, four threads per row: thread (sub = lane / 4, piece = lane % 4)
-  // holds the 8 values of columns piece * 8 .. + 7 in rows sub, sub + 8, sub + 16, sub + 24.  Every load and store
-  // instruction then covers 8 whole row segments (with a thread per row it touches 32 cache lines and the kernel was
-  // bound by the load/store unit at 40 % of the copy bandwidth), a row block's maximum needs two shuffles among the four
-  // threads of the row and a column block's maximum three among the eight threads of the column group.
-  const int lane = threadIdx.x & 31, sub = lane >> 2, piece = lane & 3;
-  const long long tiles_c = C / (32 * kQuantChunks);
-  const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const long long tr = wid / tiles_c, tc = wid - tr * tiles_c;
-  const long long row0 = tr * 32;
-  if (row0 >= R) return;                                        // warp-uniform
-  const long long kb_c = (C + 127) >> 7, kb_r = (R + 127) >> 7;
-  uint4 raw[kQuantChunks][4];
+                     uint8_t* __restrict__ qc, uint8_t* __restrict__ sfc, int group_c, long long R, long long C, uint32_t n_tiles, int* err) {
+  extern __shared__ __align__(128) uint8_t qd_smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, rsub = lane >> 3, piece = lane & 7;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(qd_smem + QD_BARS_BASE + QD_WARPS * QD_STAGES * 8);
+  const uint32_t stage0 = smem_u32(qd_smem) + (uint32_t)(warp * QD_STAGES * QD_TILE_BYTES);
+  const uint32_t bar0 = smem_u32(qd_smem) + (uint32_t)(QD_BARS_BASE + warp * QD_STAGES * 8);
+  if (threadIdx.x == 0) *abort_flag = 0;
+  if (lane == 0) {
 #pragma unroll
-  for (int c = 0; c < kQuantChunks; ++c) {
+    for (int s = 0; s < QD_STAGES; ++s) mbar_init(bar0 + 8u * s, 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  const uint32_t tiles_c = (uint32_t)(C >> 7);
+  const uint32_t stride = gridDim.x * QD_WARPS;
+  const uint32_t kb_c = (uint32_t)((C + 127) >> 7), kb_r = (uint32_t)((R + 127) >> 7);
+  // the rows of tile `tile` into stage s: every lane copies one row of 256 bytes
+  auto issue = [&](uint32_t tile, int s) {
+    const uint32_t tr = tile / tiles_c, tc = tile - tr * tiles_c;
+    const long long row0 = (long long)tr * 32;
+    const int rows_here = (int)min((long long)32, R - row0);
+    if (lane == 0) mbar_arrive_expect_tx(bar0 + 8u * s, (uint32_t)rows_here * 256u);
+    __syncwarp();
+    if (lane < rows_here)
+      bulk_load(stage0 + (uint32_t)(s * QD_TILE_BYTES + lane * 256), x + (row0 + lane) * ldx + (long long)tc * 128, 256u, bar0 + 8u * s);
+  };
+  const uint32_t first = blockIdx.x * QD_WARPS + warp;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const long long row = row0 + i * 8 + sub;
-      raw[c][i] = row < R ? *reinterpret_cast<const uint4*>(x + row * ldx + (tc * kQuantChunks + c) * 32 + piece * 8) : make_uint4(0u, 0u, 0u, 0u);
+  for (int s = 0; s < QD_STAGES; ++s)
+    if (first + s * stride < n_tiles) issue(first + s * stride, s);
+  int n = 0;
+  for (uint32_t tile = first; tile < n_tiles; tile += stride, ++n) {
+    const int s = n & 1;
+    const bool got = mbar_wait(bar0 + 8u * s, (uint32_t)((n >> 1) & 1), abort_flag, err, ERR_WAIT_FULL);
+    if (!__all_sync(0xffffffffu, got)) break;
+    const uint32_t tr = tile / tiles_c, tc = tile - tr * tiles_c;
+    const long long row0 = (long long)tr * 32;
+    const int rows_here = (int)min((long long)32, R - row0);
+    uint4 raw[2][8];
+    {
+      const uint8_t* st = qd_smem + (warp * QD_STAGES + s) * QD_TILE_BYTES + rsub * 256 + piece * 16;
+#pragma unroll
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          raw[h][i] = i * 4 + rsub < rows_here ? *reinterpret_cast<const uint4*>(st + i * 1024 + h * 128) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    // the stage goes back to the copy engine for the tile after next
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (tile + 2 * stride < n_tiles) issue(tile + 2 * stride, s);
+
+    const long long q0 = (row0 + rsub) * C + (long long)tc * 128 + piece * 8;   // this thread's first output byte, either copy
+    const long long qstep = 4 * C;
+    uint32_t rowsf[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};      // scale bytes of the row's blocks that this thread saw
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int c = 2 * h + (piece >> 2);                        // this thread's 32-column chunk of the half
+      uint32_t cm[4] = {0u, 0u, 0u, 0u};                         // packed bf16 maxima of this thread's 8 columns over its 8 rows
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const uint32_t w[4] = {raw[h][i].x, raw[h][i].y, raw[h][i].z, raw[h][i].w};
+        uint32_t a[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          a[t] = w[t] & 0x7fff7fffu;
+          if (kCol) cm[t] = q_max_bf16x2(cm[t], a[t]);
+        }
+        if (kRow) {
+          uint32_t m2 = q_max_bf16x2(q_max_bf16x2(a[0], a[1]), q_max_bf16x2(a[2], a[3]));
+          m2 = q_max_bf16x2(m2, __shfl_xor_sync(0xffffffffu, m2, 1));
+          m2 = q_max_bf16x2(m2, __shfl_xor_sync(0xffffffffu, m2, 2));
+          uint32_t biased;
+          const uint32_t inv = q_scale_bf16(max(m2 & 0xffffu, m2 >> 16), biased);
+          const uint32_t inv2[4] = {inv, inv, inv, inv};
+          const uint2 o = q_cvt_e4m3x8(w, inv2);
+          if (i * 4 + rsub < rows_here) *reinterpret_cast<uint2*>(qr + q0 + i * qstep + h * 64) = o;
+          rowsf[i] |= biased << (8 * c);
+        }
+      }
+      if (kCol) {
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+          cm[t] = q_max_bf16x2(cm[t], __shfl_xor_sync(0xffffffffu, cm[t], 8));
+          cm[t] = q_max_bf16x2(cm[t], __shfl_xor_sync(0xffffffffu, cm[t], 16));
+        }
+        // thread (rsub, piece) derives the scales of columns piece * 8 + 2 rsub and + 1 of the half (word rsub of its four)
+        const uint32_t pair = (rsub & 2) ? ((rsub & 1) ? cm[3] : cm[2]) : ((rsub & 1) ? cm[1] : cm[0]);
+        uint32_t b_lo, b_hi;
+        const uint32_t inv_lo = q_scale_bf16(pair & 0xffffu, b_lo), inv_hi = q_scale_bf16(pair >> 16, b_hi);
+        const uint32_t my_inv2 = (inv_lo & 0xffffu) | (inv_hi & 0xffff0000u);
+        // the transposed operand's "rows" are the columns; its K block is the 128-row block of row0
+        uint8_t* sp = sfc + q_sf_base32(tc * 128u + (uint32_t)c * 32u, (uint32_t)(row0 >> 7), kb_r, group_c) +
+                      (size_t)(((piece & 3) * 8 + 2 * rsub) * 16 + (int)((row0 & 127) >> 5));
+        sp[0] = (uint8_t)b_lo;
+        sp[16] = (uint8_t)b_hi;
+        uint32_t inv2[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) inv2[t] = __shfl_sync(0xffffffffu, my_inv2, (t << 3) | piece);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const uint32_t w[4] = {raw[h][i].x, raw[h][i].y, raw[h][i].z, raw[h][i].w};
+          const uint2 o = q_cvt_e4m3x8(w, inv2);
+          if (i * 4 + rsub < rows_here) *reinterpret_cast<uint2*>(qc + q0 + i * qstep + h * 64) = o;
+        }
+      }
+    }
+    if (kRow) {
+      // pieces 0 and 4 of a row hold the scale bytes of chunks 0, 2 and 1, 3
+      uint8_t* rp = sfr + q_sf_base32((uint32_t)row0, tc, kb_c, group_r) + (size_t)(rsub * 16);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const uint32_t v = rowsf[i] | __shfl_xor_sync(0xffffffffu, rowsf[i], 4);
+        if (piece == 0 && i * 4 + rsub < rows_here) *reinterpret_cast<uint32_t*>(rp + i * 64) = v;
+      }
     }
   }
-#pragma unroll
-  for (int c = 0; c < kQuantChunks; ++c) {
-    const long long col0 = (tc * kQuantChunks + c) * 32;
-    uint32_t cm[4] = {0u, 0u, 0u, 0u};                           // packed bf16 maxima of this thread's 8 columns over its 4 rows
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const long long row = row0 + i * 8 + sub;
-      const uint32_t w[4] = {raw[c][i].x, raw[c][i].y, raw[c][i].z, raw[c][i].w};
-      uint32_t a[4];
-#pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        a[t] = w[t] & 0x7fff7fffu;
-        cm[t] = q_max_bf16x2(cm[t], a[t]);
-      }
-      if (qr != nullptr) {
-        const uint32_t m2 = q_max_bf16x2(q_max_bf16x2(a[0], a[1]), q_max_bf16x2(a[2], a[3]));
-        float amax = fmaxf(__uint_as_float(m2 << 16), __uint_as_float(m2 & 0xffff0000u));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-        int biased;
-        const float inv = q_scale_pow2(amax, biased);
-        float f[8];
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const float2 u = unpack_bf16(w[t]);
-          f[2 * t] = u.x;
-          f[2 * t + 1] = u.y;
-        }
-        if (row < R) {
-          *reinterpret_cast<uint2*>(qr + row * C + col0 + piece * 8) = q_pack_e4m3x8(f, inv);
-          if (piece == 0) sfr[q_sf_offset(row, col0, kb_c, group_r)] = (uint8_t)biased;
-        }
-      }
-    }
-    if (qc != nullptr) {
-#pragma unroll
-      for (int t = 0; t < 4; ++t) {
-        cm[t] = q_max_bf16x2(cm[t], __shfl_xor_sync(0xffffffffu, cm[t], 4));
-        cm[t] = q_max_bf16x2(cm[t], __shfl_xor_sync(0xffffffffu, cm[t], 8));
-        cm[t] = q_max_bf16x2(cm[t], __shfl_xor_sync(0xffffffffu, cm[t], 16));
-      }
-      // thread (sub, piece) derives the scale of column piece * 8 + sub and hands it to the eight threads of its group
-      const uint32_t pair = (sub & 4) ? ((sub & 2) ? cm[3] : cm[2]) : ((sub & 2) ? cm[1] : cm[0]);
-      const float my_amax = __uint_as_float((sub & 1) ? (pair & 0xffff0000u) : (pair << 16));
-      int biased;
-      const float my_inv = q_scale_pow2(my_amax, biased);
-      sfc[q_sf_offset(col0 + piece * 8 + sub, row0, kb_r, group_c)] = (uint8_t)biased;
-      float inv[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) inv[e] = __shfl_sync(0xffffffffu, my_inv, (e << 2) | piece);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const long long row = row0 + i * 8 + sub;
-        const uint32_t w[4] = {raw[c][i].x, raw[c][i].y, raw[c][i].z, raw[c][i].w};
-        float f[8];
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-          const float2 u = unpack_bf16(w[t]);
-          f[2 * t] = u.x * inv[2 * t];
-          f[2 * t + 1] = u.y * inv[2 * t + 1];
-        }
-        if (row < R) *reinterpret_cast<uint2*>(qc + row * C + col0 + piece * 8) = q_pack_e4m3x8(f, 1.0f);
-      }
-    }
+  // a warp that gave up may still have a copy on its way into shared memory: stay a moment before the CTA's memory goes
+  if (*abort_flag) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
   }
 }
 
@@ -939,10 +1016,29 @@ long long bones_mx2_sf_bytes(long long rows, long long K, int group) {
 int bones_mx2_quant(const void* x, long long ldx, void* qr, void* sfr, int group_r, void* qc, void* sfc, int group_c, long long R, long long C,
                     void* stream) {
   if ((C % 128) || (ldx % 8) || ((uintptr_t)x & 15)) return -2;
-  if (R == 0) return 0;
-  const long long warps = ((R + 31) / 32) * (C / (32 * kQuantChunks));
-  mx_quant_dual_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, ldx, (uint8_t*)qr, (uint8_t*)sfr, group_r,
-                                                                                      (uint8_t*)qc, (uint8_t*)sfc, group_c, R, C);
+  if ((qr && ((group_r % 32) || ((uintptr_t)sfr & 3))) || (qc && (group_c % 32)) || R >= (1LL << 31) || C >= (1LL << 31)) return -2;
+  if (R == 0 || (!qr && !qc)) return 0;
+  const long long tiles = ((R + 31) / 32) * (C / 128);
+  if (tiles >= (1LL << 30)) return -2;
+  static bool attr_set = false;
+  if (!attr_set) {
+    BONES_CHECK(cudaFuncSetAttribute(mx_quant_dual_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, QD_SMEM_BYTES));
+    BONES_CHECK(cudaFuncSetAttribute(mx_quant_dual_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, QD_SMEM_BYTES));
+    BONES_CHECK(cudaFuncSetAttribute(mx_quant_dual_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, QD_SMEM_BYTES));
+    attr_set = true;
+  }
+  int dev = 0, sms = 0;
+  BONES_CHECK(cudaGetDevice(&dev));
+  BONES_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  const unsigned grid = (unsigned)std::min<long long>(sms, (tiles + QD_WARPS - 1) / QD_WARPS);
+  int* err = error_word();
+#define BONES_QUANT_LAUNCH(ROW, COL)                                                                                       \
+  mx_quant_dual_kernel<ROW, COL><<<grid, QD_WARPS * 32, QD_SMEM_BYTES, (cudaStream_t)stream>>>(                             \
+      (const __nv_bfloat16*)x, ldx, (uint8_t*)qr, (uint8_t*)sfr, group_r, (uint8_t*)qc, (uint8_t*)sfc, group_c, R, C, (uint32_t)tiles, err)
+  if (qr && qc) BONES_QUANT_LAUNCH(true, true);
+  else if (qr) BONES_QUANT_LAUNCH(true, false);
+  else if (qc) BONES_QUANT_LAUNCH(false, true);
+#undef BONES_QUANT_LAUNCH
   return (int)cudaGetLastError();
 }
 
