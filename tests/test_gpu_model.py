@@ -135,11 +135,13 @@ def test_bounded_peer_wait_expires_with_an_error_code():
 @pytest.mark.parametrize("capped", [0, 1])
 @pytest.mark.parametrize("vocab,ld", [(65536, 65536), (50304, 50432), (8192, 8192), (2048, 2048)])
 def test_softcap_ce_row_kernel_matches_reference(vocab, ld, capped, smooth):
-    """Loss-head kernel at full vocabulary width: per-row loss and the in-place logit gradient against fp32 PyTorch."""
+    """Loss-head kernel at full vocabulary width: per-row loss and the in-place logit gradient against fp32 PyTorch.
+    More rows than SMs, so the persistent row kernel's CTAs walk several rows each (the prefetch of the next row into the
+    shared-memory buffer and the barrier phases are exercised)."""
     from them_bones_b200.ops import _lib as L
     from them_bones_b200.ops.cuda import _F, _I, _L
     torch.manual_seed(1)
-    m, cap = 24, 15.0
+    m, cap = 333, 15.0
     lg = (torch.randn(m, ld, device="cuda") * 6).bfloat16()
     tg = torch.randint(0, vocab, (m,), device="cuda")
     tg[3] = -1

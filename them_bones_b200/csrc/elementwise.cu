@@ -616,90 +616,201 @@ __device__ __forceinline__ void ce_row_grad(const __half2 (&th)[8][4], __nv_bflo
   }
 }
 
+// Row kernel for vocabularies of 8192 .. 65536: persistent, one CTA of 1024 threads per SM walking rows.  A row's logits
+// arrive as four bulk asynchronous copies (quarter rows of up to 32 KB) in shared memory, each signalled by an mbarrier.
+// A thread takes its 16 values of a quarter into registers (as tanh values in half precision); the last of the CTA's 32
+// warps to have done so hands the quarter straight back to the copy engine for the CTA's next row, so reads are in
+// flight through both passes of a row (sum of exponentials; probabilities, gradient and stores).  With a CTA per row and
+// plain loads the row's read, its two exponential passes (2 x 65536 results at 16 per clock) and its write ran one
+// after the other, about 17 000 clocks per row where each alone needs 8 000 to 9 000.
+constexpr int CE_Q_COLS = 16384;
+constexpr int CE_SMEM_BYTES = 4 * CE_Q_COLS * 2 + 64;
+// Second pass for logits that the GEMM epilogue already soft-capped (z = cap * tanh(. / cap) as stored): the thread kept
+// its 64 logits as the bf16 pairs they arrived as, so there is no conversion on either side; p = exp2(z log2(e) - lw),
+// d tanh = 1 - (z / cap)^2.  SMOOTH: label smoothing's uniform term is live.
+template <bool FIX, bool SMOOTH>
+__device__ __forceinline__ void ce_row_grad_capped(const uint32_t (&zw)[8][4], __nv_bfloat16* d, int V, float nic2, float lw, float w_uni,
+                                                   int tg, float w_tgt, int t2, float a2, int t3, float a3) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int c = (i * 1024 + threadIdx.x) * 8;
+    if (c >= V) continue;
+    uint32_t o[4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const float z0 = __uint_as_float(zw[i][t] << 16), z1 = __uint_as_float(zw[i][t] & 0xffff0000u);
+      float p0 = ex2_fast(fmaf(z0, 1.4426950408889634f, -lw)), p1 = ex2_fast(fmaf(z1, 1.4426950408889634f, -lw));
+      if (SMOOTH) { p0 -= w_uni; p1 -= w_uni; }
+      if (FIX) {
+        const int c0i = c + 2 * t, c1i = c0i + 1;
+        if (c0i == tg) p0 -= w_tgt;
+        if (c1i == tg) p1 -= w_tgt;
+        if (c0i == t2) p0 -= a2;
+        if (c1i == t2) p1 -= a2;
+        if (c0i == t3) p0 -= a3;
+        if (c1i == t3) p1 -= a3;
+      }
+      o[t] = pack_bf16(p0 * fmaf(z0 * nic2, z0, 1.0f), p1 * fmaf(z1 * nic2, z1, 1.0f));
+    }
+    *reinterpret_cast<uint4*>(d + c) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
 template <bool CAPPED>
 __global__ void __launch_bounds__(1024, 1)
 softcap_ce_row_kernel(const __nv_bfloat16* __restrict__ logits, long long ldl, const long long* __restrict__ targets, int V, float cap,
                       float* __restrict__ nll, __nv_bfloat16* dlogits, const float* __restrict__ row_w, const float* __restrict__ n_valid,
-                      float inv_loss_div, int M, AuxTargets aux) {
+                      float inv_loss_div, int M, AuxTargets aux, int* err) {
   constexpr bool capped = CAPPED;
-  const int row = blockIdx.x;
-  if (row >= M) return;
-  const __nv_bfloat16* l = logits + (size_t)row * ldl;
-  const long long tgt = targets[row];
-  const float inv_cap = 1.0f / cap, k2 = cap * 1.4426950408889634f;
+  extern __shared__ __align__(128) uint8_t ce_smem[];
   __shared__ float red[32], red_t[32];
   __shared__ float s_total, s_tsum;
-  uint4 raw[8];
+  __shared__ int s_abort, s_taken[4];
+  const uint32_t buf = smem_u32(ce_smem), bar = buf + 4u * CE_Q_COLS * 2u;
+  const float inv_cap = 1.0f / cap, k2 = cap * 1.4426950408889634f;
+  if (threadIdx.x == 0) {
+    s_abort = 0;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int c = (i * 1024 + threadIdx.x) * 8;
-    raw[i] = make_uint4(0, 0, 0, 0);
-    if (c < V) raw[i] = *reinterpret_cast<const uint4*>(l + c);
+    for (int q = 0; q < 4; ++q) { mbar_init(bar + 8u * q, 1); s_taken[q] = 0; }
+    fence_barrier_init();
   }
-  __half2 th[8][4];
-  float s = 0.f, st = 0.f;
+  __syncthreads();
+  auto issue = [&](int row, int q) {                            // one thread: quarter q of a row
+    const int cols = min(V - q * CE_Q_COLS, CE_Q_COLS);
+    if (cols <= 0) return;
+    mbar_arrive_expect_tx(bar + 8u * q, (uint32_t)cols * 2u);
+    bulk_load(buf + (uint32_t)(q * CE_Q_COLS * 2), logits + (size_t)row * ldl + q * CE_Q_COLS, (uint32_t)cols * 2u, bar + 8u * q);
+  };
+  if (threadIdx.x == 0 && (int)blockIdx.x < M) {
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int c = (i * 1024 + threadIdx.x) * 8;
-    const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+    for (int q = 0; q < 4; ++q) issue(blockIdx.x, q);
+  }
+  const __nv_bfloat16* sl = reinterpret_cast<const __nv_bfloat16*>(ce_smem);
+  int n = 0;
+  for (int row = blockIdx.x; row < M; row += gridDim.x, ++n) {
+    const long long tgt = targets[row];
+    const bool valid = tgt >= 0 && tgt < V;
+    long long t2 = -1, t3 = -1;
+    float a2 = 0.f, a3 = 0.f;
+    if (aux.tg[0]) { t2 = aux.tg[0][row]; a2 = (t2 >= 0 && t2 < V) ? aux.w[0][row] : 0.f; }
+    if (aux.tg[1]) { t3 = aux.tg[1][row]; a3 = (t3 >= 0 && t3 < V) ? aux.w[1][row] : 0.f; }
+    // what a thread keeps of its 64 logits between the passes: the bf16 pairs themselves (already capped), or the tanh
+    // values as half pairs
+    uint32_t keep[8][4];
+    float s = 0.f, st = 0.f;                                    // sum of exponentials; sum of tanh values (of logits when capped)
+    float z_tgt = 0.f, z_2 = 0.f, z_3 = 0.f;
+    bool ok = true;
+    const bool smoothing = aux.smooth != 0.f;
 #pragma unroll
-    for (int t = 0; t < 4; ++t) {
-      const float2 f = unpack_bf16(w[t]);
-      // `capped`: the GEMM epilogue already applied cap * tanh(. / cap), only the scaling is left
-      const float t0 = capped ? f.x * inv_cap : tanh_fast(f.x * inv_cap), t1 = capped ? f.y * inv_cap : tanh_fast(f.y * inv_cap);
-      th[i][t] = __floats2half2_rn(t0, t1);
-      if (c < V) {
-        s += ex2_fast(fmaf(k2, t0, -k2)) + ex2_fast(fmaf(k2, t1, -k2));
-        st += t0 + t1;
+    for (int q = 0; q < 4; ++q) {
+      const bool live = V > q * CE_Q_COLS;                      // uniform
+      if (live) ok = ok && mbar_wait(bar + 8u * q, (uint32_t)(n & 1), &s_abort, err, ERR_WAIT_FULL);
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int i = q * 2 + j;
+        const int c = (i * 1024 + threadIdx.x) * 8;
+        uint4 raw = make_uint4(0, 0, 0, 0);
+        if (c < V && ok) raw = *reinterpret_cast<const uint4*>(ce_smem + (size_t)c * 2);
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+        if (capped) {
+          // the GEMM epilogue already applied cap * tanh(. / cap): exp2(k2 t - k2) = exp2(z log2(e) - k2)
+#pragma unroll
+          for (int t = 0; t < 4; ++t) keep[i][t] = w[t];
+          if (c < V) {
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              const float z0 = __uint_as_float(w[t] << 16), z1 = __uint_as_float(w[t] & 0xffff0000u);
+              s += ex2_fast(fmaf(z0, 1.4426950408889634f, -k2)) + ex2_fast(fmaf(z1, 1.4426950408889634f, -k2));
+              if (smoothing) st += z0 + z1;
+            }
+          }
+        } else {
+#pragma unroll
+          for (int t = 0; t < 4; ++t) {
+            const float t0 = tanh_fast(__uint_as_float(w[t] << 16) * inv_cap), t1 = tanh_fast(__uint_as_float(w[t] & 0xffff0000u) * inv_cap);
+            const __half2 hh = __floats2half2_rn(t0, t1);
+            keep[i][t] = *reinterpret_cast<const uint32_t*>(&hh);
+            if (c < V) {
+              s += ex2_fast(fmaf(k2, t0, -k2)) + ex2_fast(fmaf(k2, t1, -k2));
+              st += t0 + t1;
+            }
+          }
+        }
+      }
+      if (live) {
+        // the target logits come from the row buffer while it still holds this row: the gradient may overwrite the
+        // logits in global memory, and the quarter is refilled once every warp has taken it
+        if (threadIdx.x == 0 && ok) {
+          if (valid && (int)(tgt / CE_Q_COLS) == q) z_tgt = __bfloat162float(sl[tgt]);
+          if (a2 != 0.f && (int)(t2 / CE_Q_COLS) == q) z_2 = __bfloat162float(sl[t2]);
+          if (a3 != 0.f && (int)(t3 / CE_Q_COLS) == q) z_3 = __bfloat162float(sl[t3]);
+        }
+        __threadfence_block();                                  // this thread's reads of the quarter are done
+        __syncwarp();
+        if ((threadIdx.x & 31) == 0 && atomicAdd(&s_taken[q], 1) == 31) {
+          s_taken[q] = 0;                                       // last of the 32 warps: the quarter is free
+          if (ok && row + (int)gridDim.x < M) {
+            fence_proxy_async_smem();
+            issue(row + gridDim.x, q);
+          }
+        }
       }
     }
+    if (!capped) { z_tgt = cap * tanh_fast(z_tgt * inv_cap); z_2 = cap * tanh_fast(z_2 * inv_cap); z_3 = cap * tanh_fast(z_3 * inv_cap); }
+    s = warp_sum(s);
+    st = warp_sum(st);
+    if ((threadIdx.x & 31) == 0) { red[threadIdx.x >> 5] = s; red_t[threadIdx.x >> 5] = st; }
+    if (!__syncthreads_and(ok ? 1 : 0)) break;
+    if (threadIdx.x < 32) {
+      float v = red[threadIdx.x], vt = red_t[threadIdx.x];
+      v = warp_sum(v);
+      vt = warp_sum(vt);
+      if (threadIdx.x == 0) { s_total = v; s_tsum = vt; }
+    }
+    __syncthreads();
+    const float lse2 = log2f(s_total) + k2;          // log-sum-exp in base-2 units
+    const float sm = aux.smooth, mean_z = (capped ? 1.0f : cap) * s_tsum / (float)V;
+    if (threadIdx.x == 0) {
+      float out = 0.f;
+      if (valid) out = lse2 * 0.6931471805599453f - (1.0f - sm) * z_tgt - sm * mean_z;
+      nll[row] = out;
+      if (aux.nll_aux) {
+        const float lse = lse2 * 0.6931471805599453f;
+        float oa = 0.f;
+        if (a2 != 0.f) oa += a2 * (lse - z_2);
+        if (a3 != 0.f) oa += a3 * (lse - z_3);
+        aux.nll_aux[row] = oa;
+      }
+    }
+    if (!dlogits) continue;
+    float w = 0.f;
+    if (valid) w = row_w ? row_w[row] : inv_loss_div / fmaxf(1.0f, *n_valid);
+    const float wsum = w + a2 + a3;
+    const float w_tgt = w * (1.0f - sm), w_uni = w * sm / (float)V;
+    // a row without any live target has weight sum 0: lw = +inf makes every probability term exactly 0
+    const float lw = wsum > 0.f ? lse2 - log2f(wsum) : __int_as_float(0x7f800000);
+    const int tgi = (valid && w_tgt != 0.f) ? (int)tgt : -1, t2i = a2 != 0.f ? (int)t2 : -1, t3i = a3 != 0.f ? (int)t3 : -1;
+    // thread x holds columns (i * 1024 + x) * 8 .. + 7, so column c belongs to thread (c >> 3) & 1023
+    const int me = threadIdx.x;
+    const bool owner = (tgi >= 0 && ((tgi >> 3) & 1023) == me) || (t2i >= 0 && ((t2i >> 3) & 1023) == me) ||
+                       (t3i >= 0 && ((t3i >> 3) & 1023) == me);
+    __nv_bfloat16* d = dlogits + (size_t)row * ldl;
+    if (capped) {
+      const float nic2 = -inv_cap * inv_cap;
+      if (owner) ce_row_grad_capped<true, true>(keep, d, V, nic2, lw, w_uni, tgi, w_tgt, t2i, a2, t3i, a3);
+      else if (smoothing) ce_row_grad_capped<false, true>(keep, d, V, nic2, lw, w_uni, tgi, w_tgt, t2i, a2, t3i, a3);
+      else ce_row_grad_capped<false, false>(keep, d, V, nic2, lw, w_uni, tgi, w_tgt, t2i, a2, t3i, a3);
+    } else {
+      const __half2 (&th)[8][4] = reinterpret_cast<const __half2 (&)[8][4]>(keep);
+      if (owner) ce_row_grad<true>(th, d, V, k2, lw, w_uni, tgi, w_tgt, t2i, a2, t3i, a3);
+      else ce_row_grad<false>(th, d, V, k2, lw, w_uni, tgi, w_tgt, t2i, a2, t3i, a3);
+    }
+    for (int c = V + threadIdx.x; c < ldl; c += blockDim.x) d[c] = __float2bfloat16(0.f);
   }
-  s = warp_sum(s);
-  st = warp_sum(st);
-  if ((threadIdx.x & 31) == 0) { red[threadIdx.x >> 5] = s; red_t[threadIdx.x >> 5] = st; }
-  __syncthreads();
-  if (threadIdx.x < 32) {
-    float v = red[threadIdx.x], vt = red_t[threadIdx.x];
-    v = warp_sum(v);
-    vt = warp_sum(vt);
-    if (threadIdx.x == 0) { s_total = v; s_tsum = vt; }
+  // a CTA that gave up may still have a copy on its way into shared memory: stay a moment before the memory goes
+  if (s_abort) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
   }
-  __syncthreads();
-  const float lse2 = log2f(s_total) + k2;          // log-sum-exp in base-2 units
-  const float sm = aux.smooth, mean_z = cap * s_tsum / (float)V;
-  const bool valid = tgt >= 0 && tgt < V;
-  if (threadIdx.x == 0) {
-    float out = 0.f;
-    if (valid) out = lse2 * 0.6931471805599453f - (1.0f - sm) * (capped ? __bfloat162float(l[tgt]) : cap * tanh_fast(__bfloat162float(l[tgt]) * inv_cap)) - sm * mean_z;
-    nll[row] = out;
-  }
-  long long t2 = -1, t3 = -1;
-  float a2 = 0.f, a3 = 0.f;
-  if (aux.tg[0]) { t2 = aux.tg[0][row]; a2 = (t2 >= 0 && t2 < V) ? aux.w[0][row] : 0.f; }
-  if (aux.tg[1]) { t3 = aux.tg[1][row]; a3 = (t3 >= 0 && t3 < V) ? aux.w[1][row] : 0.f; }
-  if (threadIdx.x == 0 && aux.nll_aux) {
-    const float lse = lse2 * 0.6931471805599453f;
-    float out = 0.f;
-    if (a2 != 0.f) out += a2 * (lse - (capped ? __bfloat162float(l[t2]) : cap * tanh_fast(__bfloat162float(l[t2]) * inv_cap)));
-    if (a3 != 0.f) out += a3 * (lse - (capped ? __bfloat162float(l[t3]) : cap * tanh_fast(__bfloat162float(l[t3]) * inv_cap)));
-    aux.nll_aux[row] = out;
-  }
-  if (!dlogits) return;
-  float w = 0.f;
-  if (valid) w = row_w ? row_w[row] : inv_loss_div / fmaxf(1.0f, *n_valid);
-  const float wsum = w + a2 + a3;
-  const float w_tgt = w * (1.0f - sm), w_uni = w * sm / (float)V;
-  // a row without any live target has weight sum 0: lw = +inf makes every probability term exactly 0
-  const float lw = wsum > 0.f ? lse2 - log2f(wsum) : __int_as_float(0x7f800000);
-  const int tgi = (valid && w_tgt != 0.f) ? (int)tgt : -1, t2i = a2 != 0.f ? (int)t2 : -1, t3i = a3 != 0.f ? (int)t3 : -1;
-  // thread x holds columns (i * 1024 + x) * 8 .. + 7, so column c belongs to thread (c >> 3) & 1023
-  const int me = threadIdx.x;
-  const bool owner = (tgi >= 0 && ((tgi >> 3) & 1023) == me) || (t2i >= 0 && ((t2i >> 3) & 1023) == me) ||
-                     (t3i >= 0 && ((t3i >> 3) & 1023) == me);
-  __nv_bfloat16* d = dlogits + (size_t)row * ldl;
-  if (owner) ce_row_grad<true>(th, d, V, k2, lw, w_uni, tgi, w_tgt, t2i, a2, t3i, a3);
-  else ce_row_grad<false>(th, d, V, k2, lw, w_uni, tgi, w_tgt, t2i, a2, t3i, a3);
-  for (int c = V + threadIdx.x; c < ldl; c += blockDim.x) d[c] = __float2bfloat16(0.f);
 }
 
 // y = cap * tanh(x / cap) in fp32 from bf16 logits, first V of ldl columns
@@ -841,13 +952,24 @@ int bones_softcap_ce(const void* logits, long long ldl, const long long* targets
   AuxTargets aux;
   aux.tg[0] = tg2; aux.w[0] = w2; aux.tg[1] = tg3; aux.w[1] = w3; aux.nll_aux = nll_aux;
   aux.smooth = label_smoothing;
-  if (V <= 65536 && V >= 8192) {
+  if (V <= 65536 && V >= 8192 && ((uintptr_t)logits % 16) == 0) {
+    static bool attr_set = false;
+    if (!attr_set) {
+      BONES_CHECK(cudaFuncSetAttribute(softcap_ce_row_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, CE_SMEM_BYTES));
+      BONES_CHECK(cudaFuncSetAttribute(softcap_ce_row_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, CE_SMEM_BYTES));
+      attr_set = true;
+    }
+    int dev = 0, sms = 0;
+    BONES_CHECK(cudaGetDevice(&dev));
+    BONES_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const int grid = M < sms ? M : sms;
+    if (grid <= 0) return 0;
     if (capped)
-      softcap_ce_row_kernel<true><<<M, 1024, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, ldl, targets, V, cap, nll,
-                                                                        (__nv_bfloat16*)dlogits, row_w, n_valid, inv_loss_div, M, aux);
+      softcap_ce_row_kernel<true><<<grid, 1024, CE_SMEM_BYTES, (cudaStream_t)stream>>>(
+          (const __nv_bfloat16*)logits, ldl, targets, V, cap, nll, (__nv_bfloat16*)dlogits, row_w, n_valid, inv_loss_div, M, aux, error_word());
     else
-      softcap_ce_row_kernel<false><<<M, 1024, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, ldl, targets, V, cap, nll,
-                                                                         (__nv_bfloat16*)dlogits, row_w, n_valid, inv_loss_div, M, aux);
+      softcap_ce_row_kernel<false><<<grid, 1024, CE_SMEM_BYTES, (cudaStream_t)stream>>>(
+          (const __nv_bfloat16*)logits, ldl, targets, V, cap, nll, (__nv_bfloat16*)dlogits, row_w, n_valid, inv_loss_div, M, aux, error_word());
     return (int)cudaGetLastError();
   }
   softcap_ce_kernel<<<M, 512, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, ldl, targets, V, cap, nll, (__nv_bfloat16*)dlogits,
