@@ -219,3 +219,41 @@ def test_native_decode_with_moe_blocks_and_tables_matches_the_cached_route():
             dec2._step()
         torch.cuda.synchronize()
     assert torch.equal(full, out2) and torch.equal(full[:, :p], prompts)
+
+
+def test_local_expert_stack_matches_per_parameter_update():
+    """The stacked expert optimizer (fused prologue, one batched tcgen05 Newton-Schulz per shape, native update) against
+    the per-parameter PyTorch statement of the same Muon step on the same gradients; then a non-finite gradient entry is
+    dropped, the step is reported, and the weights stay finite."""
+    from them_bones_b200.optim.lean import MuonLocal
+    group = dict(momentum=0.95, beta2=0.95, lr=0.02, weight_decay=0.01, ns_steps=5)
+
+    def make():
+        g = torch.Generator(device="cuda").manual_seed(1)
+        shapes = [(4, 256, 128), (4, 256, 128), (4, 128, 256)]
+        return [torch.nn.Parameter((torch.randn(*s, device="cuda", generator=g) * 0.05).bfloat16()) for s in shapes]
+
+    a, b = make(), make()
+    start = [p.detach().float().clone() for p in a]
+    oa = MuonLocal([dict(group, params=a)], native=True)
+    ob = MuonLocal([dict(group, params=b)], native=False)
+    assert len(oa.stacks) == 2 and not ob.stacks
+    for p in b:
+        p.main_grad = torch.zeros_like(p, dtype=torch.float32)
+    gen = torch.Generator(device="cuda").manual_seed(2)
+    for _ in range(3):
+        for pa, pb in zip(a, b):
+            g = torch.randn(pa.shape, device="cuda", generator=gen)
+            pa.main_grad.copy_(g)
+            pb.main_grad.copy_(g)
+        bad_a, bad_b = oa.step(0.5), ob.step(0.5)
+        assert not bool(bad_a) and not bool(bad_b)
+    for pa, pb, p0 in zip(a, b, start):
+        da, db = pa.detach().float() - p0, pb.detach().float() - p0
+        rel = float((da - db).norm() / db.norm())
+        assert rel < 5e-2, rel
+        ma, mb = oa.state[pa]["master"], ob.state[pb]["master"]
+        assert float((ma - mb).norm() / (mb - p0).norm()) < 5e-2
+    a[0].main_grad[1, 3, 5] = float("nan")
+    assert bool(oa.step(0.5))
+    assert all(torch.isfinite(p).all() for p in a)

@@ -179,8 +179,6 @@ class LeanDistMuonAdamW(torch.optim.Optimizer):
             rd = self.replica_dtype or ps[0].dtype
             if g.get("moe_local"):
                 self.local_groups.append(g)
-                for p in ps:
-                    p.main_grad = torch.zeros_like(p, dtype=torch.float32)
             elif g["kind"] == "muon":
                 self.muon_units.append(_MuonUnit(g, ps, comm, rd, torch.bfloat16 if self.bf16_master else torch.float32,
                                                  counts=plan[id(g)]))
@@ -205,7 +203,11 @@ class LeanDistMuonAdamW(torch.optim.Optimizer):
             p.main_grad = self.SG[o:o + k].view(p.shape)
             self.small.append((slice(o, o + k), g))
             o += k
-        self._local = MuonLocal(self.local_groups, self.ns_dtype)
+        self._local = MuonLocal(self.local_groups, self.ns_dtype)     # stacks the expert matrices where it can
+        if not self._local.stacks:
+            for g in self.local_groups:
+                for p in g["params"]:
+                    p.main_grad = torch.zeros_like(p, dtype=torch.float32)
         self._setup_push()
 
     def _setup_push(self):
@@ -258,9 +260,7 @@ class LeanDistMuonAdamW(torch.optim.Optimizer):
         for u in self.row_units:
             u.G.zero_()
         self.SG.zero_()
-        for g in self.local_groups:
-            for p in g["params"]:
-                p.main_grad.zero_()
+        self._local.zero_grad()
         for g in self.param_groups:
             for p in g["params"]:
                 p.grad = None
@@ -425,8 +425,7 @@ class LeanDistMuonAdamW(torch.optim.Optimizer):
         ps = [p for g in self.local_groups for p in g["params"]]
         for p, st in zip(ps, sd["local"]):
             if st:
-                self._local.state[p] = {k: v.to(p.device) for k, v in st.items()}
-                p.copy_(self._local.state[p]["master"])
+                self._local.load_state(p, st)
 
     def count_bad_steps(self) -> int:
         """Steps whose reduced gradient held a non-finite value (the fused kernels zeroed those entries).  Synchronises;
@@ -442,16 +441,112 @@ class LeanDistMuonAdamW(torch.optim.Optimizer):
                 f"local expert groups: {len(self.local_groups)}; comm: {type(self.comm).__name__}")
 
 
+class _LocalStack:
+    """Local expert matrices of one shape as one stack: weights ``W [n, r, c]`` (the parameters become views of it),
+    fp32 gradient slab ``G`` (``main_grad`` views), fp32 master, momentum, second moment, and the bf16 Newton-Schulz
+    input ``X``.  One reduction-free prologue, one batched Newton-Schulz and one update for all ``n`` matrices."""
+
+    def __init__(self, group, params):
+        p0 = params[0]
+        self.group, self.params = group, params
+        self.r, self.c = p0.shape[-2:]
+        counts = [p.numel() // (self.r * self.c) for p in params]
+        self.n = n = sum(counts)
+        dev = p0.device
+        self.W = torch.empty(n, self.r, self.c, dtype=p0.dtype, device=dev)
+        self.G = torch.zeros(n, self.r, self.c, dtype=torch.float32, device=dev)
+        self.master = torch.empty(n, self.r, self.c, dtype=torch.float32, device=dev)
+        self.momentum = torch.zeros_like(self.master)
+        self.second = torch.zeros((n, self.r, 1) if self.r >= self.c else (n, 1, self.c), dtype=torch.float32, device=dev)
+        self.X = torch.empty(n, self.r, self.c, dtype=torch.bfloat16, device=dev)
+        self.sumsq = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.views = {}
+        o = 0
+        for p, e in zip(params, counts):
+            sl = slice(o, o + e)
+            self.W[sl].copy_(p.detach().reshape(e, self.r, self.c))
+            self.master[sl].copy_(p.detach().reshape(e, self.r, self.c))
+            p.data = self.W[sl].view(p.shape)
+            p.main_grad = self.G[sl].view(p.shape)
+            self.views[p] = dict(master=self.master[sl].view(p.shape), momentum=self.momentum[sl].view(p.shape),
+                                 second=self.second[sl].view(*p.shape[:-2], *self.second.shape[-2:]))
+            o += e
+
+
 class MuonLocal:
     """Expert groups: the whole gradient forms on this rank; no collective (reference: ``_moe_local_step``)."""
 
-    def __init__(self, groups, ns_dtype=None):
+    def __init__(self, groups, ns_dtype=None, native=None):
+        """``native``: stack the matrices by shape and step them with the fused prologue / batched tcgen05
+        Newton-Schulz / native update kernels (default: when every expert matrix is a bf16 CUDA tensor whose sides are
+        multiples of 32 and the plain-PyTorch path is not forced).  Otherwise one PyTorch update per parameter."""
         self.groups, self.ns_dtype, self.state = groups, ns_dtype, {}
+        ps = [p for g in groups for p in g["params"]]
+        if native is None:
+            from .. import ops
+            native = bool(ps) and not ops.reference_path() and all(
+                p.is_cuda and p.dtype == torch.bfloat16 and p.dim() >= 2 and p.shape[-1] % 32 == 0 and p.shape[-2] % 32 == 0
+                for p in ps)
+        self.stacks = []
+        if native and ps:
+            for g in groups:
+                by_shape = {}
+                for p in g["params"]:
+                    by_shape.setdefault(tuple(p.shape[-2:]), []).append(p)
+                for plist in by_shape.values():
+                    st = _LocalStack(g, plist)
+                    self.stacks.append(st)
+                    self.state.update(st.views)           # checkpoints read and restore the same tensors
+            self.gsq = torch.zeros(1, dtype=torch.float32, device=ps[0].device)
+
+    def zero_grad(self):
+        if self.stacks:
+            for st in self.stacks:
+                st.G.zero_()
+        else:
+            for g in self.groups:
+                for p in g["params"]:
+                    p.main_grad.zero_()
+
+    def load_state(self, p, st: dict):
+        """Restore one parameter's master, momentum and second moment (into the stack's views when stacked)."""
+        if p in self.state and self.stacks:
+            for k, v in st.items():
+                self.state[p][k].copy_(v)
+        else:
+            self.state[p] = {k: v.to(p.device) for k, v in st.items()}
+        p.copy_(self.state[p]["master"])
+
+    @torch.no_grad()
+    def _step_stacks(self, grad_scale: float):
+        import ctypes
+        from ..ops import _lib as L
+        from ..ops import muon_native as MN
+        _I, _L, _F = ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+        self.gsq.zero_()
+        for st in self.stacks:
+            g = st.group
+            mat = st.r * st.c
+            n = st.n * mat
+            if not hasattr(st, "src"):
+                st.src = (ctypes.c_void_p * 1)(ctypes.c_void_p(st.G.data_ptr()))
+            st.sumsq.zero_()
+            # momentum, Nesterov blend and the per-matrix sum of squares in one pass over the gradient slab (a single
+            # source: nothing to reduce); non-finite entries are dropped and show up in gsq
+            L.call("bones_rs_muon_prep", st.src, _L(0), _L(n), _I(1), _F(grad_scale), _F(g["momentum"]), L.ptr(st.momentum),
+                   L.ptr(st.X), L.ptr(st.sumsq), _L(mat), L.ptr(self.gsq), L.stream())
+            L.call("bones_muon_normalize", L.ptr(st.X), L.ptr(st.sumsq), _L(n), _L(mat), L.stream())
+            x = MN.newton_schulz(st.X, g["ns_steps"])
+            MN.muon_finish(x, st.master, st.second, beta2=g["beta2"], lr=g["lr"], wd=g["weight_decay"])
+            st.W.copy_(st.master)
+        return ~torch.isfinite(self.gsq)
 
     @torch.no_grad()
     def step(self, grad_scale: float):
         """Returns a one-element bool tensor, true when any expert gradient of this step was non-finite (None without
         expert groups); no host synchronisation."""
+        if self.stacks:
+            return self._step_stacks(grad_scale)
         bad = None
         for g in self.groups:
             for p in g["params"]:

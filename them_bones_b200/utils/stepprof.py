@@ -1,6 +1,6 @@
 """Kernel breakdown of one training step of the dense benchmark model (20 layers x 1280, vocabulary 65536, sequence 2048).
 
-    python -m them_bones_b200.utils.stepprof [--total-batch 524288] [--device-batch 64] [--mlp mxfp8] [--attn-proj bf16]
+    python -m them_bones_b200.utils.stepprof [--total-batch 524288] [--device-batch 64] [--mlp mxfp8] [--attn-proj bf16] [--moe]
     python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 -m them_bones_b200.utils.stepprof
 
 Builds the ``Trainer`` as ``bench.py`` does, runs three warm-up steps, then one step under ``torch.profiler`` (CUDA
@@ -25,14 +25,19 @@ def main():
     ap.add_argument("--mlp", default="mxfp8")
     ap.add_argument("--attn-proj", default="bf16")
     ap.add_argument("--top", type=int, default=30)
+    ap.add_argument("--moe", action="store_true", help="the MoE model: 16 experts, top-2, every MLP from layer 2 on")
     a = ap.parse_args()
-    from ..config import GPTConfig, Hyper, micro_batch_for
+    from ..config import GPTConfig, Hyper, micro_batch_for, moe_capacity_for
     from ..data.synth import SynthLoader
     from ..runtime import init_runtime
     from ..trainer import Trainer
     rt = init_runtime("cuda")
+    kw = {}
+    if a.moe:
+        kw = dict(moe_layers=tuple(range(2, a.depth)), moe_experts=16, moe_topk=2, moe_hidden=2560,
+                  moe_capacity=moe_capacity_for(1.25, 2048, 2, 16), moe_aux=0.01)
     cfg = GPTConfig(sequence_len=2048, vocab_size=65536, n_layer=a.depth, n_head=10, n_embd=1280, head_dim=128, doc_mask=True,
-                    mlp_precision=a.mlp, attn_proj_precision=a.attn_proj)
+                    mlp_precision=a.mlp, attn_proj_precision=a.attn_proj, **kw)
     h = Hyper()
     h.total_batch, h.device_batch = a.total_batch, micro_batch_for(a.total_batch, rt.world, a.device_batch, 2048)
     tr = Trainer(cfg, h, rt)
