@@ -115,16 +115,21 @@ __device__ __forceinline__ void drain_row32(uint32_t taddr, __nv_bfloat16* dst) 
   st_global_v8(dst + 16, u[2], u[3]);
 }
 
-// stats[b,h,t] = (-lse * log2(e), sum_d dO * O); sixteen lanes per (row, head), 16 bytes of each operand per lane
+// stats[b,h,t] = (-lse * log2(e), sum_d dO * O); sixteen lanes per (row, head), 16 bytes of each operand per lane.
+// Items run in the order of the output, [b, h, t] with t fastest: a group still reads 256 contiguous bytes of each
+// operand, and the statistics and the log-sum-exp values of neighbouring groups are neighbours in memory (with the
+// head fastest they were T elements apart: one 32-byte sector per 8-byte result).
 __global__ void attn_bwd_stats_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ y,
                                       const float* __restrict__ lse, float2* __restrict__ stats, long long M, int T, int H) {
   const long long item = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 4;
   const int l16 = threadIdx.x & 15;
   const long long total = M * H;
   const long long it = item < total ? item : total - 1;      // every lane takes part in the shuffles
-  const int h = (int)(it % H);
-  const long long row = it / H;
-  const long long off = it * 128 + l16 * 8;                  // == row * H * 128 + h * 128 + ...
+  const long long bh = it / T;
+  const int t = (int)(it - bh * T);
+  const long long b = bh / H;
+  const int h = (int)(bh - b * H);
+  const long long off = ((b * T + t) * H + h) * 128 + l16 * 8;
   const uint4 a = *reinterpret_cast<const uint4*>(dy + off), c = *reinterpret_cast<const uint4*>(y + off);
   const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, cw[4] = {c.x, c.y, c.z, c.w};
   float s = 0.f;
@@ -135,11 +140,7 @@ __global__ void attn_bwd_stats_kernel(const __nv_bfloat16* __restrict__ dy, cons
   }
 #pragma unroll
   for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-  if (l16 == 0 && item < total) {
-    const long long b = row / T, t = row % T;
-    const long long i = (b * H + h) * T + t;
-    stats[i] = make_float2(-lse[i] * kLog2e, s);
-  }
+  if (l16 == 0 && item < total) stats[it] = make_float2(-lse[it] * kLog2e, s);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
