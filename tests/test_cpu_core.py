@@ -370,3 +370,132 @@ def test_local_expert_step_gates_a_non_finite_gradient_per_expert():
     keep = [0, 1, 3]
     assert torch.allclose(gated[keep], clean[keep], atol=1e-6)
     assert not torch.allclose(gated[2], clean[2], atol=1e-4)      # the poisoned expert did not take the clean step
+
+
+def _docs(n, lo, hi, seed, vocab=4096):
+    from them_bones_b200.data.synth import ZipfDocs
+    return ZipfDocs(vocab, doc_len=(lo, hi), seed=seed).docs(n)
+
+
+def test_pool_mix_reaches_its_share_from_the_decision_on_and_respects_passes():
+    """A stored pool mixed into the refills at a token share, from a start fraction on, this rank's documents only, each
+    at most ``rep`` times, paid from a token debt (the reference's DSEL lane)."""
+    from them_bones_b200.data.streams import PoolMix, doc_hash
+    pool = _docs(200, 50, 150, seed=5)
+    a = PoolMix(pool, share=0.2, start=0.5, rep=2, rank=0, world=2, seed=3)
+    b = PoolMix(pool, share=0.2, start=0.5, rep=2, rank=1, world=2, seed=3)
+    assert sorted(a.mine + b.mine) == list(range(200)) and not set(a.mine) & set(b.mine)
+    refill = _docs(64, 100, 300, seed=6)
+    assert a.mix(refill) == refill                                   # before the decision: untouched
+    a.phase = 0.6
+    kit = added = 0
+    for i in range(6):
+        docs = _docs(64, 100, 300, seed=10 + i)
+        out = a.mix(docs)
+        assert out[:len(docs)] == docs
+        kit += sum(len(d) for d in docs)
+        added += sum(len(d) for d in out[len(docs):])
+        assert all(doc_hash(d, 3) % 2 == 0 for d in out[len(docs):])
+    assert abs(added / (kit + added) - 0.2) < 0.02
+    many = PoolMix(pool, share=0.9, start=0.0, rep=2, seed=3)
+    total = sum(len(many.mix(_docs(64, 100, 300, seed=40 + i))) - 64 for i in range(8))
+    assert total == 2 * 200 and many.count["short"] > 0            # every document at most twice, then nothing more
+
+
+def test_strata_mix_fills_the_stratum_furthest_below_its_first_phase_share():
+    from them_bones_b200.data.streams import StrataMix
+    pool = _docs(600, 20, 1500, seed=7)
+    sm = StrataMix(pool, share=0.3, start=0.5, split=64, seed=1)
+    long_docs = _docs(80, 600, 1500, seed=8)
+    short_docs = _docs(80, 20, 100, seed=9)
+    for _ in range(3):
+        assert sm.mix(long_docs + short_docs) == long_docs + short_docs   # phase 1: counted, nothing added
+    sm.phase = 0.7
+    out = sm.mix(short_docs)                                              # the long strata are now far below their share
+    added = out[len(short_docs):]
+    assert added and sum(len(d) for d in added) >= 0.3 / 0.7 * sum(len(d) for d in short_docs) - 1500
+    assert min(len(d) for d in added) > 512                               # all representatives come from the long buckets
+    assert int(sm.rep[0].sum()) == len(added)
+
+
+def test_masked_blocks_are_never_targets_and_follow_the_late_schedule():
+    from them_bones_b200.data.streams import MaskedBlocks, Streams, decode_row
+    from them_bones_b200.data.synth import SynthLoader, slice_windows
+    import numpy as np
+    mb = MaskedBlocks(share=0.1, sep_id=4095, examples=3, context=10, answer=4, late=True, seed=0)
+    docs = _docs(64, 100, 300, seed=2)
+    early = mb.make(docs)
+    mb.phase = 0.9
+    late = mb.make(docs)
+    assert sum(map(len, late)) > 2 * sum(map(len, early))                 # 0.75 x before 0.8 of the run, 2 x after
+    blk = early[0]
+    assert blk[0] == 0 and len(blk) == 1 + 3 * (10 + 1 + 4) and int((blk < 0).sum()) == 3 * 11
+    ids, train = decode_row(blk)
+    assert ids.min() >= 0 and int(train.sum()) == 1 + 3 * 4 and ids[11] == 4095
+    row = np.concatenate([blk, docs[0].astype(np.int64), blk])[:129]
+    x, y = slice_windows(row, 64, 0)
+    assert x.min() >= 0 and x.shape == (2, 64)
+    ids, train = decode_row(row)
+    flat_y = y.reshape(-1)
+    masked_next = ~train[1:129]
+    assert (flat_y[masked_next] == -1).all() and (flat_y[~masked_next & (ids[1:129] != 0)] >= 0).all()
+    st = Streams.parse("blocks:0.05,edge", vocab=4096, seq_len=128, seed=1)
+    ld = SynthLoader(4096, 128, 8, seed=1, doc_len=(16, 300), streams=st)
+    for _ in range(6):
+        xb, yb = ld.next_step()
+        assert int(xb.min()) >= 0 and int(yb.min()) >= -1
+    assert st.blocks.count["blocks"] > 0 and st.edge.n["rows"] == 6 and "edge relay" in st.lines()[-1]
+
+
+def test_edge_relay_keeps_the_tokens_and_moves_the_cuts_to_long_documents():
+    """Every window edge cuts some piece; the re-lay keeps every piece whole and chooses long plain documents for the
+    cuts: no block and fewer short documents are cut, and the row holds the same pieces."""
+    import numpy as np
+    from them_bones_b200.data.streams import EdgeRelay, MaskedBlocks
+    rng = np.random.default_rng(0)
+    er = EdgeRelay(256)
+    mb = MaskedBlocks(share=0.5, sep_id=4095, examples=3, context=20, answer=6, seed=1)
+    for k in range(12):
+        docs = _docs(40, 20, 300, seed=100 + k)
+        parts = docs[:14] + mb.make(docs)[:6]
+        order = rng.permutation(len(parts))
+        row = np.concatenate([np.asarray(parts[i], dtype=np.int64) for i in order])[:8 * 256 + 1]
+        out = er.relay(row)
+        assert len(out) == len(row)
+        pieces = lambda r: sorted(tuple(p) for p in np.split(r, np.flatnonzero(np.where(r < 0, -r - 1, r) == 0)[1:]))  # noqa: E731
+        assert pieces(out) == pieces(row)
+    b, a = er.split["before"], er.split["after"]
+    assert b[2] > 0 and a[2] == 0                                 # blocks were cut before, none after
+    assert a[1] < b[1] and er.n["moved"] > 0                      # fewer short documents cut
+    assert "edge relay" in er.line()
+
+
+def test_shared_dedup_drops_across_ranks_with_a_fixed_lag(tmp_path):
+    """Two ranks in one process: what rank 1 accepted in batch 0 is dropped on rank 0 from batch 2 on (lag 2), whatever
+    the timing; a document repeated on the same rank is dropped at once."""
+    from them_bones_b200.data.streams import SharedDedup
+    root = str(tmp_path / "dd")
+    r0 = SharedDedup(root, 0, 2, bits=16, wait_s=5.0)
+    r1 = SharedDedup(root, 1, 2, bits=16, wait_s=5.0)
+    docs = _docs(12, 30, 60, seed=11)
+    for b in range(4):
+        for r in (r0, r1):                                             # rank 0 first: it only needs slots of batch b - 2
+            if r is r1 and b >= 2:
+                continue
+            r.begin_batch(b)
+        if b == 0:
+            assert r0.decide(docs[:4] + docs[:1]) == [True] * 4 + [False]
+            assert r1.decide(docs[4:8]) == [True] * 4
+        elif b == 1:
+            assert r0.decide(docs[4:6]) == [True, True]               # rank 1's batch 0 is not merged yet
+            assert r1.decide(docs[8:10]) == [True, True]
+        elif b == 2:
+            assert r0.decide(docs[6:8]) == [False, False]             # merged now
+            r1.begin_batch(b)
+            assert r1.decide(docs[0:2]) == [False, False]
+        else:
+            r1.begin_batch(b)
+            assert r0.decide(docs[8:10]) == [False, False] and r1.decide(docs[10:12]) == [True, True]
+        r0.end_batch()
+        r1.end_batch()
+    assert r0.n["merged_hashes"] == 4 + 4 + 2 + 2

@@ -259,6 +259,8 @@ def switches(refresh: bool = False) -> dict:
         ANSWER_WEIGHT=e("ANSWER_WEIGHT", 2.0, float),
         EVAL_SPLIT=e("EVAL_SPLIT", False, bool),     # after the final evaluation: held-out loss by position class
         DATA_RULE=e("DATA_RULE", "", str),           # e.g. "len:64-4096,band:0.05-0.95,dedup:32,from:0.1"
+        # riders of the packer (data/streams.py), e.g. "pool:0.1@0.3x2,strata:0.05@0.3,blocks:0.02+late,edge,dedup:/dev/shm/d"
+        DATA_STREAMS=e("DATA_STREAMS", "", str),
         # kernels / system
         SELFCHECK=e("SELFCHECK", False, bool),       # compare every native op with the PyTorch path before training
         KERNELS=e("KERNELS", "auto", str),           # auto: CUDA kernels on a GPU, torch oracle on CPU | ref

@@ -49,16 +49,19 @@ class ZipfDocs:
 class PackedRows:
     """Best-fit packer: yields int32 rows of ``row_len + 1`` tokens."""
 
-    def __init__(self, source: ZipfDocs, row_len: int, buffer_docs: int = 512, rule=None):
+    def __init__(self, source: ZipfDocs, row_len: int, buffer_docs: int = 512, rule=None, streams=None):
         self.src, self.row_len, self.buffer_docs = source, row_len, buffer_docs
         self.buf: list = []
         self.rule = rule                     # data.select.DocRule: documents it rejects never enter the buffer
+        self.streams = streams               # data.streams.Streams: documents added after each refill, rows re-laid
 
     def _refill(self):
         while len(self.buf) < self.buffer_docs:
             docs = self.src.docs(self.buffer_docs)
             if self.rule is not None:
                 docs = [d for d, keep in zip(docs, self.rule.decide(docs)) if keep]
+            if self.streams is not None:
+                docs = self.streams.after_refill(docs)
             self.buf.extend(docs)
 
     def next_row(self) -> np.ndarray:
@@ -80,7 +83,7 @@ class PackedRows:
                 d = self.buf.pop(i)
                 row[pos:] = d[:room]
                 pos = need
-        return row
+        return self.streams.after_row(row) if self.streams is not None else row
 
 
 def tail_marks(row: np.ndarray, bos_id: int, frac: float) -> np.ndarray:
@@ -101,10 +104,16 @@ def slice_windows(row: np.ndarray, seq_len: int, bos_id: int, mask_bos: bool = T
     last ``mark_tail`` of each document are marked by adding ``vocab`` (the model weights their loss; reference:
     the loader's marks for ``qa_unmark``, round2/source/train.py:6504)."""
     n = (len(row) - 1) // seq_len
+    trainable = None
+    if (row < 0).any():                      # masked ids ride as -(id + 1) (data.streams.MaskedBlocks): never a target
+        from .streams import decode_row
+        row, trainable = decode_row(row)
     x = row[:n * seq_len].reshape(n, seq_len)
     y = row[1:n * seq_len + 1].astype(np.int64)
     if mask_bos:
         y = np.where(y == bos_id, -1, y)
+    if trainable is not None:
+        y = np.where(trainable[1:n * seq_len + 1], y, -1)
     if mark_tail > 0.0:
         marks = tail_marks(row, bos_id, mark_tail)[1:n * seq_len + 1]
         y = np.where(marks & (y >= 0), y + vocab, y)
@@ -117,7 +126,7 @@ class SynthLoader:
 
     def __init__(self, vocab: int, seq_len: int, local_windows: int, *, rank: int = 0, seed: int = 0,
                  doc_len=(128, 2048), zipf_s: float = 1.1, bos_id: int = 0, pin: bool = False, rule=None,
-                 shard_of: int = 0):
+                 shard_of: int = 0, streams=None):
         # shard_of = W > 0: every rank draws the same stream (the seed alone decides it), packs the whole job's step and
         # keeps windows rank, rank + W, ...: the global batch of a step is then the same set of windows at any rank
         # count, which makes losses comparable across 1, 2, 4 and 8 ranks.  0: one independent stream per rank.
@@ -125,13 +134,18 @@ class SynthLoader:
         self.mark_tail = 0.0                 # > 0: answer-span marks on the targets (set when the answer phase starts)
         self.shard_of, self.rank = int(shard_of), rank
         self.docs = ZipfDocs(vocab, zipf_s, doc_len, seed=seed * 1000003 + (0 if shard_of else rank), bos_id=bos_id)
-        self.rule = rule
-        self.rows = PackedRows(self.docs, seq_len * local_windows * max(1, self.shard_of), rule=rule)
+        self.rule, self.streams = rule, streams
+        self.rows = PackedRows(self.docs, seq_len * local_windows * max(1, self.shard_of), rule=rule, streams=streams)
         self.pin = pin and torch.cuda.is_available()
         self.epoch = 0
 
     def next_step(self):
+        if self.streams is not None:
+            self.streams.begin_batch(self.epoch)
         row = self.rows.next_row()
+        if self.streams is not None:
+            self.streams.end_batch()
+        self.epoch += 1
         x, y = slice_windows(row, self.seq_len, self.bos_id, mark_tail=self.mark_tail, vocab=self.vocab)
         if self.shard_of:
             x, y = x[self.rank::self.shard_of], y[self.rank::self.shard_of]

@@ -96,9 +96,12 @@ def main(argv=None):
     lo, hi = (int(v) for v in args.doc_len.split(","))
     from them_bones_b200.data.select import DocRule
     rule = DocRule.parse(sw["DATA_RULE"], cfg.vocab_size, cfg.bos_id)
+    from them_bones_b200.data.streams import Streams
+    streams = Streams.parse(sw["DATA_STREAMS"], vocab=cfg.vocab_size, seq_len=cfg.sequence_len, bos_id=cfg.bos_id, rank=rt.rank,
+                            world=rt.world, seed=hyper.seed)
     loader = SynthLoader(cfg.vocab_size, cfg.sequence_len, tr.local_windows, rank=rt.rank, seed=hyper.seed,
                          doc_len=(lo, min(hi, cfg.sequence_len * 4)), bos_id=cfg.bos_id, pin=rt.device_type == "cuda",
-                         rule=rule)
+                         rule=rule, streams=streams)
     if args.compile_only:
         x = torch.zeros(tr.local_windows, cfg.sequence_len, dtype=torch.int32)
         y = torch.zeros(tr.local_windows, cfg.sequence_len, dtype=torch.int64)
@@ -136,6 +139,8 @@ def main(argv=None):
                 print0(f"step {step}: window length -> {want}")
         if rule is not None:
             rule.phase = tr.progress()
+        if streams is not None:
+            streams.set_phase(tr.progress())
         if sw["ANSWER_PHASE"] > 0 and loader.mark_tail == 0.0 and tr.progress() >= 1.0 - sw["ANSWER_PHASE"]:
             loader.mark_tail = sw["ANSWER_TAIL"]         # rows fetched from here on carry answer-span marks
             print0(f"step {step}: answer phase on (tail {sw['ANSWER_TAIL']}, weight {sw['ANSWER_WEIGHT']})")
@@ -266,6 +271,10 @@ def main(argv=None):
            f"{(med or 0) * 1e3:.1f} ms tok/s {(tokens_per_step / med) if med else 0:,.0f} final_loss "
            f"{ema_loss / max(1e-9, 1 - 0.9 ** max(step, 1)):.4f}")
     print0(f"native op counts: {dict(ops.COUNTS)}")
+    if rule is not None:
+        print0(rule.line())
+    for ln in (streams.lines() if streams is not None else []):
+        print0(ln)
     if sw["MEM_PRINT"]:
         print0(memory_line(rt.device))
     cleanup_runtime()
