@@ -76,19 +76,40 @@ __global__ void peer_allreduce_small_kernel(PeerPtrs in, float* out, int n, int 
   out[i] = s * scale;
 }
 
+// NVSwitch multicast (NVLS): one load from the multicast address of a symmetric buffer returns the sum of all ranks'
+// copies, added inside the switch, so a reduction over W ranks moves one element over this GPU's links instead of W - 1;
+// one store to the multicast address lands in every rank's copy.  `mc` pointers are null when the buffer has no
+// multicast mapping (or BONES_NVLS=0): the kernels then loop over the peer pointers.
+__device__ __forceinline__ float4 ld_multimem_sum_f4(const float* mc) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(mc)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_multimem_bf16x4(__nv_bfloat16* mc, uint2 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v2.bf16x2 [%0], {%1, %2};" ::"l"(mc), "r"(v.x), "r"(v.y) : "memory");
+}
+
 // Reduce-scatter fused with the Muon prologue on the owned chunk [off, off + n):
 //   g = scale * sum_r G_r[off + i];  m += (1 - mu) (g - m);  u = g + mu (m - g);  X = bf16(u);  sumsq[mat] += u^2
 //   gsq += g^2 (finiteness gate)
 __global__ void rs_muon_prep_kernel(PeerPtrs G, long long off, long long n, int world, float scale, float mu, float* __restrict__ mom,
-                                    __nv_bfloat16* __restrict__ X, float* __restrict__ sumsq, long long mat_elems, float* __restrict__ gsq) {
+                                    __nv_bfloat16* __restrict__ X, float* __restrict__ sumsq, long long mat_elems, float* __restrict__ gsq,
+                                    const float* __restrict__ mcG) {
   const long long i4 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
   float local = 0.f, lg = 0.f;
   long long mat = 0;
   if (i4 < n) {
     float4 s = make_float4(0, 0, 0, 0);
-    for (int r = 0; r < world; ++r) {
-      const float4 v = ld_peer_f4(reinterpret_cast<const float*>(G.p[r]) + off + i4);
-      s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    if (mcG) {
+      s = ld_multimem_sum_f4(mcG + off + i4);
+    } else {
+      for (int r = 0; r < world; ++r) {
+        const float4 v = ld_peer_f4(reinterpret_cast<const float*>(G.p[r]) + off + i4);
+        s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+      }
     }
     s.x *= scale; s.y *= scale; s.z *= scale; s.w *= scale;
     lg = s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
@@ -145,14 +166,19 @@ __global__ void muon_normalize_kernel(__nv_bfloat16* X, const float* sumsq, long
 //   g = scale * sum_r G_r[off + i]; AdamW on (master, m, v); bf16(master) stored into every rank's weight slab at off + i.
 __global__ void rs_adamw_publish_kernel(PeerPtrs G, PeerPtrs Wt, long long off, long long n, int world, float scale, float* __restrict__ master,
                                         float* __restrict__ m1, float* __restrict__ m2, float lr, float b1, float b2, float eps, float wd,
-                                        float c1, float c2, float* __restrict__ gsq) {
+                                        float c1, float c2, float* __restrict__ gsq, const float* __restrict__ mcG,
+                                        __nv_bfloat16* __restrict__ mcW) {
   const long long i4 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
   float lg = 0.f;
   if (i4 < n) {
     float4 s = make_float4(0, 0, 0, 0);
-    for (int r = 0; r < world; ++r) {
-      const float4 v = ld_peer_f4(reinterpret_cast<const float*>(G.p[r]) + off + i4);
-      s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    if (mcG) {
+      s = ld_multimem_sum_f4(mcG + off + i4);
+    } else {
+      for (int r = 0; r < world; ++r) {
+        const float4 v = ld_peer_f4(reinterpret_cast<const float*>(G.p[r]) + off + i4);
+        s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+      }
     }
     float g[4] = {s.x * scale, s.y * scale, s.z * scale, s.w * scale};
     float4 p = *reinterpret_cast<float4*>(master + i4), a = *reinterpret_cast<float4*>(m1 + i4), b = *reinterpret_cast<float4*>(m2 + i4);
@@ -172,21 +198,26 @@ __global__ void rs_adamw_publish_kernel(PeerPtrs G, PeerPtrs Wt, long long off, 
     uint2 o;
     o.x = pack_bf16(pp[0], pp[1]);
     o.y = pack_bf16(pp[2], pp[3]);
-    for (int r = 0; r < world; ++r) *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(Wt.p[r]) + off + i4) = o;
+    if (mcW) st_multimem_bf16x4(mcW + off + i4, o);
+    else
+      for (int r = 0; r < world; ++r) *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(Wt.p[r]) + off + i4) = o;
   }
   lg = warp_sum(lg);
   if ((threadIdx.x & 31) == 0 && !(lg == 0.f)) atomicAdd(gsq, lg);
 }
 
 // Publish: bf16(src[i]) stored into every rank's weight slab at off + i (src fp32 master of the owned chunk).
-__global__ void peer_publish_kernel(const float* __restrict__ src, PeerPtrs Wt, long long off, long long n, int world) {
+__global__ void peer_publish_kernel(const float* __restrict__ src, PeerPtrs Wt, long long off, long long n, int world,
+                                    __nv_bfloat16* __restrict__ mcW) {
   const long long i4 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
   if (i4 >= n) return;
   const float4 v = *reinterpret_cast<const float4*>(src + i4);
   uint2 o;
   o.x = pack_bf16(v.x, v.y);
   o.y = pack_bf16(v.z, v.w);
-  for (int r = 0; r < world; ++r) *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(Wt.p[r]) + off + i4) = o;
+  if (mcW) st_multimem_bf16x4(mcW + off + i4, o);
+  else
+    for (int r = 0; r < world; ++r) *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(Wt.p[r]) + off + i4) = o;
 }
 
 // MoE / table exchange helper: rows gathered from peers.  out[i] = table_{owner[i]}[local[i]] (bf16 rows of C columns).
@@ -309,13 +340,18 @@ int bones_peer_allreduce_small(void* const* in_ptrs, float* out, int n, int worl
   return (int)cudaGetLastError();
 }
 
-int bones_rs_muon_prep(void* const* g_ptrs, long long off, long long n, int world, float scale, float mu, float* mom, void* X, float* sumsq,
-                       long long mat_elems, float* gsq, void* stream) {
-  if (world > kMaxPeers || (n % 4) || (off % 4) || (mat_elems % 1024)) return -2;
+int bones_rs_muon_prep_mc(void* const* g_ptrs, long long off, long long n, int world, float scale, float mu, float* mom, void* X, float* sumsq,
+                          long long mat_elems, float* gsq, const void* mc_g, void* stream) {
+  if (world > kMaxPeers || (n % 4) || (off % 4) || (mat_elems % 1024) || ((uintptr_t)mc_g & 15)) return -2;
   const long long threads = n / 4;
   rs_muon_prep_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(make_ptrs(g_ptrs, world), off, n, world, scale, mu, mom,
-                                                                                         (__nv_bfloat16*)X, sumsq, mat_elems, gsq);
+                                                                                         (__nv_bfloat16*)X, sumsq, mat_elems, gsq,
+                                                                                         (const float*)mc_g);
   return (int)cudaGetLastError();
+}
+int bones_rs_muon_prep(void* const* g_ptrs, long long off, long long n, int world, float scale, float mu, float* mom, void* X, float* sumsq,
+                       long long mat_elems, float* gsq, void* stream) {
+  return bones_rs_muon_prep_mc(g_ptrs, off, n, world, scale, mu, mom, X, sumsq, mat_elems, gsq, nullptr, stream);
 }
 
 int bones_muon_normalize(void* X, const float* sumsq, long long n, long long mat_elems, void* stream) {
@@ -324,19 +360,30 @@ int bones_muon_normalize(void* X, const float* sumsq, long long n, long long mat
   return (int)cudaGetLastError();
 }
 
-int bones_rs_adamw_publish(void* const* g_ptrs, void* const* w_ptrs, long long off, long long n, int world, float scale, float* master, float* m1,
-                           float* m2, float lr, float b1, float b2, float eps, float wd, int step, float* gsq, void* stream) {
-  if (world > kMaxPeers || (n % 4) || (off % 4)) return -2;
+// mc_g / mc_w: multicast addresses of the gradient and weight slabs (null: peer loops)
+int bones_rs_adamw_publish_mc(void* const* g_ptrs, void* const* w_ptrs, long long off, long long n, int world, float scale, float* master,
+                              float* m1, float* m2, float lr, float b1, float b2, float eps, float wd, int step, float* gsq, const void* mc_g,
+                              void* mc_w, void* stream) {
+  if (world > kMaxPeers || (n % 4) || (off % 4) || ((uintptr_t)mc_g & 15) || ((uintptr_t)mc_w & 7)) return -2;
   const float c1 = 1.0f - powf(b1, (float)step), c2 = 1.0f - powf(b2, (float)step);
   rs_adamw_publish_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
-      make_ptrs(g_ptrs, world), make_ptrs(w_ptrs, world), off, n, world, scale, master, m1, m2, lr, b1, b2, eps, wd, c1, c2, gsq);
+      make_ptrs(g_ptrs, world), make_ptrs(w_ptrs, world), off, n, world, scale, master, m1, m2, lr, b1, b2, eps, wd, c1, c2, gsq,
+      (const float*)mc_g, (__nv_bfloat16*)mc_w);
   return (int)cudaGetLastError();
 }
+int bones_rs_adamw_publish(void* const* g_ptrs, void* const* w_ptrs, long long off, long long n, int world, float scale, float* master, float* m1,
+                           float* m2, float lr, float b1, float b2, float eps, float wd, int step, float* gsq, void* stream) {
+  return bones_rs_adamw_publish_mc(g_ptrs, w_ptrs, off, n, world, scale, master, m1, m2, lr, b1, b2, eps, wd, step, gsq, nullptr, nullptr, stream);
+}
 
-int bones_peer_publish(const float* src, void* const* w_ptrs, long long off, long long n, int world, void* stream) {
-  if (world > kMaxPeers || (n % 4) || (off % 4)) return -2;
-  peer_publish_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(src, make_ptrs(w_ptrs, world), off, n, world);
+int bones_peer_publish_mc(const float* src, void* const* w_ptrs, long long off, long long n, int world, void* mc_w, void* stream) {
+  if (world > kMaxPeers || (n % 4) || (off % 4) || ((uintptr_t)mc_w & 7)) return -2;
+  peer_publish_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(src, make_ptrs(w_ptrs, world), off, n, world,
+                                                                                       (__nv_bfloat16*)mc_w);
   return (int)cudaGetLastError();
+}
+int bones_peer_publish(const float* src, void* const* w_ptrs, long long off, long long n, int world, void* stream) {
+  return bones_peer_publish_mc(src, w_ptrs, off, n, world, nullptr, stream);
 }
 
 int bones_peer_gather_rows(void* const* table_ptrs, const long long* ids, void* out, int n, int C, int world, long long rows_per_shard,

@@ -119,7 +119,8 @@ def main():
     L.check_error_word()
     if rt.rank == 0:
         print(f"losses nccl {ln} fused {lf} worst weight rel diff {worst:.2e} publish mismatches {mism} "
-              f"fused launches {tr.comm.launches}")
+              f"fused launches {tr.comm.launches}; buffers reduced / published through switch multicast: "
+              f"{tr.comm.multicast_mapped() if hasattr(tr.comm, 'multicast_mapped') else 0}")
         print("SELFTEST OK" if int(flag) else "SELFTEST FAILED", flush=True)
     dist.barrier()
     dist.destroy_process_group()

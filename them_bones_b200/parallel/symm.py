@@ -46,7 +46,9 @@ class PeerComm:
         self.world, self.rank = rt.world, rt.rank
         self.device = rt.device
         self.wait_seconds = wait_seconds
-        self._handles = {}                    # data_ptr -> (tensor, handle, ptr array)
+        self._handles = {}                    # data_ptr -> (tensor, handle, ptr array, multicast address or 0)
+        from ..config import switches
+        self.nvls = bool(switches()["NVLS"])  # reduce / broadcast through the switch where a buffer has a multicast mapping
         self._canaries = []
         self.epoch_dev = torch.zeros(1, dtype=torch.int32, device=self.device)    # advanced by the barrier kernel itself
         self.flags = self.alloc((64,), torch.int32, self.device)
@@ -74,7 +76,10 @@ class PeerComm:
         base[n:].view(torch.uint8).fill_(self.CANARY)
         hdl = self.symm_mem.rendezvous(base, self.group)
         t = base[:n].view(*shape)
-        self._handles[t.data_ptr()] = (t, hdl, _ptr_array(hdl.buffer_ptrs))
+        mc = int(getattr(hdl, "multicast_ptr", 0) or 0)
+        if mc:
+            mc += t.data_ptr() - int(hdl.buffer_ptrs[self.rank])
+        self._handles[t.data_ptr()] = (t, hdl, _ptr_array(hdl.buffer_ptrs), mc)
         self._canaries.append((tuple(shape), dtype, base[n:].view(torch.uint8)))
         return t
 
@@ -93,6 +98,18 @@ class PeerComm:
         if ent is None:
             raise RuntimeError("tensor is not a symmetric allocation of this communicator")
         return [int(p) for p in ent[1].buffer_ptrs]
+
+    def multicast_mapped(self) -> int:
+        """How many symmetric allocations have a multicast mapping that the kernels use (0 with ``BONES_NVLS=0``)."""
+        return sum(1 for e in self._handles.values() if len(e) > 3 and e[3]) if self.nvls else 0
+
+    def multicast(self, t):
+        """The multicast address of symmetric tensor ``t`` as a ctypes pointer: a load from it (``multimem.ld_reduce``)
+        sums all ranks' copies inside the switch, a store to it (``multimem.st``) lands in every copy.  Null when the
+        allocation has no multicast mapping or ``BONES_NVLS=0``; the kernels then loop over the peer pointers."""
+        ent = self._handles.get(t.data_ptr())
+        mc = ent[3] if (ent is not None and self.nvls and len(ent) > 3) else 0
+        return ctypes.c_void_p(mc or None)
 
     def peers(self, t):
         """ctypes array of the W peer pointers of symmetric tensor ``t`` (or of the allocation a view starts in)."""
@@ -140,9 +157,10 @@ class PeerComm:
         n = u.master.numel()
         off = self.rank * n
         b1, b2 = g["betas"]
-        L.call("bones_rs_adamw_publish", self.peers(u.G), self.peers(u.W), _L(off), _L(n), _I(self.world),
+        L.call("bones_rs_adamw_publish_mc", self.peers(u.G), self.peers(u.W), _L(off), _L(n), _I(self.world),
                _F(1.0 / self.world), L.ptr(u.master), L.ptr(u.exp_avg), L.ptr(u.exp_avg_sq), _F(g["lr"]), _F(b1), _F(b2),
-               _F(g["eps"]), _F(g["weight_decay"]), _I(step), L.ptr(self.gsq), L.stream())
+               _F(g["eps"]), _F(g["weight_decay"]), _I(step), L.ptr(self.gsq), self.multicast(u.G), self.multicast(u.W),
+               L.stream())
         self.launches += 1
 
     def fused_muon(self, u, step, ns_dtype, own_only=False):
@@ -163,15 +181,16 @@ class PeerComm:
         if own_only:
             if not hasattr(u, "own_ptr"):
                 u.own_ptr = _ptr_array([self.peer_addresses(u.G)[self.rank]])
-            src, nsrc = u.own_ptr, 1
+            src, nsrc, mc_g = u.own_ptr, 1, ctypes.c_void_p(None)
         else:
-            src, nsrc = self.peers(u.G), self.world
-        L.call("bones_rs_muon_prep", src, _L(off), _L(n), _I(nsrc), _F(1.0 / self.world),
-               _F(g["momentum"]), L.ptr(u.momentum), L.ptr(u.X), L.ptr(u.sumsq), _L(mat), L.ptr(self.gsq), L.stream())
+            src, nsrc, mc_g = self.peers(u.G), self.world, self.multicast(u.G)
+        L.call("bones_rs_muon_prep_mc", src, _L(off), _L(n), _I(nsrc), _F(1.0 / self.world),
+               _F(g["momentum"]), L.ptr(u.momentum), L.ptr(u.X), L.ptr(u.sumsq), _L(mat), L.ptr(self.gsq), mc_g, L.stream())
         L.call("bones_muon_normalize", L.ptr(u.X), L.ptr(u.sumsq), _L(n), _L(mat), L.stream())
         x = MN.newton_schulz(u.X[:kr], g["ns_steps"])
         MN.muon_finish(x, u.master[:kr], u.second[:kr], beta2=g["beta2"], lr=g["lr"], wd=g["weight_decay"])
-        L.call("bones_peer_publish", L.ptr(u.master), self.peers(u.W), _L(off), _L(n), _I(self.world), L.stream())
+        L.call("bones_peer_publish_mc", L.ptr(u.master), self.peers(u.W), _L(off), _L(n), _I(self.world), self.multicast(u.W),
+               L.stream())
         self.launches += 3
 
     # -- cross-check against the library collectives on the same live inputs ----------------------------------
@@ -262,6 +281,7 @@ class SoloComm(PeerComm):
         self.world, self.rank, self.device = 1, 0, rt.device
         self._handles = {}
         self._canaries = []
+        self.nvls = False
         self.gsq = torch.zeros(1, dtype=torch.float32, device=self.device)
         self.launches = 0
 
