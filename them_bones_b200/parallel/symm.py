@@ -267,7 +267,45 @@ def create_or_fallback(rt, factory=None):
             why = f"fused all-reduce returned {float(got[0])}, expected {want}"
     except Exception as exc:  # noqa: BLE001 - any failure of the substrate means: use the library collectives
         why = f"{type(exc).__name__}: {exc}"
-    return comm if agree(not why) else give_up(why)
+    if not agree(not why):
+        return give_up(why)
+    # stage 3: the switch-multicast forms of the reduction and the publish on known values; a wrong result on any rank
+    # switches them off on every rank (the peer-loop forms stay)
+    if getattr(comm, "nvls", False) and comm.world > 1:
+        bad = ""
+        try:
+            n = 1024
+            g = comm.alloc((n,), torch.float32, rt.device)
+            w = comm.alloc((comm.world * n,), torch.bfloat16, rt.device)
+            if comm.multicast(g).value and comm.multicast(w).value:
+                g.fill_(float(rt.rank + 1))
+                mom, x = torch.zeros(n, device=rt.device), torch.empty(n, dtype=torch.bfloat16, device=rt.device)
+                sumsq, gsq = torch.zeros(1, device=rt.device), torch.zeros(1, device=rt.device)
+                comm.barrier()
+                L.call("bones_rs_muon_prep_mc", comm.peers(g), _L(0), _L(n), _I(comm.world), _F(1.0 / comm.world), _F(0.0),
+                       L.ptr(mom), L.ptr(x), L.ptr(sumsq), _L(n), L.ptr(gsq), comm.multicast(g), L.stream())
+                src = torch.full((n,), float(rt.rank + 1), device=rt.device)
+                L.call("bones_peer_publish_mc", L.ptr(src), comm.peers(w), _L(rt.rank * n), _L(n), _I(comm.world),
+                       comm.multicast(w), L.stream())
+                comm.barrier()
+                torch.cuda.synchronize(rt.device)
+                L.check_error_word()
+                mean = (comm.world + 1) / 2.0
+                want_w = torch.arange(1, comm.world + 1, device=rt.device, dtype=torch.float32).repeat_interleave(n)
+                if not bool(((x.float() - mean).abs() < 1e-2).all()):
+                    bad = f"multicast reduction returned {float(x[0])}, expected {mean}"
+                elif not bool((w.float() == want_w).all()):
+                    bad = "a multicast store did not reach every rank's copy"
+            else:
+                bad = "no multicast mapping"
+        except Exception as exc:  # noqa: BLE001
+            bad = f"{type(exc).__name__}: {exc}"
+        if not agree(not bad):
+            comm.nvls = False
+            if rt.rank == 0:
+                print(f"switch multicast not used ({bad or 'another rank failed its probe'}); reductions and publishes "
+                      "loop over the peers", flush=True)
+    return comm
 
 
 class SoloComm(PeerComm):
