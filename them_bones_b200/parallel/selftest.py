@@ -23,7 +23,7 @@ def main():
 
     rt = init_runtime("cuda")
     w = rt.world
-    cfg = GPTConfig(sequence_len=256, vocab_size=4096, n_layer=2, n_head=2, n_embd=256, head_dim=128, doc_mask=True)
+    cfg = GPTConfig(sequence_len=256, vocab_size=4096, n_layer=3, n_head=2, n_embd=256, head_dim=128, doc_mask=True)
     hy = Hyper()
     hy.device_batch = 2
     hy.total_batch = 2 * 256 * w * 2
