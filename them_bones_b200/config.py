@@ -265,7 +265,10 @@ def switches(refresh: bool = False) -> dict:
         SELFCHECK=e("SELFCHECK", False, bool),       # compare every native op with the PyTorch path before training
         KERNELS=e("KERNELS", "auto", str),           # auto: CUDA kernels on a GPU, torch oracle on CPU | ref
         FUSED_COMM=e("FUSED_COMM", True, bool),      # in-kernel NVLink collectives (False: NCCL baseline path)
-        NVLS=e("NVLS", True, bool),                  # fused reductions / publishes through NVSwitch multicast (multimem) when mapped
+        # fused reductions / publishes through NVSwitch multicast (multimem.ld_reduce / multimem.st) where the slab has a
+        # mapping.  Off by default: for a reduce-scatter every GPU still uploads its copy of the others' chunks, so the
+        # links carry the same bytes as with peer loads (measured on 4 GPUs: 1.97 against 1.82 ms for the Muon slabs)
+        NVLS=e("NVLS", False, bool),
         WGRAD_PUSH=e("WGRAD_PUSH", False, bool),     # weight-gradient GEMMs reduce-scatter their tiles into the owner's slab
         LOSS_ROWS=e("LOSS_ROWS", 4096, int),         # rows per block of the chunked loss head (one [rows, V] logits buffer)
         GRAD_CLIP=e("GRAD_CLIP", 0.0, float),        # > 0: global-norm clip of the reduced gradients (library-collective path)
