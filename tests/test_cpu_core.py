@@ -499,3 +499,28 @@ def test_shared_dedup_drops_across_ranks_with_a_fixed_lag(tmp_path):
         r0.end_batch()
         r1.end_batch()
     assert r0.n["merged_hashes"] == 4 + 4 + 2 + 2
+
+
+def test_local_expert_stacks_alias_parameters_and_restore_state():
+    """The stacked expert optimizer keeps every parameter, its gradient and its optimizer state as views of one stack per
+    shape; restoring a checkpointed state writes through those views (the stack stays the single copy)."""
+    from them_bones_b200.optim.lean import MuonLocal
+    torch.manual_seed(0)
+    group = dict(momentum=0.95, beta2=0.95, lr=0.02, weight_decay=0.0, ns_steps=5)
+    ps = [torch.nn.Parameter(torch.randn(4, 64, 32).bfloat16()), torch.nn.Parameter(torch.randn(4, 32, 64).bfloat16()),
+          torch.nn.Parameter(torch.randn(2, 64, 32).bfloat16())]
+    before = [p.detach().clone() for p in ps]
+    opt = MuonLocal([dict(group, params=ps)], native=True)
+    assert len(opt.stacks) == 2 and sorted(st.n for st in opt.stacks) == [4, 6]
+    for p, b in zip(ps, before):
+        assert torch.equal(p.detach(), b) and p.main_grad.shape == p.shape and p.main_grad.dtype == torch.float32
+    st = next(s for s in opt.stacks if s.n == 6)
+    assert ps[0].data_ptr() == st.W.data_ptr() and ps[2].data_ptr() == st.W[4:].data_ptr()
+    ps[2].main_grad.fill_(3.0)
+    assert float(st.G[4:].min()) == 3.0 and float(st.G[:4].abs().max()) == 0.0
+    opt.zero_grad()
+    assert float(st.G.abs().max()) == 0.0
+    saved = {k: torch.full_like(v, 0.5) for k, v in opt.state[ps[2]].items()}
+    opt.load_state(ps[2], saved)
+    assert float(st.master[4:].min()) == 0.5 and float(st.momentum[4:].max()) == 0.5 and float(ps[2].detach().float().min()) == 0.5
+    assert torch.equal(st.master[:4], before[0].float())              # the other parameter of the stack is untouched

@@ -508,6 +508,7 @@ class MuonLocal:
                 for p in g["params"]:
                     p.main_grad.zero_()
 
+    @torch.no_grad()
     def load_state(self, p, st: dict):
         """Restore one parameter's master, momentum and second moment (into the stack's views when stacked)."""
         if p in self.state and self.stacks:
