@@ -356,7 +356,7 @@ class SharedDedup:
         if due < 0:
             return
         if self.rank == 0:
-            for bb in range(self._merged() + 1, due + 1):
+            for bb in range(max(0, self._merged() + 1), due + 1):
                 for r in range(self.world):
                     self._wait(lambda: os.path.exists(self._slot(bb, r)), f"rank {r}'s slot of batch {bb}")
                     h = np.load(self._slot(bb, r))
