@@ -799,10 +799,15 @@ gemm_mxfp8_pair_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_c
 // so the scale offsets are a base plus a lane term: no per-row division and no 64-bit index arithmetic.  Values are
 // scaled as packed bf16 pairs (a power of two: exact) before the conversion.
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int QD_WARPS = 12, QD_STAGES = 2;
-constexpr int QD_TILE_BYTES = 32 * 256;
-constexpr int QD_BARS_BASE = QD_WARPS * QD_STAGES * QD_TILE_BYTES;
-constexpr int QD_SMEM_BYTES = QD_BARS_BASE + QD_WARPS * QD_STAGES * 8 + 16;
+constexpr int QD_STAGES = 2;
+// kHalves 64-column halves per warp tile (2: a whole K block of the row copy per tile; 1: half of one, which needs fewer
+// registers and half the shared memory per warp, so more warps fit an SM), kWarps warps per CTA
+template <int kHalves, int kWarps>
+struct QdGeom {
+  static constexpr int kTileBytes = 32 * 128 * kHalves;
+  static constexpr int kBarsBase = kWarps * QD_STAGES * kTileBytes;
+  static constexpr int kSmemBytes = kBarsBase + kWarps * QD_STAGES * 8 + 16;
+};
 __device__ __forceinline__ uint32_t q_mul_bf16x2(uint32_t a, uint32_t b) {
   uint32_t d;
   asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
@@ -833,15 +838,17 @@ __device__ __forceinline__ size_t q_sf_base32(uint32_t r0, uint32_t kb, uint32_t
   const uint32_t chunks = ((uint32_t)group + 127u) >> 7;
   return ((size_t)g * kblocks + kb) * (size_t)(chunks * 512u) + (size_t)((t0 >> 7) * 512u + ((t0 & 127u) >> 5) * 4u);
 }
-template <bool kRow, bool kCol>
-__global__ void __launch_bounds__(QD_WARPS * 32, 1)
+template <bool kRow, bool kCol, int kHalves, int kWarps>
+__global__ void __launch_bounds__(kWarps * 32, 1)
 mx_quant_dual_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t* __restrict__ qr, uint8_t* __restrict__ sfr, int group_r,
                      uint8_t* __restrict__ qc, uint8_t* __restrict__ sfc, int group_c, long long R, long long C, uint32_t n_tiles, int* err) {
+  using G = QdGeom<kHalves, kWarps>;
+  constexpr int kCols = 64 * kHalves, kPitch = 2 * kCols;        // columns of a tile; bytes of a tile row in shared memory
   extern __shared__ __align__(128) uint8_t qd_smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, rsub = lane >> 3, piece = lane & 7;
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(qd_smem + QD_BARS_BASE + QD_WARPS * QD_STAGES * 8);
-  const uint32_t stage0 = smem_u32(qd_smem) + (uint32_t)(warp * QD_STAGES * QD_TILE_BYTES);
-  const uint32_t bar0 = smem_u32(qd_smem) + (uint32_t)(QD_BARS_BASE + warp * QD_STAGES * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(qd_smem + G::kBarsBase + kWarps * QD_STAGES * 8);
+  const uint32_t stage0 = smem_u32(qd_smem) + (uint32_t)(warp * QD_STAGES * G::kTileBytes);
+  const uint32_t bar0 = smem_u32(qd_smem) + (uint32_t)(G::kBarsBase + warp * QD_STAGES * 8);
   if (threadIdx.x == 0) *abort_flag = 0;
   if (lane == 0) {
 #pragma unroll
@@ -849,20 +856,21 @@ mx_quant_dual_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t
     fence_barrier_init();
   }
   __syncthreads();
-  const uint32_t tiles_c = (uint32_t)(C >> 7);
-  const uint32_t stride = gridDim.x * QD_WARPS;
+  const uint32_t tiles_c = (uint32_t)(C / kCols);
+  const uint32_t stride = gridDim.x * kWarps;
   const uint32_t kb_c = (uint32_t)((C + 127) >> 7), kb_r = (uint32_t)((R + 127) >> 7);
-  // the rows of tile `tile` into stage s: every lane copies one row of 256 bytes
+  // the rows of tile `tile` into stage s: every lane copies one row
   auto issue = [&](uint32_t tile, int s) {
     const uint32_t tr = tile / tiles_c, tc = tile - tr * tiles_c;
     const long long row0 = (long long)tr * 32;
     const int rows_here = (int)min((long long)32, R - row0);
-    if (lane == 0) mbar_arrive_expect_tx(bar0 + 8u * s, (uint32_t)rows_here * 256u);
+    if (lane == 0) mbar_arrive_expect_tx(bar0 + 8u * s, (uint32_t)(rows_here * kPitch));
     __syncwarp();
     if (lane < rows_here)
-      bulk_load(stage0 + (uint32_t)(s * QD_TILE_BYTES + lane * 256), x + (row0 + lane) * ldx + (long long)tc * 128, 256u, bar0 + 8u * s);
+      bulk_load(stage0 + (uint32_t)(s * G::kTileBytes + lane * kPitch), x + (row0 + lane) * ldx + (long long)tc * kCols, (uint32_t)kPitch,
+                bar0 + 8u * s);
   };
-  const uint32_t first = blockIdx.x * QD_WARPS + warp;
+  const uint32_t first = blockIdx.x * kWarps + warp;
 #pragma unroll
   for (int s = 0; s < QD_STAGES; ++s)
     if (first + s * stride < n_tiles) issue(first + s * stride, s);
@@ -874,26 +882,29 @@ mx_quant_dual_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t
     const uint32_t tr = tile / tiles_c, tc = tile - tr * tiles_c;
     const long long row0 = (long long)tr * 32;
     const int rows_here = (int)min((long long)32, R - row0);
-    uint4 raw[2][8];
+    // the tile's place in its 128-column K block of the row copy: first chunk and K block
+    const uint32_t kblock = kHalves == 2 ? tc : (tc >> 1);
+    const int chunk0 = kHalves == 2 ? 0 : (int)(tc & 1u) * 2;
+    uint4 raw[kHalves][8];
     {
-      const uint8_t* st = qd_smem + (warp * QD_STAGES + s) * QD_TILE_BYTES + rsub * 256 + piece * 16;
+      const uint8_t* st = qd_smem + (warp * QD_STAGES + s) * G::kTileBytes + rsub * kPitch + piece * 16;
 #pragma unroll
-      for (int h = 0; h < 2; ++h)
+      for (int h = 0; h < kHalves; ++h)
 #pragma unroll
         for (int i = 0; i < 8; ++i)
-          raw[h][i] = i * 4 + rsub < rows_here ? *reinterpret_cast<const uint4*>(st + i * 1024 + h * 128) : make_uint4(0u, 0u, 0u, 0u);
+          raw[h][i] = i * 4 + rsub < rows_here ? *reinterpret_cast<const uint4*>(st + i * 4 * kPitch + h * 128) : make_uint4(0u, 0u, 0u, 0u);
     }
     // the stage goes back to the copy engine for the tile after next
     fence_proxy_async_smem();
     __syncwarp();
     if (tile + 2 * stride < n_tiles) issue(tile + 2 * stride, s);
 
-    const long long q0 = (row0 + rsub) * C + (long long)tc * 128 + piece * 8;   // this thread's first output byte, either copy
+    const long long q0 = (row0 + rsub) * C + (long long)tc * kCols + piece * 8;   // this thread's first output byte, either copy
     const long long qstep = 4 * C;
     uint32_t rowsf[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};      // scale bytes of the row's blocks that this thread saw
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int c = 2 * h + (piece >> 2);                        // this thread's 32-column chunk of the half
+    for (int h = 0; h < kHalves; ++h) {
+      const int c = 2 * h + (piece >> 2);                        // this thread's 32-column chunk within the tile
       uint32_t cm[4] = {0u, 0u, 0u, 0u};                         // packed bf16 maxima of this thread's 8 columns over its 8 rows
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
@@ -928,7 +939,7 @@ mx_quant_dual_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t
         const uint32_t inv_lo = q_scale_bf16(pair & 0xffffu, b_lo), inv_hi = q_scale_bf16(pair >> 16, b_hi);
         const uint32_t my_inv2 = (inv_lo & 0xffffu) | (inv_hi & 0xffff0000u);
         // the transposed operand's "rows" are the columns; its K block is the 128-row block of row0
-        uint8_t* sp = sfc + q_sf_base32(tc * 128u + (uint32_t)c * 32u, (uint32_t)(row0 >> 7), kb_r, group_c) +
+        uint8_t* sp = sfc + q_sf_base32(tc * (uint32_t)kCols + (uint32_t)c * 32u, (uint32_t)(row0 >> 7), kb_r, group_c) +
                       (size_t)(((piece & 3) * 8 + 2 * rsub) * 16 + (int)((row0 & 127) >> 5));
         sp[0] = (uint8_t)b_lo;
         sp[16] = (uint8_t)b_hi;
@@ -944,12 +955,16 @@ mx_quant_dual_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, uint8_t
       }
     }
     if (kRow) {
-      // pieces 0 and 4 of a row hold the scale bytes of chunks 0, 2 and 1, 3
-      uint8_t* rp = sfr + q_sf_base32((uint32_t)row0, tc, kb_c, group_r) + (size_t)(rsub * 16);
+      // pieces 0 and 4 of a row hold the scale bytes of the tile's even and odd chunks; a whole K block's four bytes
+      // leave as one 32-bit store, half a block's two as one 16-bit store
+      uint8_t* rp = sfr + q_sf_base32((uint32_t)row0, kblock, kb_c, group_r) + (size_t)(rsub * 16 + chunk0);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const uint32_t v = rowsf[i] | __shfl_xor_sync(0xffffffffu, rowsf[i], 4);
-        if (piece == 0 && i * 4 + rsub < rows_here) *reinterpret_cast<uint32_t*>(rp + i * 64) = v;
+        if (piece == 0 && i * 4 + rsub < rows_here) {
+          if (kHalves == 2) *reinterpret_cast<uint32_t*>(rp + i * 64) = v;
+          else *reinterpret_cast<uint16_t*>(rp + i * 64) = (uint16_t)v;
+        }
       }
     }
   }
@@ -1018,22 +1033,26 @@ int bones_mx2_quant(const void* x, long long ldx, void* qr, void* sfr, int group
   if ((C % 128) || (ldx % 8) || ((uintptr_t)x & 15)) return -2;
   if ((qr && ((group_r % 32) || ((uintptr_t)sfr & 3))) || (qc && (group_c % 32)) || R >= (1LL << 31) || C >= (1LL << 31)) return -2;
   if (R == 0 || (!qr && !qc)) return 0;
-  const long long tiles = ((R + 31) / 32) * (C / 128);
+  // a K block of the row copy per warp tile, twelve warps per SM.  Tiles of half a K block with sixteen or twenty warps
+  // (kHalves = 1) were measured slower (0.62 - 0.63 of the copy rate against 0.70 at 131072 x 1280)
+  constexpr int kHalves = 2, kWarps = 12;
+  const long long tiles = ((R + 31) / 32) * (C / (64 * kHalves));
   if (tiles >= (1LL << 30)) return -2;
-  static bool attr_set = false;
-  if (!attr_set) {
-    BONES_CHECK(cudaFuncSetAttribute(mx_quant_dual_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, QD_SMEM_BYTES));
-    BONES_CHECK(cudaFuncSetAttribute(mx_quant_dual_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, QD_SMEM_BYTES));
-    BONES_CHECK(cudaFuncSetAttribute(mx_quant_dual_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, QD_SMEM_BYTES));
-    attr_set = true;
-  }
   int dev = 0, sms = 0;
   BONES_CHECK(cudaGetDevice(&dev));
   BONES_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  const unsigned grid = (unsigned)std::min<long long>(sms, (tiles + QD_WARPS - 1) / QD_WARPS);
+  const unsigned grid = (unsigned)std::min<long long>(sms, (tiles + kWarps - 1) / kWarps);
   int* err = error_word();
-#define BONES_QUANT_LAUNCH(ROW, COL)                                                                                       \
-  mx_quant_dual_kernel<ROW, COL><<<grid, QD_WARPS * 32, QD_SMEM_BYTES, (cudaStream_t)stream>>>(                             \
+  using G = QdGeom<kHalves, kWarps>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    BONES_CHECK(cudaFuncSetAttribute(mx_quant_dual_kernel<true, true, kHalves, kWarps>, cudaFuncAttributeMaxDynamicSharedMemorySize, G::kSmemBytes));
+    BONES_CHECK(cudaFuncSetAttribute(mx_quant_dual_kernel<true, false, kHalves, kWarps>, cudaFuncAttributeMaxDynamicSharedMemorySize, G::kSmemBytes));
+    BONES_CHECK(cudaFuncSetAttribute(mx_quant_dual_kernel<false, true, kHalves, kWarps>, cudaFuncAttributeMaxDynamicSharedMemorySize, G::kSmemBytes));
+    attr_set = true;
+  }
+#define BONES_QUANT_LAUNCH(ROW, COL)                                                                                          \
+  mx_quant_dual_kernel<ROW, COL, kHalves, kWarps><<<grid, kWarps * 32, G::kSmemBytes, (cudaStream_t)stream>>>(                 \
       (const __nv_bfloat16*)x, ldx, (uint8_t*)qr, (uint8_t*)sfr, group_r, (uint8_t*)qc, (uint8_t*)sfc, group_c, R, C, (uint32_t)tiles, err)
   if (qr && qc) BONES_QUANT_LAUNCH(true, true);
   else if (qr) BONES_QUANT_LAUNCH(true, false);
