@@ -229,3 +229,40 @@ def test_comm_probe_falls_back_on_every_rank_together():
         out = os.path.join(d, "probe")
         mp.spawn(_worker_probe, args=(WORLD, os.path.join(d, "rdv"), out), nprocs=WORLD, join=True)
         assert torch.load(f"{out}.0") is True and torch.load(f"{out}.1") is True
+
+
+def _dedup_worker(root, rank, q):
+    import numpy as np
+    from them_bones_b200.data.streams import SharedDedup
+    from them_bones_b200.data.synth import ZipfDocs
+    dd = SharedDedup(root, rank, 2, bits=18, wait_s=20.0)
+    shared = ZipfDocs(4096, doc_len=(30, 60), seed=5).docs(8)          # both ranks see these eight documents
+    own = ZipfDocs(4096, doc_len=(30, 60), seed=50 + rank).docs(16)
+    kept = []
+    for b in range(5):
+        dd.begin_batch(b)
+        docs = own[3 * b:3 * b + 3] + (shared if (b == 0 and rank == 1) or (b >= 2 and rank == 0) else [])
+        kept.append(sum(dd.decide(docs)))
+        dd.end_batch()
+    q.put((rank, kept, dd.n["dropped_filter"]))
+
+
+def test_shared_dedup_between_two_processes(tmp_path):
+    """Two processes share the filter through files: what rank 1 accepted in batch 0 is dropped on rank 0 from batch 2
+    on (the fixed lag), and each rank's own new documents are kept."""
+    import multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    root = str(tmp_path / "dedup")
+    ps = [ctx.Process(target=_dedup_worker, args=(root, r, q)) for r in range(2)]
+    for p in ps:
+        p.start()
+    out = dict()
+    for _ in ps:
+        rank, kept, dropped = q.get(timeout=120)
+        out[rank] = (kept, dropped)
+    for p in ps:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert out[1][0] == [3 + 8, 3, 3, 3, 3] and out[1][1] == 0
+    assert out[0][0] == [3, 3, 3, 3, 3] and out[0][1] == 8 * 3            # the shared documents are dropped in batches 2, 3, 4
