@@ -508,6 +508,20 @@ __global__ void softcap_ce_kernel(const __nv_bfloat16* logits, long long ldl, co
   s = warp_sum(s);
   st = warp_sum(st);
   if ((threadIdx.x & 31) == 0) { red[threadIdx.x >> 5] = s; red_t[threadIdx.x >> 5] = st; }
+  const bool valid = tgt >= 0 && tgt < V;
+  long long t2 = -1, t3 = -1;
+  float a2 = 0.f, a3 = 0.f;
+  if (aux.tg[0]) { t2 = aux.tg[0][row]; a2 = (t2 >= 0 && t2 < V) ? aux.w[0][row] : 0.f; }
+  if (aux.tg[1]) { t3 = aux.tg[1][row]; a3 = (t3 >= 0 && t3 < V) ? aux.w[1][row] : 0.f; }
+  // the target logits are read here, before the barriers: the gradient may be written over the logits (in place), and
+  // no thread stores before the second barrier
+  float z_tgt = 0.f, z_2 = 0.f, z_3 = 0.f;
+  if (threadIdx.x == 0) {
+    if (valid) z_tgt = __bfloat162float(l[tgt]);
+    if (a2 != 0.f) z_2 = __bfloat162float(l[t2]);
+    if (a3 != 0.f) z_3 = __bfloat162float(l[t3]);
+    if (!capped) { z_tgt = cap * tanhf(z_tgt * inv_cap); z_2 = cap * tanhf(z_2 * inv_cap); z_3 = cap * tanhf(z_3 * inv_cap); }
+  }
   __syncthreads();
   if (threadIdx.x < 32) {
     float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
@@ -519,20 +533,15 @@ __global__ void softcap_ce_kernel(const __nv_bfloat16* logits, long long ldl, co
   __syncthreads();
   const float lse = logf(s_total) + cap;
   const float sm = aux.smooth, mean_z = cap * s_tsum / (float)V;
-  const bool valid = tgt >= 0 && tgt < V;
   if (threadIdx.x == 0) {
     float out = 0.f;
-    if (valid) out = lse - (1.0f - sm) * (capped ? __bfloat162float(l[tgt]) : cap * tanhf(__bfloat162float(l[tgt]) * inv_cap)) - sm * mean_z;
+    if (valid) out = lse - (1.0f - sm) * z_tgt - sm * mean_z;
     nll[row] = out;
   }
-  long long t2 = -1, t3 = -1;
-  float a2 = 0.f, a3 = 0.f;
-  if (aux.tg[0]) { t2 = aux.tg[0][row]; a2 = (t2 >= 0 && t2 < V) ? aux.w[0][row] : 0.f; }
-  if (aux.tg[1]) { t3 = aux.tg[1][row]; a3 = (t3 >= 0 && t3 < V) ? aux.w[1][row] : 0.f; }
   if (threadIdx.x == 0 && aux.nll_aux) {
     float out = 0.f;
-    if (a2 != 0.f) out += a2 * (lse - (capped ? __bfloat162float(l[t2]) : cap * tanhf(__bfloat162float(l[t2]) * inv_cap)));
-    if (a3 != 0.f) out += a3 * (lse - (capped ? __bfloat162float(l[t3]) : cap * tanhf(__bfloat162float(l[t3]) * inv_cap)));
+    if (a2 != 0.f) out += a2 * (lse - z_2);
+    if (a3 != 0.f) out += a3 * (lse - z_3);
     aux.nll_aux[row] = out;
   }
   if (!dlogits) return;
